@@ -1,0 +1,58 @@
+"""Shared helpers for the parity tests: seeded inputs and the error metric."""
+import numpy as np
+
+# Tolerances of the parity bar: attention outputs within 2e-3 (f16 / bf16) and 1e-5 (f32)
+# of the oracle; cache contents, codes and scales bit-exact.
+TOL = {"f32": 1e-5, "f16": 2e-3, "bf16": 2e-3}
+
+
+def rel_err(got, ref) -> float:
+    """Max relative error with an RMS floor: max_i |got_i - ref_i| / (|ref_i| + rms(ref)).
+
+    A purely element-wise ratio is undefined where the reference output crosses zero; dividing
+    by the tensor maximum alone would hide errors on small entries.  Adding the RMS of the
+    reference to each denominator keeps the measure element-wise and finite.
+    """
+    got = np.asarray(got, dtype=np.float64)
+    ref = np.asarray(ref, dtype=np.float64)
+    assert got.shape == ref.shape, (got.shape, ref.shape)
+    if ref.size == 0:
+        return 0.0
+    rms = float(np.sqrt(np.mean(ref * ref)))
+    den = np.abs(ref) + (rms if rms > 0 else 1.0)
+    return float(np.max(np.abs(got - ref) / den))
+
+
+def rng(seed: int) -> np.random.Generator:
+    """Counter-based generator (Philox4x32-10) so every case is reproducible from its seed."""
+    return np.random.Generator(np.random.Philox(key=seed))
+
+
+def normal(seed, shape, dtype=np.float32, scale=1.0):
+    return (rng(seed).standard_normal(shape, dtype=np.float32) * np.float32(scale)).astype(dtype)
+
+
+def normal_with_outliers(seed, shape, dtype=np.float32, frac=0.01, mag=20.0):
+    """N(0,1) with `frac` of the elements (i.i.d. Bernoulli) multiplied by `mag`."""
+    g = rng(seed)
+    x = g.standard_normal(shape, dtype=np.float32)
+    x = np.where(g.random(shape, dtype=np.float32) < frac, x * np.float32(mag), x)
+    return x.astype(dtype)
+
+
+def lcg_tensor(seed: int, shape):
+    """The generator of the reference's flash-attention unit tests (flash_sdpa.rs:349-357):
+    s = s*6364136223846793005 + 1442695040888963407; value = (s >> 40) / 2^24 - 0.5."""
+    n = int(np.prod(shape))
+    out = np.empty(n, np.float32)
+    s = seed & 0xFFFFFFFFFFFFFFFF
+    for i in range(n):
+        s = (s * 6364136223846793005 + 1442695040888963407) & 0xFFFFFFFFFFFFFFFF
+        out[i] = np.float32(np.float32(s >> 40) / np.float32(1 << 24)) - np.float32(0.5)
+    return out.reshape(shape)
+
+
+def ramp(shape, start=0.0, step=0.5, dtype=np.float32):
+    """`seq_tensor` of the reference's in-place cache tests (inplace_kv_cache.rs:359-363)."""
+    n = int(np.prod(shape))
+    return (start + np.arange(n, dtype=np.float32) * np.float32(step)).reshape(shape).astype(dtype)
