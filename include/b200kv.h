@@ -1,0 +1,155 @@
+/* b200kv — C ABI of the B200 (sm_100a) KV-cache + attention library.
+ *
+ * This is the boundary a tract maintainer binds from Rust (extern "C" + raw device
+ * pointers): the functions below replace, on the "cuda" runtime, what tract does in
+ *   gpu/src/ops/dyn_kv_cache.rs            (GpuDynKVCache: alloc + copy_nd the whole past each step)
+ *   cuda/src/ops/flash_attn.rs             (CudaFlashAttention op)
+ *   cuda/src/kernels/flash_attn.rs:82-189  (CudaFlashAttn::dispatch_eval launcher)
+ *   cuda/src/transform.rs:301-409          (convert_sdpa_to_cuda_flash_attn)
+ * and give the CPU-only ops of transformers/src/ops/quant_dyn_kv_cache.rs a device form.
+ *
+ * Conventions (they mirror tract's own, api/ffi/src/lib.rs:16-60):
+ *   - every function returns B200KV_OK or B200KV_KO; after KO, b200kv_last_error() returns a
+ *     thread-local message.  All shape / dtype / capacity validation happens on the host
+ *     before anything is enqueued; a failed call enqueues nothing and changes no state.
+ *   - calls only ENQUEUE work on the given stream (a cudaStream_t / CUstream passed as void*);
+ *     there is no hidden device synchronisation.  Host-side bookkeeping (sequence lengths,
+ *     page tables) is updated at enqueue time, so the calls on one cache must be issued in
+ *     program order on streams the caller keeps ordered — one thread at a time per cache,
+ *     like an OpState.  Distinct caches are independent.
+ *   - tensors are raw device pointers plus strides in ELEMENTS; the innermost (head_dim) axis
+ *     must be contiguous.  The library never allocates caller-visible outputs.
+ *   - there is no CPU fallback: without a CUDA device every entry point fails.
+ */
+#ifndef B200KV_H
+#define B200KV_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200KV_OK 0
+#define B200KV_KO 1
+
+/* element type of caller tensors (tract DatumType F32 / F16; BF16 is an extension) */
+typedef enum { B200KV_F32 = 0, B200KV_F16 = 1, B200KV_BF16 = 2 } b200kv_dtype;
+
+/* storage format of the cache pages */
+typedef enum {
+    B200KV_FMT_F32 = 0,  /* bit copy of f32 input  (DynKeyValueCache, transformers/src/ops/dyn_kv_cache.rs) */
+    B200KV_FMT_F16 = 1,  /* bit copy of f16 input */
+    B200KV_FMT_BF16 = 2, /* bit copy of bf16 input */
+    B200KV_FMT_Q8_1 = 3, /* blocks of 32 along head_dim: f16 scale + 32 int8 codes, arithmetic of
+                            linalg/src/frame/block_quant/q8_1.rs:20-63 (the unused f16 sum is not stored) */
+    B200KV_FMT_Q4_0 = 4, /* blocks of 32 along head_dim: f16 scale + 16 bytes of nibbles,
+                            linalg/src/frame/block_quant/q4_0.rs:19-95 */
+    B200KV_FMT_KIVI8 = 5, /* QuantizedDynKeyValueCache, bits = 8 (transformers/src/ops/quant_dyn_kv_cache.rs) */
+    B200KV_FMT_KIVI4 = 6  /* QuantizedDynKeyValueCache, bits = 4 */
+} b200kv_format;
+
+typedef struct b200kv_cache b200kv_cache; /* opaque: page pool + page tables of one layer's K (and V) */
+
+typedef struct {
+    int32_t device;         /* CUDA device ordinal */
+    int32_t format;         /* b200kv_format */
+    int32_t n_kv_heads;     /* Hkv */
+    int32_t head_dim;       /* D: 64 or 128 */
+    int32_t has_values;     /* 1: the cache holds K and V (fused cache + attention); 0: one tensor only
+                               (a lone DynKeyValueCache node) */
+    int32_t max_seqs;       /* sequences that can be live at once */
+    int64_t max_seq_tokens; /* longest sequence (sizes the page table rows) */
+    int64_t pool_tokens;    /* capacity of the page pool in tokens, summed over sequences */
+} b200kv_config;
+
+/* Thread-local message of the last failed call on this thread (tract_get_last_error analogue). */
+const char* b200kv_last_error(void);
+
+/* Library / build information: "b200kv <version> sm_100a". */
+const char* b200kv_version(void);
+
+/* ---- cache life cycle (the OpState of DynKeyValueCache / the fused cache+attention op) ---- */
+
+/* Allocates the page pool and page tables on cfg->device.  Replaces the per-step cuMemAlloc of
+ * GpuDynKVCacheState::eval (gpu/src/ops/dyn_kv_cache.rs:88-108). */
+int b200kv_create(const b200kv_config* cfg, b200kv_cache** out);
+int b200kv_destroy(b200kv_cache* cache);
+
+/* A sequence is one independent state (one tract `State`); ids are small integers reused after free. */
+int b200kv_seq_new(b200kv_cache* cache, int32_t* seq_out);
+int b200kv_seq_free(b200kv_cache* cache, int32_t seq);
+
+/* Cached length of a sequence: what OpState::resolve_symbols binds the past-length symbol to
+ * (transformers/src/ops/dyn_kv_cache.rs:153-156).  Returns -1 on error. */
+int64_t b200kv_seq_len(b200kv_cache* cache, int32_t seq);
+
+/* Pages currently unused in the pool, and bytes one page holds (introspection for sizing). */
+int64_t b200kv_free_pages(b200kv_cache* cache);
+int64_t b200kv_page_bytes(b200kv_cache* cache);
+
+/* ---- append (DynKeyValueCacheState::eval, transformers/src/ops/dyn_kv_cache.rs:158-174;
+ *              QuantizedDynKvCacheState::ingest, quant_dyn_kv_cache.rs:403-430) ----
+ * Appends n_new tokens to each of n_seqs sequences.  k_new / v_new are [n_seqs, Hkv, n_new, D]
+ * with strides {batch, head, token} in elements (D contiguous).  For the bit-copy formats `dtype`
+ * must equal the storage type; the quantised formats take f32 / f16 / bf16 input and quantise on
+ * append after casting to f32, as the reference does.  v_new must be NULL iff has_values == 0. */
+int b200kv_append(b200kv_cache* cache, int32_t n_seqs, const int32_t* seqs, int32_t n_new, const void* k_new,
+                  const int64_t k_strides[3], const void* v_new, const int64_t v_strides[3], int32_t dtype,
+                  void* stream);
+
+/* ---- attention over the cache (Sdpa over the accumulated K/V: the fused form of
+ *      transformers/src/ops/inplace_kv_cache.rs:135-216; kernels replace cuda/src/kernels/cu/flash_attn.cu) ----
+ * q and out are [n_seqs, n_q_heads, n_new, D]; the n_new queries of sequence i are its LAST n_new
+ * cached positions (call after b200kv_append), so `causal` masks key j for query r iff
+ * j > len_i - n_new + r (bottom-right aligned, transformers/src/ops/flash_sdpa.rs:285-294).
+ * n_new == 1 runs the split-KV decode kernel, n_new > 1 the prefill kernel.  scale <= 0 selects
+ * 1/sqrt(D).  Quantised pages are dequantised on the fly. */
+int b200kv_attend(b200kv_cache* cache, int32_t n_seqs, const int32_t* seqs, int32_t n_q_heads, int32_t n_new,
+                  const void* q, const int64_t q_strides[3], void* out, const int64_t out_strides[3], int32_t dtype,
+                  float scale, int32_t causal, void* stream);
+
+/* ---- state access (OpState::save_to / load_from, truncate, freeze:
+ *      gpu/src/ops/dyn_kv_cache.rs:18-40,116-125,136-168) ---- */
+
+/* Writes the cached K (and V) of one sequence as contiguous-in-D tensors [Hkv, len, D] with strides
+ * {head, token}; quantised formats are dequantised (f32 arithmetic, then cast to `dtype`).  This is the
+ * tensor DynKeyValueCache returns to a consumer that is not the fused attention, and what save_to stores.
+ * v_out may be NULL. */
+int b200kv_export(b200kv_cache* cache, int32_t seq, void* k_out, const int64_t k_strides[2], void* v_out,
+                  const int64_t v_strides[2], int32_t dtype, void* stream);
+
+/* Raw quantised state of one sequence, in token order, for bit-exact checks and fast freeze:
+ *   Q8_1: codes int8 [Hkv, len, D],        scales f16 [Hkv, len, D/32]
+ *   Q4_0: codes uint8 [Hkv, len, D/2] (byte j of a block = element j | element j+16 << 4), scales as above
+ * which = 0 for K, 1 for V.  Fails for the bit-copy formats (use b200kv_export). */
+int b200kv_export_codes(b200kv_cache* cache, int32_t seq, int32_t which, void* codes, void* scales, void* stream);
+
+/* Drops the tail of a sequence (speculative-decoding rollback; DynKeyValueCacheState::truncate,
+ * transformers/src/ops/dyn_kv_cache.rs:112-119 — on device, without the host round trip of
+ * gpu/src/ops/dyn_kv_cache.rs:116-125).  Fails if len exceeds the current length. */
+int b200kv_truncate(b200kv_cache* cache, int32_t seq, int64_t len);
+
+/* Device-side copy of a sequence into a new one (OpStateFreeze::freeze / unfreeze keep the cache on
+ * device, gpu/src/ops/dyn_kv_cache.rs:136-168). */
+int b200kv_fork(b200kv_cache* cache, int32_t seq, int32_t* new_seq_out, void* stream);
+
+/* Device status word: 0 unless a kernel recorded a problem (page index out of range, a bounded wait
+ * that expired).  Synchronises the stream.  Returns KO and sets the message if the word is non-zero. */
+int b200kv_check(b200kv_cache* cache, void* stream);
+
+/* ---- lone Sdpa (transformers/src/ops/sdpa.rs:84-89; replaces convert_sdpa_to_cuda_flash_attn +
+ *      CudaFlashAttention for an Sdpa node that is not fused with a cache) ----
+ * q [B, Hq, S, D], k / v [B, Hkv, T, D], out [B, Hq, S, D]; strides {batch, head, row} in elements.
+ * mask (may be NULL) is additive, [Mb, Mh, S, T] with Mb in {1, B} and Mh in {1, Hq}, strides
+ * {batch, head, row, col} (0 to broadcast), element type mask_dtype.  Any D <= 256. */
+int b200kv_sdpa(const void* q, const int64_t q_strides[3], const void* k, const int64_t k_strides[3], const void* v,
+                const int64_t v_strides[3], const void* mask, const int64_t mask_strides[4], int32_t mask_dtype,
+                void* out, const int64_t out_strides[3], int32_t batch, int32_t n_q_heads, int32_t n_kv_heads,
+                int32_t q_len, int32_t kv_len, int32_t head_dim, int32_t dtype, float scale, int32_t causal,
+                void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200KV_H */

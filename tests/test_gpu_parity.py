@@ -1,0 +1,358 @@
+"""Parity of the CUDA path (through the C ABI) with the CPU oracle, on a B200.
+
+Bar: cache contents, codes and scales bit-exact; attention within 2e-3 (f16 / bf16) and 1e-5 (f32)
+of the oracle under util.rel_err.
+"""
+import numpy as np
+import pytest
+
+import oracle
+from util import TOL, lcg_tensor, normal, normal_with_outliers, ramp, rel_err
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+
+
+@pytest.fixture(scope="module")
+def kv():
+    import tract_b200
+
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device")
+    tract_b200.lib()  # fails loudly if the extension is missing
+    return tract_b200
+
+
+TDT = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}
+
+
+def np_dtype(name):
+    return {"f32": np.float32, "f16": np.float16, "bf16": oracle.bfloat16}[name]
+
+
+def to_dev(a, name=None):
+    """numpy (incl. ml_dtypes bf16) -> CUDA tensor."""
+    if a.dtype == np.float32 or a.dtype == np.float16:
+        return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    return torch.from_numpy(np.ascontiguousarray(a).view(np.uint16).copy()).view(torch.bfloat16).cuda()
+
+
+def to_np(t, name):
+    t = t.detach().cpu().contiguous()
+    if name == "bf16":
+        return t.view(torch.uint16).numpy().view(oracle.bfloat16)
+    return t.numpy()
+
+
+# ---- append: DynKeyValueCache semantics, bit-exact ----------------------------------------------
+
+@pytest.mark.parametrize("name", ["f32", "f16", "bf16"])
+@pytest.mark.parametrize("D", [128, 64])
+def test_append_equals_concat_bit_exact(kv, name, D):
+    # inplace_kv_cache.rs:388-399 drive: a prompt of 5 then 20 single-token steps; here for 3 sequences at once,
+    # crossing a page boundary (64 tokens) on the way
+    H, B = 2, 3
+    cache = kv.KvCache(name, H, D, max_seqs=4, max_seq_tokens=256)
+    seqs = [cache.new_seq() for _ in range(B)]
+    ref_k = ref_v = None
+    for i, s in enumerate([5] + [1] * 20 + [50, 3]):
+        k = normal(10 + i, (B, H, s, D)).astype(np_dtype(name))
+        v = ramp((B, H, s, D), start=i * 100.0).astype(np_dtype(name))
+        cache.append(seqs, to_dev(k), to_dev(v))
+        ref_k, ref_v = oracle.dyn_kv_concat(ref_k, k), oracle.dyn_kv_concat(ref_v, v)
+    cache.check()
+    for b, sq in enumerate(seqs):
+        assert cache.seq_len(sq) == ref_k.shape[2]
+        gk, gv = cache.export(sq, TDT[name])
+        assert to_np(gk, name).tobytes() == ref_k[b].tobytes()
+        assert to_np(gv, name).tobytes() == ref_v[b].tobytes()
+    cache.close()
+
+
+def test_append_strided_and_k_only(kv):
+    # the reference runs every case with transposed (strided) inputs too (test-rt/test-cuda/src/lib.rs:218-220);
+    # a lone DynKeyValueCache node holds a single tensor
+    H, D = 2, 128
+    cache = kv.KvCache("f16", H, D, max_seqs=1, max_seq_tokens=128, has_values=False)
+    sq = cache.new_seq()
+    x = normal(3, (1, 7, H, D)).astype(np.float16)         # [B, S, H, D] in memory
+    xt = to_dev(x).permute(0, 2, 1, 3)                      # logical [B, H, S, D], strided
+    cache.append([sq], xt)
+    off = torch.zeros(1 * H * 3 * D + 1, dtype=torch.float16, device="cuda")[1:].view(1, H, 3, D)  # 2-byte aligned only
+    y = normal(4, (1, H, 3, D)).astype(np.float16)
+    off.copy_(to_dev(y))
+    cache.append([sq], off)
+    gk, gv = cache.export(sq, torch.float16)
+    assert gv is None
+    want = np.concatenate([x.transpose(0, 2, 1, 3), y], axis=2)[0]
+    assert to_np(gk, "f16").tobytes() == want.tobytes()
+    cache.close()
+
+
+# ---- quantise-on-append: codes and scales bit-exact ----------------------------------------------
+
+def nasty(seed, shape):
+    x = normal_with_outliers(seed, shape)
+    f = x.reshape(-1, 32)
+    f[3] = 0.0                      # all-zero block: scale 0, reciprocal 0
+    f[4, 5] = -f[4, 9]              # tie in magnitude: first occurrence wins
+    f[5, 17] = -f[5, 2]             # tie across the two 16-element halves of a block
+    f[6] = 1e-42                    # subnormal scale, infinite reciprocal
+    f[7, 0] = np.inf
+    f[8, 1] = np.nan
+    f[9] = np.float32(65504.0) * 130.0  # f16 scale overflows to inf
+    f[10, :] = np.arange(32) - 15.5     # exact .5 products: round half away from zero
+    return x
+
+
+@pytest.mark.parametrize("fmt", ["q8_1", "q4_0"])
+@pytest.mark.parametrize("in_name", ["f32", "f16"])
+@pytest.mark.parametrize("D", [128, 64])
+def test_quantise_on_append_bit_exact(kv, fmt, in_name, D):
+    H, B = 4, 2
+    cache = kv.KvCache(fmt, H, D, max_seqs=B, max_seq_tokens=512)
+    seqs = [cache.new_seq() for _ in range(B)]
+    chunks_k, chunks_v = [], []
+    for i, s in enumerate([70, 1, 1, 1, 130, 1]):
+        with np.errstate(over="ignore", invalid="ignore"):
+            k = nasty(20 + i, (B, H, s, D)).astype(np_dtype(in_name))
+            v = normal_with_outliers(40 + i, (B, H, s, D)).astype(np_dtype(in_name))
+        cache.append(seqs, to_dev(k), to_dev(v))
+        chunks_k.append(k), chunks_v.append(v)
+    cache.check()
+    K, V = np.concatenate(chunks_k, 2), np.concatenate(chunks_v, 2)
+    for b, sq in enumerate(seqs):
+        for which, X in ((0, K), (1, V)):
+            codes, scales = cache.export_codes(sq, which)
+            codes, scales = codes.cpu().numpy(), scales.cpu().view(torch.uint16).numpy()
+            if fmt == "q8_1":
+                s_ref, _, c_ref = oracle.q8_1_quant(X[b])
+            else:
+                s_ref, c_ref = oracle.q4_0_quant(X[b])
+            assert np.array_equal(scales, s_ref), (fmt, which)
+            assert np.array_equal(codes, c_ref), (fmt, which)
+        # dequantised export == oracle dequant, bit for bit in f32
+        gk, gv = cache.export(sq, torch.float32)
+        if fmt == "q8_1":
+            s_ref, _, c_ref = oracle.q8_1_quant(V[b])
+            want = oracle.q8_1_dequant(s_ref, c_ref)
+        else:
+            want = oracle.q4_0_dequant(*oracle.q4_0_quant(V[b]))
+        assert gv.cpu().numpy().tobytes() == want.tobytes()
+    cache.close()
+
+
+# ---- decode attention ------------------------------------------------------------------------------
+
+def oracle_cache_view(fmt, X, io_name):
+    """What the reference's attention sees for a cache in format `fmt`: the concatenated tensor
+    itself, or the dequantised f32 cache cast back to the model dtype (quant_dyn_kv_cache.rs:493)."""
+    if fmt == "q8_1":
+        s, _, c = oracle.q8_1_quant(X)
+        return oracle.q8_1_dequant(s, c).astype(np_dtype(io_name))
+    if fmt == "q4_0":
+        return oracle.q4_0_dequant(*oracle.q4_0_quant(X)).astype(np_dtype(io_name))
+    return X
+
+
+DECODE_CASES = [
+    # fmt,   io,    B, Hq, Hkv, D,   lens
+    ("f32", "f32", 1, 32, 8, 128, [2049]),            # BASELINE config 1
+    ("f32", "f32", 2, 4, 2, 64, [33, 200]),
+    ("f16", "f16", 3, 32, 8, 128, [1, 64, 777]),
+    ("bf16", "bf16", 4, 32, 8, 128, [512, 65, 1300, 129]),  # ragged, like config 3
+    ("f16", "f16", 2, 4, 4, 128, [100, 300]),          # no grouping (G = 1)
+    ("f16", "f16", 2, 6, 2, 64, [100, 300]),           # G = 3
+    ("f16", "f16", 1, 16, 2, 128, [260]),              # G = 8: two group tiles
+    ("q8_1", "f16", 2, 32, 8, 128, [2000, 333]),
+    ("q8_1", "f32", 1, 8, 2, 64, [500]),
+    ("q4_0", "f16", 2, 32, 8, 128, [2000, 333]),
+    ("q4_0", "bf16", 1, 8, 2, 64, [500]),
+]
+
+
+@pytest.mark.parametrize("fmt,io,B,Hq,Hkv,D,lens", DECODE_CASES)
+def test_decode_matches_oracle(kv, fmt, io, B, Hq, Hkv, D, lens):
+    cache = kv.KvCache(fmt, Hkv, D, max_seqs=B, max_seq_tokens=max(lens) + 64)
+    seqs = [cache.new_seq() for _ in range(B)]
+    Ks, Vs = [], []
+    for b, n in enumerate(lens):  # pre-fill the past (n - 1 tokens), one sequence at a time
+        mk = normal_with_outliers if fmt.startswith("q") else normal
+        k, v = mk(100 + b, (1, Hkv, n, D)).astype(np_dtype(io)), mk(200 + b, (1, Hkv, n, D)).astype(np_dtype(io))
+        Ks.append(k), Vs.append(v)
+        if n > 1:
+            cache.append([seqs[b]], to_dev(k[:, :, : n - 1]), to_dev(v[:, :, : n - 1]))
+    # the decode step: append one token per sequence, then attend
+    k_new = np.concatenate([k[:, :, -1:] for k in Ks], 0)
+    v_new = np.concatenate([v[:, :, -1:] for v in Vs], 0)
+    q = normal(7, (B, Hq, 1, D)).astype(np_dtype(io))
+    cache.append(seqs, to_dev(k_new), to_dev(v_new))
+    out = cache.attend(seqs, to_dev(q), causal=True)
+    cache.check()
+    got = to_np(out, io).astype(np.float32)
+    for b in range(B):
+        kc, vc = oracle_cache_view(fmt, Ks[b], io), oracle_cache_view(fmt, Vs[b], io)
+        want = oracle.flash_sdpa(q[b:b + 1], kc, vc, causal=True, threads=8).astype(np.float32)
+        err = rel_err(got[b:b + 1], want)
+        assert err <= TOL[io], (b, err)
+    cache.close()
+
+
+def test_decode_explicit_scale_and_reuse_after_truncate(kv):
+    Hq, Hkv, D = 8, 2, 128
+    cache = kv.KvCache("f16", Hkv, D, max_seqs=2, max_seq_tokens=512)
+    sq = cache.new_seq()
+    k, v = normal(1, (1, Hkv, 300, D)).astype(np.float16), normal(2, (1, Hkv, 300, D)).astype(np.float16)
+    q = normal(3, (1, Hq, 1, D)).astype(np.float16)
+    cache.append([sq], to_dev(k), to_dev(v))
+    free_before = cache.free_pages()
+    # speculative rollback: drop to 130 tokens, then re-append different tokens
+    cache.truncate(sq, 130)
+    assert cache.seq_len(sq) == 130 and cache.free_pages() == free_before + 2
+    k2, v2 = normal(4, (1, Hkv, 10, D)).astype(np.float16), normal(5, (1, Hkv, 10, D)).astype(np.float16)
+    cache.append([sq], to_dev(k2), to_dev(v2))
+    kc, vc = np.concatenate([k[:, :, :130], k2], 2), np.concatenate([v[:, :, :130], v2], 2)
+    gk, gv = cache.export(sq, torch.float16)
+    assert to_np(gk, "f16").tobytes() == kc[0].tobytes() and to_np(gv, "f16").tobytes() == vc[0].tobytes()
+    out = cache.attend([sq], to_dev(q), scale=0.3, causal=True)
+    want = oracle.flash_sdpa(q, kc, vc, scale=0.3, causal=True)
+    assert rel_err(to_np(out, "f16").astype(np.float32), want.astype(np.float32)) <= TOL["f16"]
+    # fork = freeze / unfreeze on device: the copy decodes identically and then diverges independently
+    f = cache.fork(sq)
+    out_f = cache.attend([f], to_dev(q), scale=0.3, causal=True)
+    assert torch.equal(out, out_f)
+    cache.append([f], to_dev(k2[:, :, :1]), to_dev(v2[:, :, :1]))
+    assert cache.seq_len(f) == 141 and cache.seq_len(sq) == 140
+    gk2, _ = cache.export(sq, torch.float16)
+    assert torch.equal(gk, gk2)
+    cache.check()
+    cache.close()
+
+
+# ---- prefill over the cache --------------------------------------------------------------------------
+
+@pytest.mark.parametrize("fmt,io,Hq,Hkv,D,P,S", [
+    ("f16", "f16", 32, 8, 128, 0, 512),     # BASELINE config 2
+    ("f16", "f16", 4, 2, 64, 3, 12),        # inplace_kv_cache.rs:595-658: prefill 3 then more, GQA 4/2
+    ("f32", "f32", 4, 2, 64, 70, 33),
+    ("bf16", "bf16", 8, 2, 128, 100, 64),
+    ("q8_1", "f16", 8, 2, 128, 64, 64),
+])
+def test_prefill_matches_oracle(kv, fmt, io, Hq, Hkv, D, P, S):
+    scale = 0.5 if io != "f32" else 1.0
+    cache = kv.KvCache(fmt, Hkv, D, max_seqs=1, max_seq_tokens=P + S + 64)
+    sq = cache.new_seq()
+    k = normal(1, (1, Hkv, P + S, D), scale=scale).astype(np_dtype(io))
+    v = normal(2, (1, Hkv, P + S, D), scale=scale).astype(np_dtype(io))
+    q = normal(3, (1, Hq, S, D), scale=scale).astype(np_dtype(io))
+    if P:
+        cache.append([sq], to_dev(k[:, :, :P]), to_dev(v[:, :, :P]))
+    cache.append([sq], to_dev(k[:, :, P:]), to_dev(v[:, :, P:]))
+    out = cache.attend([sq], to_dev(q), causal=True)
+    cache.check()
+    want = oracle.flash_sdpa(q, oracle_cache_view(fmt, k, io), oracle_cache_view(fmt, v, io), causal=True, threads=8)
+    err = rel_err(to_np(out, io).astype(np.float32), want.astype(np.float32))
+    assert err <= TOL[io], err
+    cache.close()
+
+
+# ---- lone Sdpa: golden bundles, the reference's kernel-test shapes, property sweep ------------------------
+
+ATTN_CASES = ["simple-causal-f32", "simple-non-causal-f32", "simple-scale-f32", "simple-f16", "simple-mask-f32"]
+
+
+@pytest.mark.parametrize("case", ATTN_CASES)
+def test_sdpa_golden_bundles_on_gpu(kv, golden, case):
+    z, meta = golden
+    a = meta[case]
+    q, k, v = (z[f"{case}/{n}"] for n in a["qkv"])
+    mask = z[f"{case}/mask"] if f"{case}/mask" in z.files else None
+    if a["dtype"] == "f16":
+        q, k, v = (x.astype(np.float16) for x in (q, k, v))
+    out = kv.sdpa(to_dev(q), to_dev(k), to_dev(v), mask=to_dev(mask) if mask is not None else None,
+                  scale=a["scale"], causal=a["causal"])
+    got = out.float().cpu().numpy()
+    want = z[f"{case}/output_0"]
+    atol, rtol = (1e-3, 5e-3) if a["dtype"] == "f16" else (2e-7, 2e-7)
+    assert np.all(np.abs(got - want) <= atol + rtol * np.abs(want)), np.abs(got - want).max()
+
+
+@pytest.mark.parametrize("b,hq,hkv,p,s,d,causal,with_mask", [
+    # cuda/src/kernels/flash_attn.rs:276-287, inputs are i/len ramps in f16, scale 1.0
+    (1, 1, 1, 64, 1, 128, False, False), (1, 2, 1, 64, 1, 128, False, True), (1, 2, 2, 0, 1, 64, False, False),
+    (2, 4, 2, 123, 1, 64, False, False), (1, 2, 2, 0, 1, 64, True, False), (1, 1, 1, 64, 64, 128, False, False),
+    (2, 32, 4, 64, 64, 128, False, False), (1, 1, 1, 64, 64, 128, False, True), (1, 1, 1, 64, 64, 128, True, False),
+])
+def test_sdpa_reference_kernel_test_shapes(kv, b, hq, hkv, p, s, d, causal, with_mask):
+    def rampf16(shape):
+        n = int(np.prod(shape))
+        return (np.arange(n, dtype=np.float32) / np.float32(n)).astype(np.float16).reshape(shape)
+
+    q, k, v = rampf16((b, hq, s, d)), rampf16((b, hkv, p + s, d)), rampf16((b, hkv, p + s, d))
+    mask = np.ones((1, 1, s, p + s), np.float16) if with_mask else None
+    out = kv.sdpa(to_dev(q), to_dev(k), to_dev(v), mask=to_dev(mask) if with_mask else None, scale=1.0, causal=causal)
+    want = oracle.flash_sdpa(q, k, v, mask=mask, scale=1.0, causal=causal, threads=8)
+    assert rel_err(out.float().cpu().numpy(), want.astype(np.float32)) <= TOL["f16"]
+
+
+def test_sdpa_property_sweep(kv):
+    # strategy of test-rt/suite-unit/src/sdpa.rs:94-142 (values k/8, B 1-2, GQA repeat 1-4, kv heads 1-4,
+    # P 0-4, S 2-4, optional scale, causal or additive mask broadcast over b / h), embed dims of the CPU
+    # and CUDA runners together, f32 and f16, rank 3 and rank 4
+    g = np.random.default_rng(11)
+    for it in range(80):
+        b, rep, hkv = int(g.integers(1, 3)), int(g.integers(1, 5)), int(g.integers(1, 5))
+        p, s, d = int(g.integers(0, 5)), int(g.integers(2, 5)), int(g.choice([1, 2, 3, 64, 128]))
+        rank3 = bool(g.integers(0, 2))
+        if rank3:
+            rep = hkv = 1
+        hq = rep * hkv
+        dt = np.float16 if it % 2 else np.float32
+        mk = lambda shape: (g.integers(-3, 4, size=shape) / 8.0).astype(dt)
+        q, k, v = mk((b, hq, s, d)), mk((b, hkv, p + s, d)), mk((b, hkv, p + s, d))
+        causal = bool(g.integers(0, 2))
+        mask = None
+        if not causal and g.integers(0, 2):
+            mask = mk((b if g.integers(0, 2) else 1, hq if g.integers(0, 2) else 1, s, p + s))
+        scale = float(g.uniform(0.1, 1.0)) if g.integers(0, 2) else None
+        if rank3:
+            q, k, v = q[:, 0], k[:, 0], v[:, 0]
+            mask = mask[:, 0] if mask is not None else None
+        out = kv.sdpa(to_dev(q), to_dev(k), to_dev(v), mask=to_dev(mask) if mask is not None else None, scale=scale,
+                      causal=causal)
+        want = oracle.flash_sdpa(q, k, v, mask=mask, scale=scale, causal=causal)
+        err = rel_err(out.float().cpu().numpy(), want.astype(np.float32))
+        assert err <= (TOL["f16"] if dt == np.float16 else TOL["f32"]), (it, err)
+
+
+# ---- error behaviour: validation happens on the host, nothing is enqueued ------------------------------
+
+def test_errors_are_reported_not_swallowed(kv):
+    cache = kv.KvCache("f16", 2, 128, max_seqs=1, max_seq_tokens=128, pool_tokens=128)
+    sq = cache.new_seq()
+    with pytest.raises(kv.B200KvError, match="sequence slots"):
+        cache.new_seq()
+    x = torch.zeros(1, 2, 4, 128, dtype=torch.float32, device="cuda")
+    with pytest.raises(kv.B200KvError, match="same type"):
+        cache.append([sq], x, x)
+    h = x.half()
+    with pytest.raises(kv.B200KvError, match="v_new is required"):
+        cache.append([sq], h)
+    with pytest.raises(kv.B200KvError, match="empty|fewer"):
+        cache.attend([sq], torch.zeros(1, 4, 1, 128, dtype=torch.float16, device="cuda"))
+    big = torch.zeros(1, 2, 200, 128, dtype=torch.float16, device="cuda")
+    with pytest.raises(kv.B200KvError, match="max_seq_tokens"):
+        cache.append([sq], big, big)
+    assert cache.seq_len(sq) == 0  # a failed call changed nothing
+    cache.append([sq], h, h)
+    with pytest.raises(kv.B200KvError, match="truncate"):
+        cache.truncate(sq, 10)
+    with pytest.raises(kv.B200KvError, match="multiple"):
+        cache.attend([sq], torch.zeros(1, 3, 1, 128, dtype=torch.float16, device="cuda"))
+    with pytest.raises(kv.B200KvError, match="not live"):
+        cache.seq_len(5)
+    cache.check()
+    cache.close()
+    with pytest.raises(kv.B200KvError, match="head_dim"):
+        kv.KvCache("f16", 2, 96, max_seqs=1, max_seq_tokens=128)

@@ -1,0 +1,232 @@
+"""tract_b200 — B200 (sm_100a) KV-cache + attention path for tract, behind a C ABI.
+
+The product is ``libb200kv.so`` (``include/b200kv.h``).  This package loads it with ctypes and
+offers thin wrappers that take torch CUDA tensors (torch is used for device memory and streams
+only).  There is no CPU fallback: if the library is missing or no CUDA device is present, calls
+raise instead of computing something else.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libb200kv.so")
+
+F32, F16, BF16 = 0, 1, 2
+FMT_F32, FMT_F16, FMT_BF16, FMT_Q8_1, FMT_Q4_0 = 0, 1, 2, 3, 4
+FORMATS = {"f32": FMT_F32, "f16": FMT_F16, "bf16": FMT_BF16, "q8_1": FMT_Q8_1, "q4_0": FMT_Q4_0}
+
+# every symbol include/b200kv.h declares
+EXPORTS = [
+    "b200kv_last_error", "b200kv_version", "b200kv_create", "b200kv_destroy", "b200kv_seq_new", "b200kv_seq_free",
+    "b200kv_seq_len", "b200kv_free_pages", "b200kv_page_bytes", "b200kv_append", "b200kv_attend", "b200kv_export",
+    "b200kv_export_codes", "b200kv_truncate", "b200kv_fork", "b200kv_check", "b200kv_sdpa",
+]
+
+
+class B200KvError(RuntimeError):
+    pass
+
+
+class Config(C.Structure):
+    _fields_ = [("device", C.c_int32), ("format", C.c_int32), ("n_kv_heads", C.c_int32), ("head_dim", C.c_int32),
+                ("has_values", C.c_int32), ("max_seqs", C.c_int32), ("max_seq_tokens", C.c_int64),
+                ("pool_tokens", C.c_int64)]
+
+
+_lib = None
+
+
+def lib():
+    """Loads the CUDA library; raises if it has not been built (no fallback path exists)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise B200KvError(f"{LIB_PATH} is missing: build it with `python -m tract_b200.build`")
+        L = C.CDLL(LIB_PATH)
+        vp, i32, i64, i64p, i32p = C.c_void_p, C.c_int32, C.c_int64, C.POINTER(C.c_int64), C.POINTER(C.c_int32)
+        L.b200kv_last_error.restype = C.c_char_p
+        L.b200kv_version.restype = C.c_char_p
+        L.b200kv_create.argtypes = [C.POINTER(Config), C.POINTER(vp)]
+        L.b200kv_destroy.argtypes = [vp]
+        L.b200kv_seq_new.argtypes = [vp, i32p]
+        L.b200kv_seq_free.argtypes = [vp, i32]
+        L.b200kv_seq_len.argtypes = [vp, i32]
+        L.b200kv_seq_len.restype = i64
+        L.b200kv_free_pages.argtypes = [vp]
+        L.b200kv_free_pages.restype = i64
+        L.b200kv_page_bytes.argtypes = [vp]
+        L.b200kv_page_bytes.restype = i64
+        L.b200kv_append.argtypes = [vp, i32, i32p, i32, vp, i64p, vp, i64p, i32, vp]
+        L.b200kv_attend.argtypes = [vp, i32, i32p, i32, i32, vp, i64p, vp, i64p, i32, C.c_float, i32, vp]
+        L.b200kv_export.argtypes = [vp, i32, vp, i64p, vp, i64p, i32, vp]
+        L.b200kv_export_codes.argtypes = [vp, i32, i32, vp, vp, vp]
+        L.b200kv_truncate.argtypes = [vp, i32, i64]
+        L.b200kv_fork.argtypes = [vp, i32, i32p, vp]
+        L.b200kv_check.argtypes = [vp, vp]
+        L.b200kv_sdpa.argtypes = [vp, i64p, vp, i64p, vp, i64p, vp, i64p, i32, vp, i64p, i32, i32, i32, i32, i32, i32,
+                                  i32, C.c_float, i32, vp]
+        _lib = L
+    return _lib
+
+
+def _ck(rc):
+    if rc != 0:
+        raise B200KvError(lib().b200kv_last_error().decode())
+
+
+def _dtype_code(t):
+    import torch
+
+    try:
+        return {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}[t.dtype]
+    except KeyError:
+        raise B200KvError(f"unsupported dtype {t.dtype}") from None
+
+
+def _strides(t, n):
+    """Leading n strides of a tensor whose last axis must be contiguous."""
+    if t.stride(-1) != 1 and t.shape[-1] != 1:
+        raise B200KvError("the innermost (head_dim) axis must be contiguous")
+    return (C.c_int64 * n)(*[int(s) for s in t.stride()[:n]])
+
+
+def _stream():
+    import torch
+
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ids(seqs):
+    return (C.c_int32 * len(seqs))(*[int(s) for s in seqs])
+
+
+class KvCache:
+    """One layer's paged K (and V) store for up to ``max_seqs`` independent sequences."""
+
+    def __init__(self, fmt, n_kv_heads, head_dim, max_seqs, max_seq_tokens, pool_tokens=None, has_values=True,
+                 device=None):
+        import torch
+
+        if not torch.cuda.is_available():
+            raise B200KvError("no CUDA device: tract_b200 has no CPU fallback")
+        self.device = torch.cuda.current_device() if device is None else int(device)
+        self.fmt = FORMATS[fmt] if isinstance(fmt, str) else int(fmt)
+        self.n_kv_heads, self.head_dim, self.has_values = n_kv_heads, head_dim, bool(has_values)
+        cfg = Config(self.device, self.fmt, n_kv_heads, head_dim, int(has_values), max_seqs, max_seq_tokens,
+                     pool_tokens if pool_tokens is not None else max_seqs * max_seq_tokens)
+        h = C.c_void_p()
+        _ck(lib().b200kv_create(C.byref(cfg), C.byref(h)))
+        self._h = h
+
+    def close(self):
+        if getattr(self, "_h", None):
+            lib().b200kv_destroy(self._h)
+            self._h = None
+
+    __del__ = close
+
+    # -- sequences --
+    def new_seq(self) -> int:
+        s = C.c_int32()
+        _ck(lib().b200kv_seq_new(self._h, C.byref(s)))
+        return s.value
+
+    def free_seq(self, seq):
+        _ck(lib().b200kv_seq_free(self._h, seq))
+
+    def seq_len(self, seq) -> int:
+        n = lib().b200kv_seq_len(self._h, seq)
+        if n < 0:
+            raise B200KvError(lib().b200kv_last_error().decode())
+        return int(n)
+
+    def free_pages(self) -> int:
+        return int(lib().b200kv_free_pages(self._h))
+
+    def page_bytes(self) -> int:
+        return int(lib().b200kv_page_bytes(self._h))
+
+    # -- hot path --
+    def append(self, seqs, k_new, v_new=None):
+        """k_new / v_new: [n_seqs, Hkv, S, D] CUDA tensors."""
+        assert k_new.dim() == 4 and k_new.shape[0] == len(seqs)
+        _ck(lib().b200kv_append(self._h, len(seqs), _ids(seqs), k_new.shape[2], k_new.data_ptr(), _strides(k_new, 3),
+                                v_new.data_ptr() if v_new is not None else None,
+                                _strides(v_new, 3) if v_new is not None else None, _dtype_code(k_new), _stream()))
+
+    def attend(self, seqs, q, scale=None, causal=True, out=None):
+        """q: [n_seqs, Hq, S, D]; returns attention of the last S cached positions over the whole cache."""
+        import torch
+
+        assert q.dim() == 4 and q.shape[0] == len(seqs)
+        if out is None:
+            out = torch.empty_like(q, memory_format=torch.contiguous_format)
+        _ck(lib().b200kv_attend(self._h, len(seqs), _ids(seqs), q.shape[1], q.shape[2], q.data_ptr(), _strides(q, 3),
+                                out.data_ptr(), _strides(out, 3), _dtype_code(q), float(scale or 0.0), int(causal),
+                                _stream()))
+        return out
+
+    # -- state --
+    def export(self, seq, dtype):
+        """Contiguous [Hkv, len, D] K (and V) of one sequence, dequantised for quantised formats."""
+        import torch
+
+        n = self.seq_len(seq)
+        k = torch.empty((self.n_kv_heads, n, self.head_dim), dtype=dtype, device=f"cuda:{self.device}")
+        v = torch.empty_like(k) if self.has_values else None
+        _ck(lib().b200kv_export(self._h, seq, k.data_ptr(), _strides(k, 2), v.data_ptr() if v is not None else None,
+                                _strides(v, 2) if v is not None else None, _dtype_code(k), _stream()))
+        return k, v
+
+    def export_codes(self, seq, which):
+        """(codes, scales-as-uint16-bits) of K (which=0) or V (which=1) for the block-quantised formats."""
+        import torch
+
+        n = self.seq_len(seq)
+        row = self.head_dim if self.fmt == FMT_Q8_1 else self.head_dim // 2
+        codes = torch.empty((self.n_kv_heads, n, row), dtype=torch.int8 if self.fmt == FMT_Q8_1 else torch.uint8,
+                            device=f"cuda:{self.device}")
+        scales = torch.empty((self.n_kv_heads, n, self.head_dim // 32), dtype=torch.float16, device=f"cuda:{self.device}")
+        _ck(lib().b200kv_export_codes(self._h, seq, which, codes.data_ptr(), scales.data_ptr(), _stream()))
+        return codes, scales
+
+    def truncate(self, seq, length):
+        _ck(lib().b200kv_truncate(self._h, seq, length))
+
+    def fork(self, seq) -> int:
+        s = C.c_int32()
+        _ck(lib().b200kv_fork(self._h, seq, C.byref(s), _stream()))
+        return s.value
+
+    def check(self):
+        _ck(lib().b200kv_check(self._h, _stream()))
+
+
+def sdpa(q, k, v, mask=None, scale=None, causal=False):
+    """Lone Sdpa on dense tensors (rank 3 [B,S,D] or rank 4 [B,H,S,D]); mask is additive, broadcast over b / h."""
+    import torch
+
+    rank3 = q.dim() == 3
+    if rank3:
+        q, k, v = q.unsqueeze(1), k.unsqueeze(1), v.unsqueeze(1)
+        if mask is not None:
+            mask = mask.unsqueeze(1)
+    B, Hq, S, D = q.shape
+    _, Hkv, T, _ = k.shape
+    out = torch.empty((B, Hq, S, D), dtype=q.dtype, device=q.device)
+    ms, mptr, mdt = None, None, 0
+    if mask is not None:
+        mask = mask.expand(mask.shape[0], mask.shape[1], S, T)  # stride 0 where broadcast
+        st = list(mask.stride())
+        if mask.shape[0] == 1:
+            st[0] = 0
+        if mask.shape[1] == 1:
+            st[1] = 0
+        ms, mptr, mdt = (C.c_int64 * 4)(*st), mask.data_ptr(), _dtype_code(mask)
+    with torch.cuda.device(q.device):
+        _ck(lib().b200kv_sdpa(q.data_ptr(), _strides(q, 3), k.data_ptr(), _strides(k, 3), v.data_ptr(), _strides(v, 3),
+                              mptr, ms, mdt, out.data_ptr(), _strides(out, 3), B, Hq, Hkv, S, T, D, _dtype_code(q),
+                              float(scale or 0.0), int(causal), _stream()))
+    return out[:, 0] if rank3 else out

@@ -1,0 +1,54 @@
+// b200kv_attend: attention of the newest tokens of each sequence over its paged cache.
+//
+// The fused "cache + Sdpa" op of the reference (InPlaceKvSdpa, transformers/src/ops/inplace_kv_cache.rs:135-216)
+// appends and then attends; here the two halves are b200kv_append and b200kv_attend, enqueued back to back.
+#include <cmath>
+
+#include "internal.h"
+
+using namespace b200kv;
+
+extern "C" int b200kv_attend(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t n_q_heads, int32_t n_new,
+                             const void* q, const int64_t q_strides[3], void* out, const int64_t out_strides[3],
+                             int32_t dtype, float scale, int32_t causal, void* stream_) {
+    if (validate_seqs(c, n_seqs, seqs) != B200KV_OK) return B200KV_KO;
+    if (!c->L.has_v) return fail("this cache holds one tensor only: attention needs K and V");
+    if (!q || !out || !q_strides || !out_strides) return fail("null tensor or strides");
+    if (n_new <= 0) return fail("n_new must be positive");
+    if (n_q_heads <= 0 || n_q_heads % c->L.Hkv != 0)
+        return fail("n_q_heads (%d) must be a positive multiple of n_kv_heads (%d)", n_q_heads, c->L.Hkv);
+    if (dtype < B200KV_F32 || dtype > B200KV_BF16) return fail("unknown dtype %d", dtype);
+    for (int i = 0; i < n_seqs; i++)
+        if (c->seqs[seqs[i]].len < n_new)
+            return fail("sequence %d holds %lld tokens, fewer than the %d queries: append before attending", seqs[i],
+                        (long long)c->seqs[seqs[i]].len, n_new);
+    if (scale <= 0.f) scale = 1.0f / sqrtf((float)c->L.D);
+    cudaStream_t stream = (cudaStream_t)stream_;
+    DeviceGuard guard(c->cfg.device);
+
+    if (n_new == 1) return launch_decode(c, n_seqs, seqs, n_q_heads, q, q_strides, out, out_strides, dtype, scale, stream);
+
+    // n_new > 1: materialise K / V of one sequence at a time (dequantised to f32 for the quantised
+    // formats, a bit copy otherwise) and run the generic kernel on them.
+    const int Hkv = c->L.Hkv, D = c->L.D;
+    const int kv_dtype = fmt_is_block_quant(c->L.fmt) ? B200KV_F32 : c->L.fmt;
+    int64_t max_len = 0;
+    for (int i = 0; i < n_seqs; i++) max_len = std::max<int64_t>(max_len, c->seqs[seqs[i]].len);
+    const size_t one = (size_t)Hkv * max_len * D * dtype_size(kv_dtype);
+    if (ensure_workspace(c, 2 * one) != B200KV_OK) return B200KV_KO;
+    for (int i = 0; i < n_seqs; i++) {
+        const int64_t T = c->seqs[seqs[i]].len;
+        void* kbuf = c->ws;
+        void* vbuf = c->ws + one;
+        const int64_t st2[2] = {T * D, D};
+        if (launch_export(c, seqs[i], kbuf, st2, vbuf, st2, kv_dtype, stream) != B200KV_OK) return B200KV_KO;
+        const int64_t ks[3] = {0, T * D, D};
+        const int esz = dtype_size(dtype);
+        const void* qi = (const uint8_t*)q + (int64_t)i * q_strides[0] * esz;
+        void* oi = (uint8_t*)out + (int64_t)i * out_strides[0] * esz;
+        if (launch_sdpa_dense(qi, q_strides, kbuf, ks, vbuf, ks, nullptr, nullptr, 0, oi, out_strides, 1, n_q_heads, Hkv,
+                              n_new, (int)T, D, dtype, kv_dtype, scale, causal, stream) != B200KV_OK)
+            return B200KV_KO;
+    }
+    return B200KV_OK;
+}

@@ -1,0 +1,642 @@
+// Cache handle (page pool, page tables, descriptor ring) and the append / export kernels.
+//
+// Replaces GpuDynKVCacheState::eval (gpu/src/ops/dyn_kv_cache.rs:58-113), which allocates a fresh
+// [.., P+S, ..] tensor and copies the whole past every step, by an in-place paged append that
+// touches only the S new tokens; and gives QuantizedDynKvCacheState::ingest
+// (transformers/src/ops/quant_dyn_kv_cache.rs:403-430) a device form for the block-32 formats,
+// with the arithmetic of linalg/src/frame/block_quant/{q8_1.rs:20-48, q4_0.rs:19-45} done with
+// explicitly rounded IEEE operations so that codes and scales are bit-identical to the CPU's.
+#include <algorithm>
+#include <cstring>
+
+#include "internal.h"
+
+namespace b200kv {
+
+std::string& last_error() {
+    static thread_local std::string e;
+    return e;
+}
+int fail(const char* fmt, ...) {
+    char buf[1024];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    last_error() = buf;
+    return B200KV_KO;
+}
+
+// ---- descriptor ring ---------------------------------------------------------------------------
+int staging_acquire(b200kv_cache* c, size_t bytes, int* slot, uint8_t** host, uint8_t** dev) {
+    Staging& s = c->st;
+    if (bytes > s.slot_bytes) return fail("call descriptor of %zu bytes exceeds the %zu-byte slot", bytes, s.slot_bytes);
+    int i = s.next;
+    s.next = (s.next + 1) % Staging::SLOTS;
+    if (s.used[i]) B200KV_CUDA(cudaEventSynchronize(s.ev[i]));
+    s.used[i] = false;
+    *slot = i;
+    *host = s.host + (size_t)i * s.slot_bytes;
+    *dev = s.dev + (size_t)i * s.slot_bytes;
+    return B200KV_OK;
+}
+int staging_upload(b200kv_cache* c, int slot, size_t bytes, cudaStream_t stream) {
+    Staging& s = c->st;
+    B200KV_CUDA(cudaMemcpyAsync(s.dev + (size_t)slot * s.slot_bytes, s.host + (size_t)slot * s.slot_bytes, bytes,
+                                cudaMemcpyHostToDevice, stream));
+    return B200KV_OK;
+}
+int staging_release(b200kv_cache* c, int slot, cudaStream_t stream) {
+    B200KV_CUDA(cudaEventRecord(c->st.ev[slot], stream));
+    c->st.used[slot] = true;
+    return B200KV_OK;
+}
+int ensure_workspace(b200kv_cache* c, size_t bytes) {
+    if (bytes <= c->ws_bytes) return B200KV_OK;
+    size_t want = std::max(bytes, c->ws_bytes * 2);
+    if (c->ws) B200KV_CUDA(cudaFree(c->ws));  // cudaFree waits for work that may still read the old block
+    c->ws = nullptr;
+    c->ws_bytes = 0;
+    B200KV_CUDA(cudaMalloc(&c->ws, want));
+    c->ws_bytes = want;
+    return B200KV_OK;
+}
+int validate_seqs(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs) {
+    if (!c) return fail("null cache");
+    if (n_seqs <= 0 || !seqs) return fail("need at least one sequence");
+    for (int i = 0; i < n_seqs; i++) {
+        int s = seqs[i];
+        if (s < 0 || s >= (int)c->seqs.size() || !c->seqs[s].live) return fail("sequence %d is not live", s);
+        for (int j = 0; j < i; j++)
+            if (seqs[j] == s) return fail("sequence %d appears twice in one call", s);
+    }
+    return B200KV_OK;
+}
+
+// ---- kernels ---------------------------------------------------------------------------------------
+
+__global__ void table_scatter_kernel(int32_t* table, const int32_t* upd, int n) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) table[upd[2 * i]] = upd[2 * i + 1];
+}
+
+struct AppendParams {
+    uint8_t* pool;
+    const int32_t* table;
+    const int32_t* desc;  // per batch entry: {table row, length before the append}
+    int* status;
+    const void* src[2];
+    int64_t sb[2], sh[2], ss[2];
+    int64_t page_bytes;
+    int32_t n_pages, max_pages_per_seq;
+    int32_t n_seqs, H, S, D;
+    int32_t chunk_bytes, data_bytes, plane_w, units;  // units = 16-byte units per row
+    int32_t dtype, vec_ok, has_v;
+};
+
+// Rust `x as i8` after f32::round / truncation: saturating, NaN -> 0.
+__device__ inline int sat_i8_rz(float x) {
+    int i = __float2int_rz(x);  // saturates to int32, NaN -> 0
+    return max(-128, min(127, i));
+}
+
+// One thread per 16-byte unit of a token-head row; grid.y selects K or V.
+template <int FMT>
+__global__ void __launch_bounds__(256) append_kernel(AppendParams p) {
+    constexpr int EPU = elems_in_bytes<FMT>(16);  // elements per unit
+    const int kv = blockIdx.y;
+    const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t total_rows = (int64_t)p.n_seqs * p.H * p.S;
+    int64_t row = gid / p.units;
+    const int u = (int)(gid % p.units);
+    const bool valid = row < total_rows;
+    if (!valid) row = total_rows - 1;  // keep the lane alive for the shuffles below
+    const int b = (int)(row / ((int64_t)p.H * p.S));
+    const int h = (int)((row / p.S) % p.H);
+    const int s = (int)(row % p.S);
+    const int c0 = u * EPU;
+
+    // ---- load EPU input elements --------------------------------------------------------------
+    const int esz = dtype_size(p.dtype);
+    const uint8_t* src = (const uint8_t*)p.src[kv] + (b * p.sb[kv] + h * p.sh[kv] + s * p.ss[kv] + c0) * esz;
+    uint4 out16;  // the 16 bytes this thread stores
+    float scale_f = 0.f;
+    bool write_scale = false;
+
+    if (FMT == B200KV_FMT_F32 || FMT == B200KV_FMT_F16 || FMT == B200KV_FMT_BF16) {
+        // bit copy: storage type == input type (checked on the host)
+        if (p.vec_ok) {
+            out16 = *(const uint4*)src;
+        } else {
+            uint8_t tmp[16];
+            for (int i = 0; i < 16; i += esz)
+                for (int j = 0; j < esz; j++) tmp[i + j] = src[i + j];
+            memcpy(&out16, tmp, 16);
+        }
+    } else {
+        float v[EPU];
+        if (p.dtype == B200KV_F32) {
+            if (p.vec_ok) {
+#pragma unroll
+                for (int i = 0; i < EPU / 4; i++) {
+                    float4 f = ((const float4*)src)[i];
+                    v[4 * i] = f.x, v[4 * i + 1] = f.y, v[4 * i + 2] = f.z, v[4 * i + 3] = f.w;
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < EPU; i++) v[i] = ((const float*)src)[i];
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < EPU; i++) v[i] = ld_as_f32(src, p.dtype, i);
+        }
+        // signed value of largest magnitude, first occurrence wins (strict <); NaN never wins
+        float amax = 0.f, mx = 0.f;
+#pragma unroll
+        for (int i = 0; i < EPU; i++) {
+            float a = fabsf(v[i]);
+            if (amax < a) {
+                amax = a;
+                mx = v[i];
+            }
+        }
+        if (FMT == B200KV_FMT_Q8_1) {
+            // a block of 32 spans two units: combine with the neighbour lane, lower channels win ties
+            float o_amax = __shfl_xor_sync(0xffffffffu, amax, 1);
+            float o_mx = __shfl_xor_sync(0xffffffffu, mx, 1);
+            bool take_other = (u & 1) ? !(o_amax < amax) : (amax < o_amax);
+            if (take_other) mx = o_mx;
+            float scale = __fdiv_rn(mx, 127.0f);
+            float r = (scale == 0.f) ? 0.f : __fdiv_rn(1.0f, scale);
+            uint32_t w[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                uint32_t word = 0;
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    int code = sat_i8_rz(roundf(__fmul_rn(v[4 * i + j], r)));
+                    word |= ((uint32_t)code & 0xffu) << (8 * j);
+                }
+                w[i] = word;
+            }
+            out16 = make_uint4(w[0], w[1], w[2], w[3]);
+            scale_f = scale;
+            write_scale = (u & 1) == 0;
+        } else {  // Q4_0: the unit is the whole block
+            float scale = __fdiv_rn(mx, -8.0f);
+            float r = (scale == 0.f) ? 0.f : __fdiv_rn(1.0f, scale);
+            uint32_t w[4] = {0, 0, 0, 0};
+#pragma unroll
+            for (int j = 0; j < 16; j++) {
+                int lo = min(sat_i8_rz(__fadd_rn(__fmul_rn(v[j], r), 8.5f)), 15);
+                int hi = min(sat_i8_rz(__fadd_rn(__fmul_rn(v[j + 16], r), 8.5f)), 15);
+                // the reference ORs the two codes without masking (helpers.rs:57-68)
+                uint32_t byte = (((uint32_t)lo & 0xffu) | (((uint32_t)hi & 0xffu) << 4)) & 0xffu;
+                w[j / 4] |= byte << (8 * (j % 4));
+            }
+            out16 = make_uint4(w[0], w[1], w[2], w[3]);
+            scale_f = scale;
+            write_scale = true;
+        }
+    }
+    if (!valid) return;
+
+    // ---- locate the page slot and store --------------------------------------------------------------
+    const int32_t trow = p.desc[2 * b], len0 = p.desc[2 * b + 1];
+    const int64_t pos = (int64_t)len0 + s;
+    const int32_t pg = p.table[(int64_t)trow * p.max_pages_per_seq + pos / PAGE_TOKENS];
+    if (pg < 0 || pg >= p.n_pages) {
+        atomicOr(p.status, STATUS_PAGE_OOB);
+        return;
+    }
+    const int t = (int)(pos % PAGE_TOKENS);
+    uint8_t* chunk = p.pool + (int64_t)pg * p.page_bytes + (int64_t)(h * (p.has_v ? 2 : 1) + kv) * p.chunk_bytes;
+    *(uint4*)(chunk + chunk_addr(p.plane_w, t, u * 16)) = out16;
+    if (write_scale) {
+        int blk = (FMT == B200KV_FMT_Q8_1) ? u / 2 : u;
+        ((__half*)(chunk + p.data_bytes))[t * (p.D / 32) + blk] = __float2half_rn(scale_f);
+    }
+}
+
+struct ExportParams {
+    const uint8_t* pool;
+    const int32_t* table_row;  // page ids of the sequence
+    void* dst[2];
+    int64_t dh[2], dt[2];  // strides {head, token} in elements
+    void* codes;           // raw export: codes / scales destinations (one of K, V)
+    void* scales;
+    int64_t page_bytes, len;
+    int32_t H, D, chunk_bytes, data_bytes, plane_w, units, row_bytes;
+    int32_t dtype, has_v, which;
+};
+
+// One thread per 16-byte unit; mode 0: dequantised / bit-copied elements, mode 1: raw codes + scales.
+template <int FMT, int MODE>
+__global__ void __launch_bounds__(256) export_kernel(ExportParams p) {
+    constexpr int EPU = elems_in_bytes<FMT>(16);
+    const int kv = MODE == 1 ? p.which : blockIdx.y;
+    const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t row = gid / p.units;
+    const int u = (int)(gid % p.units);
+    if (row >= (int64_t)p.H * p.len) return;
+    const int h = (int)(row / p.len);
+    const int64_t tok = row % p.len;
+    const int32_t pg = p.table_row[tok / PAGE_TOKENS];
+    const int t = (int)(tok % PAGE_TOKENS);
+    const uint8_t* chunk = p.pool + (int64_t)pg * p.page_bytes + (int64_t)(h * (p.has_v ? 2 : 1) + kv) * p.chunk_bytes;
+    const uint8_t* unit = chunk + chunk_addr(p.plane_w, t, u * 16);
+    if (MODE == 1) {
+        *(uint4*)((uint8_t*)p.codes + ((int64_t)h * p.len + tok) * p.row_bytes + u * 16) = *(const uint4*)unit;
+        int nb = p.D / 32;
+        if (u < nb)
+            ((__half*)p.scales)[((int64_t)h * p.len + tok) * nb + u] = ((const __half*)(chunk + p.data_bytes))[t * nb + u];
+        return;
+    }
+    const int64_t base = h * p.dh[kv] + tok * p.dt[kv];
+    if (FMT == B200KV_FMT_F32 || FMT == B200KV_FMT_F16 || FMT == B200KV_FMT_BF16) {
+        // bit copy (the destination has the storage element type): no conversion, NaN payloads survive
+        const uint4 raw = *(const uint4*)unit;
+        if (FMT == B200KV_FMT_F32) {
+            uint32_t* d = (uint32_t*)p.dst[kv] + base + u * EPU;
+            d[0] = raw.x, d[1] = raw.y, d[2] = raw.z, d[3] = raw.w;
+        } else {
+            uint16_t* d = (uint16_t*)p.dst[kv] + base + u * EPU;
+            const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+            for (int i = 0; i < 4; i++) d[2 * i] = (uint16_t)w[i], d[2 * i + 1] = (uint16_t)(w[i] >> 16);
+        }
+        return;
+    }
+    float v[EPU];
+    load_piece<FMT, 16>(unit, v);
+    if (FMT == B200KV_FMT_Q8_1 || FMT == B200KV_FMT_Q4_0) {
+        int blk = (FMT == B200KV_FMT_Q8_1) ? u / 2 : u;
+        float d = __half2float(((const __half*)(chunk + p.data_bytes))[t * (p.D / 32) + blk]);
+#pragma unroll
+        for (int i = 0; i < EPU; i++) v[i] = __fmul_rn(v[i], d);  // code * f32(f16 scale): exact in f32
+    }
+#pragma unroll
+    for (int i = 0; i < EPU; i++) st_from_f32(p.dst[kv], p.dtype, base + row_channel<FMT>(u * 16, i, 16), v[i]);
+}
+
+// ---- host side --------------------------------------------------------------------------------------
+
+static int alloc_pages(b200kv_cache* c, SeqState& s, int64_t new_len, std::vector<int32_t>& upd, int row) {
+    int64_t need = (new_len + PAGE_TOKENS - 1) / PAGE_TOKENS;
+    int64_t have = (int64_t)s.pages.size();
+    if (need > c->max_pages_per_seq) return fail("sequence would exceed max_seq_tokens (%lld)", (long long)c->cfg.max_seq_tokens);
+    if (need - have > (int64_t)c->free_pages.size())
+        return fail("page pool exhausted: need %lld more pages, %zu free", (long long)(need - have), c->free_pages.size());
+    for (int64_t i = have; i < need; i++) {
+        int32_t pg = c->free_pages.back();
+        c->free_pages.pop_back();
+        s.pages.push_back(pg);
+        upd.push_back((int32_t)((int64_t)row * c->max_pages_per_seq + i));
+        upd.push_back(pg);
+    }
+    return B200KV_OK;
+}
+
+template <int FMT>
+static void launch_append_fmt(const AppendParams& p, int n_kv, cudaStream_t stream) {
+    int64_t threads = (int64_t)p.n_seqs * p.H * p.S * p.units;
+    dim3 grid((unsigned)((threads + 255) / 256), n_kv);
+    append_kernel<FMT><<<grid, 256, 0, stream>>>(p);
+}
+
+int launch_export(b200kv_cache* c, int32_t seq, void* k_out, const int64_t* ks, void* v_out, const int64_t* vs,
+                  int32_t dtype, cudaStream_t stream) {
+    const SeqState& s = c->seqs[seq];
+    if (s.len == 0) return B200KV_OK;
+    ExportParams p{};
+    p.pool = c->pool;
+    p.table_row = c->d_table + (int64_t)seq * c->max_pages_per_seq;
+    p.dst[0] = k_out, p.dst[1] = v_out;
+    p.dh[0] = ks[0], p.dt[0] = ks[1];
+    if (v_out) p.dh[1] = vs[0], p.dt[1] = vs[1];
+    p.page_bytes = c->L.page_bytes, p.len = s.len;
+    p.H = c->L.Hkv, p.D = c->L.D, p.chunk_bytes = c->L.chunk_bytes, p.data_bytes = c->L.data_bytes;
+    p.plane_w = c->L.plane_w, p.units = c->L.row_bytes / 16, p.row_bytes = c->L.row_bytes;
+    p.dtype = dtype, p.has_v = c->L.has_v;
+    int64_t threads = (int64_t)p.H * p.len * p.units;
+    dim3 grid((unsigned)((threads + 255) / 256), v_out ? 2 : 1);
+    switch (c->L.fmt) {
+        case B200KV_FMT_F32: export_kernel<B200KV_FMT_F32, 0><<<grid, 256, 0, stream>>>(p); break;
+        case B200KV_FMT_F16: export_kernel<B200KV_FMT_F16, 0><<<grid, 256, 0, stream>>>(p); break;
+        case B200KV_FMT_BF16: export_kernel<B200KV_FMT_BF16, 0><<<grid, 256, 0, stream>>>(p); break;
+        case B200KV_FMT_Q8_1: export_kernel<B200KV_FMT_Q8_1, 0><<<grid, 256, 0, stream>>>(p); break;
+        case B200KV_FMT_Q4_0: export_kernel<B200KV_FMT_Q4_0, 0><<<grid, 256, 0, stream>>>(p); break;
+        default: return fail("format %d cannot be exported", c->L.fmt);
+    }
+    B200KV_CUDA(cudaGetLastError());
+    return B200KV_OK;
+}
+
+}  // namespace b200kv
+
+using namespace b200kv;
+
+extern "C" {
+
+const char* b200kv_last_error(void) { return last_error().c_str(); }
+const char* b200kv_version(void) { return "b200kv 0.1 sm_100a"; }
+
+int b200kv_create(const b200kv_config* cfg, b200kv_cache** out) {
+    if (!cfg || !out) return fail("null argument");
+    *out = nullptr;
+    if (cfg->format < B200KV_FMT_F32 || cfg->format > B200KV_FMT_Q4_0)
+        return fail("storage format %d is not available in this build", cfg->format);
+    if (cfg->head_dim != 64 && cfg->head_dim != 128) return fail("head_dim must be 64 or 128, got %d", cfg->head_dim);
+    if (cfg->n_kv_heads <= 0 || cfg->max_seqs <= 0 || cfg->max_seq_tokens <= 0 || cfg->pool_tokens <= 0)
+        return fail("n_kv_heads, max_seqs, max_seq_tokens and pool_tokens must be positive");
+    int n_dev = 0;
+    if (cudaGetDeviceCount(&n_dev) != cudaSuccess || n_dev == 0)
+        return fail("no CUDA device: b200kv has no CPU fallback");
+    if (cfg->device < 0 || cfg->device >= n_dev) return fail("device %d out of range (%d devices)", cfg->device, n_dev);
+    cudaDeviceProp prop;
+    B200KV_CUDA(cudaGetDeviceProperties(&prop, cfg->device));
+    if (prop.major != 10) return fail("device %d is sm_%d%d; this library is built for sm_100a only", cfg->device, prop.major, prop.minor);
+    DeviceGuard guard(cfg->device);
+
+    b200kv_cache* c = new b200kv_cache();
+    c->cfg = *cfg;
+    c->L = make_layout(cfg->format, cfg->head_dim, cfg->n_kv_heads, cfg->has_values ? 1 : 0);
+    c->max_pages_per_seq = (int)((cfg->max_seq_tokens + PAGE_TOKENS - 1) / PAGE_TOKENS);
+    // every live sequence may hold one partly filled page
+    c->n_pages = (cfg->pool_tokens + PAGE_TOKENS - 1) / PAGE_TOKENS + cfg->max_seqs;
+    c->seqs.resize(cfg->max_seqs);
+    auto cleanup = [&](int rc) {
+        b200kv_destroy(c);
+        return rc;
+    };
+    size_t pool_bytes = (size_t)c->n_pages * c->L.page_bytes;
+    if (cudaMalloc(&c->pool, pool_bytes) != cudaSuccess)
+        return cleanup(fail("cannot allocate a %zu-byte page pool: %s", pool_bytes, cudaGetErrorString(cudaGetLastError())));
+    // zero the pool once: unused token slots of a partly filled page are read (and masked) by the
+    // attention kernels and must hold finite values
+    if (cudaMemset(c->pool, 0, pool_bytes) != cudaSuccess) return cleanup(fail("cudaMemset failed"));
+    size_t table_bytes = (size_t)cfg->max_seqs * c->max_pages_per_seq * sizeof(int32_t);
+    if (cudaMalloc(&c->d_table, table_bytes) != cudaSuccess || cudaMemset(c->d_table, 0xff, table_bytes) != cudaSuccess)
+        return cleanup(fail("cannot allocate the page tables"));
+    if (cudaMalloc(&c->d_status, sizeof(int)) != cudaSuccess || cudaMemset(c->d_status, 0, sizeof(int)) != cudaSuccess)
+        return cleanup(fail("cannot allocate the status word"));
+    c->free_pages.resize(c->n_pages);
+    for (int64_t i = 0; i < c->n_pages; i++) c->free_pages[i] = (int32_t)(c->n_pages - 1 - i);
+    // descriptor slots: the largest descriptor is a decode work list (64 splits per sequence at most)
+    c->st.slot_bytes = std::max<size_t>(64 << 10, (size_t)cfg->max_seqs * (16 + 64 * 32) + 4096);
+    if (cudaMallocHost(&c->st.host, c->st.slot_bytes * Staging::SLOTS) != cudaSuccess ||
+        cudaMalloc(&c->st.dev, c->st.slot_bytes * Staging::SLOTS) != cudaSuccess)
+        return cleanup(fail("cannot allocate the descriptor ring"));
+    for (int i = 0; i < Staging::SLOTS; i++)
+        if (cudaEventCreateWithFlags(&c->st.ev[i], cudaEventDisableTiming) != cudaSuccess)
+            return cleanup(fail("cannot create events"));
+    if (ensure_workspace(c, 8 << 20) != B200KV_OK) return cleanup(B200KV_KO);
+    if (cudaDeviceSynchronize() != cudaSuccess) return cleanup(fail("device error during creation"));
+    *out = c;
+    return B200KV_OK;
+}
+
+int b200kv_destroy(b200kv_cache* c) {
+    if (!c) return B200KV_OK;
+    DeviceGuard guard(c->cfg.device);
+    cudaDeviceSynchronize();
+    for (int i = 0; i < Staging::SLOTS; i++)
+        if (c->st.ev[i]) cudaEventDestroy(c->st.ev[i]);
+    if (c->st.host) cudaFreeHost(c->st.host);
+    if (c->st.dev) cudaFree(c->st.dev);
+    if (c->ws) cudaFree(c->ws);
+    if (c->d_status) cudaFree(c->d_status);
+    if (c->d_table) cudaFree(c->d_table);
+    if (c->pool) cudaFree(c->pool);
+    delete c;
+    return B200KV_OK;
+}
+
+int b200kv_seq_new(b200kv_cache* c, int32_t* seq_out) {
+    if (!c || !seq_out) return fail("null argument");
+    for (size_t i = 0; i < c->seqs.size(); i++)
+        if (!c->seqs[i].live) {
+            c->seqs[i].live = true;
+            c->seqs[i].len = 0;
+            c->seqs[i].pages.clear();
+            *seq_out = (int32_t)i;
+            return B200KV_OK;
+        }
+    return fail("all %zu sequence slots are in use", c->seqs.size());
+}
+
+int b200kv_seq_free(b200kv_cache* c, int32_t seq) {
+    if (!c || seq < 0 || seq >= (int)c->seqs.size() || !c->seqs[seq].live) return fail("sequence %d is not live", seq);
+    SeqState& s = c->seqs[seq];
+    for (int32_t pg : s.pages) c->free_pages.push_back(pg);
+    s.pages.clear();
+    s.len = 0;
+    s.live = false;
+    return B200KV_OK;
+}
+
+int64_t b200kv_seq_len(b200kv_cache* c, int32_t seq) {
+    if (!c || seq < 0 || seq >= (int)c->seqs.size() || !c->seqs[seq].live) {
+        fail("sequence %d is not live", seq);
+        return -1;
+    }
+    return c->seqs[seq].len;
+}
+
+int64_t b200kv_free_pages(b200kv_cache* c) { return c ? (int64_t)c->free_pages.size() : -1; }
+int64_t b200kv_page_bytes(b200kv_cache* c) { return c ? c->L.page_bytes : -1; }
+
+int b200kv_append(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t n_new, const void* k_new,
+                  const int64_t k_strides[3], const void* v_new, const int64_t v_strides[3], int32_t dtype,
+                  void* stream_) {
+    if (validate_seqs(c, n_seqs, seqs) != B200KV_OK) return B200KV_KO;
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (n_new < 0) return fail("n_new must be >= 0");
+    if (n_new == 0) return B200KV_OK;
+    if (!k_new || !k_strides) return fail("k_new and its strides are required");
+    if (c->L.has_v ? (!v_new || !v_strides) : (v_new != nullptr))
+        return fail(c->L.has_v ? "this cache holds K and V: v_new is required" : "this cache holds one tensor: v_new must be NULL");
+    if (dtype < B200KV_F32 || dtype > B200KV_BF16) return fail("unknown dtype %d", dtype);
+    if (!fmt_is_block_quant(c->L.fmt) && dtype != c->L.fmt)
+        return fail("a bit-copy cache of format %d takes input of the same type, got dtype %d", c->L.fmt, dtype);
+    DeviceGuard guard(c->cfg.device);
+
+    // host bookkeeping first, committed only if everything can be enqueued
+    std::vector<int32_t> upd;
+    std::vector<size_t> old_pages(n_seqs);
+    auto rollback = [&](int upto) {
+        for (int i = 0; i < upto; i++) {
+            SeqState& s = c->seqs[seqs[i]];
+            while (s.pages.size() > old_pages[i]) {
+                c->free_pages.push_back(s.pages.back());
+                s.pages.pop_back();
+            }
+        }
+    };
+    for (int i = 0; i < n_seqs; i++) {
+        SeqState& s = c->seqs[seqs[i]];
+        old_pages[i] = s.pages.size();
+        if (alloc_pages(c, s, s.len + n_new, upd, seqs[i]) != B200KV_OK) {
+            rollback(i + 1);
+            return B200KV_KO;
+        }
+    }
+    size_t desc_words = (size_t)2 * n_seqs + upd.size();
+    int slot;
+    uint8_t *h, *d;
+    if (staging_acquire(c, desc_words * 4, &slot, &h, &d) != B200KV_OK) {
+        rollback(n_seqs);
+        return B200KV_KO;
+    }
+    int32_t* hw = (int32_t*)h;
+    for (int i = 0; i < n_seqs; i++) {
+        hw[2 * i] = seqs[i];
+        hw[2 * i + 1] = (int32_t)c->seqs[seqs[i]].len;
+    }
+    if (!upd.empty()) memcpy(hw + 2 * n_seqs, upd.data(), upd.size() * 4);
+    if (staging_upload(c, slot, desc_words * 4, stream) != B200KV_OK) {
+        rollback(n_seqs);
+        return B200KV_KO;
+    }
+    if (!upd.empty()) {
+        int n = (int)(upd.size() / 2);
+        table_scatter_kernel<<<(n + 255) / 256, 256, 0, stream>>>(c->d_table, (const int32_t*)d + 2 * n_seqs, n);
+    }
+    AppendParams p{};
+    p.pool = c->pool, p.table = c->d_table, p.desc = (const int32_t*)d, p.status = c->d_status;
+    p.src[0] = k_new, p.src[1] = v_new;
+    p.sb[0] = k_strides[0], p.sh[0] = k_strides[1], p.ss[0] = k_strides[2];
+    if (v_new) p.sb[1] = v_strides[0], p.sh[1] = v_strides[1], p.ss[1] = v_strides[2];
+    p.page_bytes = c->L.page_bytes, p.n_pages = (int32_t)c->n_pages, p.max_pages_per_seq = c->max_pages_per_seq;
+    p.n_seqs = n_seqs, p.H = c->L.Hkv, p.S = n_new, p.D = c->L.D;
+    p.chunk_bytes = c->L.chunk_bytes, p.data_bytes = c->L.data_bytes, p.plane_w = c->L.plane_w;
+    p.units = c->L.row_bytes / 16;
+    p.dtype = dtype, p.has_v = c->L.has_v;
+    // 16-byte vector loads need aligned bases and strides
+    const int esz = dtype_size(dtype);
+    auto aligned = [&](const void* ptr, const int64_t* st) {
+        return ptr == nullptr ||
+               ((uintptr_t)ptr % 16 == 0 && (st[0] * esz) % 16 == 0 && (st[1] * esz) % 16 == 0 && (st[2] * esz) % 16 == 0);
+    };
+    p.vec_ok = aligned(k_new, k_strides) && aligned(v_new, v_strides);
+    const int n_kv = c->L.has_v ? 2 : 1;
+    switch (c->L.fmt) {
+        case B200KV_FMT_F32: launch_append_fmt<B200KV_FMT_F32>(p, n_kv, stream); break;
+        case B200KV_FMT_F16: launch_append_fmt<B200KV_FMT_F16>(p, n_kv, stream); break;
+        case B200KV_FMT_BF16: launch_append_fmt<B200KV_FMT_BF16>(p, n_kv, stream); break;
+        case B200KV_FMT_Q8_1: launch_append_fmt<B200KV_FMT_Q8_1>(p, n_kv, stream); break;
+        case B200KV_FMT_Q4_0: launch_append_fmt<B200KV_FMT_Q4_0>(p, n_kv, stream); break;
+    }
+    cudaError_t e = cudaGetLastError();
+    staging_release(c, slot, stream);
+    if (e != cudaSuccess) {
+        rollback(n_seqs);
+        return fail("append launch failed: %s", cudaGetErrorString(e));
+    }
+    for (int i = 0; i < n_seqs; i++) c->seqs[seqs[i]].len += n_new;
+    return B200KV_OK;
+}
+
+int b200kv_export(b200kv_cache* c, int32_t seq, void* k_out, const int64_t k_strides[2], void* v_out,
+                  const int64_t v_strides[2], int32_t dtype, void* stream) {
+    if (validate_seqs(c, 1, &seq) != B200KV_OK) return B200KV_KO;
+    if (!k_out || !k_strides) return fail("k_out and its strides are required");
+    if (v_out && (!c->L.has_v || !v_strides)) return fail("v_out given but the cache has no values / no strides");
+    if (dtype < B200KV_F32 || dtype > B200KV_BF16) return fail("unknown dtype %d", dtype);
+    if (!fmt_is_block_quant(c->L.fmt) && dtype != c->L.fmt)
+        return fail("a bit-copy cache exports its own element type (format %d), got dtype %d", c->L.fmt, dtype);
+    DeviceGuard guard(c->cfg.device);
+    return launch_export(c, seq, k_out, k_strides, v_out, v_strides, dtype, (cudaStream_t)stream);
+}
+
+int b200kv_export_codes(b200kv_cache* c, int32_t seq, int32_t which, void* codes, void* scales, void* stream) {
+    if (validate_seqs(c, 1, &seq) != B200KV_OK) return B200KV_KO;
+    if (!fmt_is_block_quant(c->L.fmt)) return fail("format %d has no codes: use b200kv_export", c->L.fmt);
+    if (which < 0 || which > (c->L.has_v ? 1 : 0)) return fail("which = %d out of range", which);
+    if (!codes || !scales) return fail("codes and scales are required");
+    DeviceGuard guard(c->cfg.device);
+    const SeqState& s = c->seqs[seq];
+    if (s.len == 0) return B200KV_OK;
+    ExportParams p{};
+    p.pool = c->pool;
+    p.table_row = c->d_table + (int64_t)seq * c->max_pages_per_seq;
+    p.codes = codes, p.scales = scales, p.which = which;
+    p.page_bytes = c->L.page_bytes, p.len = s.len;
+    p.H = c->L.Hkv, p.D = c->L.D, p.chunk_bytes = c->L.chunk_bytes, p.data_bytes = c->L.data_bytes;
+    p.plane_w = c->L.plane_w, p.units = c->L.row_bytes / 16, p.row_bytes = c->L.row_bytes, p.has_v = c->L.has_v;
+    int64_t threads = (int64_t)p.H * p.len * p.units;
+    dim3 grid((unsigned)((threads + 255) / 256));
+    if (c->L.fmt == B200KV_FMT_Q8_1) export_kernel<B200KV_FMT_Q8_1, 1><<<grid, 256, 0, (cudaStream_t)stream>>>(p);
+    else export_kernel<B200KV_FMT_Q4_0, 1><<<grid, 256, 0, (cudaStream_t)stream>>>(p);
+    B200KV_CUDA(cudaGetLastError());
+    return B200KV_OK;
+}
+
+int b200kv_truncate(b200kv_cache* c, int32_t seq, int64_t len) {
+    if (validate_seqs(c, 1, &seq) != B200KV_OK) return B200KV_KO;
+    SeqState& s = c->seqs[seq];
+    if (len < 0 || len > s.len) return fail("cannot truncate a sequence of %lld tokens to %lld", (long long)s.len, (long long)len);
+    size_t keep = (size_t)((len + PAGE_TOKENS - 1) / PAGE_TOKENS);
+    while (s.pages.size() > keep) {
+        c->free_pages.push_back(s.pages.back());
+        s.pages.pop_back();
+    }
+    s.len = len;
+    return B200KV_OK;
+}
+
+int b200kv_fork(b200kv_cache* c, int32_t seq, int32_t* new_seq_out, void* stream_) {
+    if (validate_seqs(c, 1, &seq) != B200KV_OK) return B200KV_KO;
+    if (!new_seq_out) return fail("null argument");
+    cudaStream_t stream = (cudaStream_t)stream_;
+    DeviceGuard guard(c->cfg.device);
+    int32_t ns;
+    if (b200kv_seq_new(c, &ns) != B200KV_OK) return B200KV_KO;
+    SeqState& src = c->seqs[seq];
+    SeqState& dst = c->seqs[ns];
+    std::vector<int32_t> upd;
+    if (alloc_pages(c, dst, src.len, upd, ns) != B200KV_OK) {
+        b200kv_seq_free(c, ns);
+        return B200KV_KO;
+    }
+    int slot;
+    uint8_t *h, *d;
+    if (!upd.empty()) {
+        if (staging_acquire(c, upd.size() * 4, &slot, &h, &d) != B200KV_OK) {
+            b200kv_seq_free(c, ns);
+            return B200KV_KO;
+        }
+        memcpy(h, upd.data(), upd.size() * 4);
+        if (staging_upload(c, slot, upd.size() * 4, stream) != B200KV_OK) {
+            b200kv_seq_free(c, ns);
+            return B200KV_KO;
+        }
+        int n = (int)(upd.size() / 2);
+        table_scatter_kernel<<<(n + 255) / 256, 256, 0, stream>>>(c->d_table, (const int32_t*)d, n);
+        staging_release(c, slot, stream);
+        for (size_t i = 0; i < src.pages.size(); i++)
+            B200KV_CUDA(cudaMemcpyAsync(c->pool + (int64_t)dst.pages[i] * c->L.page_bytes,
+                                        c->pool + (int64_t)src.pages[i] * c->L.page_bytes, c->L.page_bytes,
+                                        cudaMemcpyDeviceToDevice, stream));
+    }
+    dst.len = src.len;
+    *new_seq_out = ns;
+    return B200KV_OK;
+}
+
+int b200kv_check(b200kv_cache* c, void* stream) {
+    if (!c) return fail("null cache");
+    DeviceGuard guard(c->cfg.device);
+    B200KV_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    int st = 0;
+    B200KV_CUDA(cudaMemcpy(&st, c->d_status, sizeof(int), cudaMemcpyDeviceToHost));
+    if (st) {
+        int zero = 0;
+        cudaMemcpy(c->d_status, &zero, sizeof(int), cudaMemcpyHostToDevice);
+        return fail("device status %d:%s%s", st, (st & STATUS_PAGE_OOB) ? " page index out of range" : "",
+                    (st & STATUS_WAIT_EXPIRED) ? " a bounded wait expired" : "");
+    }
+    return B200KV_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,203 @@
+// Shared definitions of the b200kv kernels: page layout, element conversion, bulk-copy helpers.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/b200kv.h"
+
+namespace b200kv {
+
+// A page holds PAGE_TOKENS consecutive tokens of every kv head, K and V.
+constexpr int PAGE_TOKENS = 64;
+
+// ---- page layout ---------------------------------------------------------------------------
+// page   = [Hkv][K chunk, V chunk]            (V chunk absent when the cache has no values)
+// chunk  = data region (PAGE_TOKENS rows of ROW_BYTES) followed, for the block-quantised
+//          formats, by PAGE_TOKENS x (D/32) f16 scales in token order.
+// A row is the natural byte string of one token-head: D elements (f32 / f16 / bf16), D int8
+// codes (Q8_1) or D/32 blocks of 16 nibble bytes (Q4_0, GGML order).  The data region is cut
+// into column slabs ("planes") 128 bytes wide (or ROW_BYTES if smaller); inside a plane the
+// bytes are linear in (token, byte) with address bits [4,7) XOR-ed with bits [7,10): the
+// 128-byte swizzle that both shared-memory ldmatrix/LDS.128 readers and tcgen05 K-major /
+// MN-major operand tiles want.  Because whole chunks are contiguous in HBM, one untiled
+// cp.async.bulk brings a chunk into shared memory already in that arrangement.
+struct Layout {
+    int fmt, D, Hkv, has_v;
+    int row_bytes;    // bytes of one token-head row in the data region
+    int plane_w;      // min(row_bytes, 128)
+    int data_bytes;   // PAGE_TOKENS * row_bytes
+    int scale_bytes;  // PAGE_TOKENS * (D/32) * 2 for Q8_1 / Q4_0, else 0
+    int chunk_bytes;  // data_bytes + scale_bytes
+    int64_t page_bytes;
+};
+
+__host__ __device__ inline int fmt_row_bytes(int fmt, int D) {
+    switch (fmt) {
+        case B200KV_FMT_F32: return D * 4;
+        case B200KV_FMT_F16:
+        case B200KV_FMT_BF16: return D * 2;
+        case B200KV_FMT_Q8_1: return D;
+        case B200KV_FMT_Q4_0: return D / 2;
+        default: return 0;
+    }
+}
+__host__ __device__ inline bool fmt_is_block_quant(int fmt) { return fmt == B200KV_FMT_Q8_1 || fmt == B200KV_FMT_Q4_0; }
+
+inline Layout make_layout(int fmt, int D, int Hkv, int has_v) {
+    Layout L;
+    L.fmt = fmt;
+    L.D = D;
+    L.Hkv = Hkv;
+    L.has_v = has_v;
+    L.row_bytes = fmt_row_bytes(fmt, D);
+    L.plane_w = L.row_bytes < 128 ? L.row_bytes : 128;
+    L.data_bytes = PAGE_TOKENS * L.row_bytes;
+    L.scale_bytes = fmt_is_block_quant(fmt) ? PAGE_TOKENS * (D / 32) * 2 : 0;
+    L.chunk_bytes = L.data_bytes + L.scale_bytes;
+    L.page_bytes = (int64_t)Hkv * (has_v ? 2 : 1) * L.chunk_bytes;
+    return L;
+}
+
+// Byte offset inside a chunk's data region of row byte `rb` of token slot `t`.
+__host__ __device__ inline uint32_t chunk_addr(int plane_w, int t, int rb) {
+    uint32_t plane = (uint32_t)rb / (uint32_t)plane_w;
+    uint32_t lin = (uint32_t)t * (uint32_t)plane_w + (uint32_t)rb % (uint32_t)plane_w;
+    return plane * (uint32_t)(PAGE_TOKENS * plane_w) + (lin ^ (((lin >> 7) & 7u) << 4));
+}
+
+// Channel index of element e of the piece that starts at row byte rb (piece_bytes long).
+// Q4_0 rows are GGML blocks: byte j of block b holds channel 32b+j (low nibble) and 32b+16+j
+// (high nibble); a piece yields its low-nibble elements first, then the high-nibble ones.
+template <int FMT>
+__host__ __device__ inline int row_channel(int rb, int e, int piece_bytes) {
+    if (FMT == B200KV_FMT_F32) return rb / 4 + e;
+    if (FMT == B200KV_FMT_F16 || FMT == B200KV_FMT_BF16) return rb / 2 + e;
+    if (FMT == B200KV_FMT_Q8_1) return rb + e;
+    int b = rb / 16, j0 = rb % 16;
+    return e < piece_bytes ? b * 32 + j0 + e : b * 32 + 16 + j0 + (e - piece_bytes);
+}
+
+// Elements held by `bytes` bytes of a row.
+template <int FMT>
+__host__ __device__ constexpr int elems_in_bytes(int bytes) {
+    return FMT == B200KV_FMT_F32 ? bytes / 4
+         : (FMT == B200KV_FMT_F16 || FMT == B200KV_FMT_BF16) ? bytes / 2
+         : FMT == B200KV_FMT_Q8_1 ? bytes
+                                  : bytes * 2;
+}
+
+// ---- element conversion ------------------------------------------------------------------------
+__device__ inline float ld_as_f32(const void* p, int dtype, int64_t i) {
+    if (dtype == B200KV_F32) return ((const float*)p)[i];
+    if (dtype == B200KV_F16) return __half2float(((const __half*)p)[i]);
+    return __bfloat162float(((const __nv_bfloat16*)p)[i]);
+}
+__device__ inline void st_from_f32(void* p, int dtype, int64_t i, float v) {
+    if (dtype == B200KV_F32) ((float*)p)[i] = v;
+    else if (dtype == B200KV_F16) ((__half*)p)[i] = __float2half_rn(v);
+    else ((__nv_bfloat16*)p)[i] = __float2bfloat16_rn(v);
+}
+__host__ __device__ inline int dtype_size(int dtype) { return dtype == B200KV_F32 ? 4 : 2; }
+
+// Decodes one piece (PB bytes at p, 16-byte aligned when PB == 16) into floats.  Block-quantised
+// formats return the integer codes as floats (Q4_0: nibble - 8); the caller applies the scale.
+template <int FMT, int PB>
+__device__ inline void load_piece(const uint8_t* p, float* out) {
+    uint32_t w[4];
+    if (PB == 16) {
+        uint4 v = *(const uint4*)p;
+        w[0] = v.x, w[1] = v.y, w[2] = v.z, w[3] = v.w;
+    } else if (PB == 8) {
+        uint2 v = *(const uint2*)p;
+        w[0] = v.x, w[1] = v.y;
+    } else if (PB == 4) {
+        w[0] = *(const uint32_t*)p;
+    } else {
+        w[0] = *(const uint16_t*)p;
+    }
+    if (FMT == B200KV_FMT_F32) {
+#pragma unroll
+        for (int i = 0; i < PB / 4; i++) out[i] = __uint_as_float(w[i]);
+    } else if (FMT == B200KV_FMT_F16) {
+#pragma unroll
+        for (int i = 0; i < PB / 4; i++) {
+            float2 f = __half22float2(*(const __half2*)&w[i]);
+            out[2 * i] = f.x, out[2 * i + 1] = f.y;
+        }
+    } else if (FMT == B200KV_FMT_BF16) {
+#pragma unroll
+        for (int i = 0; i < PB / 4; i++) {
+            out[2 * i] = __uint_as_float(w[i] << 16);
+            out[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    } else if (FMT == B200KV_FMT_Q8_1) {
+#pragma unroll
+        for (int b = 0; b < PB; b++) out[b] = (float)(int)(int8_t)(w[b / 4] >> (8 * (b % 4)));
+    } else {  // Q4_0: low nibbles of the PB bytes, then high nibbles
+#pragma unroll
+        for (int b = 0; b < PB; b++) {
+            uint32_t byte = (w[b / 4] >> (8 * (b % 4))) & 0xffu;
+            out[b] = (float)((int)(byte & 0xf) - 8);
+            out[PB + b] = (float)((int)(byte >> 4) - 8);
+        }
+    }
+}
+
+// ---- shared-memory barriers and bulk copies (sm_90+ PTX; no cluster multicast anywhere) -----
+__device__ inline uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ inline void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ inline void mbar_fence_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ inline void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ inline bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ inline uint64_t globaltimer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Waits for a barrier phase, giving up after ~1 s so that a copy that never lands cannot hang the GPU.
+__device__ inline bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    uint64_t t0 = globaltimer_ns();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 64; i++)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (globaltimer_ns() - t0 > 1000000000ull) return false;
+    }
+}
+// Untiled bulk copy global -> this CTA's shared memory; completion is counted in bytes on `bar`.
+// Both addresses 16-byte aligned, size a multiple of 16.
+__device__ inline void bulk_g2s(void* dst_smem, const void* src_gmem, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_u32(dst_smem)),
+                 "l"(__cvta_generic_to_global(src_gmem)), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+
+// Device status word bits.
+constexpr int STATUS_PAGE_OOB = 1;      // a page-table entry outside the pool
+constexpr int STATUS_WAIT_EXPIRED = 2;  // a bounded barrier wait gave up
+
+}  // namespace b200kv

@@ -1,0 +1,427 @@
+// Split-KV GQA decode attention over the paged cache (one new query per sequence), and the
+// second pass that combines the split partials.
+//
+// Replaces the decode use of cuda/src/kernels/cu/flash_attn.cu (`attention_tailq_*`: one CTA per
+// (batch, q-head), 1 of 64 MMA rows useful, every q-head of a GQA group re-streams the same K/V,
+// no split along the sequence).  Here one CTA owns a run of pages of one (sequence, kv head) for
+// ALL q-heads of the group, page chunks arrive by untiled bulk copies (cp.async.bulk) into a
+// shared-memory ring guarded by mbarriers, quantised pages are dequantised in registers, and the
+// softmax is reduced with warp shuffles.  Semantics: transformers/src/ops/flash_sdpa.rs:239-341
+// with S = 1 (causal masking is vacuous for the last position).
+#include <algorithm>
+#include <cmath>
+#include <vector>
+
+#include "internal.h"
+
+namespace b200kv {
+
+struct WorkItem {
+    int32_t trow;        // page-table row of the sequence
+    int32_t len;         // cached length of the sequence
+    int32_t page_begin;  // first page of this split
+    int32_t n_pages;     // pages in this split
+    int32_t batch;       // batch entry
+    int32_t split;       // split index inside the batch entry
+    int32_t pad0, pad1;
+};
+
+struct DecodeParams {
+    const uint8_t* pool;
+    const int32_t* table;
+    const WorkItem* items;
+    int* status;
+    const void* q;
+    int64_t qb, qh;  // q strides {batch, head} in elements
+    float* part_o;   // [item][Hkv][G][D]   unnormalised partial outputs
+    float* part_ml;  // [item][Hkv][G][2]   running max, running sum
+    int64_t page_bytes;
+    int32_t n_pages, max_pages_per_seq, Hkv, G, dtype;
+    float scale;
+};
+
+template <int FMT, int D>
+struct Geo {
+    static constexpr int ROW = FMT == B200KV_FMT_F32 ? D * 4
+                             : (FMT == B200KV_FMT_F16 || FMT == B200KV_FMT_BF16) ? D * 2
+                             : FMT == B200KV_FMT_Q8_1 ? D
+                                                      : D / 2;
+    static constexpr bool QUANT = FMT == B200KV_FMT_Q8_1 || FMT == B200KV_FMT_Q4_0;
+    static constexpr int PW = ROW < 128 ? ROW : 128;
+    static constexpr int DATA = PAGE_TOKENS * ROW;
+    static constexpr int SCALES = QUANT ? PAGE_TOKENS * (D / 32) * 2 : 0;
+    static constexpr int CHUNK = DATA + SCALES;
+    static constexpr int STAGE = 2 * CHUNK;  // K chunk then V chunk, adjacent in the page
+    static constexpr int NS_RAW = 98304 / STAGE;
+    static constexpr int NS = NS_RAW < 2 ? 2 : (NS_RAW > 4 ? 4 : NS_RAW);
+    // score phase: 8 lanes share a token, each reads LB bytes of its row in pieces of PB bytes
+    static constexpr int LB = ROW / 8;
+    static constexpr int PB = LB < 16 ? LB : 16;
+    static constexpr int NPC = LB / PB;
+    static constexpr int EPP = elems_in_bytes<FMT>(PB);
+    static constexpr int EPL = NPC * EPP;  // = D / 8 channels per lane
+    // value phase: 16 threads share a token
+    static constexpr int TB = ROW / 16;
+    static constexpr int PB2 = TB < 16 ? TB : 16;
+    static constexpr int NPC2 = TB / PB2;
+    static constexpr int EPP2 = elems_in_bytes<FMT>(PB2);
+    static constexpr int CPT = NPC2 * EPP2;  // = D / 16 channels per thread
+};
+
+template <int GT>
+__host__ __device__ constexpr size_t decode_tail_bytes() {
+    // scores [GT][64] + probabilities [64][GT] + alpha [GT] + (m, l) [GT][2] + barriers
+    return (size_t)(GT * 64 + 64 * GT + GT + 2 * GT) * 4 + 16 + 4 * 8;
+}
+
+__device__ inline float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ inline float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+template <int FMT, int D, int GT>
+__global__ void __launch_bounds__(128) decode_kernel(DecodeParams p) {
+    using Gm = Geo<FMT, D>;
+    const bool PRECISE = p.dtype == B200KV_F32;  // f32 callers get expf, 16-bit callers the fast exponential
+    constexpr int NS = Gm::NS;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* stages = (uint8_t*)(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
+    float* sc = (float*)(stages + (size_t)NS * Gm::STAGE);  // [GT][64]
+    float* pT = sc + GT * 64;                                // [64][GT]
+    float* alpha_s = pT + 64 * GT;                           // [GT]
+    float* ml_s = alpha_s + GT;                              // [GT][2]
+    uint64_t* bars = (uint64_t*)(((uintptr_t)(ml_s + 2 * GT) + 15) & ~(uintptr_t)15);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int sub = lane & 7, tl = lane >> 3;
+    const int tg = tid >> 4, cu = tid & 15;
+    const WorkItem w = p.items[blockIdx.x];
+    const int kvh = blockIdx.y;
+    const int g0 = blockIdx.z * GT;
+    const int n_tiles = w.n_pages;
+
+    auto issue = [&](int i) {  // thread 0 only
+        int st = i % NS;
+        int32_t pg = p.table[(int64_t)w.trow * p.max_pages_per_seq + w.page_begin + i];
+        if (pg < 0 || pg >= p.n_pages) {
+            atomicOr(p.status, STATUS_PAGE_OOB);
+            pg = 0;  // keep the barrier protocol going; the result is flagged invalid
+        }
+        const uint8_t* src = p.pool + (int64_t)pg * p.page_bytes + (int64_t)kvh * Gm::STAGE;
+        mbar_expect_tx(&bars[st], Gm::STAGE);
+        bulk_g2s(stages + (size_t)st * Gm::STAGE, src, Gm::STAGE, &bars[st]);
+    };
+
+    if (tid == 0) {
+        for (int s = 0; s < NS; s++) mbar_init(&bars[s], 1);
+        mbar_fence_init();
+    }
+    __syncthreads();
+    if (tid == 0)
+        for (int i = 0; i < NS && i < n_tiles; i++) issue(i);
+
+    // the query rows of this group, as f32 registers laid out like the pieces each lane reads
+    float qr[GT][Gm::EPL];
+#pragma unroll
+    for (int g = 0; g < GT; g++) {
+        int head = kvh * p.G + min(g0 + g, p.G - 1);
+        const int64_t base = (int64_t)w.batch * p.qb + (int64_t)head * p.qh;
+#pragma unroll
+        for (int pc = 0; pc < Gm::NPC; pc++) {
+            int rb = pc * (8 * Gm::PB) + sub * Gm::PB;
+#pragma unroll
+            for (int e = 0; e < Gm::EPP; e++)
+                qr[g][pc * Gm::EPP + e] = ld_as_f32(p.q, p.dtype, base + row_channel<FMT>(rb, e, Gm::PB));
+        }
+    }
+
+    float m_run = -INFINITY, l_run = 0.f;  // live in warp g (< GT), uniform over its lanes
+    float acc[GT][Gm::CPT];
+#pragma unroll
+    for (int g = 0; g < GT; g++)
+#pragma unroll
+        for (int e = 0; e < Gm::CPT; e++) acc[g][e] = 0.f;
+    bool failed = false;
+
+    for (int i = 0; i < n_tiles; i++) {
+        const int st = i % NS;
+        const bool ok = mbar_wait_bounded(&bars[st], (uint32_t)((i / NS) & 1));
+        if (__syncthreads_or(!ok)) {
+            if (tid == 0) atomicOr(p.status, STATUS_WAIT_EXPIRED);
+            failed = true;
+            break;
+        }
+        const uint8_t* Ks = stages + (size_t)st * Gm::STAGE;
+        const uint8_t* Vs = Ks + Gm::CHUNK;
+        const int n_valid = min(PAGE_TOKENS, w.len - (w.page_begin + i) * PAGE_TOKENS);
+
+        // ---- scores: warp w takes tokens [16w, 16w+16), 4 at a time, 8 lanes per token ----
+#pragma unroll
+        for (int it = 0; it < 4; it++) {
+            const int t = warp * 16 + it * 4 + tl;
+            float dot[GT];
+#pragma unroll
+            for (int g = 0; g < GT; g++) dot[g] = 0.f;
+#pragma unroll
+            for (int pc = 0; pc < Gm::NPC; pc++) {
+                const int rb = pc * (8 * Gm::PB) + sub * Gm::PB;
+                float vals[Gm::EPP];
+                load_piece<FMT, Gm::PB>(Ks + chunk_addr(Gm::PW, t, rb), vals);
+                if (Gm::QUANT) {
+                    const int blk = (FMT == B200KV_FMT_Q8_1 ? rb : rb * 2) / 32;
+                    const float d = __half2float(((const __half*)(Ks + Gm::DATA))[t * (D / 32) + blk]);
+#pragma unroll
+                    for (int g = 0; g < GT; g++) {
+                        float part = 0.f;
+#pragma unroll
+                        for (int e = 0; e < Gm::EPP; e++) part = fmaf(qr[g][pc * Gm::EPP + e], vals[e], part);
+                        dot[g] = fmaf(d, part, dot[g]);
+                    }
+                } else {
+#pragma unroll
+                    for (int g = 0; g < GT; g++)
+#pragma unroll
+                        for (int e = 0; e < Gm::EPP; e++) dot[g] = fmaf(qr[g][pc * Gm::EPP + e], vals[e], dot[g]);
+                }
+            }
+#pragma unroll
+            for (int g = 0; g < GT; g++) {
+                dot[g] += __shfl_xor_sync(0xffffffffu, dot[g], 1);
+                dot[g] += __shfl_xor_sync(0xffffffffu, dot[g], 2);
+                dot[g] += __shfl_xor_sync(0xffffffffu, dot[g], 4);
+            }
+            float mine = dot[0];
+#pragma unroll
+            for (int g = 1; g < GT; g++)
+                if (sub == g) mine = dot[g];
+            if (sub < GT) sc[sub * 64 + t] = mine * p.scale;
+        }
+        __syncthreads();
+
+        // ---- online softmax: warp g owns q-head g of the group ----
+        if (warp < GT) {
+            float s0 = lane < n_valid ? sc[warp * 64 + lane] : -INFINITY;
+            float s1 = lane + 32 < n_valid ? sc[warp * 64 + lane + 32] : -INFINITY;
+            float m_new = fmaxf(m_run, warp_max(fmaxf(s0, s1)));
+            float a, p0, p1;
+            if (PRECISE) {
+                a = expf(m_run - m_new), p0 = expf(s0 - m_new), p1 = expf(s1 - m_new);
+            } else {
+                a = __expf(m_run - m_new), p0 = __expf(s0 - m_new), p1 = __expf(s1 - m_new);
+            }
+            l_run = l_run * a + warp_sum(p0 + p1);
+            m_run = m_new;
+            pT[lane * GT + warp] = p0;
+            pT[(lane + 32) * GT + warp] = p1;
+            if (lane == 0) alpha_s[warp] = a;
+        }
+        __syncthreads();
+
+        // ---- values: 16 threads per token, 8 tokens at a time; each thread keeps D/16 channels ----
+        {
+            float al[GT];
+            bool rescale = false;
+#pragma unroll
+            for (int g = 0; g < GT; g++) {
+                al[g] = alpha_s[g];
+                rescale |= al[g] != 1.f;
+            }
+            if (rescale) {
+#pragma unroll
+                for (int g = 0; g < GT; g++)
+#pragma unroll
+                    for (int e = 0; e < Gm::CPT; e++) acc[g][e] *= al[g];
+            }
+#pragma unroll 2
+            for (int tt = 0; tt < 8; tt++) {
+                const int t = tt * 8 + tg;
+                if (t < n_valid) {
+                    float pr[GT];
+#pragma unroll
+                    for (int g = 0; g < GT; g++) pr[g] = pT[t * GT + g];
+#pragma unroll
+                    for (int pc = 0; pc < Gm::NPC2; pc++) {
+                        const int rb = pc * (16 * Gm::PB2) + cu * Gm::PB2;
+                        float vals[Gm::EPP2];
+                        load_piece<FMT, Gm::PB2>(Vs + chunk_addr(Gm::PW, t, rb), vals);
+                        float d = 1.f;
+                        if (Gm::QUANT) {
+                            const int blk = (FMT == B200KV_FMT_Q8_1 ? rb : rb * 2) / 32;
+                            d = __half2float(((const __half*)(Vs + Gm::DATA))[t * (D / 32) + blk]);
+                        }
+#pragma unroll
+                        for (int g = 0; g < GT; g++) {
+                            const float pd = Gm::QUANT ? pr[g] * d : pr[g];
+#pragma unroll
+                            for (int e = 0; e < Gm::EPP2; e++)
+                                acc[g][pc * Gm::EPP2 + e] = fmaf(pd, vals[e], acc[g][pc * Gm::EPP2 + e]);
+                        }
+                    }
+                }
+            }
+        }
+        __syncthreads();  // every thread is done with stage st
+        if (tid == 0 && i + NS < n_tiles) issue(i + NS);
+    }
+
+    // ---- write the partial of this split ----
+    const int64_t pbase = ((int64_t)blockIdx.x * p.Hkv + kvh) * p.G;
+    if (failed) {
+        // outstanding copies (if any) are left to land in this CTA's shared memory, which nothing
+        // reads any more; publish an empty partial so the combine pass ignores this split
+        for (int idx = tid; idx < GT * D; idx += 128) {
+            int g = idx / D;
+            if (g0 + g < p.G) p.part_o[(pbase + g0 + g) * D + idx % D] = 0.f;
+        }
+        if (tid < GT && g0 + tid < p.G) {
+            p.part_ml[(pbase + g0 + tid) * 2] = -INFINITY;
+            p.part_ml[(pbase + g0 + tid) * 2 + 1] = 0.f;
+        }
+        return;
+    }
+    if (warp < GT && lane == 0) {
+        ml_s[warp * 2] = m_run;
+        ml_s[warp * 2 + 1] = l_run;
+    }
+    float* red = (float*)stages;  // [8 token groups][GT][D]; all stages are consumed by now
+#pragma unroll
+    for (int g = 0; g < GT; g++)
+#pragma unroll
+        for (int pc = 0; pc < Gm::NPC2; pc++) {
+            const int rb = pc * (16 * Gm::PB2) + cu * Gm::PB2;
+#pragma unroll
+            for (int e = 0; e < Gm::EPP2; e++)
+                red[(tg * GT + g) * D + row_channel<FMT>(rb, e, Gm::PB2)] = acc[g][pc * Gm::EPP2 + e];
+        }
+    __syncthreads();
+    for (int idx = tid; idx < GT * D; idx += 128) {
+        const int g = idx / D, ch = idx % D;
+        float sum = 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; k++) sum += red[(k * GT + g) * D + ch];
+        if (g0 + g < p.G) p.part_o[(pbase + g0 + g) * D + ch] = sum;
+    }
+    if (tid < GT && g0 + tid < p.G) {
+        p.part_ml[(pbase + g0 + tid) * 2] = ml_s[tid * 2];
+        p.part_ml[(pbase + g0 + tid) * 2 + 1] = ml_s[tid * 2 + 1];
+    }
+}
+
+struct CombineParams {
+    const float* part_o;
+    const float* part_ml;
+    const int32_t* batch_info;  // per batch entry: {first item, item count}
+    void* out;
+    int64_t ob, oh;
+    int32_t Hkv, G, D, dtype;
+};
+
+// Second pass: out = sum_i e^{m_i - M} O_i / sum_i e^{m_i - M} l_i over the splits of one (sequence, q-head).
+__global__ void combine_kernel(CombineParams p) {
+    const int b = blockIdx.x, hq = blockIdx.y, ch = threadIdx.x;
+    const int kvh = hq / p.G, g = hq % p.G;
+    const int first = p.batch_info[2 * b], n = p.batch_info[2 * b + 1];
+    float M = -INFINITY;
+    for (int i = 0; i < n; i++) M = fmaxf(M, p.part_ml[(((int64_t)(first + i) * p.Hkv + kvh) * p.G + g) * 2]);
+    float num = 0.f, den = 0.f;
+    for (int i = 0; i < n; i++) {
+        const int64_t idx = ((int64_t)(first + i) * p.Hkv + kvh) * p.G + g;
+        const float wgt = expf(p.part_ml[idx * 2] - M);
+        den = fmaf(wgt, p.part_ml[idx * 2 + 1], den);
+        num = fmaf(wgt, p.part_o[idx * p.D + ch], num);
+    }
+    st_from_f32(p.out, p.dtype, (int64_t)b * p.ob + (int64_t)hq * p.oh + ch, num / den);
+}
+
+template <int FMT, int D, int GT>
+static int launch_decode_t(const DecodeParams& p, int n_items, cudaStream_t stream) {
+    using Gm = Geo<FMT, D>;
+    const size_t smem = 128 + (size_t)Gm::NS * Gm::STAGE + decode_tail_bytes<GT>();
+    B200KV_CUDA(cudaFuncSetAttribute(decode_kernel<FMT, D, GT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    dim3 grid(n_items, p.Hkv, (p.G + GT - 1) / GT);
+    decode_kernel<FMT, D, GT><<<grid, 128, smem, stream>>>(p);
+    B200KV_CUDA(cudaGetLastError());
+    return B200KV_OK;
+}
+
+template <int FMT>
+static int launch_decode_f(const DecodeParams& p, int D, int n_items, cudaStream_t stream) {
+    if (p.G == 1) return D == 128 ? launch_decode_t<FMT, 128, 1>(p, n_items, stream) : launch_decode_t<FMT, 64, 1>(p, n_items, stream);
+    return D == 128 ? launch_decode_t<FMT, 128, 4>(p, n_items, stream) : launch_decode_t<FMT, 64, 4>(p, n_items, stream);
+}
+
+int launch_decode(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t n_q_heads, const void* q,
+                  const int64_t* qs, void* out, const int64_t* os, int32_t dtype, float scale, cudaStream_t stream) {
+    const int Hkv = c->L.Hkv, D = c->L.D, G = n_q_heads / Hkv;
+    const int GT = G == 1 ? 1 : 4, nz = (G + GT - 1) / GT;
+    // ---- work list: split every sequence into runs of pages so that the grid covers the GPU many times ----
+    int64_t total_pages = 0;
+    for (int i = 0; i < n_seqs; i++) {
+        int64_t len = c->seqs[seqs[i]].len;
+        if (len <= 0) return fail("sequence %d is empty: nothing to attend to", seqs[i]);
+        total_pages += (len + PAGE_TOKENS - 1) / PAGE_TOKENS;
+    }
+    const int64_t target_ctas = 148 * 16;
+    const int64_t chunk = std::max<int64_t>(1, (total_pages * Hkv * nz + target_ctas - 1) / target_ctas);
+    std::vector<WorkItem> items;
+    std::vector<int32_t> info(2 * (size_t)n_seqs);
+    for (int i = 0; i < n_seqs; i++) {
+        const SeqState& s = c->seqs[seqs[i]];
+        const int pages = (int)((s.len + PAGE_TOKENS - 1) / PAGE_TOKENS);
+        int splits = (int)std::min<int64_t>(64, (pages + chunk - 1) / chunk);
+        info[2 * i] = (int32_t)items.size();
+        info[2 * i + 1] = splits;
+        int begin = 0;
+        for (int k = 0; k < splits; k++) {
+            int n = (pages - begin + (splits - k) - 1) / (splits - k);  // even split of what is left
+            items.push_back(WorkItem{seqs[i], (int32_t)s.len, begin, n, i, k, 0, 0});
+            begin += n;
+        }
+    }
+    const size_t items_bytes = items.size() * sizeof(WorkItem);
+    const size_t desc_bytes = items_bytes + info.size() * 4;
+    const size_t n_part = items.size() * (size_t)Hkv * G;
+    const size_t ws_need = n_part * (D + 2) * sizeof(float);
+    if (ensure_workspace(c, ws_need) != B200KV_OK) return B200KV_KO;
+    int slot;
+    uint8_t *h, *d;
+    if (staging_acquire(c, desc_bytes, &slot, &h, &d) != B200KV_OK) return B200KV_KO;
+    memcpy(h, items.data(), items_bytes);
+    memcpy(h + items_bytes, info.data(), info.size() * 4);
+    if (staging_upload(c, slot, desc_bytes, stream) != B200KV_OK) return B200KV_KO;
+
+    DecodeParams p{};
+    p.pool = c->pool, p.table = c->d_table, p.items = (const WorkItem*)d, p.status = c->d_status;
+    p.q = q, p.qb = qs[0], p.qh = qs[1];
+    p.part_o = (float*)c->ws;
+    p.part_ml = p.part_o + n_part * D;
+    p.page_bytes = c->L.page_bytes, p.n_pages = (int32_t)c->n_pages, p.max_pages_per_seq = c->max_pages_per_seq;
+    p.Hkv = Hkv, p.G = G, p.dtype = dtype, p.scale = scale;
+    int rc;
+    switch (c->L.fmt) {
+        case B200KV_FMT_F32: rc = launch_decode_f<B200KV_FMT_F32>(p, D, (int)items.size(), stream); break;
+        case B200KV_FMT_F16: rc = launch_decode_f<B200KV_FMT_F16>(p, D, (int)items.size(), stream); break;
+        case B200KV_FMT_BF16: rc = launch_decode_f<B200KV_FMT_BF16>(p, D, (int)items.size(), stream); break;
+        case B200KV_FMT_Q8_1: rc = launch_decode_f<B200KV_FMT_Q8_1>(p, D, (int)items.size(), stream); break;
+        case B200KV_FMT_Q4_0: rc = launch_decode_f<B200KV_FMT_Q4_0>(p, D, (int)items.size(), stream); break;
+        default: rc = fail("format %d has no decode kernel", c->L.fmt);
+    }
+    if (rc == B200KV_OK) {
+        CombineParams cp{};
+        cp.part_o = p.part_o, cp.part_ml = p.part_ml, cp.batch_info = (const int32_t*)(d + items_bytes);
+        cp.out = out, cp.ob = os[0], cp.oh = os[1];
+        cp.Hkv = Hkv, cp.G = G, cp.D = D, cp.dtype = dtype;
+        combine_kernel<<<dim3(n_seqs, n_q_heads), D, 0, stream>>>(cp);
+        if (cudaGetLastError() != cudaSuccess) rc = fail("combine launch failed");
+    }
+    staging_release(c, slot, stream);
+    return rc;
+}
+
+}  // namespace b200kv

@@ -1,0 +1,95 @@
+// Host-side state of a cache handle and helpers shared by the translation units.
+#pragma once
+#include <cstdarg>
+#include <cstdio>
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+
+namespace b200kv {
+
+// Thread-local message of the last failure (the analogue of tract's LAST_ERROR, api/ffi/src/lib.rs:27-60).
+std::string& last_error();
+int fail(const char* fmt, ...) __attribute__((format(printf, 1, 2)));
+
+#define B200KV_CUDA(call)                                                                          \
+    do {                                                                                           \
+        cudaError_t e__ = (call);                                                                  \
+        if (e__ != cudaSuccess) return ::b200kv::fail("%s failed: %s", #call, cudaGetErrorString(e__)); \
+    } while (0)
+
+struct DeviceGuard {
+    int prev = -1;
+    bool switched = false;
+    explicit DeviceGuard(int dev) {
+        if (cudaGetDevice(&prev) == cudaSuccess && prev != dev) switched = cudaSetDevice(dev) == cudaSuccess;
+    }
+    ~DeviceGuard() {
+        if (switched) cudaSetDevice(prev);
+    }
+};
+
+struct SeqState {
+    bool live = false;
+    int64_t len = 0;
+    std::vector<int32_t> pages;
+};
+
+// Ring of descriptor slots: each call that needs per-call metadata on the device writes it into a
+// pinned host slot, enqueues one H2D copy into the matching device slot and records an event after
+// the kernels that read it, so a slot is never rewritten while the GPU may still use it.
+struct Staging {
+    static constexpr int SLOTS = 16;
+    size_t slot_bytes = 0;
+    uint8_t* host = nullptr;
+    uint8_t* dev = nullptr;
+    cudaEvent_t ev[SLOTS] = {};
+    bool used[SLOTS] = {};
+    int next = 0;
+};
+
+}  // namespace b200kv
+
+struct b200kv_cache {
+    b200kv_config cfg;
+    b200kv::Layout L;
+    int64_t n_pages = 0;
+    int max_pages_per_seq = 0;
+    uint8_t* pool = nullptr;
+    int32_t* d_table = nullptr;  // [max_seqs][max_pages_per_seq] page ids
+    int* d_status = nullptr;
+    std::vector<int32_t> free_pages;
+    std::vector<b200kv::SeqState> seqs;
+    b200kv::Staging st;
+    uint8_t* ws = nullptr;  // scratch owned by the cache: split-KV partials, prefill staging
+    size_t ws_bytes = 0;
+};
+
+namespace b200kv {
+
+// Reserves a descriptor slot (blocking only if the ring wrapped onto a slot still in flight).
+int staging_acquire(b200kv_cache* c, size_t bytes, int* slot, uint8_t** host, uint8_t** dev);
+// Copies the first `bytes` of the slot to the device on `stream`.
+int staging_upload(b200kv_cache* c, int slot, size_t bytes, cudaStream_t stream);
+// Marks the slot as consumed by everything enqueued on `stream` so far.
+int staging_release(b200kv_cache* c, int slot, cudaStream_t stream);
+// Makes sure the cache-owned scratch holds at least `bytes`.
+int ensure_workspace(b200kv_cache* c, size_t bytes);
+
+int validate_seqs(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs);
+
+// decode.cu
+int launch_decode(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t n_q_heads, const void* q,
+                  const int64_t* q_strides, void* out, const int64_t* out_strides, int32_t dtype, float scale,
+                  cudaStream_t stream);
+// sdpa_dense.cu
+int launch_sdpa_dense(const void* q, const int64_t* qs, const void* k, const int64_t* ks, const void* v,
+                      const int64_t* vs, const void* mask, const int64_t* ms, int mask_dtype, void* out,
+                      const int64_t* os, int B, int Hq, int Hkv, int S, int T, int D, int dtype, int kv_dtype,
+                      float scale, int causal, cudaStream_t stream);
+// cache.cu
+int launch_export(b200kv_cache* c, int32_t seq, void* k_out, const int64_t* ks, void* v_out, const int64_t* vs,
+                  int32_t dtype, cudaStream_t stream);
+
+}  // namespace b200kv
