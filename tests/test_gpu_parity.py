@@ -146,13 +146,16 @@ def test_quantise_on_append_bit_exact(kv, fmt, in_name, D):
 # ---- decode attention ------------------------------------------------------------------------------
 
 def oracle_cache_view(fmt, X, io_name):
-    """What the reference's attention sees for a cache in format `fmt`: the concatenated tensor
-    itself, or the dequantised f32 cache cast back to the model dtype (quant_dyn_kv_cache.rs:493)."""
+    """What the fused cache + attention op attends over: the concatenated tensor itself, or, for a
+    quantised cache, the dequantised f32 values (the reference's fused ops work in f32 internally:
+    inplace_kv_cache.rs:201-206, kv_quant.rs:246-349; only the op OUTPUT is cast back to the model
+    dtype).  The unfused chain, whose cache output is cast to the model dtype first
+    (quant_dyn_kv_cache.rs:493), is what b200kv_export reproduces."""
     if fmt == "q8_1":
         s, _, c = oracle.q8_1_quant(X)
-        return oracle.q8_1_dequant(s, c).astype(np_dtype(io_name))
+        return oracle.q8_1_dequant(s, c)
     if fmt == "q4_0":
-        return oracle.q4_0_dequant(*oracle.q4_0_quant(X)).astype(np_dtype(io_name))
+        return oracle.q4_0_dequant(*oracle.q4_0_quant(X))
     return X
 
 
