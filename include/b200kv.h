@@ -138,6 +138,14 @@ int b200kv_fork(b200kv_cache* cache, int32_t seq, int32_t* new_seq_out, void* st
  * that expired).  Synchronises the stream.  Returns KO and sets the message if the word is non-zero. */
 int b200kv_check(b200kv_cache* cache, void* stream);
 
+/* Per-launch timing, off by default.  When enabled, every kernel launched for this cache is bracketed by a
+ * CUDA event pair on the caller's stream (what tract-cuda's TractCudaStream does for its profiler,
+ * cuda/src/context.rs:364-453).  b200kv_profile_read waits for the recorded launches, returns up to
+ * max_records (kernel id, milliseconds) pairs in launch order and clears the log.  Kernel ids:
+ * 0 page-table update, 1 append, 2 decode, 3 split combine, 4 export, 5 generic sdpa, 6 prefill. */
+int b200kv_profile(b200kv_cache* cache, int32_t enable);
+int b200kv_profile_read(b200kv_cache* cache, int32_t max_records, int32_t* kernel_ids, float* ms, int32_t* n_out);
+
 /* ---- lone Sdpa (transformers/src/ops/sdpa.rs:84-89; replaces convert_sdpa_to_cuda_flash_attn +
  *      CudaFlashAttention for an Sdpa node that is not fused with a cache) ----
  * q [B, Hq, S, D], k / v [B, Hkv, T, D], out [B, Hq, S, D]; strides {batch, head, row} in elements.

@@ -21,8 +21,10 @@ FORMATS = {"f32": FMT_F32, "f16": FMT_F16, "bf16": FMT_BF16, "q8_1": FMT_Q8_1, "
 EXPORTS = [
     "b200kv_last_error", "b200kv_version", "b200kv_create", "b200kv_destroy", "b200kv_seq_new", "b200kv_seq_free",
     "b200kv_seq_len", "b200kv_free_pages", "b200kv_page_bytes", "b200kv_append", "b200kv_attend", "b200kv_export",
-    "b200kv_export_codes", "b200kv_truncate", "b200kv_fork", "b200kv_check", "b200kv_sdpa",
+    "b200kv_export_codes", "b200kv_truncate", "b200kv_fork", "b200kv_check", "b200kv_sdpa", "b200kv_profile",
+    "b200kv_profile_read",
 ]
+KERNEL_NAMES = {0: "table_scatter", 1: "append", 2: "decode", 3: "combine", 4: "export", 5: "sdpa_dense", 6: "prefill"}
 
 
 class B200KvError(RuntimeError):
@@ -65,6 +67,8 @@ def lib():
         L.b200kv_truncate.argtypes = [vp, i32, i64]
         L.b200kv_fork.argtypes = [vp, i32, i32p, vp]
         L.b200kv_check.argtypes = [vp, vp]
+        L.b200kv_profile.argtypes = [vp, i32]
+        L.b200kv_profile_read.argtypes = [vp, i32, i32p, C.POINTER(C.c_float), i32p]
         L.b200kv_sdpa.argtypes = [vp, i64p, vp, i64p, vp, i64p, vp, i64p, i32, vp, i64p, i32, i32, i32, i32, i32, i32,
                                   i32, C.c_float, i32, vp]
         _lib = L
@@ -202,6 +206,17 @@ class KvCache:
 
     def check(self):
         _ck(lib().b200kv_check(self._h, _stream()))
+
+    def profile(self, enable=True):
+        _ck(lib().b200kv_profile(self._h, int(enable)))
+
+    def profile_read(self, max_records=65536):
+        """[(kernel name, milliseconds)] of the launches recorded since the last read."""
+        ids = (C.c_int32 * max_records)()
+        ms = (C.c_float * max_records)()
+        n = C.c_int32()
+        _ck(lib().b200kv_profile_read(self._h, max_records, ids, ms, C.byref(n)))
+        return [(KERNEL_NAMES.get(ids[i], str(ids[i])), ms[i]) for i in range(n.value)]
 
 
 def sdpa(q, k, v, mask=None, scale=None, causal=False):

@@ -46,6 +46,7 @@ extern "C" int b200kv_attend(b200kv_cache* c, int32_t n_seqs, const int32_t* seq
         const int esz = dtype_size(dtype);
         const void* qi = (const uint8_t*)q + (int64_t)i * q_strides[0] * esz;
         void* oi = (uint8_t*)out + (int64_t)i * out_strides[0] * esz;
+        ProfScope ps(c, K_DENSE, stream);
         if (launch_sdpa_dense(qi, q_strides, kbuf, ks, vbuf, ks, nullptr, nullptr, 0, oi, out_strides, 1, n_q_heads, Hkv,
                               n_new, (int)T, D, dtype, kv_dtype, scale, causal, stream) != B200KV_OK)
             return B200KV_KO;

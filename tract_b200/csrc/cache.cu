@@ -320,6 +320,7 @@ int launch_export(b200kv_cache* c, int32_t seq, void* k_out, const int64_t* ks, 
     p.dtype = dtype, p.has_v = c->L.has_v;
     int64_t threads = (int64_t)p.H * p.len * p.units;
     dim3 grid((unsigned)((threads + 255) / 256), v_out ? 2 : 1);
+    ProfScope ps(c, K_EXPORT, stream);
     switch (c->L.fmt) {
         case B200KV_FMT_F32: export_kernel<B200KV_FMT_F32, 0><<<grid, 256, 0, stream>>>(p); break;
         case B200KV_FMT_F16: export_kernel<B200KV_FMT_F16, 0><<<grid, 256, 0, stream>>>(p); break;
@@ -400,6 +401,7 @@ int b200kv_destroy(b200kv_cache* c) {
     if (!c) return B200KV_OK;
     DeviceGuard guard(c->cfg.device);
     cudaDeviceSynchronize();
+    for (auto& r : c->prof) cudaEventDestroy(r.a), cudaEventDestroy(r.b);
     for (int i = 0; i < Staging::SLOTS; i++)
         if (c->st.ev[i]) cudaEventDestroy(c->st.ev[i]);
     if (c->st.host) cudaFreeHost(c->st.host);
@@ -500,6 +502,7 @@ int b200kv_append(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t 
     }
     if (!upd.empty()) {
         int n = (int)(upd.size() / 2);
+        ProfScope ps(c, K_SCATTER, stream);
         table_scatter_kernel<<<(n + 255) / 256, 256, 0, stream>>>(c->d_table, (const int32_t*)d + 2 * n_seqs, n);
     }
     AppendParams p{};
@@ -520,12 +523,15 @@ int b200kv_append(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t 
     };
     p.vec_ok = aligned(k_new, k_strides) && aligned(v_new, v_strides);
     const int n_kv = c->L.has_v ? 2 : 1;
-    switch (c->L.fmt) {
-        case B200KV_FMT_F32: launch_append_fmt<B200KV_FMT_F32>(p, n_kv, stream); break;
-        case B200KV_FMT_F16: launch_append_fmt<B200KV_FMT_F16>(p, n_kv, stream); break;
-        case B200KV_FMT_BF16: launch_append_fmt<B200KV_FMT_BF16>(p, n_kv, stream); break;
-        case B200KV_FMT_Q8_1: launch_append_fmt<B200KV_FMT_Q8_1>(p, n_kv, stream); break;
-        case B200KV_FMT_Q4_0: launch_append_fmt<B200KV_FMT_Q4_0>(p, n_kv, stream); break;
+    {
+        ProfScope ps(c, K_APPEND, stream);
+        switch (c->L.fmt) {
+            case B200KV_FMT_F32: launch_append_fmt<B200KV_FMT_F32>(p, n_kv, stream); break;
+            case B200KV_FMT_F16: launch_append_fmt<B200KV_FMT_F16>(p, n_kv, stream); break;
+            case B200KV_FMT_BF16: launch_append_fmt<B200KV_FMT_BF16>(p, n_kv, stream); break;
+            case B200KV_FMT_Q8_1: launch_append_fmt<B200KV_FMT_Q8_1>(p, n_kv, stream); break;
+            case B200KV_FMT_Q4_0: launch_append_fmt<B200KV_FMT_Q4_0>(p, n_kv, stream); break;
+        }
     }
     cudaError_t e = cudaGetLastError();
     staging_release(c, slot, stream);
@@ -621,6 +627,33 @@ int b200kv_fork(b200kv_cache* c, int32_t seq, int32_t* new_seq_out, void* stream
     }
     dst.len = src.len;
     *new_seq_out = ns;
+    return B200KV_OK;
+}
+
+int b200kv_profile(b200kv_cache* c, int32_t enable) {
+    if (!c) return fail("null cache");
+    c->prof_on = enable != 0;
+    return B200KV_OK;
+}
+
+int b200kv_profile_read(b200kv_cache* c, int32_t max_records, int32_t* kernel_ids, float* ms, int32_t* n_out) {
+    if (!c || !n_out) return fail("null argument");
+    DeviceGuard guard(c->cfg.device);
+    int n = 0;
+    for (auto& r : c->prof) {
+        float t = 0.f;
+        cudaError_t e = cudaEventSynchronize(r.b);
+        if (e == cudaSuccess) e = cudaEventElapsedTime(&t, r.a, r.b);
+        cudaEventDestroy(r.a);
+        cudaEventDestroy(r.b);
+        if (e != cudaSuccess) {
+            c->prof.clear();
+            return fail("reading a timing record failed: %s", cudaGetErrorString(e));
+        }
+        if (n < max_records && kernel_ids && ms) kernel_ids[n] = r.id, ms[n] = t, n++;
+    }
+    c->prof.clear();
+    *n_out = n;
     return B200KV_OK;
 }
 

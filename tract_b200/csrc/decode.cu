@@ -404,6 +404,8 @@ int launch_decode(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t 
     p.page_bytes = c->L.page_bytes, p.n_pages = (int32_t)c->n_pages, p.max_pages_per_seq = c->max_pages_per_seq;
     p.Hkv = Hkv, p.G = G, p.dtype = dtype, p.scale = scale;
     int rc;
+    {
+    ProfScope ps(c, K_DECODE, stream);
     switch (c->L.fmt) {
         case B200KV_FMT_F32: rc = launch_decode_f<B200KV_FMT_F32>(p, D, (int)items.size(), stream); break;
         case B200KV_FMT_F16: rc = launch_decode_f<B200KV_FMT_F16>(p, D, (int)items.size(), stream); break;
@@ -412,7 +414,9 @@ int launch_decode(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t 
         case B200KV_FMT_Q4_0: rc = launch_decode_f<B200KV_FMT_Q4_0>(p, D, (int)items.size(), stream); break;
         default: rc = fail("format %d has no decode kernel", c->L.fmt);
     }
+    }
     if (rc == B200KV_OK) {
+        ProfScope ps(c, K_COMBINE, stream);
         CombineParams cp{};
         cp.part_o = p.part_o, cp.part_ml = p.part_ml, cp.batch_info = (const int32_t*)(d + items_bytes);
         cp.out = out, cp.ob = os[0], cp.oh = os[1];

@@ -64,6 +64,14 @@ struct b200kv_cache {
     b200kv::Staging st;
     uint8_t* ws = nullptr;  // scratch owned by the cache: split-KV partials, prefill staging
     size_t ws_bytes = 0;
+    // optional per-launch timing (the analogue of tract-cuda's event pairs around every launch,
+    // cuda/src/context.rs:364-453): off by default
+    bool prof_on = false;
+    struct ProfRec {
+        int id;
+        cudaEvent_t a, b;
+    };
+    std::vector<ProfRec> prof;
 };
 
 namespace b200kv {
@@ -78,6 +86,29 @@ int staging_release(b200kv_cache* c, int slot, cudaStream_t stream);
 int ensure_workspace(b200kv_cache* c, size_t bytes);
 
 int validate_seqs(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs);
+
+// Kernel ids reported by b200kv_profile_read.
+enum { K_SCATTER = 0, K_APPEND = 1, K_DECODE = 2, K_COMBINE = 3, K_EXPORT = 4, K_DENSE = 5, K_PREFILL = 6 };
+
+// Brackets the launches made during its lifetime with an event pair when profiling is on.
+struct ProfScope {
+    b200kv_cache* c;
+    cudaStream_t stream;
+    b200kv_cache::ProfRec rec{};
+    bool live = false;
+    ProfScope(b200kv_cache* c_, int id, cudaStream_t s) : c(c_), stream(s) {
+        if (!c || !c->prof_on) return;
+        if (cudaEventCreate(&rec.a) != cudaSuccess || cudaEventCreate(&rec.b) != cudaSuccess) return;
+        rec.id = id;
+        cudaEventRecord(rec.a, stream);
+        live = true;
+    }
+    ~ProfScope() {
+        if (!live) return;
+        cudaEventRecord(rec.b, stream);
+        c->prof.push_back(rec);
+    }
+};
 
 // decode.cu
 int launch_decode(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t n_q_heads, const void* q,
