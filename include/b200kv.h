@@ -142,7 +142,9 @@ int b200kv_check(b200kv_cache* cache, void* stream);
  * CUDA event pair on the caller's stream (what tract-cuda's TractCudaStream does for its profiler,
  * cuda/src/context.rs:364-453).  b200kv_profile_read waits for the recorded launches, returns up to
  * max_records (kernel id, milliseconds) pairs in launch order and clears the log.  Kernel ids:
- * 0 page-table update, 1 append, 2 decode, 3 split combine, 4 export, 5 generic sdpa, 6 prefill. */
+ * 0 page-table update, 1 append, 2 decode, 3 split combine, 4 export, 5 generic sdpa, 6 prefill.
+ * `enable` is a bit set: bit 0 turns the timing on; bit 1 (a test hook) routes decode attention through the
+ * CUDA-core kernel even where the tensor-core kernel applies, so the two can be checked against each other. */
 int b200kv_profile(b200kv_cache* cache, int32_t enable);
 int b200kv_profile_read(b200kv_cache* cache, int32_t max_records, int32_t* kernel_ids, float* ms, int32_t* n_out);
 

@@ -7,7 +7,7 @@ import numpy as np
 import pytest
 
 import oracle
-from util import TOL, lcg_tensor, normal, normal_with_outliers, ramp, rel_err
+from util import TOL, lcg_tensor, normal, normal_with_outliers, ramp, rel_err, rel_err_bf16
 
 pytestmark = pytest.mark.gpu
 
@@ -36,6 +36,15 @@ def to_dev(a, name=None):
     if a.dtype == np.float32 or a.dtype == np.float16:
         return torch.from_numpy(np.ascontiguousarray(a)).cuda()
     return torch.from_numpy(np.ascontiguousarray(a).view(np.uint16).copy()).view(torch.bfloat16).cuda()
+
+
+def attn_err(out, io, q, k, v, **kw):
+    """Error of a GPU attention output against the oracle run on the same inputs (see util.rel_err_bf16)."""
+    if io == "bf16":
+        want = oracle.flash_sdpa(q.astype(np.float32), k.astype(np.float32), v.astype(np.float32), **kw)
+        return rel_err_bf16(to_np(out, io).astype(np.float32), want)
+    want = oracle.flash_sdpa(q, k, v, **kw)
+    return rel_err(to_np(out, io).astype(np.float32), want.astype(np.float32))
 
 
 def to_np(t, name):
@@ -172,6 +181,12 @@ DECODE_CASES = [
     ("q8_1", "f32", 1, 8, 2, 64, [500]),
     ("q4_0", "f16", 2, 32, 8, 128, [2000, 333]),
     ("q4_0", "bf16", 1, 8, 2, 64, [500]),
+    ("q8_1", "f32", 1, 8, 2, 128, [300]),               # f32 queries: CUDA-core kernel on the permuted V rows
+    ("q4_0", "f32", 2, 8, 2, 128, [300, 77]),
+    ("q8_1", "bf16", 2, 32, 8, 128, [700, 90]),
+    ("q8_1", "f16", 1, 24, 2, 128, [1000]),             # G = 12: two tensor-core group tiles (8 + 4)
+    ("q4_0", "f16", 1, 2, 2, 128, [130]),               # G = 1 on the tensor-core kernel
+    ("bf16", "bf16", 1, 8, 8, 128, [4097]),
 ]
 
 
@@ -193,12 +208,31 @@ def test_decode_matches_oracle(kv, fmt, io, B, Hq, Hkv, D, lens):
     cache.append(seqs, to_dev(k_new), to_dev(v_new))
     out = cache.attend(seqs, to_dev(q), causal=True)
     cache.check()
-    got = to_np(out, io).astype(np.float32)
     for b in range(B):
         kc, vc = oracle_cache_view(fmt, Ks[b], io), oracle_cache_view(fmt, Vs[b], io)
-        want = oracle.flash_sdpa(q[b:b + 1], kc, vc, causal=True, threads=8).astype(np.float32)
-        err = rel_err(got[b:b + 1], want)
+        err = attn_err(out[b:b + 1], io, q[b:b + 1], kc, vc, causal=True, threads=8)
         assert err <= TOL[io], (b, err)
+    cache.close()
+
+
+@pytest.mark.parametrize("fmt", ["f16", "bf16", "q8_1", "q4_0"])
+def test_tensor_core_and_cuda_core_decode_agree(kv, fmt):
+    # the two formulations of the decode kernel read the same pages; they must agree far inside the tolerance
+    io = "bf16" if fmt == "bf16" else "f16"
+    Hq, Hkv, D, lens = 32, 8, 128, [1500, 64, 129, 63]
+    cache = kv.KvCache(fmt, Hkv, D, max_seqs=4, max_seq_tokens=2048)
+    seqs = [cache.new_seq() for _ in lens]
+    for b, n in enumerate(lens):
+        k = normal_with_outliers(300 + b, (1, Hkv, n, D)).astype(np_dtype(io))
+        v = normal_with_outliers(400 + b, (1, Hkv, n, D)).astype(np_dtype(io))
+        cache.append([seqs[b]], to_dev(k), to_dev(v))
+    q = to_dev(normal(9, (4, Hq, 1, D)).astype(np_dtype(io)))
+    out_tc = cache.attend(seqs, q, causal=True).float().cpu().numpy()
+    cache.profile(False, force_simt=True)
+    out_cc = cache.attend(seqs, q, causal=True).float().cpu().numpy()
+    cache.profile(False)
+    cache.check()
+    assert rel_err(out_tc, out_cc) <= 1e-3, rel_err(out_tc, out_cc)
     cache.close()
 
 
@@ -254,8 +288,7 @@ def test_prefill_matches_oracle(kv, fmt, io, Hq, Hkv, D, P, S):
     cache.append([sq], to_dev(k[:, :, P:]), to_dev(v[:, :, P:]))
     out = cache.attend([sq], to_dev(q), causal=True)
     cache.check()
-    want = oracle.flash_sdpa(q, oracle_cache_view(fmt, k, io), oracle_cache_view(fmt, v, io), causal=True, threads=8)
-    err = rel_err(to_np(out, io).astype(np.float32), want.astype(np.float32))
+    err = attn_err(out, io, q, oracle_cache_view(fmt, k, io), oracle_cache_view(fmt, v, io), causal=True, threads=8)
     assert err <= TOL[io], err
     cache.close()
 

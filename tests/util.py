@@ -23,6 +23,23 @@ def rel_err(got, ref) -> float:
     return float(np.max(np.abs(got - ref) / den))
 
 
+def rel_err_bf16(got_bf16, ref_f32) -> float:
+    """rel_err for a bf16 result against the oracle's UNROUNDED f32 result.
+
+    bf16 keeps 8 significant bits: one unit in the last place is 2^-8 relative, twice the 2e-3 bar, so
+    two correct implementations whose f32 results straddle a rounding boundary differ by more than the
+    bar after rounding.  The bar therefore applies to the computation: the distance to the f32 oracle
+    result beyond the half-ulp that rounding to bf16 (round-to-nearest-even, exact) may add.
+    """
+    got = np.asarray(got_bf16, dtype=np.float64)
+    ref = np.asarray(ref_f32, dtype=np.float64)
+    assert got.shape == ref.shape
+    rms = float(np.sqrt(np.mean(ref * ref)))
+    half_ulp = np.where(ref != 0, 2.0 ** (np.floor(np.log2(np.maximum(np.abs(ref), 1e-300))) - 8), 0.0)
+    excess = np.maximum(np.abs(got - ref) - half_ulp, 0.0)
+    return float(np.max(excess / (np.abs(ref) + (rms if rms > 0 else 1.0))))
+
+
 def rng(seed: int) -> np.random.Generator:
     """Counter-based generator (Philox4x32-10) so every case is reproducible from its seed."""
     return np.random.Generator(np.random.Philox(key=seed))

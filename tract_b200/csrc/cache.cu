@@ -119,11 +119,12 @@ __global__ void __launch_bounds__(256) append_kernel(AppendParams p) {
     // ---- load EPU input elements --------------------------------------------------------------
     const int esz = dtype_size(p.dtype);
     const uint8_t* src = (const uint8_t*)p.src[kv] + (b * p.sb[kv] + h * p.sh[kv] + s * p.ss[kv] + c0) * esz;
-    uint4 out16;  // the 16 bytes this thread stores
+    uint4 out16 = make_uint4(0, 0, 0, 0);  // bit-copy formats: the 16 bytes this thread stores
+    uint8_t codes[EPU > 16 ? EPU : 16];      // quantised formats: one code per element of the unit
     float scale_f = 0.f;
     bool write_scale = false;
 
-    if (FMT == B200KV_FMT_F32 || FMT == B200KV_FMT_F16 || FMT == B200KV_FMT_BF16) {
+    if constexpr (FMT == B200KV_FMT_F32 || FMT == B200KV_FMT_F16 || FMT == B200KV_FMT_BF16) {
         // bit copy: storage type == input type (checked on the host)
         if (p.vec_ok) {
             out16 = *(const uint4*)src;
@@ -160,7 +161,7 @@ __global__ void __launch_bounds__(256) append_kernel(AppendParams p) {
                 mx = v[i];
             }
         }
-        if (FMT == B200KV_FMT_Q8_1) {
+        if constexpr (FMT == B200KV_FMT_Q8_1) {
             // a block of 32 spans two units: combine with the neighbour lane, lower channels win ties
             float o_amax = __shfl_xor_sync(0xffffffffu, amax, 1);
             float o_mx = __shfl_xor_sync(0xffffffffu, mx, 1);
@@ -168,33 +169,26 @@ __global__ void __launch_bounds__(256) append_kernel(AppendParams p) {
             if (take_other) mx = o_mx;
             float scale = __fdiv_rn(mx, 127.0f);
             float r = (scale == 0.f) ? 0.f : __fdiv_rn(1.0f, scale);
-            uint32_t w[4];
+            // codes are stored offset-binary (code + 128) so that the decode kernel can widen them to
+            // f16 with byte permutes only; b200kv_export_codes returns the two's-complement int8
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
-                uint32_t word = 0;
-#pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    int code = sat_i8_rz(roundf(__fmul_rn(v[4 * i + j], r)));
-                    word |= ((uint32_t)code & 0xffu) << (8 * j);
-                }
-                w[i] = word;
-            }
-            out16 = make_uint4(w[0], w[1], w[2], w[3]);
+            for (int i = 0; i < 16; i++)
+                codes[i] = (uint8_t)((sat_i8_rz(roundf(__fmul_rn(v[i], r))) + 128) & 0xff);
             scale_f = scale;
             write_scale = (u & 1) == 0;
         } else {  // Q4_0: the unit is the whole block
             float scale = __fdiv_rn(mx, -8.0f);
             float r = (scale == 0.f) ? 0.f : __fdiv_rn(1.0f, scale);
-            uint32_t w[4] = {0, 0, 0, 0};
 #pragma unroll
             for (int j = 0; j < 16; j++) {
                 int lo = min(sat_i8_rz(__fadd_rn(__fmul_rn(v[j], r), 8.5f)), 15);
                 int hi = min(sat_i8_rz(__fadd_rn(__fmul_rn(v[j + 16], r), 8.5f)), 15);
-                // the reference ORs the two codes without masking (helpers.rs:57-68)
-                uint32_t byte = (((uint32_t)lo & 0xffu) | (((uint32_t)hi & 0xffu) << 4)) & 0xffu;
-                w[j / 4] |= byte << (8 * (j % 4));
+                // The reference writes `lo as u8 | (hi as u8) << 4` without masking (helpers.rs:57-68): a
+                // negative lo code (reachable only through an infinite reciprocal) spills its upper bits
+                // into the high nibble.  Store the nibbles that byte would hold.
+                codes[j] = (uint8_t)(lo & 0xf);
+                codes[j + 16] = (uint8_t)((hi | (lo >> 4)) & 0xf);
             }
-            out16 = make_uint4(w[0], w[1], w[2], w[3]);
             scale_f = scale;
             write_scale = true;
         }
@@ -211,7 +205,38 @@ __global__ void __launch_bounds__(256) append_kernel(AppendParams p) {
     }
     const int t = (int)(pos % PAGE_TOKENS);
     uint8_t* chunk = p.pool + (int64_t)pg * p.page_bytes + (int64_t)(h * (p.has_v ? 2 : 1) + kv) * p.chunk_bytes;
-    *(uint4*)(chunk + chunk_addr(p.plane_w, t, u * 16)) = out16;
+    uint8_t* data = chunk;
+    if constexpr (FMT == B200KV_FMT_F32 || FMT == B200KV_FMT_F16 || FMT == B200KV_FMT_BF16) {
+        *(uint4*)(data + chunk_addr(FMT, p.D, kv, t, u * 16)) = out16;
+    } else if constexpr (FMT == B200KV_FMT_Q8_1) {
+        if (v_permuted(FMT, p.D, kv)) {
+            // channels 16u + r and 16u + r + 8 sit side by side at position 16r + 2u
+#pragma unroll
+            for (int r = 0; r < 8; r++)
+                *(uint16_t*)(data + chunk_addr(FMT, p.D, kv, t, r * 16) + 2 * u) =
+                    (uint16_t)(codes[r] | ((uint16_t)codes[r + 8] << 8));
+        } else {
+            uint32_t w[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+                w[i] = codes[4 * i] | (codes[4 * i + 1] << 8) | (codes[4 * i + 2] << 16) | ((uint32_t)codes[4 * i + 3] << 24);
+            *(uint4*)(data + chunk_addr(FMT, p.D, kv, t, u * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+    } else {  // Q4_0, codes[i] = nibble of channel 32u + i
+        if (v_permuted(FMT, p.D, kv)) {
+            // byte 8r + j = channel 16j + r | channel 16j + r + 8 << 4 ; this block covers j = 2u, 2u + 1
+#pragma unroll
+            for (int r = 0; r < 8; r++) {
+                uint32_t b0 = codes[r] | (codes[r + 8] << 4), b1 = codes[16 + r] | (codes[24 + r] << 4);
+                *(uint16_t*)(data + chunk_addr(FMT, p.D, kv, t, r * 8) + 2 * u) = (uint16_t)(b0 | (b1 << 8));
+            }
+        } else {
+            uint32_t w[4] = {0, 0, 0, 0};
+#pragma unroll
+            for (int j = 0; j < 16; j++) w[j / 4] |= (uint32_t)(codes[j] | (codes[j + 16] << 4)) << (8 * (j % 4));
+            *(uint4*)(data + chunk_addr(FMT, p.D, kv, t, u * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+    }
     if (write_scale) {
         int blk = (FMT == B200KV_FMT_Q8_1) ? u / 2 : u;
         ((__half*)(chunk + p.data_bytes))[t * (p.D / 32) + blk] = __float2half_rn(scale_f);
@@ -230,7 +255,17 @@ struct ExportParams {
     int32_t dtype, has_v, which;
 };
 
-// One thread per 16-byte unit; mode 0: dequantised / bit-copied elements, mode 1: raw codes + scales.
+// Integer code of channel ch of a quantised row: Q8_1 -> -128..127, Q4_0 -> nibble 0..15.
+template <int FMT>
+__device__ inline int load_code(const uint8_t* chunk, int D, int kv, int t, int ch) {
+    const int pos = code_pos(FMT, D, kv, ch);
+    const uint32_t byte = chunk[chunk_addr(FMT, D, kv, t, pos)];
+    if (FMT == B200KV_FMT_Q8_1) return (int)byte - 128;
+    return code_nibble(FMT, D, kv, ch) ? (int)(byte >> 4) : (int)(byte & 0xf);
+}
+
+// One thread per 16 bytes of the natural row; mode 0: dequantised / bit-copied elements,
+// mode 1: raw codes (int8 two's complement / GGML nibble bytes) + scales.
 template <int FMT, int MODE>
 __global__ void __launch_bounds__(256) export_kernel(ExportParams p) {
     constexpr int EPU = elems_in_bytes<FMT>(16);
@@ -244,18 +279,10 @@ __global__ void __launch_bounds__(256) export_kernel(ExportParams p) {
     const int32_t pg = p.table_row[tok / PAGE_TOKENS];
     const int t = (int)(tok % PAGE_TOKENS);
     const uint8_t* chunk = p.pool + (int64_t)pg * p.page_bytes + (int64_t)(h * (p.has_v ? 2 : 1) + kv) * p.chunk_bytes;
-    const uint8_t* unit = chunk + chunk_addr(p.plane_w, t, u * 16);
-    if (MODE == 1) {
-        *(uint4*)((uint8_t*)p.codes + ((int64_t)h * p.len + tok) * p.row_bytes + u * 16) = *(const uint4*)unit;
-        int nb = p.D / 32;
-        if (u < nb)
-            ((__half*)p.scales)[((int64_t)h * p.len + tok) * nb + u] = ((const __half*)(chunk + p.data_bytes))[t * nb + u];
-        return;
-    }
     const int64_t base = h * p.dh[kv] + tok * p.dt[kv];
     if (FMT == B200KV_FMT_F32 || FMT == B200KV_FMT_F16 || FMT == B200KV_FMT_BF16) {
         // bit copy (the destination has the storage element type): no conversion, NaN payloads survive
-        const uint4 raw = *(const uint4*)unit;
+        const uint4 raw = *(const uint4*)(chunk + chunk_addr(FMT, p.D, kv, t, u * 16));
         if (FMT == B200KV_FMT_F32) {
             uint32_t* d = (uint32_t*)p.dst[kv] + base + u * EPU;
             d[0] = raw.x, d[1] = raw.y, d[2] = raw.z, d[3] = raw.w;
@@ -267,16 +294,32 @@ __global__ void __launch_bounds__(256) export_kernel(ExportParams p) {
         }
         return;
     }
-    float v[EPU];
-    load_piece<FMT, 16>(unit, v);
-    if (FMT == B200KV_FMT_Q8_1 || FMT == B200KV_FMT_Q4_0) {
-        int blk = (FMT == B200KV_FMT_Q8_1) ? u / 2 : u;
-        float d = __half2float(((const __half*)(chunk + p.data_bytes))[t * (p.D / 32) + blk]);
+    const int nb = p.D / 32;
+    const __half* scales = (const __half*)(chunk + p.data_bytes) + t * nb;
+    const int c0 = u * EPU;  // first channel of this thread (Q8_1: 16 channels, Q4_0: one block of 32)
+    if (MODE == 1) {
+        uint8_t out[16];
+        if (FMT == B200KV_FMT_Q8_1) {
 #pragma unroll
-        for (int i = 0; i < EPU; i++) v[i] = __fmul_rn(v[i], d);  // code * f32(f16 scale): exact in f32
+            for (int i = 0; i < 16; i++) out[i] = (uint8_t)(load_code<FMT>(chunk, p.D, kv, t, c0 + i) & 0xff);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; i++)
+                out[i] = (uint8_t)(load_code<FMT>(chunk, p.D, kv, t, c0 + i) | (load_code<FMT>(chunk, p.D, kv, t, c0 + 16 + i) << 4));
+        }
+        uint8_t* dst = (uint8_t*)p.codes + ((int64_t)h * p.len + tok) * p.row_bytes + u * 16;
+#pragma unroll
+        for (int i = 0; i < 16; i++) dst[i] = out[i];
+        if (u < nb) ((__half*)p.scales)[((int64_t)h * p.len + tok) * nb + u] = scales[u];
+        return;
     }
 #pragma unroll
-    for (int i = 0; i < EPU; i++) st_from_f32(p.dst[kv], p.dtype, base + row_channel<FMT>(u * 16, i, 16), v[i]);
+    for (int i = 0; i < EPU; i++) {
+        const int ch = c0 + i;
+        const int code = load_code<FMT>(chunk, p.D, kv, t, ch) - (FMT == B200KV_FMT_Q4_0 ? 8 : 0);
+        // code * f32(f16 scale): exact in f32 (q8_1.rs:50-63, q4_0.rs:82-95)
+        st_from_f32(p.dst[kv], p.dtype, base + ch, __fmul_rn((float)code, __half2float(scales[ch / 32])));
+    }
 }
 
 // ---- host side --------------------------------------------------------------------------------------
@@ -632,7 +675,8 @@ int b200kv_fork(b200kv_cache* c, int32_t seq, int32_t* new_seq_out, void* stream
 
 int b200kv_profile(b200kv_cache* c, int32_t enable) {
     if (!c) return fail("null cache");
-    c->prof_on = enable != 0;
+    c->prof_on = (enable & 1) != 0;
+    c->force_simt = (enable & 2) != 0;
     return B200KV_OK;
 }
 

@@ -16,13 +16,22 @@ constexpr int PAGE_TOKENS = 64;
 // page   = [Hkv][K chunk, V chunk]            (V chunk absent when the cache has no values)
 // chunk  = data region (PAGE_TOKENS rows of ROW_BYTES) followed, for the block-quantised
 //          formats, by PAGE_TOKENS x (D/32) f16 scales in token order.
-// A row is the natural byte string of one token-head: D elements (f32 / f16 / bf16), D int8
-// codes (Q8_1) or D/32 blocks of 16 nibble bytes (Q4_0, GGML order).  The data region is cut
+// A row is the byte string of one token-head: D elements (f32 / f16 / bf16), D code bytes
+// (Q8_1, stored offset-binary: code + 128) or D/2 nibble bytes (Q4_0).  The data region is cut
 // into column slabs ("planes") 128 bytes wide (or ROW_BYTES if smaller); inside a plane the
-// bytes are linear in (token, byte) with address bits [4,7) XOR-ed with bits [7,10): the
-// 128-byte swizzle that both shared-memory ldmatrix/LDS.128 readers and tcgen05 K-major /
-// MN-major operand tiles want.  Because whole chunks are contiguous in HBM, one untiled
-// cp.async.bulk brings a chunk into shared memory already in that arrangement.
+// bytes are linear in (token, byte) and the index of each 16-byte unit inside its 128-byte line
+// is XOR-ed with a function of the line number (swz_mask) chosen so that the shared-memory
+// access patterns of the kernels are free of bank conflicts.  For f16 / bf16 that function is
+// the 128-byte swizzle of ldmatrix / tcgen05 operand tiles.  Because whole chunks are contiguous
+// in HBM, one untiled cp.async.bulk brings a chunk into shared memory already in that arrangement.
+//
+// The layout is private to the library: at head_dim 128 the V rows of the quantised formats
+// also store their codes in a permuted channel order that lets the tensor-core decode kernel
+// build V^T operand fragments from 16 contiguous bytes per thread:
+//   Q8_1 V: byte position 16r + 2j + h holds channel 16j + r + 8h        (r < 8, j < 8, h < 2)
+//   Q4_0 V: byte position  8r + j holds channel 16j + r (low nibble) and 16j + r + 8 (high nibble)
+// K rows keep the natural order (Q4_0: GGML block bytes, byte i of block b = channel 32b + i |
+// channel 32b + 16 + i << 4).  b200kv_export_codes undoes all of this.
 struct Layout {
     int fmt, D, Hkv, has_v;
     int row_bytes;    // bytes of one token-head row in the data region
@@ -60,16 +69,40 @@ inline Layout make_layout(int fmt, int D, int Hkv, int has_v) {
     return L;
 }
 
-// Byte offset inside a chunk's data region of row byte `rb` of token slot `t`.
-__host__ __device__ inline uint32_t chunk_addr(int plane_w, int t, int rb) {
-    uint32_t plane = (uint32_t)rb / (uint32_t)plane_w;
-    uint32_t lin = (uint32_t)t * (uint32_t)plane_w + (uint32_t)rb % (uint32_t)plane_w;
-    return plane * (uint32_t)(PAGE_TOKENS * plane_w) + (lin ^ (((lin >> 7) & 7u) << 4));
+// True when the V rows of this cache store their codes in the permuted channel order.
+__host__ __device__ constexpr bool v_permuted(int fmt, int D, int kv) {
+    return kv == 1 && D == 128 && (fmt == B200KV_FMT_Q8_1 || fmt == B200KV_FMT_Q4_0);
 }
 
-// Channel index of element e of the piece that starts at row byte rb (piece_bytes long).
-// Q4_0 rows are GGML blocks: byte j of block b holds channel 32b+j (low nibble) and 32b+16+j
-// (high nibble); a piece yields its low-nibble elements first, then the high-nibble ones.
+// XOR mask for the 16-byte-unit index inside 128-byte line `line` of a plane.
+__host__ __device__ constexpr uint32_t swz_mask(int fmt, int D, int kv, uint32_t line) {
+    // Q8_1 K at D = 128: the tensor-core kernel reads 32 bytes per row from 4 rows per wavefront
+    if (D == 128 && fmt == B200KV_FMT_Q8_1 && kv == 0) return ((line & 3u) << 1) | ((line >> 2) & 1u);
+    // Q4_0 V at D = 128: 32 bytes per row from rows two lines apart
+    if (D == 128 && fmt == B200KV_FMT_Q4_0 && kv == 1) return (line & 3u) << 1;
+    return line & 7u;
+}
+
+// Byte offset inside a chunk's data region of row byte `rb` of token slot `t`.
+__host__ __device__ constexpr uint32_t chunk_addr(int fmt, int D, int kv, int t, int rb) {
+    const uint32_t row = (uint32_t)fmt_row_bytes(fmt, D);
+    const uint32_t pw = row < 128u ? row : 128u;
+    const uint32_t plane = (uint32_t)rb / pw;
+    const uint32_t lin = (uint32_t)t * pw + (uint32_t)rb % pw;
+    return plane * (uint32_t)PAGE_TOKENS * pw + (lin ^ (swz_mask(fmt, D, kv, lin >> 7) << 4));
+}
+
+// Where the code of channel `ch` lives in a quantised row: byte position, and for Q4_0 the nibble.
+__host__ __device__ constexpr int code_pos(int fmt, int D, int kv, int ch) {
+    if (fmt == B200KV_FMT_Q8_1) return v_permuted(fmt, D, kv) ? (ch % 8) * 16 + 2 * (ch / 16) + ((ch / 8) & 1) : ch;
+    return v_permuted(fmt, D, kv) ? (ch % 8) * 8 + ch / 16 : (ch / 32) * 16 + ch % 16;
+}
+__host__ __device__ constexpr int code_nibble(int fmt, int D, int kv, int ch) {
+    return v_permuted(fmt, D, kv) ? (ch / 8) & 1 : (ch % 32) / 16;
+}
+
+// Channel index of element e of the piece that starts at row byte rb (piece_bytes long), natural
+// row order.  Q4_0 pieces yield their low-nibble elements first, then the high-nibble ones.
 template <int FMT>
 __host__ __device__ inline int row_channel(int rb, int e, int piece_bytes) {
     if (FMT == B200KV_FMT_F32) return rb / 4 + e;
@@ -77,6 +110,16 @@ __host__ __device__ inline int row_channel(int rb, int e, int piece_bytes) {
     if (FMT == B200KV_FMT_Q8_1) return rb + e;
     int b = rb / 16, j0 = rb % 16;
     return e < piece_bytes ? b * 32 + j0 + e : b * 32 + 16 + j0 + (e - piece_bytes);
+}
+// The same for a row in the permuted V order (Q8_1 / Q4_0, D = 128).
+template <int FMT>
+__host__ __device__ inline int row_channel_vperm(int rb, int e, int piece_bytes) {
+    if (FMT == B200KV_FMT_Q8_1) {
+        int pos = rb + e;
+        return 16 * ((pos % 16) / 2) + pos / 16 + 8 * (pos & 1);
+    }
+    int pos = rb + (e < piece_bytes ? e : e - piece_bytes);
+    return 16 * (pos % 8) + pos / 8 + (e < piece_bytes ? 0 : 8);
 }
 
 // Elements held by `bytes` bytes of a row.
@@ -102,7 +145,7 @@ __device__ inline void st_from_f32(void* p, int dtype, int64_t i, float v) {
 __host__ __device__ inline int dtype_size(int dtype) { return dtype == B200KV_F32 ? 4 : 2; }
 
 // Decodes one piece (PB bytes at p, 16-byte aligned when PB == 16) into floats.  Block-quantised
-// formats return the integer codes as floats (Q4_0: nibble - 8); the caller applies the scale.
+// formats return the integer codes as floats (Q8_1: byte - 128, Q4_0: nibble - 8); the caller applies the scale.
 template <int FMT, int PB>
 __device__ inline void load_piece(const uint8_t* p, float* out) {
     uint32_t w[4];
@@ -134,7 +177,7 @@ __device__ inline void load_piece(const uint8_t* p, float* out) {
         }
     } else if (FMT == B200KV_FMT_Q8_1) {
 #pragma unroll
-        for (int b = 0; b < PB; b++) out[b] = (float)(int)(int8_t)(w[b / 4] >> (8 * (b % 4)));
+        for (int b = 0; b < PB; b++) out[b] = (float)((int)((w[b / 4] >> (8 * (b % 4))) & 0xffu) - 128);  // offset-binary
     } else {  // Q4_0: low nibbles of the PB bytes, then high nibbles
 #pragma unroll
         for (int b = 0; b < PB; b++) {

@@ -12,33 +12,9 @@
 #include <cmath>
 #include <vector>
 
-#include "internal.h"
+#include "decode_common.h"
 
 namespace b200kv {
-
-struct WorkItem {
-    int32_t trow;        // page-table row of the sequence
-    int32_t len;         // cached length of the sequence
-    int32_t page_begin;  // first page of this split
-    int32_t n_pages;     // pages in this split
-    int32_t batch;       // batch entry
-    int32_t split;       // split index inside the batch entry
-    int32_t pad0, pad1;
-};
-
-struct DecodeParams {
-    const uint8_t* pool;
-    const int32_t* table;
-    const WorkItem* items;
-    int* status;
-    const void* q;
-    int64_t qb, qh;  // q strides {batch, head} in elements
-    float* part_o;   // [item][Hkv][G][D]   unnormalised partial outputs
-    float* part_ml;  // [item][Hkv][G][2]   running max, running sum
-    int64_t page_bytes;
-    int32_t n_pages, max_pages_per_seq, Hkv, G, dtype;
-    float scale;
-};
 
 template <int FMT, int D>
 struct Geo {
@@ -172,7 +148,7 @@ __global__ void __launch_bounds__(128) decode_kernel(DecodeParams p) {
             for (int pc = 0; pc < Gm::NPC; pc++) {
                 const int rb = pc * (8 * Gm::PB) + sub * Gm::PB;
                 float vals[Gm::EPP];
-                load_piece<FMT, Gm::PB>(Ks + chunk_addr(Gm::PW, t, rb), vals);
+                load_piece<FMT, Gm::PB>(Ks + chunk_addr(FMT, D, 0, t, rb), vals);
                 if (Gm::QUANT) {
                     const int blk = (FMT == B200KV_FMT_Q8_1 ? rb : rb * 2) / 32;
                     const float d = __half2float(((const __half*)(Ks + Gm::DATA))[t * (D / 32) + blk]);
@@ -249,18 +225,32 @@ __global__ void __launch_bounds__(128) decode_kernel(DecodeParams p) {
                     for (int pc = 0; pc < Gm::NPC2; pc++) {
                         const int rb = pc * (16 * Gm::PB2) + cu * Gm::PB2;
                         float vals[Gm::EPP2];
-                        load_piece<FMT, Gm::PB2>(Vs + chunk_addr(Gm::PW, t, rb), vals);
-                        float d = 1.f;
-                        if (Gm::QUANT) {
-                            const int blk = (FMT == B200KV_FMT_Q8_1 ? rb : rb * 2) / 32;
-                            d = __half2float(((const __half*)(Vs + Gm::DATA))[t * (D / 32) + blk]);
-                        }
+                        load_piece<FMT, Gm::PB2>(Vs + chunk_addr(FMT, D, 1, t, rb), vals);
+                        if constexpr (v_permuted(FMT, D, 1)) {
+                            // permuted V row: this thread's elements fall into blocks 2(cu & 1) and 2(cu & 1) + 1
+                            const float2 d2 = __half22float2(((const __half2*)(Vs + Gm::DATA))[t * 2 + (cu & 1)]);
 #pragma unroll
-                        for (int g = 0; g < GT; g++) {
-                            const float pd = Gm::QUANT ? pr[g] * d : pr[g];
+                            for (int e = 0; e < Gm::EPP2; e++) {
+                                const bool upper = FMT == B200KV_FMT_Q8_1 ? (e >= 4) : ((e % 4) >= 2);
+                                vals[e] *= upper ? d2.y : d2.x;
+                            }
 #pragma unroll
-                            for (int e = 0; e < Gm::EPP2; e++)
-                                acc[g][pc * Gm::EPP2 + e] = fmaf(pd, vals[e], acc[g][pc * Gm::EPP2 + e]);
+                            for (int g = 0; g < GT; g++)
+#pragma unroll
+                                for (int e = 0; e < Gm::EPP2; e++) acc[g][e] = fmaf(pr[g], vals[e], acc[g][e]);
+                        } else {
+                            float d = 1.f;
+                            if (Gm::QUANT) {
+                                const int blk = (FMT == B200KV_FMT_Q8_1 ? rb : rb * 2) / 32;
+                                d = __half2float(((const __half*)(Vs + Gm::DATA))[t * (D / 32) + blk]);
+                            }
+#pragma unroll
+                            for (int g = 0; g < GT; g++) {
+                                const float pd = Gm::QUANT ? pr[g] * d : pr[g];
+#pragma unroll
+                                for (int e = 0; e < Gm::EPP2; e++)
+                                    acc[g][pc * Gm::EPP2 + e] = fmaf(pd, vals[e], acc[g][pc * Gm::EPP2 + e]);
+                            }
                         }
                     }
                 }
@@ -297,7 +287,8 @@ __global__ void __launch_bounds__(128) decode_kernel(DecodeParams p) {
             const int rb = pc * (16 * Gm::PB2) + cu * Gm::PB2;
 #pragma unroll
             for (int e = 0; e < Gm::EPP2; e++)
-                red[(tg * GT + g) * D + row_channel<FMT>(rb, e, Gm::PB2)] = acc[g][pc * Gm::EPP2 + e];
+                red[(tg * GT + g) * D + (v_permuted(FMT, D, 1) ? row_channel_vperm<FMT>(rb, e, Gm::PB2) : row_channel<FMT>(rb, e, Gm::PB2))] =
+                    acc[g][pc * Gm::EPP2 + e];
         }
     __syncthreads();
     for (int idx = tid; idx < GT * D; idx += 128) {
@@ -359,7 +350,8 @@ static int launch_decode_f(const DecodeParams& p, int D, int n_items, cudaStream
 int launch_decode(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t n_q_heads, const void* q,
                   const int64_t* qs, void* out, const int64_t* os, int32_t dtype, float scale, cudaStream_t stream) {
     const int Hkv = c->L.Hkv, D = c->L.D, G = n_q_heads / Hkv;
-    const int GT = G == 1 ? 1 : 4, nz = (G + GT - 1) / GT;
+    const bool use_mma = decode_mma_supported(c->L.fmt, D, dtype) && !c->force_simt;
+    const int GT = use_mma ? 8 : (G == 1 ? 1 : 4), nz = (G + GT - 1) / GT;
     // ---- work list: split every sequence into runs of pages so that the grid covers the GPU many times ----
     int64_t total_pages = 0;
     for (int i = 0; i < n_seqs; i++) {
@@ -406,6 +398,9 @@ int launch_decode(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t 
     int rc;
     {
     ProfScope ps(c, K_DECODE, stream);
+    if (decode_mma_supported(c->L.fmt, D, dtype) && !c->force_simt) {
+        rc = launch_decode_mma(c->L.fmt, p, (int)items.size(), stream);
+    } else
     switch (c->L.fmt) {
         case B200KV_FMT_F32: rc = launch_decode_f<B200KV_FMT_F32>(p, D, (int)items.size(), stream); break;
         case B200KV_FMT_F16: rc = launch_decode_f<B200KV_FMT_F16>(p, D, (int)items.size(), stream); break;
