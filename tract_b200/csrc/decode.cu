@@ -66,13 +66,13 @@ __global__ void __launch_bounds__(128) decode_kernel(DecodeParams p) {
     using Gm = Geo<FMT, D>;
     const bool PRECISE = p.dtype == B200KV_F32;  // f32 callers get expf, 16-bit callers the fast exponential
     constexpr int NS = Gm::NS;
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* stages = (uint8_t*)(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
+    // declared aligned (not rounded up by hand) so that the compiler keeps every access in the shared window
+    extern __shared__ __align__(1024) uint8_t stages[];
     float* sc = (float*)(stages + (size_t)NS * Gm::STAGE);  // [GT][64]
     float* pT = sc + GT * 64;                                // [64][GT]
     float* alpha_s = pT + 64 * GT;                           // [GT]
     float* ml_s = alpha_s + GT;                              // [GT][2]
-    uint64_t* bars = (uint64_t*)(((uintptr_t)(ml_s + 2 * GT) + 15) & ~(uintptr_t)15);
+    uint64_t* bars = (uint64_t*)(ml_s + 2 * GT + (GT & 1));  // 8-byte aligned: the counts before it are even
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int sub = lane & 7, tl = lane >> 3;
@@ -97,10 +97,10 @@ __global__ void __launch_bounds__(128) decode_kernel(DecodeParams p) {
     if (tid == 0) {
         for (int s = 0; s < NS; s++) mbar_init(&bars[s], 1);
         mbar_fence_init();
+        // start streaming right away; the other threads first meet the barriers after the __syncthreads below
+        for (int i = 0; i < NS && i < n_tiles; i++) issue(i);
     }
     __syncthreads();
-    if (tid == 0)
-        for (int i = 0; i < NS && i < n_tiles; i++) issue(i);
 
     // the query rows of this group, as f32 registers laid out like the pieces each lane reads
     float qr[GT][Gm::EPL];
@@ -333,7 +333,7 @@ __global__ void combine_kernel(CombineParams p) {
 template <int FMT, int D, int GT>
 static int launch_decode_t(const DecodeParams& p, int n_items, cudaStream_t stream) {
     using Gm = Geo<FMT, D>;
-    const size_t smem = 128 + (size_t)Gm::NS * Gm::STAGE + decode_tail_bytes<GT>();
+    const size_t smem = (size_t)Gm::NS * Gm::STAGE + decode_tail_bytes<GT>();
     B200KV_CUDA(cudaFuncSetAttribute(decode_kernel<FMT, D, GT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     dim3 grid(n_items, p.Hkv, (p.G + GT - 1) / GT);
     decode_kernel<FMT, D, GT><<<grid, 128, smem, stream>>>(p);

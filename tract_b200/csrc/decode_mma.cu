@@ -88,10 +88,10 @@ __device__ inline float quad_row_sum(float v) {
 }
 
 // Shared memory after the stage ring: q as f32 [8][128], then the barriers.
-constexpr size_t MMA_TAIL = 8 * MD * 4 + 64;
+constexpr size_t MMA_TAIL = 8 * MD * 4 + 32 * 4 + 64;
 
 template <int FMT>
-__global__ void __launch_bounds__(128) decode_mma_kernel(DecodeParams p) {
+__global__ void __launch_bounds__(128, 3) decode_mma_kernel(DecodeParams p) {
     using Gm = MGeo<FMT>;
     constexpr int NS = Gm::NS;
     constexpr bool QUANT = Gm::QUANT;
@@ -103,10 +103,11 @@ __global__ void __launch_bounds__(128) decode_mma_kernel(DecodeParams p) {
     constexpr float TWO24 = 16777216.f;
     constexpr float PSCALE = 1024.f;  // probabilities * V scale are lifted into the normal f16 range
 
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* stages = (uint8_t*)(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
+    // declared aligned (not rounded up by hand) so that the compiler keeps every access in the shared window
+    extern __shared__ __align__(1024) uint8_t stages[];
     float* q_s = (float*)(stages + (size_t)NS * Gm::STAGE);  // [8][128]
-    uint64_t* bars = (uint64_t*)(q_s + 8 * MD);
+    float* qsum_s = q_s + 8 * MD;                             // [8 heads][4 blocks]
+    uint64_t* bars = (uint64_t*)(qsum_s + 32);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int r = lane >> 2, c = lane & 3;
@@ -130,6 +131,8 @@ __global__ void __launch_bounds__(128) decode_mma_kernel(DecodeParams p) {
     if (tid == 0) {
         for (int s = 0; s < NS; s++) mbar_init(&bars[s], 1);
         mbar_fence_init();
+        // start streaming right away; the other threads first meet the barriers after the __syncthreads below
+        for (int i = 0; i < NS && i < n_tiles; i++) issue(i);
     }
     // q of the group as f32 in shared memory, rows beyond the group zero
     for (int idx = tid; idx < 8 * MD; idx += 128) {
@@ -140,8 +143,6 @@ __global__ void __launch_bounds__(128) decode_mma_kernel(DecodeParams p) {
         q_s[idx] = v;
     }
     __syncthreads();
-    if (tid == 0)
-        for (int i = 0; i < NS && i < n_tiles; i++) issue(i);
 
     // ---- B fragments of Q^T for the 8 k-steps (head n = lane / 4) --------------------------------------
     uint32_t qb[8][2];
@@ -169,14 +170,20 @@ __global__ void __launch_bounds__(128) decode_mma_kernel(DecodeParams p) {
     // offset term of the K side: OFFS * sum of q over each 32-channel block, for heads 2c and 2c + 1
     float kbias[QUANT ? 4 : 1][2];
     if (QUANT) {
+        {  // 16 threads per head, 8 channels each; 4 neighbouring threads make up one block
+            const float* src = q_s + (tid >> 4) * MD + (tid & 15) * 8;
+            float sum = 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; i++) sum += src[i];
+            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+            if ((tid & 3) == 0) qsum_s[(tid >> 4) * 4 + ((tid & 15) >> 2)] = sum;
+        }
+        __syncthreads();
 #pragma unroll
         for (int b = 0; b < 4; b++)
 #pragma unroll
-            for (int h = 0; h < 2; h++) {
-                float sum = 0.f;
-                for (int i = 0; i < 32; i++) sum += q_s[(2 * c + h) * MD + 32 * b + i];
-                kbias[b][h] = OFFS * sum;
-            }
+            for (int h = 0; h < 2; h++) kbias[b][h] = OFFS * qsum_s[(2 * c + h) * 4 + b];
     }
 
     const float sl2 = p.scale * LOG2E;  // scores are kept in log2 units
@@ -390,7 +397,7 @@ __global__ void __launch_bounds__(128) decode_mma_kernel(DecodeParams p) {
         if (tid < ng) p.part_ml[(pbase + tid) * 2] = -INFINITY, p.part_ml[(pbase + tid) * 2 + 1] = 0.f;
         return;
     }
-    float* om = (float*)stages;                 // [4 warps][8 heads][128 ch]
+    float* om = (float*)stages;                 // [4 warps][8 heads][128 ch]; every stage is consumed by now
     float* ml = om + 4 * 8 * MD;                // [4 warps][8 heads][2]
     const float l0 = quad_row_sum(l_part[0]), l1 = quad_row_sum(l_part[1]);
     if (r == 0) {
@@ -439,7 +446,7 @@ static int launch_mma_t(const DecodeParams& p, int n_items, cudaStream_t stream)
     using Gm = MGeo<FMT>;
     const size_t ring = (size_t)Gm::NS * Gm::STAGE;
     const size_t merge = (size_t)(4 * 8 * MD + 4 * 8 * 2) * 4;  // the warp merge reuses the ring
-    const size_t smem = 128 + std::max(ring, merge) + MMA_TAIL;
+    const size_t smem = std::max(ring, merge) + MMA_TAIL;
     B200KV_CUDA(cudaFuncSetAttribute(decode_mma_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     dim3 grid(n_items, p.Hkv, (p.G + 7) / 8);
     decode_mma_kernel<FMT><<<grid, 128, smem, stream>>>(p);
