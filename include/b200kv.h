@@ -138,6 +138,27 @@ int b200kv_fork(b200kv_cache* cache, int32_t seq, int32_t* new_seq_out, void* st
  * that expired).  Synchronises the stream.  Returns KO and sets the message if the word is non-zero. */
 int b200kv_check(b200kv_cache* cache, void* stream);
 
+/* Decode attention (one query per sequence: the n_new == 1 case of b200kv_attend, same arguments and
+ * result) that performs no device allocation, for callers that cannot afford one while a step runs: a
+ * server that has given every free byte of HBM to its page pools, a runtime whose device arena was sized
+ * once and may not grow, or a latency-critical loop in which the device-wide synchronisation implied by
+ * cudaMalloc / cudaFree would stall the other streams.  b200kv_attend keeps its split-KV partials in a
+ * workspace that it re-allocates when a call needs more of them than any earlier call; this entry point
+ * keeps them in a fixed 8 MiB device array inside the library (held by every GPU that loads the library,
+ * from load to exit) and calls neither cudaMalloc nor cudaFree nor any allocating library routine.
+ *   - Limit: page runs x n_kv_heads x (n_q_heads / n_kv_heads) x (head_dim + 2) floats <= 2 Mi floats, where
+ *     page runs is the number of splits of the batch (at most 64 per sequence).  A call beyond the limit
+ *     fails with a message that states both numbers; nothing is enqueued.
+ *   - The first call on a device looks up the device address of the array (cudaGetSymbolAddress, with that
+ *     device current); make that first call before any stream capture begins.
+ *   - All calls on one device share the array, and a call leaves its partials behind; each call overwrites
+ *     every slot it reads, so nothing needs clearing, but two calls whose kernels overlap on the GPU
+ *     (different streams, or different caches, without an ordering between them) race on it.
+ * This entry point has no counterpart in the reference. */
+int b200kv_attend_static_scratch(b200kv_cache* cache, int32_t n_seqs, const int32_t* seqs, int32_t n_q_heads,
+                                 const void* q, const int64_t q_strides[3], void* out, const int64_t out_strides[3],
+                                 int32_t dtype, float scale, void* stream);
+
 /* Per-launch timing, off by default.  When enabled, every kernel launched for this cache is bracketed by a
  * CUDA event pair on the caller's stream (what tract-cuda's TractCudaStream does for its profiler,
  * cuda/src/context.rs:364-453).  b200kv_profile_read waits for the recorded launches, returns up to

@@ -22,7 +22,7 @@ EXPORTS = [
     "b200kv_last_error", "b200kv_version", "b200kv_create", "b200kv_destroy", "b200kv_seq_new", "b200kv_seq_free",
     "b200kv_seq_len", "b200kv_free_pages", "b200kv_page_bytes", "b200kv_append", "b200kv_attend", "b200kv_export",
     "b200kv_export_codes", "b200kv_truncate", "b200kv_fork", "b200kv_check", "b200kv_sdpa", "b200kv_profile",
-    "b200kv_profile_read",
+    "b200kv_profile_read", "b200kv_attend_static_scratch",
 ]
 KERNEL_NAMES = {0: "table_scatter", 1: "append", 2: "decode", 3: "combine", 4: "export", 5: "sdpa_dense", 6: "prefill"}
 
@@ -66,6 +66,7 @@ def lib():
         L.b200kv_export_codes.argtypes = [vp, i32, i32, vp, vp, vp]
         L.b200kv_truncate.argtypes = [vp, i32, i64]
         L.b200kv_fork.argtypes = [vp, i32, i32p, vp]
+        L.b200kv_attend_static_scratch.argtypes = [vp, i32, i32p, i32, vp, i64p, vp, i64p, i32, C.c_float, vp]
         L.b200kv_check.argtypes = [vp, vp]
         L.b200kv_profile.argtypes = [vp, i32]
         L.b200kv_profile_read.argtypes = [vp, i32, i32p, C.POINTER(C.c_float), i32p]
@@ -170,6 +171,19 @@ class KvCache:
         _ck(lib().b200kv_attend(self._h, len(seqs), _ids(seqs), q.shape[1], q.shape[2], q.data_ptr(), _strides(q, 3),
                                 out.data_ptr(), _strides(out, 3), _dtype_code(q), float(scale or 0.0), int(causal),
                                 _stream()))
+        return out
+
+    def attend_static_scratch(self, seqs, q, scale=None, out=None):
+        """Decode attention (q: [n_seqs, Hq, 1, D]) that allocates nothing on the device: the split partials go
+        to a fixed array inside the library.  Raises if the call needs more partials than the array holds."""
+        import torch
+
+        assert q.dim() == 4 and q.shape[0] == len(seqs) and q.shape[2] == 1
+        if out is None:
+            raise B200KvError("pass `out`: this call path must not allocate")
+        _ck(lib().b200kv_attend_static_scratch(self._h, len(seqs), _ids(seqs), q.shape[1], q.data_ptr(), _strides(q, 3),
+                                               out.data_ptr(), _strides(out, 3), _dtype_code(q), float(scale or 0.0),
+                                               _stream()))
         return out
 
     # -- state --

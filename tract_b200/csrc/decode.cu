@@ -347,6 +347,28 @@ static int launch_decode_f(const DecodeParams& p, int D, int n_items, cudaStream
     return D == 128 ? launch_decode_t<FMT, 128, 4>(p, n_items, stream) : launch_decode_t<FMT, 64, 4>(p, n_items, stream);
 }
 
+// The two launch steps of a decode call, for callers in other translation units.
+int launch_decode_simt(int fmt, int D, const DecodeParams& p, int n_items, cudaStream_t stream) {
+    switch (fmt) {
+        case B200KV_FMT_F32: return launch_decode_f<B200KV_FMT_F32>(p, D, n_items, stream);
+        case B200KV_FMT_F16: return launch_decode_f<B200KV_FMT_F16>(p, D, n_items, stream);
+        case B200KV_FMT_BF16: return launch_decode_f<B200KV_FMT_BF16>(p, D, n_items, stream);
+        case B200KV_FMT_Q8_1: return launch_decode_f<B200KV_FMT_Q8_1>(p, D, n_items, stream);
+        case B200KV_FMT_Q4_0: return launch_decode_f<B200KV_FMT_Q4_0>(p, D, n_items, stream);
+    }
+    return fail("format %d has no decode kernel", fmt);
+}
+int launch_combine(const DecodeParams& p, const int32_t* batch_info, void* out, int64_t ob, int64_t oh, int n_seqs,
+                   int n_q_heads, int D, cudaStream_t stream) {
+    CombineParams cp{};
+    cp.part_o = p.part_o, cp.part_ml = p.part_ml, cp.batch_info = batch_info;
+    cp.out = out, cp.ob = ob, cp.oh = oh;
+    cp.Hkv = p.Hkv, cp.G = p.G, cp.D = D, cp.dtype = p.dtype;
+    combine_kernel<<<dim3(n_seqs, n_q_heads), D, 0, stream>>>(cp);
+    B200KV_CUDA(cudaGetLastError());
+    return B200KV_OK;
+}
+
 int launch_decode(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t n_q_heads, const void* q,
                   const int64_t* qs, void* out, const int64_t* os, int32_t dtype, float scale, cudaStream_t stream) {
     const int Hkv = c->L.Hkv, D = c->L.D, G = n_q_heads / Hkv;

@@ -28,6 +28,10 @@ struct DecodeParams {
     float scale;
 };
 
+// decode.cu
+int launch_decode_simt(int fmt, int D, const DecodeParams& p, int n_items, cudaStream_t stream);
+int launch_combine(const DecodeParams& p, const int32_t* batch_info, void* out, int64_t ob, int64_t oh, int n_seqs,
+                   int n_q_heads, int D, cudaStream_t stream);
 // decode_mma.cu
 bool decode_mma_supported(int fmt, int D, int dtype);
 int launch_decode_mma(int fmt, const DecodeParams& p, int n_items, cudaStream_t stream);
