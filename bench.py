@@ -38,6 +38,14 @@ WORKLOADS = {
     "cfg3-bf16": ("bf16", "bf16", 256, "ragged", "BASELINE config 3: 256 sequences, past ~ U[512,16384], bf16"),
     "cfg1-f32": ("f32", "f32", 1, 2048, "BASELINE config 1: batch 1, past 2048, f32"),
 }
+# prefill workloads: name -> (io dtype, sequences per GPU, past tokens, chunk tokens, description)
+PREFILL = {
+    "cfg2-prefill": ("f16", 1, 0, 512, "BASELINE config 2: 512-token chunk appended to an empty cache, causal Sdpa 512x512, f16"),
+    "prefill-2k": ("f16", 1, 0, 2048, "config 2 geometry with a 2048-token chunk"),
+    "prefill-8k": ("f16", 1, 0, 8192, "config 2 geometry with an 8192-token chunk"),
+    "prefill-32k": ("f16", 1, 0, 32768, "config 2 geometry with a 32768-token chunk"),
+    "prefill-chunked": ("f16", 8, 7680, 512, "8 sequences, a 512-token chunk after 7680 cached tokens"),
+}
 HQ, HKV, D = 32, 8, 128
 OVERRIDE = {}  # --seqs / --past: smaller cases of a workload, for profiler captures
 ROW_BYTES = {"f32": 512, "f16": 256, "bf16": 256, "q8_1": 128 + 8, "q4_0": 64 + 8}  # stored bytes per token-head (codes + scales)
@@ -286,6 +294,124 @@ def run_ours(args, rank, world):
     return result
 
 
+def run_prefill(args, rank, world):
+    """Prefill chunk: append S tokens per sequence, then causal attention of the S queries over the cache.
+    Metric: causal-useful attention TFLOP/s (4 * Hq * D * sum over queries of visible keys)."""
+    import torch
+
+    import tract_b200 as kv
+
+    dev = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(dev)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{dev}"))
+    io, n_seq, past, S, desc = PREFILL[args.workload]
+    io_dt = {"f16": torch.float16, "bf16": torch.bfloat16}[io]
+    cache = kv.KvCache(io, HKV, D, max_seqs=n_seq, max_seq_tokens=past + S + 128)
+    seqs = [cache.new_seq() for _ in range(n_seq)]
+    if past:
+        fill_cache(torch, cache, seqs, [past] * n_seq, io_dt, seed=11 + rank)
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(3 + rank)
+    mk = lambda h: (torch.randn((n_seq, h, S, D), generator=gen, device="cuda") * 0.5).to(io_dt)
+    q, k_new, v_new = mk(HQ), mk(HKV), mk(HKV)
+    out = torch.empty_like(q)
+    hq, hk, hv = (t.cpu().pin_memory() for t in (q, k_new, v_new))
+    hout = torch.empty_like(out, device="cpu").pin_memory()
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k_new), torch.empty_like(v_new)
+
+    def step():
+        cache.append(seqs, k_new, v_new)
+        cache.attend(seqs, q, causal=True, out=out)
+        for s in seqs:
+            cache.truncate(s, past)
+
+    def step_e2e():
+        dq.copy_(hq, non_blocking=True), dk.copy_(hk, non_blocking=True), dv.copy_(hv, non_blocking=True)
+        cache.append(seqs, dk, dv)
+        cache.attend(seqs, dq, causal=True, out=out)
+        hout.copy_(out, non_blocking=True)
+        for s in seqs:
+            cache.truncate(s, past)
+
+    def timed(fn, steps):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        a.record()
+        for _ in range(steps):
+            fn()
+        b.record()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b)
+        if world > 1:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    sampler = ClockSampler(dev)
+    if rank == 0:
+        sampler.start()
+    n_warm, t_w = 0, time.perf_counter()
+    while n_warm < max(args.warmup, 3) or time.perf_counter() - t_w < (0.0 if args.quick else 1.0):
+        step()
+        n_warm += 1
+        if n_warm % 8 == 0:
+            torch.cuda.synchronize()
+    sampler.mark()
+    ms = timed(step, args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+    for _ in range(3):
+        step_e2e()
+    ms_e2e = timed(step_e2e, args.steps)
+    cache.profile(True)
+    torch.cuda.synchronize()
+    for _ in range(args.steps):
+        step()
+    recs = cache.profile_read()
+    cache.profile(False)
+    cache.check()
+    per_kernel = {}
+    for name, t in recs:
+        per_kernel.setdefault(name, []).append(t)
+    useful = 4.0 * HQ * D * n_seq * sum(past + i + 1 for i in range(S))  # causal-useful flops per step per GPU
+    result = None
+    if rank == 0:
+        pk, pk_kind = peaks()
+        ms_step = ms / args.steps
+        k_ms = statistics.mean(per_kernel["prefill"])
+        achieved = useful / (k_ms * 1e-3) / 1e12
+        peak = pk.get("bf16_tflops", 1590.0)
+        h2d = sum(t.numel() * t.element_size() for t in (hq, hk, hv))
+        result = {
+            "metric": "prefill causal-useful attention TFLOP/s (sum over GPUs)", "value": world * useful / (ms_step * 1e-3) / 1e12,
+            "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": f"{io} operands, f32 accumulation",
+            "data": "synthetic",
+            "config": {"workload": args.workload, "description": desc, "sequences_per_gpu": n_seq, "past_tokens": past,
+                       "chunk_tokens": S, "q_heads": HQ, "kv_heads": HKV, "head_dim": D, "io_dtype": io,
+                       "parallelism": f"by-sequence x{world}, no collective",
+                       "l2": "working set fits L2 (warm)" if (past + S) * n_seq * HKV * D * 4 < 100e6 else "inputs larger than L2",
+                       "flops_per_step_per_gpu": useful},
+            "tokens_per_s": world * n_seq * S / (ms_step * 1e-3),
+            "e2e": {"value": world * useful / (ms_e2e / args.steps * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": hout.numel() * hout.element_size(), "ms_per_step": ms_e2e / args.steps},
+            "gpu_launches": len(recs), "kernels_ms": {k: statistics.mean(v) for k, v in per_kernel.items()},
+            "roofline": {"bound": "tensor", "kernel": "prefill_tc_kernel", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                         "frac": achieved / peak, "peak_kind": pk_kind + " (bf16 cuBLAS burst)", "traffic": None,
+                         "flops": "causal-useful (masked half of the diagonal tiles not counted)"},
+            "clocks": clocks,
+        }
+    cache.close()
+    return result
+
+
 # ---------------------------------------------------------------------------------------------------
 # CPU arm: the restatement of tract's own CPU algorithm (the Rust reference cannot be built here)
 # ---------------------------------------------------------------------------------------------------
@@ -388,7 +514,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=1000)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="cfg4-q8", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="cfg4-q8", choices=sorted(WORKLOADS) + sorted(PREFILL))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--quick", action="store_true", help="profiler runs: exactly W warm-up steps, no 1 s warm-up floor")
@@ -402,6 +528,11 @@ def main():
             args.steps = 10  # each CPU step takes seconds; keep the run within minutes
         r = run_reference(args, rank, world)
         if r:
+            print(json.dumps(r))
+        return
+    if args.workload in PREFILL:
+        r = run_prefill(args, rank, world)
+        if rank == 0:
             print(json.dumps(r))
         return
     r = run_ours(args, rank, world)

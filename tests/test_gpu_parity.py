@@ -275,6 +275,13 @@ def test_decode_explicit_scale_and_reuse_after_truncate(kv):
     ("f32", "f32", 4, 2, 64, 70, 33),
     ("bf16", "bf16", 8, 2, 128, 100, 64),
     ("q8_1", "f16", 8, 2, 128, 64, 64),
+    # the tcgen05 prefill kernel (f16 / bf16 pages, head_dim 128)
+    ("f16", "f16", 4, 1, 128, 0, 32),       # one partly filled page
+    ("f16", "f16", 8, 2, 128, 100, 33),     # S not a multiple of the queries per tile, past not page aligned
+    ("f16", "f16", 8, 8, 128, 70, 200),     # no grouping: 128 queries per tile
+    ("f16", "f16", 6, 2, 128, 5, 100),      # G = 3: 42 queries per tile, two dead rows
+    ("bf16", "bf16", 16, 2, 128, 300, 50),  # G = 8
+    ("f16", "f16", 32, 8, 128, 4000, 512),  # chunked prefill: a 512-token chunk after 4000 cached tokens
 ])
 def test_prefill_matches_oracle(kv, fmt, io, Hq, Hkv, D, P, S):
     scale = 0.5 if io != "f32" else 1.0
@@ -290,6 +297,28 @@ def test_prefill_matches_oracle(kv, fmt, io, Hq, Hkv, D, P, S):
     cache.check()
     err = attn_err(out, io, q, oracle_cache_view(fmt, k, io), oracle_cache_view(fmt, v, io), causal=True, threads=8)
     assert err <= TOL[io], err
+    cache.close()
+
+
+@pytest.mark.parametrize("io,causal", [("f16", True), ("f16", False), ("bf16", True)])
+def test_prefill_tensor_core_and_generic_paths_agree(kv, io, causal):
+    # two sequences of different length in one call; the tcgen05 kernel against export + generic kernel
+    Hq, Hkv, D, S, pasts = 16, 4, 128, 96, [200, 31]
+    cache = kv.KvCache(io, Hkv, D, max_seqs=2, max_seq_tokens=512)
+    seqs = [cache.new_seq() for _ in pasts]
+    for b, P in enumerate(pasts):
+        k, v = normal(500 + b, (1, Hkv, P, D)).astype(np_dtype(io)), normal(600 + b, (1, Hkv, P, D)).astype(np_dtype(io))
+        cache.append([seqs[b]], to_dev(k), to_dev(v))
+    kn, vn = normal(7, (2, Hkv, S, D)).astype(np_dtype(io)), normal(8, (2, Hkv, S, D)).astype(np_dtype(io))
+    cache.append(seqs, to_dev(kn), to_dev(vn))
+    q = to_dev(normal(9, (2, Hq, S, D)).astype(np_dtype(io)))
+    out_tc = cache.attend(seqs, q, causal=causal).float().cpu().numpy()
+    cache.profile(False, force_simt=True)
+    out_gen = cache.attend(seqs, q, causal=causal).float().cpu().numpy()
+    cache.profile(False)
+    cache.check()
+    # both round an f32 result to 16 bits: about one unit in the last place apart, measured against the tensor's scale
+    assert rel_err(out_tc, out_gen) <= (8e-3 if io == "bf16" else 1e-3)  # one ulp: 2^-7 (bf16), 2^-10 (f16) at most
     cache.close()
 
 

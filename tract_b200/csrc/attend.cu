@@ -28,7 +28,10 @@ extern "C" int b200kv_attend(b200kv_cache* c, int32_t n_seqs, const int32_t* seq
 
     if (n_new == 1) return launch_decode(c, n_seqs, seqs, n_q_heads, q, q_strides, out, out_strides, dtype, scale, stream);
 
-    // n_new > 1: materialise K / V of one sequence at a time (dequantised to f32 for the quantised
+    if (!c->force_simt && prefill_tc_supported(c, n_q_heads, dtype, q, q_strides, out, out_strides))
+        return launch_prefill_tc(c, n_seqs, seqs, n_q_heads, n_new, q, q_strides, out, out_strides, dtype, scale, causal, stream);
+
+    // otherwise: materialise K / V of one sequence at a time (dequantised to f32 for the quantised
     // formats, a bit copy otherwise) and run the generic kernel on them.
     const int Hkv = c->L.Hkv, D = c->L.D;
     const int kv_dtype = fmt_is_block_quant(c->L.fmt) ? B200KV_F32 : c->L.fmt;
