@@ -61,6 +61,9 @@ typedef struct {
     int32_t max_seqs;       /* sequences that can be live at once */
     int64_t max_seq_tokens; /* longest sequence (sizes the page table rows) */
     int64_t pool_tokens;    /* capacity of the page pool in tokens, summed over sequences */
+    int32_t flags;          /* bit 0: a lone (has_values == 0) KIVI cache quantises per token (the Value layout of
+                               QuantizedDynKeyValueCache, per_channel = false) instead of per channel */
+    int32_t reserved;       /* 0 */
 } b200kv_config;
 
 /* Thread-local message of the last failed call on this thread (tract_get_last_error analogue). */
@@ -124,6 +127,16 @@ int b200kv_export(b200kv_cache* cache, int32_t seq, void* k_out, const int64_t k
  *   Q4_0: codes uint8 [Hkv, len, D/2] (byte j of a block = element j | element j+16 << 4), scales as above
  * which = 0 for K, 1 for V.  Fails for the bit-copy formats (use b200kv_export). */
 int b200kv_export_codes(b200kv_cache* cache, int32_t seq, int32_t which, void* codes, void* scales, void* stream);
+
+/* Raw state of one stream (which = 0: K, 1: V) of a KIVI cache, in the order the reference's stores hold it
+ * (transformers/src/ops/quant_dyn_kv_cache.rs:98-116,159-180), for bit-exact checks:
+ *   sink      f32 [Hkv, min(len, 4), D]                     the first tokens, never quantised
+ *   codes     u8  [Hkv, n_q, D * bits / 8]                  packed codes of the n_q quantised tokens
+ *   lo, scale f32 [Hkv, n_q] (per-token stream) or [Hkv, n_q / 32, D] (per-channel stream)
+ *   residual  f32 [Hkv, n_res, D]                           per-channel stream: the partial block
+ * with n_q = len - 4 (per token) or 32 * ((len - 4) / 32) (per channel), n_res = (len - 4) % 32. */
+int b200kv_export_kivi(b200kv_cache* cache, int32_t seq, int32_t which, void* codes, float* lo, float* scale,
+                       float* sink, float* residual, void* stream);
 
 /* Drops the tail of a sequence (speculative-decoding rollback; DynKeyValueCacheState::truncate,
  * transformers/src/ops/dyn_kv_cache.rs:112-119 — on device, without the host round trip of

@@ -1,0 +1,121 @@
+"""KIVI storage quantisation (QuantizedDynKeyValueCache) on the GPU against the oracle's stores:
+codes, lo, scale, sinks and residual bit-exact; dequantised export bit-exact; attention within tolerance."""
+import numpy as np
+import pytest
+
+import oracle
+from util import TOL, normal, normal_with_outliers, rel_err
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+
+
+@pytest.fixture(scope="module")
+def kv():
+    import tract_b200
+
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device")
+    tract_b200.lib()
+    return tract_b200
+
+
+STEPS = [3, 2, 40, 1, 1, 1, 70, 1, 33]  # sinks filled over two calls, blocks completing inside and across calls
+
+
+def drive(cache, seqs, H, D, dt, seed, with_v=True):
+    """Appends STEPS chunks to every sequence; returns the concatenated K (and V) inputs [B, H, T, D]."""
+    ks, vs = [], []
+    for i, s in enumerate(STEPS):
+        k = normal_with_outliers(seed + i, (len(seqs), H, s, D)).astype(dt)
+        v = normal_with_outliers(seed + 100 + i, (len(seqs), H, s, D)).astype(dt)
+        if i == 4:
+            k[0, 0, 0, :] = 2.5          # hi == lo over a row / a channel run: scale 1
+            v[0, 0, 0, :] = -1.25
+        cache.append(seqs, torch.from_numpy(k).cuda(), torch.from_numpy(v).cuda() if with_v else None)
+        ks.append(k), vs.append(v)
+    return np.concatenate(ks, 2), np.concatenate(vs, 2)
+
+
+def check_stream(cache, sq, which, per_channel, X, bits):
+    """X: [H, T, D] inputs of one sequence; compares the raw stores of every head with the oracle's."""
+    raw = {k: v.cpu().numpy() for k, v in cache.export_kivi(sq, which, per_channel).items()}
+    H, T, D = X.shape
+    for h in range(H):
+        st = oracle.KiviStore(per_channel, D, bits)
+        st.push(X[h])
+        want = st.raw()
+        assert np.array_equal(raw["sink"][h], want["sink"])
+        assert np.array_equal(raw["codes"][h], want["codes"]), (which, h)
+        assert np.array_equal(raw["lo"][h].reshape(-1), want["lo"]) and np.array_equal(raw["scale"][h].reshape(-1), want["scale"])
+        if per_channel:
+            assert np.array_equal(raw["residual"][h], want["residual"])
+
+
+@pytest.mark.parametrize("fmt,bits", [("kivi8", 8), ("kivi4", 4)])
+@pytest.mark.parametrize("D", [128, 64])
+@pytest.mark.parametrize("dt", [np.float32, np.float16])
+def test_kivi_stores_bit_exact(kv, fmt, bits, D, dt):
+    H, B = 2, 2
+    T = sum(STEPS)
+    cache = kv.KvCache(fmt, H, D, max_seqs=B, max_seq_tokens=T + 64)
+    seqs = [cache.new_seq() for _ in range(B)]
+    K, V = drive(cache, seqs, H, D, dt, seed=10)
+    cache.check()
+    tdt = torch.float32 if dt == np.float32 else torch.float16
+    for b, sq in enumerate(seqs):
+        assert cache.seq_len(sq) == T
+        check_stream(cache, sq, 0, True, K[b], bits)
+        check_stream(cache, sq, 1, False, V[b], bits)
+        # the op's output: dequantised f32 cache cast to the input dtype (quant_dyn_kv_cache.rs:493)
+        gk, gv = cache.export(sq, tdt)
+        for got, X, pc in ((gk, K[b], True), (gv, V[b], False)):
+            for h in range(H):
+                st = oracle.KiviStore(pc, D, bits)
+                st.push(X[h])
+                assert got[h].cpu().numpy().tobytes() == st.dequant().astype(dt).tobytes()
+    with pytest.raises(kv.B200KvError, match="cannot be truncated"):
+        cache.truncate(seqs[0], 10)
+    cache.close()
+
+
+@pytest.mark.parametrize("per_token", [False, True])
+def test_lone_kivi_cache_and_fork(kv, per_token):
+    # a single QuantizedDynKeyValueCache node: one tensor, per channel (Keys) or per token (Values)
+    H, D = 2, 64
+    cache = kv.KvCache("kivi8", H, D, max_seqs=2, max_seq_tokens=256, has_values=False, per_token=per_token)
+    sq = cache.new_seq()
+    X, _ = drive(cache, [sq], H, D, np.float32, seed=50, with_v=False)
+    check_stream(cache, sq, 0, not per_token, X[0], 8)
+    f = cache.fork(sq)  # freeze / unfreeze on device
+    extra = normal(77, (1, H, 9, D))
+    cache.append([f], torch.from_numpy(extra).cuda())
+    check_stream(cache, f, 0, not per_token, np.concatenate([X[0], extra[0]], 1), 8)
+    check_stream(cache, sq, 0, not per_token, X[0], 8)
+    cache.check()
+    cache.close()
+
+
+@pytest.mark.parametrize("fmt,bits,io", [("kivi8", 8, "f16"), ("kivi4", 4, "f32")])
+def test_kivi_attention_matches_oracle(kv, fmt, bits, io):
+    # prefill 3 + decode steps like the fused-op test of the reference (inplace_kv_cache.rs:595-658), GQA 4/2
+    Hq, Hkv, D = 8, 2, 128
+    dt = np.float16 if io == "f16" else np.float32
+    cache = kv.KvCache(fmt, Hkv, D, max_seqs=1, max_seq_tokens=256)
+    sq = cache.new_seq()
+    kstore = [oracle.KiviStore(True, D, bits) for _ in range(Hkv)]
+    vstore = [oracle.KiviStore(False, D, bits) for _ in range(Hkv)]
+    for step, s in enumerate([3, 1, 1, 45, 1, 1]):
+        k, v = normal(200 + step, (1, Hkv, s, D)).astype(dt), normal(300 + step, (1, Hkv, s, D)).astype(dt)
+        q = normal(400 + step, (1, Hq, s, D)).astype(dt)
+        cache.append([sq], torch.from_numpy(k).cuda(), torch.from_numpy(v).cuda())
+        out = cache.attend([sq], torch.from_numpy(q).cuda(), causal=True)
+        for h in range(Hkv):
+            kstore[h].push(k[0, h]), vstore[h].push(v[0, h])
+        kd = np.stack([st.dequant() for st in kstore])[None]
+        vd = np.stack([st.dequant() for st in vstore])[None]
+        want = oracle.flash_sdpa(q, kd, vd, causal=True)
+        assert rel_err(out.float().cpu().numpy(), want.astype(np.float32)) <= TOL[io], step
+    cache.check()
+    cache.close()

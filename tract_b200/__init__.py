@@ -14,15 +14,16 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libb200kv.so")
 
 F32, F16, BF16 = 0, 1, 2
-FMT_F32, FMT_F16, FMT_BF16, FMT_Q8_1, FMT_Q4_0 = 0, 1, 2, 3, 4
-FORMATS = {"f32": FMT_F32, "f16": FMT_F16, "bf16": FMT_BF16, "q8_1": FMT_Q8_1, "q4_0": FMT_Q4_0}
+FMT_F32, FMT_F16, FMT_BF16, FMT_Q8_1, FMT_Q4_0, FMT_KIVI8, FMT_KIVI4 = 0, 1, 2, 3, 4, 5, 6
+FORMATS = {"f32": FMT_F32, "f16": FMT_F16, "bf16": FMT_BF16, "q8_1": FMT_Q8_1, "q4_0": FMT_Q4_0,
+           "kivi8": FMT_KIVI8, "kivi4": FMT_KIVI4}
 
 # every symbol include/b200kv.h declares
 EXPORTS = [
     "b200kv_last_error", "b200kv_version", "b200kv_create", "b200kv_destroy", "b200kv_seq_new", "b200kv_seq_free",
     "b200kv_seq_len", "b200kv_free_pages", "b200kv_page_bytes", "b200kv_append", "b200kv_attend", "b200kv_export",
     "b200kv_export_codes", "b200kv_truncate", "b200kv_fork", "b200kv_check", "b200kv_sdpa", "b200kv_profile",
-    "b200kv_profile_read", "b200kv_attend_static_scratch",
+    "b200kv_profile_read", "b200kv_attend_static_scratch", "b200kv_export_kivi",
 ]
 KERNEL_NAMES = {0: "table_scatter", 1: "append", 2: "decode", 3: "combine", 4: "export", 5: "sdpa_dense", 6: "prefill"}
 
@@ -34,7 +35,7 @@ class B200KvError(RuntimeError):
 class Config(C.Structure):
     _fields_ = [("device", C.c_int32), ("format", C.c_int32), ("n_kv_heads", C.c_int32), ("head_dim", C.c_int32),
                 ("has_values", C.c_int32), ("max_seqs", C.c_int32), ("max_seq_tokens", C.c_int64),
-                ("pool_tokens", C.c_int64)]
+                ("pool_tokens", C.c_int64), ("flags", C.c_int32), ("reserved", C.c_int32)]
 
 
 _lib = None
@@ -67,6 +68,7 @@ def lib():
         L.b200kv_truncate.argtypes = [vp, i32, i64]
         L.b200kv_fork.argtypes = [vp, i32, i32p, vp]
         L.b200kv_attend_static_scratch.argtypes = [vp, i32, i32p, i32, vp, i64p, vp, i64p, i32, C.c_float, vp]
+        L.b200kv_export_kivi.argtypes = [vp, i32, i32, vp, vp, vp, vp, vp, vp]
         L.b200kv_check.argtypes = [vp, vp]
         L.b200kv_profile.argtypes = [vp, i32]
         L.b200kv_profile_read.argtypes = [vp, i32, i32p, C.POINTER(C.c_float), i32p]
@@ -111,7 +113,7 @@ class KvCache:
     """One layer's paged K (and V) store for up to ``max_seqs`` independent sequences."""
 
     def __init__(self, fmt, n_kv_heads, head_dim, max_seqs, max_seq_tokens, pool_tokens=None, has_values=True,
-                 device=None):
+                 device=None, per_token=False):
         import torch
 
         if not torch.cuda.is_available():
@@ -120,7 +122,7 @@ class KvCache:
         self.fmt = FORMATS[fmt] if isinstance(fmt, str) else int(fmt)
         self.n_kv_heads, self.head_dim, self.has_values = n_kv_heads, head_dim, bool(has_values)
         cfg = Config(self.device, self.fmt, n_kv_heads, head_dim, int(has_values), max_seqs, max_seq_tokens,
-                     pool_tokens if pool_tokens is not None else max_seqs * max_seq_tokens)
+                     pool_tokens if pool_tokens is not None else max_seqs * max_seq_tokens, int(bool(per_token)), 0)
         h = C.c_void_p()
         _ck(lib().b200kv_create(C.byref(cfg), C.byref(h)))
         self._h = h
@@ -209,6 +211,24 @@ class KvCache:
         scales = torch.empty((self.n_kv_heads, n, self.head_dim // 32), dtype=torch.float16, device=f"cuda:{self.device}")
         _ck(lib().b200kv_export_codes(self._h, seq, which, codes.data_ptr(), scales.data_ptr(), _stream()))
         return codes, scales
+
+    def export_kivi(self, seq, which, per_channel):
+        """Raw stores of a KIVI cache: dict(codes, lo, scale, sink, residual) in the reference's order."""
+        import torch
+
+        n, H, D = self.seq_len(seq), self.n_kv_heads, self.head_dim
+        bits = 8 if self.fmt == FMT_KIVI8 else 4
+        n_sink, n_after = min(n, 4), max(n - 4, 0)
+        n_q = (n_after // 32) * 32 if per_channel else n_after
+        n_res = n_after - n_q if per_channel else 0
+        dev = f"cuda:{self.device}"
+        codes = torch.zeros((H, n_q, D * bits // 8), dtype=torch.uint8, device=dev)
+        npar = (H, n_q // 32, D) if per_channel else (H, n_q)
+        lo, scale = torch.zeros(npar, device=dev), torch.zeros(npar, device=dev)
+        sink, res = torch.zeros((H, n_sink, D), device=dev), torch.zeros((H, n_res, D), device=dev)
+        _ck(lib().b200kv_export_kivi(self._h, seq, which, codes.data_ptr(), lo.data_ptr(), scale.data_ptr(), sink.data_ptr(),
+                                     res.data_ptr(), _stream()))
+        return dict(codes=codes, lo=lo, scale=scale, sink=sink, residual=res)
 
     def truncate(self, seq, length):
         _ck(lib().b200kv_truncate(self._h, seq, length))

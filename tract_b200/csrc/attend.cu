@@ -26,15 +26,16 @@ extern "C" int b200kv_attend(b200kv_cache* c, int32_t n_seqs, const int32_t* seq
     cudaStream_t stream = (cudaStream_t)stream_;
     DeviceGuard guard(c->cfg.device);
 
-    if (n_new == 1) return launch_decode(c, n_seqs, seqs, n_q_heads, q, q_strides, out, out_strides, dtype, scale, stream);
+    const bool kivi = fmt_is_kivi(c->L.fmt);
+    if (n_new == 1 && !kivi) return launch_decode(c, n_seqs, seqs, n_q_heads, q, q_strides, out, out_strides, dtype, scale, stream);
 
-    if (!c->force_simt && prefill_tc_supported(c, n_q_heads, dtype, q, q_strides, out, out_strides))
+    if (!kivi && !c->force_simt && prefill_tc_supported(c, n_q_heads, dtype, q, q_strides, out, out_strides))
         return launch_prefill_tc(c, n_seqs, seqs, n_q_heads, n_new, q, q_strides, out, out_strides, dtype, scale, causal, stream);
 
     // otherwise: materialise K / V of one sequence at a time (dequantised to f32 for the quantised
     // formats, a bit copy otherwise) and run the generic kernel on them.
     const int Hkv = c->L.Hkv, D = c->L.D;
-    const int kv_dtype = fmt_is_block_quant(c->L.fmt) ? B200KV_F32 : c->L.fmt;
+    const int kv_dtype = (fmt_is_block_quant(c->L.fmt) || kivi) ? B200KV_F32 : c->L.fmt;
     int64_t max_len = 0;
     for (int i = 0; i < n_seqs; i++) max_len = std::max<int64_t>(max_len, c->seqs[seqs[i]].len);
     const size_t one = (size_t)Hkv * max_len * D * dtype_size(kv_dtype);
@@ -44,7 +45,9 @@ extern "C" int b200kv_attend(b200kv_cache* c, int32_t n_seqs, const int32_t* seq
         void* kbuf = c->ws;
         void* vbuf = c->ws + one;
         const int64_t st2[2] = {T * D, D};
-        if (launch_export(c, seqs[i], kbuf, st2, vbuf, st2, kv_dtype, stream) != B200KV_OK) return B200KV_KO;
+        if ((kivi ? kivi_export(c, seqs[i], kbuf, st2, vbuf, st2, kv_dtype, stream)
+                  : launch_export(c, seqs[i], kbuf, st2, vbuf, st2, kv_dtype, stream)) != B200KV_OK)
+            return B200KV_KO;
         const int64_t ks[3] = {0, T * D, D};
         const int esz = dtype_size(dtype);
         const void* qi = (const uint8_t*)q + (int64_t)i * q_strides[0] * esz;

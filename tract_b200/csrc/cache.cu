@@ -325,7 +325,7 @@ __global__ void __launch_bounds__(256) export_kernel(ExportParams p) {
 // ---- host side --------------------------------------------------------------------------------------
 
 static int alloc_pages(b200kv_cache* c, SeqState& s, int64_t new_len, std::vector<int32_t>& upd, int row) {
-    int64_t need = (new_len + PAGE_TOKENS - 1) / PAGE_TOKENS;
+    int64_t need = fmt_is_kivi(c->cfg.format) ? kivi_pages_for(new_len) : (new_len + PAGE_TOKENS - 1) / PAGE_TOKENS;
     int64_t have = (int64_t)s.pages.size();
     if (need > c->max_pages_per_seq) return fail("sequence would exceed max_seq_tokens (%lld)", (long long)c->cfg.max_seq_tokens);
     if (need - have > (int64_t)c->free_pages.size())
@@ -388,7 +388,7 @@ const char* b200kv_version(void) { return "b200kv 0.1 sm_100a"; }
 int b200kv_create(const b200kv_config* cfg, b200kv_cache** out) {
     if (!cfg || !out) return fail("null argument");
     *out = nullptr;
-    if (cfg->format < B200KV_FMT_F32 || cfg->format > B200KV_FMT_Q4_0)
+    if (cfg->format < B200KV_FMT_F32 || cfg->format > B200KV_FMT_KIVI4)
         return fail("storage format %d is not available in this build", cfg->format);
     if (cfg->head_dim != 64 && cfg->head_dim != 128) return fail("head_dim must be 64 or 128, got %d", cfg->head_dim);
     if (cfg->n_kv_heads <= 0 || cfg->max_seqs <= 0 || cfg->max_seq_tokens <= 0 || cfg->pool_tokens <= 0)
@@ -413,12 +413,16 @@ int b200kv_create(const b200kv_config* cfg, b200kv_cache** out) {
         b200kv_destroy(c);
         return rc;
     };
-    size_t pool_bytes = (size_t)c->n_pages * c->L.page_bytes;
-    if (cudaMalloc(&c->pool, pool_bytes) != cudaSuccess)
-        return cleanup(fail("cannot allocate a %zu-byte page pool: %s", pool_bytes, cudaGetErrorString(cudaGetLastError())));
-    // zero the pool once: unused token slots of a partly filled page are read (and masked) by the
-    // attention kernels and must hold finite values
-    if (cudaMemset(c->pool, 0, pool_bytes) != cudaSuccess) return cleanup(fail("cudaMemset failed"));
+    if (fmt_is_kivi(cfg->format)) {
+        if (kivi_create(c) != B200KV_OK) return cleanup(B200KV_KO);
+    } else {
+        size_t pool_bytes = (size_t)c->n_pages * c->L.page_bytes;
+        if (cudaMalloc(&c->pool, pool_bytes) != cudaSuccess)
+            return cleanup(fail("cannot allocate a %zu-byte page pool: %s", pool_bytes, cudaGetErrorString(cudaGetLastError())));
+        // zero the pool once: unused token slots of a partly filled page are read (and masked) by the
+        // attention kernels and must hold finite values
+        if (cudaMemset(c->pool, 0, pool_bytes) != cudaSuccess) return cleanup(fail("cudaMemset failed"));
+    }
     size_t table_bytes = (size_t)cfg->max_seqs * c->max_pages_per_seq * sizeof(int32_t);
     if (cudaMalloc(&c->d_table, table_bytes) != cudaSuccess || cudaMemset(c->d_table, 0xff, table_bytes) != cudaSuccess)
         return cleanup(fail("cannot allocate the page tables"));
@@ -453,6 +457,7 @@ int b200kv_destroy(b200kv_cache* c) {
     if (c->d_status) cudaFree(c->d_status);
     if (c->d_table) cudaFree(c->d_table);
     if (c->pool) cudaFree(c->pool);
+    kivi_destroy(c);
     delete c;
     return B200KV_OK;
 }
@@ -489,7 +494,10 @@ int64_t b200kv_seq_len(b200kv_cache* c, int32_t seq) {
 }
 
 int64_t b200kv_free_pages(b200kv_cache* c) { return c ? (int64_t)c->free_pages.size() : -1; }
-int64_t b200kv_page_bytes(b200kv_cache* c) { return c ? c->L.page_bytes : -1; }
+int64_t b200kv_page_bytes(b200kv_cache* c) {
+    if (!c) return -1;
+    return fmt_is_kivi(c->cfg.format) ? kivi_page_bytes(c) : c->L.page_bytes;
+}
 
 int b200kv_append(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t n_new, const void* k_new,
                   const int64_t k_strides[3], const void* v_new, const int64_t v_strides[3], int32_t dtype,
@@ -502,7 +510,7 @@ int b200kv_append(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t 
     if (c->L.has_v ? (!v_new || !v_strides) : (v_new != nullptr))
         return fail(c->L.has_v ? "this cache holds K and V: v_new is required" : "this cache holds one tensor: v_new must be NULL");
     if (dtype < B200KV_F32 || dtype > B200KV_BF16) return fail("unknown dtype %d", dtype);
-    if (!fmt_is_block_quant(c->L.fmt) && dtype != c->L.fmt)
+    if (!fmt_is_block_quant(c->L.fmt) && !fmt_is_kivi(c->L.fmt) && dtype != c->L.fmt)
         return fail("a bit-copy cache of format %d takes input of the same type, got dtype %d", c->L.fmt, dtype);
     DeviceGuard guard(c->cfg.device);
 
@@ -566,7 +574,9 @@ int b200kv_append(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t 
     };
     p.vec_ok = aligned(k_new, k_strides) && aligned(v_new, v_strides);
     const int n_kv = c->L.has_v ? 2 : 1;
-    {
+    if (fmt_is_kivi(c->L.fmt)) {
+        kivi_append(c, n_seqs, seqs, n_new, k_new, k_strides, v_new, v_strides, dtype, (const int32_t*)d, stream);
+    } else {
         ProfScope ps(c, K_APPEND, stream);
         switch (c->L.fmt) {
             case B200KV_FMT_F32: launch_append_fmt<B200KV_FMT_F32>(p, n_kv, stream); break;
@@ -592,9 +602,10 @@ int b200kv_export(b200kv_cache* c, int32_t seq, void* k_out, const int64_t k_str
     if (!k_out || !k_strides) return fail("k_out and its strides are required");
     if (v_out && (!c->L.has_v || !v_strides)) return fail("v_out given but the cache has no values / no strides");
     if (dtype < B200KV_F32 || dtype > B200KV_BF16) return fail("unknown dtype %d", dtype);
-    if (!fmt_is_block_quant(c->L.fmt) && dtype != c->L.fmt)
+    if (!fmt_is_block_quant(c->L.fmt) && !fmt_is_kivi(c->L.fmt) && dtype != c->L.fmt)
         return fail("a bit-copy cache exports its own element type (format %d), got dtype %d", c->L.fmt, dtype);
     DeviceGuard guard(c->cfg.device);
+    if (fmt_is_kivi(c->L.fmt)) return kivi_export(c, seq, k_out, k_strides, v_out, v_strides, dtype, (cudaStream_t)stream);
     return launch_export(c, seq, k_out, k_strides, v_out, v_strides, dtype, (cudaStream_t)stream);
 }
 
@@ -625,6 +636,9 @@ int b200kv_truncate(b200kv_cache* c, int32_t seq, int64_t len) {
     if (validate_seqs(c, 1, &seq) != B200KV_OK) return B200KV_KO;
     SeqState& s = c->seqs[seq];
     if (len < 0 || len > s.len) return fail("cannot truncate a sequence of %lld tokens to %lld", (long long)s.len, (long long)len);
+    // QuantizedDynKvCacheState has no truncate: a finalised block cannot give its f32 rows back
+    if (fmt_is_kivi(c->L.fmt) && len != s.len)
+        return fail("a KIVI cache cannot be truncated (blocks are frozen once quantised; the reference has no truncate either)");
     size_t keep = (size_t)((len + PAGE_TOKENS - 1) / PAGE_TOKENS);
     while (s.pages.size() > keep) {
         c->free_pages.push_back(s.pages.back());
@@ -663,10 +677,15 @@ int b200kv_fork(b200kv_cache* c, int32_t seq, int32_t* new_seq_out, void* stream
         int n = (int)(upd.size() / 2);
         table_scatter_kernel<<<(n + 255) / 256, 256, 0, stream>>>(c->d_table, (const int32_t*)d, n);
         staging_release(c, slot, stream);
-        for (size_t i = 0; i < src.pages.size(); i++)
-            B200KV_CUDA(cudaMemcpyAsync(c->pool + (int64_t)dst.pages[i] * c->L.page_bytes,
-                                        c->pool + (int64_t)src.pages[i] * c->L.page_bytes, c->L.page_bytes,
-                                        cudaMemcpyDeviceToDevice, stream));
+        if (!fmt_is_kivi(c->L.fmt))
+            for (size_t i = 0; i < src.pages.size(); i++)
+                B200KV_CUDA(cudaMemcpyAsync(c->pool + (int64_t)dst.pages[i] * c->L.page_bytes,
+                                            c->pool + (int64_t)src.pages[i] * c->L.page_bytes, c->L.page_bytes,
+                                            cudaMemcpyDeviceToDevice, stream));
+    }
+    if (fmt_is_kivi(c->L.fmt) && kivi_fork(c, seq, ns, stream) != B200KV_OK) {
+        b200kv_seq_free(c, ns);
+        return B200KV_KO;
     }
     dst.len = src.len;
     *new_seq_out = ns;

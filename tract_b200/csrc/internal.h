@@ -51,8 +51,21 @@ struct Staging {
 
 }  // namespace b200kv
 
+namespace b200kv {
+// Stores of the KIVI formats (kivi.cu); null for every other format.
+struct KiviStore {
+    uint8_t* codes[2] = {nullptr, nullptr};
+    float* params[2] = {nullptr, nullptr};
+    float* sinks = nullptr;
+    float* residual = nullptr;
+    int bits = 0, row_bytes = 0, n_streams = 0;
+    int per_channel[2] = {0, 0};
+};
+}  // namespace b200kv
+
 struct b200kv_cache {
     b200kv_config cfg;
+    b200kv::KiviStore kivi;
     b200kv::Layout L;
     int64_t n_pages = 0;
     int max_pages_per_seq = 0;
@@ -120,6 +133,17 @@ int launch_sdpa_dense(const void* q, const int64_t* qs, const void* k, const int
                       const int64_t* vs, const void* mask, const int64_t* ms, int mask_dtype, void* out,
                       const int64_t* os, int B, int Hq, int Hkv, int S, int T, int D, int dtype, int kv_dtype,
                       float scale, int causal, cudaStream_t stream);
+// kivi.cu
+bool fmt_is_kivi(int fmt);
+int kivi_create(b200kv_cache* c);
+void kivi_destroy(b200kv_cache* c);
+int64_t kivi_page_bytes(const b200kv_cache* c);
+int64_t kivi_pages_for(int64_t len);
+int kivi_append(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t n_new, const void* k_new, const int64_t* ks,
+                const void* v_new, const int64_t* vs, int32_t dtype, const int32_t* d_desc, cudaStream_t stream);
+int kivi_export(b200kv_cache* c, int32_t seq, void* k_out, const int64_t* ks, void* v_out, const int64_t* vs, int32_t dtype,
+                cudaStream_t stream);
+int kivi_fork(b200kv_cache* c, int32_t src, int32_t dst, cudaStream_t stream);
 // prefill_tc.cu
 bool prefill_tc_supported(const b200kv_cache* c, int n_q_heads, int dtype, const void* q, const int64_t* qs, const void* out,
                           const int64_t* os);
