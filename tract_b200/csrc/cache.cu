@@ -82,8 +82,11 @@ __global__ void table_scatter_kernel(int32_t* table, const int32_t* upd, int n) 
 
 struct AppendParams {
     uint8_t* pool;
-    const int32_t* table;
-    const int32_t* desc;  // per batch entry: {table row, length before the append}
+    int32_t* table;
+    const int32_t* desc;  // per batch entry: {table row, length before the append, offset of its first new page in
+                          // `upd` (or -1), page number of that first new page}
+    const int32_t* upd;   // (page-table index, page id) pairs of the pages this call allocated
+    int32_t n_upd;
     int* status;
     const void* src[2];
     int64_t sb[2], sh[2], ss[2];
@@ -94,6 +97,15 @@ struct AppendParams {
     int32_t dtype, vec_ok, has_v;
 };
 
+// Batch description of an append small enough to travel as a kernel parameter (no copy, no staging slot).
+constexpr int INLINE_APPEND = 256;
+struct InlineAppend {
+    int32_t n;  // entries in use; 0 = read p.desc / p.upd from device memory
+    int32_t pad[3];
+    int4 ent[INLINE_APPEND];  // {table row, length before the append, offset of the first new page in upd or -1, its page number}
+    int2 upd[INLINE_APPEND];  // (page-table index, page id) pairs
+};
+
 // Rust `x as i8` after f32::round / truncation: saturating, NaN -> 0.
 __device__ inline int sat_i8_rz(float x) {
     int i = __float2int_rz(x);  // saturates to int32, NaN -> 0
@@ -102,9 +114,15 @@ __device__ inline int sat_i8_rz(float x) {
 
 // One thread per 16-byte unit of a token-head row; grid.y selects K or V.
 template <int FMT>
-__global__ void __launch_bounds__(256) append_kernel(AppendParams p) {
+__global__ void __launch_bounds__(256) append_kernel(AppendParams p, const __grid_constant__ InlineAppend ia) {
     constexpr int EPU = elems_in_bytes<FMT>(16);  // elements per unit
     const int kv = blockIdx.y;
+    grid_launch_dependents();  // a decode launch that follows may be scheduled now; it waits for this grid before reading pages
+    if (blockIdx.x == 0 && blockIdx.y == 0)  // publish the new page-table entries (replaces a separate launch)
+        for (int i = threadIdx.x; i < p.n_upd; i += blockDim.x) {
+            const int2 u = ia.n ? ia.upd[i] : ((const int2*)p.upd)[i];
+            p.table[u.x] = u.y;
+        }
     const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int64_t total_rows = (int64_t)p.n_seqs * p.H * p.S;
     int64_t row = gid / p.units;
@@ -196,9 +214,15 @@ __global__ void __launch_bounds__(256) append_kernel(AppendParams p) {
     if (!valid) return;
 
     // ---- locate the page slot and store --------------------------------------------------------------
-    const int32_t trow = p.desc[2 * b], len0 = p.desc[2 * b + 1];
+    const int4 ent = ia.n ? ia.ent[b] : ((const int4*)p.desc)[b];
+    const int32_t trow = ent.x, len0 = ent.y, upd_off = ent.z, new_pn = ent.w;
     const int64_t pos = (int64_t)len0 + s;
-    const int32_t pg = p.table[(int64_t)trow * p.max_pages_per_seq + pos / PAGE_TOKENS];
+    const int32_t pn = (int32_t)(pos / PAGE_TOKENS);
+    // pages allocated by this very call are taken from the call descriptor: the table entries are written by
+    // block 0 of this launch (above) for the kernels that follow, not for this one
+    const int32_t pg = (upd_off >= 0 && pn >= new_pn)
+                           ? (ia.n ? ia.upd[upd_off + pn - new_pn].y : p.upd[2 * (upd_off + pn - new_pn) + 1])
+                           : p.table[(int64_t)trow * p.max_pages_per_seq + pn];
     if (pg < 0 || pg >= p.n_pages) {
         atomicOr(p.status, STATUS_PAGE_OOB);
         return;
@@ -341,10 +365,10 @@ static int alloc_pages(b200kv_cache* c, SeqState& s, int64_t new_len, std::vecto
 }
 
 template <int FMT>
-static void launch_append_fmt(const AppendParams& p, int n_kv, cudaStream_t stream) {
+static void launch_append_fmt(const AppendParams& p, const InlineAppend& ia, int n_kv, cudaStream_t stream) {
     int64_t threads = (int64_t)p.n_seqs * p.H * p.S * p.units;
     dim3 grid((unsigned)((threads + 255) / 256), n_kv);
-    append_kernel<FMT><<<grid, 256, 0, stream>>>(p);
+    append_kernel<FMT><<<grid, 256, 0, stream>>>(p, ia);
 }
 
 int launch_export(b200kv_cache* c, int32_t seq, void* k_out, const int64_t* ks, void* v_out, const int64_t* vs,
@@ -534,29 +558,51 @@ int b200kv_append(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t 
             return B200KV_KO;
         }
     }
-    size_t desc_words = (size_t)2 * n_seqs + upd.size();
-    int slot;
-    uint8_t *h, *d;
-    if (staging_acquire(c, desc_words * 4, &slot, &h, &d) != B200KV_OK) {
-        rollback(n_seqs);
-        return B200KV_KO;
+    std::vector<int32_t> upd_off(n_seqs, -1), new_pn(n_seqs, 0);
+    {
+        // alloc_pages appended this call's pages sequence by sequence: recover each sequence's run
+        size_t at = 0;
+        for (int i = 0; i < n_seqs; i++) {
+            const size_t grown = c->seqs[seqs[i]].pages.size() - old_pages[i];
+            if (grown) upd_off[i] = (int32_t)at, new_pn[i] = (int32_t)old_pages[i];
+            at += grown;
+        }
     }
-    int32_t* hw = (int32_t*)h;
-    for (int i = 0; i < n_seqs; i++) {
-        hw[2 * i] = seqs[i];
-        hw[2 * i + 1] = (int32_t)c->seqs[seqs[i]].len;
+    // small batches travel as a kernel parameter; larger ones (and the KIVI kernels) through a descriptor slot
+    InlineAppend ia{};
+    const bool inline_batch = n_seqs <= INLINE_APPEND && upd.size() / 2 <= (size_t)INLINE_APPEND && !fmt_is_kivi(c->L.fmt);
+    int slot = -1;
+    uint8_t *h = nullptr, *d = nullptr;
+    if (inline_batch) {
+        ia.n = n_seqs;
+        for (int i = 0; i < n_seqs; i++) ia.ent[i] = make_int4(seqs[i], (int)c->seqs[seqs[i]].len, upd_off[i], new_pn[i]);
+        for (size_t i = 0; i < upd.size() / 2; i++) ia.upd[i] = make_int2(upd[2 * i], upd[2 * i + 1]);
+    } else {
+        size_t desc_words = (size_t)4 * n_seqs + upd.size();
+        if (staging_acquire(c, desc_words * 4, &slot, &h, &d) != B200KV_OK) {
+            rollback(n_seqs);
+            return B200KV_KO;
+        }
+        int32_t* hw = (int32_t*)h;
+        for (int i = 0; i < n_seqs; i++) {
+            hw[4 * i] = seqs[i];
+            hw[4 * i + 1] = (int32_t)c->seqs[seqs[i]].len;
+            hw[4 * i + 2] = upd_off[i];
+            hw[4 * i + 3] = new_pn[i];
+        }
+        if (!upd.empty()) memcpy(hw + 4 * n_seqs, upd.data(), upd.size() * 4);
+        if (staging_upload(c, slot, desc_words * 4, stream) != B200KV_OK) {
+            rollback(n_seqs);
+            return B200KV_KO;
+        }
     }
-    if (!upd.empty()) memcpy(hw + 2 * n_seqs, upd.data(), upd.size() * 4);
-    if (staging_upload(c, slot, desc_words * 4, stream) != B200KV_OK) {
-        rollback(n_seqs);
-        return B200KV_KO;
-    }
-    if (!upd.empty()) {
+    if (!upd.empty() && fmt_is_kivi(c->L.fmt)) {  // the KIVI kernels read the table; the others take new pages from the descriptor
         int n = (int)(upd.size() / 2);
         ProfScope ps(c, K_SCATTER, stream);
-        table_scatter_kernel<<<(n + 255) / 256, 256, 0, stream>>>(c->d_table, (const int32_t*)d + 2 * n_seqs, n);
+        table_scatter_kernel<<<(n + 255) / 256, 256, 0, stream>>>(c->d_table, (const int32_t*)d + 4 * n_seqs, n);
     }
     AppendParams p{};
+    p.upd = (const int32_t*)d + 4 * n_seqs, p.n_upd = (int32_t)(upd.size() / 2);
     p.pool = c->pool, p.table = c->d_table, p.desc = (const int32_t*)d, p.status = c->d_status;
     p.src[0] = k_new, p.src[1] = v_new;
     p.sb[0] = k_strides[0], p.sh[0] = k_strides[1], p.ss[0] = k_strides[2];
@@ -579,15 +625,15 @@ int b200kv_append(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t 
     } else {
         ProfScope ps(c, K_APPEND, stream);
         switch (c->L.fmt) {
-            case B200KV_FMT_F32: launch_append_fmt<B200KV_FMT_F32>(p, n_kv, stream); break;
-            case B200KV_FMT_F16: launch_append_fmt<B200KV_FMT_F16>(p, n_kv, stream); break;
-            case B200KV_FMT_BF16: launch_append_fmt<B200KV_FMT_BF16>(p, n_kv, stream); break;
-            case B200KV_FMT_Q8_1: launch_append_fmt<B200KV_FMT_Q8_1>(p, n_kv, stream); break;
-            case B200KV_FMT_Q4_0: launch_append_fmt<B200KV_FMT_Q4_0>(p, n_kv, stream); break;
+            case B200KV_FMT_F32: launch_append_fmt<B200KV_FMT_F32>(p, ia, n_kv, stream); break;
+            case B200KV_FMT_F16: launch_append_fmt<B200KV_FMT_F16>(p, ia, n_kv, stream); break;
+            case B200KV_FMT_BF16: launch_append_fmt<B200KV_FMT_BF16>(p, ia, n_kv, stream); break;
+            case B200KV_FMT_Q8_1: launch_append_fmt<B200KV_FMT_Q8_1>(p, ia, n_kv, stream); break;
+            case B200KV_FMT_Q4_0: launch_append_fmt<B200KV_FMT_Q4_0>(p, ia, n_kv, stream); break;
         }
     }
     cudaError_t e = cudaGetLastError();
-    staging_release(c, slot, stream);
+    if (slot >= 0) staging_release(c, slot, stream);
     if (e != cudaSuccess) {
         rollback(n_seqs);
         return fail("append launch failed: %s", cudaGetErrorString(e));

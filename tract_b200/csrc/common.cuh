@@ -239,6 +239,25 @@ __device__ inline void bulk_g2s(void* dst_smem, const void* src_gmem, uint32_t b
                  : "memory");
 }
 
+// ---- programmatic dependent launch ------------------------------------------------------------------
+// A kernel launched with launch_after_predecessor may be scheduled while the kernel before it in the
+// stream is still draining; it must call grid_dependency_wait() before it touches anything that kernel
+// wrote.  A kernel calls grid_launch_dependents() once it no longer minds its successor being scheduled.
+__device__ inline void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ inline void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... P>
+inline cudaError_t launch_after_predecessor(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                            const P&... params) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr, cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, params...);
+}
+
 // Device status word bits.
 constexpr int STATUS_PAGE_OOB = 1;      // a page-table entry outside the pool
 constexpr int STATUS_WAIT_EXPIRED = 2;  // a bounded barrier wait gave up

@@ -62,7 +62,7 @@ __device__ inline float warp_sum(float v) {
 }
 
 template <int FMT, int D, int GT>
-__global__ void __launch_bounds__(128) decode_kernel(DecodeParams p) {
+__global__ void __launch_bounds__(128) decode_kernel(DecodeParams p, const __grid_constant__ InlineBatch ib) {
     using Gm = Geo<FMT, D>;
     const bool PRECISE = p.dtype == B200KV_F32;  // f32 callers get expf, 16-bit callers the fast exponential
     constexpr int NS = Gm::NS;
@@ -77,7 +77,7 @@ __global__ void __launch_bounds__(128) decode_kernel(DecodeParams p) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int sub = lane & 7, tl = lane >> 3;
     const int tg = tid >> 4, cu = tid & 15;
-    const WorkItem w = p.items[blockIdx.x];
+    const WorkItem w = ib.n ? resolve_work_item(ib, blockIdx.x) : p.items[blockIdx.x];
     const int kvh = blockIdx.y;
     const int g0 = blockIdx.z * GT;
     const int n_tiles = w.n_pages;
@@ -94,6 +94,8 @@ __global__ void __launch_bounds__(128) decode_kernel(DecodeParams p) {
         bulk_g2s(stages + (size_t)st * Gm::STAGE, src, Gm::STAGE, &bars[st]);
     };
 
+    grid_dependency_wait();    // the append that precedes this launch has written its pages
+    grid_launch_dependents();  // the combine pass may be scheduled; it waits for this grid before reading partials
     if (tid == 0) {
         for (int s = 0; s < NS; s++) mbar_init(&bars[s], 1);
         mbar_fence_init();
@@ -314,58 +316,87 @@ struct CombineParams {
 };
 
 // Second pass: out = sum_i e^{m_i - M} O_i / sum_i e^{m_i - M} l_i over the splits of one (sequence, q-head).
-__global__ void combine_kernel(CombineParams p) {
+// The pass is pure latency (a few KB per CTA), so nothing in it forms a chain of dependent round trips: the
+// (max, sum) pairs of all splits are fetched at once, and so are the partial outputs of each channel.
+__global__ void combine_kernel(CombineParams p, const __grid_constant__ InlineBatch ib) {
+    __shared__ float wgt_s[64], sum_s[64];  // at most 64 splits per sequence
+    __shared__ float den_s;
     const int b = blockIdx.x, hq = blockIdx.y, ch = threadIdx.x;
     const int kvh = hq / p.G, g = hq % p.G;
-    const int first = p.batch_info[2 * b], n = p.batch_info[2 * b + 1];
-    float M = -INFINITY;
-    for (int i = 0; i < n; i++) M = fmaxf(M, p.part_ml[(((int64_t)(first + i) * p.Hkv + kvh) * p.G + g) * 2]);
-    float num = 0.f, den = 0.f;
-    for (int i = 0; i < n; i++) {
-        const int64_t idx = ((int64_t)(first + i) * p.Hkv + kvh) * p.G + g;
-        const float wgt = expf(p.part_ml[idx * 2] - M);
-        den = fmaf(wgt, p.part_ml[idx * 2 + 1], den);
-        num = fmaf(wgt, p.part_o[idx * p.D + ch], num);
+    grid_dependency_wait();  // the decode kernel has published every partial
+    const int first = ib.n ? ib.ent[b].z : p.batch_info[2 * b], n = ib.n ? ib.ent[b].w : p.batch_info[2 * b + 1];
+    const int64_t stride = (int64_t)p.Hkv * p.G;
+    const int64_t base = ((int64_t)first * p.Hkv + kvh) * p.G + g;
+    if (ch < n) {
+        const float2 ml = *(const float2*)(p.part_ml + (base + ch * stride) * 2);
+        wgt_s[ch] = ml.x, sum_s[ch] = ml.y;
     }
-    st_from_f32(p.out, p.dtype, (int64_t)b * p.ob + (int64_t)hq * p.oh + ch, num / den);
+    __syncthreads();
+    if (ch == 0) {
+        float M = -INFINITY, den = 0.f;
+        for (int i = 0; i < n; i++) M = fmaxf(M, wgt_s[i]);
+        for (int i = 0; i < n; i++) {
+            const float wgt = expf(wgt_s[i] - M);
+            den = fmaf(wgt, sum_s[i], den);
+            wgt_s[i] = wgt;
+        }
+        den_s = den;
+    }
+    __syncthreads();
+    float num = 0.f;
+    const float* src = p.part_o + base * p.D + ch;
+#pragma unroll 1
+    for (int i0 = 0; i0 < n; i0 += 8) {  // eight partials in flight per round
+        float v[8];
+#pragma unroll
+        for (int k = 0; k < 8; k++) v[k] = (i0 + k < n) ? src[(int64_t)(i0 + k) * stride * p.D] : 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; k++) num = fmaf((i0 + k < n) ? wgt_s[i0 + k] : 0.f, v[k], num);
+    }
+    st_from_f32(p.out, p.dtype, (int64_t)b * p.ob + (int64_t)hq * p.oh + ch, num / den_s);
 }
 
 template <int FMT, int D, int GT>
-static int launch_decode_t(const DecodeParams& p, int n_items, cudaStream_t stream) {
+static int launch_decode_t(const DecodeParams& p, int n_items, cudaStream_t stream, const InlineBatch& ib) {
     using Gm = Geo<FMT, D>;
     const size_t smem = (size_t)Gm::NS * Gm::STAGE + decode_tail_bytes<GT>();
     B200KV_CUDA(cudaFuncSetAttribute(decode_kernel<FMT, D, GT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     dim3 grid(n_items, p.Hkv, (p.G + GT - 1) / GT);
-    decode_kernel<FMT, D, GT><<<grid, 128, smem, stream>>>(p);
-    B200KV_CUDA(cudaGetLastError());
+    B200KV_CUDA(launch_after_predecessor(decode_kernel<FMT, D, GT>, grid, dim3(128), smem, stream, p, ib));
     return B200KV_OK;
 }
 
 template <int FMT>
-static int launch_decode_f(const DecodeParams& p, int D, int n_items, cudaStream_t stream) {
-    if (p.G == 1) return D == 128 ? launch_decode_t<FMT, 128, 1>(p, n_items, stream) : launch_decode_t<FMT, 64, 1>(p, n_items, stream);
-    return D == 128 ? launch_decode_t<FMT, 128, 4>(p, n_items, stream) : launch_decode_t<FMT, 64, 4>(p, n_items, stream);
+static int launch_decode_f(const DecodeParams& p, int D, int n_items, cudaStream_t stream, const InlineBatch& ib) {
+    if (p.G == 1) return D == 128 ? launch_decode_t<FMT, 128, 1>(p, n_items, stream, ib) : launch_decode_t<FMT, 64, 1>(p, n_items, stream, ib);
+    return D == 128 ? launch_decode_t<FMT, 128, 4>(p, n_items, stream, ib) : launch_decode_t<FMT, 64, 4>(p, n_items, stream, ib);
 }
 
 // The two launch steps of a decode call, for callers in other translation units.
-int launch_decode_simt(int fmt, int D, const DecodeParams& p, int n_items, cudaStream_t stream) {
+const InlineBatch& empty_inline_batch() {
+    static const InlineBatch e = {};
+    return e;
+}
+
+int launch_decode_simt(int fmt, int D, const DecodeParams& p, int n_items, cudaStream_t stream, const InlineBatch* ibp) {
+    const InlineBatch& ib = ibp ? *ibp : empty_inline_batch();
     switch (fmt) {
-        case B200KV_FMT_F32: return launch_decode_f<B200KV_FMT_F32>(p, D, n_items, stream);
-        case B200KV_FMT_F16: return launch_decode_f<B200KV_FMT_F16>(p, D, n_items, stream);
-        case B200KV_FMT_BF16: return launch_decode_f<B200KV_FMT_BF16>(p, D, n_items, stream);
-        case B200KV_FMT_Q8_1: return launch_decode_f<B200KV_FMT_Q8_1>(p, D, n_items, stream);
-        case B200KV_FMT_Q4_0: return launch_decode_f<B200KV_FMT_Q4_0>(p, D, n_items, stream);
+        case B200KV_FMT_F32: return launch_decode_f<B200KV_FMT_F32>(p, D, n_items, stream, ib);
+        case B200KV_FMT_F16: return launch_decode_f<B200KV_FMT_F16>(p, D, n_items, stream, ib);
+        case B200KV_FMT_BF16: return launch_decode_f<B200KV_FMT_BF16>(p, D, n_items, stream, ib);
+        case B200KV_FMT_Q8_1: return launch_decode_f<B200KV_FMT_Q8_1>(p, D, n_items, stream, ib);
+        case B200KV_FMT_Q4_0: return launch_decode_f<B200KV_FMT_Q4_0>(p, D, n_items, stream, ib);
     }
     return fail("format %d has no decode kernel", fmt);
 }
 int launch_combine(const DecodeParams& p, const int32_t* batch_info, void* out, int64_t ob, int64_t oh, int n_seqs,
-                   int n_q_heads, int D, cudaStream_t stream) {
+                   int n_q_heads, int D, cudaStream_t stream, const InlineBatch* ibp) {
+    const InlineBatch& ib = ibp ? *ibp : empty_inline_batch();
     CombineParams cp{};
     cp.part_o = p.part_o, cp.part_ml = p.part_ml, cp.batch_info = batch_info;
     cp.out = out, cp.ob = ob, cp.oh = oh;
     cp.Hkv = p.Hkv, cp.G = p.G, cp.D = D, cp.dtype = p.dtype;
-    combine_kernel<<<dim3(n_seqs, n_q_heads), D, 0, stream>>>(cp);
-    B200KV_CUDA(cudaGetLastError());
+    B200KV_CUDA(launch_after_predecessor(combine_kernel, dim3(n_seqs, n_q_heads), dim3(D), 0, stream, cp, ib));
     return B200KV_OK;
 }
 
@@ -383,32 +414,39 @@ int launch_decode(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t 
     }
     const int64_t target_ctas = 148 * 16;
     const int64_t chunk = std::max<int64_t>(1, (total_pages * Hkv * nz + target_ctas - 1) / target_ctas);
-    std::vector<WorkItem> items;
-    std::vector<int32_t> info(2 * (size_t)n_seqs);
+    // one entry per sequence: {table row, length, first work item, splits}; the work items follow from it
+    InlineBatch ib{};
+    std::vector<int4> ent((size_t)n_seqs);
+    int n_items = 0;
     for (int i = 0; i < n_seqs; i++) {
         const SeqState& s = c->seqs[seqs[i]];
         const int pages = (int)((s.len + PAGE_TOKENS - 1) / PAGE_TOKENS);
-        int splits = (int)std::min<int64_t>(64, (pages + chunk - 1) / chunk);
-        info[2 * i] = (int32_t)items.size();
-        info[2 * i + 1] = splits;
-        int begin = 0;
-        for (int k = 0; k < splits; k++) {
-            int n = (pages - begin + (splits - k) - 1) / (splits - k);  // even split of what is left
-            items.push_back(WorkItem{seqs[i], (int32_t)s.len, begin, n, i, k, 0, 0});
-            begin += n;
-        }
+        const int splits = (int)std::min<int64_t>(64, (pages + chunk - 1) / chunk);
+        ent[i] = make_int4(seqs[i], (int)s.len, n_items, splits);
+        n_items += splits;
     }
-    const size_t items_bytes = items.size() * sizeof(WorkItem);
-    const size_t desc_bytes = items_bytes + info.size() * 4;
-    const size_t n_part = items.size() * (size_t)Hkv * G;
+    const bool inline_batch = n_seqs <= INLINE_BATCH;  // small batches travel as a kernel parameter: no copy, no slot
+    const size_t n_part = (size_t)n_items * Hkv * G;
     const size_t ws_need = n_part * (D + 2) * sizeof(float);
     if (ensure_workspace(c, ws_need) != B200KV_OK) return B200KV_KO;
-    int slot;
-    uint8_t *h, *d;
-    if (staging_acquire(c, desc_bytes, &slot, &h, &d) != B200KV_OK) return B200KV_KO;
-    memcpy(h, items.data(), items_bytes);
-    memcpy(h + items_bytes, info.data(), info.size() * 4);
-    if (staging_upload(c, slot, desc_bytes, stream) != B200KV_OK) return B200KV_KO;
+    int slot = -1;
+    uint8_t *h = nullptr, *d = nullptr;
+    size_t items_bytes = 0;
+    if (inline_batch) {
+        ib.n = n_seqs;
+        memcpy(ib.ent, ent.data(), (size_t)n_seqs * sizeof(int4));
+    } else {
+        items_bytes = (size_t)n_items * sizeof(WorkItem);
+        const size_t desc_bytes = items_bytes + (size_t)n_seqs * 8;
+        if (staging_acquire(c, desc_bytes, &slot, &h, &d) != B200KV_OK) return B200KV_KO;
+        WorkItem* items = (WorkItem*)h;
+        int32_t* info = (int32_t*)(h + items_bytes);
+        for (int i = 0; i < n_seqs; i++) {
+            info[2 * i] = ent[i].z, info[2 * i + 1] = ent[i].w;
+            for (int k = 0; k < ent[i].w; k++) items[ent[i].z + k] = make_work_item(ent[i], i, k);
+        }
+        if (staging_upload(c, slot, desc_bytes, stream) != B200KV_OK) return B200KV_KO;
+    }
 
     DecodeParams p{};
     p.pool = c->pool, p.table = c->d_table, p.items = (const WorkItem*)d, p.status = c->d_status;
@@ -421,14 +459,14 @@ int launch_decode(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t 
     {
     ProfScope ps(c, K_DECODE, stream);
     if (decode_mma_supported(c->L.fmt, D, dtype) && !c->force_simt) {
-        rc = launch_decode_mma(c->L.fmt, p, (int)items.size(), stream);
+        rc = launch_decode_mma(c->L.fmt, p, n_items, stream, &ib);
     } else
     switch (c->L.fmt) {
-        case B200KV_FMT_F32: rc = launch_decode_f<B200KV_FMT_F32>(p, D, (int)items.size(), stream); break;
-        case B200KV_FMT_F16: rc = launch_decode_f<B200KV_FMT_F16>(p, D, (int)items.size(), stream); break;
-        case B200KV_FMT_BF16: rc = launch_decode_f<B200KV_FMT_BF16>(p, D, (int)items.size(), stream); break;
-        case B200KV_FMT_Q8_1: rc = launch_decode_f<B200KV_FMT_Q8_1>(p, D, (int)items.size(), stream); break;
-        case B200KV_FMT_Q4_0: rc = launch_decode_f<B200KV_FMT_Q4_0>(p, D, (int)items.size(), stream); break;
+        case B200KV_FMT_F32: rc = launch_decode_f<B200KV_FMT_F32>(p, D, n_items, stream, ib); break;
+        case B200KV_FMT_F16: rc = launch_decode_f<B200KV_FMT_F16>(p, D, n_items, stream, ib); break;
+        case B200KV_FMT_BF16: rc = launch_decode_f<B200KV_FMT_BF16>(p, D, n_items, stream, ib); break;
+        case B200KV_FMT_Q8_1: rc = launch_decode_f<B200KV_FMT_Q8_1>(p, D, n_items, stream, ib); break;
+        case B200KV_FMT_Q4_0: rc = launch_decode_f<B200KV_FMT_Q4_0>(p, D, n_items, stream, ib); break;
         default: rc = fail("format %d has no decode kernel", c->L.fmt);
     }
     }
@@ -438,10 +476,10 @@ int launch_decode(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t 
         cp.part_o = p.part_o, cp.part_ml = p.part_ml, cp.batch_info = (const int32_t*)(d + items_bytes);
         cp.out = out, cp.ob = os[0], cp.oh = os[1];
         cp.Hkv = Hkv, cp.G = G, cp.D = D, cp.dtype = dtype;
-        combine_kernel<<<dim3(n_seqs, n_q_heads), D, 0, stream>>>(cp);
-        if (cudaGetLastError() != cudaSuccess) rc = fail("combine launch failed");
+        if (launch_after_predecessor(combine_kernel, dim3(n_seqs, n_q_heads), dim3(D), 0, stream, cp, ib) != cudaSuccess)
+            rc = fail("combine launch failed: %s", cudaGetErrorString(cudaGetLastError()));
     }
-    staging_release(c, slot, stream);
+    if (slot >= 0) staging_release(c, slot, stream);
     return rc;
 }
 

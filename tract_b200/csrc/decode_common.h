@@ -28,12 +28,46 @@ struct DecodeParams {
     float scale;
 };
 
+// Per-call batch description small enough to travel as a kernel parameter (no host-to-device copy, no
+// staging slot): one entry per sequence of the call, {page-table row, cached length, first work item,
+// number of splits}.  The work items are a pure function of it: split k of a sequence with `pages` pages
+// covers pages [k * base + min(k, rem), ...) where base = pages / splits, rem = pages % splits.
+constexpr int INLINE_BATCH = 256;
+struct InlineBatch {
+    int32_t n;  // entries in use; 0 = the kernels read p.items / batch_info from device memory instead
+    int32_t pad[3];
+    int4 ent[INLINE_BATCH];
+};
+
+__host__ __device__ inline WorkItem make_work_item(const int4& e, int batch, int k) {
+    const int pages = (e.y + PAGE_TOKENS - 1) / PAGE_TOKENS;
+    const int base = pages / e.w, rem = pages % e.w;
+    WorkItem w;
+    w.trow = e.x, w.len = e.y;
+    w.page_begin = k * base + (k < rem ? k : rem);
+    w.n_pages = base + (k < rem ? 1 : 0);
+    w.batch = batch, w.split = k, w.pad0 = w.pad1 = 0;
+    return w;
+}
+// Work item `item` of an inline batch: binary search for the sequence that owns it.
+__device__ inline WorkItem resolve_work_item(const InlineBatch& ib, int item) {
+    int lo = 0, hi = ib.n - 1;
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (ib.ent[mid].z <= item) lo = mid;
+        else hi = mid - 1;
+    }
+    return make_work_item(ib.ent[lo], lo, item - ib.ent[lo].z);
+}
+
 // decode.cu
-int launch_decode_simt(int fmt, int D, const DecodeParams& p, int n_items, cudaStream_t stream);
+int launch_decode_simt(int fmt, int D, const DecodeParams& p, int n_items, cudaStream_t stream, const InlineBatch* ib = nullptr);
 int launch_combine(const DecodeParams& p, const int32_t* batch_info, void* out, int64_t ob, int64_t oh, int n_seqs,
-                   int n_q_heads, int D, cudaStream_t stream);
+                   int n_q_heads, int D, cudaStream_t stream, const InlineBatch* ib = nullptr);
 // decode_mma.cu
 bool decode_mma_supported(int fmt, int D, int dtype);
-int launch_decode_mma(int fmt, const DecodeParams& p, int n_items, cudaStream_t stream);
+int launch_decode_mma(int fmt, const DecodeParams& p, int n_items, cudaStream_t stream, const InlineBatch* ib = nullptr);
+// An InlineBatch with n = 0, for launches that read their batch from device memory.
+const InlineBatch& empty_inline_batch();
 
 }  // namespace b200kv

@@ -91,7 +91,7 @@ __device__ inline float quad_row_sum(float v) {
 constexpr size_t MMA_TAIL = 8 * MD * 4 + 32 * 4 + 64;
 
 template <int FMT>
-__global__ void __launch_bounds__(128, 3) decode_mma_kernel(DecodeParams p) {
+__global__ void __launch_bounds__(128, 3) decode_mma_kernel(DecodeParams p, const __grid_constant__ InlineBatch ib) {
     using Gm = MGeo<FMT>;
     constexpr int NS = Gm::NS;
     constexpr bool QUANT = Gm::QUANT;
@@ -111,7 +111,7 @@ __global__ void __launch_bounds__(128, 3) decode_mma_kernel(DecodeParams p) {
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int r = lane >> 2, c = lane & 3;
-    const WorkItem w = p.items[blockIdx.x];
+    const WorkItem w = ib.n ? resolve_work_item(ib, blockIdx.x) : p.items[blockIdx.x];
     const int kvh = blockIdx.y;
     const int g0 = blockIdx.z * 8;
     const int ng = min(8, p.G - g0);  // q heads of this CTA
@@ -128,6 +128,8 @@ __global__ void __launch_bounds__(128, 3) decode_mma_kernel(DecodeParams p) {
         mbar_expect_tx(&bars[st], Gm::STAGE);
         bulk_g2s(stages + (size_t)st * Gm::STAGE, src, Gm::STAGE, &bars[st]);
     };
+    grid_dependency_wait();    // the append that precedes this launch has written its pages
+    grid_launch_dependents();  // the combine pass may be scheduled; it waits for this grid before reading partials
     if (tid == 0) {
         for (int s = 0; s < NS; s++) mbar_init(&bars[s], 1);
         mbar_fence_init();
@@ -442,15 +444,14 @@ __global__ void __launch_bounds__(128, 3) decode_mma_kernel(DecodeParams p) {
 }
 
 template <int FMT>
-static int launch_mma_t(const DecodeParams& p, int n_items, cudaStream_t stream) {
+static int launch_mma_t(const DecodeParams& p, int n_items, cudaStream_t stream, const InlineBatch& ib) {
     using Gm = MGeo<FMT>;
     const size_t ring = (size_t)Gm::NS * Gm::STAGE;
     const size_t merge = (size_t)(4 * 8 * MD + 4 * 8 * 2) * 4;  // the warp merge reuses the ring
     const size_t smem = std::max(ring, merge) + MMA_TAIL;
     B200KV_CUDA(cudaFuncSetAttribute(decode_mma_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     dim3 grid(n_items, p.Hkv, (p.G + 7) / 8);
-    decode_mma_kernel<FMT><<<grid, 128, smem, stream>>>(p);
-    B200KV_CUDA(cudaGetLastError());
+    B200KV_CUDA(launch_after_predecessor(decode_mma_kernel<FMT>, grid, dim3(128), smem, stream, p, ib));
     return B200KV_OK;
 }
 
@@ -462,12 +463,13 @@ bool decode_mma_supported(int fmt, int D, int dtype) {
     return false;
 }
 
-int launch_decode_mma(int fmt, const DecodeParams& p, int n_items, cudaStream_t stream) {
+int launch_decode_mma(int fmt, const DecodeParams& p, int n_items, cudaStream_t stream, const InlineBatch* ibp) {
+    const InlineBatch& ib = ibp ? *ibp : empty_inline_batch();
     switch (fmt) {
-        case B200KV_FMT_F16: return launch_mma_t<B200KV_FMT_F16>(p, n_items, stream);
-        case B200KV_FMT_BF16: return launch_mma_t<B200KV_FMT_BF16>(p, n_items, stream);
-        case B200KV_FMT_Q8_1: return launch_mma_t<B200KV_FMT_Q8_1>(p, n_items, stream);
-        case B200KV_FMT_Q4_0: return launch_mma_t<B200KV_FMT_Q4_0>(p, n_items, stream);
+        case B200KV_FMT_F16: return launch_mma_t<B200KV_FMT_F16>(p, n_items, stream, ib);
+        case B200KV_FMT_BF16: return launch_mma_t<B200KV_FMT_BF16>(p, n_items, stream, ib);
+        case B200KV_FMT_Q8_1: return launch_mma_t<B200KV_FMT_Q8_1>(p, n_items, stream, ib);
+        case B200KV_FMT_Q4_0: return launch_mma_t<B200KV_FMT_Q4_0>(p, n_items, stream, ib);
     }
     return fail("format %d has no tensor-core decode kernel", fmt);
 }

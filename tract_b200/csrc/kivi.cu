@@ -57,7 +57,7 @@ __device__ inline uint32_t kivi_load_code(const KiviView& v, int stream, int32_t
 
 struct KiviAppend {
     KiviView v;
-    const int32_t* desc;  // per batch entry {sequence, length before the append}
+    const int32_t* desc;  // per batch entry {sequence, length before the append, -, -}
     const void* src[2];
     int64_t sb[2], sh[2], ss[2];
     int32_t n_seqs, S, dtype;
@@ -70,7 +70,7 @@ struct KiviAppend {
 __global__ void kivi_block_kernel(KiviAppend a, int stream) {
     const KiviView& v = a.v;
     const int b = blockIdx.z, h = blockIdx.y, c = threadIdx.x;
-    const int32_t seq = a.desc[2 * b], len0 = a.desc[2 * b + 1];
+    const int32_t seq = a.desc[4 * b], len0 = a.desc[4 * b + 1];
     const int i_begin = max(len0 - SINK, 0), i_end = max(len0 + a.S - SINK, 0);
     const int j = i_begin / KBLOCK + blockIdx.x;  // block index
     if (j >= i_end / KBLOCK) return;              // not completed by this call
@@ -112,7 +112,7 @@ __global__ void kivi_row_kernel(KiviAppend a) {
     const KiviView& v = a.v;
     const int stream = blockIdx.x / a.S, s = blockIdx.x % a.S;
     const int b = blockIdx.z, h = blockIdx.y, c = threadIdx.x;
-    const int32_t seq = a.desc[2 * b], len0 = a.desc[2 * b + 1];
+    const int32_t seq = a.desc[4 * b], len0 = a.desc[4 * b + 1];
     const int t = len0 + s;
     const float x = ld_as_f32(a.src[stream], a.dtype, b * a.sb[stream] + h * a.sh[stream] + s * a.ss[stream] + c);
     if (t < SINK) {
