@@ -263,7 +263,7 @@ __global__ void __launch_bounds__(256) append_kernel(AppendParams p, const __gri
     }
     if (write_scale) {
         int blk = (FMT == B200KV_FMT_Q8_1) ? u / 2 : u;
-        ((__half*)(chunk + p.data_bytes))[t * (p.D / 32) + blk] = __float2half_rn(scale_f);
+        ((__half*)(chunk + p.data_bytes))[scale_index(FMT, p.D, kv, t, blk)] = __float2half_rn(scale_f);
     }
 }
 
@@ -319,7 +319,7 @@ __global__ void __launch_bounds__(256) export_kernel(ExportParams p) {
         return;
     }
     const int nb = p.D / 32;
-    const __half* scales = (const __half*)(chunk + p.data_bytes) + t * nb;
+    const __half* scales = (const __half*)(chunk + p.data_bytes);
     const int c0 = u * EPU;  // first channel of this thread (Q8_1: 16 channels, Q4_0: one block of 32)
     if (MODE == 1) {
         uint8_t out[16];
@@ -334,7 +334,7 @@ __global__ void __launch_bounds__(256) export_kernel(ExportParams p) {
         uint8_t* dst = (uint8_t*)p.codes + ((int64_t)h * p.len + tok) * p.row_bytes + u * 16;
 #pragma unroll
         for (int i = 0; i < 16; i++) dst[i] = out[i];
-        if (u < nb) ((__half*)p.scales)[((int64_t)h * p.len + tok) * nb + u] = scales[u];
+        if (u < nb) ((__half*)p.scales)[((int64_t)h * p.len + tok) * nb + u] = scales[scale_index(FMT, p.D, kv, t, u)];
         return;
     }
 #pragma unroll
@@ -342,7 +342,7 @@ __global__ void __launch_bounds__(256) export_kernel(ExportParams p) {
         const int ch = c0 + i;
         const int code = load_code<FMT>(chunk, p.D, kv, t, ch) - (FMT == B200KV_FMT_Q4_0 ? 8 : 0);
         // code * f32(f16 scale): exact in f32 (q8_1.rs:50-63, q4_0.rs:82-95)
-        st_from_f32(p.dst[kv], p.dtype, base + ch, __fmul_rn((float)code, __half2float(scales[ch / 32])));
+        st_from_f32(p.dst[kv], p.dtype, base + ch, __fmul_rn((float)code, __half2float(scales[scale_index(FMT, p.D, kv, t, ch / 32)])));
     }
 }
 

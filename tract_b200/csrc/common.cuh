@@ -101,6 +101,13 @@ __host__ __device__ constexpr int code_nibble(int fmt, int D, int kv, int ch) {
     return v_permuted(fmt, D, kv) ? (ch / 8) & 1 : (ch % 32) / 16;
 }
 
+// Index (in f16 units) of the scale of block `blk` of token slot `t` inside a chunk's scale region.  K rows
+// and all D = 64 rows keep [token][block]; the permuted V rows keep [token pair][block][2], so that the
+// tensor-core decode kernel reads (scale of token 2p, scale of token 2p + 1) of a block as one f16 pair.
+__host__ __device__ constexpr int scale_index(int fmt, int D, int kv, int t, int blk) {
+    return v_permuted(fmt, D, kv) ? ((t >> 1) * 4 + blk) * 2 + (t & 1) : t * (D / 32) + blk;
+}
+
 // Channel index of element e of the piece that starts at row byte rb (piece_bytes long), natural
 // row order.  Q4_0 pieces yield their low-nibble elements first, then the high-nibble ones.
 template <int FMT>

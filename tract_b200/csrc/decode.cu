@@ -230,7 +230,9 @@ __global__ void __launch_bounds__(128) decode_kernel(DecodeParams p, const __gri
                         load_piece<FMT, Gm::PB2>(Vs + chunk_addr(FMT, D, 1, t, rb), vals);
                         if constexpr (v_permuted(FMT, D, 1)) {
                             // permuted V row: this thread's elements fall into blocks 2(cu & 1) and 2(cu & 1) + 1
-                            const float2 d2 = __half22float2(((const __half2*)(Vs + Gm::DATA))[t * 2 + (cu & 1)]);
+                            const __half* vsc = (const __half*)(Vs + Gm::DATA);
+                            const float2 d2 = make_float2(__half2float(vsc[scale_index(FMT, D, 1, t, 2 * (cu & 1))]),
+                                                          __half2float(vsc[scale_index(FMT, D, 1, t, 2 * (cu & 1) + 1)]));
 #pragma unroll
                             for (int e = 0; e < Gm::EPP2; e++) {
                                 const bool upper = FMT == B200KV_FMT_Q8_1 ? (e >= 4) : ((e % 4) >= 2);

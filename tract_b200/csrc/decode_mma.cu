@@ -36,7 +36,9 @@ struct MGeo {
     static constexpr int SCALES = QUANT ? PAGE_TOKENS * (MD / 32) * 2 : 0;
     static constexpr int CHUNK = DATA + SCALES;
     static constexpr int STAGE = 2 * CHUNK;
-    static constexpr int NS = FMT == B200KV_FMT_Q4_0 ? 6 : (QUANT ? 4 : 3);
+    static constexpr int NS = FMT == B200KV_FMT_Q4_0 ? 5 : (QUANT ? 4 : 3);
+    // measured: Q8_1 is best with 3 CTAs x 4 stages, Q4_0 with 4 CTAs x 5 stages, the 16-bit formats are HBM bound at 2
+    static constexpr int MIN_CTAS = FMT == B200KV_FMT_Q4_0 ? 4 : (QUANT ? 3 : 2);  // resident CTAs per SM the register budget is set for
 };
 
 __device__ inline void mma_f16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
@@ -76,6 +78,11 @@ __device__ inline uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
     return *(uint32_t*)&h;
 }
+__device__ inline float fast_ex2(float x) {  // 2^x, one MUFU instruction; 2^-inf = 0
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ inline float quad_row_max(float v) {  // over the 8 rows of a fragment (lanes differing in bits 2..4)
     v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 4));
     v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 8));
@@ -91,7 +98,7 @@ __device__ inline float quad_row_sum(float v) {
 constexpr size_t MMA_TAIL = 8 * MD * 4 + 32 * 4 + 64;
 
 template <int FMT>
-__global__ void __launch_bounds__(128, 3) decode_mma_kernel(DecodeParams p, const __grid_constant__ InlineBatch ib) {
+__global__ void __launch_bounds__(128, MGeo<FMT>::MIN_CTAS) decode_mma_kernel(DecodeParams p, const __grid_constant__ InlineBatch ib) {
     using Gm = MGeo<FMT>;
     constexpr int NS = Gm::NS;
     constexpr bool QUANT = Gm::QUANT;
@@ -153,9 +160,14 @@ __global__ void __launch_bounds__(128, 3) decode_mma_kernel(DecodeParams p, cons
 #pragma unroll
         for (int s = 0; s < 8; s++) {
             int k0, k1;
-            if (QUANT) {  // k-step (block b = s/2, half hh = s%2): channels 32b + 8c + 4hh + {0,1 | 2,3}
+            float qf = 1.f;
+            if (FMT == B200KV_FMT_Q8_1) {  // k-step (block b = s/2, half hh = s%2): channels 32b + 8c + 4hh + {0,1 | 2,3}
                 k0 = 32 * (s >> 1) + 8 * c + 4 * (s & 1);
                 k1 = k0 + 2;
+            } else if (FMT == B200KV_FMT_Q4_0) {  // channels 32b + 16hh + 4c + {0,1 | 2,3}; hh = 1 meets 16 * code
+                k0 = 32 * (s >> 1) + 16 * (s & 1) + 4 * c;
+                k1 = k0 + 2;
+                qf = (s & 1) ? 0.0625f : 1.f;
             } else {  // natural order: channels 16s + 2c + {0,1 | 8,9}
                 k0 = 16 * s + 2 * c;
                 k1 = k0 + 8;
@@ -164,8 +176,8 @@ __global__ void __launch_bounds__(128, 3) decode_mma_kernel(DecodeParams p, cons
                 qb[s][0] = pack_bf16(qrow[k0], qrow[k0 + 1]);
                 qb[s][1] = pack_bf16(qrow[k1], qrow[k1 + 1]);
             } else {
-                qb[s][0] = pack_f16(qrow[k0], qrow[k0 + 1]);
-                qb[s][1] = pack_f16(qrow[k1], qrow[k1 + 1]);
+                qb[s][0] = pack_f16(qrow[k0] * qf, qrow[k0 + 1] * qf);
+                qb[s][1] = pack_f16(qrow[k1] * qf, qrow[k1 + 1] * qf);
             }
         }
     }
@@ -239,16 +251,16 @@ __global__ void __launch_bounds__(128, 3) decode_mma_kernel(DecodeParams p, cons
                         a1[0] = __byte_perm(wa.y, 0, 0x4140), a1[1] = __byte_perm(wb.y, 0, 0x4140);
                         a1[2] = __byte_perm(wa.y, 0, 0x4342), a1[3] = __byte_perm(wb.y, 0, 0x4342);
                     } else {
-                        // GGML block bytes: lanes c < 2 take the low nibbles of bytes 8c .. 8c+8, lanes c >= 2 the high ones
-                        uint2 wa = *(const uint2*)(Ks + chunk_addr(FMT, MD, 0, tA, 16 * b + 8 * (c & 1)));
-                        uint2 wb = *(const uint2*)(Ks + chunk_addr(FMT, MD, 0, tB, 16 * b + 8 * (c & 1)));
-                        const int sh = (c >> 1) * 4;
-                        wa.x = (wa.x >> sh) & 0x0f0f0f0fu, wa.y = (wa.y >> sh) & 0x0f0f0f0fu;
-                        wb.x = (wb.x >> sh) & 0x0f0f0f0fu, wb.y = (wb.y >> sh) & 0x0f0f0f0fu;
-                        a0[0] = __byte_perm(wa.x, 0, 0x4140), a0[1] = __byte_perm(wb.x, 0, 0x4140);
-                        a0[2] = __byte_perm(wa.x, 0, 0x4342), a0[3] = __byte_perm(wb.x, 0, 0x4342);
-                        a1[0] = __byte_perm(wa.y, 0, 0x4140), a1[1] = __byte_perm(wb.y, 0, 0x4140);
-                        a1[2] = __byte_perm(wa.y, 0, 0x4342), a1[3] = __byte_perm(wb.y, 0, 0x4342);
+                        // GGML block bytes 4c .. 4c+3: the low nibbles are channels 32b + 4c + {0..3} (first k-step), the
+                        // high nibbles channels 32b + 16 + 4c + {0..3} (second k-step).  The high nibbles are used in
+                        // place, i.e. as 16 * code; the matching q operands carry the factor 1/16 (exact in f16).
+                        const uint32_t wa = *(const uint32_t*)(Ks + chunk_addr(FMT, MD, 0, tA, 16 * b + 4 * c));
+                        const uint32_t wb = *(const uint32_t*)(Ks + chunk_addr(FMT, MD, 0, tB, 16 * b + 4 * c));
+                        const uint32_t la = wa & 0x0f0f0f0fu, ha = wa & 0xf0f0f0f0u, lb = wb & 0x0f0f0f0fu, hb = wb & 0xf0f0f0f0u;
+                        a0[0] = __byte_perm(la, 0, 0x4140), a0[1] = __byte_perm(lb, 0, 0x4140);
+                        a0[2] = __byte_perm(la, 0, 0x4342), a0[3] = __byte_perm(lb, 0, 0x4342);
+                        a1[0] = __byte_perm(ha, 0, 0x4140), a1[1] = __byte_perm(hb, 0, 0x4140);
+                        a1[2] = __byte_perm(ha, 0, 0x4342), a1[3] = __byte_perm(hb, 0, 0x4342);
                     }
                     float acc[4] = {0.f, 0.f, 0.f, 0.f};
                     mma_f16(acc, a0, qb[2 * b][0], qb[2 * b][1]);
@@ -277,8 +289,8 @@ __global__ void __launch_bounds__(128, 3) decode_mma_kernel(DecodeParams p, cons
             const float s2 = vB ? sacc[2] * sl2 : -INFINITY, s3 = vB ? sacc[3] * sl2 : -INFINITY;
             const float mn0 = fmaxf(m_run[0], quad_row_max(fmaxf(s0, s2)));
             const float mn1 = fmaxf(m_run[1], quad_row_max(fmaxf(s1, s3)));
-            const float al0 = exp2f(m_run[0] - mn0), al1 = exp2f(m_run[1] - mn1);
-            const float p0 = exp2f(s0 - mn0), p1 = exp2f(s1 - mn1), p2 = exp2f(s2 - mn0), p3 = exp2f(s3 - mn1);
+            const float al0 = fast_ex2(m_run[0] - mn0), al1 = fast_ex2(m_run[1] - mn1);
+            const float p0 = fast_ex2(s0 - mn0), p1 = fast_ex2(s1 - mn1), p2 = fast_ex2(s2 - mn0), p3 = fast_ex2(s3 - mn1);
             m_run[0] = mn0, m_run[1] = mn1;
             l_part[0] = fmaf(l_part[0], al0, p0 + p2);
             l_part[1] = fmaf(l_part[1], al1, p1 + p3);
@@ -293,22 +305,29 @@ __global__ void __launch_bounds__(128, 3) decode_mma_kernel(DecodeParams p, cons
 
             // ================= O^T[128 ch x 8 heads] += V^T . P^T =================
             if constexpr (QUANT) {
-                // P^T B fragments, one per block with the V scale folded in
-                const float2* vsc = (const float2*)(Vs + Gm::DATA);
-                const float2 rawA = vsc[tA], rawB = vsc[tB];
-                const float2 a01 = __half22float2(*(const __half2*)&rawA.x), a23 = __half22float2(*(const __half2*)&rawA.y);
-                const float2 b01 = __half22float2(*(const __half2*)&rawB.x), b23 = __half22float2(*(const __half2*)&rawB.y);
-                const float vsA[4] = {a01.x, a01.y, a23.x, a23.y}, vsB[4] = {b01.x, b01.y, b23.x, b23.y};
+                // P^T B fragments: transpose the probabilities once, then fold the V scale of each block in with
+                // one packed multiply.  The scale region of a V chunk holds, per token pair and block, the f16 pair
+                // (scale of the even token, scale of the odd token): exactly the k-slot pairs of a B fragment.
+                const uint32_t pt0 = movmatrix_trans(pack_f16(p0 * PSCALE, p1 * PSCALE));  // tokens 2c, 2c+1 of head n
+                const uint32_t pt1 = movmatrix_trans(pack_f16(p2 * PSCALE, p3 * PSCALE));  // tokens 2c+8, 2c+9
+                const int T0 = warp * 16 + 2 * c;
+                uint4 sc01 = *(const uint4*)(Vs + Gm::DATA + (T0 >> 1) * 16);        // 4 blocks x (T0, T0+1)
+                uint4 sc23 = *(const uint4*)(Vs + Gm::DATA + ((T0 >> 1) + 4) * 16);  // 4 blocks x (T0+8, T0+9)
+                if (warp * 16 + 16 > n_valid) {
+                    // a stale scale in a dead token slot must not turn 0 * inf into NaN: zero it
+                    const uint32_t k01 = (T0 < n_valid ? 0x0000ffffu : 0u) | (T0 + 1 < n_valid ? 0xffff0000u : 0u);
+                    const uint32_t k23 = (T0 + 8 < n_valid ? 0x0000ffffu : 0u) | (T0 + 9 < n_valid ? 0xffff0000u : 0u);
+                    sc01.x &= k01, sc01.y &= k01, sc01.z &= k01, sc01.w &= k01;
+                    sc23.x &= k23, sc23.y &= k23, sc23.z &= k23, sc23.w &= k23;
+                }
                 uint32_t pb[4][2];
 #pragma unroll
                 for (int b = 0; b < 4; b++) {
-                    // a stale scale in a dead token slot must not turn 0 * inf into NaN
-                    const float fa = vA ? vsA[b] * PSCALE : 0.f, fb = vB ? vsB[b] * PSCALE : 0.f;
-                    pb[b][0] = movmatrix_trans(pack_f16(p0 * fa, p1 * fa));
-                    pb[b][1] = movmatrix_trans(pack_f16(p2 * fb, p3 * fb));
+                    const __half2 h0 = __hmul2(*(const __half2*)&pt0, *(const __half2*)&(&sc01.x)[b]);
+                    const __half2 h1 = __hmul2(*(const __half2*)&pt1, *(const __half2*)&(&sc23.x)[b]);
+                    pb[b][0] = *(const uint32_t*)&h0, pb[b][1] = *(const uint32_t*)&h1;
                 }
                 // this thread's four V token rows: k-slots 2c, 2c+1, 2c+8, 2c+9 of the warp's 16 tokens
-                const int T0 = warp * 16 + 2 * c;
                 if constexpr (FMT == B200KV_FMT_Q8_1) {
                     uint4 x[4];  // 16 bytes at positions 16r.. of each row: channel slot (r | r + 8) of every m-tile
                     x[0] = *(const uint4*)(Vs + chunk_addr(FMT, MD, 1, T0, 16 * r));
@@ -337,8 +356,9 @@ __global__ void __launch_bounds__(128, 3) decode_mma_kernel(DecodeParams p, cons
                         const uint32_t w0 = (&x[0].x)[jj >> 1], w1 = (&x[1].x)[jj >> 1], w2 = (&x[2].x)[jj >> 1], w3 = (&x[3].x)[jj >> 1];
                         const uint32_t sel = (jj & 1) ? 0x7632u : 0x5410u;
                         const uint32_t v01 = __byte_perm(w0, w1, sel), v23 = __byte_perm(w2, w3, sel);
-                        const uint32_t lo01 = v01 & 0x0f0f0f0fu, hi01 = (v01 >> 4) & 0x0f0f0f0fu;
-                        const uint32_t lo23 = v23 & 0x0f0f0f0fu, hi23 = (v23 >> 4) & 0x0f0f0f0fu;
+                        // high nibbles in place (16 * code): rows r + 8 of O^T come out 16 times too large, undone at the end
+                        const uint32_t lo01 = v01 & 0x0f0f0f0fu, hi01 = v01 & 0xf0f0f0f0u;
+                        const uint32_t lo23 = v23 & 0x0f0f0f0fu, hi23 = v23 & 0xf0f0f0f0u;
                         uint32_t a[4];
                         a[0] = __byte_perm(lo01, 0, 0x4240), a[1] = __byte_perm(hi01, 0, 0x4240);
                         a[2] = __byte_perm(lo23, 0, 0x4240), a[3] = __byte_perm(hi23, 0, 0x4240);
@@ -349,7 +369,8 @@ __global__ void __launch_bounds__(128, 3) decode_mma_kernel(DecodeParams p, cons
                     }
                 }
                 // offset term: the same (rounded) probabilities against a constant operand
-                const uint32_t ofs[4] = {OFFS_FRAG, OFFS_FRAG, OFFS_FRAG, OFFS_FRAG};
+                constexpr uint32_t OFFS_HI = FMT == B200KV_FMT_Q4_0 ? 0x00800080u : OFFS_FRAG;  // rows r + 8 of Q4_0: 16 * 8
+                const uint32_t ofs[4] = {OFFS_FRAG, OFFS_HI, OFFS_FRAG, OFFS_HI};
 #pragma unroll
                 for (int b = 0; b < 4; b++) mma_f16(ob[b], ofs, pb[b][0], pb[b][1]);
             } else {
@@ -412,7 +433,8 @@ __global__ void __launch_bounds__(128, 3) decode_mma_kernel(DecodeParams p, cons
         if (QUANT) {  // remove the offset term and the 2^-24 * 1024 operand scaling
             constexpr float UNDO = TWO24 / PSCALE;
             const int b = j >> 1;
-            v0 = (v0 - ob[b][0]) * UNDO, v1 = (v1 - ob[b][1]) * UNDO, v2 = (v2 - ob[b][2]) * UNDO, v3 = (v3 - ob[b][3]) * UNDO;
+            constexpr float UNDO_HI = FMT == B200KV_FMT_Q4_0 ? UNDO / 16.f : UNDO;
+            v0 = (v0 - ob[b][0]) * UNDO, v1 = (v1 - ob[b][1]) * UNDO, v2 = (v2 - ob[b][2]) * UNDO_HI, v3 = (v3 - ob[b][3]) * UNDO_HI;
         }
         float* base = om + (warp * 8 + 2 * c) * MD + 16 * j + r;
         base[0] = v0, base[MD] = v1, base[8] = v2, base[MD + 8] = v3;
