@@ -9,7 +9,7 @@
 // so the whole GQA group shares each K/V page.  Per page of 64 cached tokens:
 //   S[128 x 64]  = Q . K^T      tcgen05.mma, A = Q tile in shared memory (K-major, 128-byte swizzle),
 //                               B = the K chunk exactly as it lies in the page (same swizzle), D in TMEM
-//   softmax                     thread r owns row r: tcgen05.ld its 64 scores, mask, exponentiate in the
+//   softmax                     two threads own a row: each tcgen05.ld's 32 of its 64 scores, masks, exponentiates in the
 //                               log2 domain against a lazily raised reference maximum, write P (16-bit)
 //                               back to TMEM with tcgen05.st
 //   O[128 x 128] += P . V       tcgen05.mma, A = P from TMEM (as a 16-bit value plus its 16-bit rounding remainder:
@@ -99,6 +99,13 @@ __device__ inline void tmem_st32(uint32_t taddr, const uint32_t* r) {
         "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
         : "memory");
 }
+__device__ inline void tmem_st16(uint32_t taddr, const uint32_t* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
 __device__ inline void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptor, 128-byte swizzle, sm_100 descriptor version.
@@ -117,7 +124,11 @@ __device__ inline float fast_exp2(float x) {
     return y;
 }
 
-__global__ void __launch_bounds__(128, 2) prefill_tc_kernel(PrefillParams p) {
+constexpr int P_THREADS = 256;
+
+// Two threads share a row of the 128-row tile: warps w and w + 4 both address TMEM lanes 32 (w & 3) .. + 32;
+// the first takes score columns 0..31 and output channels 0..63, the second the other halves.
+__global__ void __launch_bounds__(P_THREADS, 2) prefill_tc_kernel(PrefillParams p) {
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* q_s = smem;                    // [2 planes][128 rows][128 B], swizzled
     uint8_t* stages = smem + P_QBYTES;      // P_NS x (K chunk, V chunk)
@@ -125,20 +136,23 @@ __global__ void __launch_bounds__(128, 2) prefill_tc_kernel(PrefillParams p) {
     uint64_t* bar_mma = bar_full + P_NS;                        // [1]
     uint32_t* tmem_slot = (uint32_t*)(bar_mma + 1);
     int* fail_s = (int*)(tmem_slot + 1);
+    float* xchg = (float*)(fail_s + 1);     // [2 halves][128 rows]: row maxima, later row sums
 
-    const int tid = threadIdx.x, warp = tid >> 5;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int row = (warp & 3) * 32 + lane, half = warp >> 2;
     const int kvh = blockIdx.y, b = blockIdx.z;
     const int G = p.G, qpt = PM / G;              // queries per tile
     const int q0 = blockIdx.x * qpt;              // first query of this tile
     const int32_t trow = p.desc[2 * b], T = p.desc[2 * b + 1];
     const int P0 = T - p.S;                       // cached tokens before the first new query
     // row -> (query, head of the group); rows past the tile's queries are dead
-    const int rq = tid / G, rg = tid % G;
+    const int rq = row / G, rg = row % G;
     const bool live = rq < qpt && q0 + rq < p.S;
     const int q_last = min(q0 + qpt, p.S) - 1;    // last live query of the tile
     const int my_q = live ? q0 + rq : q_last;
     const int my_limit = p.causal ? P0 + my_q : T - 1;           // last visible key of this row
     const int tile_limit = p.causal ? P0 + q_last : T - 1;       // last key any row of the tile sees
+    const int min_limit = p.causal ? P0 + q0 : T - 1;            // last key EVERY row of the tile sees
     const int n_tiles = tile_limit / PAGE_TOKENS + 1;
 
     if (tid == 0) {
@@ -161,15 +175,15 @@ __global__ void __launch_bounds__(128, 2) prefill_tc_kernel(PrefillParams p) {
         for (int j = 0; j < P_NS && j < n_tiles; j++) issue_load(j);
     if (warp == 0) tmem_alloc(tmem_slot, TMEM_COLS);
 
-    // ---- Q tile -> shared memory, K-major with the 128-byte swizzle (row r: 16-byte unit u of plane pl at u ^ (r & 7)) ----
+    // ---- Q tile -> shared memory, K-major with the 128-byte swizzle (row r: 16-byte unit u of plane pl at u ^ (r & 7));
+    //      this thread moves the 64 channels of plane `half` of its row ----
     {
         const int head = kvh * G + rg;
-        const uint4* src = (const uint4*)((const uint16_t*)p.q + (int64_t)b * p.qb + (int64_t)head * p.qh + (int64_t)my_q * p.qs);
+        const uint4* src = (const uint4*)((const uint16_t*)p.q + (int64_t)b * p.qb + (int64_t)head * p.qh + (int64_t)my_q * p.qs) + half * 8;
 #pragma unroll
-        for (int u = 0; u < 16; u++) {
-            uint4 v = live ? src[u] : make_uint4(0, 0, 0, 0);
-            const int pl = u >> 3, uu = u & 7;
-            *(uint4*)(q_s + pl * (PM * 128) + tid * 128 + ((uu ^ (tid & 7)) << 4)) = v;
+        for (int uu = 0; uu < 8; uu++) {
+            uint4 v = live ? src[uu] : make_uint4(0, 0, 0, 0);
+            *(uint4*)(q_s + half * (PM * 128) + row * 128 + ((uu ^ (row & 7)) << 4)) = v;
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the tensor core
     }
@@ -182,7 +196,7 @@ __global__ void __launch_bounds__(128, 2) prefill_tc_kernel(PrefillParams p) {
         return;
     }
     const uint32_t tmem = *tmem_slot;
-    const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);  // this warp's quarter of the 128 lanes
+    const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);  // this warp's quarter of the 128 lanes
     const uint32_t idesc_s = instr_desc(p.is_bf16, 0, PM, PAGE_TOKENS);
     const uint32_t idesc_o = instr_desc(p.is_bf16, 1, PM, PD);
     const uint32_t q_addr = smem_u32(q_s);
@@ -204,34 +218,38 @@ __global__ void __launch_bounds__(128, 2) prefill_tc_kernel(PrefillParams p) {
         if (ok) issue_s(0);
     }
 
-    const float sl2 = p.scale * 1.4426950408889634f;
-    float m_ref = -INFINITY, l_run = 0.f;
+    const float sl2 = p.scale * 1.4426950408889634f;  // scores enter the exponent in log2 units
+    float m_ref = -INFINITY, l_run = 0.f;             // l_run: this thread's half of the row sum
 
     for (int j = 0; j < n_tiles; j++) {
         // S(j) ready; every MMA issued before it (P.V of tile j-1) has completed as well
         ok = ok && mbar_wait_bounded(bar_mma, (uint32_t)(j & 1));
-        if (__syncthreads_or(!ok)) {
+        tc_fence_after();
+        // ---- this thread's 32 of the row's 64 scores ----
+        uint32_t sr[32];
+        tmem_ld32(lane_base + COL_S + 32 * half, sr);
+        tmem_ld_wait();
+        float tmax = -INFINITY;
+        if (j * PAGE_TOKENS + PAGE_TOKENS - 1 > min_limit) {  // only tiles on the causal diagonal / past the end need a mask
+            const int t0 = j * PAGE_TOKENS + 32 * half;
+#pragma unroll
+            for (int c = 0; c < 32; c++) {
+                const float s = (t0 + c <= my_limit) ? __uint_as_float(sr[c]) : -INFINITY;
+                sr[c] = __float_as_uint(s);
+                tmax = fmaxf(tmax, s);
+            }
+        } else {
+#pragma unroll
+            for (int c = 0; c < 32; c++) tmax = fmaxf(tmax, __uint_as_float(sr[c]));
+        }
+        xchg[half * PM + row] = tmax;
+        if (__syncthreads_or(!ok)) {  // also the barrier of the maxima exchange
             ok = false;
             break;
         }
-        tc_fence_after();
         // stage of tile j-1 is free now: refill it
         if (tid == 0 && j >= 1 && j - 1 + P_NS < n_tiles) issue_load(j - 1 + P_NS);
-
-        // ---- this thread's row of scores ----
-        uint32_t sr[64];
-        tmem_ld32(lane_base + COL_S, sr);
-        tmem_ld32(lane_base + COL_S + 32, sr + 32);
-        tmem_ld_wait();
-        const int t0 = j * PAGE_TOKENS;
-        float tmax = -INFINITY;
-#pragma unroll
-        for (int c = 0; c < 64; c++) {
-            float s = __uint_as_float(sr[c]) * sl2;
-            s = (t0 + c <= my_limit) ? s : -INFINITY;
-            sr[c] = __float_as_uint(s);
-            tmax = fmaxf(tmax, s);
-        }
+        tmax = fmaxf(tmax, xchg[(half ^ 1) * PM + row]) * sl2;
         // raise the reference maximum only when it is exceeded by more than 2^8: the exponentials stay below
         // 256, exact enough in 16 bits, and O has to be rescaled only rarely
         float alpha = 1.f;
@@ -244,24 +262,24 @@ __global__ void __launch_bounds__(128, 2) prefill_tc_kernel(PrefillParams p) {
         }
         if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
 #pragma unroll
-            for (int cc = 0; cc < 4; cc++) {
+            for (int cc = 0; cc < 2; cc++) {  // this thread's 64 of the row's 128 output channels
                 uint32_t orow[32];
-                tmem_ld32(lane_base + COL_O + cc * 32, orow);
+                tmem_ld32(lane_base + COL_O + 64 * half + cc * 32, orow);
                 tmem_ld_wait();
 #pragma unroll
                 for (int c = 0; c < 32; c++) orow[c] = __float_as_uint(__uint_as_float(orow[c]) * alpha);
-                tmem_st32(lane_base + COL_O + cc * 32, orow);
+                tmem_st32(lane_base + COL_O + 64 * half + cc * 32, orow);
             }
         }
         // P goes to the tensor core as two 16-bit operands, the rounded value and the rounding remainder:
         // a row that sees only a few keys gets no averaging of the 2^-11 (f16) / 2^-8 (bf16) rounding errors,
         // and with the remainder the product P . V is exact to ~2^-22
-        uint32_t pr[32], pr2[32];
+        uint32_t pr[16], pr2[16];
         float lsum = 0.f;
 #pragma unroll
-        for (int c = 0; c < 32; c++) {
-            const float p0 = fast_exp2(__uint_as_float(sr[2 * c]) - m_ref);
-            const float p1 = fast_exp2(__uint_as_float(sr[2 * c + 1]) - m_ref);
+        for (int c = 0; c < 16; c++) {
+            const float p0 = fast_exp2(fmaf(__uint_as_float(sr[2 * c]), sl2, -m_ref));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(sr[2 * c + 1]), sl2, -m_ref));
             lsum += p0 + p1;
             if (p.is_bf16) {
                 __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
@@ -274,8 +292,8 @@ __global__ void __launch_bounds__(128, 2) prefill_tc_kernel(PrefillParams p) {
             }
         }
         l_run += lsum;
-        tmem_st32(lane_base + COL_P, pr);
-        tmem_st32(lane_base + COL_P2, pr2);
+        tmem_st16(lane_base + COL_P + 16 * half, pr);
+        tmem_st16(lane_base + COL_P2 + 16 * half, pr2);
         tmem_st_wait();
         tc_fence_before();
         __syncthreads();
@@ -298,18 +316,17 @@ __global__ void __launch_bounds__(128, 2) prefill_tc_kernel(PrefillParams p) {
         }
     }
     // ---- epilogue: wait for the last P.V, normalise, store ----
-    if (ok) {
-        ok = mbar_wait_bounded(bar_mma, (uint32_t)(n_tiles & 1));
-        ok = !__syncthreads_or(!ok);
-    }
+    if (ok) ok = mbar_wait_bounded(bar_mma, (uint32_t)(n_tiles & 1));
+    xchg[half * PM + row] = l_run;
+    ok = !__syncthreads_or(!ok);
     if (ok) {
         tc_fence_after();
-        const float inv = 1.f / l_run;
-        uint16_t* dst = (uint16_t*)p.out + (int64_t)b * p.ob + (int64_t)(kvh * G + rg) * p.oh + (int64_t)my_q * p.os;
+        const float inv = 1.f / (l_run + xchg[(half ^ 1) * PM + row]);
+        uint16_t* dst = (uint16_t*)p.out + (int64_t)b * p.ob + (int64_t)(kvh * G + rg) * p.oh + (int64_t)my_q * p.os + 64 * half;
 #pragma unroll
-        for (int cc = 0; cc < 4; cc++) {
+        for (int cc = 0; cc < 2; cc++) {
             uint32_t orow[32];
-            tmem_ld32(lane_base + COL_O + cc * 32, orow);
+            tmem_ld32(lane_base + COL_O + 64 * half + cc * 32, orow);
             tmem_ld_wait();
             if (live) {
 #pragma unroll
@@ -374,13 +391,13 @@ int launch_prefill_tc(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int3
     // V chunk = 2 planes of 64 channels (8192 bytes apart), 8-token groups 1024 bytes apart
     p.v_lbo = 8192, p.v_sbo = 1024;
     p.scale = scale;
-    const size_t smem = P_QBYTES + (size_t)P_NS * P_STAGE + 64;
+    const size_t smem = P_QBYTES + (size_t)P_NS * P_STAGE + 64 + 2 * PM * 4;
     B200KV_CUDA(cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const int qpt = PM / G;
     dim3 grid((n_new + qpt - 1) / qpt, c->L.Hkv, n_seqs);
     {
         ProfScope ps(c, K_PREFILL, stream);
-        prefill_tc_kernel<<<grid, 128, smem, stream>>>(p);
+        prefill_tc_kernel<<<grid, P_THREADS, smem, stream>>>(p);
     }
     cudaError_t e = cudaGetLastError();
     staging_release(c, slot, stream);
