@@ -35,6 +35,8 @@ WORKLOADS = {
     "cfg4-q8": ("q8_1", "f16", 16, 32768, "BASELINE config 4: batch 16, past 32768, Q8 block-32 KV (f16 scale + int8 codes)"),
     "cfg4-q4": ("q4_0", "f16", 16, 32768, "BASELINE config 4, 4-bit variant (Q4_0)"),
     "cfg4-f16": ("f16", "f16", 16, 32768, "config 4 shape with an unquantised f16 cache"),
+    "cfg4-kivi8": ("kivi8", "f16", 16, 32768, "config 4 shape with tract's own KIVI int8 storage (QuantizedDynKeyValueCache)"),
+    "cfg4-kivi4": ("kivi4", "f16", 16, 32768, "config 4 shape with tract's own KIVI int4 storage"),
     "cfg3-bf16": ("bf16", "bf16", 256, "ragged", "BASELINE config 3: 256 sequences, past ~ U[512,16384], bf16"),
     "cfg1-f32": ("f32", "f32", 1, 2048, "BASELINE config 1: batch 1, past 2048, f32"),
 }
@@ -48,7 +50,13 @@ PREFILL = {
 }
 HQ, HKV, D = 32, 8, 128
 OVERRIDE = {}  # --seqs / --past: smaller cases of a workload, for profiler captures
-ROW_BYTES = {"f32": 512, "f16": 256, "bf16": 256, "q8_1": 128 + 8, "q4_0": 64 + 8}  # stored bytes per token-head (codes + scales)
+# DRAM traffic of the decode kernel per algorithmic byte (dram__bytes_read + dram__bytes_write over the K/V bytes of the
+# launch), from the ncu captures summarised under profiles/ on a smaller case of the same workload (traffic grows in
+# proportion to the tokens streamed, so it is scaled to the full launch by the units processed).
+NCU_TRAFFIC_RATIO = {"q8_1": 1.028}
+ROW_BYTES = {"f32": 512, "f16": 256, "bf16": 256, "q8_1": 128 + 8, "q4_0": 64 + 8,
+             # KIVI: K = codes + 2 x D f32 parameters per 32 tokens, V = codes + 8 bytes per token; mean of K and V
+             "kivi8": 128 + (32 + 8) // 2, "kivi4": 64 + (32 + 8) // 2}  # stored bytes per token-head (codes + scales)
 
 
 def peaks():
@@ -285,9 +293,12 @@ def run_ours(args, rank, world):
                     "tokens_per_s": all_seqs / (ms_e2e / args.steps * 1e-3)},
             "gpu_launches": len(recs),
             "kernels_ms": {k: statistics.mean(v) for k, v in per_kernel.items()},
-            "roofline": {"bound": "hbm", "kernel": "decode_kernel", "achieved": achieved, "peak": pk["hbm_gbs"],
+            "roofline": {"bound": "hbm", "kernel": "decode_mma_kernel" if (fmt != "f32") else "decode_kernel", "achieved": achieved, "peak": pk["hbm_gbs"],
                          "unit": "GB/s", "frac": achieved / pk["hbm_gbs"], "peak_kind": pk_kind,
-                         "traffic": None, "frac_of_nominal_8TBps": achieved / 8000.0},
+                         "algorithmic_bytes": total_bytes,
+                         "traffic": int(total_bytes * NCU_TRAFFIC_RATIO[fmt]) if fmt in NCU_TRAFFIC_RATIO else None,
+                         "traffic_source": "profiles/decode_mma_q8_b8_p16384.md, scaled by tokens" if fmt in NCU_TRAFFIC_RATIO else None,
+                         "frac_of_nominal_8TBps": achieved / 8000.0},
             "clocks": clocks,
         }
     cache.close()

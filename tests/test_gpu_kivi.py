@@ -119,3 +119,35 @@ def test_kivi_attention_matches_oracle(kv, fmt, bits, io):
         assert rel_err(out.float().cpu().numpy(), want.astype(np.float32)) <= TOL[io], step
     cache.check()
     cache.close()
+
+
+@pytest.mark.parametrize("fmt,bits,D,Hq,Hkv", [("kivi8", 8, 128, 32, 8), ("kivi4", 4, 64, 6, 2)])
+def test_kivi_decode_kernel_ragged_batch(kv, fmt, bits, D, Hq, Hkv):
+    # batched decode over sequences that are sinks only, shorter than one key block, and long
+    lens = [700, 37, 5, 3, 1300]
+    cache = kv.KvCache(fmt, Hkv, D, max_seqs=len(lens), max_seq_tokens=2048)
+    seqs = [cache.new_seq() for _ in lens]
+    Ks, Vs = [], []
+    for b, n in enumerate(lens):
+        k, v = normal_with_outliers(700 + b, (1, Hkv, n, D)).astype(np.float16), normal(800 + b, (1, Hkv, n, D)).astype(np.float16)
+        cache.append([seqs[b]], torch.from_numpy(k).cuda(), torch.from_numpy(v).cuda())
+        Ks.append(k), Vs.append(v)
+    q = normal(9, (len(lens), Hq, 1, D)).astype(np.float16)
+    out = cache.attend(seqs, torch.from_numpy(q).cuda(), causal=True)
+    cache.profile(False, force_simt=True)  # the same through export + the generic kernel
+    out_gen = cache.attend(seqs, torch.from_numpy(q).cuda(), causal=True)
+    cache.profile(False)
+    cache.check()
+    assert rel_err(out.float().cpu().numpy(), out_gen.float().cpu().numpy()) <= 1e-3
+    for b in range(len(lens)):
+        kd = np.stack([_deq(True, D, bits, Ks[b][0, h]) for h in range(Hkv)])[None]
+        vd = np.stack([_deq(False, D, bits, Vs[b][0, h]) for h in range(Hkv)])[None]
+        want = oracle.flash_sdpa(q[b:b + 1], kd, vd, causal=True)
+        assert rel_err(out[b:b + 1].float().cpu().numpy(), want.astype(np.float32)) <= TOL["f16"], b
+    cache.close()
+
+
+def _deq(per_channel, D, bits, rows):
+    st = oracle.KiviStore(per_channel, D, bits)
+    st.push(rows)
+    return st.dequant()

@@ -27,6 +27,8 @@ extern "C" int b200kv_attend(b200kv_cache* c, int32_t n_seqs, const int32_t* seq
     DeviceGuard guard(c->cfg.device);
 
     const bool kivi = fmt_is_kivi(c->L.fmt);
+    if (n_new == 1 && kivi && !c->force_simt && n_seqs <= 256)
+        return kivi_decode(c, n_seqs, seqs, n_q_heads, q, q_strides, out, out_strides, dtype, scale, stream);
     if (n_new == 1 && !kivi) return launch_decode(c, n_seqs, seqs, n_q_heads, q, q_strides, out, out_strides, dtype, scale, stream);
 
     if (!kivi && !c->force_simt && prefill_tc_supported(c, n_q_heads, dtype, q, q_strides, out, out_strides))

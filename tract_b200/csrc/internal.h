@@ -144,6 +144,8 @@ int kivi_append(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t n_
 int kivi_export(b200kv_cache* c, int32_t seq, void* k_out, const int64_t* ks, void* v_out, const int64_t* vs, int32_t dtype,
                 cudaStream_t stream);
 int kivi_fork(b200kv_cache* c, int32_t src, int32_t dst, cudaStream_t stream);
+int kivi_decode(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t n_q_heads, const void* q, const int64_t* qs, void* out,
+                const int64_t* os, int32_t dtype, float scale, cudaStream_t stream);
 // prefill_tc.cu
 bool prefill_tc_supported(const b200kv_cache* c, int n_q_heads, int dtype, const void* q, const int64_t* qs, const void* out,
                           const int64_t* os);

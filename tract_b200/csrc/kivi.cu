@@ -10,6 +10,7 @@
 // uses explicitly rounded IEEE operations in the reference's order so that codes, lo and scale are
 // bit-identical to the CPU's:  scale = (hi > lo) ? (hi - lo) / lv : 1 ;  code = clamp(round((x - lo) / scale), 0, lv)
 // (round half away from zero, NaN -> 0) ;  dequant = lo + code * scale (multiply, then add).
+#include <algorithm>
 #include <cstring>
 
 #include "internal.h"
@@ -375,3 +376,160 @@ extern "C" int b200kv_export_kivi(b200kv_cache* c, int32_t seq, int32_t which, v
     B200KV_CUDA(cudaGetLastError());
     return B200KV_OK;
 }
+
+// ---- decode attention over a KIVI cache ---------------------------------------------------------------
+// Dequantise-inside-attention for the reference's own quantised layout (the CPU op rebuilds the whole f32
+// cache every step, quant_dyn_kv_cache.rs:432-449, and hands it to Sdpa).  CUDA-core formulation: a CTA takes a
+// run of 32-token tiles of one (sequence, kv head) for up to 4 query heads of the group, dequantises each tile
+// into shared memory with exactly the reference's arithmetic (lo + code * scale), and runs the usual online
+// softmax; splits are merged by the same combine pass as the other decode kernels.
+#include "decode_common.h"
+
+namespace b200kv {
+
+constexpr int KTILE = 32;  // tokens per tile
+constexpr int KGT = 4;     // query heads per CTA
+
+struct KiviDecode {
+    KiviView v;
+    const void* q;
+    int64_t qb, qh;
+    float* part_o;
+    float* part_ml;
+    int32_t G, dtype, n_splits;
+    float scale;
+};
+
+// Value of channel c of token t of stream s, as the reference's dequant_all would produce it.
+__device__ inline float kivi_value(const KiviView& v, int s, int32_t seq, int64_t len, int h, int64_t t, int c) {
+    if (t < SINK) return v.sinks[((((int64_t)seq * v.H + h) * 2 + s) * SINK + t) * v.D + c];
+    const int64_t i = t - SINK;
+    const int32_t pg = v.table[(int64_t)seq * v.max_pages_per_seq + i / PAGE_TOKENS];
+    const int slot = (int)(i % PAGE_TOKENS);
+    if (v.per_channel[s]) {
+        if (i >= ((len - SINK) / KBLOCK) * KBLOCK) return v.residual[((((int64_t)seq * v.H + h) * 2 + s) * KBLOCK + i % KBLOCK) * v.D + c];
+        const float* par = v.params[s] + (((int64_t)pg * v.H + h) * 2 + slot / KBLOCK) * 2 * v.D;
+        return kivi_dequant(kivi_load_code(v, s, pg, h, slot, c), par[c], par[v.D + c]);
+    }
+    const float* par = v.params[s] + (((int64_t)pg * v.H + h) * PAGE_TOKENS + slot) * 2;
+    return kivi_dequant(kivi_load_code(v, s, pg, h, slot, c), par[0], par[1]);
+}
+
+template <int D>
+__global__ void __launch_bounds__(128) kivi_decode_kernel(KiviDecode p, const __grid_constant__ InlineBatch ib) {
+    constexpr int LD = D + 4;  // padded row of the f32 tiles
+    __shared__ float k_s[KTILE * LD], v_s[KTILE * LD];
+    __shared__ float q_s[KGT * D], sc_s[KGT * KTILE], alpha_s[KGT], ml_s[KGT * 2];
+    const KiviView& v = p.v;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int b = blockIdx.x / p.n_splits, split = blockIdx.x % p.n_splits;
+    const int kvh = blockIdx.y, g0 = blockIdx.z * KGT, ng = min(KGT, p.G - g0);
+    const int32_t seq = ib.ent[b].x;
+    const int64_t len = ib.ent[b].y;
+    const int tiles = (int)((len + KTILE - 1) / KTILE);
+    const int tile_lo = (int)((int64_t)tiles * split / p.n_splits), tile_hi = (int)((int64_t)tiles * (split + 1) / p.n_splits);
+
+    for (int idx = tid; idx < KGT * D; idx += 128) {
+        const int g = idx / D;
+        q_s[idx] = g < ng ? ld_as_f32(p.q, p.dtype, (int64_t)b * p.qb + (int64_t)(kvh * p.G + g0 + g) * p.qh + idx % D) : 0.f;
+    }
+    float m_run = -INFINITY, l_run = 0.f;  // warp g keeps the state of head g
+    float acc[KGT] = {0.f, 0.f, 0.f, 0.f};  // thread = output channel
+    for (int tile = tile_lo; tile < tile_hi; tile++) {
+        const int64_t t0 = (int64_t)tile * KTILE;
+        const int n_valid = (int)min((int64_t)KTILE, len - t0);
+        __syncthreads();  // the previous tile is consumed (and q_s is written)
+        for (int idx = tid; idx < KTILE * D; idx += 128) {
+            const int tt = idx / D, c = idx % D;
+            float kv0 = 0.f, kv1 = 0.f;
+            if (tt < n_valid) kv0 = kivi_value(v, 0, seq, len, kvh, t0 + tt, c), kv1 = kivi_value(v, 1, seq, len, kvh, t0 + tt, c);
+            k_s[tt * LD + c] = kv0, v_s[tt * LD + c] = kv1;
+        }
+        __syncthreads();
+        {  // scores: 4 threads per token, each over a quarter of the channels
+            const int tt = tid >> 2, part = tid & 3;
+            float dot[KGT] = {0.f, 0.f, 0.f, 0.f};
+            for (int c = part; c < D; c += 4) {
+                const float kx = k_s[tt * LD + c];
+#pragma unroll
+                for (int g = 0; g < KGT; g++) dot[g] = fmaf(q_s[g * D + c], kx, dot[g]);
+            }
+#pragma unroll
+            for (int g = 0; g < KGT; g++) {
+                dot[g] += __shfl_xor_sync(0xffffffffu, dot[g], 1);
+                dot[g] += __shfl_xor_sync(0xffffffffu, dot[g], 2);
+            }
+            if (part == 0) {
+#pragma unroll
+                for (int g = 0; g < KGT; g++) sc_s[g * KTILE + tt] = dot[g] * p.scale;
+            }
+        }
+        __syncthreads();
+        if (warp < KGT) {  // online softmax of head `warp`: one lane per token of the tile
+            const float s = lane < n_valid ? sc_s[warp * KTILE + lane] : -INFINITY;
+            float mx = s;
+#pragma unroll
+            for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+            const float m_new = fmaxf(m_run, mx);
+            const float a = expf(m_run - m_new), pw = expf(s - m_new);
+            float sum = pw;
+#pragma unroll
+            for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            l_run = l_run * a + sum, m_run = m_new;
+            sc_s[warp * KTILE + lane] = pw;
+            if (lane == 0) alpha_s[warp] = a;
+        }
+        __syncthreads();
+        if (tid < D) {
+#pragma unroll
+            for (int g = 0; g < KGT; g++) acc[g] *= alpha_s[g];
+            for (int tt = 0; tt < n_valid; tt++) {
+                const float vx = v_s[tt * LD + tid];
+#pragma unroll
+                for (int g = 0; g < KGT; g++) acc[g] = fmaf(sc_s[g * KTILE + tt], vx, acc[g]);
+            }
+        }
+    }
+    if (warp < KGT && lane == 0) ml_s[warp * 2] = m_run, ml_s[warp * 2 + 1] = l_run;
+    __syncthreads();
+    const int64_t pbase = ((int64_t)blockIdx.x * v.H + kvh) * p.G + g0;
+    if (tid < D)
+        for (int g = 0; g < ng; g++) p.part_o[(pbase + g) * D + tid] = acc[g];
+    if (tid < ng) p.part_ml[(pbase + tid) * 2] = ml_s[tid * 2], p.part_ml[(pbase + tid) * 2 + 1] = ml_s[tid * 2 + 1];
+}
+
+int kivi_decode(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t n_q_heads, const void* q, const int64_t* qs, void* out,
+                const int64_t* os, int32_t dtype, float scale, cudaStream_t stream) {
+    const int H = c->cfg.n_kv_heads, D = c->cfg.head_dim, G = n_q_heads / H;
+    if (n_seqs > INLINE_BATCH) return fail("a KIVI decode call takes at most %d sequences", INLINE_BATCH);
+    int64_t max_len = 0;
+    for (int i = 0; i < n_seqs; i++) max_len = std::max<int64_t>(max_len, c->seqs[seqs[i]].len);
+    // enough splits to cover the GPU a few times, at least 8 tiles (256 tokens) each
+    const int64_t tiles = (max_len + KTILE - 1) / KTILE;
+    const int nz = (G + KGT - 1) / KGT;
+    int ns = (int)std::min<int64_t>(64, std::max<int64_t>(1, (148 * 4 + (int64_t)n_seqs * H * nz - 1) / ((int64_t)n_seqs * H * nz)));
+    ns = (int)std::max<int64_t>(1, std::min<int64_t>(ns, tiles / 8));
+    InlineBatch ib{};
+    ib.n = n_seqs;
+    for (int i = 0; i < n_seqs; i++) ib.ent[i] = make_int4(seqs[i], (int)c->seqs[seqs[i]].len, i * ns, ns);
+    const size_t n_part = (size_t)n_seqs * ns * H * G;
+    if (ensure_workspace(c, n_part * (D + 2) * sizeof(float)) != B200KV_OK) return B200KV_KO;
+    KiviDecode p{};
+    p.v = kivi_view(c);
+    p.q = q, p.qb = qs[0], p.qh = qs[1];
+    p.part_o = (float*)c->ws, p.part_ml = p.part_o + n_part * D;
+    p.G = G, p.dtype = dtype, p.n_splits = ns, p.scale = scale;
+    {
+        ProfScope ps(c, K_DECODE, stream);
+        dim3 grid(n_seqs * ns, H, nz);
+        if (D == 128) kivi_decode_kernel<128><<<grid, 128, 0, stream>>>(p, ib);
+        else kivi_decode_kernel<64><<<grid, 128, 0, stream>>>(p, ib);
+        B200KV_CUDA(cudaGetLastError());
+    }
+    DecodeParams dp{};
+    dp.part_o = p.part_o, dp.part_ml = p.part_ml, dp.Hkv = H, dp.G = G, dp.dtype = dtype;
+    ProfScope ps(c, K_COMBINE, stream);
+    return launch_combine(dp, nullptr, out, os[0], os[1], n_seqs, n_q_heads, D, stream, &ib);
+}
+
+}  // namespace b200kv
