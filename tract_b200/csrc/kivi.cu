@@ -400,25 +400,25 @@ struct KiviDecode {
     float scale;
 };
 
-// Value of channel c of token t of stream s, as the reference's dequant_all would produce it.
-__device__ inline float kivi_value(const KiviView& v, int s, int32_t seq, int64_t len, int h, int64_t t, int c) {
-    if (t < SINK) return v.sinks[((((int64_t)seq * v.H + h) * 2 + s) * SINK + t) * v.D + c];
-    const int64_t i = t - SINK;
-    const int32_t pg = v.table[(int64_t)seq * v.max_pages_per_seq + i / PAGE_TOKENS];
-    const int slot = (int)(i % PAGE_TOKENS);
-    if (v.per_channel[s]) {
-        if (i >= ((len - SINK) / KBLOCK) * KBLOCK) return v.residual[((((int64_t)seq * v.H + h) * 2 + s) * KBLOCK + i % KBLOCK) * v.D + c];
-        const float* par = v.params[s] + (((int64_t)pg * v.H + h) * 2 + slot / KBLOCK) * 2 * v.D;
-        return kivi_dequant(kivi_load_code(v, s, pg, h, slot, c), par[c], par[v.D + c]);
-    }
-    const float* par = v.params[s] + (((int64_t)pg * v.H + h) * PAGE_TOKENS + slot) * 2;
-    return kivi_dequant(kivi_load_code(v, s, pg, h, slot, c), par[0], par[1]);
+__device__ inline void cp_async16(void* dst_smem, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst_smem)), "l"(__cvta_generic_to_global(src)) : "memory");
 }
+__device__ inline void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ inline void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
+// Tiles follow the stores: tile -1 is the f32 sinks, tile k >= 0 the 32 tokens 4 + 32k .. 4 + 32k + 31, i.e. exactly
+// one key block (finalised: codes + per-channel parameters; the last, partial one: f32 residual rows) and 32
+// per-token value rows.  The raw bytes of tile k + 1 are fetched with cp.async while tile k is being consumed.
 template <int D>
 __global__ void __launch_bounds__(128) kivi_decode_kernel(KiviDecode p, const __grid_constant__ InlineBatch ib) {
-    constexpr int LD = D + 4;  // padded row of the f32 tiles
-    __shared__ float k_s[KTILE * LD], v_s[KTILE * LD];
+    constexpr int RS = 144;  // row stride of the staged code rows: 16-byte aligned, and 36 words so that 8 rows hit 32 banks
+    struct Stage {
+        uint8_t kc[KTILE * RS], vc[KTILE * RS];  // code rows
+        float kpar[2 * D];                       // lo[D], scale[D] of the key block
+        float vpar[2 * KTILE];                   // (lo, scale) per value token
+    };
+    __shared__ __align__(16) Stage st[2];
     __shared__ float q_s[KGT * D], sc_s[KGT * KTILE], alpha_s[KGT], ml_s[KGT * 2];
     const KiviView& v = p.v;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -426,33 +426,80 @@ __global__ void __launch_bounds__(128) kivi_decode_kernel(KiviDecode p, const __
     const int kvh = blockIdx.y, g0 = blockIdx.z * KGT, ng = min(KGT, p.G - g0);
     const int32_t seq = ib.ent[b].x;
     const int64_t len = ib.ent[b].y;
-    const int tiles = (int)((len + KTILE - 1) / KTILE);
-    const int tile_lo = (int)((int64_t)tiles * split / p.n_splits), tile_hi = (int)((int64_t)tiles * (split + 1) / p.n_splits);
+    const int n_after = (int)max((int64_t)0, len - SINK), n_fin = n_after / KBLOCK;
+    const int tiles = (n_after + KTILE - 1) / KTILE;
+    // split s takes tiles [lo, hi) of -1 .. tiles-1
+    const int tile_lo = (int)((int64_t)(tiles + 1) * split / p.n_splits) - 1, tile_hi = (int)((int64_t)(tiles + 1) * (split + 1) / p.n_splits) - 1;
+    const int row_bytes = v.row_bytes, chunks = row_bytes / 16;
+    const float* sink_k = v.sinks + (((int64_t)seq * v.H + kvh) * 2 + 0) * SINK * D;
+    const float* sink_v = v.sinks + (((int64_t)seq * v.H + kvh) * 2 + 1) * SINK * D;
+    const float* resid = v.residual + (((int64_t)seq * v.H + kvh) * 2 + 0) * KBLOCK * D;
+
+    auto prefetch = [&](int k) {  // raw bytes of tile k (>= 0) into stage k & 1
+        Stage& s = st[k & 1];
+        const int32_t pg = v.table[(int64_t)seq * v.max_pages_per_seq + (k * KTILE) / PAGE_TOKENS];
+        const int slot0 = (k * KTILE) % PAGE_TOKENS;
+        const int nrow = min(KTILE, n_after - k * KTILE);
+        const uint8_t* vrow = v.codes[1] + (((int64_t)pg * v.H + kvh) * PAGE_TOKENS + slot0) * row_bytes;
+        for (int i = tid; i < nrow * chunks; i += 128) cp_async16(s.vc + (i / chunks) * RS + (i % chunks) * 16, vrow + (i / chunks) * row_bytes + (i % chunks) * 16);
+        const float* vp = v.params[1] + (((int64_t)pg * v.H + kvh) * PAGE_TOKENS + slot0) * 2;
+        if (tid < KTILE / 2) cp_async16(s.vpar + tid * 4, vp + tid * 4);  // whole 256-byte run; rows past nrow are ignored
+        if (k < n_fin) {
+            const uint8_t* krow = v.codes[0] + (((int64_t)pg * v.H + kvh) * PAGE_TOKENS + slot0) * row_bytes;
+            for (int i = tid; i < KTILE * chunks; i += 128) cp_async16(s.kc + (i / chunks) * RS + (i % chunks) * 16, krow + (i / chunks) * row_bytes + (i % chunks) * 16);
+            const float* kp = v.params[0] + (((int64_t)pg * v.H + kvh) * 2 + slot0 / KBLOCK) * 2 * D;
+            for (int i = tid; i < 2 * D / 4; i += 128) cp_async16(s.kpar + i * 4, kp + i * 4);
+        }
+    };
+    if (max(tile_lo, 0) < tile_hi) prefetch(max(tile_lo, 0));
+    cp_async_commit();
 
     for (int idx = tid; idx < KGT * D; idx += 128) {
         const int g = idx / D;
         q_s[idx] = g < ng ? ld_as_f32(p.q, p.dtype, (int64_t)b * p.qb + (int64_t)(kvh * p.G + g0 + g) * p.qh + idx % D) : 0.f;
     }
-    float m_run = -INFINITY, l_run = 0.f;  // warp g keeps the state of head g
+    float m_run = -INFINITY, l_run = 0.f;   // warp g keeps the state of head g
     float acc[KGT] = {0.f, 0.f, 0.f, 0.f};  // thread = output channel
+    const bool eight = v.bits == 8;
+
     for (int tile = tile_lo; tile < tile_hi; tile++) {
-        const int64_t t0 = (int64_t)tile * KTILE;
-        const int n_valid = (int)min((int64_t)KTILE, len - t0);
-        __syncthreads();  // the previous tile is consumed (and q_s is written)
-        for (int idx = tid; idx < KTILE * D; idx += 128) {
-            const int tt = idx / D, c = idx % D;
-            float kv0 = 0.f, kv1 = 0.f;
-            if (tt < n_valid) kv0 = kivi_value(v, 0, seq, len, kvh, t0 + tt, c), kv1 = kivi_value(v, 1, seq, len, kvh, t0 + tt, c);
-            k_s[tt * LD + c] = kv0, v_s[tt * LD + c] = kv1;
-        }
+        // the next tile's bytes start moving before this one is touched
+        if (tile + 1 < tile_hi && tile + 1 >= 0 && tile + 1 != max(tile_lo, 0)) prefetch(tile + 1);
+        cp_async_commit();
+        if (tile >= 0) cp_async_wait<1>();  // everything but the group just committed has landed
         __syncthreads();
-        {  // scores: 4 threads per token, each over a quarter of the channels
+        const Stage& s = st[tile & 1];
+        const int n_valid = tile < 0 ? (int)min((int64_t)SINK, len) : min(KTILE, n_after - tile * KTILE);
+        const bool k_f32 = tile < 0 || tile >= n_fin;  // sinks / residual rows: f32 straight from global memory
+        const float* kf = tile < 0 ? sink_k : resid;
+        {  // scores: 4 threads per token; thread `part` takes the 4-channel words part, part + 4, ...
             const int tt = tid >> 2, part = tid & 3;
             float dot[KGT] = {0.f, 0.f, 0.f, 0.f};
-            for (int c = part; c < D; c += 4) {
-                const float kx = k_s[tt * LD + c];
+            if (tt < n_valid) {
+                for (int w = part; w < D / 4; w += 4) {
+                    float kx[4];
+                    if (k_f32) {
+                        const float4 f = *(const float4*)(kf + tt * D + 4 * w);
+                        kx[0] = f.x, kx[1] = f.y, kx[2] = f.z, kx[3] = f.w;
+                    } else {
+                        uint32_t codes[4];
+                        if (eight) {
+                            const uint32_t word = *(const uint32_t*)(s.kc + tt * RS + 4 * w);
 #pragma unroll
-                for (int g = 0; g < KGT; g++) dot[g] = fmaf(q_s[g * D + c], kx, dot[g]);
+                            for (int e = 0; e < 4; e++) codes[e] = (word >> (8 * e)) & 0xffu;
+                        } else {
+                            const uint32_t half = *(const uint16_t*)(s.kc + tt * RS + 2 * w);
+#pragma unroll
+                            for (int e = 0; e < 4; e++) codes[e] = (half >> (4 * e)) & 0xfu;
+                        }
+#pragma unroll
+                        for (int e = 0; e < 4; e++) kx[e] = kivi_dequant(codes[e], s.kpar[4 * w + e], s.kpar[D + 4 * w + e]);
+                    }
+#pragma unroll
+                    for (int e = 0; e < 4; e++)
+#pragma unroll
+                        for (int g = 0; g < KGT; g++) dot[g] = fmaf(q_s[g * D + 4 * w + e], kx[e], dot[g]);
+                }
             }
 #pragma unroll
             for (int g = 0; g < KGT; g++) {
@@ -466,12 +513,12 @@ __global__ void __launch_bounds__(128) kivi_decode_kernel(KiviDecode p, const __
         }
         __syncthreads();
         if (warp < KGT) {  // online softmax of head `warp`: one lane per token of the tile
-            const float s = lane < n_valid ? sc_s[warp * KTILE + lane] : -INFINITY;
-            float mx = s;
+            const float sv = lane < n_valid ? sc_s[warp * KTILE + lane] : -INFINITY;
+            float mx = sv;
 #pragma unroll
             for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
             const float m_new = fmaxf(m_run, mx);
-            const float a = expf(m_run - m_new), pw = expf(s - m_new);
+            const float a = expf(m_run - m_new), pw = expf(sv - m_new);
             float sum = pw;
 #pragma unroll
             for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
@@ -484,12 +531,21 @@ __global__ void __launch_bounds__(128) kivi_decode_kernel(KiviDecode p, const __
 #pragma unroll
             for (int g = 0; g < KGT; g++) acc[g] *= alpha_s[g];
             for (int tt = 0; tt < n_valid; tt++) {
-                const float vx = v_s[tt * LD + tid];
+                float vx;
+                if (tile < 0) {
+                    vx = sink_v[tt * D + tid];
+                } else {
+                    const uint32_t byte = s.vc[tt * RS + (eight ? tid : tid >> 1)];
+                    const uint32_t code = eight ? byte : ((tid & 1) ? byte >> 4 : byte & 0xfu);
+                    vx = kivi_dequant(code, s.vpar[2 * tt], s.vpar[2 * tt + 1]);
+                }
 #pragma unroll
                 for (int g = 0; g < KGT; g++) acc[g] = fmaf(sc_s[g * KTILE + tt], vx, acc[g]);
             }
         }
+        __syncthreads();  // the stage and sc_s are free again
     }
+    cp_async_wait<0>();
     if (warp < KGT && lane == 0) ml_s[warp * 2] = m_run, ml_s[warp * 2 + 1] = l_run;
     __syncthreads();
     const int64_t pbase = ((int64_t)blockIdx.x * v.H + kvh) * p.G + g0;
@@ -505,9 +561,9 @@ int kivi_decode(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t n_
     int64_t max_len = 0;
     for (int i = 0; i < n_seqs; i++) max_len = std::max<int64_t>(max_len, c->seqs[seqs[i]].len);
     // enough splits to cover the GPU a few times, at least 8 tiles (256 tokens) each
-    const int64_t tiles = (max_len + KTILE - 1) / KTILE;
+    const int64_t tiles = (std::max<int64_t>(max_len - SINK, 0) + KTILE - 1) / KTILE + 1;
     const int nz = (G + KGT - 1) / KGT;
-    int ns = (int)std::min<int64_t>(64, std::max<int64_t>(1, (148 * 4 + (int64_t)n_seqs * H * nz - 1) / ((int64_t)n_seqs * H * nz)));
+    int ns = (int)std::min<int64_t>(64, std::max<int64_t>(1, (148 * 10 + (int64_t)n_seqs * H * nz - 1) / ((int64_t)n_seqs * H * nz)));
     ns = (int)std::max<int64_t>(1, std::min<int64_t>(ns, tiles / 8));
     InlineBatch ib{};
     ib.n = n_seqs;
