@@ -101,6 +101,21 @@ int b200kv_append(b200kv_cache* cache, int32_t n_seqs, const int32_t* seqs, int3
                   const int64_t k_strides[3], const void* v_new, const int64_t v_strides[3], int32_t dtype,
                   void* stream);
 
+/* b200kv_append with the rotary position embedding of the keys fused in: K_new goes through ApplyRope
+ * (transformers/src/ops/apply_rope.rs:143-176, x * cos + rotate_half(x) * sin, each operation rounded to `dtype`) on its
+ * way into the pages, which saves the separate pass over K that the graph `ApplyRope -> DynKeyValueCache` makes.
+ * cos / sin are [n_seqs, n_new, D] of type `dtype` (the same for every head), strides {batch, token} in elements
+ * (0 to broadcast over the batch).  V is stored as given.  Not available for the KIVI formats. */
+int b200kv_append_rope(b200kv_cache* cache, int32_t n_seqs, const int32_t* seqs, int32_t n_new, const void* k_new,
+                       const int64_t k_strides[3], const void* v_new, const int64_t v_strides[3], const void* cos,
+                       const void* sin, const int64_t rope_strides[2], int32_t dtype, void* stream);
+
+/* Stand-alone ApplyRope for the query side (replaces cuda/src/kernels/cu/nn.cu `apply_rope_nd*`): x and out are
+ * [batch, n_heads, n_tokens, head_dim] with strides {batch, head, token}; cos / sin as above.  Not in place. */
+int b200kv_rope(const void* x, const int64_t x_strides[3], const void* cos, const void* sin, const int64_t rope_strides[2],
+                void* out, const int64_t out_strides[3], int32_t batch, int32_t n_heads, int32_t n_tokens, int32_t head_dim,
+                int32_t dtype, void* stream);
+
 /* ---- attention over the cache (Sdpa over the accumulated K/V: the fused form of
  *      transformers/src/ops/inplace_kv_cache.rs:135-216; kernels replace cuda/src/kernels/cu/flash_attn.cu) ----
  * q and out are [n_seqs, n_q_heads, n_new, D]; the n_new queries of sequence i are its LAST n_new

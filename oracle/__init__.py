@@ -217,6 +217,21 @@ class QuantizedDynKeyValueCache:
         return np.stack([s.dequant() for s in self.stores]).reshape(b, h, t, d)
 
 
+# ---- rotary embedding (the step right before the cache) ---------------------------------------------------
+
+def rotate_half(x: np.ndarray) -> np.ndarray:
+    """RotateHalf (transformers/src/ops/apply_rope.rs:58-74): concat(-x[.., D/2:], x[.., :D/2])."""
+    half = x.shape[-1] // 2
+    return np.concatenate([-x[..., half:], x[..., :half]], axis=-1)
+
+
+def apply_rope(x: np.ndarray, cos: np.ndarray, sin: np.ndarray) -> np.ndarray:
+    """ApplyRope::eval (apply_rope.rs:155-163): Mul, Mul, Add as three ops of the input's dtype; numpy rounds
+    every f16 / bf16 operation to the type, as the reference's element-wise ops do."""
+    dt = x.dtype
+    return ((x * cos.astype(dt)).astype(dt) + (rotate_half(x) * sin.astype(dt)).astype(dt)).astype(dt)
+
+
 # ---- a7 -------------------------------------------------------------------------------------------
 
 def _prep_sdpa(q, k, v, mask):

@@ -23,7 +23,7 @@ EXPORTS = [
     "b200kv_last_error", "b200kv_version", "b200kv_create", "b200kv_destroy", "b200kv_seq_new", "b200kv_seq_free",
     "b200kv_seq_len", "b200kv_free_pages", "b200kv_page_bytes", "b200kv_append", "b200kv_attend", "b200kv_export",
     "b200kv_export_codes", "b200kv_truncate", "b200kv_fork", "b200kv_check", "b200kv_sdpa", "b200kv_profile",
-    "b200kv_profile_read", "b200kv_attend_static_scratch", "b200kv_export_kivi",
+    "b200kv_profile_read", "b200kv_attend_static_scratch", "b200kv_export_kivi", "b200kv_append_rope", "b200kv_rope",
 ]
 KERNEL_NAMES = {0: "table_scatter", 1: "append", 2: "decode", 3: "combine", 4: "export", 5: "sdpa_dense", 6: "prefill"}
 
@@ -62,6 +62,8 @@ def lib():
         L.b200kv_page_bytes.argtypes = [vp]
         L.b200kv_page_bytes.restype = i64
         L.b200kv_append.argtypes = [vp, i32, i32p, i32, vp, i64p, vp, i64p, i32, vp]
+        L.b200kv_append_rope.argtypes = [vp, i32, i32p, i32, vp, i64p, vp, i64p, vp, vp, i64p, i32, vp]
+        L.b200kv_rope.argtypes = [vp, i64p, vp, vp, i64p, vp, i64p, i32, i32, i32, i32, i32, vp]
         L.b200kv_attend.argtypes = [vp, i32, i32p, i32, i32, vp, i64p, vp, i64p, i32, C.c_float, i32, vp]
         L.b200kv_export.argtypes = [vp, i32, vp, i64p, vp, i64p, i32, vp]
         L.b200kv_export_codes.argtypes = [vp, i32, i32, vp, vp, vp]
@@ -163,6 +165,15 @@ class KvCache:
                                 v_new.data_ptr() if v_new is not None else None,
                                 _strides(v_new, 3) if v_new is not None else None, _dtype_code(k_new), _stream()))
 
+    def append_rope(self, seqs, k_new, v_new, cos, sin):
+        """append() with ApplyRope fused on the key side; cos / sin: [n_seqs or 1, S, D] of k_new's dtype."""
+        assert k_new.dim() == 4 and cos.dim() == 3 and cos.shape == sin.shape and cos.stride() == sin.stride()
+        rs = (C.c_int64 * 2)(0 if cos.shape[0] == 1 else cos.stride(0), cos.stride(1))
+        _ck(lib().b200kv_append_rope(self._h, len(seqs), _ids(seqs), k_new.shape[2], k_new.data_ptr(), _strides(k_new, 3),
+                                     v_new.data_ptr() if v_new is not None else None,
+                                     _strides(v_new, 3) if v_new is not None else None, cos.data_ptr(), sin.data_ptr(), rs,
+                                     _dtype_code(k_new), _stream()))
+
     def attend(self, seqs, q, scale=None, causal=True, out=None):
         """q: [n_seqs, Hq, S, D]; returns attention of the last S cached positions over the whole cache."""
         import torch
@@ -251,6 +262,18 @@ class KvCache:
         n = C.c_int32()
         _ck(lib().b200kv_profile_read(self._h, max_records, ids, ms, C.byref(n)))
         return [(KERNEL_NAMES.get(ids[i], str(ids[i])), ms[i]) for i in range(n.value)]
+
+
+def rope(x, cos, sin):
+    """ApplyRope on a [B, H, S, D] tensor; cos / sin: [B or 1, S, D]."""
+    import torch
+
+    out = torch.empty_like(x, memory_format=torch.contiguous_format)
+    rs = (C.c_int64 * 2)(0 if cos.shape[0] == 1 else cos.stride(0), cos.stride(1))
+    with torch.cuda.device(x.device):
+        _ck(lib().b200kv_rope(x.data_ptr(), _strides(x, 3), cos.data_ptr(), sin.data_ptr(), rs, out.data_ptr(), _strides(out, 3),
+                              x.shape[0], x.shape[1], x.shape[2], x.shape[3], _dtype_code(x), _stream()))
+    return out
 
 
 def sdpa(q, k, v, mask=None, scale=None, causal=False):

@@ -95,6 +95,10 @@ struct AppendParams {
     int32_t n_seqs, H, S, D;
     int32_t chunk_bytes, data_bytes, plane_w, units;  // units = 16-byte units per row
     int32_t dtype, vec_ok, has_v;
+    // optional rotary embedding applied to K on the way in: cos / sin [n_seqs, S, D], strides {batch, token}
+    const void* rope_cos;
+    const void* rope_sin;
+    int64_t rope_b, rope_s;
 };
 
 // Batch description of an append small enough to travel as a kernel parameter (no copy, no staging slot).
@@ -142,9 +146,23 @@ __global__ void __launch_bounds__(256) append_kernel(AppendParams p, const __gri
     float scale_f = 0.f;
     bool write_scale = false;
 
+    const bool rope = p.rope_cos != nullptr && kv == 0;
+    const uint8_t* row0 = (const uint8_t*)p.src[kv] + (b * p.sb[kv] + h * p.sh[kv] + s * p.ss[kv]) * esz;  // channel 0 of the row
+    const uint8_t* cos_row = (const uint8_t*)p.rope_cos + (b * p.rope_b + s * p.rope_s) * esz;
+    const uint8_t* sin_row = (const uint8_t*)p.rope_sin + (b * p.rope_b + s * p.rope_s) * esz;
     if constexpr (FMT == B200KV_FMT_F32 || FMT == B200KV_FMT_F16 || FMT == B200KV_FMT_BF16) {
         // bit copy: storage type == input type (checked on the host)
-        if (p.vec_ok) {
+        if (rope) {
+            uint32_t w[4] = {0, 0, 0, 0};
+#pragma unroll
+            for (int i = 0; i < EPU; i++) {
+                const float r = rope_row_elem(row0, cos_row, sin_row, p.dtype, p.D, c0 + i);
+                if (FMT == B200KV_FMT_F32) w[i % 4] = __float_as_uint(r);
+                else if (FMT == B200KV_FMT_F16) w[(i / 2) % 4] |= (uint32_t)__half_as_ushort(__float2half_rn(r)) << (16 * (i & 1));
+                else w[(i / 2) % 4] |= (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(r)) << (16 * (i & 1));
+            }
+            out16 = make_uint4(w[0], w[1], w[2], w[3]);
+        } else if (p.vec_ok) {
             out16 = *(const uint4*)src;
         } else {
             uint8_t tmp[16];
@@ -154,7 +172,10 @@ __global__ void __launch_bounds__(256) append_kernel(AppendParams p, const __gri
         }
     } else {
         float v[EPU];
-        if (p.dtype == B200KV_F32) {
+        if (rope) {
+#pragma unroll
+            for (int i = 0; i < EPU; i++) v[i] = rope_row_elem(row0, cos_row, sin_row, p.dtype, p.D, c0 + i);
+        } else if (p.dtype == B200KV_F32) {
             if (p.vec_ok) {
 #pragma unroll
                 for (int i = 0; i < EPU / 4; i++) {
@@ -523,10 +544,12 @@ int64_t b200kv_page_bytes(b200kv_cache* c) {
     return fmt_is_kivi(c->cfg.format) ? kivi_page_bytes(c) : c->L.page_bytes;
 }
 
-int b200kv_append(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t n_new, const void* k_new,
-                  const int64_t k_strides[3], const void* v_new, const int64_t v_strides[3], int32_t dtype,
-                  void* stream_) {
+static int append_impl(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t n_new, const void* k_new,
+                       const int64_t k_strides[3], const void* v_new, const int64_t v_strides[3], const void* rope_cos,
+                       const void* rope_sin, const int64_t* rope_strides, int32_t dtype, void* stream_) {
     if (validate_seqs(c, n_seqs, seqs) != B200KV_OK) return B200KV_KO;
+    if ((rope_cos != nullptr) != (rope_sin != nullptr) || (rope_cos && !rope_strides)) return fail("cos, sin and their strides come together");
+    if (rope_cos && fmt_is_kivi(c->L.fmt)) return fail("the fused rotary embedding is not available for KIVI caches: apply b200kv_rope first");
     cudaStream_t stream = (cudaStream_t)stream_;
     if (n_new < 0) return fail("n_new must be >= 0");
     if (n_new == 0) return B200KV_OK;
@@ -612,6 +635,7 @@ int b200kv_append(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t 
     p.chunk_bytes = c->L.chunk_bytes, p.data_bytes = c->L.data_bytes, p.plane_w = c->L.plane_w;
     p.units = c->L.row_bytes / 16;
     p.dtype = dtype, p.has_v = c->L.has_v;
+    if (rope_cos) p.rope_cos = rope_cos, p.rope_sin = rope_sin, p.rope_b = rope_strides[0], p.rope_s = rope_strides[1];
     // 16-byte vector loads need aligned bases and strides
     const int esz = dtype_size(dtype);
     auto aligned = [&](const void* ptr, const int64_t* st) {
@@ -640,6 +664,18 @@ int b200kv_append(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t 
     }
     for (int i = 0; i < n_seqs; i++) c->seqs[seqs[i]].len += n_new;
     return B200KV_OK;
+}
+
+int b200kv_append(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t n_new, const void* k_new,
+                  const int64_t k_strides[3], const void* v_new, const int64_t v_strides[3], int32_t dtype, void* stream) {
+    return append_impl(c, n_seqs, seqs, n_new, k_new, k_strides, v_new, v_strides, nullptr, nullptr, nullptr, dtype, stream);
+}
+
+int b200kv_append_rope(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t n_new, const void* k_new,
+                       const int64_t k_strides[3], const void* v_new, const int64_t v_strides[3], const void* cos,
+                       const void* sin, const int64_t rope_strides[2], int32_t dtype, void* stream) {
+    if (!cos || !sin) return fail("cos and sin are required");
+    return append_impl(c, n_seqs, seqs, n_new, k_new, k_strides, v_new, v_strides, cos, sin, rope_strides, dtype, stream);
 }
 
 int b200kv_export(b200kv_cache* c, int32_t seq, void* k_out, const int64_t k_strides[2], void* v_out,

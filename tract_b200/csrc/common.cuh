@@ -151,6 +151,26 @@ __device__ inline void st_from_f32(void* p, int dtype, int64_t i, float v) {
 }
 __host__ __device__ inline int dtype_size(int dtype) { return dtype == B200KV_F32 ? 4 : 2; }
 
+// ApplyRope (transformers/src/ops/apply_rope.rs:155-163): x * cos + rotate_half(x) * sin, where the three
+// operations are separate ops of the tensor's own type: each result is rounded to that type (for f16 / bf16 the
+// arithmetic is done in f32 and rounded back, as the `half` crate does), and nothing is fused.
+__device__ inline float round_to_dtype(float v, int dtype) {
+    if (dtype == B200KV_F16) return __half2float(__float2half_rn(v));
+    if (dtype == B200KV_BF16) return __bfloat162float(__float2bfloat16_rn(v));
+    return v;
+}
+__device__ inline float rope_value(float x, float rot, float c, float s, int dtype) {
+    const float a = round_to_dtype(__fmul_rn(x, c), dtype), b = round_to_dtype(__fmul_rn(rot, s), dtype);
+    return round_to_dtype(__fadd_rn(a, b), dtype);
+}
+// Element `ch` of ApplyRope(row, cos_row, sin_row) for rows of D elements of type dtype.
+__device__ inline float rope_row_elem(const void* row, const void* cos_row, const void* sin_row, int dtype, int D, int ch) {
+    const int half = D / 2;
+    const float x = ld_as_f32(row, dtype, ch);
+    const float rot = ch < half ? -ld_as_f32(row, dtype, ch + half) : ld_as_f32(row, dtype, ch - half);
+    return rope_value(x, rot, ld_as_f32(cos_row, dtype, ch), ld_as_f32(sin_row, dtype, ch), dtype);
+}
+
 // Decodes one piece (PB bytes at p, 16-byte aligned when PB == 16) into floats.  Block-quantised
 // formats return the integer codes as floats (Q8_1: byte - 128, Q4_0: nibble - 8); the caller applies the scale.
 template <int FMT, int PB>
