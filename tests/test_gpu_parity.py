@@ -282,6 +282,9 @@ def test_decode_explicit_scale_and_reuse_after_truncate(kv):
     ("f16", "f16", 6, 2, 128, 5, 100),      # G = 3: 42 queries per tile, two dead rows
     ("bf16", "bf16", 16, 2, 128, 300, 50),  # G = 8
     ("f16", "f16", 32, 8, 128, 4000, 512),  # chunked prefill: a 512-token chunk after 4000 cached tokens
+    # enough query tiles for the double-tile CTAs (two 128-row tiles share each staged K/V chunk)
+    ("f16", "f16", 32, 8, 128, 100, 1200),  # 1200 = 18 double tiles + 48 queries: the last CTA's second tile is half dead
+    ("bf16", "bf16", 32, 8, 128, 37, 1250),
 ])
 def test_prefill_matches_oracle(kv, fmt, io, Hq, Hkv, D, P, S):
     scale = 0.5 if io != "f32" else 1.0
@@ -300,11 +303,15 @@ def test_prefill_matches_oracle(kv, fmt, io, Hq, Hkv, D, P, S):
     cache.close()
 
 
-@pytest.mark.parametrize("io,causal", [("f16", True), ("f16", False), ("bf16", True)])
-def test_prefill_tensor_core_and_generic_paths_agree(kv, io, causal):
+@pytest.mark.parametrize("io,causal,Hq,Hkv,S", [
+    ("f16", True, 16, 4, 96), ("f16", False, 16, 4, 96), ("bf16", True, 16, 4, 96),
+    # double-tile CTAs; 600 = 9 x 64 + 24: the last CTA of each (sequence, head) has a second tile with no live row
+    ("f16", True, 32, 8, 600), ("bf16", False, 32, 8, 600),
+])
+def test_prefill_tensor_core_and_generic_paths_agree(kv, io, causal, Hq, Hkv, S):
     # two sequences of different length in one call; the tcgen05 kernel against export + generic kernel
-    Hq, Hkv, D, S, pasts = 16, 4, 128, 96, [200, 31]
-    cache = kv.KvCache(io, Hkv, D, max_seqs=2, max_seq_tokens=512)
+    D, pasts = 128, [200, 31]
+    cache = kv.KvCache(io, Hkv, D, max_seqs=2, max_seq_tokens=1024)
     seqs = [cache.new_seq() for _ in pasts]
     for b, P in enumerate(pasts):
         k, v = normal(500 + b, (1, Hkv, P, D)).astype(np_dtype(io)), normal(600 + b, (1, Hkv, P, D)).astype(np_dtype(io))

@@ -5,33 +5,50 @@
 // one q-head per CTA so every head of a GQA group re-streams K/V).  Semantics:
 // transformers/src/ops/flash_sdpa.rs:239-341 (causal aligned bottom-right, scale, f32 accumulation).
 //
-// One CTA = one 128-row query tile of one (sequence, kv head): the rows are (query, head-of-group) pairs,
-// so the whole GQA group shares each K/V page.  Per page of 64 cached tokens:
+// A query tile is 128 rows = (query, head-of-group) pairs of one (sequence, kv head), so the whole GQA group
+// shares each K/V page.  A CTA owns NQ such tiles of consecutive queries (NQ = 2: one CTA per SM, both tiles
+// read each K/V chunk from the same shared-memory stage; NQ = 1: two CTAs per SM, for launches too small to
+// fill the GPU with double tiles).  Per tile and per page of 64 cached tokens:
 //   S[128 x 64]  = Q . K^T      tcgen05.mma, A = Q tile in shared memory (K-major, 128-byte swizzle),
-//                               B = the K chunk exactly as it lies in the page (same swizzle), D in TMEM
-//   softmax                     two threads own a row: each tcgen05.ld's 32 of its 64 scores, masks, exponentiates in the
-//                               log2 domain against a lazily raised reference maximum, write P (16-bit)
-//                               back to TMEM with tcgen05.st
-//   O[128 x 128] += P . V       tcgen05.mma, A = P from TMEM (as a 16-bit value plus its 16-bit rounding remainder:
-//                               two MMAs), B = the V chunk as it lies in the page
-//                               (MN-major operand: channels contiguous), D accumulates in TMEM
-// K/V chunks arrive by untiled cp.async.bulk into a two-stage ring; two CTAs fit per SM so that one CTA's
-// softmax overlaps the other's MMAs.  Every wait is bounded; on expiry the CTA flags the status word,
-// frees its TMEM and returns.
+//                               B = the K chunk exactly as it lies in the page (same swizzle), D in TMEM;
+//                               S is double-buffered, so the product for page j+1 runs under the softmax of page j
+//   softmax                     two threads own a row: each tcgen05.ld's 32 of its 64 scores, masks, exponentiates in
+//                               the log2 domain against a lazily raised reference maximum and writes P (16-bit)
+//                               over the S buffer it came from with tcgen05.st
+//   O[128 x 128] += P . V       tcgen05.mma, A = P from TMEM, B = the V chunk as it lies in the page (MN-major
+//                               operand: channels contiguous), D accumulates in TMEM.  f16: one MMA per 16 tokens
+//                               (P carries 11 bits); bf16: P goes in as its 16-bit value plus the 16-bit rounding
+//                               remainder (two MMAs), or a row that sees few keys would carry the 2^-9 rounding
+// Roles: 256 softmax threads per tile; one warp that issues the K / V bulk copies (untiled cp.async.bulk into
+// two rings); one warp per tile that issues its MMAs and their commits.  Every wait is bounded; on expiry the
+// CTA flags the status word, lets every role run to the end of its loop without waiting any more, frees its
+// TMEM and returns.
 #include <cmath>
 
 #include "internal.h"
 
 namespace b200kv {
 
-constexpr int PD = 128;        // head_dim
-constexpr int PM = 128;        // rows of a query tile
-constexpr int P_NS = 2;        // K/V stages
+constexpr int PD = 128;                        // head_dim
+constexpr int PM = 128;                        // rows of a query tile
 constexpr int P_CHUNK = PAGE_TOKENS * PD * 2;  // bytes of one K (or V) chunk: 16 KiB
-constexpr int P_STAGE = 2 * P_CHUNK;
-constexpr int P_QBYTES = PM * PD * 2;          // 32 KiB
-constexpr uint32_t TMEM_COLS = 256;            // O: 128 columns, S: 64, P: 32 (16-bit pairs), P remainder: 32
-constexpr uint32_t COL_O = 0, COL_S = 128, COL_P = 192, COL_P2 = 224;
+constexpr int P_QBYTES = PM * PD * 2;          // 32 KiB per query tile
+constexpr int SM_THREADS = 256;                // softmax threads per query tile
+// TMEM columns of one query tile: O 0..127, S buffers at 128 and 192; P(j) overwrites S(j): value in columns
+// 0..31 of the buffer, rounding remainder in 32..63
+constexpr uint32_t COL_O = 0, COL_S = 128, COLS_PER_TILE = 256;
+// f16 P carries 11 bits: enough on average, but a row whose few visible keys cancel keeps the full 2^-12 of each
+// weight, which measured 2.4e-3 of the output's scale on a 512-token causal chunk; the remainder MMA removes it
+constexpr bool P_F16_REMAINDER = true;
+
+template <int NQ>
+struct PGeo {
+    static constexpr int NK = NQ == 2 ? 4 : 2;  // K stages
+    static constexpr int NV = NQ == 2 ? 5 : 2;  // V stages
+    static constexpr int THREADS = NQ * SM_THREADS + 32 * (1 + NQ);  // softmax threads, the copy warp, one MMA warp per tile
+    static constexpr int N_BARS = 2 * NK + 2 * NV + 5 * NQ;
+    static constexpr size_t SMEM = (size_t)NQ * P_QBYTES + (size_t)(NK + NV) * P_CHUNK + N_BARS * 8 + 16 + NQ * 2 * PM * 4;
+};
 
 struct PrefillParams {
     const uint8_t* pool;
@@ -88,6 +105,14 @@ __device__ inline void tmem_ld32(uint32_t taddr, uint32_t* r) {
         : "r"(taddr)
         : "memory");
 }
+__device__ inline void tmem_ld16(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
 __device__ inline void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ inline void tmem_st32(uint32_t taddr, const uint32_t* r) {
     asm volatile(
@@ -124,236 +149,332 @@ __device__ inline float fast_exp2(float x) {
     return y;
 }
 
-constexpr int P_THREADS = 256;
 
-// Two threads share a row of the 128-row tile: warps w and w + 4 both address TMEM lanes 32 (w & 3) .. + 32;
-// the first takes score columns 0..31 and output channels 0..63, the second the other halves.
-__global__ void __launch_bounds__(P_THREADS, 2) prefill_tc_kernel(PrefillParams p) {
+__device__ inline void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ inline bool mbar_test(uint64_t* bar, uint32_t parity) {  // one look, never suspends
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Waits for a barrier phase unless the CTA has already failed; gives up after ~1 s and marks the CTA failed.
+__device__ inline void wait_or_fail(uint64_t* bar, uint32_t parity, volatile int* fail) {
+    if (mbar_try_wait(bar, parity)) return;
+    const uint64_t t0 = globaltimer_ns();
+    for (;;) {
+        if (*fail) return;
+#pragma unroll 1
+        for (int i = 0; i < 32; i++)
+            if (mbar_try_wait(bar, parity)) return;
+        if (globaltimer_ns() - t0 > 1000000000ull) {
+            *fail = 1;
+            return;
+        }
+    }
+}
+// One lane of a converged warp (always the same one).
+__device__ inline bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n.reg .pred p;\nelect.sync _|p, 0xffffffff;\nselp.u32 %0, 1, 0, p;\n}\n" : "=r"(pred));
+    return pred != 0;
+}
+__device__ inline void pair_barrier(int id) { asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory"); }
+
+// Softmax threads of tile qt: warps w and w + 4 of the tile both address TMEM lanes 32 (w & 3) .. + 32 (a warp may
+// touch only the lane quarter of its index modulo 4); the first takes score columns 0..31 and output channels
+// 0..63 of its row, the second the other halves.
+template <int NQ>
+__global__ void __launch_bounds__(PGeo<NQ>::THREADS, NQ == 2 ? 1 : 2) prefill_tc_kernel(PrefillParams p) {
+    using GEO = PGeo<NQ>;
+    constexpr int NK = GEO::NK, NV = GEO::NV;
     extern __shared__ __align__(1024) uint8_t smem[];
-    uint8_t* q_s = smem;                    // [2 planes][128 rows][128 B], swizzled
-    uint8_t* stages = smem + P_QBYTES;      // P_NS x (K chunk, V chunk)
-    uint64_t* bar_full = (uint64_t*)(stages + P_NS * P_STAGE);  // [P_NS]
-    uint64_t* bar_mma = bar_full + P_NS;                        // [1]
-    uint32_t* tmem_slot = (uint32_t*)(bar_mma + 1);
-    int* fail_s = (int*)(tmem_slot + 1);
-    float* xchg = (float*)(fail_s + 1);     // [2 halves][128 rows]: row maxima, later row sums
+    uint8_t* q_s = smem;                                   // [NQ][2 planes][128 rows][128 B], swizzled
+    uint8_t* k_ring = smem + NQ * P_QBYTES;                // NK K chunks
+    uint8_t* v_ring = k_ring + NK * P_CHUNK;               // NV V chunks
+    uint64_t* full_k = (uint64_t*)(v_ring + NV * P_CHUNK);  // [NK] bytes landed
+    uint64_t* full_v = full_k + NK;                        // [NV]
+    uint64_t* free_k = full_v + NV;                        // [NK] every tile's Q.K^T on the stage has completed
+    uint64_t* free_v = free_k + NK;                        // [NV] every tile's P.V on the stage has completed
+    uint64_t* bar_s = free_v + NV;                         // [NQ][2] S buffer written
+    uint64_t* bar_p = bar_s + 2 * NQ;                      // [NQ][2] P written by the softmax warps
+    uint64_t* bar_o = bar_p + 2 * NQ;                      // [NQ] P.V of the latest page completed
+    uint32_t* tmem_slot = (uint32_t*)(bar_o + NQ);
+    volatile int* fail_s = (volatile int*)(tmem_slot + 1);
+    float* xchg = (float*)(tmem_slot + 4);                 // [NQ][2 halves][128 rows]: row maxima, later row sums
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int row = (warp & 3) * 32 + lane, half = warp >> 2;
     const int kvh = blockIdx.y, b = blockIdx.z;
-    const int G = p.G, qpt = PM / G;              // queries per tile
-    const int q0 = blockIdx.x * qpt;              // first query of this tile
+    const int G = p.G, qpt = PM / G;                       // queries per tile
+    const int cta_tile = (int)(gridDim.x - 1 - blockIdx.x);  // late queries see the most keys: schedule them first
     const int32_t trow = p.desc[2 * b], T = p.desc[2 * b + 1];
-    const int P0 = T - p.S;                       // cached tokens before the first new query
-    // row -> (query, head of the group); rows past the tile's queries are dead
-    const int rq = row / G, rg = row % G;
-    const bool live = rq < qpt && q0 + rq < p.S;
-    const int q_last = min(q0 + qpt, p.S) - 1;    // last live query of the tile
-    const int my_q = live ? q0 + rq : q_last;
-    const int my_limit = p.causal ? P0 + my_q : T - 1;           // last visible key of this row
-    const int tile_limit = p.causal ? P0 + q_last : T - 1;       // last key any row of the tile sees
-    const int min_limit = p.causal ? P0 + q0 : T - 1;            // last key EVERY row of the tile sees
-    const int n_tiles = tile_limit / PAGE_TOKENS + 1;
+    const int P0 = T - p.S;                                // cached tokens before the first new query
+    const int cta_q0 = cta_tile * NQ * qpt;
+    const int cta_q_last = min(cta_q0 + NQ * qpt, p.S) - 1;
+    // every tile of the CTA walks the pages up to the last key its last tile sees; a tile that ends earlier finds
+    // its extra page fully masked
+    const int n_tiles = (p.causal ? P0 + cta_q_last : T - 1) / PAGE_TOKENS + 1;
 
     if (tid == 0) {
-        for (int s = 0; s < P_NS; s++) mbar_init(&bar_full[s], 1);
-        mbar_init(bar_mma, 1);
+        for (int s = 0; s < NK; s++) mbar_init(&full_k[s], 1), mbar_init(&free_k[s], NQ);
+        for (int s = 0; s < NV; s++) mbar_init(&full_v[s], 1), mbar_init(&free_v[s], NQ);
+        for (int i = 0; i < 2 * NQ; i++) mbar_init(&bar_s[i], 1), mbar_init(&bar_p[i], SM_THREADS / 32);
+        for (int i = 0; i < NQ; i++) mbar_init(&bar_o[i], 1);
         *fail_s = (smem_u32(smem) & 1023u) ? 1 : 0;  // the swizzled operand tiles need a 1024-byte aligned base
         mbar_fence_init();
     }
-    auto issue_load = [&](int j) {  // thread 0
-        const int st = j % P_NS;
-        int32_t pg = p.table[(int64_t)trow * p.max_pages_per_seq + j];
-        if (pg < 0 || pg >= p.n_pages) {
-            atomicOr(p.status, STATUS_PAGE_OOB);
-            pg = 0;
-        }
-        mbar_expect_tx(&bar_full[st], P_STAGE);
-        bulk_g2s(stages + st * P_STAGE, p.pool + (int64_t)pg * p.page_bytes + (int64_t)kvh * P_STAGE, P_STAGE, &bar_full[st]);
-    };
-    if (tid == 0)
-        for (int j = 0; j < P_NS && j < n_tiles; j++) issue_load(j);
-    if (warp == 0) tmem_alloc(tmem_slot, TMEM_COLS);
+    if (warp == 0) tmem_alloc(tmem_slot, COLS_PER_TILE * NQ);
+
+    // per-thread tile geometry (softmax threads only; the extra warp gets harmless values)
+    const int qt = min(tid / SM_THREADS, NQ - 1), w8 = (tid % SM_THREADS) >> 5;
+    const int row = (w8 & 3) * 32 + lane, half = w8 >> 2;
+    const int q0 = cta_q0 + qt * qpt;
+    const int rq = row / G, rg = row % G;
+    const bool live = rq < qpt && q0 + rq < p.S;
+    const int q_last = max(min(q0 + qpt, p.S) - 1, 0);   // last live query of the tile (the tile may be all dead)
+    const int my_q = live ? q0 + rq : min(q_last, p.S - 1);
+    const int my_limit = p.causal ? P0 + my_q : T - 1;  // last visible key of this row
+    const int min_limit = p.causal ? P0 + min(q0, p.S - 1) : T - 1;  // last key EVERY row of the tile sees
+    const bool is_softmax = tid < NQ * SM_THREADS;
 
     // ---- Q tile -> shared memory, K-major with the 128-byte swizzle (row r: 16-byte unit u of plane pl at u ^ (r & 7));
     //      this thread moves the 64 channels of plane `half` of its row ----
-    {
+    if (is_softmax) {
         const int head = kvh * G + rg;
         const uint4* src = (const uint4*)((const uint16_t*)p.q + (int64_t)b * p.qb + (int64_t)head * p.qh + (int64_t)my_q * p.qs) + half * 8;
 #pragma unroll
         for (int uu = 0; uu < 8; uu++) {
             uint4 v = live ? src[uu] : make_uint4(0, 0, 0, 0);
-            *(uint4*)(q_s + half * (PM * 128) + row * 128 + ((uu ^ (row & 7)) << 4)) = v;
+            *(uint4*)(q_s + qt * P_QBYTES + half * (PM * 128) + row * 128 + ((uu ^ (row & 7)) << 4)) = v;
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the tensor core
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    if (*fail_s) {
-        if (tid == 0) atomicOr(p.status, STATUS_WAIT_EXPIRED);
-        if (warp == 0) tmem_dealloc(*tmem_slot, TMEM_COLS);
-        return;
-    }
     const uint32_t tmem = *tmem_slot;
-    const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);  // this warp's quarter of the 128 lanes
-    const uint32_t idesc_s = instr_desc(p.is_bf16, 0, PM, PAGE_TOKENS);
-    const uint32_t idesc_o = instr_desc(p.is_bf16, 1, PM, PD);
-    const uint32_t q_addr = smem_u32(q_s);
 
-    auto issue_s = [&](int j) {  // thread 0: S = Q . K^T for tile j (8 MMAs of K = 16)
-        const uint32_t k_addr = smem_u32(stages + (j % P_NS) * P_STAGE);
-#pragma unroll
-        for (int pl = 0; pl < 2; pl++)
-#pragma unroll
-            for (int kk = 0; kk < 4; kk++)
-                tc_mma_ss(tmem + COL_S, smem_desc(q_addr + pl * (PM * 128) + kk * 32, 0, 1024),
-                          smem_desc(k_addr + pl * (PAGE_TOKENS * 128) + kk * 32, 0, 1024), idesc_s, (pl | kk) ? 1u : 0u);
-        tc_commit(bar_mma);
-    };
-
-    bool ok = true;
-    if (tid == 0) {
-        ok = mbar_wait_bounded(&bar_full[0], 0);
-        if (ok) issue_s(0);
-    }
-
-    const float sl2 = p.scale * 1.4426950408889634f;  // scores enter the exponent in log2 units
-    float m_ref = -INFINITY, l_run = 0.f;             // l_run: this thread's half of the row sum
-
-    for (int j = 0; j < n_tiles; j++) {
-        // S(j) ready; every MMA issued before it (P.V of tile j-1) has completed as well
-        ok = ok && mbar_wait_bounded(bar_mma, (uint32_t)(j & 1));
-        tc_fence_after();
-        // ---- this thread's 32 of the row's 64 scores ----
-        uint32_t sr[32];
-        tmem_ld32(lane_base + COL_S + 32 * half, sr);
-        tmem_ld_wait();
-        float tmax = -INFINITY;
-        if (j * PAGE_TOKENS + PAGE_TOKENS - 1 > min_limit) {  // only tiles on the causal diagonal / past the end need a mask
-            const int t0 = j * PAGE_TOKENS + 32 * half;
-#pragma unroll
-            for (int c = 0; c < 32; c++) {
-                const float s = (t0 + c <= my_limit) ? __uint_as_float(sr[c]) : -INFINITY;
-                sr[c] = __float_as_uint(s);
-                tmax = fmaxf(tmax, s);
+    if (!is_softmax) {
+        // Every lane of these warps walks the loop (the values stay warp-uniform); one elected lane issues.
+        const int role = warp - NQ * (SM_THREADS / 32);  // 0: copies, 1 + t: MMAs of tile t
+        if (role == 0) {
+            // ================= K / V copies into the two rings =================
+            const int32_t* trow_p = p.table + (int64_t)trow * p.max_pages_per_seq;
+            int32_t pg_next = trow_p[0];
+            for (int i = 0; i < n_tiles; i++) {
+                int32_t pg = pg_next;
+                if (i + 1 < n_tiles) pg_next = trow_p[i + 1];  // fetched one page ahead of its use
+                if (pg < 0 || pg >= p.n_pages) {
+                    if (lane == 0) atomicOr(p.status, STATUS_PAGE_OOB);
+                    pg = 0;
+                }
+                const uint8_t* src = p.pool + (int64_t)pg * p.page_bytes + (int64_t)kvh * (2 * P_CHUNK);
+                if (i >= NK) wait_or_fail(&free_k[i % NK], (uint32_t)((i / NK - 1) & 1), fail_s);
+                if (elect_one()) {
+                    mbar_expect_tx(&full_k[i % NK], P_CHUNK);
+                    bulk_g2s(k_ring + (i % NK) * P_CHUNK, src, P_CHUNK, &full_k[i % NK]);
+                }
+                __syncwarp();
+                if (i >= NV) wait_or_fail(&free_v[i % NV], (uint32_t)((i / NV - 1) & 1), fail_s);
+                if (elect_one()) {
+                    mbar_expect_tx(&full_v[i % NV], P_CHUNK);
+                    bulk_g2s(v_ring + (i % NV) * P_CHUNK, src + P_CHUNK, P_CHUNK, &full_v[i % NV]);
+                }
+                __syncwarp();
             }
         } else {
+            // ================= MMAs of tile t = role - 1 =================
+            const int t = role - 1;
+            const uint32_t tm = tmem + t * COLS_PER_TILE;
+            const uint32_t idesc_s = instr_desc(p.is_bf16, 0, PM, PAGE_TOKENS);
+            const uint32_t idesc_o = instr_desc(p.is_bf16, 1, PM, PD);
+            // descriptors of the ring bases; a byte offset inside the 256 KiB window adds offset / 16 to the address field
+            const uint64_t q_desc = smem_desc(smem_u32(q_s) + t * P_QBYTES, 0, 1024);
+            const uint64_t k_desc = smem_desc(smem_u32(k_ring), 0, 1024);
+            const uint64_t v_desc = smem_desc(smem_u32(v_ring), p.v_lbo, p.v_sbo);
+            const bool two = p.is_bf16 != 0 || P_F16_REMAINDER;
+            // S(j) = Q . K(j)^T into buffer j & 1
+            auto issue_qk = [&](int j) {
+                wait_or_fail(&full_k[j % NK], (uint32_t)((j / NK) & 1), fail_s);
+                tc_fence_after();
+                if (elect_one()) {
+                    const uint64_t kd = k_desc + (uint64_t)(((j % NK) * P_CHUNK) >> 4);
 #pragma unroll
-            for (int c = 0; c < 32; c++) tmax = fmaxf(tmax, __uint_as_float(sr[c]));
-        }
-        xchg[half * PM + row] = tmax;
-        if (__syncthreads_or(!ok)) {  // also the barrier of the maxima exchange
-            ok = false;
-            break;
-        }
-        // stage of tile j-1 is free now: refill it
-        if (tid == 0 && j >= 1 && j - 1 + P_NS < n_tiles) issue_load(j - 1 + P_NS);
-        tmax = fmaxf(tmax, xchg[(half ^ 1) * PM + row]) * sl2;
-        // raise the reference maximum only when it is exceeded by more than 2^8: the exponentials stay below
-        // 256, exact enough in 16 bits, and O has to be rescaled only rarely
-        float alpha = 1.f;
-        if (j == 0) {
-            m_ref = tmax;
-        } else if (tmax > m_ref + 8.f) {
-            alpha = fast_exp2(m_ref - tmax);
-            m_ref = tmax;
-            l_run *= alpha;
-        }
-        if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+                    for (int pl = 0; pl < 2; pl++)
 #pragma unroll
-            for (int cc = 0; cc < 2; cc++) {  // this thread's 64 of the row's 128 output channels
-                uint32_t orow[32];
-                tmem_ld32(lane_base + COL_O + 64 * half + cc * 32, orow);
-                tmem_ld_wait();
-#pragma unroll
-                for (int c = 0; c < 32; c++) orow[c] = __float_as_uint(__uint_as_float(orow[c]) * alpha);
-                tmem_st32(lane_base + COL_O + 64 * half + cc * 32, orow);
-            }
-        }
-        // P goes to the tensor core as two 16-bit operands, the rounded value and the rounding remainder:
-        // a row that sees only a few keys gets no averaging of the 2^-11 (f16) / 2^-8 (bf16) rounding errors,
-        // and with the remainder the product P . V is exact to ~2^-22
-        uint32_t pr[16], pr2[16];
-        float lsum = 0.f;
-#pragma unroll
-        for (int c = 0; c < 16; c++) {
-            const float p0 = fast_exp2(fmaf(__uint_as_float(sr[2 * c]), sl2, -m_ref));
-            const float p1 = fast_exp2(fmaf(__uint_as_float(sr[2 * c + 1]), sl2, -m_ref));
-            lsum += p0 + p1;
-            if (p.is_bf16) {
-                __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-                __nv_bfloat162 l = __floats2bfloat162_rn(p0 - __low2float(h), p1 - __high2float(h));
-                pr[c] = *(uint32_t*)&h, pr2[c] = *(uint32_t*)&l;
-            } else {
-                __half2 h = __floats2half2_rn(p0, p1);
-                __half2 l = __floats2half2_rn(p0 - __low2float(h), p1 - __high2float(h));
-                pr[c] = *(uint32_t*)&h, pr2[c] = *(uint32_t*)&l;
-            }
-        }
-        l_run += lsum;
-        tmem_st16(lane_base + COL_P + 16 * half, pr);
-        tmem_st16(lane_base + COL_P2 + 16 * half, pr2);
-        tmem_st_wait();
-        tc_fence_before();
-        __syncthreads();
-        if (tid == 0) {
-            tc_fence_after();
-            // O (+)= P . V : 4 MMAs of K = 16 tokens; the V chunk is an MN-major operand
-            const uint32_t v_addr = smem_u32(stages + (j % P_NS) * P_STAGE + P_CHUNK);
-#pragma unroll
-            for (int kk = 0; kk < 4; kk++) {
-                const uint64_t vdesc = smem_desc(v_addr + kk * 2048, p.v_lbo, p.v_sbo);
-                tc_mma_ts(tmem + COL_O, tmem + COL_P + kk * 8, vdesc, idesc_o, (j | kk) ? 1u : 0u);
-                tc_mma_ts(tmem + COL_O, tmem + COL_P2 + kk * 8, vdesc, idesc_o, 1u);
-            }
-            if (j + 1 < n_tiles) {
-                ok = mbar_wait_bounded(&bar_full[(j + 1) % P_NS], (uint32_t)(((j + 1) / P_NS) & 1));
-                if (ok) issue_s(j + 1);  // commits for S(j+1) and, in order, for P.V(j)
-            } else {
-                tc_commit(bar_mma);
-            }
-        }
-    }
-    // ---- epilogue: wait for the last P.V, normalise, store ----
-    if (ok) ok = mbar_wait_bounded(bar_mma, (uint32_t)(n_tiles & 1));
-    xchg[half * PM + row] = l_run;
-    ok = !__syncthreads_or(!ok);
-    if (ok) {
-        tc_fence_after();
-        const float inv = 1.f / (l_run + xchg[(half ^ 1) * PM + row]);
-        uint16_t* dst = (uint16_t*)p.out + (int64_t)b * p.ob + (int64_t)(kvh * G + rg) * p.oh + (int64_t)my_q * p.os + 64 * half;
-#pragma unroll
-        for (int cc = 0; cc < 2; cc++) {
-            uint32_t orow[32];
-            tmem_ld32(lane_base + COL_O + 64 * half + cc * 32, orow);
-            tmem_ld_wait();
-            if (live) {
-#pragma unroll
-                for (int c = 0; c < 32; c += 8) {
-                    uint32_t w[4];
-#pragma unroll
-                    for (int e = 0; e < 4; e++) {
-                        const float a = __uint_as_float(orow[c + 2 * e]) * inv, bb = __uint_as_float(orow[c + 2 * e + 1]) * inv;
-                        if (p.is_bf16) {
-                            __nv_bfloat162 h = __floats2bfloat162_rn(a, bb);
-                            w[e] = *(uint32_t*)&h;
-                        } else {
-                            __half2 h = __floats2half2_rn(a, bb);
-                            w[e] = *(uint32_t*)&h;
+                        for (int kk = 0; kk < 4; kk++) {
+                            const uint64_t off = (uint64_t)((pl * (PM * 128) + kk * 32) >> 4);
+                            tc_mma_ss(tm + COL_S + 64 * (j & 1), q_desc + off, kd + (uint64_t)((pl * (PAGE_TOKENS * 128) + kk * 32) >> 4),
+                                      idesc_s, (pl | kk) ? 1u : 0u);
                         }
-                    }
-                    *(uint4*)(dst + cc * 32 + c) = make_uint4(w[0], w[1], w[2], w[3]);
+                    tc_commit(&bar_s[2 * t + (j & 1)]);
+                    tc_commit(&free_k[j % NK]);
                 }
+                __syncwarp();
+            };
+            issue_qk(0);
+            if (n_tiles > 1) issue_qk(1);
+            for (int j = 0; j < n_tiles; j++) {
+                // O += P(j) . V(j): 4 steps of 16 tokens; the V chunk is an MN-major operand
+                wait_or_fail(&full_v[j % NV], (uint32_t)((j / NV) & 1), fail_s);
+                wait_or_fail(&bar_p[2 * t + (j & 1)], (uint32_t)((j >> 1) & 1), fail_s);
+                tc_fence_after();
+                if (elect_one()) {
+                    const uint64_t vd = v_desc + (uint64_t)(((j % NV) * P_CHUNK) >> 4);
+                    const uint32_t pa = tm + COL_S + 64 * (j & 1);
+#pragma unroll
+                    for (int kk = 0; kk < 4; kk++) {
+                        tc_mma_ts(tm + COL_O, pa + kk * 8, vd + (uint64_t)((kk * 2048) >> 4), idesc_o, (j | kk) ? 1u : 0u);
+                        if (two) tc_mma_ts(tm + COL_O, pa + 32 + kk * 8, vd + (uint64_t)((kk * 2048) >> 4), idesc_o, 1u);
+                    }
+                    tc_commit(&bar_o[t]);
+                    tc_commit(&free_v[j % NV]);
+                }
+                __syncwarp();
+                // S(j + 2) reuses the buffer P(j) sits in: the tensor core runs one thread's MMAs in issue order, so the
+                // product just issued has read P before this one writes S
+                if (j + 2 < n_tiles) issue_qk(j + 2);
             }
         }
     } else {
-        if (tid == 0) atomicOr(p.status, STATUS_WAIT_EXPIRED);
-        __nanosleep(200000);  // give copies that may still be in flight time to land before the CTA's memory is released
+
+        // ================= softmax threads =================
+        const uint32_t lane_base = tmem + qt * COLS_PER_TILE + ((uint32_t)((w8 & 3) * 32) << 16);  // this warp's lane quarter
+        float* xq = xchg + qt * (2 * PM);
+        const int pair_id = 1 + qt * 4 + (w8 & 3);        // named barrier of the two warps that share these 32 rows
+        const float sl2 = p.scale * 1.4426950408889634f;  // scores enter the exponent in log2 units
+        float m_ref = -INFINITY, l_run = 0.f;             // l_run: this thread's half of the row sum
+
+        for (int j = 0; j < n_tiles; j++) {
+            const uint32_t sbuf = lane_base + COL_S + 64 * (j & 1);
+            wait_or_fail(&bar_s[2 * qt + (j & 1)], (uint32_t)((j >> 1) & 1), fail_s);
+            tc_fence_after();
+            // ---- this thread's 32 of the row's 64 scores ----
+            uint32_t sr[32];
+            tmem_ld32(sbuf + 32 * half, sr);
+            tmem_ld_wait();
+            float tmax = -INFINITY;
+            if (j * PAGE_TOKENS + PAGE_TOKENS - 1 > min_limit) {  // only pages on the causal diagonal / past the end need a mask
+                const int t0 = j * PAGE_TOKENS + 32 * half;
+#pragma unroll
+                for (int c = 0; c < 32; c++) {
+                    const float s = (t0 + c <= my_limit) ? __uint_as_float(sr[c]) : -INFINITY;
+                    sr[c] = __float_as_uint(s);
+                    tmax = fmaxf(tmax, s);
+                }
+            } else {
+#pragma unroll
+                for (int c = 0; c < 32; c++) tmax = fmaxf(tmax, __uint_as_float(sr[c]));
+            }
+            xq[half * PM + row] = tmax;
+            pair_barrier(pair_id);  // maxima exchanged; both halves of S(j) are in registers, so P may overwrite them
+            tmax = fmaxf(tmax, xq[(half ^ 1) * PM + row]) * sl2;
+            // raise the reference maximum only when it is exceeded by more than 2^8: the exponentials stay below
+            // 256, exact enough in 16 bits, and O has to be rescaled only rarely
+            float alpha = 1.f;
+            if (j == 0) {
+                m_ref = tmax;
+            } else if (tmax > m_ref + 8.f) {
+                alpha = fast_exp2(m_ref - tmax);
+                m_ref = tmax;
+                l_run *= alpha;
+            }
+            if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+                wait_or_fail(&bar_o[qt], (uint32_t)((j - 1) & 1), fail_s);  // O holds every page before this one
+                tc_fence_after();
+#pragma unroll
+                for (int cc = 0; cc < 4; cc++) {  // this thread's 64 of the row's 128 output channels
+                    uint32_t orow[16];
+                    tmem_ld16(lane_base + COL_O + 64 * half + cc * 16, orow);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int c = 0; c < 16; c++) orow[c] = __float_as_uint(__uint_as_float(orow[c]) * alpha);
+                    tmem_st16(lane_base + COL_O + 64 * half + cc * 16, orow);
+                }
+            }
+            uint32_t pr[16];
+            float lsum = 0.f;
+            if (p.is_bf16) {
+                uint32_t pr2[16];
+#pragma unroll
+                for (int c = 0; c < 16; c++) {
+                    const float p0 = fast_exp2(fmaf(__uint_as_float(sr[2 * c]), sl2, -m_ref));
+                    const float p1 = fast_exp2(fmaf(__uint_as_float(sr[2 * c + 1]), sl2, -m_ref));
+                    lsum += p0 + p1;
+                    __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+                    __nv_bfloat162 l = __floats2bfloat162_rn(p0 - __low2float(h), p1 - __high2float(h));
+                    pr[c] = *(uint32_t*)&h, pr2[c] = *(uint32_t*)&l;
+                }
+                tmem_st16(sbuf + 32 + 16 * half, pr2);
+            } else {
+                uint32_t pr2[16];
+#pragma unroll
+                for (int c = 0; c < 16; c++) {
+                    const float p0 = fast_exp2(fmaf(__uint_as_float(sr[2 * c]), sl2, -m_ref));
+                    const float p1 = fast_exp2(fmaf(__uint_as_float(sr[2 * c + 1]), sl2, -m_ref));
+                    lsum += p0 + p1;
+                    __half2 h = __floats2half2_rn(p0, p1);
+                    pr[c] = *(uint32_t*)&h;
+                    if (P_F16_REMAINDER) {
+                        __half2 l = __floats2half2_rn(p0 - __low2float(h), p1 - __high2float(h));
+                        pr2[c] = *(uint32_t*)&l;
+                    }
+                }
+                if (P_F16_REMAINDER) tmem_st16(sbuf + 32 + 16 * half, pr2);
+            }
+            l_run += lsum;
+            tmem_st16(sbuf + 16 * half, pr);
+            tmem_st_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bar_p[2 * qt + (j & 1)]);
+        }
+        // ---- epilogue: wait for the last P.V, normalise, store ----
+        wait_or_fail(&bar_o[qt], (uint32_t)((n_tiles - 1) & 1), fail_s);
+        tc_fence_after();
+        xq[half * PM + row] = l_run;
+        pair_barrier(pair_id);
+        if (!*fail_s) {
+            const float inv = 1.f / (l_run + xq[(half ^ 1) * PM + row]);
+            uint16_t* dst = (uint16_t*)p.out + (int64_t)b * p.ob + (int64_t)(kvh * G + rg) * p.oh + (int64_t)my_q * p.os + 64 * half;
+#pragma unroll
+            for (int cc = 0; cc < 2; cc++) {
+                uint32_t orow[32];
+                tmem_ld32(lane_base + COL_O + 64 * half + cc * 32, orow);
+                tmem_ld_wait();
+                if (live) {
+#pragma unroll
+                    for (int c = 0; c < 32; c += 8) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int e = 0; e < 4; e++) {
+                            const float a = __uint_as_float(orow[c + 2 * e]) * inv, bb = __uint_as_float(orow[c + 2 * e + 1]) * inv;
+                            if (p.is_bf16) {
+                                __nv_bfloat162 h = __floats2bfloat162_rn(a, bb);
+                                w[e] = *(uint32_t*)&h;
+                            } else {
+                                __half2 h = __floats2half2_rn(a, bb);
+                                w[e] = *(uint32_t*)&h;
+                            }
+                        }
+                        *(uint4*)(dst + cc * 32 + c) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                }
+            }
+        }
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 0) tmem_dealloc(tmem, TMEM_COLS);
+    if (*fail_s) {
+        if (tid == 0) atomicOr(p.status, STATUS_WAIT_EXPIRED);
+        __nanosleep(200000);  // give copies that may still be in flight time to land before the CTA's memory is released
+        __syncthreads();
+    }
+    if (warp == 0) tmem_dealloc(tmem, COLS_PER_TILE * NQ);
 }
 
 bool prefill_tc_supported(const b200kv_cache* c, int n_q_heads, int dtype, const void* q, const int64_t* qs, const void* out,
@@ -367,6 +488,17 @@ bool prefill_tc_supported(const b200kv_cache* c, int n_q_heads, int dtype, const
         return (uintptr_t)ptr % 16 == 0 && (st[0] * 2) % 16 == 0 && (st[1] * 2) % 16 == 0 && (st[2] * 2) % 16 == 0;
     };
     return aligned(q, qs) && aligned(out, os);
+}
+
+template <int NQ>
+static cudaError_t launch_tiles(const PrefillParams& p, int n_seqs, cudaStream_t stream) {
+    using GEO = PGeo<NQ>;
+    cudaError_t e = cudaFuncSetAttribute(prefill_tc_kernel<NQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEO::SMEM);
+    if (e != cudaSuccess) return e;
+    const int per_cta = NQ * (PM / p.G);
+    dim3 grid((p.S + per_cta - 1) / per_cta, p.Hkv, n_seqs);
+    prefill_tc_kernel<NQ><<<grid, GEO::THREADS, GEO::SMEM, stream>>>(p);
+    return cudaGetLastError();
 }
 
 int launch_prefill_tc(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t n_q_heads, int32_t n_new, const void* q,
@@ -391,15 +523,14 @@ int launch_prefill_tc(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int3
     // V chunk = 2 planes of 64 channels (8192 bytes apart), 8-token groups 1024 bytes apart
     p.v_lbo = 8192, p.v_sbo = 1024;
     p.scale = scale;
-    const size_t smem = P_QBYTES + (size_t)P_NS * P_STAGE + 64 + 2 * PM * 4;
-    B200KV_CUDA(cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    // double tiles (one CTA per SM, K/V staged once for 2 x 128 rows) when they still fill the GPU
     const int qpt = PM / G;
-    dim3 grid((n_new + qpt - 1) / qpt, c->L.Hkv, n_seqs);
+    const int64_t double_ctas = (int64_t)((n_new + 2 * qpt - 1) / (2 * qpt)) * c->L.Hkv * n_seqs;
+    cudaError_t e;
     {
         ProfScope ps(c, K_PREFILL, stream);
-        prefill_tc_kernel<<<grid, P_THREADS, smem, stream>>>(p);
+        e = double_ctas >= 148 /* SMs of a B200 */ ? launch_tiles<2>(p, n_seqs, stream) : launch_tiles<1>(p, n_seqs, stream);
     }
-    cudaError_t e = cudaGetLastError();
     staging_release(c, slot, stream);
     if (e != cudaSuccess) return fail("prefill launch failed: %s", cudaGetErrorString(e));
     return B200KV_OK;
