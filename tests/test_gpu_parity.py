@@ -329,6 +329,23 @@ def test_prefill_tensor_core_and_generic_paths_agree(kv, io, causal, Hq, Hkv, S)
     cache.close()
 
 
+def test_prefill_repeats_bit_identically(kv):
+    # 25 launches of one chunk whose last page is visible to the last eight queries of each tile only: a wait that
+    # lets the epilogue read O before the last product has landed shows up as a changing result in exactly those rows
+    Hq, Hkv, D, S, P = 32, 8, 128, 600, 200
+    cache = kv.KvCache("f16", Hkv, D, max_seqs=1, max_seq_tokens=1024)
+    sq = cache.new_seq()
+    k, v = normal(31, (1, Hkv, P + S, D)).astype(np.float16), normal(32, (1, Hkv, P + S, D)).astype(np.float16)
+    cache.append([sq], to_dev(k), to_dev(v))
+    q = to_dev(normal(33, (1, Hq, S, D)).astype(np.float16))
+    first = cache.attend([sq], q, causal=True).cpu().numpy()
+    for _ in range(24):
+        again = cache.attend([sq], q, causal=True).cpu().numpy()
+        assert again.tobytes() == first.tobytes()
+    cache.check()
+    cache.close()
+
+
 # ---- lone Sdpa: golden bundles, the reference's kernel-test shapes, property sweep ------------------------
 
 ATTN_CASES = ["simple-causal-f32", "simple-non-causal-f32", "simple-scale-f32", "simple-f16", "simple-mask-f32"]

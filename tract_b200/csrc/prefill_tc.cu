@@ -24,6 +24,7 @@
 // CTA flags the status word, lets every role run to the end of its loop without waiting any more, frees its
 // TMEM and returns.
 #include <cmath>
+#include <cstdlib>
 
 #include "internal.h"
 
@@ -37,9 +38,16 @@ constexpr int SM_THREADS = 256;                // softmax threads per query tile
 // TMEM columns of one query tile: O 0..127, S buffers at 128 and 192; P(j) overwrites S(j): value in columns
 // 0..31 of the buffer, rounding remainder in 32..63
 constexpr uint32_t COL_O = 0, COL_S = 128, COLS_PER_TILE = 256;
-// f16 P carries 11 bits: enough on average, but a row whose few visible keys cancel keeps the full 2^-12 of each
-// weight, which measured 2.4e-3 of the output's scale on a 512-token causal chunk; the remainder MMA removes it
-constexpr bool P_F16_REMAINDER = true;
+// (f16 P carries 11 bits: enough once a row's sum is spread over many keys, but a row whose few visible keys cancel
+// keeps the full 2^-12 of each weight, which measured 2.4e-3 of the output's scale on a 512-token causal chunk;
+// the remainder MMA removes it and is dropped page by page, see P_SKIP_FRACTION)
+
+// per query tile and per parity of the page index: the two half-row maxima of every row, then one flag per softmax warp
+constexpr int XCHG_FLOATS = 2 * PM + 8;
+// f16 weights skip the remainder MMA of a page once, for every row of the tile, sqrt(32) x the largest weight of the
+// page is below this fraction of the row's running sum (each half row judged on its own 32 columns): what the
+// rounding of such a page can add is then below 2^-12 / 8 of the row's scale
+constexpr float P_SKIP_FRACTION = 0.125f;
 
 template <int NQ>
 struct PGeo {
@@ -47,7 +55,7 @@ struct PGeo {
     static constexpr int NV = NQ == 2 ? 5 : 2;  // V stages
     static constexpr int THREADS = NQ * SM_THREADS + 32 * (1 + NQ);  // softmax threads, the copy warp, one MMA warp per tile
     static constexpr int N_BARS = 2 * NK + 2 * NV + 5 * NQ;
-    static constexpr size_t SMEM = (size_t)NQ * P_QBYTES + (size_t)(NK + NV) * P_CHUNK + N_BARS * 8 + 16 + NQ * 2 * PM * 4;
+    static constexpr size_t SMEM = (size_t)NQ * P_QBYTES + (size_t)(NK + NV) * P_CHUNK + N_BARS * 8 + 32 + NQ * 2 * XCHG_FLOATS * 4;
 };
 
 struct PrefillParams {
@@ -62,6 +70,7 @@ struct PrefillParams {
     int32_t n_pages, max_pages_per_seq, Hkv, G, S, causal, is_bf16;
     uint32_t v_lbo, v_sbo;  // V operand descriptor strides (bytes)
     float scale;
+    float skip_fraction;
 };
 
 // ---- tcgen05 wrappers -------------------------------------------------------------------------------
@@ -203,9 +212,9 @@ __global__ void __launch_bounds__(PGeo<NQ>::THREADS, NQ == 2 ? 1 : 2) prefill_tc
     uint64_t* bar_s = free_v + NV;                         // [NQ][2] S buffer written
     uint64_t* bar_p = bar_s + 2 * NQ;                      // [NQ][2] P written by the softmax warps
     uint64_t* bar_o = bar_p + 2 * NQ;                      // [NQ] P.V of the latest page completed
-    uint32_t* tmem_slot = (uint32_t*)(bar_o + NQ);
+    uint32_t* tmem_slot = (uint32_t*)(((uintptr_t)(bar_o + NQ) + 15) & ~(uintptr_t)15);
     volatile int* fail_s = (volatile int*)(tmem_slot + 1);
-    float* xchg = (float*)(tmem_slot + 4);                 // [NQ][2 halves][128 rows]: row maxima, later row sums
+    float* xchg = (float*)(tmem_slot + 4);                 // [NQ][2 parities][XCHG_FLOATS]: row maxima / sums and remainder flags
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int kvh = blockIdx.y, b = blockIdx.z;
@@ -296,7 +305,7 @@ __global__ void __launch_bounds__(PGeo<NQ>::THREADS, NQ == 2 ? 1 : 2) prefill_tc
             const uint64_t q_desc = smem_desc(smem_u32(q_s) + t * P_QBYTES, 0, 1024);
             const uint64_t k_desc = smem_desc(smem_u32(k_ring), 0, 1024);
             const uint64_t v_desc = smem_desc(smem_u32(v_ring), p.v_lbo, p.v_sbo);
-            const bool two = p.is_bf16 != 0 || P_F16_REMAINDER;
+            const bool adaptive = !p.is_bf16;
             // S(j) = Q . K(j)^T into buffer j & 1
             auto issue_qk = [&](int j) {
                 wait_or_fail(&full_k[j % NK], (uint32_t)((j / NK) & 1), fail_s);
@@ -323,6 +332,9 @@ __global__ void __launch_bounds__(PGeo<NQ>::THREADS, NQ == 2 ? 1 : 2) prefill_tc
                 wait_or_fail(&full_v[j % NV], (uint32_t)((j / NV) & 1), fail_s);
                 wait_or_fail(&bar_p[2 * t + (j & 1)], (uint32_t)((j >> 1) & 1), fail_s);
                 tc_fence_after();
+                // the softmax warps say, one flag each, whether this page's weights need their remainder
+                const int* flags = (const int*)(xchg + (2 * t + (j & 1)) * XCHG_FLOATS + 2 * PM);
+                const bool two = !adaptive || __any_sync(0xffffffffu, flags[lane & 7] != 0);
                 if (elect_one()) {
                     const uint64_t vd = v_desc + (uint64_t)(((j % NV) * P_CHUNK) >> 4);
                     const uint32_t pa = tm + COL_S + 64 * (j & 1);
@@ -344,8 +356,8 @@ __global__ void __launch_bounds__(PGeo<NQ>::THREADS, NQ == 2 ? 1 : 2) prefill_tc
 
         // ================= softmax threads =================
         const uint32_t lane_base = tmem + qt * COLS_PER_TILE + ((uint32_t)((w8 & 3) * 32) << 16);  // this warp's lane quarter
-        float* xq = xchg + qt * (2 * PM);
         const int pair_id = 1 + qt * 4 + (w8 & 3);        // named barrier of the two warps that share these 32 rows
+        const bool adaptive = !p.is_bf16;
         const float sl2 = p.scale * 1.4426950408889634f;  // scores enter the exponent in log2 units
         float m_ref = -INFINITY, l_run = 0.f;             // l_run: this thread's half of the row sum
 
@@ -370,6 +382,16 @@ __global__ void __launch_bounds__(PGeo<NQ>::THREADS, NQ == 2 ? 1 : 2) prefill_tc
 #pragma unroll
                 for (int c = 0; c < 32; c++) tmax = fmaxf(tmax, __uint_as_float(sr[c]));
             }
+            float* xq = xchg + (2 * qt + (j & 1)) * XCHG_FLOATS;
+            int* flags = (int*)(xq + 2 * PM);
+            bool two = true;
+            // see P_SKIP_FRACTION; page 0 always keeps its remainder (l_run is 0).  The MMA warp issues the remainder
+            // product if any warp asks for it, so a warp that does not need it writes zeros there
+            if (adaptive) {
+                const bool mine = j == 0 || fast_exp2(fmaf(tmax, sl2, -m_ref)) * 5.657f > p.skip_fraction * l_run;
+                two = __any_sync(0xffffffffu, mine);
+                if (lane == 0) flags[w8] = two ? 1 : 0;
+            }
             xq[half * PM + row] = tmax;
             pair_barrier(pair_id);  // maxima exchanged; both halves of S(j) are in registers, so P may overwrite them
             tmax = fmaxf(tmax, xq[(half ^ 1) * PM + row]) * sl2;
@@ -384,7 +406,10 @@ __global__ void __launch_bounds__(PGeo<NQ>::THREADS, NQ == 2 ? 1 : 2) prefill_tc
                 l_run *= alpha;
             }
             if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-                wait_or_fail(&bar_o[qt], (uint32_t)((j - 1) & 1), fail_s);  // O holds every page before this one
+                // O must hold every page before this one.  A parity wait only tells two consecutive phases apart, so
+                // step through them: S(j) being there says no more than that P.V(j - 2) was issued before it
+                if (j > 1) wait_or_fail(&bar_o[qt], (uint32_t)((j - 2) & 1), fail_s);
+                wait_or_fail(&bar_o[qt], (uint32_t)((j - 1) & 1), fail_s);
                 tc_fence_after();
 #pragma unroll
                 for (int cc = 0; cc < 4; cc++) {  // this thread's 64 of the row's 128 output channels
@@ -410,7 +435,7 @@ __global__ void __launch_bounds__(PGeo<NQ>::THREADS, NQ == 2 ? 1 : 2) prefill_tc
                     pr[c] = *(uint32_t*)&h, pr2[c] = *(uint32_t*)&l;
                 }
                 tmem_st16(sbuf + 32 + 16 * half, pr2);
-            } else {
+            } else if (two) {
                 uint32_t pr2[16];
 #pragma unroll
                 for (int c = 0; c < 16; c++) {
@@ -418,13 +443,27 @@ __global__ void __launch_bounds__(PGeo<NQ>::THREADS, NQ == 2 ? 1 : 2) prefill_tc
                     const float p1 = fast_exp2(fmaf(__uint_as_float(sr[2 * c + 1]), sl2, -m_ref));
                     lsum += p0 + p1;
                     __half2 h = __floats2half2_rn(p0, p1);
-                    pr[c] = *(uint32_t*)&h;
-                    if (P_F16_REMAINDER) {
-                        __half2 l = __floats2half2_rn(p0 - __low2float(h), p1 - __high2float(h));
-                        pr2[c] = *(uint32_t*)&l;
-                    }
+                    __half2 l = __floats2half2_rn(p0 - __low2float(h), p1 - __high2float(h));
+                    pr[c] = *(uint32_t*)&h, pr2[c] = *(uint32_t*)&l;
                 }
-                if (P_F16_REMAINDER) tmem_st16(sbuf + 32 + 16 * half, pr2);
+                tmem_st16(sbuf + 32 + 16 * half, pr2);
+            } else {
+                float lsum2 = 0.f;
+#pragma unroll
+                for (int c = 0; c < 16; c += 2) {
+                    const float p0 = fast_exp2(fmaf(__uint_as_float(sr[2 * c]), sl2, -m_ref));
+                    const float p1 = fast_exp2(fmaf(__uint_as_float(sr[2 * c + 1]), sl2, -m_ref));
+                    const float p2 = fast_exp2(fmaf(__uint_as_float(sr[2 * c + 2]), sl2, -m_ref));
+                    const float p3 = fast_exp2(fmaf(__uint_as_float(sr[2 * c + 3]), sl2, -m_ref));
+                    lsum += p0 + p1, lsum2 += p2 + p3;
+                    __half2 h = __floats2half2_rn(p0, p1), h2 = __floats2half2_rn(p2, p3);
+                    pr[c] = *(uint32_t*)&h, pr[c + 1] = *(uint32_t*)&h2;
+                }
+                lsum += lsum2;
+                uint32_t zero[16];
+#pragma unroll
+                for (int c = 0; c < 16; c++) zero[c] = 0u;
+                tmem_st16(sbuf + 32 + 16 * half, zero);
             }
             l_run += lsum;
             tmem_st16(sbuf + 16 * half, pr);
@@ -434,8 +473,10 @@ __global__ void __launch_bounds__(PGeo<NQ>::THREADS, NQ == 2 ? 1 : 2) prefill_tc
             if (lane == 0) mbar_arrive(&bar_p[2 * qt + (j & 1)]);
         }
         // ---- epilogue: wait for the last P.V, normalise, store ----
+        if (n_tiles > 1) wait_or_fail(&bar_o[qt], (uint32_t)((n_tiles - 2) & 1), fail_s);  // see the rescale above
         wait_or_fail(&bar_o[qt], (uint32_t)((n_tiles - 1) & 1), fail_s);
         tc_fence_after();
+        float* xq = xchg + (2 * qt + (n_tiles & 1)) * XCHG_FLOATS;  // the buffer page n_tiles - 2 used: everyone is past it
         xq[half * PM + row] = l_run;
         pair_barrier(pair_id);
         if (!*fail_s) {
@@ -523,6 +564,8 @@ int launch_prefill_tc(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int3
     // V chunk = 2 planes of 64 channels (8192 bytes apart), 8-token groups 1024 bytes apart
     p.v_lbo = 8192, p.v_sbo = 1024;
     p.scale = scale;
+    p.skip_fraction = P_SKIP_FRACTION;
+    if (const char* e = getenv("B200KV_PREFILL_SKIP")) p.skip_fraction = (float)atof(e);
     // double tiles (one CTA per SM, K/V staged once for 2 x 128 rows) when they still fill the GPU
     const int qpt = PM / G;
     const int64_t double_ctas = (int64_t)((n_new + 2 * qpt - 1) / (2 * qpt)) * c->L.Hkv * n_seqs;
