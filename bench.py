@@ -299,7 +299,7 @@ def run_ours(args, rank, world):
                     "tokens_per_s": all_seqs / (ms_e2e / args.steps * 1e-3)},
             "gpu_launches": len(recs),
             "kernels_ms": {k: statistics.mean(v) for k, v in per_kernel.items()},
-            "roofline": {"bound": "hbm", "kernel": "decode_mma_kernel" if (fmt != "f32") else "decode_kernel", "achieved": achieved, "peak": pk["hbm_gbs"],
+            "roofline": {"bound": "hbm", "kernel": "kivi_decode_kernel" if fmt.startswith("kivi") else ("decode_kernel" if fmt == "f32" else "decode_mma_kernel"), "achieved": achieved, "peak": pk["hbm_gbs"],
                          "unit": "GB/s", "frac": achieved / pk["hbm_gbs"], "peak_kind": pk_kind,
                          "algorithmic_bytes": total_bytes,
                          "traffic": int(total_bytes * NCU_TRAFFIC_RATIO[fmt]) if fmt in NCU_TRAFFIC_RATIO else None,
