@@ -193,7 +193,9 @@ int b200kv_attend_static_scratch(b200kv_cache* cache, int32_t n_seqs, const int3
  * max_records (kernel id, milliseconds) pairs in launch order and clears the log.  Kernel ids:
  * 0 page-table update, 1 append, 2 decode, 3 split combine, 4 export, 5 generic sdpa, 6 prefill.
  * `enable` is a bit set: bit 0 turns the timing on; bit 1 (a test hook) routes decode attention through the
- * CUDA-core kernel even where the tensor-core kernel applies, so the two can be checked against each other. */
+ * CUDA-core kernel even where the tensor-core kernel applies (KIVI caches: through export + the generic kernel), so
+ * the two can be checked against each other; bit 2 (a test hook) keeps KIVI decode attention on its CUDA-core
+ * kernel alone. */
 int b200kv_profile(b200kv_cache* cache, int32_t enable);
 int b200kv_profile_read(b200kv_cache* cache, int32_t max_records, int32_t* kernel_ids, float* ms, int32_t* n_out);
 

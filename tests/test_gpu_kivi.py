@@ -4,7 +4,7 @@ import numpy as np
 import pytest
 
 import oracle
-from util import TOL, normal, normal_with_outliers, rel_err
+from util import TOL, normal, normal_with_outliers, rel_err, rel_err_bf16
 
 pytestmark = pytest.mark.gpu
 
@@ -139,6 +139,10 @@ def test_kivi_decode_kernel_ragged_batch(kv, fmt, bits, D, Hq, Hkv):
     cache.profile(False)
     cache.check()
     assert rel_err(out.float().cpu().numpy(), out_gen.float().cpu().numpy()) <= 1e-3
+    cache.profile(False, kivi_cuda_core=True)  # and through the CUDA-core decode kernel alone
+    out_cc = cache.attend(seqs, torch.from_numpy(q).cuda(), causal=True)
+    cache.profile(False)
+    assert rel_err(out_cc.float().cpu().numpy(), out_gen.float().cpu().numpy()) <= 1e-3
     for b in range(len(lens)):
         kd = np.stack([_deq(True, D, bits, Ks[b][0, h]) for h in range(Hkv)])[None]
         vd = np.stack([_deq(False, D, bits, Vs[b][0, h]) for h in range(Hkv)])[None]
@@ -151,3 +155,33 @@ def _deq(per_channel, D, bits, rows):
     st = oracle.KiviStore(per_channel, D, bits)
     st.push(rows)
     return st.dequant()
+
+
+@pytest.mark.parametrize("io", ["f16", "bf16"])
+def test_kivi_tensor_core_decode_step_by_step(kv, io):
+    # decode steps across the points where a key block is finalised (length 4 + 32k) and a page fills; the tensor-core
+    # kernel takes the finalised blocks, the CUDA-core kernel the sinks and the residual block
+    Hq, Hkv, D, bits = 8, 2, 128, 8
+    cache = kv.KvCache("kivi8", Hkv, D, max_seqs=1, max_seq_tokens=512)
+    sq = cache.new_seq()
+    kstore = [oracle.KiviStore(True, D, bits) for _ in range(Hkv)]
+    vstore = [oracle.KiviStore(False, D, bits) for _ in range(Hkv)]
+    tdt = torch.float16 if io == "f16" else torch.bfloat16
+    for step, s in enumerate([30] + [1] * 12 + [55] + [1] * 12 + [60] + [1] * 6):
+        k = normal_with_outliers(1200 + step, (1, Hkv, s, D)).astype(np.float32)
+        v = normal_with_outliers(1300 + step, (1, Hkv, s, D)).astype(np.float32)
+        kt, vt = torch.from_numpy(k).to(tdt), torch.from_numpy(v).to(tdt)
+        cache.append([sq], kt.cuda(), vt.cuda())
+        kf, vf = kt.float().numpy(), vt.float().numpy()
+        for h in range(Hkv):
+            kstore[h].push(kf[0, h]), vstore[h].push(vf[0, h])
+        qt = torch.from_numpy(normal(1400 + step, (1, Hq, 1, D)).astype(np.float32)).to(tdt)
+        out = cache.attend([sq], qt.cuda(), causal=True)
+        kd = np.stack([st.dequant() for st in kstore])[None]
+        vd = np.stack([st.dequant() for st in vstore])[None]
+        want = oracle.flash_sdpa(qt.float().numpy(), kd, vd, causal=True).astype(np.float32)
+        got = out.float().cpu().numpy()
+        err = rel_err(got, want) if io == "f16" else rel_err_bf16(got, want)
+        assert err <= TOL[io], (step, err)
+    cache.check()
+    cache.close()

@@ -252,8 +252,8 @@ class KvCache:
     def check(self):
         _ck(lib().b200kv_check(self._h, _stream()))
 
-    def profile(self, enable=True, force_simt=False):
-        _ck(lib().b200kv_profile(self._h, int(bool(enable)) | (2 if force_simt else 0)))
+    def profile(self, enable=True, force_simt=False, kivi_cuda_core=False):
+        _ck(lib().b200kv_profile(self._h, int(bool(enable)) | (2 if force_simt else 0) | (4 if kivi_cuda_core else 0)))
 
     def profile_read(self, max_records=65536):
         """[(kernel name, milliseconds)] of the launches recorded since the last read."""

@@ -778,6 +778,7 @@ int b200kv_profile(b200kv_cache* c, int32_t enable) {
     if (!c) return fail("null cache");
     c->prof_on = (enable & 1) != 0;
     c->force_simt = (enable & 2) != 0;
+    c->kivi_cuda_core = (enable & 4) != 0;
     return B200KV_OK;
 }
 

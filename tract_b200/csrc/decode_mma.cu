@@ -23,6 +23,7 @@
 #include <vector>
 
 #include "decode_common.h"
+#include "mma_common.cuh"
 
 namespace b200kv {
 
@@ -40,59 +41,6 @@ struct MGeo {
     // measured: Q8_1 is best with 3 CTAs x 4 stages, Q4_0 with 4 CTAs x 5 stages, the 16-bit formats are HBM bound at 2
     static constexpr int MIN_CTAS = FMT == B200KV_FMT_Q4_0 ? 4 : (QUANT ? 3 : 2);  // resident CTAs per SM the register budget is set for
 };
-
-__device__ inline void mma_f16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-__device__ inline void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-__device__ inline void ldmatrix_x4(uint32_t (&r)[4], const void* smem_ptr) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-                 : "r"(smem_u32(smem_ptr)));
-}
-__device__ inline void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem_ptr) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-                 : "r"(smem_u32(smem_ptr)));
-}
-// Transposes an 8x8 matrix of 16-bit elements held one row per 4 lanes (the C-fragment arrangement)
-// into the B-fragment arrangement.
-__device__ inline uint32_t movmatrix_trans(uint32_t x) {
-    uint32_t y;
-    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
-    return y;
-}
-__device__ inline uint32_t pack_f16(float lo, float hi) {
-    __half2 h = __floats2half2_rn(lo, hi);
-    return *(uint32_t*)&h;
-}
-__device__ inline uint32_t pack_bf16(float lo, float hi) {
-    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
-    return *(uint32_t*)&h;
-}
-__device__ inline float fast_ex2(float x) {  // 2^x, one MUFU instruction; 2^-inf = 0
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
-__device__ inline float quad_row_max(float v) {  // over the 8 rows of a fragment (lanes differing in bits 2..4)
-    v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 4));
-    v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 8));
-    return fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 16));
-}
-__device__ inline float quad_row_sum(float v) {
-    v += __shfl_xor_sync(0xffffffffu, v, 4);
-    v += __shfl_xor_sync(0xffffffffu, v, 8);
-    return v + __shfl_xor_sync(0xffffffffu, v, 16);
-}
 
 // Shared memory after the stage ring: q as f32 [8][128], then the barriers.
 constexpr size_t MMA_TAIL = 8 * MD * 4 + 32 * 4 + 64;

@@ -79,6 +79,7 @@ struct b200kv_cache {
     size_t ws_bytes = 0;
     // optional per-launch timing (the analogue of tract-cuda's event pairs around every launch,
     // cuda/src/context.rs:364-453): off by default
+    bool kivi_cuda_core = false;  // test hook: KIVI decode through the CUDA-core kernel alone
     bool force_simt = false;  // test hook: route decode through the CUDA-core kernel even where the tensor-core one applies
     bool prof_on = false;
     struct ProfRec {

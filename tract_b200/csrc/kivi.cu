@@ -13,22 +13,9 @@
 #include <algorithm>
 #include <cstring>
 
-#include "internal.h"
+#include "kivi_common.cuh"
 
 namespace b200kv {
-
-constexpr int SINK = 4;     // SINK_TOKENS
-constexpr int KBLOCK = 32;  // KEY_BLOCK
-
-struct KiviView {  // device pointers + geometry, passed by value to the kernels
-    uint8_t* codes[2];   // [n_pages][H][64][row_bytes] per stream
-    float* params[2];    // per-token stream: [n_pages][H][64][2] ; per-channel stream: [n_pages][H][2 blocks][2][D]
-    float* sinks;        // [max_seqs][H][2 streams][SINK][D]
-    float* residual;     // [max_seqs][H][2 streams][KBLOCK][D]  (used by per-channel streams)
-    const int32_t* table;
-    int32_t max_pages_per_seq, n_pages, H, D, bits, row_bytes, n_streams;
-    int32_t per_channel[2];
-};
 
 __device__ inline float kivi_lv(int bits) { return bits == 8 ? 255.f : 15.f; }
 __device__ inline float kivi_scale(float lo, float hi, float lv) { return hi > lo ? __fdiv_rn(__fsub_rn(hi, lo), lv) : 1.0f; }
@@ -41,6 +28,10 @@ __device__ inline uint32_t kivi_code(float x, float lo, float scale, float lv) {
 __device__ inline float kivi_dequant(uint32_t code, float lo, float scale) { return __fadd_rn(lo, __fmul_rn((float)code, scale)); }
 
 __device__ inline void kivi_store_code(const KiviView& v, int stream, int32_t pg, int h, int slot, int c, uint32_t code) {
+    if (kivi_mma_layout(v.bits, v.D)) {
+        v.codes[stream][((int64_t)pg * v.H + h) * PAGE_TOKENS * v.row_bytes + kivi_code_offset(stream, slot, c)] = (uint8_t)code;
+        return;
+    }
     uint8_t* row = v.codes[stream] + (((int64_t)pg * v.H + h) * PAGE_TOKENS + slot) * v.row_bytes;
     if (v.bits == 8) {
         row[c] = (uint8_t)code;
@@ -50,6 +41,8 @@ __device__ inline void kivi_store_code(const KiviView& v, int stream, int32_t pg
     }
 }
 __device__ inline uint32_t kivi_load_code(const KiviView& v, int stream, int32_t pg, int h, int slot, int c) {
+    if (kivi_mma_layout(v.bits, v.D))
+        return v.codes[stream][((int64_t)pg * v.H + h) * PAGE_TOKENS * v.row_bytes + kivi_code_offset(stream, slot, c)];
     const uint8_t* row = v.codes[stream] + (((int64_t)pg * v.H + h) * PAGE_TOKENS + slot) * v.row_bytes;
     if (v.bits == 8) return row[c];
     const uint32_t b = row[c >> 1];
@@ -221,7 +214,9 @@ __global__ void kivi_raw_kernel(KiviRaw r) {
     const int64_t n_fin = n_after / KBLOCK;
     const int64_t n_q = v.per_channel[s] ? n_fin * KBLOCK : n_after;
     if (i < n_q) {
-        if (c < v.row_bytes)
+        if (kivi_mma_layout(v.bits, v.D))
+            r.codes[((int64_t)h * n_q + i) * v.row_bytes + c] = (uint8_t)kivi_load_code(v, s, pg, h, slot, c);
+        else if (c < v.row_bytes)
             r.codes[((int64_t)h * n_q + i) * v.row_bytes + c] =
                 v.codes[s][(((int64_t)pg * v.H + h) * PAGE_TOKENS + slot) * v.row_bytes + c];
         if (v.per_channel[s]) {
@@ -246,7 +241,7 @@ __global__ void kivi_raw_kernel(KiviRaw r) {
 
 bool fmt_is_kivi(int fmt) { return fmt == B200KV_FMT_KIVI8 || fmt == B200KV_FMT_KIVI4; }
 
-static KiviView kivi_view(const b200kv_cache* c) {
+KiviView kivi_view(const b200kv_cache* c) {
     KiviView v{};
     const KiviStore& k = c->kivi;
     for (int s = 0; s < 2; s++) v.codes[s] = k.codes[s], v.params[s] = k.params[s], v.per_channel[s] = k.per_channel[s];
@@ -397,6 +392,8 @@ struct KiviDecode {
     float* part_o;
     float* part_ml;
     int32_t G, dtype, n_splits;
+    int32_t f32_only;               // 1: only the tiles the tensor-core kernel leaves out (sinks, residual block)
+    int32_t part_stride, part_off;  // partial of (batch b, split s) = b * part_stride + part_off + s
     float scale;
 };
 
@@ -430,7 +427,12 @@ __global__ void __launch_bounds__(128) kivi_decode_kernel(KiviDecode p, const __
     const int tiles = (n_after + KTILE - 1) / KTILE;
     // split s takes tiles [lo, hi) of -1 .. tiles-1
     const int tile_lo = (int)((int64_t)(tiles + 1) * split / p.n_splits) - 1, tile_hi = (int)((int64_t)(tiles + 1) * (split + 1) / p.n_splits) - 1;
+    // the tile after t: every tile, or (f32_only) the sinks and then the residual block, if there is one
+    auto next_tile = [&](int t) { return p.f32_only ? (t < 0 ? n_fin : tiles) : t + 1; };
+    const int first_staged = tile_lo >= 0 ? tile_lo : next_tile(tile_lo);  // tile -1 needs no staging
     const int row_bytes = v.row_bytes, chunks = row_bytes / 16;
+    const bool mma_layout = kivi_mma_layout(v.bits, v.D);
+    const int v_pos = mma_layout ? code_pos(B200KV_FMT_Q8_1, 128, 1, tid & 127) : tid;  // where channel `tid` sits in a staged V row
     const float* sink_k = v.sinks + (((int64_t)seq * v.H + kvh) * 2 + 0) * SINK * D;
     const float* sink_v = v.sinks + (((int64_t)seq * v.H + kvh) * 2 + 1) * SINK * D;
     const float* resid = v.residual + (((int64_t)seq * v.H + kvh) * 2 + 0) * KBLOCK * D;
@@ -441,17 +443,26 @@ __global__ void __launch_bounds__(128) kivi_decode_kernel(KiviDecode p, const __
         const int slot0 = (k * KTILE) % PAGE_TOKENS;
         const int nrow = min(KTILE, n_after - k * KTILE);
         const uint8_t* vrow = v.codes[1] + (((int64_t)pg * v.H + kvh) * PAGE_TOKENS + slot0) * row_bytes;
-        for (int i = tid; i < nrow * chunks; i += 128) cp_async16(s.vc + (i / chunks) * RS + (i % chunks) * 16, vrow + (i / chunks) * row_bytes + (i % chunks) * 16);
+        // (rows in the tensor-core layout are un-swizzled on the way in: the staged rows are in byte-position order)
+        for (int i = tid; i < nrow * chunks; i += 128) {
+            const int rr = i / chunks, u = i % chunks;
+            const int ud = mma_layout ? u ^ (int)swz_mask(B200KV_FMT_Q8_1, 128, 1, slot0 + rr) : u;
+            cp_async16(s.vc + rr * RS + ud * 16, vrow + rr * row_bytes + u * 16);
+        }
         const float* vp = v.params[1] + (((int64_t)pg * v.H + kvh) * PAGE_TOKENS + slot0) * 2;
         if (tid < KTILE / 2) cp_async16(s.vpar + tid * 4, vp + tid * 4);  // whole 256-byte run; rows past nrow are ignored
         if (k < n_fin) {
             const uint8_t* krow = v.codes[0] + (((int64_t)pg * v.H + kvh) * PAGE_TOKENS + slot0) * row_bytes;
-            for (int i = tid; i < KTILE * chunks; i += 128) cp_async16(s.kc + (i / chunks) * RS + (i % chunks) * 16, krow + (i / chunks) * row_bytes + (i % chunks) * 16);
+            for (int i = tid; i < KTILE * chunks; i += 128) {
+                const int rr = i / chunks, u = i % chunks;
+                const int ud = mma_layout ? u ^ (int)swz_mask(B200KV_FMT_Q8_1, 128, 0, slot0 + rr) : u;
+                cp_async16(s.kc + rr * RS + ud * 16, krow + rr * row_bytes + u * 16);
+            }
             const float* kp = v.params[0] + (((int64_t)pg * v.H + kvh) * 2 + slot0 / KBLOCK) * 2 * D;
             for (int i = tid; i < 2 * D / 4; i += 128) cp_async16(s.kpar + i * 4, kp + i * 4);
         }
     };
-    if (max(tile_lo, 0) < tile_hi) prefetch(max(tile_lo, 0));
+    if (first_staged < tile_hi) prefetch(first_staged);
     cp_async_commit();
 
     for (int idx = tid; idx < KGT * D; idx += 128) {
@@ -462,9 +473,10 @@ __global__ void __launch_bounds__(128) kivi_decode_kernel(KiviDecode p, const __
     float acc[KGT] = {0.f, 0.f, 0.f, 0.f};  // thread = output channel
     const bool eight = v.bits == 8;
 
-    for (int tile = tile_lo; tile < tile_hi; tile++) {
+    for (int tile = tile_lo; tile < tile_hi; tile = next_tile(tile)) {
         // the next tile's bytes start moving before this one is touched
-        if (tile + 1 < tile_hi && tile + 1 >= 0 && tile + 1 != max(tile_lo, 0)) prefetch(tile + 1);
+        const int nt = next_tile(tile);
+        if (nt < tile_hi && nt != first_staged) prefetch(nt);
         cp_async_commit();
         if (tile >= 0) cp_async_wait<1>();  // everything but the group just committed has landed
         __syncthreads();
@@ -535,7 +547,7 @@ __global__ void __launch_bounds__(128) kivi_decode_kernel(KiviDecode p, const __
                 if (tile < 0) {
                     vx = sink_v[tt * D + tid];
                 } else {
-                    const uint32_t byte = s.vc[tt * RS + (eight ? tid : tid >> 1)];
+                    const uint32_t byte = s.vc[tt * RS + (eight ? v_pos : tid >> 1)];
                     const uint32_t code = eight ? byte : ((tid & 1) ? byte >> 4 : byte & 0xfu);
                     vx = kivi_dequant(code, s.vpar[2 * tt], s.vpar[2 * tt + 1]);
                 }
@@ -548,11 +560,16 @@ __global__ void __launch_bounds__(128) kivi_decode_kernel(KiviDecode p, const __
     cp_async_wait<0>();
     if (warp < KGT && lane == 0) ml_s[warp * 2] = m_run, ml_s[warp * 2 + 1] = l_run;
     __syncthreads();
-    const int64_t pbase = ((int64_t)blockIdx.x * v.H + kvh) * p.G + g0;
+    const int64_t pbase = (((int64_t)b * p.part_stride + p.part_off + split) * v.H + kvh) * p.G + g0;
     if (tid < D)
         for (int g = 0; g < ng; g++) p.part_o[(pbase + g) * D + tid] = acc[g];
     if (tid < ng) p.part_ml[(pbase + tid) * 2] = ml_s[tid * 2], p.part_ml[(pbase + tid) * 2 + 1] = ml_s[tid * 2 + 1];
 }
+
+// kivi_mma.cu
+bool kivi_mma_supported(const b200kv_cache* c, int dtype);
+int launch_kivi_mma(b200kv_cache* c, const void* q, const int64_t* qs, int n_seqs, int G, int dtype, float scale, int n_splits,
+                    float* part_o, float* part_ml, const InlineBatch& ib, cudaStream_t stream);
 
 int kivi_decode(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t n_q_heads, const void* q, const int64_t* qs, void* out,
                 const int64_t* os, int32_t dtype, float scale, cudaStream_t stream) {
@@ -560,27 +577,52 @@ int kivi_decode(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t n_
     if (n_seqs > INLINE_BATCH) return fail("a KIVI decode call takes at most %d sequences", INLINE_BATCH);
     int64_t max_len = 0;
     for (int i = 0; i < n_seqs; i++) max_len = std::max<int64_t>(max_len, c->seqs[seqs[i]].len);
-    // enough splits to cover the GPU a few times, at least 8 tiles (256 tokens) each
-    const int64_t tiles = (std::max<int64_t>(max_len - SINK, 0) + KTILE - 1) / KTILE + 1;
-    const int nz = (G + KGT - 1) / KGT;
-    int ns = (int)std::min<int64_t>(64, std::max<int64_t>(1, (148 * 10 + (int64_t)n_seqs * H * nz - 1) / ((int64_t)n_seqs * H * nz)));
-    ns = (int)std::max<int64_t>(1, std::min<int64_t>(ns, tiles / 8));
+    const bool mma = !c->kivi_cuda_core && kivi_mma_supported(c, dtype);
+    int ns, n_part_per_seq;
+    if (mma) {
+        // tensor-core kernel over the finalised blocks in `ns` splits (a few CTAs per SM, at least 4 pages each), plus one
+        // partial from the CUDA-core kernel for the sinks and the residual block
+        const int64_t pages = (std::max<int64_t>(max_len - SINK, 0) / KBLOCK + 1) / 2;
+        const int nz = (G + 7) / 8;
+        // 3 CTAs fit an SM: pick the split count that fills whole waves of 148 x 3 CTAs best (the splits of a batch of
+        // equally long sequences cost the same), with at least 4 pages per split and at most 4 waves
+        const int64_t units = (int64_t)n_seqs * H * nz, slots = 148 * 3;
+        const int ns_max = (int)std::max<int64_t>(1, std::min<int64_t>(64, pages / 4));
+        double best = -1.0;
+        ns = 1;
+        for (int cand = 1; cand <= ns_max; cand++) {
+            const int64_t ctas = units * cand, waves = (ctas + slots - 1) / slots;
+            if (waves > 4 && cand > 1) break;
+            const double eff = (double)ctas / (double)(waves * slots);
+            if (eff > best + 0.02) best = eff, ns = cand;
+        }
+        n_part_per_seq = ns + 1;
+    } else {
+        // enough splits to cover the GPU a few times, at least 8 tiles (256 tokens) each
+        const int64_t tiles = (std::max<int64_t>(max_len - SINK, 0) + KTILE - 1) / KTILE + 1;
+        const int nz = (G + KGT - 1) / KGT;
+        ns = (int)std::min<int64_t>(64, std::max<int64_t>(1, (148 * 10 + (int64_t)n_seqs * H * nz - 1) / ((int64_t)n_seqs * H * nz)));
+        ns = (int)std::max<int64_t>(1, std::min<int64_t>(ns, tiles / 8));
+        n_part_per_seq = ns;
+    }
     InlineBatch ib{};
     ib.n = n_seqs;
-    for (int i = 0; i < n_seqs; i++) ib.ent[i] = make_int4(seqs[i], (int)c->seqs[seqs[i]].len, i * ns, ns);
-    const size_t n_part = (size_t)n_seqs * ns * H * G;
+    for (int i = 0; i < n_seqs; i++) ib.ent[i] = make_int4(seqs[i], (int)c->seqs[seqs[i]].len, i * n_part_per_seq, n_part_per_seq);
+    const size_t n_part = (size_t)n_seqs * n_part_per_seq * H * G;
     if (ensure_workspace(c, n_part * (D + 2) * sizeof(float)) != B200KV_OK) return B200KV_KO;
     KiviDecode p{};
     p.v = kivi_view(c);
     p.q = q, p.qb = qs[0], p.qh = qs[1];
     p.part_o = (float*)c->ws, p.part_ml = p.part_o + n_part * D;
-    p.G = G, p.dtype = dtype, p.n_splits = ns, p.scale = scale;
+    p.G = G, p.dtype = dtype, p.scale = scale;
+    p.n_splits = mma ? 1 : ns, p.f32_only = mma ? 1 : 0, p.part_stride = n_part_per_seq, p.part_off = 0;
     {
         ProfScope ps(c, K_DECODE, stream);
-        dim3 grid(n_seqs * ns, H, nz);
+        dim3 grid(n_seqs * p.n_splits, H, (G + KGT - 1) / KGT);
         if (D == 128) kivi_decode_kernel<128><<<grid, 128, 0, stream>>>(p, ib);
         else kivi_decode_kernel<64><<<grid, 128, 0, stream>>>(p, ib);
         B200KV_CUDA(cudaGetLastError());
+        if (mma && launch_kivi_mma(c, q, qs, n_seqs, G, dtype, scale, ns, p.part_o, p.part_ml, ib, stream) != B200KV_OK) return B200KV_KO;
     }
     DecodeParams dp{};
     dp.part_o = p.part_o, dp.part_ml = p.part_ml, dp.Hkv = H, dp.G = G, dp.dtype = dtype;
