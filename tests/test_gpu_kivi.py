@@ -121,7 +121,7 @@ def test_kivi_attention_matches_oracle(kv, fmt, bits, io):
     cache.close()
 
 
-@pytest.mark.parametrize("fmt,bits,D,Hq,Hkv", [("kivi8", 8, 128, 32, 8), ("kivi4", 4, 64, 6, 2)])
+@pytest.mark.parametrize("fmt,bits,D,Hq,Hkv", [("kivi8", 8, 128, 32, 8), ("kivi4", 4, 64, 6, 2), ("kivi4", 4, 128, 32, 8)])
 def test_kivi_decode_kernel_ragged_batch(kv, fmt, bits, D, Hq, Hkv):
     # batched decode over sequences that are sinks only, shorter than one key block, and long
     lens = [700, 37, 5, 3, 1300]
@@ -157,12 +157,12 @@ def _deq(per_channel, D, bits, rows):
     return st.dequant()
 
 
-@pytest.mark.parametrize("io", ["f16", "bf16"])
-def test_kivi_tensor_core_decode_step_by_step(kv, io):
+@pytest.mark.parametrize("fmt,bits,io", [("kivi8", 8, "f16"), ("kivi8", 8, "bf16"), ("kivi4", 4, "f16"), ("kivi4", 4, "bf16")])
+def test_kivi_tensor_core_decode_step_by_step(kv, fmt, bits, io):
     # decode steps across the points where a key block is finalised (length 4 + 32k) and a page fills; the tensor-core
     # kernel takes the finalised blocks, the CUDA-core kernel the sinks and the residual block
-    Hq, Hkv, D, bits = 8, 2, 128, 8
-    cache = kv.KvCache("kivi8", Hkv, D, max_seqs=1, max_seq_tokens=512)
+    Hq, Hkv, D = 8, 2, 128
+    cache = kv.KvCache(fmt, Hkv, D, max_seqs=1, max_seq_tokens=512)
     sq = cache.new_seq()
     kstore = [oracle.KiviStore(True, D, bits) for _ in range(Hkv)]
     vstore = [oracle.KiviStore(False, D, bits) for _ in range(Hkv)]

@@ -29,7 +29,13 @@ __device__ inline float kivi_dequant(uint32_t code, float lo, float scale) { ret
 
 __device__ inline void kivi_store_code(const KiviView& v, int stream, int32_t pg, int h, int slot, int c, uint32_t code) {
     if (kivi_mma_layout(v.bits, v.D)) {
-        v.codes[stream][((int64_t)pg * v.H + h) * PAGE_TOKENS * v.row_bytes + kivi_code_offset(stream, slot, c)] = (uint8_t)code;
+        uint8_t* at = v.codes[stream] + ((int64_t)pg * v.H + h) * PAGE_TOKENS * v.row_bytes + kivi_code_offset(v.bits, stream, slot, c);
+        if (v.bits == 8) {
+            *at = (uint8_t)code;
+        } else {  // the channel that shares the byte is 16 (K rows) or 8 (permuted V rows) away: the low-nibble lane writes
+            const uint32_t other = __shfl_xor_sync(0xffffffffu, code, stream == 0 ? 16 : 8);
+            if (code_nibble(B200KV_FMT_Q4_0, 128, stream, c) == 0) *at = (uint8_t)((code & 0xf) | ((other & 0xf) << 4));
+        }
         return;
     }
     uint8_t* row = v.codes[stream] + (((int64_t)pg * v.H + h) * PAGE_TOKENS + slot) * v.row_bytes;
@@ -41,8 +47,11 @@ __device__ inline void kivi_store_code(const KiviView& v, int stream, int32_t pg
     }
 }
 __device__ inline uint32_t kivi_load_code(const KiviView& v, int stream, int32_t pg, int h, int slot, int c) {
-    if (kivi_mma_layout(v.bits, v.D))
-        return v.codes[stream][((int64_t)pg * v.H + h) * PAGE_TOKENS * v.row_bytes + kivi_code_offset(stream, slot, c)];
+    if (kivi_mma_layout(v.bits, v.D)) {
+        const uint32_t b = v.codes[stream][((int64_t)pg * v.H + h) * PAGE_TOKENS * v.row_bytes + kivi_code_offset(v.bits, stream, slot, c)];
+        if (v.bits == 8) return b;
+        return code_nibble(B200KV_FMT_Q4_0, 128, stream, c) ? (b >> 4) : (b & 0xf);
+    }
     const uint8_t* row = v.codes[stream] + (((int64_t)pg * v.H + h) * PAGE_TOKENS + slot) * v.row_bytes;
     if (v.bits == 8) return row[c];
     const uint32_t b = row[c >> 1];
@@ -214,8 +223,12 @@ __global__ void kivi_raw_kernel(KiviRaw r) {
     const int64_t n_fin = n_after / KBLOCK;
     const int64_t n_q = v.per_channel[s] ? n_fin * KBLOCK : n_after;
     if (i < n_q) {
-        if (kivi_mma_layout(v.bits, v.D))
-            r.codes[((int64_t)h * n_q + i) * v.row_bytes + c] = (uint8_t)kivi_load_code(v, s, pg, h, slot, c);
+        if (kivi_mma_layout(v.bits, v.D)) {
+            if (v.bits == 8) r.codes[((int64_t)h * n_q + i) * v.row_bytes + c] = (uint8_t)kivi_load_code(v, s, pg, h, slot, c);
+            else if (c < v.row_bytes)  // the reference's packing: even channel in the low nibble
+                r.codes[((int64_t)h * n_q + i) * v.row_bytes + c] =
+                    (uint8_t)(kivi_load_code(v, s, pg, h, slot, 2 * c) | (kivi_load_code(v, s, pg, h, slot, 2 * c + 1) << 4));
+        }
         else if (c < v.row_bytes)
             r.codes[((int64_t)h * n_q + i) * v.row_bytes + c] =
                 v.codes[s][(((int64_t)pg * v.H + h) * PAGE_TOKENS + slot) * v.row_bytes + c];
@@ -432,7 +445,10 @@ __global__ void __launch_bounds__(128) kivi_decode_kernel(KiviDecode p, const __
     const int first_staged = tile_lo >= 0 ? tile_lo : next_tile(tile_lo);  // tile -1 needs no staging
     const int row_bytes = v.row_bytes, chunks = row_bytes / 16;
     const bool mma_layout = kivi_mma_layout(v.bits, v.D);
-    const int v_pos = mma_layout ? code_pos(B200KV_FMT_Q8_1, 128, 1, tid & 127) : tid;  // where channel `tid` sits in a staged V row
+    const int lfmt = kivi_layout_fmt(v.bits);
+    // where channel `tid` sits in a staged V row: byte and, for int4, nibble
+    const int v_pos = mma_layout ? code_pos(lfmt, 128, 1, tid & 127) : (v.bits == 8 ? tid : tid >> 1);
+    const int v_nib = mma_layout ? code_nibble(lfmt, 128, 1, tid & 127) : (tid & 1);
     const float* sink_k = v.sinks + (((int64_t)seq * v.H + kvh) * 2 + 0) * SINK * D;
     const float* sink_v = v.sinks + (((int64_t)seq * v.H + kvh) * 2 + 1) * SINK * D;
     const float* resid = v.residual + (((int64_t)seq * v.H + kvh) * 2 + 0) * KBLOCK * D;
@@ -444,19 +460,21 @@ __global__ void __launch_bounds__(128) kivi_decode_kernel(KiviDecode p, const __
         const int nrow = min(KTILE, n_after - k * KTILE);
         const uint8_t* vrow = v.codes[1] + (((int64_t)pg * v.H + kvh) * PAGE_TOKENS + slot0) * row_bytes;
         // (rows in the tensor-core layout are un-swizzled on the way in: the staged rows are in byte-position order)
+        const uint8_t* vpage = v.codes[1] + ((int64_t)pg * v.H + kvh) * PAGE_TOKENS * row_bytes;
         for (int i = tid; i < nrow * chunks; i += 128) {
             const int rr = i / chunks, u = i % chunks;
-            const int ud = mma_layout ? u ^ (int)swz_mask(B200KV_FMT_Q8_1, 128, 1, slot0 + rr) : u;
-            cp_async16(s.vc + rr * RS + ud * 16, vrow + rr * row_bytes + u * 16);
+            const uint8_t* src = mma_layout ? vpage + chunk_addr(lfmt, 128, 1, slot0 + rr, 16 * u) : vrow + rr * row_bytes + u * 16;
+            cp_async16(s.vc + rr * RS + u * 16, src);
         }
         const float* vp = v.params[1] + (((int64_t)pg * v.H + kvh) * PAGE_TOKENS + slot0) * 2;
         if (tid < KTILE / 2) cp_async16(s.vpar + tid * 4, vp + tid * 4);  // whole 256-byte run; rows past nrow are ignored
         if (k < n_fin) {
             const uint8_t* krow = v.codes[0] + (((int64_t)pg * v.H + kvh) * PAGE_TOKENS + slot0) * row_bytes;
+            const uint8_t* kpage = v.codes[0] + ((int64_t)pg * v.H + kvh) * PAGE_TOKENS * row_bytes;
             for (int i = tid; i < KTILE * chunks; i += 128) {
                 const int rr = i / chunks, u = i % chunks;
-                const int ud = mma_layout ? u ^ (int)swz_mask(B200KV_FMT_Q8_1, 128, 0, slot0 + rr) : u;
-                cp_async16(s.kc + rr * RS + ud * 16, krow + rr * row_bytes + u * 16);
+                const uint8_t* src = mma_layout ? kpage + chunk_addr(lfmt, 128, 0, slot0 + rr, 16 * u) : krow + rr * row_bytes + u * 16;
+                cp_async16(s.kc + rr * RS + u * 16, src);
             }
             const float* kp = v.params[0] + (((int64_t)pg * v.H + kvh) * 2 + slot0 / KBLOCK) * 2 * D;
             for (int i = tid; i < 2 * D / 4; i += 128) cp_async16(s.kpar + i * 4, kp + i * 4);
@@ -500,9 +518,16 @@ __global__ void __launch_bounds__(128) kivi_decode_kernel(KiviDecode p, const __
 #pragma unroll
                             for (int e = 0; e < 4; e++) codes[e] = (word >> (8 * e)) & 0xffu;
                         } else {
-                            const uint32_t half = *(const uint16_t*)(s.kc + tt * RS + 2 * w);
+                            if (mma_layout) {  // channels 4w .. 4w+3 share a nibble position in four consecutive bytes
+                                const uint32_t word = *(const uint32_t*)(s.kc + tt * RS + code_pos(B200KV_FMT_Q4_0, 128, 0, 4 * w));
+                                const int sh = 4 * code_nibble(B200KV_FMT_Q4_0, 128, 0, 4 * w);
 #pragma unroll
-                            for (int e = 0; e < 4; e++) codes[e] = (half >> (4 * e)) & 0xfu;
+                                for (int e = 0; e < 4; e++) codes[e] = (word >> (8 * e + sh)) & 0xfu;
+                            } else {
+                                const uint32_t half = *(const uint16_t*)(s.kc + tt * RS + 2 * w);
+#pragma unroll
+                                for (int e = 0; e < 4; e++) codes[e] = (half >> (4 * e)) & 0xfu;
+                            }
                         }
 #pragma unroll
                         for (int e = 0; e < 4; e++) kx[e] = kivi_dequant(codes[e], s.kpar[4 * w + e], s.kpar[D + 4 * w + e]);
@@ -547,8 +572,8 @@ __global__ void __launch_bounds__(128) kivi_decode_kernel(KiviDecode p, const __
                 if (tile < 0) {
                     vx = sink_v[tt * D + tid];
                 } else {
-                    const uint32_t byte = s.vc[tt * RS + (eight ? v_pos : tid >> 1)];
-                    const uint32_t code = eight ? byte : ((tid & 1) ? byte >> 4 : byte & 0xfu);
+                    const uint32_t byte = s.vc[tt * RS + v_pos];
+                    const uint32_t code = eight ? byte : (v_nib ? byte >> 4 : byte & 0xfu);
                     vx = kivi_dequant(code, s.vpar[2 * tt], s.vpar[2 * tt + 1]);
                 }
 #pragma unroll
@@ -568,6 +593,7 @@ __global__ void __launch_bounds__(128) kivi_decode_kernel(KiviDecode p, const __
 
 // kivi_mma.cu
 bool kivi_mma_supported(const b200kv_cache* c, int dtype);
+int kivi_mma_ctas_per_sm(int bits);
 int launch_kivi_mma(b200kv_cache* c, const void* q, const int64_t* qs, int n_seqs, int G, int dtype, float scale, int n_splits,
                     float* part_o, float* part_ml, const InlineBatch& ib, cudaStream_t stream);
 
@@ -584,9 +610,9 @@ int kivi_decode(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t n_
         // partial from the CUDA-core kernel for the sinks and the residual block
         const int64_t pages = (std::max<int64_t>(max_len - SINK, 0) / KBLOCK + 1) / 2;
         const int nz = (G + 7) / 8;
-        // 3 CTAs fit an SM: pick the split count that fills whole waves of 148 x 3 CTAs best (the splits of a batch of
+        // pick the split count that fills whole waves of 148 x (CTAs per SM) best (the splits of a batch of
         // equally long sequences cost the same), with at least 4 pages per split and at most 4 waves
-        const int64_t units = (int64_t)n_seqs * H * nz, slots = 148 * 3;
+        const int64_t units = (int64_t)n_seqs * H * nz, slots = 148 * kivi_mma_ctas_per_sm(c->kivi.bits);
         const int ns_max = (int)std::max<int64_t>(1, std::min<int64_t>(64, pages / 4));
         double best = -1.0;
         ns = 1;

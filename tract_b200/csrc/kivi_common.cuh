@@ -19,13 +19,16 @@ struct KiviView {  // device pointers + geometry, passed by value to the kernels
 };
 
 
-// int8 codes at head_dim 128 lie in the (page, head) region exactly like the data region of a Q8_1 chunk
-// (common.cuh: 16-byte units XOR-swizzled per 128-byte token line, V rows in the permuted channel order), so that the
-// tensor-core decode kernel builds its fragments from contiguous bytes without bank conflicts.  Everything else
-// keeps natural rows.
-__host__ __device__ inline bool kivi_mma_layout(int bits, int D) { return bits == 8 && D == 128; }
-__device__ inline uint32_t kivi_code_offset(int stream, int slot, int c) {
-    return chunk_addr(B200KV_FMT_Q8_1, 128, stream, slot, code_pos(B200KV_FMT_Q8_1, 128, stream, c));
+// At head_dim 128 the codes of a (page, head) lie exactly like the data region of a block-quantised chunk (common.cuh):
+// int8 like Q8_1, int4 like Q4_0 -- 16-byte units XOR-swizzled per 128-byte line, V rows in the permuted channel order,
+// int4 nibbles paired as that format pairs them -- so that the tensor-core decode kernel builds its fragments from
+// contiguous bytes without bank conflicts.  The order the reference packs (quant_dyn_kv_cache.rs:63-75) is restored by
+// the export kernels.  head_dim 64 keeps natural rows.
+__host__ __device__ inline bool kivi_mma_layout(int bits, int D) { return D == 128 && (bits == 8 || bits == 4); }
+__host__ __device__ constexpr int kivi_layout_fmt(int bits) { return bits == 8 ? B200KV_FMT_Q8_1 : B200KV_FMT_Q4_0; }
+__device__ inline uint32_t kivi_code_offset(int bits, int stream, int slot, int c) {
+    const int fmt = kivi_layout_fmt(bits);
+    return chunk_addr(fmt, 128, stream, slot, code_pos(fmt, 128, stream, c));
 }
 
 KiviView kivi_view(const b200kv_cache* c);

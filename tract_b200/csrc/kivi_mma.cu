@@ -1,4 +1,4 @@
-// Tensor-core decode attention over the finalised part of a KIVI int8 cache (head_dim 128, 16-bit queries).
+// Tensor-core decode attention over the finalised part of a KIVI int8 / int4 cache (head_dim 128, 16-bit queries).
 //
 // The stores are those of transformers/src/ops/quant_dyn_kv_cache.rs: Keys per channel and 32-token block
 // (K^[t][c] = lo_b[c] + scale_b[c] * u[t][c], :231-240), Values per token (V^[t][c] = lo_t + scale_t * u[t][c],
@@ -8,7 +8,8 @@
 //   K side: q . K^[t] = q . lo_b + sum_c (q[c] * scale_b[c]) * u[t][c].  Once per block the four warps rebuild the B
 //           operand q' = q * scale_b as an f16 value plus its f16 remainder (two MMAs per k-step, exact to 2^-22) and
 //           the scalar q . lo_b in f32; a code byte placed in the low byte of an f16 is the subnormal u * 2^-24, which
-//           the tensor cores multiply exactly, so the codes enter the MMA after a byte permute and nothing else;
+//           the tensor cores multiply exactly, so the codes enter the MMA after a byte permute and nothing else (int4:
+//           a mask; the high nibbles are used in place as 16 * code, with 1/16 folded into the matching part of q');
 //   V side: V^[t][c] = m_t + scale_t * (u[t][c] - k_t), with k_t the code of the value 0 (clamped to 0..255) and
 //           m_t = lo_t + scale_t * k_t.  The per-token scale is folded into the softmax weights before they are rounded
 //           to f16, the codes enter the MMA as u * 2^-24, and the scalars sum_t w_t k_t (rounded weights) and
@@ -26,13 +27,26 @@
 namespace b200kv {
 
 constexpr int KM_D = 128;
-constexpr int KM_NS = 3;                                  // stages (3 CTAs of 62 KB per SM)
-constexpr int KM_KC = PAGE_TOKENS * KM_D;                 // 8192 bytes of K codes per page and head
 constexpr int KM_KP = 2 * 2 * KM_D * 4;                   // 2 blocks x (lo[D], scale[D]) f32
 constexpr int KM_VP = PAGE_TOKENS * 2 * 4;                // (lo, scale) f32 per token
-constexpr int KM_STAGE = 2 * KM_KC + KM_KP + KM_VP;       // 18944
+template <int BITS>
+struct KGeo {
+    static constexpr int FMT = BITS == 8 ? B200KV_FMT_Q8_1 : B200KV_FMT_Q4_0;  // the block format whose row layout the codes borrow
+    static constexpr int KC = PAGE_TOKENS * KM_D * BITS / 8;                   // bytes of K (or V) codes per page and head
+    static constexpr int STAGE = 2 * KC + KM_KP + KM_VP;                       // 18944 / 10752
+    static constexpr float LV = BITS == 8 ? 255.f : 15.f;
+    static constexpr int NS = 3;                     // stages
+    static constexpr int CTAS = BITS == 8 ? 3 : 4;   // resident CTAs per SM (73.5 KB / 48.9 KB each); measured: a fourth CTA with 2 stages loses for int8
+};
 constexpr int KM_PARAMS = 2 * (2 * 8 * 32 * 16 + 2 * 2 * 8 * 4);  // two buffers of: q' fragments [2 blocks][8 k-steps][32 lanes], q . lo [2 blocks][2 halves][8 heads]
 constexpr float KM_PSCALE = 64.f;                         // softmax weights * V scale are lifted away from the f16 subnormals
+
+// First of the four channels that k-step s holds for the thread with lane % 4 = c.  int8: s = 2 grp + hh covers channels
+// 32 grp + 8c + 4hh + {0,1 | 2,3}; int4: 32 grp + 16 hh + 4c + {0,1 | 2,3} (hh = 1: the high nibbles).
+template <int BITS>
+__host__ __device__ constexpr int kstep_channel(int s, int c) {
+    return BITS == 8 ? 32 * (s >> 1) + 8 * c + 4 * (s & 1) : 32 * (s >> 1) + 16 * (s & 1) + 4 * c;
+}
 
 struct KiviMmaParams {
     KiviView v;
@@ -45,7 +59,10 @@ struct KiviMmaParams {
     float scale;
 };
 
-__global__ void __launch_bounds__(128, 3) kivi_mma_kernel(KiviMmaParams p, const __grid_constant__ InlineBatch ib) {
+template <int BITS>
+__global__ void __launch_bounds__(128, KGeo<BITS>::CTAS) kivi_mma_kernel(KiviMmaParams p, const __grid_constant__ InlineBatch ib) {
+    using Kg = KGeo<BITS>;
+    constexpr int KM_KC = Kg::KC, KM_STAGE = Kg::STAGE, CFMT = Kg::FMT, KM_NS = Kg::NS;
     constexpr float LOG2E = 1.4426950408889634f;
     constexpr float TWO24 = 16777216.f;
     extern __shared__ __align__(1024) uint8_t stages[];
@@ -103,7 +120,7 @@ __global__ void __launch_bounds__(128, 3) kivi_mma_kernel(KiviMmaParams p, const
 #pragma unroll
     for (int j = 0; j < 4; j++)
 #pragma unroll
-        for (int e = 0; e < 4; e++) qf[4 * j + e] = q_s[r * KM_D + 32 * (2 * hf + (j >> 1)) + 8 * c + 4 * (j & 1) + e];
+        for (int e = 0; e < 4; e++) qf[4 * j + e] = q_s[r * KM_D + kstep_channel<BITS>(4 * hf + j, c) + e];
     const float sl2 = p.scale * LOG2E;
     float m_run[2] = {-INFINITY, -INFINITY};
     float l_part[2] = {0.f, 0.f};
@@ -130,9 +147,10 @@ __global__ void __launch_bounds__(128, 3) kivi_mma_kernel(KiviMmaParams p, const
             float bpart[4];
 #pragma unroll
             for (int j = 0; j < 4; j++) {
-                const int ks = 4 * hf + j, k0 = 32 * (ks >> 1) + 8 * c + 4 * (ks & 1);
+                const int ks = 4 * hf + j, k0 = kstep_channel<BITS>(ks, c);
                 const float4 sc = *(const float4*)(sc_p + k0), lo = *(const float4*)(lo_p + k0);
-                const float x0 = qf[4 * j] * sc.x, x1 = qf[4 * j + 1] * sc.y, x2 = qf[4 * j + 2] * sc.z, x3 = qf[4 * j + 3] * sc.w;
+                const float hn = (BITS == 4 && (ks & 1)) ? 0.0625f : 1.f;  // int4: the odd k-steps meet high nibbles in place, 16 * code
+                const float x0 = qf[4 * j] * sc.x * hn, x1 = qf[4 * j + 1] * sc.y * hn, x2 = qf[4 * j + 2] * sc.z * hn, x3 = qf[4 * j + 3] * sc.w * hn;
                 const __half2 h01 = __floats2half2_rn(x0, x1), h23 = __floats2half2_rn(x2, x3);
                 const __half2 l01 = __floats2half2_rn(x0 - __low2float(h01), x1 - __high2float(h01));
                 const __half2 l23 = __floats2half2_rn(x2 - __low2float(h23), x3 - __high2float(h23));
@@ -172,15 +190,22 @@ __global__ void __launch_bounds__(128, 3) kivi_mma_kernel(KiviMmaParams p, const
             const uint4* qp = qp_s + (i & 1) * (2 * 8 * 32) + blk * 8 * 32 + lane;
 #pragma unroll
             for (int g = 0; g < 4; g++) {
-                const uint2 wa = *(const uint2*)(Kc + chunk_addr(B200KV_FMT_Q8_1, KM_D, 0, tA, 32 * g + 8 * c));
-                const uint2 wb = *(const uint2*)(Kc + chunk_addr(B200KV_FMT_Q8_1, KM_D, 0, tB, 32 * g + 8 * c));
+                uint32_t xa[2], xb[2];  // this thread's codes of channel group g, rows tA and tB, first and second k-step
+                if constexpr (BITS == 8) {
+                    const uint2 wa = *(const uint2*)(Kc + chunk_addr(CFMT, KM_D, 0, tA, 32 * g + 8 * c));
+                    const uint2 wb = *(const uint2*)(Kc + chunk_addr(CFMT, KM_D, 0, tB, 32 * g + 8 * c));
+                    xa[0] = wa.x, xa[1] = wa.y, xb[0] = wb.x, xb[1] = wb.y;
+                } else {  // bytes 4c .. 4c+3 of the group: low nibbles = channels 32g + 4c + 0..3, high nibbles = 32g + 16 + 4c + 0..3
+                    const uint32_t wa = *(const uint32_t*)(Kc + chunk_addr(CFMT, KM_D, 0, tA, 16 * g + 4 * c));
+                    const uint32_t wb = *(const uint32_t*)(Kc + chunk_addr(CFMT, KM_D, 0, tB, 16 * g + 4 * c));
+                    xa[0] = wa & 0x0f0f0f0fu, xa[1] = wa & 0xf0f0f0f0u, xb[0] = wb & 0x0f0f0f0fu, xb[1] = wb & 0xf0f0f0f0u;
+                }
 #pragma unroll
                 for (int hh = 0; hh < 2; hh++) {
-                    const uint32_t xa = hh ? wa.y : wa.x, xb = hh ? wb.y : wb.x;
                     const uint4 w = qp[(2 * g + hh) * 32];
                     uint32_t a[4];
-                    a[0] = __byte_perm(xa, 0, 0x4140), a[1] = __byte_perm(xb, 0, 0x4140);
-                    a[2] = __byte_perm(xa, 0, 0x4342), a[3] = __byte_perm(xb, 0, 0x4342);
+                    a[0] = __byte_perm(xa[hh], 0, 0x4140), a[1] = __byte_perm(xb[hh], 0, 0x4140);
+                    a[2] = __byte_perm(xa[hh], 0, 0x4342), a[3] = __byte_perm(xb[hh], 0, 0x4342);
                     mma_f16(sacc, a, w.x, w.y);
                     mma_f16(sacc, a, w.z, w.w);
                 }
@@ -199,8 +224,8 @@ __global__ void __launch_bounds__(128, 3) kivi_mma_kernel(KiviMmaParams p, const
             l_part[0] = fmaf(l_part[0], al0, p0 + p2);
             l_part[1] = fmaf(l_part[1], al1, p1 + p3);
             const float2 vpA = *(const float2*)(Vp + tA * 2), vpB = *(const float2*)(Vp + tB * 2);  // (lo, scale) of the two tokens
-            const float kA = fminf(fmaxf(rintf(__fdividef(-vpA.x, vpA.y)), 0.f), 255.f);
-            const float kB = fminf(fmaxf(rintf(__fdividef(-vpB.x, vpB.y)), 0.f), 255.f);
+            const float kA = fminf(fmaxf(rintf(__fdividef(-vpA.x, vpA.y)), 0.f), Kg::LV);
+            const float kB = fminf(fmaxf(rintf(__fdividef(-vpB.x, vpB.y)), 0.f), Kg::LV);
             const float mA = fmaf(kA, vpA.y, vpA.x), mB = fmaf(kB, vpB.y, vpB.x);
             // weights times the token's scale, rounded once to f16, then transposed into B fragments
             const float fA = vpA.y * KM_PSCALE, fB = vpB.y * KM_PSCALE;
@@ -218,21 +243,45 @@ __global__ void __launch_bounds__(128, 3) kivi_mma_kernel(KiviMmaParams p, const
             const uint32_t pb0 = movmatrix_trans(hA);  // tokens 2c, 2c+1 of head n
             const uint32_t pb1 = movmatrix_trans(hB);  // tokens 2c+8, 2c+9
             const int T0 = warp * 16 + 2 * c;
-            uint4 x[4];  // 16 bytes at positions 16r.. of each row: channel slot (r | r + 8) of every m-tile
-            x[0] = *(const uint4*)(Vc + chunk_addr(B200KV_FMT_Q8_1, KM_D, 1, T0, 16 * r));
-            x[1] = *(const uint4*)(Vc + chunk_addr(B200KV_FMT_Q8_1, KM_D, 1, T0 + 1, 16 * r));
-            x[2] = *(const uint4*)(Vc + chunk_addr(B200KV_FMT_Q8_1, KM_D, 1, T0 + 8, 16 * r));
-            x[3] = *(const uint4*)(Vc + chunk_addr(B200KV_FMT_Q8_1, KM_D, 1, T0 + 9, 16 * r));
+            if constexpr (BITS == 8) {
+                uint4 x[4];  // 16 bytes at positions 16r.. of each row: channel slot (r | r + 8) of every m-tile
+                x[0] = *(const uint4*)(Vc + chunk_addr(CFMT, KM_D, 1, T0, 16 * r));
+                x[1] = *(const uint4*)(Vc + chunk_addr(CFMT, KM_D, 1, T0 + 1, 16 * r));
+                x[2] = *(const uint4*)(Vc + chunk_addr(CFMT, KM_D, 1, T0 + 8, 16 * r));
+                x[3] = *(const uint4*)(Vc + chunk_addr(CFMT, KM_D, 1, T0 + 9, 16 * r));
 #pragma unroll
-            for (int j = 0; j < 8; j++) {
-                const uint32_t w0 = (&x[0].x)[j >> 1], w1 = (&x[1].x)[j >> 1], w2 = (&x[2].x)[j >> 1], w3 = (&x[3].x)[j >> 1];
-                const uint32_t sel = (j & 1) ? 0x7632u : 0x5410u;
-                const uint32_t u01 = __byte_perm(w0, w1, sel);  // [T0.b2j, T0.b2j+1, T1.b2j, T1.b2j+1]
-                const uint32_t u23 = __byte_perm(w2, w3, sel);
-                uint32_t a[4];
-                a[0] = __byte_perm(u01, 0, 0x4240), a[1] = __byte_perm(u01, 0, 0x4341);
-                a[2] = __byte_perm(u23, 0, 0x4240), a[3] = __byte_perm(u23, 0, 0x4341);
-                mma_f16(o[j], a, pb0, pb1);
+                for (int j = 0; j < 8; j++) {
+                    const uint32_t w0 = (&x[0].x)[j >> 1], w1 = (&x[1].x)[j >> 1], w2 = (&x[2].x)[j >> 1], w3 = (&x[3].x)[j >> 1];
+                    const uint32_t sel = (j & 1) ? 0x7632u : 0x5410u;
+                    const uint32_t u01 = __byte_perm(w0, w1, sel);  // [T0.b2j, T0.b2j+1, T1.b2j, T1.b2j+1]
+                    const uint32_t u23 = __byte_perm(w2, w3, sel);
+                    uint32_t a[4];
+                    a[0] = __byte_perm(u01, 0, 0x4240), a[1] = __byte_perm(u01, 0, 0x4341);
+                    a[2] = __byte_perm(u23, 0, 0x4240), a[3] = __byte_perm(u23, 0, 0x4341);
+                    mma_f16(o[j], a, pb0, pb1);
+                }
+            } else {
+                uint2 x[4];  // 8 bytes at positions 8r..: byte j = slot r (low nibble) | slot r + 8 (high) of m-tile j
+                x[0] = *(const uint2*)(Vc + chunk_addr(CFMT, KM_D, 1, T0, 8 * r));
+                x[1] = *(const uint2*)(Vc + chunk_addr(CFMT, KM_D, 1, T0 + 1, 8 * r));
+                x[2] = *(const uint2*)(Vc + chunk_addr(CFMT, KM_D, 1, T0 + 8, 8 * r));
+                x[3] = *(const uint2*)(Vc + chunk_addr(CFMT, KM_D, 1, T0 + 9, 8 * r));
+#pragma unroll
+                for (int jj = 0; jj < 4; jj++) {  // m-tiles 2jj and 2jj + 1
+                    const uint32_t w0 = (&x[0].x)[jj >> 1], w1 = (&x[1].x)[jj >> 1], w2 = (&x[2].x)[jj >> 1], w3 = (&x[3].x)[jj >> 1];
+                    const uint32_t sel = (jj & 1) ? 0x7632u : 0x5410u;
+                    const uint32_t u01 = __byte_perm(w0, w1, sel), u23 = __byte_perm(w2, w3, sel);
+                    // high nibbles in place (16 * code): rows r + 8 of O^T come out 16 times too large, undone at the end
+                    const uint32_t lo01 = u01 & 0x0f0f0f0fu, hi01 = u01 & 0xf0f0f0f0u;
+                    const uint32_t lo23 = u23 & 0x0f0f0f0fu, hi23 = u23 & 0xf0f0f0f0u;
+                    uint32_t a[4];
+                    a[0] = __byte_perm(lo01, 0, 0x4240), a[1] = __byte_perm(hi01, 0, 0x4240);
+                    a[2] = __byte_perm(lo23, 0, 0x4240), a[3] = __byte_perm(hi23, 0, 0x4240);
+                    mma_f16(o[2 * jj], a, pb0, pb1);
+                    a[0] = __byte_perm(lo01, 0, 0x4341), a[1] = __byte_perm(hi01, 0, 0x4341);
+                    a[2] = __byte_perm(lo23, 0, 0x4341), a[3] = __byte_perm(hi23, 0, 0x4341);
+                    mma_f16(o[2 * jj + 1], a, pb0, pb1);
+                }
             }
         }
         if (__syncthreads_or(!ok)) {  // every warp is done with stage st and has built its share of the next page
@@ -259,12 +308,12 @@ __global__ void __launch_bounds__(128, 3) kivi_mma_kernel(KiviMmaParams p, const
         ml[(warp * 8 + 2 * c) * 2] = m_run[0], ml[(warp * 8 + 2 * c) * 2 + 1] = l0;
         ml[(warp * 8 + 2 * c + 1) * 2] = m_run[1], ml[(warp * 8 + 2 * c + 1) * 2 + 1] = l1;
     }
-    constexpr float UNDO = TWO24 / KM_PSCALE;
+    constexpr float UNDO = TWO24 / KM_PSCALE, UNDO_HI = BITS == 4 ? UNDO / 16.f : UNDO;  // int4: rows r + 8 carry 16 * code
 #pragma unroll
     for (int j = 0; j < 8; j++) {
         float* base = om + (warp * 8 + 2 * c) * KM_D + 16 * j + r;
         base[0] = fmaf(o[j][0], UNDO, b0), base[KM_D] = fmaf(o[j][1], UNDO, b1);
-        base[8] = fmaf(o[j][2], UNDO, b0), base[KM_D + 8] = fmaf(o[j][3], UNDO, b1);
+        base[8] = fmaf(o[j][2], UNDO_HI, b0), base[KM_D + 8] = fmaf(o[j][3], UNDO_HI, b1);
     }
     __syncthreads();
     for (int idx = tid; idx < ng * KM_D; idx += 128) {
@@ -293,7 +342,7 @@ __global__ void __launch_bounds__(128, 3) kivi_mma_kernel(KiviMmaParams p, const
 }
 
 bool kivi_mma_supported(const b200kv_cache* c, int dtype) {
-    return c->kivi.bits == 8 && c->cfg.head_dim == KM_D && c->cfg.has_values && (dtype == B200KV_F16 || dtype == B200KV_BF16);
+    return c->cfg.head_dim == KM_D && c->cfg.has_values && (dtype == B200KV_F16 || dtype == B200KV_BF16);
 }
 
 int launch_kivi_mma(b200kv_cache* c, const void* q, const int64_t* qs, int n_seqs, int G, int dtype, float scale, int n_splits,
@@ -304,12 +353,22 @@ int launch_kivi_mma(b200kv_cache* c, const void* q, const int64_t* qs, int n_seq
     p.part_o = part_o, p.part_ml = part_ml, p.status = c->d_status;
     p.G = G, p.dtype = dtype, p.n_splits = n_splits, p.part_stride = n_splits + 1, p.part_off = 1;
     p.scale = scale;
-    const size_t ring = (size_t)KM_NS * KM_STAGE;
-    const size_t smem = ring + KM_PARAMS + 64;  // ring (reused by the warp merge: 17 KB), q' fragments and q . lo, barriers
-    B200KV_CUDA(cudaFuncSetAttribute(kivi_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     dim3 grid(n_seqs * n_splits, c->cfg.n_kv_heads, (G + 7) / 8);
-    B200KV_CUDA(launch_after_predecessor(kivi_mma_kernel, grid, dim3(128), smem, stream, p, ib));
+    // ring (reused by the warp merge, 17 KB), q' fragments and q . lo, barriers
+    if (c->kivi.bits == 8) {
+        const size_t smem = (size_t)KGeo<8>::NS * KGeo<8>::STAGE + KM_PARAMS + 64;
+        B200KV_CUDA(cudaFuncSetAttribute(kivi_mma_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        B200KV_CUDA(launch_after_predecessor(kivi_mma_kernel<8>, grid, dim3(128), smem, stream, p, ib));
+    } else {
+        const size_t smem = (size_t)KGeo<4>::NS * KGeo<4>::STAGE + KM_PARAMS + 64;
+        B200KV_CUDA(cudaFuncSetAttribute(kivi_mma_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        B200KV_CUDA(launch_after_predecessor(kivi_mma_kernel<4>, grid, dim3(128), smem, stream, p, ib));
+    }
     return B200KV_OK;
 }
 
+}  // namespace b200kv
+
+namespace b200kv {
+int kivi_mma_ctas_per_sm(int bits) { return bits == 8 ? KGeo<8>::CTAS : KGeo<4>::CTAS; }
 }  // namespace b200kv
