@@ -187,6 +187,28 @@ int b200kv_attend_static_scratch(b200kv_cache* cache, int32_t n_seqs, const int3
                                  const void* q, const int64_t q_strides[3], void* out, const int64_t out_strides[3],
                                  int32_t dtype, float scale, void* stream);
 
+/* ---- Q4_0 weights x activations: the decode-time linear layers either side of the cache path ----
+ * Arithmetic of Q4_0::w4a8_gemm / w4a8_gemv (linalg/src/frame/block_quant/q4_0.rs:199-310), bit for bit: activations
+ * quantised per block of 32 to int8 with an f32 scale, exact int32 block dot products, contributions added in
+ * ascending block order.  Replaces cuda/src/kernels/cu/mm_mv_q.cu (`mul_vec_q40_m_*`) and cu/quantize.cu behind
+ * dispatch_ggml_matvec_q40 (cuda/src/kernels/matmul/mod.rs:481-520). */
+
+/* Bytes of the packed form of an [n, k] Q4_0 matrix (k a multiple of 32), or -1. */
+int64_t b200kv_q40_packed_bytes(int64_t n, int64_t k);
+/* Repacks `blocks` (device memory; the reference's storage: n rows of k/32 blocks of 18 bytes, f16 scale then 16
+ * nibble bytes, cuda/src/rewrite_rules/pad_q40_weights.rs does the reference's own repacking) into `packed`
+ * (device memory, 16-byte aligned, b200kv_q40_packed_bytes long).  Done once per weight matrix. */
+int b200kv_q40_pack(const void* blocks, int64_t n, int64_t k, void* packed, void* stream);
+/* Bytes of device scratch a GEMM with m activation rows needs (quantised activations + a status word), or -1. */
+int64_t b200kv_q40_scratch_bytes(int64_t k, int32_t m);
+/* out[m, n] = a[m, k] . W[n, k]^T.  `a` is device memory of type `dtype` (cast to f32 first, as the reference's callers
+ * do), rows a_stride elements apart; `out` is f32, rows out_stride elements apart; `scratch` is caller-provided device
+ * memory (16-byte aligned) that must not be shared by two calls in flight.  Allocates nothing. */
+int b200kv_q40_gemm(const void* packed, int64_t n, int64_t k, const void* a, int64_t a_stride, int32_t m, int32_t dtype,
+                    void* scratch, float* out, int64_t out_stride, void* stream);
+/* Synchronises `stream` and reports whether a bounded wait of the last GEMM that used `scratch` expired. */
+int b200kv_q40_check(const void* scratch, void* stream);
+
 /* Per-launch timing, off by default.  When enabled, every kernel launched for this cache is bracketed by a
  * CUDA event pair on the caller's stream (what tract-cuda's TractCudaStream does for its profiler,
  * cuda/src/context.rs:364-453).  b200kv_profile_read waits for the recorded launches, returns up to

@@ -47,6 +47,8 @@ def lib():
         L.orc_q8_1_dequant.argtypes = [u16p, i8p, C.c_int64, fp]
         L.orc_q4_0_quant.argtypes = [fp, C.c_int64, u16p, u8p]
         L.orc_q4_0_dequant.argtypes = [u16p, u8p, C.c_int64, fp]
+        L.orc_w4a8_quantize_row.argtypes = [fp, C.c_int64, i8p, fp]
+        L.orc_w4a8_gemm.argtypes = [u16p, u8p, C.c_int64, C.c_int64, fp, C.c_int64, fp, ip]
         L.orc_kivi_new.restype = C.c_void_p
         L.orc_kivi_new.argtypes = [ip, ip, ip]
         L.orc_kivi_free.argtypes = [C.c_void_p]
@@ -143,6 +145,33 @@ def q4_0_dequant(scales: np.ndarray, packed: np.ndarray) -> np.ndarray:
     packed = np.ascontiguousarray(packed, np.uint8)
     out = np.empty(packed.shape[:-1] + (packed.shape[-1] * 2,), np.float32)
     lib().orc_q4_0_dequant(_p(scales, C.c_uint16), _p(packed, C.c_uint8), scales.size, _p(out, C.c_float))
+    return out
+
+
+def w4a8_quantize_row(a: np.ndarray):
+    """Q4_0::quantize_row_q8 (q4_0.rs:199-214): (int8 codes [..., K], f32 scales [..., K/32])."""
+    a = to_f32(a)
+    assert a.shape[-1] % 32 == 0
+    rows = a.reshape(-1, a.shape[-1])
+    q = np.empty(rows.shape, np.int8)
+    sc = np.empty((rows.shape[0], rows.shape[1] // 32), np.float32)
+    for i in range(rows.shape[0]):
+        lib().orc_w4a8_quantize_row(_p(rows[i], C.c_float), rows.shape[1], _p(q[i], C.c_int8), _p(sc[i], C.c_float))
+    return q.reshape(a.shape), sc.reshape(a.shape[:-1] + (a.shape[-1] // 32,))
+
+
+def w4a8_gemm(scales: np.ndarray, packed: np.ndarray, a: np.ndarray, threads: int = 0) -> np.ndarray:
+    """Q4_0::w4a8_gemm (q4_0.rs:260-310): weights [N, K] as Q4_0 (scales uint16 [N, K/32], packed uint8 [N, K/2]),
+    activations f32 [M, K]; returns f32 [M, N]."""
+    scales = np.ascontiguousarray(scales, np.uint16)
+    packed = np.ascontiguousarray(packed, np.uint8)
+    a = to_f32(a)
+    n, k = packed.shape[0], packed.shape[1] * 2
+    m = a.shape[0]
+    assert a.shape[1] == k and scales.shape == (n, k // 32)
+    out = np.empty((m, n), np.float32)
+    lib().orc_w4a8_gemm(_p(scales, C.c_uint16), _p(packed, C.c_uint8), n, k, _p(a, C.c_float), m, _p(out, C.c_float),
+                        threads or hardware_threads())
     return out
 
 

@@ -539,6 +539,49 @@ void orc_naive_sdpa_f64(const float* q, const float* k, const float* v, const fl
     });
 }
 
+// ---- Q4_0 weights x int8-quantised activations (linalg/src/frame/block_quant/q4_0.rs) ------------------
+// Q4_0::quantize_row_q8 (:199-214): per block of 32, scale = max|a| / 127 (1 when the block is all zero),
+// q = round(a * (1 / scale)) clamped to +-127 (round half away from zero; a NaN becomes 0 in the cast).
+void orc_w4a8_quantize_row(const float* a, int64_t k, int8_t* q, float* scales) {
+    for (int64_t b = 0; b < k / 32; b++) {
+        const float* blk = a + b * 32;
+        float amax = 0.f;
+        for (int i = 0; i < 32; i++) amax = std::fmax(amax, std::fabs(blk[i]));  // f32::max ignores a NaN operand
+        const float scale = amax > 0.f ? amax / 127.0f : 1.0f;
+        scales[b] = scale;
+        const float r = 1.0f / scale;
+        for (int i = 0; i < 32; i++) q[b * 32 + i] = sat_i8(clampf(std::round(blk[i] * r), -127.f, 127.f));
+    }
+}
+
+// Q4_0::w4a8_gemm (:260-310; w4a8_gemv :221-254 is the m = 1 case, bit-identical per row): out[m, n] accumulates,
+// block after block in ascending order, (dot as f32) * w_scale * a_scale with dot the exact int32 dot product of
+// the block's 32 weights (nibble - 8, GGML order: byte j = element j | element 16 + j << 4) and activations.
+// `scales` / `packed` are the two halves of every 18-byte block: [n, k/32] f16 bits and [n, k/32, 16] nibble bytes.
+void orc_w4a8_gemm(const uint16_t* scales, const uint8_t* packed, int64_t n, int64_t k, const float* a, int64_t m, float* out,
+                   int threads) {
+    const int64_t nb = k / 32;
+    std::vector<int8_t> aq((size_t)(m * k));
+    std::vector<float> asc((size_t)(m * nb));
+    for (int64_t mi = 0; mi < m; mi++) orc_w4a8_quantize_row(a + mi * k, k, aq.data() + mi * k, asc.data() + mi * nb);
+    parallel_for((int)n, threads, [&](int ni) {
+        std::vector<float> accs((size_t)m, 0.f);
+        int8_t w[32];
+        for (int64_t b = 0; b < nb; b++) {
+            const uint8_t* blk = packed + ((int64_t)ni * nb + b) * 16;
+            const float wscale = f16_to_f32(scales[(int64_t)ni * nb + b]);
+            for (int j = 0; j < 16; j++) w[j] = (int8_t)((blk[j] & 0x0F) - 8), w[16 + j] = (int8_t)((blk[j] >> 4) - 8);
+            for (int64_t mi = 0; mi < m; mi++) {
+                const int8_t* aqb = aq.data() + mi * k + b * 32;
+                int32_t dot = 0;
+                for (int i = 0; i < 32; i++) dot += (int32_t)w[i] * (int32_t)aqb[i];
+                accs[mi] += (float)dot * wscale * asc[mi * nb + b];
+            }
+        }
+        for (int64_t mi = 0; mi < m; mi++) out[mi * n + ni] = accs[mi];
+    });
+}
+
 int orc_hardware_threads() { return (int)std::thread::hardware_concurrency(); }
 
 }  // extern "C"

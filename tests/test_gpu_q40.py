@@ -1,0 +1,74 @@
+"""Q4_0 weights x int8-quantised activations on the GPU: bit-exact against the CPU restatement of Q4_0::w4a8_gemm."""
+import numpy as np
+import pytest
+
+import oracle
+from util import normal, normal_with_outliers
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+
+
+@pytest.fixture(scope="module")
+def kv():
+    import tract_b200
+
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device")
+    tract_b200.lib()
+    return tract_b200
+
+
+def ggml_blocks(sc, pk):
+    """The reference's storage: [N, K/32] blocks of 18 bytes, f16 scale (little endian) then 16 nibble bytes."""
+    n, nb = sc.shape
+    blob = np.empty((n, nb, 18), np.uint8)
+    blob[:, :, :2] = sc.reshape(n, nb, 1).view(np.uint8)
+    blob[:, :, 2:] = pk.reshape(n, nb, 16)
+    return blob
+
+
+@pytest.mark.parametrize("m,n,k,adt", [
+    (1, 64, 64, "f32"),
+    (5, 7, 64, "f32"),        # the shape of the reference's own GEMM test: a ragged tile of rows, 5 activation rows
+    (4, 6, 96, "f32"),
+    (8, 100, 4096, "f32"),    # 128 blocks: 16 stages of the ring
+    (3, 48, 14336, "f16"),    # the FFN inner dimension of the Llama-3-8B shape: 448 blocks
+    (1, 1024, 4096, "bf16"),  # a K/V projection
+    (13, 40, 352, "f32"),     # two groups of activation rows, a last stage of 3 blocks
+])
+def test_q40_gemm_bit_exact(kv, m, n, k, adt):
+    w = normal_with_outliers(11, (n, k)).astype(np.float32)
+    tdt = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}[adt]
+    a_t = torch.from_numpy(normal(12, (m, k)).astype(np.float32)).to(tdt)
+    sc, pk = oracle.q4_0_quant(w)
+    lin = kv.Q40Linear(torch.from_numpy(ggml_blocks(sc, pk)).cuda(), max_m=16)
+    got = lin.gemm(a_t.cuda()).cpu().numpy()
+    lin.check()
+    want = oracle.w4a8_gemm(sc, pk, a_t.float().numpy())
+    assert got.tobytes() == want.tobytes()
+
+
+def test_q40_gemm_special_activations(kv):
+    # zero blocks (scale 1), a NaN inside a block (code 0, ignored by the maximum), a block of equal magnitudes
+    n, k = 32, 128
+    w = normal(21, (n, k)).astype(np.float32)
+    a = normal(22, (2, k)).astype(np.float32)
+    a[0, :32] = 0.0
+    a[0, 40] = np.nan
+    a[1, 96:] = -2.5
+    sc, pk = oracle.q4_0_quant(w)
+    lin = kv.Q40Linear(torch.from_numpy(ggml_blocks(sc, pk)).cuda())
+    got = lin.gemm(torch.from_numpy(a).cuda()).cpu().numpy()
+    want = oracle.w4a8_gemm(sc, pk, a)
+    assert got.tobytes() == want.tobytes()
+
+
+def test_q40_errors(kv):
+    blocks = torch.zeros((4, 2, 18), dtype=torch.uint8, device="cuda")
+    lin = kv.Q40Linear(blocks)
+    with pytest.raises(kv.B200KvError):
+        kv._ck(kv.lib().b200kv_q40_gemm(None, 4, 64, None, 64, 1, 0, None, None, 4, None))
+    assert kv.lib().b200kv_q40_packed_bytes(4, 33) == -1
+    assert lin.gemm(torch.zeros((1, 64), device="cuda")).abs().sum().item() == 0.0

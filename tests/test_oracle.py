@@ -315,3 +315,63 @@ def test_quantized_cache_close_to_concat_over_40_steps(per_channel):
         out = cache.eval(c)
     want = np.concatenate(chunks, 2)
     assert out.shape == want.shape and np.all(np.abs(out - want) <= 0.1 + 0.05 * np.abs(want))
+
+
+# ---- Q4_0 weights x int8 activations (q4_0.rs:199-310): the reference's own tests for the path, restated ----
+
+def _w4a8_case(m, n, k, fw, fa):
+    wf = np.array([fw(i) for i in range(n * k)], np.float32).reshape(n, k)
+    a = np.array([fa(i) for i in range(m * k)], np.float32).reshape(m, k)
+    sc, pk = oracle.q4_0_quant(wf)
+    return a, sc, pk, oracle.w4a8_gemm(sc, pk, a, threads=2)
+
+
+def test_w4a8_gemm_matches_gemv():
+    # q4_0.rs:538-550: the GEMM is bit-identical to the GEMV run per activation row
+    a, sc, pk, out = _w4a8_case(5, 7, 64, lambda i: ((i * 37 % 53) - 26.0) / 9.0, lambda i: ((i * 19 % 41) - 20.0) / 7.0)
+    for mi in range(5):
+        assert np.array_equal(oracle.w4a8_gemm(sc, pk, a[mi:mi + 1], threads=1)[0], out[mi])
+
+
+def test_w4a8_gemm_approx_dequant_matmul():
+    # q4_0.rs:553-575: within 0.15 |acc| + 1 of the sequential f32 product over the dequantised weights
+    a, sc, pk, out = _w4a8_case(4, 6, 96, lambda i: ((i * 31 % 47) - 23.0) / 11.0, lambda i: ((i * 23 % 43) - 21.0) / 8.0)
+    wd = oracle.q4_0_dequant(sc, pk)
+    for mi in range(4):
+        for ni in range(6):
+            acc = np.float32(0)
+            for ki in range(96):
+                acc = np.float32(acc + np.float32(wd[ni, ki] * a[mi, ki]))
+            assert abs(out[mi, ni] - acc) <= 0.15 * abs(acc) + 1.0
+
+
+def test_w4a8_gemv_near_f32_dequant():
+    # q4_0.rs:697-720: the reference's LCG inputs; relative L2 deviation from the f32-dequant GEMV below 2 %
+    n, k = 8, 64
+    state = 1
+    vals = []
+    for _ in range(n * k + k):
+        state = (state * 6364136223846793005 + 1) % (1 << 64)
+        vals.append(np.float32(np.float32(state >> 40) / np.float32(1 << 24)) - np.float32(0.5))
+    w = np.array(vals[:n * k], np.float32).reshape(n, k)
+    a = np.array(vals[n * k:], np.float32).reshape(1, k)
+    sc, pk = oracle.q4_0_quant(w)
+    deq = oracle.q4_0_dequant(sc, pk)
+    y_ref = np.zeros(n, np.float32)
+    for ni in range(n):
+        for kk in range(k):
+            y_ref[ni] = np.float32(y_ref[ni] + np.float32(deq[ni, kk] * a[0, kk]))
+    y = oracle.w4a8_gemm(sc, pk, a)[0]
+    assert np.sqrt(((y - y_ref) ** 2).sum()) / max(np.sqrt((y_ref ** 2).sum()), 1e-9) < 0.02
+
+
+def test_w4a8_activation_quantiser_edges():
+    # q4_0.rs:199-214: an all-zero block takes scale 1; the largest magnitude maps to +-127; a NaN becomes code 0
+    a = np.zeros((1, 96), np.float32)
+    a[0, 32:64] = np.linspace(-3, 5, 32, dtype=np.float32)
+    a[0, 64] = np.nan
+    a[0, 65] = 2.0
+    q, sc = oracle.w4a8_quantize_row(a)
+    assert sc[0, 0] == 1.0 and not q[0, :32].any()
+    assert sc[0, 1] == np.float32(5.0) / np.float32(127.0) and q[0, 63] == 127 and q[0, 32] == round(-3 / (5 / 127))
+    assert q[0, 64] == 0 and q[0, 65] == 127 and sc[0, 2] == np.float32(2.0) / np.float32(127.0)

@@ -24,6 +24,7 @@ EXPORTS = [
     "b200kv_seq_len", "b200kv_free_pages", "b200kv_page_bytes", "b200kv_append", "b200kv_attend", "b200kv_export",
     "b200kv_export_codes", "b200kv_truncate", "b200kv_fork", "b200kv_check", "b200kv_sdpa", "b200kv_profile",
     "b200kv_profile_read", "b200kv_attend_static_scratch", "b200kv_export_kivi", "b200kv_append_rope", "b200kv_rope",
+    "b200kv_q40_packed_bytes", "b200kv_q40_pack", "b200kv_q40_scratch_bytes", "b200kv_q40_gemm", "b200kv_q40_check",
 ]
 KERNEL_NAMES = {0: "table_scatter", 1: "append", 2: "decode", 3: "combine", 4: "export", 5: "sdpa_dense", 6: "prefill"}
 
@@ -262,6 +263,45 @@ class KvCache:
         n = C.c_int32()
         _ck(lib().b200kv_profile_read(self._h, max_records, ids, ms, C.byref(n)))
         return [(KERNEL_NAMES.get(ids[i], str(ids[i])), ms[i]) for i in range(n.value)]
+
+
+class Q40Linear:
+    """A Q4_0 weight matrix [N, K] on the device, applied with the arithmetic of Q4_0::w4a8_gemm
+    (linalg/src/frame/block_quant/q4_0.rs:260-310).  `blocks`: uint8 CUDA tensor [N, K/32, 18], the reference's storage."""
+
+    def __init__(self, blocks, max_m=8):
+        import torch
+
+        assert blocks.dtype == torch.uint8 and blocks.dim() == 3 and blocks.shape[2] == 18 and blocks.is_contiguous()
+        self.n, self.k = int(blocks.shape[0]), int(blocks.shape[1]) * 32
+        L = lib()
+        L.b200kv_q40_packed_bytes.restype = C.c_int64
+        L.b200kv_q40_scratch_bytes.restype = C.c_int64
+        nbytes = L.b200kv_q40_packed_bytes(C.c_int64(self.n), C.c_int64(self.k))
+        if nbytes < 0:
+            raise B200KvError("Q4_0 weights need K a multiple of 32")
+        self.packed = torch.empty(nbytes, dtype=torch.uint8, device=blocks.device)
+        self.max_m = max_m
+        self.scratch = torch.empty(L.b200kv_q40_scratch_bytes(C.c_int64(self.k), max_m), dtype=torch.uint8, device=blocks.device)
+        with torch.cuda.device(blocks.device):
+            _ck(L.b200kv_q40_pack(C.c_void_p(blocks.data_ptr()), C.c_int64(self.n), C.c_int64(self.k), C.c_void_p(self.packed.data_ptr()),
+                                  _stream()))
+
+    def gemm(self, a, out=None):
+        """a: [M, K] f32 / f16 / bf16 CUDA tensor (rows contiguous); returns f32 [M, N]."""
+        import torch
+
+        assert a.dim() == 2 and a.shape[1] == self.k and a.stride(1) == 1 and a.shape[0] <= self.max_m
+        if out is None:
+            out = torch.empty((a.shape[0], self.n), dtype=torch.float32, device=a.device)
+        with torch.cuda.device(a.device):
+            _ck(lib().b200kv_q40_gemm(C.c_void_p(self.packed.data_ptr()), C.c_int64(self.n), C.c_int64(self.k), C.c_void_p(a.data_ptr()),
+                                      C.c_int64(a.stride(0)), int(a.shape[0]), _dtype_code(a), C.c_void_p(self.scratch.data_ptr()),
+                                      C.c_void_p(out.data_ptr()), C.c_int64(out.stride(0)), _stream()))
+        return out
+
+    def check(self):
+        _ck(lib().b200kv_q40_check(C.c_void_p(self.scratch.data_ptr()), _stream()))
 
 
 def rope(x, cos, sin):
