@@ -433,6 +433,147 @@ def run_prefill(args, rank, world):
 # CPU arm: the restatement of tract's own CPU algorithm (the Rust reference cannot be built here)
 # ---------------------------------------------------------------------------------------------------
 
+LINEAR = {
+    # the Q4_0 linear layers of the BASELINE config 5 decoder shape (hidden 4096, FFN 14336), 8 sequences per GPU;
+    # `layers` distinct weight matrices are walked per step so that the weights of a step exceed L2
+    "q40-ffn-up": dict(n=14336, k=4096, m=8, layers=8, desc="FFN gate/up projection [14336 x 4096], Q4_0, 8 activation rows"),
+    "q40-ffn-down": dict(n=4096, k=14336, m=8, layers=8, desc="FFN down projection [4096 x 14336], Q4_0, 8 activation rows"),
+    "q40-attn-proj": dict(n=4096, k=4096, m=8, layers=32, desc="attention q / o projection [4096 x 4096], Q4_0, 8 activation rows"),
+    "q40-gemv": dict(n=14336, k=4096, m=1, layers=8, desc="FFN gate/up projection, one activation row (GEMV)"),
+}
+
+
+def run_linear(args, rank, world):
+    """Q4_0 weights x int8-quantised activations (Q4_0::w4a8_gemm arithmetic): weight bytes per second against HBM."""
+    import torch
+    import torch.distributed as dist
+    import tract_b200 as kv
+    import oracle
+
+    wl = LINEAR[args.workload]
+    n, k, m, layers = wl["n"], wl["k"], wl["m"], wl["layers"]
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0)))
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    g = torch.Generator(device="cpu").manual_seed(4242 + rank)
+    # random blocks are valid Q4_0 weights: any nibbles, f16 scales drawn positive and small
+    lins = []
+    for _ in range(layers):
+        blocks = torch.randint(0, 256, (n, k // 32, 18), dtype=torch.uint8, generator=g)
+        scales = (torch.rand((n, k // 32), generator=g) * 0.05 + 0.001).to(torch.float16)
+        blocks[:, :, :2] = scales.view(torch.uint8).reshape(n, k // 32, 2)
+        lins.append(kv.Q40Linear(blocks.to(dev), max_m=m))
+    a_host = torch.randn((m, k), generator=g).pin_memory()
+    a_dev = a_host.to(dev)
+    out = torch.empty((m, n), dtype=torch.float32, device=dev)
+    out_host = torch.empty((m, n), dtype=torch.float32).pin_memory()
+    weight_bytes = layers * n * (k // 32) * 18
+
+    def launch_all():
+        for lin in lins:
+            lin.gemm(a_dev, out)
+
+    # the step is launch bound from Python (2 launches per layer): replay it as a CUDA graph, as a decode loop would
+    launch_all()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        launch_all()
+        side.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            launch_all()
+    torch.cuda.synchronize()
+
+    def step():
+        graph.replay()
+
+    def step_e2e():
+        a_dev.copy_(a_host, non_blocking=True)
+        step()
+        out_host.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    sampler = ClockSampler(dev.index or 0)
+    if rank == 0:
+        sampler.start()
+    for _ in range(max(args.warmup, 3)):
+        step()
+    sampler.mark()
+    ms = timed(step, args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+    ms_e2e = timed(step_e2e, max(10, args.steps // 10)) / max(10, args.steps // 10)
+    lins[0].check()
+    ms_step = ms / args.steps
+    # the GEMM kernel alone, timed on the launching stream
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(20):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    kern_ms = e0.elapsed_time(e1) / 20
+    pk, pk_kind = peaks()
+    value = world * weight_bytes / (ms_step * 1e-3) / 1e9
+    achieved = weight_bytes / (kern_ms * 1e-3) / 1e9
+    if rank == 0:
+        line = {
+            "metric": "Q4_0 weight-read GB/s (sum over GPUs)", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "u4 weights x s8 activations, s32 block dot products, f32 accumulation", "data": "synthetic",
+            "config": {"workload": args.workload, "description": wl["desc"], "n": n, "k": k, "activation_rows": m, "layers_per_step": layers, "launch": "one CUDA graph replay per step",
+                       "weight_bytes_per_step_per_gpu": weight_bytes, "parallelism": f"replicas x{world}, no collective",
+                       "l2": "weights of one step exceed L2" if weight_bytes > 126e6 else "weights fit L2 (warm)"},
+            "tokens_per_s": world * m * layers / (ms_step * 1e-3),
+            "e2e": {"value": world * weight_bytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": m * k * 4,
+                    "d2h_bytes_per_step": m * n * 4, "ms_per_step": ms_e2e},
+            "gpu_launches": 2 * layers,
+            "roofline": {"bound": "hbm", "kernel": "q40_gemm_kernel (+ activation quantiser)", "achieved": achieved, "peak": pk["hbm_gbs"],
+                         "unit": "GB/s", "frac": achieved / pk["hbm_gbs"], "peak_kind": pk_kind, "traffic": None,
+                         "algorithmic_bytes": weight_bytes},
+            "clocks": clocks,
+        }
+        if not args.no_cpu_baseline:
+            import time
+            sc = np.random.default_rng(1).integers(0, 65535, (min(n, 512), k // 32)).astype(np.uint16) & 0x2fff
+            pkd = np.random.default_rng(2).integers(0, 256, (min(n, 512), k // 2)).astype(np.uint8)
+            a_np = a_host.numpy()
+            thr = oracle.hardware_threads()
+            t0 = time.perf_counter()
+            reps = 0
+            while time.perf_counter() - t0 < 5.0:
+                oracle.w4a8_gemm(sc, pkd, a_np, threads=thr)
+                reps += 1
+            dt = (time.perf_counter() - t0) / reps
+            line["cpu_baseline"] = {"value": min(n, 512) * (k // 32) * 18 / dt / 1e9, "unit": "GB/s", "cores": thr, "kind": "port",
+                                    "sample": f"{min(n, 512)} of the {n} output rows of one layer, {m} activation rows, {reps} repetitions"}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def cpu_step_factory(workload, sample_seqs, sample_past, threads):
     """Returns (step_fn, bytes_per_step): one decode step of `sample_seqs` sequences on the CPU:
     quantise the new token, dequantise the whole cache (what QuantizedDynKvCacheState::eval does every
@@ -531,7 +672,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=1000)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="cfg4-q8", choices=sorted(WORKLOADS) + sorted(PREFILL))
+    ap.add_argument("--workload", default="cfg4-q8", choices=sorted(WORKLOADS) + sorted(PREFILL) + sorted(LINEAR))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--quick", action="store_true", help="profiler runs: exactly W warm-up steps, no 1 s warm-up floor")
@@ -546,6 +687,9 @@ def main():
         r = run_reference(args, rank, world)
         if r:
             print(json.dumps(r))
+        return
+    if args.workload in LINEAR:
+        run_linear(args, rank, world)
         return
     if args.workload in PREFILL:
         r = run_prefill(args, rank, world)

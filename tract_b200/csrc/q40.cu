@@ -8,11 +8,12 @@
 // whose Q8_1 activation format (f16 scales) gives different bits from the CPU.
 //
 // Kernel: HBM bound (18 bytes per 32 weights, read once).  The weights are repacked once into tiles of 16 output rows
-// x all blocks, [block][16 rows x 16 nibble bytes | 16 f16 scales], so that a tile is one contiguous stream.  One warp
-// owns a tile: it pulls the stream through a private ring of cp.async.bulk stages, turns each block into the A operand
+// x all blocks, [block][16 rows x 16 nibble bytes | 16 f16 scales], so that a tile is one contiguous stream.  A CTA
+// owns a tile and its warps take turns at the stages of 8 blocks: a warp pulls its stage, and the quantised activations
+// beside it (L2 resident, shared by every tile), through cp.async.bulk, turns each block into the A operand
 // of one mma.sync.m16n8k32 (u8 nibbles x s8 activations -> s32: 16 rows x 8 activation rows of exact dot products;
-// the -8 of the nibbles is removed with the block's activation sum), and keeps the 16 x 8 f32 accumulators in the
-// C-fragment registers, where consecutive blocks arrive in order -- the order the reference adds them in.
+// the -8 of the nibbles is removed with the block's activation sum), and adds the 8 contributions to the 16 x 8 f32
+// accumulators, which travel from warp to warp in stage order -- the order the reference adds the blocks in.
 #include "internal.h"
 
 namespace b200kv {
@@ -22,9 +23,10 @@ constexpr int Q_TILE_ROWS = 16;           // output rows per warp (the M of the 
 constexpr int Q_BLOCK_BYTES = 16 * 16 + 16 * 2;  // one block of a tile: 256 nibble bytes + 16 f16 scales
 constexpr int Q_STAGE_BLOCKS = 8;
 constexpr int Q_STAGE_BYTES = Q_STAGE_BLOCKS * Q_BLOCK_BYTES;  // 2304
-constexpr int Q_STAGES = 6;
+constexpr int Q_DEPTH = 2;                // stages in flight per warp
 constexpr int Q_ACT_BLOCK = 2 * 8 * 16 + 8 * 4 + 8 * 4;  // per block and group of 8 activation rows: codes [2 halves][8][16], scales f32 [8], sums i32 [8]
 constexpr int Q_HEADER = 256;             // scratch header: the status word
+constexpr int Q_RING_STAGE = Q_STAGE_BYTES + Q_STAGE_BLOCKS * Q_ACT_BLOCK;  // weights then activations of 8 blocks: 4864 bytes
 
 // ---- repack: GGML blocks [n][k/32][18 B] -> tiles ------------------------------------------------------
 __global__ void q40_pack_kernel(const uint8_t* __restrict__ blocks, int64_t n, int64_t nb, uint8_t* __restrict__ packed) {
@@ -48,7 +50,9 @@ __global__ void q40_pack_kernel(const uint8_t* __restrict__ blocks, int64_t n, i
 
 // ---- activation quantiser: one warp per (block, activation row slot) ----------------------------------------------
 __global__ void q40_quant_act_kernel(const void* __restrict__ a, int64_t a_stride, int32_t m, int32_t dtype, int64_t nb,
-                                     uint8_t* __restrict__ act) {
+                                     uint8_t* __restrict__ act, int* __restrict__ status) {
+    grid_launch_dependents();  // the GEMM may be scheduled: it starts pulling weights and waits for this grid before it reads `act`
+    if (blockIdx.x == 0 && threadIdx.x == 0) *status = 0;
     const int lane = threadIdx.x & 31;
     const int64_t wid = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int64_t groups = (m + 7) / 8;
@@ -85,90 +89,154 @@ struct Q40Gemm {
 };
 
 __device__ inline void mma_u8s8(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// grid: (tiles, groups of 8 activation rows); one warp per CTA.
-__global__ void __launch_bounds__(32) q40_gemm_kernel(Q40Gemm p) {
-    __shared__ __align__(128) uint8_t ring[Q_STAGES * Q_STAGE_BYTES];
-    __shared__ uint64_t bars[Q_STAGES];
-    const int lane = threadIdx.x, r = lane >> 2, c = lane & 3;
+// Waits for a barrier phase unless the CTA has already failed; gives up after ~1 s and marks the CTA failed.
+__device__ inline void q40_wait(uint64_t* bar, uint32_t parity, volatile int* fail) {
+    if (mbar_try_wait(bar, parity)) return;
+    const uint64_t t0 = globaltimer_ns();
+    for (;;) {
+        if (*fail) return;
+#pragma unroll 1
+        for (int i = 0; i < 32; i++)
+            if (mbar_try_wait(bar, parity)) return;
+        if (globaltimer_ns() - t0 > 1000000000ull) {
+            *fail = 1;
+            return;
+        }
+    }
+}
+__device__ inline void q40_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// grid: (tiles, groups of 8 activation rows); Q_WARPS warps per tile.  Warp w takes the stages s = w, w + Q_WARPS, ...:
+// it computes the 8 x (16 x 8) contributions of its stage on its own, then receives the running accumulators from the
+// warp that had stage s - 1, adds its contributions in block order and hands the accumulators on.  Only that short
+// hand-off is serial; it keeps the additions in the order of the reference.
+template <int Q_WARPS>
+__global__ void __launch_bounds__(Q_WARPS * 32, 2) q40_gemm_kernel(Q40Gemm p) {
+    extern __shared__ __align__(128) uint8_t ring[];                      // Q_WARPS * Q_DEPTH stages; warp w owns slots w * Q_DEPTH ..
+    float4* hand = (float4*)(ring + Q_WARPS * Q_DEPTH * Q_RING_STAGE);    // [Q_WARPS][32 lanes]: accumulators on their way to warp w
+    uint64_t* full = (uint64_t*)(hand + Q_WARPS * 32);                    // [Q_WARPS * Q_DEPTH] bytes landed
+    uint64_t* token = full + Q_WARPS * Q_DEPTH;                           // [Q_WARPS] accumulators handed to warp w
+    volatile int* fail_s = (volatile int*)(token + Q_WARPS);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, r = lane >> 2, c = lane & 3;
     const int64_t tile = blockIdx.x, g = blockIdx.y;
     const uint8_t* wsrc = p.packed + tile * p.nb * Q_BLOCK_BYTES;
     const uint8_t* asrc = p.act + g * p.nb * Q_ACT_BLOCK;
     const int n_stages = (int)((p.nb + Q_STAGE_BLOCKS - 1) / Q_STAGE_BLOCKS);
-    auto issue = [&](int s) {  // lane 0 only
+    // stage s lives in slot (s % Q_WARPS) * Q_DEPTH + (s / Q_WARPS) % Q_DEPTH
+    auto slot_of = [&](int s) { return (s % Q_WARPS) * Q_DEPTH + (s / Q_WARPS) % Q_DEPTH; };
+    auto issue = [&](int s, bool weights, bool acts) {  // one lane of the owning warp
         const int64_t b0 = (int64_t)s * Q_STAGE_BLOCKS;
-        const uint32_t bytes = (uint32_t)(min((int64_t)Q_STAGE_BLOCKS, p.nb - b0) * Q_BLOCK_BYTES);
-        mbar_expect_tx(&bars[s % Q_STAGES], bytes);
-        bulk_g2s(ring + (s % Q_STAGES) * Q_STAGE_BYTES, wsrc + b0 * Q_BLOCK_BYTES, bytes, &bars[s % Q_STAGES]);
+        const uint32_t nblk = (uint32_t)min((int64_t)Q_STAGE_BLOCKS, p.nb - b0);
+        const int sl = slot_of(s);
+        uint8_t* dst = ring + sl * Q_RING_STAGE;
+        if (weights) {
+            mbar_expect_tx(&full[sl], nblk * (Q_BLOCK_BYTES + Q_ACT_BLOCK));
+            bulk_g2s(dst, wsrc + b0 * Q_BLOCK_BYTES, nblk * Q_BLOCK_BYTES, &full[sl]);
+        }
+        if (acts) bulk_g2s(dst + Q_STAGE_BYTES, asrc + b0 * Q_ACT_BLOCK, nblk * Q_ACT_BLOCK, &full[sl]);
     };
-    if (lane == 0) {
-        for (int s = 0; s < Q_STAGES; s++) mbar_init(&bars[s], 1);
+    if (tid == 0) {
+        for (int i = 0; i < Q_WARPS * Q_DEPTH; i++) mbar_init(&full[i], 1);
+        for (int i = 0; i < Q_WARPS; i++) mbar_init(&token[i], 1);
+        *fail_s = 0;
         mbar_fence_init();
-        for (int s = 0; s < Q_STAGES && s < n_stages; s++) issue(s);
     }
+    __syncthreads();
+    if (lane == 0)  // the weights do not depend on the launch before: start pulling them
+        for (int d = 0; d < Q_DEPTH; d++)
+            if (warp + d * Q_WARPS < n_stages) issue(warp + d * Q_WARPS, true, false);
+    grid_dependency_wait();  // the activation quantiser has finished
+    if (lane == 0)
+        for (int d = 0; d < Q_DEPTH; d++)
+            if (warp + d * Q_WARPS < n_stages) issue(warp + d * Q_WARPS, false, true);
     __syncwarp();
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};  // (row r, act 2c), (r, 2c + 1), (r + 8, 2c), (r + 8, 2c + 1)
-    bool failed = false;
-    for (int s = 0; s < n_stages && !failed; s++) {
+
+    for (int s = warp; s < n_stages; s += Q_WARPS) {
+        const int turn = s / Q_WARPS;  // how many stages this warp has had before
         const int64_t b0 = (int64_t)s * Q_STAGE_BLOCKS;
         const int nblk = (int)min((int64_t)Q_STAGE_BLOCKS, p.nb - b0);
-        // this stage's activation fragments come straight from L2 and do not depend on the accumulators: fetch them all first
-        uint32_t bq[Q_STAGE_BLOCKS][2];
+        const int sl = slot_of(s);
+        q40_wait(&full[sl], (uint32_t)((turn / Q_DEPTH) & 1), fail_s);
+        const uint8_t* st = ring + sl * Q_RING_STAGE;
+        // Three passes over the blocks of the stage, so that the loads, the MMAs and the conversions of different blocks overlap.
+        uint32_t af[Q_STAGE_BLOCKS][4], bf[Q_STAGE_BLOCKS][2];
         float2 asc[Q_STAGE_BLOCKS];
         int2 asum[Q_STAGE_BLOCKS];
+        float wsA[Q_STAGE_BLOCKS], wsB[Q_STAGE_BLOCKS];
 #pragma unroll
         for (int j = 0; j < Q_STAGE_BLOCKS; j++) {
-            if (j < nblk) {
-                const uint8_t* ab = asrc + (b0 + j) * Q_ACT_BLOCK;
-                bq[j][0] = __ldg((const uint32_t*)(ab + r * 16 + 4 * c));        // activation row r, elements 4c .. 4c+3
-                bq[j][1] = __ldg((const uint32_t*)(ab + 128 + r * 16 + 4 * c));  // elements 16 + 4c ..
-                asc[j] = __ldg((const float2*)(ab + 256) + c);
-                asum[j] = __ldg((const int2*)(ab + 288) + c);
-            }
+            const uint8_t* wb = st + j * Q_BLOCK_BYTES;
+            const uint8_t* ab = st + Q_STAGE_BYTES + j * Q_ACT_BLOCK;
+            // bytes 4c .. 4c+3 of a row's 16: low nibbles = elements 4c .. 4c+3, high nibbles = elements 16 + 4c ..
+            const uint32_t wa = *(const uint32_t*)(wb + r * 16 + 4 * c), wc = *(const uint32_t*)(wb + (r + 8) * 16 + 4 * c);
+            af[j][0] = wa & 0x0f0f0f0fu, af[j][1] = wc & 0x0f0f0f0fu, af[j][2] = (wa >> 4) & 0x0f0f0f0fu, af[j][3] = (wc >> 4) & 0x0f0f0f0fu;
+            bf[j][0] = *(const uint32_t*)(ab + r * 16 + 4 * c);        // activation row r, elements 4c .. 4c+3
+            bf[j][1] = *(const uint32_t*)(ab + 128 + r * 16 + 4 * c);  // elements 16 + 4c ..
+            asc[j] = *((const float2*)(ab + 256) + c);                 // scales of activation rows 2c, 2c + 1
+            asum[j] = *((const int2*)(ab + 288) + c);
+            wsA[j] = __half2float(*(const __half*)(wb + 256 + 2 * r)), wsB[j] = __half2float(*(const __half*)(wb + 256 + 2 * (r + 8)));
         }
-        if (!__all_sync(0xffffffffu, mbar_wait_bounded(&bars[s % Q_STAGES], (uint32_t)((s / Q_STAGES) & 1)))) {
-            failed = true;
-            break;
-        }
-        const uint8_t* st = ring + (s % Q_STAGES) * Q_STAGE_BYTES;
+        int d[Q_STAGE_BLOCKS][4];
 #pragma unroll
         for (int j = 0; j < Q_STAGE_BLOCKS; j++) {
-            if (j < nblk) {
-                const uint8_t* wb = st + j * Q_BLOCK_BYTES;
-                // bytes 4c .. 4c+3 of a row's 16: low nibbles = elements 4c .. 4c+3, high nibbles = elements 16 + 4c ..
-                const uint32_t wa = *(const uint32_t*)(wb + r * 16 + 4 * c), wc = *(const uint32_t*)(wb + (r + 8) * 16 + 4 * c);
-                const uint32_t a[4] = {wa & 0x0f0f0f0fu, wc & 0x0f0f0f0fu, (wa >> 4) & 0x0f0f0f0fu, (wc >> 4) & 0x0f0f0f0fu};
-                int d[4] = {0, 0, 0, 0};
-                mma_u8s8(d, a, bq[j][0], bq[j][1]);
-                const float wsA = __half2float(*(const __half*)(wb + 256 + 2 * r)), wsB = __half2float(*(const __half*)(wb + 256 + 2 * (r + 8)));
-                // (dot as f32) * w_scale * a_scale, then +=, each operation rounded on its own
-                acc[0] = __fadd_rn(acc[0], __fmul_rn(__fmul_rn((float)(d[0] - 8 * asum[j].x), wsA), asc[j].x));
-                acc[1] = __fadd_rn(acc[1], __fmul_rn(__fmul_rn((float)(d[1] - 8 * asum[j].y), wsA), asc[j].y));
-                acc[2] = __fadd_rn(acc[2], __fmul_rn(__fmul_rn((float)(d[2] - 8 * asum[j].x), wsB), asc[j].x));
-                acc[3] = __fadd_rn(acc[3], __fmul_rn(__fmul_rn((float)(d[3] - 8 * asum[j].y), wsB), asc[j].y));
+            d[j][0] = d[j][1] = d[j][2] = d[j][3] = 0;
+            mma_u8s8(d[j], af[j], bf[j][0], bf[j][1]);
+        }
+        float t[Q_STAGE_BLOCKS][4];  // (dot as f32) * w_scale * a_scale, each operation rounded on its own
+#pragma unroll
+        for (int j = 0; j < Q_STAGE_BLOCKS; j++) {
+            t[j][0] = __fmul_rn(__fmul_rn((float)(d[j][0] - 8 * asum[j].x), wsA[j]), asc[j].x);
+            t[j][1] = __fmul_rn(__fmul_rn((float)(d[j][1] - 8 * asum[j].y), wsA[j]), asc[j].y);
+            t[j][2] = __fmul_rn(__fmul_rn((float)(d[j][2] - 8 * asum[j].x), wsB[j]), asc[j].x);
+            t[j][3] = __fmul_rn(__fmul_rn((float)(d[j][3] - 8 * asum[j].y), wsB[j]), asc[j].y);
+        }
+        // the stage's bytes are in registers: refill the slot for this warp's stage after next
+        __syncwarp();
+        if (lane == 0 && s + Q_DEPTH * Q_WARPS < n_stages) issue(s + Q_DEPTH * Q_WARPS, true, true);
+        // ---- the ordered part: take the accumulators over, add this stage's blocks in order, hand them on ----
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);  // (row r, act 2c), (r, 2c + 1), (r + 8, 2c), (r + 8, 2c + 1)
+        if (s > 0) {
+            const int received = warp == 0 ? turn - 1 : turn;  // hand-offs this warp has taken before
+            q40_wait(&token[warp], (uint32_t)(received & 1), fail_s);
+            acc = hand[warp * 32 + lane];
+        }
+#pragma unroll
+        for (int j = 0; j < Q_STAGE_BLOCKS; j++) {
+            if (j < nblk) {  // the blocks of a short last stage hold stale bytes: leave them out
+                acc.x = __fadd_rn(acc.x, t[j][0]), acc.y = __fadd_rn(acc.y, t[j][1]);
+                acc.z = __fadd_rn(acc.z, t[j][2]), acc.w = __fadd_rn(acc.w, t[j][3]);
             }
         }
-        __syncwarp();  // every lane is done with the stage
-        if (lane == 0 && s + Q_STAGES < n_stages) issue(s + Q_STAGES);
+        if (s + 1 < n_stages) {
+            const int nw = (warp + 1) % Q_WARPS;
+            hand[nw * 32 + lane] = acc;
+            __syncwarp();
+            if (lane == 0) q40_arrive(&token[nw]);
+        } else {  // the last stage: this warp holds the result
+            if (*fail_s) acc = make_float4(__int_as_float(0x7fc00000), __int_as_float(0x7fc00000), __int_as_float(0x7fc00000), __int_as_float(0x7fc00000));
+            const int64_t row = tile * Q_TILE_ROWS + r, m0 = g * 8 + 2 * c;
+            if (row < p.n) {
+                if (m0 < p.m) p.out[m0 * p.out_stride + row] = acc.x;
+                if (m0 + 1 < p.m) p.out[(m0 + 1) * p.out_stride + row] = acc.y;
+            }
+            if (row + 8 < p.n) {
+                if (m0 < p.m) p.out[m0 * p.out_stride + row + 8] = acc.z;
+                if (m0 + 1 < p.m) p.out[(m0 + 1) * p.out_stride + row + 8] = acc.w;
+            }
+        }
     }
-    if (failed) {
-        if (lane == 0) atomicOr(p.status, STATUS_WAIT_EXPIRED);
+    __syncthreads();
+    if (*fail_s) {
+        if (tid == 0) atomicOr(p.status, STATUS_WAIT_EXPIRED);
         __nanosleep(200000);  // copies that may still be in flight land before the CTA's memory is released
-        acc[0] = acc[1] = acc[2] = acc[3] = __int_as_float(0x7fc00000);
-    }
-    const int64_t row = tile * Q_TILE_ROWS + r, m0 = g * 8 + 2 * c;
-    if (row < p.n) {
-        if (m0 < p.m) p.out[m0 * p.out_stride + row] = acc[0];
-        if (m0 + 1 < p.m) p.out[(m0 + 1) * p.out_stride + row] = acc[1];
-    }
-    if (row + 8 < p.n) {
-        if (m0 < p.m) p.out[m0 * p.out_stride + row + 8] = acc[2];
-        if (m0 + 1 < p.m) p.out[(m0 + 1) * p.out_stride + row + 8] = acc[3];
     }
 }
 
@@ -207,16 +275,30 @@ extern "C" int b200kv_q40_gemm(const void* packed, int64_t n, int64_t k, const v
     cudaStream_t stream = (cudaStream_t)stream_;
     const int64_t nb = k / QK, groups = (m + 7) / 8;
     uint8_t* act = (uint8_t*)scratch + Q_HEADER;
-    B200KV_CUDA(cudaMemsetAsync(scratch, 0, 4, stream));
     const int64_t warps = groups * nb * 8;
-    q40_quant_act_kernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, stream>>>(a, a_stride, m, dtype, nb, act);
+    q40_quant_act_kernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, stream>>>(a, a_stride, m, dtype, nb, act, (int*)scratch);
     B200KV_CUDA(cudaGetLastError());
     Q40Gemm p{};
     p.packed = (const uint8_t*)packed, p.act = act, p.out = out, p.status = (int*)scratch;
     p.n = n, p.nb = nb, p.out_stride = out_stride, p.m = m;
     dim3 grid((unsigned)((n + Q_TILE_ROWS - 1) / Q_TILE_ROWS), (unsigned)groups);
-    q40_gemm_kernel<<<grid, 32, 0, stream>>>(p);
-    B200KV_CUDA(cudaGetLastError());
+    // warps per tile: enough stages per warp (>= 4) that the start-up of a CTA is amortised
+    const int64_t n_stages = (nb + Q_STAGE_BLOCKS - 1) / Q_STAGE_BLOCKS;
+    const int tile_warps = n_stages >= 32 ? 8 : (n_stages >= 16 ? 4 : 2);
+    const size_t smem = (size_t)tile_warps * Q_DEPTH * Q_RING_STAGE + tile_warps * 32 * 16 + (tile_warps * Q_DEPTH + tile_warps) * 8 + 16;
+    static thread_local int attr_device = -1;  // the attribute is per device and sticks: set it once per (thread, device)
+    int cur = 0;
+    B200KV_CUDA(cudaGetDevice(&cur));
+    if (attr_device != cur) {
+        const size_t most = (size_t)8 * Q_DEPTH * Q_RING_STAGE + 8 * 32 * 16 + (8 * Q_DEPTH + 8) * 8 + 16;
+        B200KV_CUDA(cudaFuncSetAttribute(q40_gemm_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most));
+        B200KV_CUDA(cudaFuncSetAttribute(q40_gemm_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most));
+        B200KV_CUDA(cudaFuncSetAttribute(q40_gemm_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most));
+        attr_device = cur;
+    }
+    if (tile_warps == 8) B200KV_CUDA(launch_after_predecessor(q40_gemm_kernel<8>, grid, dim3(256), smem, stream, p));
+    else if (tile_warps == 4) B200KV_CUDA(launch_after_predecessor(q40_gemm_kernel<4>, grid, dim3(128), smem, stream, p));
+    else B200KV_CUDA(launch_after_predecessor(q40_gemm_kernel<2>, grid, dim3(64), smem, stream, p));
     return B200KV_OK;
 }
 
