@@ -209,6 +209,24 @@ int b200kv_q40_gemm(const void* packed, int64_t n, int64_t k, const void* a, int
 /* Synchronises `stream` and reports whether a bounded wait of the last GEMM that used `scratch` expired. */
 int b200kv_q40_check(const void* scratch, void* stream);
 
+/* ---- decoder glue between the linear layers and the attention ----
+ * RmsNorm over the last axis of [rows, d] (core/src/ops/nn/rms_norm.rs:28-66; kernel rms_norm_f32,
+ * linalg/src/generic/rms_norm.rs:7-18; replaces cuda/src/kernels/cu/nn.cu `rms_norm_*`): f32 arithmetic, result cast to `dtype`.
+ * `weight` ([d], type `dtype`, may be NULL) is the Mul that follows RmsNorm in the graph, fused.  Strides in elements. */
+int b200kv_rms_norm(const void* x, int64_t x_stride, const void* weight, void* out, int64_t out_stride, int64_t rows, int32_t d,
+                    float eps, int32_t dtype, void* stream);
+/* out = silu(gate) * up over n elements (up may be NULL: plain Silu).  Silu is x * sigmoid(x) with tract-linalg's generic
+ * rational sigmoid (linalg/src/generic/sigmoid.rs:11-45, silu.rs:26-30), bit for bit in f32; its result is rounded to `dtype`
+ * before the product, as the graph's Silu -> Mul does.  May run in place. */
+int b200kv_silu_mul(const void* gate, const void* up, void* out, int64_t n, int32_t dtype, void* stream);
+/* out = a + b over n elements (the residual connections; cuda/src/kernels/cu/binary.cu).  May run in place. */
+int b200kv_add(const void* a, const void* b, void* out, int64_t n, int32_t dtype, void* stream);
+/* out[r] = index of the first maximum of row r of the f32 matrix [rows, n] (ArgMax over the logits: greedy decoding). */
+int b200kv_argmax(const float* x, int64_t stride, int64_t rows, int32_t n, int32_t* out, void* stream);
+/* out[i] = table[ids[i]]: rows of row_bytes bytes (a multiple of 16); the embedding lookup (core Gather on axis 0). */
+int b200kv_gather_rows(const void* table, int64_t n_rows_table, int64_t row_bytes, const int32_t* ids, int64_t n_ids, void* out,
+                       void* stream);
+
 /* Per-launch timing, off by default.  When enabled, every kernel launched for this cache is bracketed by a
  * CUDA event pair on the caller's stream (what tract-cuda's TractCudaStream does for its profiler,
  * cuda/src/context.rs:364-453).  b200kv_profile_read waits for the recorded launches, returns up to

@@ -49,6 +49,9 @@ def lib():
         L.orc_q4_0_dequant.argtypes = [u16p, u8p, C.c_int64, fp]
         L.orc_w4a8_quantize_row.argtypes = [fp, C.c_int64, i8p, fp]
         L.orc_w4a8_gemm.argtypes = [u16p, u8p, C.c_int64, C.c_int64, fp, C.c_int64, fp, ip]
+        L.orc_rms_norm_f32.argtypes = [fp, C.c_int64, C.c_int64, C.c_float]
+        L.orc_ssigmoid.argtypes = [fp, C.c_int64, fp]
+        L.orc_silu_f32.argtypes = [fp, C.c_int64, fp]
         L.orc_kivi_new.restype = C.c_void_p
         L.orc_kivi_new.argtypes = [ip, ip, ip]
         L.orc_kivi_free.argtypes = [C.c_void_p]
@@ -173,6 +176,31 @@ def w4a8_gemm(scales: np.ndarray, packed: np.ndarray, a: np.ndarray, threads: in
     lib().orc_w4a8_gemm(_p(scales, C.c_uint16), _p(packed, C.c_uint8), n, k, _p(a, C.c_float), m, _p(out, C.c_float),
                         threads or hardware_threads())
     return out
+
+
+def rms_norm(x: np.ndarray, eps: float) -> np.ndarray:
+    """RmsNorm over the last axis (core/src/ops/nn/rms_norm.rs:28-66 with the generic rms_norm_f32 kernel): the
+    input is cast to f32, normalised, and cast back to its own type."""
+    dt = np.asarray(x).dtype
+    buf = np.ascontiguousarray(to_f32(x)).copy()
+    lib().orc_rms_norm_f32(_p(buf, C.c_float), buf.size // buf.shape[-1], buf.shape[-1], C.c_float(eps))
+    return buf if dt == np.float32 else buf.astype(dt)
+
+
+def ssigmoid(x: np.ndarray) -> np.ndarray:
+    x = np.ascontiguousarray(to_f32(x))
+    out = np.empty_like(x)
+    lib().orc_ssigmoid(_p(x, C.c_float), x.size, _p(out, C.c_float))
+    return out
+
+
+def silu(x: np.ndarray) -> np.ndarray:
+    """Silu with the generic kernels (linalg/src/generic/silu.rs:26-30, :48-56): f32 in f32; f16 through f32 and back."""
+    dt = np.asarray(x).dtype
+    xf = np.ascontiguousarray(to_f32(x))
+    out = np.empty_like(xf)
+    lib().orc_silu_f32(_p(xf, C.c_float), xf.size, _p(out, C.c_float))
+    return out if dt == np.float32 else out.astype(dt)
 
 
 # ---- a3 -------------------------------------------------------------------------------------------

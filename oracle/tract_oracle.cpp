@@ -582,6 +582,44 @@ void orc_w4a8_gemm(const uint16_t* scales, const uint8_t* packed, int64_t n, int
     });
 }
 
+// ---- decoder glue: generic tract-linalg kernels -------------------------------------------------------
+// rms_norm_f32 (linalg/src/generic/rms_norm.rs:7-18): left-to-right sum of squares, / n, + eps, sqrt, recip, scale.
+void orc_rms_norm_f32(float* buf, int64_t rows, int64_t d, float eps) {
+    for (int64_t r = 0; r < rows; r++) {
+        float* x = buf + r * d;
+        float sum_sq = 0.f;
+        for (int64_t i = 0; i < d; i++) sum_sq += x[i] * x[i];
+        const float inv_std = 1.0f / std::sqrt(sum_sq / (float)d + eps);
+        for (int64_t i = 0; i < d; i++) x[i] *= inv_std;
+    }
+}
+// ssigmoid (linalg/src/generic/sigmoid.rs:11-45)
+static inline float clamp_keep_nan(float x, float lo, float hi) { return x != x ? x : std::fmin(std::fmax(x, lo), hi); }
+static float ssigmoid(float x) {
+    x = clamp_keep_nan(x, -18.6f, 18.6f);
+    const float x2 = x * x;
+    float p = -4.433153405e-18f;
+    p = x2 * p + 1.169974371e-14f;
+    p = x2 * p + -1.875289645e-11f;
+    p = x2 * p + 4.257889523e-8f;
+    p = x2 * p + 0.00004811817576f;
+    p = x2 * p + 0.008163842030f;
+    p = x2 * p + 0.2499999971f;
+    p = p * x;
+    float q = 3.922935744e-6f;
+    q = x2 * q + 0.001524872358f;
+    q = x2 * q + 0.1159886749f;
+    q = x2 * q + 1.0f;
+    return clamp_keep_nan(p / q + 0.5f, 0.f, 1.f);
+}
+void orc_ssigmoid(const float* x, int64_t n, float* out) {
+    for (int64_t i = 0; i < n; i++) out[i] = ssigmoid(x[i]);
+}
+// SSiLU4::run (linalg/src/generic/silu.rs:26-30): x *= ssigmoid(x)
+void orc_silu_f32(const float* x, int64_t n, float* out) {
+    for (int64_t i = 0; i < n; i++) out[i] = x[i] * ssigmoid(x[i]);
+}
+
 int orc_hardware_threads() { return (int)std::thread::hardware_concurrency(); }
 
 }  // extern "C"

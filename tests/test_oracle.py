@@ -375,3 +375,27 @@ def test_w4a8_activation_quantiser_edges():
     assert sc[0, 0] == 1.0 and not q[0, :32].any()
     assert sc[0, 1] == np.float32(5.0) / np.float32(127.0) and q[0, 63] == 127 and q[0, 32] == round(-3 / (5 / 127))
     assert q[0, 64] == 0 and q[0, 65] == 127 and sc[0, 2] == np.float32(2.0) / np.float32(127.0)
+
+
+# ---- decoder glue: the reference's own known answers -----------------------------------------------------
+
+def test_rms_norm_known_answers():
+    # linalg/src/generic/rms_norm.rs:28-61
+    assert np.allclose(oracle.rms_norm(np.ones((1, 16), np.float32), 0.0), 1.0, atol=1e-5)
+    got = oracle.rms_norm(np.array([[1.0, 2.0, 3.0, 4.0]], np.float32), 0.0)
+    assert np.allclose(got, np.arange(1, 5, dtype=np.float32) / np.sqrt(np.float32(7.5)), atol=1e-5)
+    z = oracle.rms_norm(np.zeros((1, 4), np.float32), 1e-5)
+    assert np.isfinite(z).all() and not z.any()
+
+
+def test_ssigmoid_and_silu_properties():
+    # the rational fit stays within 2e-7 of the exact sigmoid, saturates to exactly 0 / 1, keeps NaN, and SiLU is x * sigmoid(x)
+    x = np.linspace(-30, 30, 4001, dtype=np.float32)
+    s = oracle.ssigmoid(x)
+    exact = 1.0 / (1.0 + np.exp(-x.astype(np.float64)))
+    assert np.abs(s - exact).max() < 2e-7
+    assert s.min() >= 0.0 and s.max() <= 1.0 and s[0] < 1e-7 and s[-1] > 1 - 1e-7
+    assert np.isnan(oracle.ssigmoid(np.array([np.nan], np.float32))[0])
+    assert np.array_equal(oracle.silu(x), x * s)
+    h = x.astype(np.float16)
+    assert np.array_equal(oracle.silu(h), (h.astype(np.float32) * oracle.ssigmoid(h.astype(np.float32))).astype(np.float16))

@@ -25,6 +25,7 @@ EXPORTS = [
     "b200kv_export_codes", "b200kv_truncate", "b200kv_fork", "b200kv_check", "b200kv_sdpa", "b200kv_profile",
     "b200kv_profile_read", "b200kv_attend_static_scratch", "b200kv_export_kivi", "b200kv_append_rope", "b200kv_rope",
     "b200kv_q40_packed_bytes", "b200kv_q40_pack", "b200kv_q40_scratch_bytes", "b200kv_q40_gemm", "b200kv_q40_check",
+    "b200kv_rms_norm", "b200kv_silu_mul", "b200kv_add", "b200kv_argmax", "b200kv_gather_rows",
 ]
 KERNEL_NAMES = {0: "table_scatter", 1: "append", 2: "decode", 3: "combine", 4: "export", 5: "sdpa_dense", 6: "prefill"}
 
@@ -302,6 +303,68 @@ class Q40Linear:
 
     def check(self):
         _ck(lib().b200kv_q40_check(C.c_void_p(self.scratch.data_ptr()), _stream()))
+
+
+def rms_norm(x, eps, weight=None, out=None):
+    """RmsNorm over the last axis of a 2-D CUDA tensor (rows contiguous), optionally times a weight vector."""
+    import torch
+
+    assert x.dim() == 2 and x.stride(1) == 1
+    if out is None:
+        out = torch.empty_like(x, memory_format=torch.contiguous_format)
+    with torch.cuda.device(x.device):
+        _ck(lib().b200kv_rms_norm(C.c_void_p(x.data_ptr()), C.c_int64(x.stride(0)), C.c_void_p(weight.data_ptr() if weight is not None else 0),
+                                  C.c_void_p(out.data_ptr()), C.c_int64(out.stride(0)), C.c_int64(x.shape[0]), int(x.shape[1]),
+                                  C.c_float(eps), _dtype_code(x), _stream()))
+    return out
+
+
+def silu_mul(gate, up=None, out=None):
+    import torch
+
+    assert gate.is_contiguous() and (up is None or up.is_contiguous())
+    if out is None:
+        out = torch.empty_like(gate)
+    with torch.cuda.device(gate.device):
+        _ck(lib().b200kv_silu_mul(C.c_void_p(gate.data_ptr()), C.c_void_p(up.data_ptr() if up is not None else 0), C.c_void_p(out.data_ptr()),
+                                  C.c_int64(gate.numel()), _dtype_code(gate), _stream()))
+    return out
+
+
+def add(a, b, out=None):
+    import torch
+
+    assert a.is_contiguous() and b.is_contiguous() and a.shape == b.shape
+    if out is None:
+        out = torch.empty_like(a)
+    with torch.cuda.device(a.device):
+        _ck(lib().b200kv_add(C.c_void_p(a.data_ptr()), C.c_void_p(b.data_ptr()), C.c_void_p(out.data_ptr()), C.c_int64(a.numel()),
+                             _dtype_code(a), _stream()))
+    return out
+
+
+def argmax(x, out=None):
+    import torch
+
+    assert x.dim() == 2 and x.dtype == torch.float32 and x.stride(1) == 1
+    if out is None:
+        out = torch.empty(x.shape[0], dtype=torch.int32, device=x.device)
+    with torch.cuda.device(x.device):
+        _ck(lib().b200kv_argmax(C.c_void_p(x.data_ptr()), C.c_int64(x.stride(0)), C.c_int64(x.shape[0]), int(x.shape[1]),
+                                C.c_void_p(out.data_ptr()), _stream()))
+    return out
+
+
+def gather_rows(table, ids, out=None):
+    import torch
+
+    assert table.dim() == 2 and table.is_contiguous() and ids.dtype == torch.int32
+    if out is None:
+        out = torch.empty((ids.numel(), table.shape[1]), dtype=table.dtype, device=table.device)
+    with torch.cuda.device(table.device):
+        _ck(lib().b200kv_gather_rows(C.c_void_p(table.data_ptr()), C.c_int64(table.shape[0]), C.c_int64(table.shape[1] * table.element_size()),
+                                     C.c_void_p(ids.data_ptr()), C.c_int64(ids.numel()), C.c_void_p(out.data_ptr()), _stream()))
+    return out
 
 
 def rope(x, cos, sin):

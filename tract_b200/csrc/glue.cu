@@ -1,0 +1,171 @@
+// The element-wise and row-wise ops that sit between the linear layers and the attention of a decoder block:
+// RmsNorm, SiLU(gate) * up, residual add, greedy argmax, embedding gather.  Small, HBM / launch bound.
+//
+//   RmsNorm   core/src/ops/nn/rms_norm.rs:28-66 -> tract-linalg rms_norm_f32 (generic: linalg/src/generic/rms_norm.rs:7-18):
+//             out_i = x_i * (1 / sqrt(mean(x^2) + eps)), f32 arithmetic whatever the tensor type; replaces
+//             cuda/src/kernels/cu/nn.cu `rms_norm_*`.  The sum of squares is a tree here and a left-to-right fold there:
+//             equal to the reference's own tolerance (1e-5), not bit for bit.  The optional weight is the Mul that follows
+//             RmsNorm in the graph, fused.
+//   SiLU      x * sigmoid(x) with tract-linalg's generic rational sigmoid (linalg/src/generic/sigmoid.rs:11-45, silu.rs:26-30),
+//             every operation rounded on its own, in the reference's order: bit for bit in f32.  The product with `up` is
+//             the Mul that follows in the graph (cu/element_wise.cu, cu/binary.cu).
+//   argmax    first index of the row maximum (core/src/ops/nn/reduce.rs ArgMax { last: false }).
+#include "internal.h"
+
+namespace b200kv {
+
+__device__ inline float clamp_keep_nan(float x, float lo, float hi) {  // f32::clamp: a NaN stays a NaN
+    return x != x ? x : fminf(fmaxf(x, lo), hi);
+}
+
+// linalg/src/generic/sigmoid.rs:11-45
+__device__ inline float ssigmoid(float x) {
+    x = clamp_keep_nan(x, -18.6f, 18.6f);
+    const float x2 = __fmul_rn(x, x);
+    float p = -4.433153405e-18f;
+    p = __fadd_rn(__fmul_rn(x2, p), 1.169974371e-14f);
+    p = __fadd_rn(__fmul_rn(x2, p), -1.875289645e-11f);
+    p = __fadd_rn(__fmul_rn(x2, p), 4.257889523e-8f);
+    p = __fadd_rn(__fmul_rn(x2, p), 0.00004811817576f);
+    p = __fadd_rn(__fmul_rn(x2, p), 0.008163842030f);
+    p = __fadd_rn(__fmul_rn(x2, p), 0.2499999971f);
+    p = __fmul_rn(p, x);
+    float q = 3.922935744e-6f;
+    q = __fadd_rn(__fmul_rn(x2, q), 0.001524872358f);
+    q = __fadd_rn(__fmul_rn(x2, q), 0.1159886749f);
+    q = __fadd_rn(__fmul_rn(x2, q), 1.0f);
+    return clamp_keep_nan(__fadd_rn(__fdiv_rn(p, q), 0.5f), 0.f, 1.f);
+}
+
+// One CTA per row.
+__global__ void rms_norm_kernel(const void* __restrict__ x, int64_t x_stride, const void* __restrict__ w, void* __restrict__ out,
+                                int64_t out_stride, int d, float eps, int dtype) {
+    __shared__ float part[32];
+    const int64_t row = blockIdx.x;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        const float v = ld_as_f32(x, dtype, row * x_stride + i);
+        ss = fmaf(v, v, ss);
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float t = threadIdx.x < (blockDim.x >> 5) ? part[threadIdx.x] : 0.f;
+#pragma unroll
+        for (int o = 16; o; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+        if (threadIdx.x == 0) part[0] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(t, (float)d), eps)));
+    }
+    __syncthreads();
+    const float inv = part[0];
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        float v = __fmul_rn(ld_as_f32(x, dtype, row * x_stride + i), inv);
+        if (w) v = __fmul_rn(round_to_dtype(v, dtype), ld_as_f32(w, dtype, i));  // RmsNorm's result is a tensor of `dtype` before the Mul
+        st_from_f32(out, dtype, row * out_stride + i, v);
+    }
+}
+
+__global__ void silu_mul_kernel(const void* __restrict__ gate, const void* __restrict__ up, void* __restrict__ out, int64_t n, int dtype) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float g = ld_as_f32(gate, dtype, i);
+    float s = round_to_dtype(__fmul_rn(g, ssigmoid(g)), dtype);  // Silu's output tensor
+    if (up) s = __fmul_rn(s, ld_as_f32(up, dtype, i));
+    st_from_f32(out, dtype, i, s);
+}
+
+__global__ void add_kernel(const void* __restrict__ a, const void* __restrict__ b, void* __restrict__ out, int64_t n, int dtype) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) st_from_f32(out, dtype, i, __fadd_rn(ld_as_f32(a, dtype, i), ld_as_f32(b, dtype, i)));
+}
+
+// One CTA per row; ties go to the smallest index; a NaN never wins (f32 partial order: `>` is false for it).
+__global__ void argmax_kernel(const float* __restrict__ x, int64_t stride, int n, int32_t* __restrict__ out) {
+    __shared__ float bv[32];
+    __shared__ int bi[32];
+    const float* row = x + (int64_t)blockIdx.x * stride;
+    float best = -INFINITY;
+    int idx = 0x7fffffff;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const float v = row[i];
+        if (v > best || (v == best && i < idx)) best = v, idx = i;
+    }
+    auto merge = [&](float ov, int oi) {
+        if (ov > best || (ov == best && oi < idx)) best = ov, idx = oi;
+    };
+#pragma unroll
+    for (int o = 16; o; o >>= 1) merge(__shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, idx, o));
+    if ((threadIdx.x & 31) == 0) bv[threadIdx.x >> 5] = best, bi[threadIdx.x >> 5] = idx;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        best = threadIdx.x < (blockDim.x >> 5) ? bv[threadIdx.x] : -INFINITY;
+        idx = threadIdx.x < (blockDim.x >> 5) ? bi[threadIdx.x] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o; o >>= 1) merge(__shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, idx, o));
+        if (threadIdx.x == 0) out[blockIdx.x] = idx == 0x7fffffff ? 0 : idx;  // a row of -inf / NaN only: index 0
+    }
+}
+
+__global__ void gather_rows_kernel(const uint8_t* __restrict__ table, const int32_t* __restrict__ ids, uint8_t* __restrict__ out,
+                                   int64_t row_bytes, int64_t n_rows_table) {
+    const int64_t r = blockIdx.x;
+    int64_t id = ids[r];
+    if (id < 0 || id >= n_rows_table) id = 0;
+    const uint4* src = (const uint4*)(table + id * row_bytes);
+    uint4* dst = (uint4*)(out + r * row_bytes);
+    for (int64_t i = threadIdx.x; i < row_bytes / 16; i += blockDim.x) dst[i] = src[i];
+}
+
+}  // namespace b200kv
+
+using namespace b200kv;
+
+static int check_dtype(int dtype) { return (dtype < B200KV_F32 || dtype > B200KV_BF16) ? fail("unknown dtype %d", dtype) : B200KV_OK; }
+
+extern "C" int b200kv_rms_norm(const void* x, int64_t x_stride, const void* weight, void* out, int64_t out_stride, int64_t rows, int32_t d,
+                               float eps, int32_t dtype, void* stream) {
+    if (!x || !out) return fail("null tensor");
+    if (rows <= 0 || d <= 0) return fail("rows and d must be positive");
+    if (check_dtype(dtype) != B200KV_OK) return B200KV_KO;
+    const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
+    rms_norm_kernel<<<(unsigned)rows, threads, 0, (cudaStream_t)stream>>>(x, x_stride, weight, out, out_stride, d, eps, dtype);
+    B200KV_CUDA(cudaGetLastError());
+    return B200KV_OK;
+}
+
+extern "C" int b200kv_silu_mul(const void* gate, const void* up, void* out, int64_t n, int32_t dtype, void* stream) {
+    if (!gate || !out) return fail("null tensor");
+    if (n <= 0) return fail("n must be positive");
+    if (check_dtype(dtype) != B200KV_OK) return B200KV_KO;
+    silu_mul_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(gate, up, out, n, dtype);
+    B200KV_CUDA(cudaGetLastError());
+    return B200KV_OK;
+}
+
+extern "C" int b200kv_add(const void* a, const void* b, void* out, int64_t n, int32_t dtype, void* stream) {
+    if (!a || !b || !out) return fail("null tensor");
+    if (n <= 0) return fail("n must be positive");
+    if (check_dtype(dtype) != B200KV_OK) return B200KV_KO;
+    add_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(a, b, out, n, dtype);
+    B200KV_CUDA(cudaGetLastError());
+    return B200KV_OK;
+}
+
+extern "C" int b200kv_argmax(const float* x, int64_t stride, int64_t rows, int32_t n, int32_t* out, void* stream) {
+    if (!x || !out) return fail("null tensor");
+    if (rows <= 0 || n <= 0) return fail("rows and n must be positive");
+    argmax_kernel<<<(unsigned)rows, 1024, 0, (cudaStream_t)stream>>>(x, stride, n, out);
+    B200KV_CUDA(cudaGetLastError());
+    return B200KV_OK;
+}
+
+extern "C" int b200kv_gather_rows(const void* table, int64_t n_rows_table, int64_t row_bytes, const int32_t* ids, int64_t n_ids, void* out,
+                                  void* stream) {
+    if (!table || !ids || !out) return fail("null tensor");
+    if (row_bytes <= 0 || row_bytes % 16 || (uintptr_t)table % 16 || (uintptr_t)out % 16) return fail("rows must be 16-byte multiples, 16-byte aligned");
+    if (n_ids <= 0) return fail("n_ids must be positive");
+    gather_rows_kernel<<<(unsigned)n_ids, 256, 0, (cudaStream_t)stream>>>((const uint8_t*)table, ids, (uint8_t*)out, row_bytes, n_rows_table);
+    B200KV_CUDA(cudaGetLastError());
+    return B200KV_OK;
+}
