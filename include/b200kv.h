@@ -227,6 +227,11 @@ int b200kv_argmax(const float* x, int64_t stride, int64_t rows, int32_t n, int32
 int b200kv_gather_rows(const void* table, int64_t n_rows_table, int64_t row_bytes, const int32_t* ids, int64_t n_ids, void* out,
                        void* stream);
 
+/* dst[r, c] = (dst_dtype) src[r, c] through f32 (core Cast; cuda/src/kernels/cu/array.cu `cast_*`): [rows, cols] windows of row-major
+ * matrices, strides in elements.  The same types both sides make it a strided copy. */
+int b200kv_cast(const void* src, int64_t src_stride, int32_t src_dtype, void* dst, int64_t dst_stride, int32_t dst_dtype,
+                int64_t rows, int64_t cols, void* stream);
+
 /* Per-launch timing, off by default.  When enabled, every kernel launched for this cache is bracketed by a
  * CUDA event pair on the caller's stream (what tract-cuda's TractCudaStream does for its profiler,
  * cuda/src/context.rs:364-453).  b200kv_profile_read waits for the recorded launches, returns up to

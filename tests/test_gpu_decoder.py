@@ -1,0 +1,86 @@
+"""The decode-loop driver on a small Llama-shaped model against the same block composed from the CPU restatements."""
+import numpy as np
+import pytest
+
+import oracle
+from util import rel_err
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+
+
+def split_blocks(blob):
+    """[n, k/32, 18] uint8 -> (scales uint16 [n, k/32], packed uint8 [n, k/2])"""
+    n, nb, _ = blob.shape
+    return np.ascontiguousarray(blob[:, :, :2]).view(np.uint16).reshape(n, nb), np.ascontiguousarray(blob[:, :, 2:]).reshape(n, nb * 16)
+
+
+class OracleDecoder:
+    def __init__(self, dec):
+        sh = dec.shape
+        self.sh, self.B = sh, dec.B
+        self.w = {k: split_blocks(v) for k, v in dec.host_blocks.items()}
+        self.norm = [(L["attn_norm"].cpu().numpy(), L["ffn_norm"].cpu().numpy()) for L in dec.layers]
+        self.final_norm = dec.final_norm.cpu().numpy()
+        self.embed = dec.embed.cpu().numpy()
+        self.cos, self.sin = dec.cos.cpu().numpy(), dec.sin.cpu().numpy()
+        self.K = [np.zeros((self.B, sh.n_kv_heads, 0, sh.head_dim), np.float16) for _ in dec.layers]
+        self.V = [np.zeros((self.B, sh.n_kv_heads, 0, sh.head_dim), np.float16) for _ in dec.layers]
+        self.pos = 0
+
+    def lin(self, name, a):
+        return oracle.w4a8_gemm(*self.w[name], a)
+
+    def step(self, tokens):
+        sh, B = self.sh, self.B
+        x = self.embed[tokens]
+        cos, sin = self.cos[self.pos][None, None, None, :], self.sin[self.pos][None, None, None, :]
+        nq, nk = sh.n_q_heads * sh.head_dim, sh.n_kv_heads * sh.head_dim
+        for i in range(sh.n_layers):
+            xn = oracle.rms_norm(x, sh.eps) * self.norm[i][0]
+            qkv = self.lin(f"l{i}.wqkv", xn)
+            q = qkv[:, :nq].astype(np.float16).reshape(B, sh.n_q_heads, 1, sh.head_dim)
+            k = qkv[:, nq:nq + nk].astype(np.float16).reshape(B, sh.n_kv_heads, 1, sh.head_dim)
+            v = qkv[:, nq + nk:].astype(np.float16).reshape(B, sh.n_kv_heads, 1, sh.head_dim)
+            q, k = oracle.apply_rope(q, cos, sin), oracle.apply_rope(k, cos, sin)
+            self.K[i], self.V[i] = np.concatenate([self.K[i], k], 2), np.concatenate([self.V[i], v], 2)
+            attn = oracle.flash_sdpa(q, self.K[i], self.V[i], causal=True).astype(np.float32).reshape(B, nq)
+            x = x + self.lin(f"l{i}.wo", attn)
+            xn = oracle.rms_norm(x, sh.eps) * self.norm[i][1]
+            act = oracle.silu(self.lin(f"l{i}.wg", xn)) * self.lin(f"l{i}.wu", xn)
+            x = x + self.lin(f"l{i}.wd", act)
+        logits = self.lin("lm_head", oracle.rms_norm(x, sh.eps) * self.final_norm)
+        self.pos += 1
+        return logits
+
+
+@pytest.mark.parametrize("use_graphs", [False, True])
+def test_decoder_steps_match_oracle_composition(use_graphs):
+    from tract_b200.decoder import Decoder, Shape
+
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device")
+    sh = Shape(hidden=256, n_layers=2, n_q_heads=4, n_kv_heads=2, head_dim=128, ffn=512, vocab=640, rope_theta=10000.0)
+    dec = Decoder(sh, n_seqs=3, max_tokens=64, kv_format="f16", seed=5, use_graphs=use_graphs)
+    ref = OracleDecoder(dec)
+    tokens = np.array([1, 17, 400], np.int32)
+    dec.set_tokens(tokens)
+    for step in range(6):
+        want = ref.step(tokens)
+        dec.step()
+        got = dec.logits.cpu().numpy()
+        # Every op is held to its own bar elsewhere; composed, the int8 activation quantiser of the W4A8 layers is a step
+        # function: where the 16-bit attention output differs from the oracle's by an ulp, a few per cent of the
+        # activation codes of the next layer change by 1 and its outputs move by ~0.5 %.  The first step has one key
+        # per sequence (attention returns V itself) and must agree to f32 rounding; later steps are held to a mean and
+        # a maximum that a wiring mistake (wrong position, wrong cache, wrong slice: O(1) errors) cannot meet.
+        rms = np.sqrt((want ** 2).mean())
+        mean_err, max_err = np.abs(got - want).mean() / rms, rel_err(got, want)
+        assert (mean_err <= 1e-5 and max_err <= 1e-4) if step == 0 else (mean_err <= 2e-2 and max_err <= 0.15), (step, mean_err, max_err)
+        tokens = dec.tokens.cpu().numpy().astype(np.int32)
+        margin = np.sort(want, axis=1)[:, -1] - np.sort(want, axis=1)[:, -2]
+        clear = margin > 0.1 * np.abs(want).max()
+        assert np.array_equal(tokens[clear], want.argmax(1).astype(np.int32)[clear])  # greedy choice, where it is not a near tie
+    dec.check()
+    dec.close()

@@ -25,7 +25,7 @@ EXPORTS = [
     "b200kv_export_codes", "b200kv_truncate", "b200kv_fork", "b200kv_check", "b200kv_sdpa", "b200kv_profile",
     "b200kv_profile_read", "b200kv_attend_static_scratch", "b200kv_export_kivi", "b200kv_append_rope", "b200kv_rope",
     "b200kv_q40_packed_bytes", "b200kv_q40_pack", "b200kv_q40_scratch_bytes", "b200kv_q40_gemm", "b200kv_q40_check",
-    "b200kv_rms_norm", "b200kv_silu_mul", "b200kv_add", "b200kv_argmax", "b200kv_gather_rows",
+    "b200kv_rms_norm", "b200kv_silu_mul", "b200kv_add", "b200kv_argmax", "b200kv_gather_rows", "b200kv_cast",
 ]
 KERNEL_NAMES = {0: "table_scatter", 1: "append", 2: "decode", 3: "combine", 4: "export", 5: "sdpa_dense", 6: "prefill"}
 
@@ -367,11 +367,23 @@ def gather_rows(table, ids, out=None):
     return out
 
 
-def rope(x, cos, sin):
+def cast(src, dst):
+    """dst[...] = src[...] converted through f32; 2-D windows (last axis contiguous) of CUDA tensors of equal shape."""
+    import torch
+
+    assert src.dim() == 2 and dst.shape == src.shape and src.stride(1) == 1 and dst.stride(1) == 1
+    with torch.cuda.device(src.device):
+        _ck(lib().b200kv_cast(C.c_void_p(src.data_ptr()), C.c_int64(src.stride(0)), _dtype_code(src), C.c_void_p(dst.data_ptr()),
+                              C.c_int64(dst.stride(0)), _dtype_code(dst), C.c_int64(src.shape[0]), C.c_int64(src.shape[1]), _stream()))
+    return dst
+
+
+def rope(x, cos, sin, out=None):
     """ApplyRope on a [B, H, S, D] tensor; cos / sin: [B or 1, S, D]."""
     import torch
 
-    out = torch.empty_like(x, memory_format=torch.contiguous_format)
+    if out is None:
+        out = torch.empty_like(x, memory_format=torch.contiguous_format)
     rs = (C.c_int64 * 2)(0 if cos.shape[0] == 1 else cos.stride(0), cos.stride(1))
     with torch.cuda.device(x.device):
         _ck(lib().b200kv_rope(x.data_ptr(), _strides(x, 3), cos.data_ptr(), sin.data_ptr(), rs, out.data_ptr(), _strides(out, 3),

@@ -117,6 +117,14 @@ __global__ void gather_rows_kernel(const uint8_t* __restrict__ table, const int3
     for (int64_t i = threadIdx.x; i < row_bytes / 16; i += blockDim.x) dst[i] = src[i];
 }
 
+__global__ void cast2d_kernel(const void* __restrict__ src, int64_t src_stride, int src_dtype, void* __restrict__ dst, int64_t dst_stride,
+                              int dst_dtype, int64_t rows, int64_t cols) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= rows * cols) return;
+    const int64_t r = i / cols, c = i % cols;
+    st_from_f32(dst, dst_dtype, r * dst_stride + c, ld_as_f32(src, src_dtype, r * src_stride + c));
+}
+
 }  // namespace b200kv
 
 using namespace b200kv;
@@ -166,6 +174,17 @@ extern "C" int b200kv_gather_rows(const void* table, int64_t n_rows_table, int64
     if (row_bytes <= 0 || row_bytes % 16 || (uintptr_t)table % 16 || (uintptr_t)out % 16) return fail("rows must be 16-byte multiples, 16-byte aligned");
     if (n_ids <= 0) return fail("n_ids must be positive");
     gather_rows_kernel<<<(unsigned)n_ids, 256, 0, (cudaStream_t)stream>>>((const uint8_t*)table, ids, (uint8_t*)out, row_bytes, n_rows_table);
+    B200KV_CUDA(cudaGetLastError());
+    return B200KV_OK;
+}
+
+extern "C" int b200kv_cast(const void* src, int64_t src_stride, int32_t src_dtype, void* dst, int64_t dst_stride, int32_t dst_dtype,
+                           int64_t rows, int64_t cols, void* stream) {
+    if (!src || !dst) return fail("null tensor");
+    if (rows <= 0 || cols <= 0) return fail("rows and cols must be positive");
+    if (check_dtype(src_dtype) != B200KV_OK || check_dtype(dst_dtype) != B200KV_OK) return B200KV_KO;
+    const int64_t n = rows * cols;
+    cast2d_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(src, src_stride, src_dtype, dst, dst_stride, dst_dtype, rows, cols);
     B200KV_CUDA(cudaGetLastError());
     return B200KV_OK;
 }
