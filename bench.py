@@ -574,6 +574,108 @@ def run_linear(args, rank, world):
         dist.destroy_process_group()
 
 
+DECODER = {
+    # BASELINE config 5: the Llama-3-8B shape, Q4_0 weights from a seed, 8 sequences per GPU (64 over 8 GPUs), caches at
+    # 2048 tokens (filled with synthetic K / V: the prompt pass needs the large-M GEMM, which is not built), greedy steps
+    "cfg5-decoder": dict(past=2048, seqs=8, kv="f16", desc="32-layer Llama-3-8B-shaped decoder, Q4_0 weights, f16 KV cache, 8 sequences x 2048 cached tokens, greedy decode"),
+    "cfg5-decoder-q8kv": dict(past=2048, seqs=8, kv="q8_1", desc="the same with the int8 block-32 KV cache"),
+}
+
+
+def run_decoder(args, rank, world):
+    import torch
+    import torch.distributed as dist
+    from tract_b200.decoder import Decoder, Shape
+
+    wl = DECODER[args.workload]
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0)))
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    sh = Shape()
+    B, past = args.seqs or wl["seqs"], args.past or wl["past"]
+    dec = Decoder(sh, n_seqs=B, max_tokens=past + args.steps + max(args.warmup, 3) + 64, kv_format=wl["kv"], seed=100 + rank, device=dev)
+    dec.prefill_synthetic(past)
+    tok_host = torch.randint(0, sh.vocab, (B,), dtype=torch.int32).pin_memory()
+    out_host = torch.empty(B, dtype=torch.int32).pin_memory()
+    dec.set_tokens(tok_host)
+
+    def step():
+        dec.step()
+
+    def step_e2e():
+        dec.tokens.copy_(tok_host, non_blocking=True)
+        dec.step()
+        out_host.copy_(dec.tokens, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    def timed(fn, steps):
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    sampler = ClockSampler(dev.index or 0)
+    if rank == 0:
+        sampler.start()
+    for _ in range(max(args.warmup, 3)):
+        step()
+    sampler.mark()
+    n_e2e = max(2, args.steps // 4)
+    ms = timed(step, args.steps - n_e2e) / (args.steps - n_e2e)
+    clocks = sampler.stop() if rank == 0 else None
+    ms_e2e = timed(step_e2e, n_e2e) / n_e2e
+    # the hot-path share: one layer's cache kernels, timed by the library's own event pairs
+    c0 = dec.layers[0]["cache"]
+    c0.profile(True)
+    torch.cuda.synchronize()
+    dec.step()
+    recs = dict()
+    for name, t in c0.profile_read():
+        recs.setdefault(name, []).append(t)
+    c0.profile(False)
+    dec.check()
+    weight_bytes = sum(L[k].packed.numel() for L in dec.layers for k in ("wqkv", "wo", "wg", "wu", "wd")) + dec.lm_head.packed.numel()
+    kv_bytes = sh.n_layers * B * (past + args.steps // 2) * sh.n_kv_heads * sh.head_dim * 2 * (2 if wl["kv"] == "f16" else 1.0625)
+    pk, pk_kind = peaks()
+    if rank == 0:
+        line = {
+            "metric": "decode tokens/s of the full decoder (sum over GPUs)", "value": world * B / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "Q4_0 weights x int8 activations, f32 residual stream, 16-bit attention", "data": "synthetic",
+            "config": {"workload": args.workload, "description": wl["desc"], "sequences_per_gpu": B, "cached_tokens": past,
+                       "layers": sh.n_layers, "hidden": sh.hidden, "ffn": sh.ffn, "vocab": sh.vocab, "vocab_note": "assumed (not given by the config)",
+                       "parallelism": f"by-sequence x{world}, no collective", "l2": "weights (4.2 GB) and caches exceed L2",
+                       "weight_bytes_per_step": weight_bytes, "kv_bytes_per_step": kv_bytes,
+                       "launch": "CUDA-graph segments between cache calls; cache calls from the host"},
+            "e2e": {"value": world * B / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": B * 4, "d2h_bytes_per_step": B * 4,
+                    "ms_per_step": ms_e2e},
+            "gpu_launches": sh.n_layers * 26 + 8,
+            "kernels_ms": {k: statistics.mean(v) for k, v in recs.items()},
+            "roofline": {"bound": "hbm", "kernel": "whole step (Q4_0 GEMMs dominate)", "achieved": (weight_bytes + kv_bytes) / (ms * 1e-3) / 1e9,
+                         "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": (weight_bytes + kv_bytes) / (ms * 1e-3) / 1e9 / pk["hbm_gbs"],
+                         "peak_kind": pk_kind, "traffic": None, "algorithmic_bytes": weight_bytes + kv_bytes},
+            "clocks": clocks,
+        }
+        print(json.dumps(line))
+    dec.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def cpu_step_factory(workload, sample_seqs, sample_past, threads):
     """Returns (step_fn, bytes_per_step): one decode step of `sample_seqs` sequences on the CPU:
     quantise the new token, dequantise the whole cache (what QuantizedDynKvCacheState::eval does every
@@ -672,7 +774,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=1000)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="cfg4-q8", choices=sorted(WORKLOADS) + sorted(PREFILL) + sorted(LINEAR))
+    ap.add_argument("--workload", default="cfg4-q8", choices=sorted(WORKLOADS) + sorted(PREFILL) + sorted(LINEAR) + sorted(DECODER))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--quick", action="store_true", help="profiler runs: exactly W warm-up steps, no 1 s warm-up floor")
@@ -690,6 +792,11 @@ def main():
         return
     if args.workload in LINEAR:
         run_linear(args, rank, world)
+        return
+    if args.workload in DECODER:
+        if args.steps > 256:
+            args.steps = 64  # the default step count is sized for the attention-only workloads
+        run_decoder(args, rank, world)
         return
     if args.workload in PREFILL:
         r = run_prefill(args, rank, world)

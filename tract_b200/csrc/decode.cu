@@ -414,8 +414,11 @@ int launch_decode(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t 
         if (len <= 0) return fail("sequence %d is empty: nothing to attend to", seqs[i]);
         total_pages += (len + PAGE_TOKENS - 1) / PAGE_TOKENS;
     }
-    const int64_t target_ctas = 148 * 16;
-    const int64_t chunk = std::max<int64_t>(1, (total_pages * Hkv * nz + target_ctas - 1) / target_ctas);
+    // Pages per split.  Large launches: 16 CTAs per SM over the run, so that the tail is short.  Small launches would get
+    // one page per CTA that way, several waves of CTAs that are all set-up: they fill one wave (3 CTAs per SM) with up to
+    // 8 pages per split instead, and stay at 8 pages until the large-launch rule asks for more.
+    const int64_t work = total_pages * Hkv * nz, target_ctas = 148 * 16, one_wave = 148 * 3;
+    const int64_t chunk = std::max<int64_t>((work + target_ctas - 1) / target_ctas, std::min<int64_t>((work + one_wave - 1) / one_wave, 8));
     // one entry per sequence: {table row, length, first work item, splits}; the work items follow from it
     InlineBatch ib{};
     std::vector<int4> ent((size_t)n_seqs);
