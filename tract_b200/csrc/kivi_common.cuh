@@ -31,6 +31,9 @@ __device__ inline uint32_t kivi_code_offset(int bits, int stream, int slot, int 
     return chunk_addr(fmt, 128, stream, slot, code_pos(fmt, 128, stream, c));
 }
 
+// lo + code * scale, multiply then add (quant_dyn_kv_cache.rs:141-146, :231-240)
+__device__ inline float kivi_dequant(uint32_t code, float lo, float scale) { return __fadd_rn(lo, __fmul_rn((float)code, scale)); }
+
 KiviView kivi_view(const b200kv_cache* c);
 
 }  // namespace b200kv

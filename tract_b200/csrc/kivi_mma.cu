@@ -17,11 +17,12 @@
 //           weight meet the value itself and not its distance from lo_t, which an outlier in the row makes large;
 // A CTA walks a run of 64-token pages of one (sequence, kv head); the four arrays of a page (K codes, V codes,
 // K parameters, V parameters) arrive by cp.async.bulk into one stage of a ring.  Sinks, the f32 residual block and
-// the value tokens that go with it are left to the CUDA-core kernel, which publishes them as one more partial.
+// the value tokens that go with it are left to the CUDA-core formulation (kivi_simt.cuh), run by a few extra CTAs of
+// the same grid, which publish them as one more partial per sequence.
 #include <algorithm>
 
 #include "decode_common.h"
-#include "kivi_common.cuh"
+#include "kivi_simt.cuh"
 #include "mma_common.cuh"
 
 namespace b200kv {
@@ -56,6 +57,7 @@ struct KiviMmaParams {
     float* part_ml;
     int* status;
     int32_t G, dtype, n_splits, part_stride, part_off;
+    int32_t n_mma_ctas;  // blockIdx.x below this: tensor-core work; from it on: the f32 tiles, one CTA per (sequence, group of 4 heads)
     float scale;
 };
 
@@ -72,9 +74,11 @@ __global__ void __launch_bounds__(128, KGeo<BITS>::CTAS) kivi_mma_kernel(KiviMma
     uint64_t* bars = (uint64_t*)(bias_s + 2 * 2 * 2 * 8);
 
     const KiviView& v = p.v;
+    const int kvh_simt = blockIdx.y;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int r = lane >> 2, c = lane & 3;
-    const int b = blockIdx.x / p.n_splits, split = blockIdx.x % p.n_splits;
+    const int bxm = min((int)blockIdx.x, p.n_mma_ctas - 1);  // the extra CTAs (f32 tiles) branch off below; keep their indices in range
+    const int b = bxm / p.n_splits, split = bxm % p.n_splits;
     const int kvh = blockIdx.y, g0 = blockIdx.z * 8, ng = min(8, p.G - g0);
     const int32_t seq = ib.ent[b].x;
     const int len = ib.ent[b].y;
@@ -100,6 +104,15 @@ __global__ void __launch_bounds__(128, KGeo<BITS>::CTAS) kivi_mma_kernel(KiviMma
     };
     grid_dependency_wait();    // the append that precedes this launch has written its pages
     grid_launch_dependents();
+    if ((int)blockIdx.x >= p.n_mma_ctas) {  // CTA-uniform: sinks + residual block of one sequence on the CUDA cores
+        if (blockIdx.z != 0) return;
+        KiviDecode d;
+        d.v = p.v, d.q = p.q, d.qb = p.qb, d.qh = p.qh, d.part_o = p.part_o, d.part_ml = p.part_ml;
+        d.G = p.G, d.dtype = p.dtype, d.n_splits = 1, d.f32_only = 1, d.part_stride = p.part_stride, d.part_off = 0, d.scale = p.scale;
+        const int nzs = (p.G + KGT - 1) / KGT, e = (int)blockIdx.x - p.n_mma_ctas;
+        kivi_simt_body<KM_D>(d, ib, *reinterpret_cast<KiviSimtSmem<KM_D>*>(stages), e / nzs, kvh_simt, e % nzs);
+        return;
+    }
     if (tid == 0) {
         for (int s = 0; s < KM_NS; s++) mbar_init(&bars[s], 1);
         mbar_fence_init();
@@ -352,8 +365,9 @@ int launch_kivi_mma(b200kv_cache* c, const void* q, const int64_t* qs, int n_seq
     p.q = q, p.qb = qs[0], p.qh = qs[1];
     p.part_o = part_o, p.part_ml = part_ml, p.status = c->d_status;
     p.G = G, p.dtype = dtype, p.n_splits = n_splits, p.part_stride = n_splits + 1, p.part_off = 1;
+    p.n_mma_ctas = n_seqs * n_splits;
     p.scale = scale;
-    dim3 grid(n_seqs * n_splits, c->cfg.n_kv_heads, (G + 7) / 8);
+    dim3 grid(n_seqs * n_splits + n_seqs * ((G + KGT - 1) / KGT), c->cfg.n_kv_heads, (G + 7) / 8);
     // ring (reused by the warp merge, 17 KB), q' fragments and q . lo, barriers
     if (c->kivi.bits == 8) {
         const size_t smem = (size_t)KGeo<8>::NS * KGeo<8>::STAGE + KM_PARAMS + 64;

@@ -24,7 +24,6 @@
 // CTA flags the status word, lets every role run to the end of its loop without waiting any more, frees its
 // TMEM and returns.
 #include <cmath>
-#include <cstdlib>
 
 #include "internal.h"
 
@@ -565,7 +564,6 @@ int launch_prefill_tc(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int3
     p.v_lbo = 8192, p.v_sbo = 1024;
     p.scale = scale;
     p.skip_fraction = P_SKIP_FRACTION;
-    if (const char* e = getenv("B200KV_PREFILL_SKIP")) p.skip_fraction = (float)atof(e);
     // double tiles (one CTA per SM, K/V staged once for 2 x 128 rows) when they still fill the GPU
     const int qpt = PM / G;
     const int64_t double_ctas = (int64_t)((n_new + 2 * qpt - 1) / (2 * qpt)) * c->L.Hkv * n_seqs;
