@@ -118,17 +118,21 @@ __device__ inline void q40_arrive(uint64_t* bar) {
 // it computes the 8 x (16 x 8) contributions of its stage on its own, then receives the running accumulators from the
 // warp that had stage s - 1, adds its contributions in block order and hands the accumulators on.  Only that short
 // hand-off is serial; it keeps the additions in the order of the reference.
-template <int Q_WARPS>
-__global__ void __launch_bounds__(Q_WARPS * 32, 2) q40_gemm_kernel(Q40Gemm p) {
+// MG > 1 (more than 8 activation rows): a CTA keeps each weight stage for MG groups of 8 rows; every group has its own
+// chain of hand-offs, so the warps work as a wavefront over (stage, group).
+template <int Q_WARPS, int MG>
+__global__ void __launch_bounds__(Q_WARPS * 32, MG == 1 ? 2 : 1) q40_gemm_kernel(Q40Gemm p) {
+    constexpr int STAGE = Q_STAGE_BYTES + MG * Q_STAGE_BLOCKS * Q_ACT_BLOCK;  // weights, then the activations of each group
     extern __shared__ __align__(128) uint8_t ring[];                      // Q_WARPS * Q_DEPTH stages; warp w owns slots w * Q_DEPTH ..
-    float4* hand = (float4*)(ring + Q_WARPS * Q_DEPTH * Q_RING_STAGE);    // [Q_WARPS][32 lanes]: accumulators on their way to warp w
-    uint64_t* full = (uint64_t*)(hand + Q_WARPS * 32);                    // [Q_WARPS * Q_DEPTH] bytes landed
-    uint64_t* token = full + Q_WARPS * Q_DEPTH;                           // [Q_WARPS] accumulators handed to warp w
-    volatile int* fail_s = (volatile int*)(token + Q_WARPS);
+    float4* hand = (float4*)(ring + Q_WARPS * Q_DEPTH * STAGE);           // [Q_WARPS][MG][32 lanes]: accumulators on their way to warp w
+    uint64_t* full = (uint64_t*)(hand + Q_WARPS * MG * 32);               // [Q_WARPS * Q_DEPTH] bytes landed
+    uint64_t* token = full + Q_WARPS * Q_DEPTH;                           // [Q_WARPS][MG] accumulators handed to warp w
+    volatile int* fail_s = (volatile int*)(token + Q_WARPS * MG);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, r = lane >> 2, c = lane & 3;
-    const int64_t tile = blockIdx.x, g = blockIdx.y;
+    const int64_t tile = blockIdx.x, g0 = (int64_t)blockIdx.y * MG;
+    const int ng = (int)min((int64_t)MG, (p.m + 7) / 8 - g0);             // groups of 8 activation rows this CTA has
     const uint8_t* wsrc = p.packed + tile * p.nb * Q_BLOCK_BYTES;
-    const uint8_t* asrc = p.act + g * p.nb * Q_ACT_BLOCK;
+    const uint8_t* asrc = p.act + g0 * p.nb * Q_ACT_BLOCK;
     const int n_stages = (int)((p.nb + Q_STAGE_BLOCKS - 1) / Q_STAGE_BLOCKS);
     // stage s lives in slot (s % Q_WARPS) * Q_DEPTH + (s / Q_WARPS) % Q_DEPTH
     auto slot_of = [&](int s) { return (s % Q_WARPS) * Q_DEPTH + (s / Q_WARPS) % Q_DEPTH; };
@@ -136,16 +140,19 @@ __global__ void __launch_bounds__(Q_WARPS * 32, 2) q40_gemm_kernel(Q40Gemm p) {
         const int64_t b0 = (int64_t)s * Q_STAGE_BLOCKS;
         const uint32_t nblk = (uint32_t)min((int64_t)Q_STAGE_BLOCKS, p.nb - b0);
         const int sl = slot_of(s);
-        uint8_t* dst = ring + sl * Q_RING_STAGE;
+        uint8_t* dst = ring + sl * STAGE;
         if (weights) {
-            mbar_expect_tx(&full[sl], nblk * (Q_BLOCK_BYTES + Q_ACT_BLOCK));
+            mbar_expect_tx(&full[sl], nblk * (Q_BLOCK_BYTES + ng * Q_ACT_BLOCK));
             bulk_g2s(dst, wsrc + b0 * Q_BLOCK_BYTES, nblk * Q_BLOCK_BYTES, &full[sl]);
         }
-        if (acts) bulk_g2s(dst + Q_STAGE_BYTES, asrc + b0 * Q_ACT_BLOCK, nblk * Q_ACT_BLOCK, &full[sl]);
+        if (acts)
+            for (int gi = 0; gi < ng; gi++)
+                bulk_g2s(dst + Q_STAGE_BYTES + gi * Q_STAGE_BLOCKS * Q_ACT_BLOCK, asrc + (gi * p.nb + b0) * Q_ACT_BLOCK, nblk * Q_ACT_BLOCK,
+                         &full[sl]);
     };
     if (tid == 0) {
         for (int i = 0; i < Q_WARPS * Q_DEPTH; i++) mbar_init(&full[i], 1);
-        for (int i = 0; i < Q_WARPS; i++) mbar_init(&token[i], 1);
+        for (int i = 0; i < Q_WARPS * MG; i++) mbar_init(&token[i], 1);
         *fail_s = 0;
         mbar_fence_init();
     }
@@ -165,71 +172,79 @@ __global__ void __launch_bounds__(Q_WARPS * 32, 2) q40_gemm_kernel(Q40Gemm p) {
         const int nblk = (int)min((int64_t)Q_STAGE_BLOCKS, p.nb - b0);
         const int sl = slot_of(s);
         q40_wait(&full[sl], (uint32_t)((turn / Q_DEPTH) & 1), fail_s);
-        const uint8_t* st = ring + sl * Q_RING_STAGE;
-        // Three passes over the blocks of the stage, so that the loads, the MMAs and the conversions of different blocks overlap.
-        uint32_t af[Q_STAGE_BLOCKS][4], bf[Q_STAGE_BLOCKS][2];
-        float2 asc[Q_STAGE_BLOCKS];
-        int2 asum[Q_STAGE_BLOCKS];
+        const uint8_t* st = ring + sl * STAGE;
+        // Passes over the blocks of the stage, so that the loads, the MMAs and the conversions of different blocks overlap.
+        uint32_t af[Q_STAGE_BLOCKS][4];
         float wsA[Q_STAGE_BLOCKS], wsB[Q_STAGE_BLOCKS];
 #pragma unroll
         for (int j = 0; j < Q_STAGE_BLOCKS; j++) {
             const uint8_t* wb = st + j * Q_BLOCK_BYTES;
-            const uint8_t* ab = st + Q_STAGE_BYTES + j * Q_ACT_BLOCK;
             // bytes 4c .. 4c+3 of a row's 16: low nibbles = elements 4c .. 4c+3, high nibbles = elements 16 + 4c ..
             const uint32_t wa = *(const uint32_t*)(wb + r * 16 + 4 * c), wc = *(const uint32_t*)(wb + (r + 8) * 16 + 4 * c);
             af[j][0] = wa & 0x0f0f0f0fu, af[j][1] = wc & 0x0f0f0f0fu, af[j][2] = (wa >> 4) & 0x0f0f0f0fu, af[j][3] = (wc >> 4) & 0x0f0f0f0fu;
-            bf[j][0] = *(const uint32_t*)(ab + r * 16 + 4 * c);        // activation row r, elements 4c .. 4c+3
-            bf[j][1] = *(const uint32_t*)(ab + 128 + r * 16 + 4 * c);  // elements 16 + 4c ..
-            asc[j] = *((const float2*)(ab + 256) + c);                 // scales of activation rows 2c, 2c + 1
-            asum[j] = *((const int2*)(ab + 288) + c);
             wsA[j] = __half2float(*(const __half*)(wb + 256 + 2 * r)), wsB[j] = __half2float(*(const __half*)(wb + 256 + 2 * (r + 8)));
         }
-        int d[Q_STAGE_BLOCKS][4];
+#pragma unroll 1
+        for (int gi = 0; gi < ng; gi++) {
+            uint32_t bf[Q_STAGE_BLOCKS][2];
+            float2 asc[Q_STAGE_BLOCKS];
+            int2 asum[Q_STAGE_BLOCKS];
 #pragma unroll
-        for (int j = 0; j < Q_STAGE_BLOCKS; j++) {
-            d[j][0] = d[j][1] = d[j][2] = d[j][3] = 0;
-            mma_u8s8(d[j], af[j], bf[j][0], bf[j][1]);
-        }
-        float t[Q_STAGE_BLOCKS][4];  // (dot as f32) * w_scale * a_scale, each operation rounded on its own
-#pragma unroll
-        for (int j = 0; j < Q_STAGE_BLOCKS; j++) {
-            t[j][0] = __fmul_rn(__fmul_rn((float)(d[j][0] - 8 * asum[j].x), wsA[j]), asc[j].x);
-            t[j][1] = __fmul_rn(__fmul_rn((float)(d[j][1] - 8 * asum[j].y), wsA[j]), asc[j].y);
-            t[j][2] = __fmul_rn(__fmul_rn((float)(d[j][2] - 8 * asum[j].x), wsB[j]), asc[j].x);
-            t[j][3] = __fmul_rn(__fmul_rn((float)(d[j][3] - 8 * asum[j].y), wsB[j]), asc[j].y);
-        }
-        // the stage's bytes are in registers: refill the slot for this warp's stage after next
-        __syncwarp();
-        if (lane == 0 && s + Q_DEPTH * Q_WARPS < n_stages) issue(s + Q_DEPTH * Q_WARPS, true, true);
-        // ---- the ordered part: take the accumulators over, add this stage's blocks in order, hand them on ----
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);  // (row r, act 2c), (r, 2c + 1), (r + 8, 2c), (r + 8, 2c + 1)
-        if (s > 0) {
-            const int received = warp == 0 ? turn - 1 : turn;  // hand-offs this warp has taken before
-            q40_wait(&token[warp], (uint32_t)(received & 1), fail_s);
-            acc = hand[warp * 32 + lane];
-        }
-#pragma unroll
-        for (int j = 0; j < Q_STAGE_BLOCKS; j++) {
-            if (j < nblk) {  // the blocks of a short last stage hold stale bytes: leave them out
-                acc.x = __fadd_rn(acc.x, t[j][0]), acc.y = __fadd_rn(acc.y, t[j][1]);
-                acc.z = __fadd_rn(acc.z, t[j][2]), acc.w = __fadd_rn(acc.w, t[j][3]);
+            for (int j = 0; j < Q_STAGE_BLOCKS; j++) {
+                const uint8_t* ab = st + Q_STAGE_BYTES + (gi * Q_STAGE_BLOCKS + j) * Q_ACT_BLOCK;
+                bf[j][0] = *(const uint32_t*)(ab + r * 16 + 4 * c);        // activation row r, elements 4c .. 4c+3
+                bf[j][1] = *(const uint32_t*)(ab + 128 + r * 16 + 4 * c);  // elements 16 + 4c ..
+                asc[j] = *((const float2*)(ab + 256) + c);                 // scales of activation rows 2c, 2c + 1
+                asum[j] = *((const int2*)(ab + 288) + c);
             }
-        }
-        if (s + 1 < n_stages) {
-            const int nw = (warp + 1) % Q_WARPS;
-            hand[nw * 32 + lane] = acc;
-            __syncwarp();
-            if (lane == 0) q40_arrive(&token[nw]);
-        } else {  // the last stage: this warp holds the result
-            if (*fail_s) acc = make_float4(__int_as_float(0x7fc00000), __int_as_float(0x7fc00000), __int_as_float(0x7fc00000), __int_as_float(0x7fc00000));
-            const int64_t row = tile * Q_TILE_ROWS + r, m0 = g * 8 + 2 * c;
-            if (row < p.n) {
-                if (m0 < p.m) p.out[m0 * p.out_stride + row] = acc.x;
-                if (m0 + 1 < p.m) p.out[(m0 + 1) * p.out_stride + row] = acc.y;
+            int d[Q_STAGE_BLOCKS][4];
+#pragma unroll
+            for (int j = 0; j < Q_STAGE_BLOCKS; j++) {
+                d[j][0] = d[j][1] = d[j][2] = d[j][3] = 0;
+                mma_u8s8(d[j], af[j], bf[j][0], bf[j][1]);
             }
-            if (row + 8 < p.n) {
-                if (m0 < p.m) p.out[m0 * p.out_stride + row + 8] = acc.z;
-                if (m0 + 1 < p.m) p.out[(m0 + 1) * p.out_stride + row + 8] = acc.w;
+            float t[Q_STAGE_BLOCKS][4];  // (dot as f32) * w_scale * a_scale, each operation rounded on its own
+#pragma unroll
+            for (int j = 0; j < Q_STAGE_BLOCKS; j++) {
+                t[j][0] = __fmul_rn(__fmul_rn((float)(d[j][0] - 8 * asum[j].x), wsA[j]), asc[j].x);
+                t[j][1] = __fmul_rn(__fmul_rn((float)(d[j][1] - 8 * asum[j].y), wsA[j]), asc[j].y);
+                t[j][2] = __fmul_rn(__fmul_rn((float)(d[j][2] - 8 * asum[j].x), wsB[j]), asc[j].x);
+                t[j][3] = __fmul_rn(__fmul_rn((float)(d[j][3] - 8 * asum[j].y), wsB[j]), asc[j].y);
+            }
+            if (gi == ng - 1) {  // the stage's bytes are in registers: refill the slot for this warp's stage after next
+                __syncwarp();
+                if (lane == 0 && s + Q_DEPTH * Q_WARPS < n_stages) issue(s + Q_DEPTH * Q_WARPS, true, true);
+            }
+            // ---- the ordered part: take the group's accumulators over, add this stage's blocks in order, hand them on ----
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);  // (row r, act 2c), (r, 2c + 1), (r + 8, 2c), (r + 8, 2c + 1)
+            if (s > 0) {
+                const int received = warp == 0 ? turn - 1 : turn;  // hand-offs this warp has taken before (per group)
+                q40_wait(&token[warp * MG + gi], (uint32_t)(received & 1), fail_s);
+                acc = hand[(warp * MG + gi) * 32 + lane];
+            }
+#pragma unroll
+            for (int j = 0; j < Q_STAGE_BLOCKS; j++) {
+                if (j < nblk) {  // the blocks of a short last stage hold stale bytes: leave them out
+                    acc.x = __fadd_rn(acc.x, t[j][0]), acc.y = __fadd_rn(acc.y, t[j][1]);
+                    acc.z = __fadd_rn(acc.z, t[j][2]), acc.w = __fadd_rn(acc.w, t[j][3]);
+                }
+            }
+            if (s + 1 < n_stages) {
+                const int nw = (warp + 1) % Q_WARPS;
+                hand[(nw * MG + gi) * 32 + lane] = acc;
+                __syncwarp();
+                if (lane == 0) q40_arrive(&token[nw * MG + gi]);
+            } else {  // the last stage: this warp holds the result
+                if (*fail_s) acc = make_float4(__int_as_float(0x7fc00000), __int_as_float(0x7fc00000), __int_as_float(0x7fc00000), __int_as_float(0x7fc00000));
+                const int64_t row = tile * Q_TILE_ROWS + r, m0 = (g0 + gi) * 8 + 2 * c;
+                if (row < p.n) {
+                    if (m0 < p.m) p.out[m0 * p.out_stride + row] = acc.x;
+                    if (m0 + 1 < p.m) p.out[(m0 + 1) * p.out_stride + row] = acc.y;
+                }
+                if (row + 8 < p.n) {
+                    if (m0 < p.m) p.out[m0 * p.out_stride + row + 8] = acc.z;
+                    if (m0 + 1 < p.m) p.out[(m0 + 1) * p.out_stride + row + 8] = acc.w;
+                }
             }
         }
     }
@@ -281,24 +296,39 @@ extern "C" int b200kv_q40_gemm(const void* packed, int64_t n, int64_t k, const v
     Q40Gemm p{};
     p.packed = (const uint8_t*)packed, p.act = act, p.out = out, p.status = (int*)scratch;
     p.n = n, p.nb = nb, p.out_stride = out_stride, p.m = m;
-    dim3 grid((unsigned)((n + Q_TILE_ROWS - 1) / Q_TILE_ROWS), (unsigned)groups);
     // warps per tile: enough stages per warp (>= 4) that the start-up of a CTA is amortised
     const int64_t n_stages = (nb + Q_STAGE_BLOCKS - 1) / Q_STAGE_BLOCKS;
     const int tile_warps = n_stages >= 32 ? 8 : (n_stages >= 16 ? 4 : 2);
-    const size_t smem = (size_t)tile_warps * Q_DEPTH * Q_RING_STAGE + tile_warps * 32 * 16 + (tile_warps * Q_DEPTH + tile_warps) * 8 + 16;
+    // more than 8 activation rows: 4 groups share each weight stage (a prompt pass re-reads the weights M / 32 times, from L2)
+    const int mg = groups > 1 ? 4 : 1;
+    auto smem_of = [](int w, int g) {
+        return (size_t)w * Q_DEPTH * (Q_STAGE_BYTES + g * Q_STAGE_BLOCKS * Q_ACT_BLOCK) + (size_t)w * g * 32 * 16 + (w * Q_DEPTH + w * g) * 8 + 16;
+    };
+    const size_t smem = smem_of(tile_warps, mg);
     static thread_local int attr_device = -1;  // the attribute is per device and sticks: set it once per (thread, device)
     int cur = 0;
     B200KV_CUDA(cudaGetDevice(&cur));
     if (attr_device != cur) {
-        const size_t most = (size_t)8 * Q_DEPTH * Q_RING_STAGE + 8 * 32 * 16 + (8 * Q_DEPTH + 8) * 8 + 16;
-        B200KV_CUDA(cudaFuncSetAttribute(q40_gemm_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most));
-        B200KV_CUDA(cudaFuncSetAttribute(q40_gemm_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most));
-        B200KV_CUDA(cudaFuncSetAttribute(q40_gemm_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most));
+        const int most = (int)smem_of(8, 4);
+        B200KV_CUDA(cudaFuncSetAttribute(q40_gemm_kernel<8, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, most));
+        B200KV_CUDA(cudaFuncSetAttribute(q40_gemm_kernel<4, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, most));
+        B200KV_CUDA(cudaFuncSetAttribute(q40_gemm_kernel<2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, most));
+        B200KV_CUDA(cudaFuncSetAttribute(q40_gemm_kernel<8, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, most));
+        B200KV_CUDA(cudaFuncSetAttribute(q40_gemm_kernel<4, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, most));
+        B200KV_CUDA(cudaFuncSetAttribute(q40_gemm_kernel<2, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, most));
         attr_device = cur;
     }
-    if (tile_warps == 8) B200KV_CUDA(launch_after_predecessor(q40_gemm_kernel<8>, grid, dim3(256), smem, stream, p));
-    else if (tile_warps == 4) B200KV_CUDA(launch_after_predecessor(q40_gemm_kernel<4>, grid, dim3(128), smem, stream, p));
-    else B200KV_CUDA(launch_after_predecessor(q40_gemm_kernel<2>, grid, dim3(64), smem, stream, p));
+    dim3 grid((unsigned)((n + Q_TILE_ROWS - 1) / Q_TILE_ROWS), (unsigned)((groups + mg - 1) / mg));
+    dim3 block(tile_warps * 32);
+    if (mg == 1) {
+        if (tile_warps == 8) B200KV_CUDA(launch_after_predecessor(q40_gemm_kernel<8, 1>, grid, block, smem, stream, p));
+        else if (tile_warps == 4) B200KV_CUDA(launch_after_predecessor(q40_gemm_kernel<4, 1>, grid, block, smem, stream, p));
+        else B200KV_CUDA(launch_after_predecessor(q40_gemm_kernel<2, 1>, grid, block, smem, stream, p));
+    } else {
+        if (tile_warps == 8) B200KV_CUDA(launch_after_predecessor(q40_gemm_kernel<8, 4>, grid, block, smem, stream, p));
+        else if (tile_warps == 4) B200KV_CUDA(launch_after_predecessor(q40_gemm_kernel<4, 4>, grid, block, smem, stream, p));
+        else B200KV_CUDA(launch_after_predecessor(q40_gemm_kernel<2, 4>, grid, block, smem, stream, p));
+    }
     return B200KV_OK;
 }
 
