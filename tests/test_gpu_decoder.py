@@ -84,3 +84,28 @@ def test_decoder_steps_match_oracle_composition(use_graphs):
         assert np.array_equal(tokens[clear], want.argmax(1).astype(np.int32)[clear])  # greedy choice, where it is not a near tie
     dec.check()
     dec.close()
+
+
+def test_decoder_prompt_pass_matches_token_by_token_oracle():
+    from tract_b200.decoder import Decoder, Shape
+
+    sh = Shape(hidden=256, n_layers=2, n_q_heads=4, n_kv_heads=2, head_dim=128, ffn=512, vocab=640, rope_theta=10000.0)
+    dec = Decoder(sh, n_seqs=3, max_tokens=128, kv_format="f16", seed=7, use_graphs=True)
+    ref = OracleDecoder(dec)
+    prompt = np.random.default_rng(3).integers(0, sh.vocab, (3, 37)).astype(np.int32)  # 111 rows: 14 groups of 8, the last short
+    for s in range(prompt.shape[1]):  # causal attention: the prompt pass equals feeding the prompt one token at a time
+        want = ref.step(prompt[:, s])
+    dec.prefill(torch.from_numpy(prompt))
+    got = dec.logits.cpu().numpy()
+    rms = np.sqrt((want ** 2).mean())
+    assert np.abs(got - want).mean() / rms <= 2e-2 and rel_err(got, want) <= 0.15  # see the note in the decode-step test
+    # and the decode steps carry on from the prompt's caches
+    tokens = dec.tokens.cpu().numpy().astype(np.int32)
+    for step in range(3):
+        want = ref.step(tokens)
+        dec.step()
+        got = dec.logits.cpu().numpy()
+        assert np.abs(got - want).mean() / np.sqrt((want ** 2).mean()) <= 2e-2, step
+        tokens = dec.tokens.cpu().numpy().astype(np.int32)
+    dec.check()
+    dec.close()

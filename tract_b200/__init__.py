@@ -288,16 +288,28 @@ class Q40Linear:
             _ck(L.b200kv_q40_pack(C.c_void_p(blocks.data_ptr()), C.c_int64(self.n), C.c_int64(self.k), C.c_void_p(self.packed.data_ptr()),
                                   _stream()))
 
-    def gemm(self, a, out=None):
-        """a: [M, K] f32 / f16 / bf16 CUDA tensor (rows contiguous); returns f32 [M, N]."""
+    @staticmethod
+    def scratch_bytes(k, m):
+        L = lib()
+        L.b200kv_q40_scratch_bytes.restype = C.c_int64
+        return L.b200kv_q40_scratch_bytes(C.c_int64(k), int(m))
+
+    def gemm(self, a, out=None, scratch=None):
+        """a: [M, K] f32 / f16 / bf16 CUDA tensor (rows contiguous); returns f32 [M, N].  `scratch`: a uint8 CUDA tensor of at
+        least scratch_bytes(K, M), for callers that share one scratch between layers (M above this layer's max_m needs it)."""
         import torch
 
-        assert a.dim() == 2 and a.shape[1] == self.k and a.stride(1) == 1 and a.shape[0] <= self.max_m
+        assert a.dim() == 2 and a.shape[1] == self.k and a.stride(1) == 1
+        if scratch is None:
+            assert a.shape[0] <= self.max_m
+            scratch = self.scratch
+        else:
+            assert scratch.numel() >= self.scratch_bytes(self.k, a.shape[0])
         if out is None:
             out = torch.empty((a.shape[0], self.n), dtype=torch.float32, device=a.device)
         with torch.cuda.device(a.device):
             _ck(lib().b200kv_q40_gemm(C.c_void_p(self.packed.data_ptr()), C.c_int64(self.n), C.c_int64(self.k), C.c_void_p(a.data_ptr()),
-                                      C.c_int64(a.stride(0)), int(a.shape[0]), _dtype_code(a), C.c_void_p(self.scratch.data_ptr()),
+                                      C.c_int64(a.stride(0)), int(a.shape[0]), _dtype_code(a), C.c_void_p(scratch.data_ptr()),
                                       C.c_void_p(out.data_ptr()), C.c_int64(out.stride(0)), _stream()))
         return out
 

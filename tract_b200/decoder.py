@@ -172,9 +172,56 @@ class Decoder:
     def set_tokens(self, tokens):
         self.tokens.copy_(self.torch.as_tensor(tokens, dtype=self.torch.int32))
 
+    def prefill(self, prompt):
+        """Prompt pass: `prompt` is an int32 [B, S] tensor of token ids, all sequences S tokens long, appended after whatever
+        the caches hold.  Runs every layer over all B * S rows (the GEMMs share each weight stage between 4 groups of 8
+        rows), fills the caches, and leaves the greedy next token of every sequence in self.tokens."""
+        torch, sh, B = self.torch, self.shape, self.B
+        S = int(prompt.shape[1])
+        R = B * S
+        dev, f32, kdt = self.dev, torch.float32, self.kv_dtype
+        nq, nk = sh.n_q_heads * sh.head_dim, sh.n_kv_heads * sh.head_dim
+        pos0 = self.lengths[0]
+        assert all(n == pos0 for n in self.lengths) and prompt.shape[0] == B
+        ids = prompt.to(dev, torch.int32).reshape(R).contiguous()
+        x = kv.gather_rows(self.embed, ids)
+        xn = torch.empty_like(x)
+        scratch = torch.empty(kv.Q40Linear.scratch_bytes(max(sh.hidden, sh.ffn, nq), R), dtype=torch.uint8, device=dev)
+        qkv = torch.empty((R, nq + 2 * nk), dtype=f32, device=dev)
+        # 16-bit q / k / v as [B, S, H, D] in memory, seen by the cache ops as [B, H, S, D] through their strides
+        q16, q16r = torch.empty((B, S, sh.n_q_heads, sh.head_dim), dtype=kdt, device=dev), torch.empty((B, S, sh.n_q_heads, sh.head_dim), dtype=kdt, device=dev)
+        k16, v16 = torch.empty((B, S, sh.n_kv_heads, sh.head_dim), dtype=kdt, device=dev), torch.empty((B, S, sh.n_kv_heads, sh.head_dim), dtype=kdt, device=dev)
+        attn16, attn = torch.empty_like(q16), torch.empty((R, nq), dtype=f32, device=dev)
+        proj = torch.empty((R, sh.hidden), dtype=f32, device=dev)
+        gate, up = torch.empty((R, sh.ffn), dtype=f32, device=dev), torch.empty((R, sh.ffn), dtype=f32, device=dev)
+        cos, sin = self.cos[pos0:pos0 + S].unsqueeze(0), self.sin[pos0:pos0 + S].unsqueeze(0)  # [1, S, D]: the same for every sequence
+        bhsd = lambda t: t.permute(0, 2, 1, 3)
+        for i, L in enumerate(self.layers):
+            kv.rms_norm(x, sh.eps, weight=L["attn_norm"], out=xn)
+            L["wqkv"].gemm(xn, qkv, scratch=scratch)
+            kv.cast(qkv[:, :nq], q16.view(R, nq))
+            kv.cast(qkv[:, nq:nq + nk], k16.view(R, nk))
+            kv.cast(qkv[:, nq + nk:], v16.view(R, nk))
+            kv.rope(bhsd(q16), cos, sin, out=bhsd(q16r))
+            L["cache"].append_rope(self.seqs[i], bhsd(k16), bhsd(v16), cos, sin)
+            L["cache"].attend(self.seqs[i], bhsd(q16r), causal=True, out=bhsd(attn16))
+            kv.cast(attn16.view(R, nq), attn)
+            L["wo"].gemm(attn, proj, scratch=scratch)
+            kv.add(x, proj, out=x)
+            kv.rms_norm(x, sh.eps, weight=L["ffn_norm"], out=xn)
+            L["wg"].gemm(xn, gate, scratch=scratch)
+            L["wu"].gemm(xn, up, scratch=scratch)
+            kv.silu_mul(gate, up, out=gate)
+            L["wd"].gemm(gate, proj, scratch=scratch)
+            kv.add(x, proj, out=x)
+        kv.cast(x[S - 1::S], self.x)  # the last row of every sequence
+        self._tail()
+        self.pos += S
+        self.lengths = [n + S for n in self.lengths]
+
     def prefill_synthetic(self, n_tokens, seed=1):
-        """Fills every layer's cache with n_tokens of random K / V per sequence (a stand-in for prompt processing:
-        the prompt pass needs the large-M GEMM, which is not built) and moves the positions there."""
+        """Fills every layer's cache with n_tokens of random K / V per sequence and moves the positions there: a stand-in for
+        a long prompt where only the decode steps are of interest."""
         torch = self.torch
         gen = torch.Generator(device=self.dev).manual_seed(seed)
         sh = self.shape
