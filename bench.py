@@ -579,6 +579,8 @@ DECODER = {
     # 2048 tokens (filled with synthetic K / V: the prompt pass needs the large-M GEMM, which is not built), greedy steps
     "cfg5-decoder": dict(past=2048, seqs=8, kv="f16", desc="32-layer Llama-3-8B-shaped decoder, Q4_0 weights, f16 KV cache, 8 sequences x 2048 cached tokens, greedy decode"),
     "cfg5-decoder-q8kv": dict(past=2048, seqs=8, kv="q8_1", desc="the same with the int8 block-32 KV cache"),
+    # the pp512 / tg128 methodology of the reference's llm bench (cli/src/llm.rs:47-139): a real prompt pass, then decode steps
+    "cfg5-pp512": dict(past=0, prompt=512, seqs=8, kv="f16", desc="the same decoder: 512-token prompt pass through the model (timed), then greedy decode"),
 }
 
 
@@ -594,8 +596,24 @@ def run_decoder(args, rank, world):
         dist.init_process_group("nccl", device_id=dev)
     sh = Shape()
     B, past = args.seqs or wl["seqs"], args.past or wl["past"]
-    dec = Decoder(sh, n_seqs=B, max_tokens=past + args.steps + max(args.warmup, 3) + 64, kv_format=wl["kv"], seed=100 + rank, device=dev)
-    dec.prefill_synthetic(past)
+    dec = Decoder(sh, n_seqs=B, max_tokens=past + wl.get("prompt", 0) + args.steps + max(args.warmup, 3) + 64, kv_format=wl["kv"], seed=100 + rank,
+                  device=dev)
+    pp = None
+    if wl.get("prompt"):
+        P = wl["prompt"]
+        prompt = torch.randint(0, sh.vocab, (B, P), dtype=torch.int32)
+        dec.prefill(prompt)  # warm-up (lazy allocations, attribute calls)
+        torch.cuda.synchronize()
+        dec.reset()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        dec.prefill(prompt)
+        e1.record()
+        torch.cuda.synchronize()
+        pp = {"prompt_tokens": B * P, "ms": e0.elapsed_time(e1), "tokens_per_s": B * P / (e0.elapsed_time(e1) * 1e-3)}
+        past = P
+    else:
+        dec.prefill_synthetic(past)
     tok_host = torch.randint(0, sh.vocab, (B,), dtype=torch.int32).pin_memory()
     out_host = torch.empty(B, dtype=torch.int32).pin_memory()
     dec.set_tokens(tok_host)
@@ -665,6 +683,7 @@ def run_decoder(args, rank, world):
                     "ms_per_step": ms_e2e},
             "gpu_launches": sh.n_layers * 26 + 8,
             "kernels_ms": {k: statistics.mean(v) for k, v in recs.items()},
+            "prompt_pass": pp,
             "roofline": {"bound": "hbm", "kernel": "whole step (Q4_0 GEMMs dominate)", "achieved": (weight_bytes + kv_bytes) / (ms * 1e-3) / 1e9,
                          "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": (weight_bytes + kv_bytes) / (ms * 1e-3) / 1e9 / pk["hbm_gbs"],
                          "peak_kind": pk_kind, "traffic": None, "algorithmic_bytes": weight_bytes + kv_bytes},

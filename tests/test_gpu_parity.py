@@ -329,6 +329,29 @@ def test_prefill_tensor_core_and_generic_paths_agree(kv, io, causal, Hq, Hkv, S)
     cache.close()
 
 
+@pytest.mark.parametrize("io", ["f16", "bf16"])
+def test_prefill_raises_its_reference_maximum_on_every_page(kv, io):
+    # scores that grow along the key axis by ~30 (in log2 units) per page: every page past the first lifts the running
+    # maximum by more than the 2^8 the kernel tolerates, so the rescale of O -- and its wait for the product before -- runs
+    # on every page, for every tile
+    Hq, Hkv, D, P, S = 8, 2, 128, 0, 700
+    rng = np.random.default_rng(77)
+    d = rng.standard_normal(D).astype(np.float32)
+    d /= np.linalg.norm(d)
+    ramp_t = (np.arange(P + S, dtype=np.float32) / 64.0)[None, None, :, None]
+    k = (normal(71, (1, Hkv, P + S, D)) * 0.05 + ramp_t * 2.0 * d).astype(np_dtype(io))
+    v = normal(72, (1, Hkv, P + S, D)).astype(np_dtype(io))
+    q = (normal(73, (1, Hq, S, D)) * 0.05 + 120.0 * d).astype(np_dtype(io))  # q . k * scale ~ 120 * 2 * (t / 64) / 11.3 = 21 t / 64
+    cache = kv.KvCache(io, Hkv, D, max_seqs=1, max_seq_tokens=P + S + 64)
+    sq = cache.new_seq()
+    cache.append([sq], to_dev(k), to_dev(v))
+    out = cache.attend([sq], to_dev(q), causal=True)
+    cache.check()
+    err = attn_err(out, io, q, k, v, causal=True, threads=8)
+    assert err <= TOL[io], err
+    cache.close()
+
+
 def test_prefill_repeats_bit_identically(kv):
     # 25 launches of one chunk whose last page is visible to the last eight queries of each tile only: a wait that
     # lets the epilogue read O before the last product has landed shows up as a changing result in exactly those rows

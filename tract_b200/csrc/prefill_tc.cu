@@ -53,7 +53,7 @@ struct PGeo {
     static constexpr int NK = NQ == 2 ? 4 : 2;  // K stages
     static constexpr int NV = NQ == 2 ? 5 : 2;  // V stages
     static constexpr int THREADS = NQ * SM_THREADS + 32 * (1 + NQ);  // softmax threads, the copy warp, one MMA warp per tile
-    static constexpr int N_BARS = 2 * NK + 2 * NV + 5 * NQ;
+    static constexpr int N_BARS = 2 * NK + 2 * NV + 6 * NQ;
     static constexpr size_t SMEM = (size_t)NQ * P_QBYTES + (size_t)(NK + NV) * P_CHUNK + N_BARS * 8 + 32 + NQ * 2 * XCHG_FLOATS * 4;
 };
 
@@ -210,8 +210,8 @@ __global__ void __launch_bounds__(PGeo<NQ>::THREADS, NQ == 2 ? 1 : 2) prefill_tc
     uint64_t* free_v = free_k + NK;                        // [NV] every tile's P.V on the stage has completed
     uint64_t* bar_s = free_v + NV;                         // [NQ][2] S buffer written
     uint64_t* bar_p = bar_s + 2 * NQ;                      // [NQ][2] P written by the softmax warps
-    uint64_t* bar_o = bar_p + 2 * NQ;                      // [NQ] P.V of the latest page completed
-    uint32_t* tmem_slot = (uint32_t*)(((uintptr_t)(bar_o + NQ) + 15) & ~(uintptr_t)15);
+    uint64_t* bar_o = bar_p + 2 * NQ;                      // [NQ][2] P.V of page j completed, on barrier j & 1
+    uint32_t* tmem_slot = (uint32_t*)(((uintptr_t)(bar_o + 2 * NQ) + 15) & ~(uintptr_t)15);
     volatile int* fail_s = (volatile int*)(tmem_slot + 1);
     float* xchg = (float*)(tmem_slot + 4);                 // [NQ][2 parities][XCHG_FLOATS]: row maxima / sums and remainder flags
 
@@ -231,7 +231,7 @@ __global__ void __launch_bounds__(PGeo<NQ>::THREADS, NQ == 2 ? 1 : 2) prefill_tc
         for (int s = 0; s < NK; s++) mbar_init(&full_k[s], 1), mbar_init(&free_k[s], NQ);
         for (int s = 0; s < NV; s++) mbar_init(&full_v[s], 1), mbar_init(&free_v[s], NQ);
         for (int i = 0; i < 2 * NQ; i++) mbar_init(&bar_s[i], 1), mbar_init(&bar_p[i], SM_THREADS / 32);
-        for (int i = 0; i < NQ; i++) mbar_init(&bar_o[i], 1);
+        for (int i = 0; i < 2 * NQ; i++) mbar_init(&bar_o[i], 1);
         *fail_s = (smem_u32(smem) & 1023u) ? 1 : 0;  // the swizzled operand tiles need a 1024-byte aligned base
         mbar_fence_init();
     }
@@ -342,7 +342,7 @@ __global__ void __launch_bounds__(PGeo<NQ>::THREADS, NQ == 2 ? 1 : 2) prefill_tc
                         tc_mma_ts(tm + COL_O, pa + kk * 8, vd + (uint64_t)((kk * 2048) >> 4), idesc_o, (j | kk) ? 1u : 0u);
                         if (two) tc_mma_ts(tm + COL_O, pa + 32 + kk * 8, vd + (uint64_t)((kk * 2048) >> 4), idesc_o, 1u);
                     }
-                    tc_commit(&bar_o[t]);
+                    tc_commit(&bar_o[2 * t + (j & 1)]);
                     tc_commit(&free_v[j % NV]);
                 }
                 __syncwarp();
@@ -405,10 +405,12 @@ __global__ void __launch_bounds__(PGeo<NQ>::THREADS, NQ == 2 ? 1 : 2) prefill_tc
                 l_run *= alpha;
             }
             if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-                // O must hold every page before this one.  A parity wait only tells two consecutive phases apart, so
-                // step through them: S(j) being there says no more than that P.V(j - 2) was issued before it
-                if (j > 1) wait_or_fail(&bar_o[qt], (uint32_t)((j - 2) & 1), fail_s);
-                wait_or_fail(&bar_o[qt], (uint32_t)((j - 1) & 1), fail_s);
+                // O must hold every page before this one.  S(j) being there says that P.V(j - 2) has completed (Q.K(j) was
+                // issued behind it); P.V(j - 1) may or may not have.  A parity wait tells only two consecutive phases of a
+                // barrier apart, so the products alternate between two barriers: on barrier (j - 1) & 1 the phase before the one
+                // waited for belongs to P.V(j - 3), known complete, and the one after it to P.V(j + 1), which needs this
+                // thread's P(j) first -- the wait cannot mistake one for the other.
+                wait_or_fail(&bar_o[2 * qt + ((j - 1) & 1)], (uint32_t)(((j - 1) >> 1) & 1), fail_s);
                 tc_fence_after();
 #pragma unroll
                 for (int cc = 0; cc < 4; cc++) {  // this thread's 64 of the row's 128 output channels
@@ -472,8 +474,7 @@ __global__ void __launch_bounds__(PGeo<NQ>::THREADS, NQ == 2 ? 1 : 2) prefill_tc
             if (lane == 0) mbar_arrive(&bar_p[2 * qt + (j & 1)]);
         }
         // ---- epilogue: wait for the last P.V, normalise, store ----
-        if (n_tiles > 1) wait_or_fail(&bar_o[qt], (uint32_t)((n_tiles - 2) & 1), fail_s);  // see the rescale above
-        wait_or_fail(&bar_o[qt], (uint32_t)((n_tiles - 1) & 1), fail_s);
+        wait_or_fail(&bar_o[2 * qt + ((n_tiles - 1) & 1)], (uint32_t)(((n_tiles - 1) >> 1) & 1), fail_s);  // see the rescale above
         tc_fence_after();
         float* xq = xchg + (2 * qt + (n_tiles & 1)) * XCHG_FLOATS;  // the buffer page n_tiles - 2 used: everyone is past it
         xq[half * PM + row] = l_run;

@@ -219,6 +219,14 @@ class Decoder:
         self.pos += S
         self.lengths = [n + S for n in self.lengths]
 
+    def reset(self):
+        """Empties every cache (the sequences stay allocated) and moves the positions back to 0."""
+        for i, L in enumerate(self.layers):
+            for s in self.seqs[i]:
+                L["cache"].truncate(s, 0)
+        self.pos.zero_()
+        self.lengths = [0] * self.B
+
     def prefill_synthetic(self, n_tokens, seed=1):
         """Fills every layer's cache with n_tokens of random K / V per sequence and moves the positions there: a stand-in for
         a long prompt where only the decode steps are of interest."""
