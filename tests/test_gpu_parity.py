@@ -369,6 +369,49 @@ def test_prefill_repeats_bit_identically(kv):
     cache.close()
 
 
+def _sweep_cases():
+    rng = np.random.default_rng(20260)
+    cases = []
+    for i in range(28):
+        fmt = ["f16", "bf16", "q8_1", "q4_0", "f32"][i % 5]
+        io = {"f16": "f16", "bf16": "bf16", "f32": "f32"}.get(fmt, ["f16", "bf16"][i % 2])
+        D = 64 if i % 7 == 3 else 128
+        Hkv = int(rng.choice([1, 2, 4]))
+        G = int(rng.choice([1, 2, 4, 8]))
+        P = int(rng.integers(0, 700))
+        S = int(rng.choice([1, 1, 1, 7, 33, 130, 257]))
+        B = int(rng.choice([1, 2, 3]))
+        mag = float(rng.choice([0.3, 1.0, 3.0]))  # scale of q and k: from nearly uniform to sharply peaked attention
+        cases.append((i, fmt, io, B, Hkv * G, Hkv, D, P, S, mag))
+    return cases
+
+
+@pytest.mark.parametrize("i,fmt,io,B,Hq,Hkv,D,P,S,mag", _sweep_cases())
+def test_attend_property_sweep(kv, i, fmt, io, B, Hq, Hkv, D, P, S, mag):
+    # seeded random geometry: every format, both head dims, group sizes 1..8, decode and prefill, batches whose sequences
+    # differ in length, inputs from flat to sharply peaked score distributions; causal and (for S = 1) trivially so
+    lens = [P + S + 13 * b for b in range(B)]
+    cache = kv.KvCache(fmt, Hkv, D, max_seqs=B, max_seq_tokens=max(lens) + 64)
+    seqs = [cache.new_seq() for _ in range(B)]
+    ks, vs = [], []
+    for b in range(B):
+        k = (normal(9000 + 10 * i + b, (1, Hkv, lens[b], D)) * mag).astype(np_dtype(io))
+        v = normal_with_outliers(9500 + 10 * i + b, (1, Hkv, lens[b], D)).astype(np_dtype(io))
+        if lens[b] > S:
+            cache.append([seqs[b]], to_dev(k[:, :, :-S]), to_dev(v[:, :, :-S]))
+        ks.append(k), vs.append(v)
+    k_new = np.concatenate([k[:, :, -S:] for k in ks]).astype(np_dtype(io))
+    v_new = np.concatenate([v[:, :, -S:] for v in vs]).astype(np_dtype(io))
+    cache.append(seqs, to_dev(k_new), to_dev(v_new))
+    q = (normal(9900 + i, (B, Hq, S, D)) * mag).astype(np_dtype(io))
+    out = cache.attend(seqs, to_dev(q), causal=True)
+    cache.check()
+    for b in range(B):
+        err = attn_err(out[b:b + 1], io, q[b:b + 1], oracle_cache_view(fmt, ks[b], io), oracle_cache_view(fmt, vs[b], io), causal=True, threads=8)
+        assert err <= TOL[io], (b, err)
+    cache.close()
+
+
 # ---- lone Sdpa: golden bundles, the reference's kernel-test shapes, property sweep ------------------------
 
 ATTN_CASES = ["simple-causal-f32", "simple-non-causal-f32", "simple-scale-f32", "simple-f16", "simple-mask-f32"]
