@@ -153,6 +153,20 @@ int b200kv_export_codes(b200kv_cache* cache, int32_t seq, int32_t which, void* c
 int b200kv_export_kivi(b200kv_cache* cache, int32_t seq, int32_t which, void* codes, float* lo, float* scale,
                        float* sink, float* residual, void* stream);
 
+/* Sliding-window decode attention (WindowKvSdpa, transformers/src/ops/window_kv_cache.rs:160-228: K / V ring buffers of
+ * `window` slots, attention over the valid slots without a mask): the one query of every sequence (q, out:
+ * [n_seqs, n_q_heads, 1, D]) attends over its last `window` cached tokens.  Call after b200kv_append, like b200kv_attend.
+ * Not available for the KIVI formats. */
+int b200kv_attend_window(b200kv_cache* cache, int32_t n_seqs, const int32_t* seqs, int32_t n_q_heads, const void* q,
+                         const int64_t q_strides[3], void* out, const int64_t out_strides[3], int32_t dtype, float scale,
+                         int64_t window, void* stream);
+
+/* Gives the pages that lie wholly before the last `keep_last` tokens of a sequence back to the pool: the bounded memory of
+ * the reference's ring buffer (window_kv_cache.rs:77-137) on the paged store.  The sequence keeps its length (positions go
+ * on counting); from now on attention sees at most the tokens from len - keep_last on, export / fork / truncation below
+ * that point / multi-query attention fail. */
+int b200kv_trim(b200kv_cache* cache, int32_t seq, int64_t keep_last);
+
 /* Drops the tail of a sequence (speculative-decoding rollback; DynKeyValueCacheState::truncate,
  * transformers/src/ops/dyn_kv_cache.rs:112-119 — on device, without the host round trip of
  * gpu/src/ops/dyn_kv_cache.rs:116-125).  Fails if len exceeds the current length. */

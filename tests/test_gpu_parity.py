@@ -369,6 +369,50 @@ def test_prefill_repeats_bit_identically(kv):
     cache.close()
 
 
+@pytest.mark.parametrize("fmt,io,D,G,window", [("f16", "f16", 128, 4, 100), ("q8_1", "f16", 128, 4, 257), ("bf16", "bf16", 128, 1, 64),
+                                               ("f32", "f32", 64, 2, 33), ("q4_0", "bf16", 128, 8, 1000)])
+def test_sliding_window_decode(kv, fmt, io, D, G, window):
+    # WindowKvSdpa (window_kv_cache.rs:160-228): each step pushes one token and attends, unmasked, over the last `window`
+    # cached tokens.  Sequences shorter than, equal to and longer than the window; pages given back as the window moves on.
+    Hkv, lens = 2, [window - 7 if window > 7 else 1, window, 3 * window + 5, 700]
+    B = len(lens)
+    cache = kv.KvCache(fmt, Hkv, D, max_seqs=B, max_seq_tokens=max(lens) + 80)
+    seqs = [cache.new_seq() for _ in range(B)]
+    ks = [normal(5100 + b, (1, Hkv, lens[b] + 3, D)).astype(np_dtype(io)) for b in range(B)]
+    vs = [normal_with_outliers(5200 + b, (1, Hkv, lens[b] + 3, D)).astype(np_dtype(io)) for b in range(B)]
+    for b in range(B):
+        cache.append([seqs[b]], to_dev(ks[b][:, :, :lens[b]]), to_dev(vs[b][:, :, :lens[b]]))
+    free0 = cache.free_pages()
+    for step in range(3):
+        n = [l + step for l in lens]
+        if step:
+            k_new = np.concatenate([ks[b][:, :, n[b] - 1:n[b]] for b in range(B)]).astype(np_dtype(io))
+            v_new = np.concatenate([vs[b][:, :, n[b] - 1:n[b]] for b in range(B)]).astype(np_dtype(io))
+            cache.append(seqs, to_dev(k_new), to_dev(v_new))
+        q = normal(5300 + step, (B, Hkv * G, 1, D)).astype(np_dtype(io))
+        out = cache.attend_window(seqs, to_dev(q), window)
+        cache.check()
+        for b in range(B):
+            lo = max(0, n[b] - window)
+            kw, vw = ks[b][:, :, lo:n[b]], vs[b][:, :, lo:n[b]]
+            err = attn_err(out[b:b + 1], io, q[b:b + 1], oracle_cache_view(fmt, kw, io), oracle_cache_view(fmt, vw, io), causal=False, threads=4)
+            assert err <= TOL[io], (step, b, err)
+        for s in seqs:  # bound the memory like the ring buffer does: nothing before the window is kept
+            cache.trim(s, window)
+    assert cache.free_pages() > free0  # the long sequences gave pages back
+    # a trimmed sequence still answers plain decode attention (over what it holds) but no longer exports
+    q = normal(5400, (B, Hkv * G, 1, D)).astype(np_dtype(io))
+    out = cache.attend(seqs, to_dev(q), causal=True)
+    b = 3
+    lo = max(0, lens[b] + 2 - window)
+    err = attn_err(out[b:b + 1], io, q[b:b + 1], oracle_cache_view(fmt, ks[b][:, :, lo:lens[b] + 2], io),
+                   oracle_cache_view(fmt, vs[b][:, :, lo:lens[b] + 2], io), causal=False, threads=4)
+    assert err <= TOL[io], err
+    with pytest.raises(kv.B200KvError):
+        cache.export(seqs[2], torch.float32)  # 3 * window + 7 tokens: always trimmed
+    cache.close()
+
+
 def _sweep_cases():
     rng = np.random.default_rng(20260)
     cases = []

@@ -26,6 +26,7 @@ EXPORTS = [
     "b200kv_profile_read", "b200kv_attend_static_scratch", "b200kv_export_kivi", "b200kv_append_rope", "b200kv_rope",
     "b200kv_q40_packed_bytes", "b200kv_q40_pack", "b200kv_q40_scratch_bytes", "b200kv_q40_gemm", "b200kv_q40_check",
     "b200kv_rms_norm", "b200kv_silu_mul", "b200kv_add", "b200kv_argmax", "b200kv_gather_rows", "b200kv_cast",
+    "b200kv_attend_window", "b200kv_trim",
 ]
 KERNEL_NAMES = {0: "table_scatter", 1: "append", 2: "decode", 3: "combine", 4: "export", 5: "sdpa_dense", 6: "prefill"}
 
@@ -78,6 +79,8 @@ def lib():
         L.b200kv_profile_read.argtypes = [vp, i32, i32p, C.POINTER(C.c_float), i32p]
         L.b200kv_sdpa.argtypes = [vp, i64p, vp, i64p, vp, i64p, vp, i64p, i32, vp, i64p, i32, i32, i32, i32, i32, i32,
                                   i32, C.c_float, i32, vp]
+        L.b200kv_attend_window.argtypes = [vp, i32, i32p, i32, vp, i64p, vp, i64p, i32, C.c_float, i64, vp]
+        L.b200kv_trim.argtypes = [vp, i32, i64]
         _lib = L
     return _lib
 
@@ -245,6 +248,21 @@ class KvCache:
 
     def truncate(self, seq, length):
         _ck(lib().b200kv_truncate(self._h, seq, length))
+
+    def trim(self, seq, keep_last):
+        """Gives the pages before the last keep_last tokens back to the pool (sliding-window memory bound)."""
+        _ck(lib().b200kv_trim(self._h, seq, C.c_int64(keep_last)))
+
+    def attend_window(self, seqs, q, window, scale=None, out=None):
+        """Decode attention (q: [n_seqs, Hq, 1, D]) over the last `window` cached tokens of every sequence."""
+        import torch
+
+        assert q.dim() == 4 and q.shape[0] == len(seqs) and q.shape[2] == 1
+        if out is None:
+            out = torch.empty_like(q, memory_format=torch.contiguous_format)
+        _ck(lib().b200kv_attend_window(self._h, len(seqs), _ids(seqs), q.shape[1], q.data_ptr(), _strides(q, 3), out.data_ptr(),
+                                       _strides(out, 3), _dtype_code(q), C.c_float(scale or 0.0), C.c_int64(window), _stream()))
+        return out
 
     def fork(self, seq) -> int:
         s = C.c_int32()

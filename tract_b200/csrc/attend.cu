@@ -30,6 +30,8 @@ extern "C" int b200kv_attend(b200kv_cache* c, int32_t n_seqs, const int32_t* seq
     if (n_new == 1 && kivi && !c->force_simt && n_seqs <= 256)
         return kivi_decode(c, n_seqs, seqs, n_q_heads, q, q_strides, out, out_strides, dtype, scale, stream);
     if (n_new == 1 && !kivi) return launch_decode(c, n_seqs, seqs, n_q_heads, q, q_strides, out, out_strides, dtype, scale, stream);
+    for (int i = 0; i < n_seqs; i++)
+        if (c->seqs[seqs[i]].start > 0) return fail("sequence %d was trimmed: only one query per sequence can attend over it", seqs[i]);
 
     if (!kivi && !c->force_simt && prefill_tc_supported(c, n_q_heads, dtype, q, q_strides, out, out_strides))
         return launch_prefill_tc(c, n_seqs, seqs, n_q_heads, n_new, q, q_strides, out, out_strides, dtype, scale, causal, stream);
@@ -60,4 +62,23 @@ extern "C" int b200kv_attend(b200kv_cache* c, int32_t n_seqs, const int32_t* seq
             return B200KV_KO;
     }
     return B200KV_OK;
+}
+
+// Sliding-window decode attention: the one query of every sequence attends over its last `window` cached tokens.
+// The fused op of transformers/src/ops/window_kv_cache.rs:160-228 (WindowKvSdpa: push K_new / V_new into ring buffers of
+// `window` slots, then attend over the valid slots, no mask) is b200kv_append + this call (+ b200kv_trim to bound memory).
+extern "C" int b200kv_attend_window(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t n_q_heads, const void* q,
+                                    const int64_t q_strides[3], void* out, const int64_t out_strides[3], int32_t dtype, float scale,
+                                    int64_t window, void* stream_) {
+    if (validate_seqs(c, n_seqs, seqs) != B200KV_OK) return B200KV_KO;
+    if (!c->L.has_v) return fail("this cache holds one tensor only: attention needs K and V");
+    if (fmt_is_kivi(c->L.fmt)) return fail("a KIVI cache has no sliding-window attention");
+    if (!q || !out || !q_strides || !out_strides) return fail("null tensor or strides");
+    if (window <= 0) return fail("window must be positive");
+    if (n_q_heads <= 0 || n_q_heads % c->L.Hkv != 0)
+        return fail("n_q_heads (%d) must be a positive multiple of n_kv_heads (%d)", n_q_heads, c->L.Hkv);
+    if (dtype < B200KV_F32 || dtype > B200KV_BF16) return fail("unknown dtype %d", dtype);
+    if (scale <= 0.f) scale = 1.0f / sqrtf((float)c->L.D);
+    DeviceGuard guard(c->cfg.device);
+    return launch_decode(c, n_seqs, seqs, n_q_heads, q, q_strides, out, out_strides, dtype, scale, (cudaStream_t)stream_, window);
 }

@@ -513,6 +513,7 @@ int b200kv_seq_new(b200kv_cache* c, int32_t* seq_out) {
         if (!c->seqs[i].live) {
             c->seqs[i].live = true;
             c->seqs[i].len = 0;
+            c->seqs[i].start = 0;
             c->seqs[i].pages.clear();
             *seq_out = (int32_t)i;
             return B200KV_OK;
@@ -523,9 +524,11 @@ int b200kv_seq_new(b200kv_cache* c, int32_t* seq_out) {
 int b200kv_seq_free(b200kv_cache* c, int32_t seq) {
     if (!c || seq < 0 || seq >= (int)c->seqs.size() || !c->seqs[seq].live) return fail("sequence %d is not live", seq);
     SeqState& s = c->seqs[seq];
-    for (int32_t pg : s.pages) c->free_pages.push_back(pg);
+    for (int32_t pg : s.pages)
+        if (pg >= 0) c->free_pages.push_back(pg);  // trimmed entries are -1
     s.pages.clear();
     s.len = 0;
+    s.start = 0;
     s.live = false;
     return B200KV_OK;
 }
@@ -681,6 +684,7 @@ int b200kv_append_rope(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int
 int b200kv_export(b200kv_cache* c, int32_t seq, void* k_out, const int64_t k_strides[2], void* v_out,
                   const int64_t v_strides[2], int32_t dtype, void* stream) {
     if (validate_seqs(c, 1, &seq) != B200KV_OK) return B200KV_KO;
+    if (c->seqs[seq].start > 0) return fail("sequence %d was trimmed to its last tokens: its front pages are gone", seq);
     if (!k_out || !k_strides) return fail("k_out and its strides are required");
     if (v_out && (!c->L.has_v || !v_strides)) return fail("v_out given but the cache has no values / no strides");
     if (dtype < B200KV_F32 || dtype > B200KV_BF16) return fail("unknown dtype %d", dtype);
@@ -693,6 +697,7 @@ int b200kv_export(b200kv_cache* c, int32_t seq, void* k_out, const int64_t k_str
 
 int b200kv_export_codes(b200kv_cache* c, int32_t seq, int32_t which, void* codes, void* scales, void* stream) {
     if (validate_seqs(c, 1, &seq) != B200KV_OK) return B200KV_KO;
+    if (c->seqs[seq].start > 0) return fail("sequence %d was trimmed to its last tokens: its front pages are gone", seq);
     if (!fmt_is_block_quant(c->L.fmt)) return fail("format %d has no codes: use b200kv_export", c->L.fmt);
     if (which < 0 || which > (c->L.has_v ? 1 : 0)) return fail("which = %d out of range", which);
     if (!codes || !scales) return fail("codes and scales are required");
@@ -718,6 +723,7 @@ int b200kv_truncate(b200kv_cache* c, int32_t seq, int64_t len) {
     if (validate_seqs(c, 1, &seq) != B200KV_OK) return B200KV_KO;
     SeqState& s = c->seqs[seq];
     if (len < 0 || len > s.len) return fail("cannot truncate a sequence of %lld tokens to %lld", (long long)s.len, (long long)len);
+    if (len < s.start) return fail("cannot truncate below token %lld: the pages before it were trimmed away", (long long)s.start);
     // QuantizedDynKvCacheState has no truncate: a finalised block cannot give its f32 rows back
     if (fmt_is_kivi(c->L.fmt) && len != s.len)
         return fail("a KIVI cache cannot be truncated (blocks are frozen once quantised; the reference has no truncate either)");
@@ -730,8 +736,27 @@ int b200kv_truncate(b200kv_cache* c, int32_t seq, int64_t len) {
     return B200KV_OK;
 }
 
+// Gives the pages that lie wholly before the last `keep_last` tokens back to the pool: the bounded memory of the
+// reference's sliding-window ring buffer (transformers/src/ops/window_kv_cache.rs:77-137) on a paged store.  Positions
+// keep counting from the sequence's real start; attention from now on sees tokens >= len - keep_last at most.
+int b200kv_trim(b200kv_cache* c, int32_t seq, int64_t keep_last) {
+    if (validate_seqs(c, 1, &seq) != B200KV_OK) return B200KV_KO;
+    if (keep_last <= 0) return fail("keep_last must be positive");
+    if (fmt_is_kivi(c->L.fmt)) return fail("a KIVI cache keeps its sinks and blocks: it cannot be trimmed");
+    SeqState& s = c->seqs[seq];
+    const int64_t start = std::max<int64_t>(s.start, s.len - keep_last);
+    for (int64_t pgi = s.start / PAGE_TOKENS; pgi < start / PAGE_TOKENS; pgi++)
+        if (s.pages[(size_t)pgi] >= 0) {
+            c->free_pages.push_back(s.pages[(size_t)pgi]);
+            s.pages[(size_t)pgi] = -1;
+        }
+    s.start = start;
+    return B200KV_OK;
+}
+
 int b200kv_fork(b200kv_cache* c, int32_t seq, int32_t* new_seq_out, void* stream_) {
     if (validate_seqs(c, 1, &seq) != B200KV_OK) return B200KV_KO;
+    if (c->seqs[seq].start > 0) return fail("sequence %d was trimmed to its last tokens: its front pages are gone", seq);
     if (!new_seq_out) return fail("null argument");
     cudaStream_t stream = (cudaStream_t)stream_;
     DeviceGuard guard(c->cfg.device);

@@ -138,6 +138,7 @@ __global__ void __launch_bounds__(128) decode_kernel(DecodeParams p, const __gri
         const uint8_t* Ks = stages + (size_t)st * Gm::STAGE;
         const uint8_t* Vs = Ks + Gm::CHUNK;
         const int n_valid = min(PAGE_TOKENS, w.len - (w.page_begin + i) * PAGE_TOKENS);
+        const int n_first = max(0, w.first - (w.page_begin + i) * PAGE_TOKENS);  // slots below it lie before the window
 
         // ---- scores: warp w takes tokens [16w, 16w+16), 4 at a time, 8 lanes per token ----
 #pragma unroll
@@ -184,8 +185,8 @@ __global__ void __launch_bounds__(128) decode_kernel(DecodeParams p, const __gri
 
         // ---- online softmax: warp g owns q-head g of the group ----
         if (warp < GT) {
-            float s0 = lane < n_valid ? sc[warp * 64 + lane] : -INFINITY;
-            float s1 = lane + 32 < n_valid ? sc[warp * 64 + lane + 32] : -INFINITY;
+            float s0 = (lane < n_valid && lane >= n_first) ? sc[warp * 64 + lane] : -INFINITY;
+            float s1 = (lane + 32 < n_valid && lane + 32 >= n_first) ? sc[warp * 64 + lane + 32] : -INFINITY;
             float m_new = fmaxf(m_run, warp_max(fmaxf(s0, s1)));
             float a, p0, p1;
             if (PRECISE) {
@@ -403,16 +404,18 @@ int launch_combine(const DecodeParams& p, const int32_t* batch_info, void* out, 
 }
 
 int launch_decode(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t n_q_heads, const void* q,
-                  const int64_t* qs, void* out, const int64_t* os, int32_t dtype, float scale, cudaStream_t stream) {
+                  const int64_t* qs, void* out, const int64_t* os, int32_t dtype, float scale, cudaStream_t stream, int64_t window) {
     const int Hkv = c->L.Hkv, D = c->L.D, G = n_q_heads / Hkv;
     const bool use_mma = decode_mma_supported(c->L.fmt, D, dtype) && !c->force_simt;
     const int GT = use_mma ? 8 : (G == 1 ? 1 : 4), nz = (G + GT - 1) / GT;
     // ---- work list: split every sequence into runs of pages so that the grid covers the GPU many times ----
+    // first visible token of every sequence: the last `window` tokens (window > 0), never before what was trimmed away
+    auto first_of = [&](const SeqState& s) { return std::max<int64_t>(s.start, window > 0 ? s.len - window : 0); };
     int64_t total_pages = 0;
     for (int i = 0; i < n_seqs; i++) {
-        int64_t len = c->seqs[seqs[i]].len;
-        if (len <= 0) return fail("sequence %d is empty: nothing to attend to", seqs[i]);
-        total_pages += (len + PAGE_TOKENS - 1) / PAGE_TOKENS;
+        const SeqState& s = c->seqs[seqs[i]];
+        if (s.len <= 0) return fail("sequence %d is empty: nothing to attend to", seqs[i]);
+        total_pages += (s.len + PAGE_TOKENS - 1) / PAGE_TOKENS - first_of(s) / PAGE_TOKENS;
     }
     // Pages per split.  Large launches: 16 CTAs per SM over the run, so that the tail is short.  Small launches would get
     // one page per CTA that way, several waves of CTAs that are all set-up: they fill one wave (3 CTAs per SM) with up to
@@ -422,10 +425,12 @@ int launch_decode(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t 
     // one entry per sequence: {table row, length, first work item, splits}; the work items follow from it
     InlineBatch ib{};
     std::vector<int4> ent((size_t)n_seqs);
+    std::vector<int32_t> first((size_t)n_seqs);
     int n_items = 0;
     for (int i = 0; i < n_seqs; i++) {
         const SeqState& s = c->seqs[seqs[i]];
-        const int pages = (int)((s.len + PAGE_TOKENS - 1) / PAGE_TOKENS);
+        first[i] = (int32_t)first_of(s);
+        const int pages = (int)((s.len + PAGE_TOKENS - 1) / PAGE_TOKENS) - first[i] / PAGE_TOKENS;
         const int splits = (int)std::min<int64_t>(64, (pages + chunk - 1) / chunk);
         ent[i] = make_int4(seqs[i], (int)s.len, n_items, splits);
         n_items += splits;
@@ -440,6 +445,7 @@ int launch_decode(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t 
     if (inline_batch) {
         ib.n = n_seqs;
         memcpy(ib.ent, ent.data(), (size_t)n_seqs * sizeof(int4));
+        memcpy(ib.first, first.data(), (size_t)n_seqs * sizeof(int32_t));
     } else {
         items_bytes = (size_t)n_items * sizeof(WorkItem);
         const size_t desc_bytes = items_bytes + (size_t)n_seqs * 8;
@@ -448,7 +454,7 @@ int launch_decode(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t 
         int32_t* info = (int32_t*)(h + items_bytes);
         for (int i = 0; i < n_seqs; i++) {
             info[2 * i] = ent[i].z, info[2 * i + 1] = ent[i].w;
-            for (int k = 0; k < ent[i].w; k++) items[ent[i].z + k] = make_work_item(ent[i], i, k);
+            for (int k = 0; k < ent[i].w; k++) items[ent[i].z + k] = make_work_item(ent[i], i, k, first[i]);
         }
         if (staging_upload(c, slot, desc_bytes, stream) != B200KV_OK) return B200KV_KO;
     }

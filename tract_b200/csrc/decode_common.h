@@ -11,7 +11,8 @@ struct WorkItem {
     int32_t n_pages;     // pages in this split
     int32_t batch;       // batch entry
     int32_t split;       // split index inside the batch entry
-    int32_t pad0, pad1;
+    int32_t first;       // first visible token: a sliding window, or a sequence whose front pages were given back (0: all)
+    int32_t pad1;
 };
 
 struct DecodeParams {
@@ -37,16 +38,18 @@ struct InlineBatch {
     int32_t n;  // entries in use; 0 = the kernels read p.items / batch_info from device memory instead
     int32_t pad[3];
     int4 ent[INLINE_BATCH];
+    int32_t first[INLINE_BATCH];  // first visible token of each entry (0: the whole sequence)
 };
 
-__host__ __device__ inline WorkItem make_work_item(const int4& e, int batch, int k) {
-    const int pages = (e.y + PAGE_TOKENS - 1) / PAGE_TOKENS;
+__host__ __device__ inline WorkItem make_work_item(const int4& e, int batch, int k, int first = 0) {
+    const int p0 = first / PAGE_TOKENS;  // pages before the first visible token are not walked (they may have been freed)
+    const int pages = (e.y + PAGE_TOKENS - 1) / PAGE_TOKENS - p0;
     const int base = pages / e.w, rem = pages % e.w;
     WorkItem w;
     w.trow = e.x, w.len = e.y;
-    w.page_begin = k * base + (k < rem ? k : rem);
+    w.page_begin = p0 + k * base + (k < rem ? k : rem);
     w.n_pages = base + (k < rem ? 1 : 0);
-    w.batch = batch, w.split = k, w.pad0 = w.pad1 = 0;
+    w.batch = batch, w.split = k, w.first = first, w.pad1 = 0;
     return w;
 }
 // Work item `item` of an inline batch: binary search for the sequence that owns it.
@@ -57,7 +60,7 @@ __device__ inline WorkItem resolve_work_item(const InlineBatch& ib, int item) {
         if (ib.ent[mid].z <= item) lo = mid;
         else hi = mid - 1;
     }
-    return make_work_item(ib.ent[lo], lo, item - ib.ent[lo].z);
+    return make_work_item(ib.ent[lo], lo, item - ib.ent[lo].z, ib.first[lo]);
 }
 
 // decode.cu

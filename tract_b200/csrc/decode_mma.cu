@@ -176,8 +176,9 @@ __global__ void __launch_bounds__(128, MGeo<FMT>::MIN_CTAS) decode_mma_kernel(De
         const uint8_t* Ks = stages + (size_t)st * Gm::STAGE;
         const uint8_t* Vs = Ks + Gm::CHUNK;
         const int n_valid = min(PAGE_TOKENS, w.len - (w.page_begin + i) * PAGE_TOKENS);
+        const int n_first = max(0, w.first - (w.page_begin + i) * PAGE_TOKENS);  // slots below it lie before the window
         if (warp * 16 < n_valid) {  // warp-uniform: this warp has at least one live token in the tile
-            const bool vA = tA < n_valid, vB = tB < n_valid;
+            const bool vA = tA < n_valid && tA >= n_first, vB = tB < n_valid && tB >= n_first;
 
             // ================= scores: S^T[16 tokens x 8 heads] = K . Q^T =================
             float sacc[4] = {0.f, 0.f, 0.f, 0.f};

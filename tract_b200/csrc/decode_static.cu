@@ -63,6 +63,7 @@ extern "C" int b200kv_attend_static_scratch(b200kv_cache* c, int32_t n_seqs, con
     const int GT = use_mma ? 8 : (G == 1 ? 1 : 4), nz = (G + GT - 1) / GT;
     int64_t total_pages = 0;
     for (int i = 0; i < n_seqs; i++) {
+        if (c->seqs[seqs[i]].start > 0) return fail("sequence %d was trimmed: use b200kv_attend or b200kv_attend_window", seqs[i]);
         const int64_t len = c->seqs[seqs[i]].len;
         if (len <= 0) return fail("sequence %d is empty: nothing to attend to", seqs[i]);
         total_pages += (len + PAGE_TOKENS - 1) / PAGE_TOKENS;

@@ -33,6 +33,7 @@ struct DeviceGuard {
 struct SeqState {
     bool live = false;
     int64_t len = 0;
+    int64_t start = 0;  // first token still held: the pages before start / 64 were given back by b200kv_trim (entries -1)
     std::vector<int32_t> pages;
 };
 
@@ -128,7 +129,7 @@ struct ProfScope {
 // decode.cu
 int launch_decode(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t n_q_heads, const void* q,
                   const int64_t* q_strides, void* out, const int64_t* out_strides, int32_t dtype, float scale,
-                  cudaStream_t stream);
+                  cudaStream_t stream, int64_t window = 0);
 // sdpa_dense.cu
 int launch_sdpa_dense(const void* q, const int64_t* qs, const void* k, const int64_t* ks, const void* v,
                       const int64_t* vs, const void* mask, const int64_t* ms, int mask_dtype, void* out,
