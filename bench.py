@@ -763,6 +763,9 @@ def run_reference(args, rank, world):
     import oracle
 
     threads = oracle.hardware_threads()
+    if args.workload not in WORKLOADS:
+        return {"impl": "reference", "unavailable": f"the CPU arm times the decode workloads only ({', '.join(sorted(WORKLOADS))}); "
+                                                    f"the {args.workload} line carries its own cpu_baseline where it has one"}
     fmt, io, n_seq, past, desc = WORKLOADS[args.workload]
     sample_past = 8192 if past == "ragged" else int(past)
     sample_seqs = max(1, min(n_seq, 2))
