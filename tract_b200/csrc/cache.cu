@@ -116,26 +116,24 @@ __device__ inline int sat_i8_rz(float x) {
     return max(-128, min(127, i));
 }
 
-// One thread per 16-byte unit of a token-head row; grid.y selects K or V.
+// One thread per 16-byte unit of a token-head row.  grid.z = 2 * batch entry + (K or V); grid.x walks the (head, token,
+// unit) triples of that entry, so that the index arithmetic is three 32-bit divisions and no 64-bit one.
 template <int FMT>
 __global__ void __launch_bounds__(256) append_kernel(AppendParams p, const __grid_constant__ InlineAppend ia) {
     constexpr int EPU = elems_in_bytes<FMT>(16);  // elements per unit
-    const int kv = blockIdx.y;
+    const int kv = p.has_v ? (int)(blockIdx.z & 1) : 0;
     grid_launch_dependents();  // a decode launch that follows may be scheduled now; it waits for this grid before reading pages
-    if (blockIdx.x == 0 && blockIdx.y == 0)  // publish the new page-table entries (replaces a separate launch)
+    if (blockIdx.x == 0 && blockIdx.z == 0)  // publish the new page-table entries (replaces a separate launch)
         for (int i = threadIdx.x; i < p.n_upd; i += blockDim.x) {
             const int2 u = ia.n ? ia.upd[i] : ((const int2*)p.upd)[i];
             p.table[u.x] = u.y;
         }
-    const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    const int64_t total_rows = (int64_t)p.n_seqs * p.H * p.S;
-    int64_t row = gid / p.units;
-    const int u = (int)(gid % p.units);
-    const bool valid = row < total_rows;
-    if (!valid) row = total_rows - 1;  // keep the lane alive for the shuffles below
-    const int b = (int)(row / ((int64_t)p.H * p.S));
-    const int h = (int)((row / p.S) % p.H);
-    const int s = (int)(row % p.S);
+    const int b = p.has_v ? (int)(blockIdx.z >> 1) : (int)blockIdx.z;
+    const uint32_t per_head = (uint32_t)p.S * (uint32_t)p.units, idx = blockIdx.x * blockDim.x + threadIdx.x;
+    const uint32_t hq = idx / per_head, rem = idx - hq * per_head;
+    const bool valid = hq < (uint32_t)p.H;
+    // lanes past the end stay alive for the shuffles below (their partner lanes are past the end as well): point them at the last row
+    const int h = valid ? (int)hq : p.H - 1, s = valid ? (int)(rem / (uint32_t)p.units) : p.S - 1, u = (int)(idx % (uint32_t)p.units);
     const int c0 = u * EPU;
 
     // ---- load EPU input elements --------------------------------------------------------------
@@ -288,6 +286,52 @@ __global__ void __launch_bounds__(256) append_kernel(AppendParams p, const __gri
     }
 }
 
+// The bit-copy formats without rotary embedding, aligned input: four units per thread, the four 16-byte loads issued
+// before the first store so that a thread keeps 64 bytes in flight.  Same indexing as append_kernel.
+template <int FMT>
+__global__ void __launch_bounds__(256) append_copy_kernel(AppendParams p, const __grid_constant__ InlineAppend ia) {
+    constexpr int REP = 4;
+    const int kv = p.has_v ? (int)(blockIdx.z & 1) : 0;
+    grid_launch_dependents();
+    if (blockIdx.x == 0 && blockIdx.z == 0)
+        for (int i = threadIdx.x; i < p.n_upd; i += blockDim.x) {
+            const int2 u = ia.n ? ia.upd[i] : ((const int2*)p.upd)[i];
+            p.table[u.x] = u.y;
+        }
+    const int b = p.has_v ? (int)(blockIdx.z >> 1) : (int)blockIdx.z;
+    const uint32_t units = (uint32_t)p.units, per_head = (uint32_t)p.S * units;
+    const int esz = dtype_size(p.dtype);
+    const int4 ent = ia.n ? ia.ent[b] : ((const int4*)p.desc)[b];
+    const int32_t trow = ent.x, len0 = ent.y, upd_off = ent.z, new_pn = ent.w;
+    uint4 val[REP];
+    int hh[REP], ss[REP], uu[REP];
+    bool ok[REP];
+#pragma unroll
+    for (int r = 0; r < REP; r++) {
+        const uint32_t idx = (blockIdx.x * REP + r) * blockDim.x + threadIdx.x;
+        const uint32_t hq = idx / per_head, rem = idx - hq * per_head;
+        ok[r] = hq < (uint32_t)p.H;
+        hh[r] = (int)hq, ss[r] = (int)(rem / units), uu[r] = (int)(rem % units);
+        if (ok[r])
+            val[r] = *(const uint4*)((const uint8_t*)p.src[kv] + (b * p.sb[kv] + hh[r] * p.sh[kv] + ss[r] * p.ss[kv]) * esz + uu[r] * 16);
+    }
+#pragma unroll
+    for (int r = 0; r < REP; r++) {
+        if (!ok[r]) continue;
+        const int64_t pos = (int64_t)len0 + ss[r];
+        const int32_t pn = (int32_t)(pos / PAGE_TOKENS);
+        const int32_t pg = (upd_off >= 0 && pn >= new_pn)
+                               ? (ia.n ? ia.upd[upd_off + pn - new_pn].y : p.upd[2 * (upd_off + pn - new_pn) + 1])
+                               : p.table[(int64_t)trow * p.max_pages_per_seq + pn];
+        if (pg < 0 || pg >= p.n_pages) {
+            atomicOr(p.status, STATUS_PAGE_OOB);
+            continue;
+        }
+        uint8_t* chunk = p.pool + (int64_t)pg * p.page_bytes + (int64_t)(hh[r] * (p.has_v ? 2 : 1) + kv) * p.chunk_bytes;
+        *(uint4*)(chunk + chunk_addr(FMT, p.D, kv, (int)(pos % PAGE_TOKENS), uu[r] * 16)) = val[r];
+    }
+}
+
 struct ExportParams {
     const uint8_t* pool;
     const int32_t* table_row;  // page ids of the sequence
@@ -387,8 +431,15 @@ static int alloc_pages(b200kv_cache* c, SeqState& s, int64_t new_len, std::vecto
 
 template <int FMT>
 static void launch_append_fmt(const AppendParams& p, const InlineAppend& ia, int n_kv, cudaStream_t stream) {
-    int64_t threads = (int64_t)p.n_seqs * p.H * p.S * p.units;
-    dim3 grid((unsigned)((threads + 255) / 256), n_kv);
+    const int64_t per_entry = (int64_t)p.H * p.S * p.units;  // < 2^31: checked by the caller
+    if constexpr (FMT == B200KV_FMT_F32 || FMT == B200KV_FMT_F16 || FMT == B200KV_FMT_BF16) {
+        if (p.vec_ok && !p.rope_cos && per_entry >= 4096) {  // bulk appends (prompt chunks): four units per thread
+            dim3 grid((unsigned)((per_entry + 1023) / 1024), 1, (unsigned)(p.n_seqs * n_kv));
+            append_copy_kernel<FMT><<<grid, 256, 0, stream>>>(p, ia);
+            return;
+        }
+    }
+    dim3 grid((unsigned)((per_entry + 255) / 256), 1, (unsigned)(p.n_seqs * n_kv));
     append_kernel<FMT><<<grid, 256, 0, stream>>>(p, ia);
 }
 
@@ -647,6 +698,8 @@ static int append_impl(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int
     };
     p.vec_ok = aligned(k_new, k_strides) && aligned(v_new, v_strides);
     const int n_kv = c->L.has_v ? 2 : 1;
+    if (!fmt_is_kivi(c->L.fmt) && ((int64_t)n_seqs * n_kv > 65535 || (int64_t)p.H * p.S * p.units >= (1ll << 31)))
+        return fail("append of %d sequences x %d tokens exceeds the launch geometry: split the call", n_seqs, n_new);
     if (fmt_is_kivi(c->L.fmt)) {
         kivi_append(c, n_seqs, seqs, n_new, k_new, k_strides, v_new, v_strides, dtype, (const int32_t*)d, stream);
     } else {
