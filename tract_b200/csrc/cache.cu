@@ -184,6 +184,21 @@ __global__ void __launch_bounds__(256) append_kernel(AppendParams p, const __gri
 #pragma unroll
                 for (int i = 0; i < EPU; i++) v[i] = ((const float*)src)[i];
             }
+        } else if (p.vec_ok) {  // 16-bit input: 8 elements per 128-bit load
+#pragma unroll
+            for (int i = 0; i < EPU / 8; i++) {
+                const uint4 w = ((const uint4*)src)[i];
+                const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    if (p.dtype == B200KV_F16) {
+                        const float2 f = __half22float2(*(const __half2*)&ws[j]);
+                        v[8 * i + 2 * j] = f.x, v[8 * i + 2 * j + 1] = f.y;
+                    } else {  // bf16 -> f32 is a shift
+                        v[8 * i + 2 * j] = __uint_as_float(ws[j] << 16), v[8 * i + 2 * j + 1] = __uint_as_float(ws[j] & 0xffff0000u);
+                    }
+                }
+            }
         } else {
 #pragma unroll
             for (int i = 0; i < EPU; i++) v[i] = ld_as_f32(src, p.dtype, i);
