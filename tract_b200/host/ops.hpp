@@ -150,6 +150,12 @@ class KvState {
         ck(b200kv_attend(cache_, 1, &seq_, (int32_t)q.shape[1], (int32_t)q.shape[2], q.ptr, q.strides, out.ptr, out.strides, (int)q.dt,
                          scale, causal ? 1 : 0, stream));
     }
+    // WindowKvSdpa (transformers/src/ops/window_kv_cache.rs:160-228): decode attention over the last `window` tokens, then the
+    // pages before the window go back to the pool, as the reference's ring buffer forgets them.
+    void attend_window(const DeviceTensor& q, const DeviceTensor& out, float scale, int64_t window, void* stream) {
+        ck(b200kv_attend_window(cache_, 1, &seq_, (int32_t)q.shape[1], q.ptr, q.strides, out.ptr, out.strides, (int)q.dt, scale, window, stream));
+        ck(b200kv_trim(cache_, seq_, window));
+    }
     void check(void* stream) { ck(b200kv_check(cache_, stream)); }
     const CacheSpec& spec() const { return spec_; }
 
@@ -185,5 +191,51 @@ struct PagedKvSdpa {
         st.attend(q, out, scale, is_causal, stream);
     }
 };
+
+// ---- the ops either side of the cache path ---------------------------------------------------------------
+// A Q4_0 weight constant [n, k] applied with the arithmetic of Q4_0::w4a8_gemm (linalg/src/frame/block_quant/q4_0.rs:260-310);
+// what dispatch_ggml_matvec_q40 (cuda/src/kernels/matmul/mod.rs:481-520) does today.  `packed` and `scratch` are device
+// buffers the caller owns (sizes from packed_bytes / scratch_bytes): nothing is allocated here.
+struct Q40MatMul {
+    int64_t n = 0, k = 0;
+    const void* packed = nullptr;
+    static int64_t packed_bytes(int64_t n, int64_t k) { return b200kv_q40_packed_bytes(n, k); }
+    static int64_t scratch_bytes(int64_t k, int32_t m) { return b200kv_q40_scratch_bytes(k, m); }
+    // once per weight: `blocks` is the reference's storage, n rows of k / 32 blocks of 18 bytes
+    void pack(const void* blocks, void* packed_out, void* stream) {
+        ck(b200kv_q40_pack(blocks, n, k, packed_out, stream));
+        packed = packed_out;
+    }
+    // out[m, n] (f32) = a[m, k] . W^T
+    void eval(const void* a, int64_t a_stride, int32_t m, DatumType dt, void* scratch, float* out, int64_t out_stride, void* stream) const {
+        if (!packed) throw Error("Q4_0 weights were not packed");
+        ck(b200kv_q40_gemm(packed, n, k, a, a_stride, m, (int)dt, scratch, out, out_stride, stream));
+    }
+};
+
+// RmsNorm over the last axis (core/src/ops/nn/rms_norm.rs), optionally fused with the Mul by a weight vector that follows it.
+struct RmsNorm {
+    float eps = 1e-5f;
+    void eval(const void* x, int64_t x_stride, const void* weight, void* out, int64_t out_stride, int64_t rows, int32_t d, DatumType dt,
+              void* stream) const {
+        ck(b200kv_rms_norm(x, x_stride, weight, out, out_stride, rows, d, eps, (int)dt, stream));
+    }
+};
+
+// Silu (and the Mul that follows it in a gated FFN), Add, Cast, ArgMax, Gather on axis 0: the element-wise nodes of a decoder block.
+inline void silu_mul(const void* gate, const void* up, void* out, int64_t n, DatumType dt, void* stream) {
+    ck(b200kv_silu_mul(gate, up, out, n, (int)dt, stream));
+}
+inline void add(const void* a, const void* b, void* out, int64_t n, DatumType dt, void* stream) { ck(b200kv_add(a, b, out, n, (int)dt, stream)); }
+inline void cast(const void* src, int64_t src_stride, DatumType src_dt, void* dst, int64_t dst_stride, DatumType dst_dt, int64_t rows,
+                 int64_t cols, void* stream) {
+    ck(b200kv_cast(src, src_stride, (int)src_dt, dst, dst_stride, (int)dst_dt, rows, cols, stream));
+}
+inline void argmax(const float* x, int64_t stride, int64_t rows, int32_t n, int32_t* out, void* stream) {
+    ck(b200kv_argmax(x, stride, rows, n, out, stream));
+}
+inline void gather_rows(const void* table, int64_t n_rows, int64_t row_bytes, const int32_t* ids, int64_t n_ids, void* out, void* stream) {
+    ck(b200kv_gather_rows(table, n_rows, row_bytes, ids, n_ids, out, stream));
+}
 
 }  // namespace tract_b200
