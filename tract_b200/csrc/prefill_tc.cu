@@ -44,7 +44,7 @@ constexpr uint32_t COL_O = 0, COL_S = 128, COLS_PER_TILE = 256;
 // per query tile and per parity of the page index: the two half-row maxima of every row, then one flag per softmax warp
 constexpr int XCHG_FLOATS = 2 * PM + 8;
 // f16 weights skip the remainder MMA of a page once, for every row of the tile, sqrt(32) x the largest weight of the
-// page is below this fraction of the row's running sum (each half row judged on its own 32 columns): what the
+// page is below this fraction of the row's running sum (each half row tested on its own 32 columns): what the
 // rounding of such a page can add is then below 2^-12 / 8 of the row's scale
 constexpr float P_SKIP_FRACTION = 0.125f;
 
