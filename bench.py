@@ -666,7 +666,7 @@ def run_decoder(args, rank, world):
         recs.setdefault(name, []).append(t)
     c0.profile(False)
     dec.check()
-    weight_bytes = sum(L[k].packed.numel() for L in dec.layers for k in ("wqkv", "wo", "wg", "wu", "wd")) + dec.lm_head.packed.numel()
+    weight_bytes = sum(L[k].packed.numel() for L in dec.layers for k in ("wqkv", "wo", "wgu", "wd")) + dec.lm_head.packed.numel()
     kv_bytes = sh.n_layers * B * (past + args.steps // 2) * sh.n_kv_heads * sh.head_dim * 2 * (2 if wl["kv"] == "f16" else 1.0625)
     pk, pk_kind = peaks()
     if rank == 0:
@@ -681,7 +681,7 @@ def run_decoder(args, rank, world):
                        "launch": "CUDA-graph segments between cache calls; cache calls from the host"},
             "e2e": {"value": world * B / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": B * 4, "d2h_bytes_per_step": B * 4,
                     "ms_per_step": ms_e2e},
-            "gpu_launches": sh.n_layers * 26 + 8,
+            "gpu_launches": sh.n_layers * 12 + 6,  # per layer: 5 GEMMs and their 4 fused + 1 plain producers... see Decoder
             "kernels_ms": {k: statistics.mean(v) for k, v in recs.items()},
             "prompt_pass": pp,
             "roofline": {"bound": "hbm", "kernel": "whole step (Q4_0 GEMMs dominate)", "achieved": (weight_bytes + kv_bytes) / (ms * 1e-3) / 1e9,

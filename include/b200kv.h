@@ -161,6 +161,14 @@ int b200kv_attend_window(b200kv_cache* cache, int32_t n_seqs, const int32_t* seq
                          const int64_t q_strides[3], void* out, const int64_t out_strides[3], int32_t dtype, float scale,
                          int64_t window, void* stream);
 
+/* Decode attention with ApplyRope (transformers/src/ops/apply_rope.rs:143-176) folded into the query load: the result of
+ * b200kv_rope on q followed by b200kv_attend with n_new = 1, bit for bit, without the intermediate tensor.  q, out:
+ * [n_seqs, n_q_heads, 1, D]; cos / sin: one row of D values of type `dtype` per sequence, `rope_stride` elements apart.
+ * Not available for the KIVI formats. */
+int b200kv_attend_rope(b200kv_cache* cache, int32_t n_seqs, const int32_t* seqs, int32_t n_q_heads, const void* q,
+                       const int64_t q_strides[3], const void* cos, const void* sin, int64_t rope_stride, void* out,
+                       const int64_t out_strides[3], int32_t dtype, float scale, void* stream);
+
 /* Gives the pages that lie wholly before the last `keep_last` tokens of a sequence back to the pool: the bounded memory of
  * the reference's ring buffer (window_kv_cache.rs:77-137) on the paged store.  The sequence keeps its length (positions go
  * on counting); from now on attention sees at most the tokens from len - keep_last on, export / fork / truncation below
@@ -220,6 +228,23 @@ int64_t b200kv_q40_scratch_bytes(int64_t k, int32_t m);
  * memory (16-byte aligned) that must not be shared by two calls in flight.  Allocates nothing. */
 int b200kv_q40_gemm(const void* packed, int64_t n, int64_t k, const void* a, int64_t a_stride, int32_t m, int32_t dtype,
                     void* scratch, float* out, int64_t out_stride, void* stream);
+/* The two halves of b200kv_q40_gemm, for callers that feed several matrices from one activation (the gate and up
+ * projections of a gated FFN) or that produce the activation with one of the fused calls below.
+ * b200kv_q40_quantize is Q4_0::quantize_row_q8 (q4_0.rs:199-222) for m rows into `scratch`; b200kv_q40_gemm_quantized
+ * multiplies what `scratch` holds (m rows of k values) with a packed matrix.  Same stream, same scratch. */
+int b200kv_q40_quantize(const void* a, int64_t a_stride, int32_t m, int32_t dtype, int64_t k, void* scratch, void* stream);
+int b200kv_q40_gemm_quantized(const void* packed, int64_t n, int64_t k, int32_t m, void* scratch, float* out, int64_t out_stride,
+                              void* stream);
+/* Producers fused with the quantiser: the activation never visits HBM as floats.  Each gives the bits of the separate
+ * calls run one after the other.
+ *   silu_mul:      scratch <- quantise(Silu(gate) * up)            (b200kv_silu_mul, then b200kv_q40_quantize)
+ *   add_rms_norm:  v = x + residual (residual may be null); x_out <- v when x_out is given (it may be x or residual);
+ *                  scratch <- quantise(RmsNorm(v, eps) * weight)   (b200kv_add, b200kv_rms_norm, b200kv_q40_quantize); f32 only */
+int b200kv_q40_silu_mul_quantize(const void* gate, int64_t gate_stride, const void* up, int64_t up_stride, int32_t m, int32_t dtype,
+                                 int64_t k, void* scratch, void* stream);
+int b200kv_q40_add_rms_norm_quantize(const float* x, int64_t x_stride, const float* residual, int64_t residual_stride,
+                                     const float* weight, float eps, float* x_out, int64_t x_out_stride, int32_t m, int64_t k,
+                                     void* scratch, void* stream);
 /* Synchronises `stream` and reports whether a bounded wait of the last GEMM that used `scratch` expired. */
 int b200kv_q40_check(const void* scratch, void* stream);
 

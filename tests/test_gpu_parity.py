@@ -413,6 +413,40 @@ def test_sliding_window_decode(kv, fmt, io, D, G, window):
     cache.close()
 
 
+@pytest.mark.parametrize("fmt,io,D,G", [("f16", "f16", 128, 4), ("q8_1", "f16", 128, 4), ("q8_1", "bf16", 128, 8), ("q4_0", "f16", 128, 3),
+                                        ("bf16", "bf16", 64, 1), ("f32", "f32", 64, 2), ("f16", "f16", 64, 4), ("f32", "f32", 128, 1)])
+def test_decode_with_rope_on_the_query_load(kv, fmt, io, D, G):
+    # ApplyRope (apply_rope.rs:143-176) folded into the decode kernels' query load: the same bits as rope, then attend,
+    # on both decode kernels (tensor-core and CUDA-core), and the oracle's ApplyRope + Sdpa within the attention bound.
+    Hkv, lens = 2, [1, 63, 64, 65, 700, 2049]
+    B = len(lens)
+    cache = kv.KvCache(fmt, Hkv, D, max_seqs=B, max_seq_tokens=max(lens))
+    seqs = [cache.new_seq() for _ in range(B)]
+    ks = [normal(6100 + b, (1, Hkv, lens[b], D)).astype(np_dtype(io)) for b in range(B)]
+    vs = [normal_with_outliers(6200 + b, (1, Hkv, lens[b], D)).astype(np_dtype(io)) for b in range(B)]
+    for b in range(B):
+        cache.append([seqs[b]], to_dev(ks[b]), to_dev(vs[b]))
+    q = normal(6300, (B, Hkv * G, 1, D)).astype(np_dtype(io))
+    ang = np.random.default_rng(6400).uniform(-np.pi, np.pi, size=(B, 1, D // 2)).astype(np.float32)
+    cos = np.concatenate([np.cos(ang), np.cos(ang)], -1).astype(np_dtype(io))
+    sin = np.concatenate([np.sin(ang), np.sin(ang)], -1).astype(np_dtype(io))
+    # cos / sin rows as windows of a wider table (a row stride that is not D)
+    wide_c, wide_s = torch.zeros((B, 3 * D), dtype=to_dev(cos).dtype, device="cuda"), torch.zeros((B, 3 * D), dtype=to_dev(cos).dtype, device="cuda")
+    wide_c[:, D:2 * D], wide_s[:, D:2 * D] = to_dev(cos)[:, 0], to_dev(sin)[:, 0]
+    for force_simt in (False, True):
+        cache.profile(False, force_simt=force_simt)
+        two = cache.attend(seqs, kv.rope(to_dev(q), to_dev(cos), to_dev(sin)), causal=True)
+        one = cache.attend_rope(seqs, to_dev(q), wide_c[:, D:2 * D], wide_s[:, D:2 * D])
+        cache.check()
+        assert torch.equal(one.view(torch.uint8), two.view(torch.uint8)), (force_simt, fmt)
+    q_rot = oracle.apply_rope(q, cos[:, None], sin[:, None])
+    for b in range(B):
+        err = attn_err(one[b:b + 1], io, q_rot[b:b + 1], oracle_cache_view(fmt, ks[b], io), oracle_cache_view(fmt, vs[b], io), causal=False, threads=4)
+        assert err <= TOL[io], (b, err)
+    cache.profile(False)
+    cache.close()
+
+
 def _sweep_cases():
     rng = np.random.default_rng(20260)
     cases = []

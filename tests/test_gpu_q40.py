@@ -74,3 +74,50 @@ def test_q40_errors(kv):
         kv._ck(kv.lib().b200kv_q40_gemm(None, 4, 64, None, 64, 1, 0, None, None, 4, None))
     assert kv.lib().b200kv_q40_packed_bytes(4, 33) == -1
     assert lin.gemm(torch.zeros((1, 64), device="cuda")).abs().sum().item() == 0.0
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 48, 64), (8, 64, 4096), (5, 32, 14336), (19, 48, 512), (40, 32, 2048)])
+def test_fused_producers_give_the_bits_of_the_separate_calls(kv, m, n, k):
+    # add -> RmsNorm * weight -> quantise -> GEMM and Silu(gate) * up -> quantise -> GEMM, fused into the quantiser, against
+    # the same ops launched one by one, and the first of them against the CPU restatements composed the same way
+    w = normal_with_outliers(31, (n, k)).astype(np.float32)
+    sc, pk = oracle.q4_0_quant(w)
+    lin = kv.Q40Linear(torch.from_numpy(ggml_blocks(sc, pk)).cuda(), max_m=64)
+    scratch = torch.empty(kv.Q40Linear.scratch_bytes(k, m), dtype=torch.uint8, device="cuda")
+    x = torch.from_numpy(normal_with_outliers(32, (m, k)).astype(np.float32)).cuda()
+    res = torch.from_numpy(normal(33, (m, k)).astype(np.float32)).cuda()
+    gain = torch.from_numpy((normal(34, (k,)) * 0.1 + 1.0).astype(np.float32)).cuda()
+    eps = 1e-5
+    # separate launches
+    s = kv.add(x, res)
+    want_norm = lin.gemm(kv.rms_norm(s, eps, weight=gain))
+    # fused, the sum written in place of x
+    x_io = x.clone()
+    kv.q40_add_rms_norm_quantize(x_io, scratch, eps, weight=gain, residual=res, x_out=x_io)
+    got = lin.gemm_quantized(m, scratch=scratch)
+    lin.check(scratch)
+    assert torch.equal(x_io, s)
+    assert got.cpu().numpy().tobytes() == want_norm.cpu().numpy().tobytes()
+    # fused, nothing written back; and without residual or weight
+    kv.q40_add_rms_norm_quantize(x, scratch, eps, weight=gain, residual=res)
+    assert torch.equal(lin.gemm_quantized(m, scratch=scratch), want_norm)
+    kv.q40_add_rms_norm_quantize(s, scratch, eps)
+    assert torch.equal(lin.gemm_quantized(m, scratch=scratch), lin.gemm(kv.rms_norm(s, eps)))
+    # the oracle: its RmsNorm folds the squares left to right (1e-5 apart from the tree here), so compare as values
+    ref = oracle.w4a8_gemm(sc, pk, (oracle.rms_norm(s.cpu().numpy(), eps) * gain.cpu().numpy()).astype(np.float32))
+    err = np.abs(got.cpu().numpy() - ref).max() / max(np.abs(ref).max(), 1e-30)
+    assert err < 2e-2, err  # quantiser flips of single codes; the bit-exact check is the one against the separate launches
+
+    # gated activation: windows of one wide buffer, as the stacked gate / up GEMM leaves them
+    gu = torch.from_numpy(normal(35, (m, 2 * k)).astype(np.float32) * 3).cuda()
+    want_act = lin.gemm(kv.silu_mul(gu[:, :k].contiguous(), gu[:, k:].contiguous()))
+    kv.q40_silu_mul_quantize(gu[:, :k], gu[:, k:], scratch)
+    got_act = lin.gemm_quantized(m, scratch=scratch)
+    assert torch.equal(got_act, want_act)
+    ref_act = oracle.w4a8_gemm(sc, pk, (oracle.silu(gu[:, :k].cpu().numpy()) * gu[:, k:].cpu().numpy()).astype(np.float32))
+    assert got_act.cpu().numpy().tobytes() == ref_act.tobytes()  # Silu and the product are bit-exact restatements
+    # one quantisation feeding two matrices
+    kv.q40_quantize(x, scratch)
+    assert torch.equal(lin.gemm_quantized(m, scratch=scratch), lin.gemm(x))
+    assert torch.equal(lin.gemm_quantized(m, scratch=scratch), lin.gemm(x))
+    lin.check(scratch)

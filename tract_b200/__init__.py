@@ -26,7 +26,8 @@ EXPORTS = [
     "b200kv_profile_read", "b200kv_attend_static_scratch", "b200kv_export_kivi", "b200kv_append_rope", "b200kv_rope",
     "b200kv_q40_packed_bytes", "b200kv_q40_pack", "b200kv_q40_scratch_bytes", "b200kv_q40_gemm", "b200kv_q40_check",
     "b200kv_rms_norm", "b200kv_silu_mul", "b200kv_add", "b200kv_argmax", "b200kv_gather_rows", "b200kv_cast",
-    "b200kv_attend_window", "b200kv_trim",
+    "b200kv_attend_window", "b200kv_trim", "b200kv_attend_rope", "b200kv_q40_quantize", "b200kv_q40_gemm_quantized",
+    "b200kv_q40_silu_mul_quantize", "b200kv_q40_add_rms_norm_quantize",
 ]
 KERNEL_NAMES = {0: "table_scatter", 1: "append", 2: "decode", 3: "combine", 4: "export", 5: "sdpa_dense", 6: "prefill"}
 
@@ -79,6 +80,7 @@ def lib():
         L.b200kv_profile_read.argtypes = [vp, i32, i32p, C.POINTER(C.c_float), i32p]
         L.b200kv_sdpa.argtypes = [vp, i64p, vp, i64p, vp, i64p, vp, i64p, i32, vp, i64p, i32, i32, i32, i32, i32, i32,
                                   i32, C.c_float, i32, vp]
+        L.b200kv_attend_rope.argtypes = [vp, i32, i32p, i32, vp, i64p, vp, vp, i64, vp, i64p, i32, C.c_float, vp]
         L.b200kv_attend_window.argtypes = [vp, i32, i32p, i32, vp, i64p, vp, i64p, i32, C.c_float, i64, vp]
         L.b200kv_trim.argtypes = [vp, i32, i64]
         _lib = L
@@ -264,6 +266,21 @@ class KvCache:
                                        _strides(out, 3), _dtype_code(q), C.c_float(scale or 0.0), C.c_int64(window), _stream()))
         return out
 
+    def attend_rope(self, seqs, q, cos, sin, scale=None, out=None):
+        """Decode attention of ApplyRope(q, cos, sin) (q: [n_seqs, Hq, 1, D]; cos, sin: [n_seqs, 1, D] or [n_seqs, D])."""
+        import torch
+
+        assert q.dim() == 4 and q.shape[0] == len(seqs) and q.shape[2] == 1
+        cos, sin = cos.reshape(len(seqs), -1), sin.reshape(len(seqs), -1)
+        assert cos.dtype == q.dtype and sin.dtype == q.dtype and cos.stride(1) == 1 and sin.stride(1) == 1
+        assert cos.stride(0) == sin.stride(0) and cos.shape[1] == q.shape[3]
+        if out is None:
+            out = torch.empty_like(q, memory_format=torch.contiguous_format)
+        _ck(lib().b200kv_attend_rope(self._h, len(seqs), _ids(seqs), q.shape[1], q.data_ptr(), _strides(q, 3), cos.data_ptr(),
+                                     sin.data_ptr(), C.c_int64(cos.stride(0)), out.data_ptr(), _strides(out, 3), _dtype_code(q),
+                                     C.c_float(scale or 0.0), _stream()))
+        return out
+
     def fork(self, seq) -> int:
         s = C.c_int32()
         _ck(lib().b200kv_fork(self._h, seq, C.byref(s), _stream()))
@@ -331,8 +348,60 @@ class Q40Linear:
                                       C.c_void_p(out.data_ptr()), C.c_int64(out.stride(0)), _stream()))
         return out
 
-    def check(self):
-        _ck(lib().b200kv_q40_check(C.c_void_p(self.scratch.data_ptr()), _stream()))
+    def gemm_quantized(self, m, out=None, scratch=None):
+        """The product with the m activation rows that `scratch` already holds in quantised form (q40_quantize,
+        q40_silu_mul_quantize or q40_add_rms_norm_quantize on the same stream)."""
+        import torch
+
+        scratch = self.scratch if scratch is None else scratch
+        assert scratch.numel() >= self.scratch_bytes(self.k, m)
+        if out is None:
+            out = torch.empty((m, self.n), dtype=torch.float32, device=self.packed.device)
+        with torch.cuda.device(self.packed.device):
+            _ck(lib().b200kv_q40_gemm_quantized(C.c_void_p(self.packed.data_ptr()), C.c_int64(self.n), C.c_int64(self.k), int(m),
+                                                C.c_void_p(scratch.data_ptr()), C.c_void_p(out.data_ptr()), C.c_int64(out.stride(0)), _stream()))
+        return out
+
+    def check(self, scratch=None):
+        _ck(lib().b200kv_q40_check(C.c_void_p((self.scratch if scratch is None else scratch).data_ptr()), _stream()))
+
+
+def q40_quantize(a, scratch):
+    """Q4_0::quantize_row_q8 of the rows of `a` ([M, K], rows contiguous) into `scratch` (Q40Linear.scratch_bytes(K, M))."""
+    import torch
+
+    assert a.dim() == 2 and a.stride(1) == 1 and scratch.numel() >= Q40Linear.scratch_bytes(a.shape[1], a.shape[0])
+    with torch.cuda.device(a.device):
+        _ck(lib().b200kv_q40_quantize(C.c_void_p(a.data_ptr()), C.c_int64(a.stride(0)), int(a.shape[0]), _dtype_code(a), C.c_int64(a.shape[1]),
+                                      C.c_void_p(scratch.data_ptr()), _stream()))
+
+
+def q40_silu_mul_quantize(gate, up, scratch):
+    """scratch <- quantised Silu(gate) * up; gate, up: [M, K] windows with contiguous rows."""
+    import torch
+
+    assert gate.dim() == 2 and gate.shape == up.shape and gate.dtype == up.dtype and gate.stride(1) == 1 and up.stride(1) == 1
+    assert scratch.numel() >= Q40Linear.scratch_bytes(gate.shape[1], gate.shape[0])
+    with torch.cuda.device(gate.device):
+        _ck(lib().b200kv_q40_silu_mul_quantize(C.c_void_p(gate.data_ptr()), C.c_int64(gate.stride(0)), C.c_void_p(up.data_ptr()),
+                                               C.c_int64(up.stride(0)), int(gate.shape[0]), _dtype_code(gate), C.c_int64(gate.shape[1]),
+                                               C.c_void_p(scratch.data_ptr()), _stream()))
+
+
+def q40_add_rms_norm_quantize(x, scratch, eps, weight=None, residual=None, x_out=None):
+    """v = x + residual (stored to x_out when given; x_out may be x); scratch <- quantised RmsNorm(v, eps) * weight.  f32."""
+    import torch
+
+    f32 = torch.float32
+    assert x.dim() == 2 and x.dtype == f32 and x.stride(1) == 1 and scratch.numel() >= Q40Linear.scratch_bytes(x.shape[1], x.shape[0])
+    for t in (residual, x_out):
+        assert t is None or (t.dtype == f32 and t.shape == x.shape and t.stride(1) == 1)
+    assert weight is None or (weight.dtype == f32 and weight.numel() == x.shape[1] and weight.is_contiguous())
+    ptr = lambda t: C.c_void_p(t.data_ptr() if t is not None else 0)
+    st = lambda t: C.c_int64(t.stride(0) if t is not None else 0)
+    with torch.cuda.device(x.device):
+        _ck(lib().b200kv_q40_add_rms_norm_quantize(ptr(x), st(x), ptr(residual), st(residual), ptr(weight), C.c_float(eps), ptr(x_out), st(x_out),
+                                                   int(x.shape[0]), C.c_int64(x.shape[1]), C.c_void_p(scratch.data_ptr()), _stream()))
 
 
 def rms_norm(x, eps, weight=None, out=None):

@@ -82,3 +82,23 @@ extern "C" int b200kv_attend_window(b200kv_cache* c, int32_t n_seqs, const int32
     DeviceGuard guard(c->cfg.device);
     return launch_decode(c, n_seqs, seqs, n_q_heads, q, q_strides, out, out_strides, dtype, scale, (cudaStream_t)stream_, window);
 }
+
+// Decode attention with ApplyRope (transformers/src/ops/apply_rope.rs:143-176) folded into the query load: what
+// b200kv_rope on q followed by b200kv_attend would give, bit for bit, in one launch less.  cos / sin hold one row of D
+// values of type `dtype` per sequence (the position of its newest token); rope_stride is the distance between rows.
+extern "C" int b200kv_attend_rope(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t n_q_heads, const void* q,
+                                  const int64_t q_strides[3], const void* cos, const void* sin, int64_t rope_stride, void* out,
+                                  const int64_t out_strides[3], int32_t dtype, float scale, void* stream_) {
+    if (validate_seqs(c, n_seqs, seqs) != B200KV_OK) return B200KV_KO;
+    if (!c->L.has_v) return fail("this cache holds one tensor only: attention needs K and V");
+    if (fmt_is_kivi(c->L.fmt)) return fail("a KIVI cache takes its query already rotated: b200kv_rope, then b200kv_attend");
+    if (!q || !out || !cos || !sin || !q_strides || !out_strides) return fail("null tensor or strides");
+    if (n_q_heads <= 0 || n_q_heads % c->L.Hkv != 0)
+        return fail("n_q_heads (%d) must be a positive multiple of n_kv_heads (%d)", n_q_heads, c->L.Hkv);
+    if (dtype < B200KV_F32 || dtype > B200KV_BF16) return fail("unknown dtype %d", dtype);
+    if (c->L.D % 2 != 0) return fail("ApplyRope needs an even head_dim");
+    if (scale <= 0.f) scale = 1.0f / sqrtf((float)c->L.D);
+    DeviceGuard guard(c->cfg.device);
+    const QueryRope rope{cos, sin, rope_stride};
+    return launch_decode(c, n_seqs, seqs, n_q_heads, q, q_strides, out, out_strides, dtype, scale, (cudaStream_t)stream_, 0, &rope);
+}

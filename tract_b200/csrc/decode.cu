@@ -109,13 +109,12 @@ __global__ void __launch_bounds__(128) decode_kernel(DecodeParams p, const __gri
 #pragma unroll
     for (int g = 0; g < GT; g++) {
         int head = kvh * p.G + min(g0 + g, p.G - 1);
-        const int64_t base = (int64_t)w.batch * p.qb + (int64_t)head * p.qh;
 #pragma unroll
         for (int pc = 0; pc < Gm::NPC; pc++) {
             int rb = pc * (8 * Gm::PB) + sub * Gm::PB;
 #pragma unroll
             for (int e = 0; e < Gm::EPP; e++)
-                qr[g][pc * Gm::EPP + e] = ld_as_f32(p.q, p.dtype, base + row_channel<FMT>(rb, e, Gm::PB));
+                qr[g][pc * Gm::EPP + e] = load_query(p, D, w.batch, head, row_channel<FMT>(rb, e, Gm::PB));
         }
     }
 
@@ -404,7 +403,8 @@ int launch_combine(const DecodeParams& p, const int32_t* batch_info, void* out, 
 }
 
 int launch_decode(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t n_q_heads, const void* q,
-                  const int64_t* qs, void* out, const int64_t* os, int32_t dtype, float scale, cudaStream_t stream, int64_t window) {
+                  const int64_t* qs, void* out, const int64_t* os, int32_t dtype, float scale, cudaStream_t stream, int64_t window,
+                  const QueryRope* rope) {
     const int Hkv = c->L.Hkv, D = c->L.D, G = n_q_heads / Hkv;
     const bool use_mma = decode_mma_supported(c->L.fmt, D, dtype) && !c->force_simt;
     const int GT = use_mma ? 8 : (G == 1 ? 1 : 4), nz = (G + GT - 1) / GT;
@@ -462,6 +462,7 @@ int launch_decode(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t 
     DecodeParams p{};
     p.pool = c->pool, p.table = c->d_table, p.items = (const WorkItem*)d, p.status = c->d_status;
     p.q = q, p.qb = qs[0], p.qh = qs[1];
+    if (rope) p.q_cos = rope->cos, p.q_sin = rope->sin, p.rope_b = rope->stride_b;
     p.part_o = (float*)c->ws;
     p.part_ml = p.part_o + n_part * D;
     p.page_bytes = c->L.page_bytes, p.n_pages = (int32_t)c->n_pages, p.max_pages_per_seq = c->max_pages_per_seq;

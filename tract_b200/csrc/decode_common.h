@@ -22,6 +22,10 @@ struct DecodeParams {
     int* status;
     const void* q;
     int64_t qb, qh;  // q strides {batch, head} in elements
+    // ApplyRope on the query as it is loaded (null: q is used as it is): rows of D values of type dtype, one per batch entry
+    const void* q_cos;
+    const void* q_sin;
+    int64_t rope_b;  // cos / sin stride between batch entries, in elements
     float* part_o;   // [item][Hkv][G][D]   unnormalised partial outputs
     float* part_ml;  // [item][Hkv][G][2]   running max (natural-log units), running sum
     int64_t page_bytes;
@@ -40,6 +44,17 @@ struct InlineBatch {
     int4 ent[INLINE_BATCH];
     int32_t first[INLINE_BATCH];  // first visible token of each entry (0: the whole sequence)
 };
+
+// Channel `ch` of the query row of (batch, head), after ApplyRope when the call carries cos / sin.  The rotated value is
+// rounded to dtype after every operation, so it equals what a separate rope kernel would have stored and this load
+// would have read back.
+__device__ inline float load_query(const DecodeParams& p, int D, int batch, int head, int ch) {
+    const int64_t row = (int64_t)batch * p.qb + (int64_t)head * p.qh;
+    if (!p.q_cos) return ld_as_f32(p.q, p.dtype, row + ch);
+    const int esz = p.dtype == B200KV_F32 ? 4 : 2;
+    return rope_row_elem((const uint8_t*)p.q + row * esz, (const uint8_t*)p.q_cos + (int64_t)batch * p.rope_b * esz,
+                         (const uint8_t*)p.q_sin + (int64_t)batch * p.rope_b * esz, p.dtype, D, ch);
+}
 
 __host__ __device__ inline WorkItem make_work_item(const int4& e, int batch, int k, int first = 0) {
     const int p0 = first / PAGE_TOKENS;  // pages before the first visible token are not walked (they may have been freed)

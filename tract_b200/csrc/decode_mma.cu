@@ -95,7 +95,7 @@ __global__ void __launch_bounds__(128, MGeo<FMT>::MIN_CTAS) decode_mma_kernel(De
     for (int idx = tid; idx < 8 * MD; idx += 128) {
         int g = idx / MD, ch = idx % MD;
         float v = 0.f;
-        if (g < ng) v = ld_as_f32(p.q, p.dtype, (int64_t)w.batch * p.qb + (int64_t)(kvh * p.G + g0 + g) * p.qh + ch);
+        if (g < ng) v = load_query(p, MD, w.batch, kvh * p.G + g0 + g, ch);
         if (QUANT) v = __half2float(__float2half_rn(v));  // the operand the tensor cores will see
         q_s[idx] = v;
     }

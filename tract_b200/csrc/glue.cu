@@ -10,32 +10,10 @@
 //             every operation rounded on its own, in the reference's order: bit for bit in f32.  The product with `up` is
 //             the Mul that follows in the graph (cu/element_wise.cu, cu/binary.cu).
 //   argmax    first index of the row maximum (core/src/ops/nn/reduce.rs ArgMax { last: false }).
+#include "glue_math.cuh"
 #include "internal.h"
 
 namespace b200kv {
-
-__device__ inline float clamp_keep_nan(float x, float lo, float hi) {  // f32::clamp: a NaN stays a NaN
-    return x != x ? x : fminf(fmaxf(x, lo), hi);
-}
-
-// linalg/src/generic/sigmoid.rs:11-45
-__device__ inline float ssigmoid(float x) {
-    x = clamp_keep_nan(x, -18.6f, 18.6f);
-    const float x2 = __fmul_rn(x, x);
-    float p = -4.433153405e-18f;
-    p = __fadd_rn(__fmul_rn(x2, p), 1.169974371e-14f);
-    p = __fadd_rn(__fmul_rn(x2, p), -1.875289645e-11f);
-    p = __fadd_rn(__fmul_rn(x2, p), 4.257889523e-8f);
-    p = __fadd_rn(__fmul_rn(x2, p), 0.00004811817576f);
-    p = __fadd_rn(__fmul_rn(x2, p), 0.008163842030f);
-    p = __fadd_rn(__fmul_rn(x2, p), 0.2499999971f);
-    p = __fmul_rn(p, x);
-    float q = 3.922935744e-6f;
-    q = __fadd_rn(__fmul_rn(x2, q), 0.001524872358f);
-    q = __fadd_rn(__fmul_rn(x2, q), 0.1159886749f);
-    q = __fadd_rn(__fmul_rn(x2, q), 1.0f);
-    return clamp_keep_nan(__fadd_rn(__fdiv_rn(p, q), 0.5f), 0.f, 1.f);
-}
 
 // One CTA per row.
 __global__ void rms_norm_kernel(const void* __restrict__ x, int64_t x_stride, const void* __restrict__ w, void* __restrict__ out,
@@ -47,18 +25,7 @@ __global__ void rms_norm_kernel(const void* __restrict__ x, int64_t x_stride, co
         const float v = ld_as_f32(x, dtype, row * x_stride + i);
         ss = fmaf(v, v, ss);
     }
-#pragma unroll
-    for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = ss;
-    __syncthreads();
-    if (threadIdx.x < 32) {
-        float t = threadIdx.x < (blockDim.x >> 5) ? part[threadIdx.x] : 0.f;
-#pragma unroll
-        for (int o = 16; o; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
-        if (threadIdx.x == 0) part[0] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(t, (float)d), eps)));
-    }
-    __syncthreads();
-    const float inv = part[0];
+    const float inv = rms_norm_inv(ss, part, d, eps);
     for (int i = threadIdx.x; i < d; i += blockDim.x) {
         float v = __fmul_rn(ld_as_f32(x, dtype, row * x_stride + i), inv);
         if (w) v = __fmul_rn(round_to_dtype(v, dtype), ld_as_f32(w, dtype, i));  // RmsNorm's result is a tensor of `dtype` before the Mul
@@ -136,7 +103,7 @@ extern "C" int b200kv_rms_norm(const void* x, int64_t x_stride, const void* weig
     if (!x || !out) return fail("null tensor");
     if (rows <= 0 || d <= 0) return fail("rows and d must be positive");
     if (check_dtype(dtype) != B200KV_OK) return B200KV_KO;
-    const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
+    const int threads = rms_norm_threads(d);
     rms_norm_kernel<<<(unsigned)rows, threads, 0, (cudaStream_t)stream>>>(x, x_stride, weight, out, out_stride, d, eps, dtype);
     B200KV_CUDA(cudaGetLastError());
     return B200KV_OK;

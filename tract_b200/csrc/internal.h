@@ -127,9 +127,14 @@ struct ProfScope {
 };
 
 // decode.cu
+struct QueryRope {  // ApplyRope of the query inside the decode kernels: one cos / sin row of D values per batch entry
+    const void* cos;
+    const void* sin;
+    int64_t stride_b;  // elements
+};
 int launch_decode(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t n_q_heads, const void* q,
                   const int64_t* q_strides, void* out, const int64_t* out_strides, int32_t dtype, float scale,
-                  cudaStream_t stream, int64_t window = 0);
+                  cudaStream_t stream, int64_t window = 0, const QueryRope* rope = nullptr);
 // sdpa_dense.cu
 int launch_sdpa_dense(const void* q, const int64_t* qs, const void* k, const int64_t* ks, const void* v,
                       const int64_t* vs, const void* mask, const int64_t* ms, int mask_dtype, void* out,

@@ -14,6 +14,7 @@
 // of one mma.sync.m16n8k32 (u8 nibbles x s8 activations -> s32: 16 rows x 8 activation rows of exact dot products;
 // the -8 of the nibbles is removed with the block's activation sum), and adds the 8 contributions to the 16 x 8 f32
 // accumulators, which travel from warp to warp in stage order -- the order the reference adds the blocks in.
+#include "glue_math.cuh"
 #include "internal.h"
 
 namespace b200kv {
@@ -48,21 +49,12 @@ __global__ void q40_pack_kernel(const uint8_t* __restrict__ blocks, int64_t n, i
     for (int i = 0; i < 4; i++) q[i] = (uint32_t)w[1 + 2 * i] | ((uint32_t)w[2 + 2 * i] << 16);
 }
 
-// ---- activation quantiser: one warp per (block, activation row slot) ----------------------------------------------
-__global__ void q40_quant_act_kernel(const void* __restrict__ a, int64_t a_stride, int32_t m, int32_t dtype, int64_t nb,
-                                     uint8_t* __restrict__ act, int* __restrict__ status) {
-    grid_launch_dependents();  // the GEMM may be scheduled: it starts pulling weights and waits for this grid before it reads `act`
-    if (blockIdx.x == 0 && threadIdx.x == 0) *status = 0;
-    const int lane = threadIdx.x & 31;
-    const int64_t wid = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    const int64_t groups = (m + 7) / 8;
-    if (wid >= groups * nb * 8) return;
-    const int slot = (int)(wid % 8);
-    const int64_t b = (wid / 8) % nb, g = wid / (8 * nb);
-    const int64_t mi = g * 8 + slot;
-    uint8_t* dst = act + (g * nb + b) * Q_ACT_BLOCK;
-    float x = 0.f;
-    if (mi < m) x = ld_as_f32(a, dtype, mi * a_stride + b * QK + lane);
+// ---- activation quantisers --------------------------------------------------------------------------------------
+// Q4_0::quantize_row_q8 (q4_0.rs:199-222) for one block: the 32 lanes of a warp hold its 32 values.  Writes the codes,
+// the scale and the code sum of activation row slot `slot` into the block's record.  `valid` false (a slot past the last
+// row): zero codes, scale 0.
+__device__ inline void q40_quantize_block(float x, bool valid, uint8_t* dst, int slot, int lane) {
+    if (!valid) x = 0.f;
     float amax = fabsf(x);
 #pragma unroll
     for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));  // fmaxf ignores a NaN operand, as f32::max does
@@ -74,8 +66,65 @@ __global__ void q40_quant_act_kernel(const void* __restrict__ a, int64_t a_strid
     const int sum = __reduce_add_sync(0xffffffffu, q);
     dst[(lane >> 4) * 128 + slot * 16 + (lane & 15)] = (uint8_t)(int8_t)q;
     if (lane == 0) {
-        ((float*)(dst + 256))[slot] = mi < m ? scale : 0.f;
+        ((float*)(dst + 256))[slot] = valid ? scale : 0.f;
         ((int32_t*)(dst + 288))[slot] = sum;
+    }
+}
+
+// One warp per (block, activation row slot).  With `up`, the value quantised is Silu(a) * up (the gate of a gated FFN), each
+// of the two ops rounded to `dtype` as the stand-alone kernels round them.
+__global__ void q40_quant_act_kernel(const void* __restrict__ a, int64_t a_stride, const void* __restrict__ up, int64_t up_stride, int32_t m,
+                                     int32_t dtype, int64_t nb, uint8_t* __restrict__ act, int* __restrict__ status) {
+    grid_launch_dependents();  // the GEMM may be scheduled: it starts pulling weights and waits for this grid before it reads `act`
+    if (blockIdx.x == 0 && threadIdx.x == 0) *status = 0;
+    const int lane = threadIdx.x & 31;
+    const int64_t wid = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int64_t groups = (m + 7) / 8;
+    if (wid >= groups * nb * 8) return;
+    const int slot = (int)(wid % 8);
+    const int64_t b = (wid / 8) % nb, g = wid / (8 * nb);
+    const int64_t mi = g * 8 + slot;
+    float x = 0.f;
+    if (mi < m) {
+        x = ld_as_f32(a, dtype, mi * a_stride + b * QK + lane);
+        if (up) {
+            const float s = round_to_dtype(__fmul_rn(x, ssigmoid(x)), dtype);
+            x = round_to_dtype(__fmul_rn(s, ld_as_f32(up, dtype, mi * up_stride + b * QK + lane)), dtype);
+        }
+    }
+    q40_quantize_block(x, mi < m, act + (g * nb + b) * Q_ACT_BLOCK, slot, lane);
+}
+
+// One CTA per activation row slot: v = x (+ residual), stored to x_out when given; then RmsNorm(v) * weight, quantised.
+// The same arithmetic, in the same order, as the add, RmsNorm and quantiser kernels run one after the other.
+__global__ void q40_norm_quant_kernel(const float* __restrict__ x, int64_t x_stride, const float* residual, int64_t res_stride,
+                                      const float* __restrict__ weight, float eps, float* x_out, int64_t xo_stride, int32_t m, int d,
+                                      uint8_t* __restrict__ act, int* __restrict__ status) {
+    __shared__ float part[32];
+    grid_launch_dependents();
+    if (blockIdx.x == 0 && threadIdx.x == 0) *status = 0;
+    const int64_t mi = blockIdx.x, nb = d / QK;
+    const int slot = (int)(mi % 8), lane = threadIdx.x & 31;
+    uint8_t* dst = act + (mi / 8) * nb * Q_ACT_BLOCK;
+    const bool valid = mi < m;
+    float ss = 0.f;
+    if (valid)
+        for (int i = threadIdx.x; i < d; i += blockDim.x) {
+            float v = x[mi * x_stride + i];
+            if (residual) v = __fadd_rn(v, residual[mi * res_stride + i]);
+            if (x_out) x_out[mi * xo_stride + i] = v;
+            ss = fmaf(v, v, ss);
+        }
+    const float inv = rms_norm_inv(ss, part, d, eps);
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {  // d and the CTA are multiples of 32: a warp covers one block per turn
+        float v = 0.f;
+        if (valid) {
+            // the thread that stored x_out[i] reads it back; without x_out the sum is formed again from the inputs
+            v = x_out ? x_out[mi * xo_stride + i] : (residual ? __fadd_rn(x[mi * x_stride + i], residual[mi * res_stride + i]) : x[mi * x_stride + i]);
+            v = __fmul_rn(v, inv);
+            if (weight) v = __fmul_rn(v, weight[i]);
+        }
+        q40_quantize_block(v, valid, dst + (int64_t)(i / QK) * Q_ACT_BLOCK, slot, lane);
     }
 }
 
@@ -279,20 +328,62 @@ extern "C" int b200kv_q40_pack(const void* blocks, int64_t n, int64_t k, void* p
     return B200KV_OK;
 }
 
-extern "C" int b200kv_q40_gemm(const void* packed, int64_t n, int64_t k, const void* a, int64_t a_stride, int32_t m, int32_t dtype,
-                               void* scratch, float* out, int64_t out_stride, void* stream_) {
-    if (!packed || !a || !scratch || !out) return fail("null pointer");
-    if (n <= 0 || k <= 0 || k % QK) return fail("W4A8 GEMM needs K a multiple of %d, got %lld", QK, (long long)k);
+static int q40_check_shape(const void* scratch, int64_t k, int32_t m) {
+    if (!scratch) return fail("null pointer");
+    if (k <= 0 || k % QK) return fail("W4A8 GEMM needs K a multiple of %d, got %lld", QK, (long long)k);
     if (m <= 0) return fail("m must be positive");
+    if ((uintptr_t)scratch % 16) return fail("scratch must be 16-byte aligned");
+    return B200KV_OK;
+}
+
+extern "C" int b200kv_q40_quantize(const void* a, int64_t a_stride, int32_t m, int32_t dtype, int64_t k, void* scratch, void* stream) {
+    if (q40_check_shape(scratch, k, m) != B200KV_OK) return B200KV_KO;
+    if (!a) return fail("null pointer");
     if (dtype < B200KV_F32 || dtype > B200KV_BF16) return fail("unknown dtype %d", dtype);
-    if ((uintptr_t)packed % 16 || (uintptr_t)scratch % 16) return fail("packed weights and scratch must be 16-byte aligned");
-    if (a_stride < k || out_stride < n) return fail("strides shorter than the rows");
+    if (a_stride < k) return fail("strides shorter than the rows");
+    const int64_t nb = k / QK, warps = (int64_t)((m + 7) / 8) * nb * 8;
+    q40_quant_act_kernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(a, a_stride, nullptr, 0, m, dtype, nb,
+                                                                                            (uint8_t*)scratch + Q_HEADER, (int*)scratch);
+    B200KV_CUDA(cudaGetLastError());
+    return B200KV_OK;
+}
+
+extern "C" int b200kv_q40_silu_mul_quantize(const void* gate, int64_t gate_stride, const void* up, int64_t up_stride, int32_t m, int32_t dtype,
+                                            int64_t k, void* scratch, void* stream) {
+    if (q40_check_shape(scratch, k, m) != B200KV_OK) return B200KV_KO;
+    if (!gate || !up) return fail("null pointer");
+    if (dtype < B200KV_F32 || dtype > B200KV_BF16) return fail("unknown dtype %d", dtype);
+    if (gate_stride < k || up_stride < k) return fail("strides shorter than the rows");
+    const int64_t nb = k / QK, warps = (int64_t)((m + 7) / 8) * nb * 8;
+    q40_quant_act_kernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(gate, gate_stride, up, up_stride, m, dtype, nb,
+                                                                                            (uint8_t*)scratch + Q_HEADER, (int*)scratch);
+    B200KV_CUDA(cudaGetLastError());
+    return B200KV_OK;
+}
+
+extern "C" int b200kv_q40_add_rms_norm_quantize(const float* x, int64_t x_stride, const float* residual, int64_t residual_stride,
+                                                const float* weight, float eps, float* x_out, int64_t x_out_stride, int32_t m, int64_t k,
+                                                void* scratch, void* stream) {
+    if (q40_check_shape(scratch, k, m) != B200KV_OK) return B200KV_KO;
+    if (!x) return fail("null pointer");
+    if (k > INT32_MAX) return fail("row too long");
+    if (x_stride < k || (residual && residual_stride < k) || (x_out && x_out_stride < k)) return fail("strides shorter than the rows");
+    q40_norm_quant_kernel<<<(unsigned)((m + 7) / 8 * 8), rms_norm_threads((int)k), 0, (cudaStream_t)stream>>>(
+        x, x_stride, residual, residual_stride, weight, eps, x_out, x_out_stride, m, (int)k, (uint8_t*)scratch + Q_HEADER, (int*)scratch);
+    B200KV_CUDA(cudaGetLastError());
+    return B200KV_OK;
+}
+
+extern "C" int b200kv_q40_gemm_quantized(const void* packed, int64_t n, int64_t k, int32_t m, void* scratch, float* out, int64_t out_stride,
+                                         void* stream_) {
+    if (q40_check_shape(scratch, k, m) != B200KV_OK) return B200KV_KO;
+    if (!packed || !out) return fail("null pointer");
+    if (n <= 0) return fail("n must be positive");
+    if ((uintptr_t)packed % 16) return fail("packed weights must be 16-byte aligned");
+    if (out_stride < n) return fail("strides shorter than the rows");
     cudaStream_t stream = (cudaStream_t)stream_;
     const int64_t nb = k / QK, groups = (m + 7) / 8;
     uint8_t* act = (uint8_t*)scratch + Q_HEADER;
-    const int64_t warps = groups * nb * 8;
-    q40_quant_act_kernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, stream>>>(a, a_stride, m, dtype, nb, act, (int*)scratch);
-    B200KV_CUDA(cudaGetLastError());
     Q40Gemm p{};
     p.packed = (const uint8_t*)packed, p.act = act, p.out = out, p.status = (int*)scratch;
     p.n = n, p.nb = nb, p.out_stride = out_stride, p.m = m;
@@ -330,6 +421,14 @@ extern "C" int b200kv_q40_gemm(const void* packed, int64_t n, int64_t k, const v
         else B200KV_CUDA(launch_after_predecessor(q40_gemm_kernel<2, 4>, grid, block, smem, stream, p));
     }
     return B200KV_OK;
+}
+
+extern "C" int b200kv_q40_gemm(const void* packed, int64_t n, int64_t k, const void* a, int64_t a_stride, int32_t m, int32_t dtype,
+                               void* scratch, float* out, int64_t out_stride, void* stream) {
+    if (!packed || !out || n <= 0 || (uintptr_t)packed % 16 || out_stride < n)  // nothing is enqueued for a call that cannot finish
+        return fail("W4A8 GEMM: null pointer, packed weights not 16-byte aligned, or out_stride shorter than n");
+    if (b200kv_q40_quantize(a, a_stride, m, dtype, k, scratch, stream) != B200KV_OK) return B200KV_KO;
+    return b200kv_q40_gemm_quantized(packed, n, k, m, scratch, out, out_stride, stream);
 }
 
 extern "C" int b200kv_q40_check(const void* scratch, void* stream) {

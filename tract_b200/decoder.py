@@ -62,6 +62,15 @@ class Decoder:
                 self.host_blocks[name] = blocks.cpu().numpy()  # small models: kept for the parity tests
             return kv.Q40Linear(blocks.to(dev), max_m=n_seqs)
 
+        def linear_rows(names, n, k):
+            """Matrices that read the same activation (gate and up), stacked row-wise into one: one quantisation, one launch."""
+            parts = []
+            for name in names:
+                parts.append(weights[name].to(dev) if weights is not None else random_q40_blocks(torch, n, k, gen, dev))
+                if weights is None and n * k <= 1 << 22:
+                    self.host_blocks[name] = parts[-1].cpu().numpy()
+            return kv.Q40Linear(torch.cat(parts, 0).contiguous(), max_m=n_seqs)
+
         def norm_weight(name):
             w = weights[name] if weights is not None else (torch.rand(sh.hidden, generator=gen, device=dev) * 0.2 + 0.9)
             return w.to(dev, torch.float32)
@@ -71,7 +80,7 @@ class Decoder:
             self.layers.append(dict(
                 attn_norm=norm_weight(f"l{i}.attn_norm"), ffn_norm=norm_weight(f"l{i}.ffn_norm"),
                 wqkv=linear(f"l{i}.wqkv", qkv_rows, sh.hidden), wo=linear(f"l{i}.wo", sh.hidden, sh.n_q_heads * sh.head_dim),
-                wg=linear(f"l{i}.wg", sh.ffn, sh.hidden), wu=linear(f"l{i}.wu", sh.ffn, sh.hidden), wd=linear(f"l{i}.wd", sh.hidden, sh.ffn),
+                wgu=linear_rows([f"l{i}.wg", f"l{i}.wu"], sh.ffn, sh.hidden), wd=linear(f"l{i}.wd", sh.hidden, sh.ffn),
                 cache=kv.KvCache(kv_format, sh.n_kv_heads, sh.head_dim, max_seqs=n_seqs, max_seq_tokens=max_tokens)))
         self.final_norm = norm_weight("final_norm")
         self.lm_head = linear("lm_head", sh.vocab, sh.hidden)
@@ -84,12 +93,17 @@ class Decoder:
         self.sin = torch.cat([ang.sin(), ang.sin()], 1).to(self.kv_dtype).contiguous()
         B, f32 = n_seqs, torch.float32
         z = lambda *s, dt=f32: torch.zeros(s, dtype=dt, device=dev)
-        self.x, self.xn = z(B, sh.hidden), z(B, sh.hidden)
+        self.x = z(B, sh.hidden)  # the residual stream
         self.qkv = z(B, qkv_rows)
-        self.q16, self.q16r = z(B, sh.n_q_heads, 1, sh.head_dim, dt=self.kv_dtype), z(B, sh.n_q_heads, 1, sh.head_dim, dt=self.kv_dtype)
-        self.k16, self.v16 = z(B, sh.n_kv_heads, 1, sh.head_dim, dt=self.kv_dtype), z(B, sh.n_kv_heads, 1, sh.head_dim, dt=self.kv_dtype)
-        self.attn16, self.attn = z(B, sh.n_q_heads, 1, sh.head_dim, dt=self.kv_dtype), z(B, sh.n_q_heads * sh.head_dim)
-        self.proj, self.gate, self.up, self.act = z(B, sh.hidden), z(B, sh.ffn), z(B, sh.ffn), z(B, sh.ffn)
+        # q, k and v of one step in the cache's tensor type: one buffer (one cast launch), three strided views of it
+        nq, nk = sh.n_q_heads * sh.head_dim, sh.n_kv_heads * sh.head_dim
+        self.qkv16 = z(B, nq + 2 * nk, dt=self.kv_dtype)
+        heads = lambda lo, n: self.qkv16[:, lo:lo + n * sh.head_dim].unflatten(1, (n, 1, sh.head_dim))
+        self.q16, self.k16, self.v16 = heads(0, sh.n_q_heads), heads(nq, sh.n_kv_heads), heads(nq + nk, sh.n_kv_heads)
+        self.attn16 = z(B, sh.n_q_heads, 1, sh.head_dim, dt=self.kv_dtype)
+        self.proj, self.gate_up = z(B, sh.hidden), z(B, 2 * sh.ffn)
+        # the quantised activation of the GEMM in flight; every producer and GEMM of a step runs on one stream, in order
+        self.scratch = torch.empty(kv.Q40Linear.scratch_bytes(max(sh.hidden, sh.ffn, nq), B), dtype=torch.uint8, device=dev)
         self.logits = z(B, sh.vocab)
         self.tokens = torch.zeros(B, dtype=torch.int32, device=dev)
         self.pos = torch.zeros(B, dtype=torch.int32, device=dev)
@@ -100,44 +114,40 @@ class Decoder:
             self._capture()
 
     # ---- the launches between two cache calls ----------------------------------------------------------
-    def _pre_attention(self, L):
+    # The residual add of a block's output is folded into the RmsNorm that follows it, and every RmsNorm and the gated
+    # activation into the quantiser of the GEMM they feed: `proj` holds the output that is still to be added to `x`.
+    def _pre_attention(self, L, first):
         sh = self.shape
-        kv.rms_norm(self.x, sh.eps, weight=L["attn_norm"], out=self.xn)
-        L["wqkv"].gemm(self.xn, self.qkv)
-        nq, nk = sh.n_q_heads * sh.head_dim, sh.n_kv_heads * sh.head_dim
-        kv.cast(self.qkv[:, :nq], self.q16.view(self.B, nq))
-        kv.cast(self.qkv[:, nq:nq + nk], self.k16.view(self.B, nk))
-        kv.cast(self.qkv[:, nq + nk:], self.v16.view(self.B, nk))
-        kv.rope(self.q16, self.cos_t.view(self.B, 1, sh.head_dim), self.sin_t.view(self.B, 1, sh.head_dim), out=self.q16r)
+        kv.q40_add_rms_norm_quantize(self.x, self.scratch, sh.eps, weight=L["attn_norm"], residual=None if first else self.proj,
+                                     x_out=None if first else self.x)
+        L["wqkv"].gemm_quantized(self.B, self.qkv, scratch=self.scratch)
+        kv.cast(self.qkv, self.qkv16)  # the query is rotated where the decode kernel loads it (attend_rope)
 
     def _post_attention(self, L):
         sh = self.shape
-        kv.cast(self.attn16.view(self.B, -1), self.attn)
-        L["wo"].gemm(self.attn, self.proj)
-        kv.add(self.x, self.proj, out=self.x)
-        kv.rms_norm(self.x, sh.eps, weight=L["ffn_norm"], out=self.xn)
-        L["wg"].gemm(self.xn, self.gate)
-        L["wu"].gemm(self.xn, self.up)
-        kv.silu_mul(self.gate, self.up, out=self.act)
-        L["wd"].gemm(self.act, self.proj)
-        kv.add(self.x, self.proj, out=self.x)
+        L["wo"].gemm(self.attn16.view(self.B, -1), self.proj, scratch=self.scratch)
+        kv.q40_add_rms_norm_quantize(self.x, self.scratch, sh.eps, weight=L["ffn_norm"], residual=self.proj, x_out=self.x)
+        L["wgu"].gemm_quantized(self.B, self.gate_up, scratch=self.scratch)
+        kv.q40_silu_mul_quantize(self.gate_up[:, :sh.ffn], self.gate_up[:, sh.ffn:], self.scratch)
+        L["wd"].gemm_quantized(self.B, self.proj, scratch=self.scratch)
 
     def _head(self):
         kv.gather_rows(self.cos, self.pos, out=self.cos_t)
         kv.gather_rows(self.sin, self.pos, out=self.sin_t)
         kv.gather_rows(self.embed, self.tokens, out=self.x)
 
-    def _tail(self):
-        kv.rms_norm(self.x, self.shape.eps, weight=self.final_norm, out=self.xn)
-        self.lm_head.gemm(self.xn, self.logits)
+    def _tail(self, residual=True):
+        kv.q40_add_rms_norm_quantize(self.x, self.scratch, self.shape.eps, weight=self.final_norm, residual=self.proj if residual else None,
+                                     x_out=self.x if residual else None)
+        self.lm_head.gemm_quantized(self.B, self.logits, scratch=self.scratch)
         kv.argmax(self.logits, out=self.tokens)
 
     def _segments(self):
         """The launch sequences of one step that touch no cache: [head + pre(0)], [post(i) + pre(i+1)] ..., [post(last) + tail]."""
         n = len(self.layers)
-        segs = [lambda: (self._head(), self._pre_attention(self.layers[0]))]
+        segs = [lambda: (self._head(), self._pre_attention(self.layers[0], True))]
         for i in range(n - 1):
-            segs.append(lambda i=i: (self._post_attention(self.layers[i]), self._pre_attention(self.layers[i + 1])))
+            segs.append(lambda i=i: (self._post_attention(self.layers[i]), self._pre_attention(self.layers[i + 1], False)))
         segs.append(lambda: (self._post_attention(self.layers[n - 1]), self._tail()))
         return segs
 
@@ -164,7 +174,7 @@ class Decoder:
         for i, L in enumerate(self.layers):
             ids = self.seqs[i]
             L["cache"].append_rope(ids, self.k16, self.v16, self.cos_t.view(self.B, 1, -1), self.sin_t.view(self.B, 1, -1))
-            L["cache"].attend(ids, self.q16r, causal=True, out=self.attn16)
+            L["cache"].attend_rope(ids, self.q16, self.cos_t, self.sin_t, out=self.attn16)
             run(i + 1)
         self.pos += 1
         self.lengths = [n + 1 for n in self.lengths]
@@ -185,37 +195,32 @@ class Decoder:
         assert all(n == pos0 for n in self.lengths) and prompt.shape[0] == B
         ids = prompt.to(dev, torch.int32).reshape(R).contiguous()
         x = kv.gather_rows(self.embed, ids)
-        xn = torch.empty_like(x)
         scratch = torch.empty(kv.Q40Linear.scratch_bytes(max(sh.hidden, sh.ffn, nq), R), dtype=torch.uint8, device=dev)
         qkv = torch.empty((R, nq + 2 * nk), dtype=f32, device=dev)
-        # 16-bit q / k / v as [B, S, H, D] in memory, seen by the cache ops as [B, H, S, D] through their strides
-        q16, q16r = torch.empty((B, S, sh.n_q_heads, sh.head_dim), dtype=kdt, device=dev), torch.empty((B, S, sh.n_q_heads, sh.head_dim), dtype=kdt, device=dev)
-        k16, v16 = torch.empty((B, S, sh.n_kv_heads, sh.head_dim), dtype=kdt, device=dev), torch.empty((B, S, sh.n_kv_heads, sh.head_dim), dtype=kdt, device=dev)
-        attn16, attn = torch.empty_like(q16), torch.empty((R, nq), dtype=f32, device=dev)
+        # 16-bit q | k | v rows, seen by the cache ops as [B, H, S, D] tensors through their strides
+        qkv16 = torch.empty((R, nq + 2 * nk), dtype=kdt, device=dev)
+        bhsd = lambda lo, n: qkv16[:, lo:lo + n * sh.head_dim].unflatten(1, (n, sh.head_dim)).unflatten(0, (B, S)).permute(0, 2, 1, 3)
+        q16, k16, v16 = bhsd(0, sh.n_q_heads), bhsd(nq, sh.n_kv_heads), bhsd(nq + nk, sh.n_kv_heads)
+        q16r = torch.empty((B, S, sh.n_q_heads, sh.head_dim), dtype=kdt, device=dev).permute(0, 2, 1, 3)
+        attn16 = torch.empty((B, S, sh.n_q_heads, sh.head_dim), dtype=kdt, device=dev)
         proj = torch.empty((R, sh.hidden), dtype=f32, device=dev)
-        gate, up = torch.empty((R, sh.ffn), dtype=f32, device=dev), torch.empty((R, sh.ffn), dtype=f32, device=dev)
+        gate_up = torch.empty((R, 2 * sh.ffn), dtype=f32, device=dev)
         cos, sin = self.cos[pos0:pos0 + S].unsqueeze(0), self.sin[pos0:pos0 + S].unsqueeze(0)  # [1, S, D]: the same for every sequence
-        bhsd = lambda t: t.permute(0, 2, 1, 3)
         for i, L in enumerate(self.layers):
-            kv.rms_norm(x, sh.eps, weight=L["attn_norm"], out=xn)
-            L["wqkv"].gemm(xn, qkv, scratch=scratch)
-            kv.cast(qkv[:, :nq], q16.view(R, nq))
-            kv.cast(qkv[:, nq:nq + nk], k16.view(R, nk))
-            kv.cast(qkv[:, nq + nk:], v16.view(R, nk))
-            kv.rope(bhsd(q16), cos, sin, out=bhsd(q16r))
-            L["cache"].append_rope(self.seqs[i], bhsd(k16), bhsd(v16), cos, sin)
-            L["cache"].attend(self.seqs[i], bhsd(q16r), causal=True, out=bhsd(attn16))
-            kv.cast(attn16.view(R, nq), attn)
-            L["wo"].gemm(attn, proj, scratch=scratch)
-            kv.add(x, proj, out=x)
-            kv.rms_norm(x, sh.eps, weight=L["ffn_norm"], out=xn)
-            L["wg"].gemm(xn, gate, scratch=scratch)
-            L["wu"].gemm(xn, up, scratch=scratch)
-            kv.silu_mul(gate, up, out=gate)
-            L["wd"].gemm(gate, proj, scratch=scratch)
-            kv.add(x, proj, out=x)
+            kv.q40_add_rms_norm_quantize(x, scratch, sh.eps, weight=L["attn_norm"], residual=proj if i else None, x_out=x if i else None)
+            L["wqkv"].gemm_quantized(R, qkv, scratch=scratch)
+            kv.cast(qkv, qkv16)
+            kv.rope(q16, cos, sin, out=q16r)
+            L["cache"].append_rope(self.seqs[i], k16, v16, cos, sin)
+            L["cache"].attend(self.seqs[i], q16r, causal=True, out=attn16.permute(0, 2, 1, 3))
+            L["wo"].gemm(attn16.view(R, nq), proj, scratch=scratch)
+            kv.q40_add_rms_norm_quantize(x, scratch, sh.eps, weight=L["ffn_norm"], residual=proj, x_out=x)
+            L["wgu"].gemm_quantized(R, gate_up, scratch=scratch)
+            kv.q40_silu_mul_quantize(gate_up[:, :sh.ffn], gate_up[:, sh.ffn:], scratch)
+            L["wd"].gemm_quantized(R, proj, scratch=scratch)
+        kv.add(x, proj, out=x)
         kv.cast(x[S - 1::S], self.x)  # the last row of every sequence
-        self._tail()
+        self._tail(residual=False)
         self.pos += S
         self.lengths = [n + S for n in self.lengths]
 
@@ -247,7 +252,7 @@ class Decoder:
     def check(self):
         for L in self.layers:
             L["cache"].check()
-        self.lm_head.check()
+        self.lm_head.check(self.scratch)
 
     def close(self):
         for L in self.layers:

@@ -156,6 +156,13 @@ class KvState {
         ck(b200kv_attend_window(cache_, 1, &seq_, (int32_t)q.shape[1], q.ptr, q.strides, out.ptr, out.strides, (int)q.dt, scale, window, stream));
         ck(b200kv_trim(cache_, seq_, window));
     }
+    // ApplyRope (transformers/src/ops/apply_rope.rs:143-176) on the query, then Sdpa over the cache, as one launch:
+    // cos / sin are the [1, 1, D] rows of the newest position.
+    void attend_rope(const DeviceTensor& q, const DeviceTensor& cos, const DeviceTensor& sin, const DeviceTensor& out, float scale,
+                     void* stream) {
+        ck(b200kv_attend_rope(cache_, 1, &seq_, (int32_t)q.shape[1], q.ptr, q.strides, cos.ptr, sin.ptr, 0, out.ptr, out.strides,
+                              (int)q.dt, scale, stream));
+    }
     void check(void* stream) { ck(b200kv_check(cache_, stream)); }
     const CacheSpec& spec() const { return spec_; }
 
