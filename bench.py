@@ -681,7 +681,7 @@ def run_decoder(args, rank, world):
                        "launch": "CUDA-graph segments between cache calls; cache calls from the host"},
             "e2e": {"value": world * B / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": B * 4, "d2h_bytes_per_step": B * 4,
                     "ms_per_step": ms_e2e},
-            "gpu_launches": sh.n_layers * 12 + 6,  # per layer: 5 GEMMs and their 4 fused + 1 plain producers... see Decoder
+            "gpu_launches": sh.n_layers * 11 + 6,  # per layer: 4 GEMMs, 4 quantising producers, append, decode, combine
             "kernels_ms": {k: statistics.mean(v) for k, v in recs.items()},
             "prompt_pass": pp,
             "roofline": {"bound": "hbm", "kernel": "whole step (Q4_0 GEMMs dominate)", "achieved": (weight_bytes + kv_bytes) / (ms * 1e-3) / 1e9,

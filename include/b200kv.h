@@ -235,6 +235,10 @@ int b200kv_q40_gemm(const void* packed, int64_t n, int64_t k, const void* a, int
 int b200kv_q40_quantize(const void* a, int64_t a_stride, int32_t m, int32_t dtype, int64_t k, void* scratch, void* stream);
 int b200kv_q40_gemm_quantized(const void* packed, int64_t n, int64_t k, int32_t m, void* scratch, float* out, int64_t out_stride,
                               void* stream);
+/* b200kv_q40_gemm_quantized with the result stored as `out_dtype` (the f32 result rounded once: the Cast that follows
+ * the MatMul in the graph, core/src/ops/cast.rs, folded into the store). */
+int b200kv_q40_gemm_quantized_as(const void* packed, int64_t n, int64_t k, int32_t m, void* scratch, void* out, int64_t out_stride,
+                                 int32_t out_dtype, void* stream);
 /* Producers fused with the quantiser: the activation never visits HBM as floats.  Each gives the bits of the separate
  * calls run one after the other.
  *   silu_mul:      scratch <- quantise(Silu(gate) * up)            (b200kv_silu_mul, then b200kv_q40_quantize)

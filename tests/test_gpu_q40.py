@@ -121,3 +121,20 @@ def test_fused_producers_give_the_bits_of_the_separate_calls(kv, m, n, k):
     assert torch.equal(lin.gemm_quantized(m, scratch=scratch), lin.gemm(x))
     assert torch.equal(lin.gemm_quantized(m, scratch=scratch), lin.gemm(x))
     lin.check(scratch)
+
+
+@pytest.mark.parametrize("odt", ["f16", "bf16"])
+def test_gemm_result_stored_in_a_16_bit_type(kv, odt):
+    # the Cast after the MatMul folded into the store: the f32 result rounded once
+    m, n, k = 11, 80, 1024
+    sc, pk = oracle.q4_0_quant(normal_with_outliers(41, (n, k)).astype(np.float32))
+    lin = kv.Q40Linear(torch.from_numpy(ggml_blocks(sc, pk)).cuda(), max_m=16)
+    a = torch.from_numpy(normal(42, (m, k)).astype(np.float32)).cuda()
+    tdt = {"f16": torch.float16, "bf16": torch.bfloat16}[odt]
+    wide = torch.zeros((m, n + 48), dtype=tdt, device="cuda")  # a window of a wider buffer
+    kv.q40_quantize(a, lin.scratch)
+    lin.gemm_quantized(m, out=wide[:, 16:16 + n])
+    lin.check()
+    want = torch.from_numpy(oracle.w4a8_gemm(sc, pk, a.cpu().numpy())).to(tdt)
+    assert torch.equal(wide[:, 16:16 + n].cpu(), want)
+    assert not wide[:, :16].any() and not wide[:, 16 + n:].any()

@@ -26,7 +26,7 @@ EXPORTS = [
     "b200kv_profile_read", "b200kv_attend_static_scratch", "b200kv_export_kivi", "b200kv_append_rope", "b200kv_rope",
     "b200kv_q40_packed_bytes", "b200kv_q40_pack", "b200kv_q40_scratch_bytes", "b200kv_q40_gemm", "b200kv_q40_check",
     "b200kv_rms_norm", "b200kv_silu_mul", "b200kv_add", "b200kv_argmax", "b200kv_gather_rows", "b200kv_cast",
-    "b200kv_attend_window", "b200kv_trim", "b200kv_attend_rope", "b200kv_q40_quantize", "b200kv_q40_gemm_quantized",
+    "b200kv_attend_window", "b200kv_trim", "b200kv_attend_rope", "b200kv_q40_quantize", "b200kv_q40_gemm_quantized", "b200kv_q40_gemm_quantized_as",
     "b200kv_q40_silu_mul_quantize", "b200kv_q40_add_rms_norm_quantize",
 ]
 KERNEL_NAMES = {0: "table_scatter", 1: "append", 2: "decode", 3: "combine", 4: "export", 5: "sdpa_dense", 6: "prefill"}
@@ -357,9 +357,11 @@ class Q40Linear:
         assert scratch.numel() >= self.scratch_bytes(self.k, m)
         if out is None:
             out = torch.empty((m, self.n), dtype=torch.float32, device=self.packed.device)
+        assert out.shape == (m, self.n) and out.stride(1) == 1  # f32, or f16 / bf16: the result rounded once on the way out
         with torch.cuda.device(self.packed.device):
-            _ck(lib().b200kv_q40_gemm_quantized(C.c_void_p(self.packed.data_ptr()), C.c_int64(self.n), C.c_int64(self.k), int(m),
-                                                C.c_void_p(scratch.data_ptr()), C.c_void_p(out.data_ptr()), C.c_int64(out.stride(0)), _stream()))
+            _ck(lib().b200kv_q40_gemm_quantized_as(C.c_void_p(self.packed.data_ptr()), C.c_int64(self.n), C.c_int64(self.k), int(m),
+                                                   C.c_void_p(scratch.data_ptr()), C.c_void_p(out.data_ptr()), C.c_int64(out.stride(0)),
+                                                   _dtype_code(out), _stream()))
         return out
 
     def check(self, scratch=None):

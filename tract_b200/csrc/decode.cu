@@ -402,6 +402,41 @@ int launch_combine(const DecodeParams& p, const int32_t* batch_info, void* out, 
     return B200KV_OK;
 }
 
+// Pages per split of a decode call.
+// (1) Few sequences (every (sequence, head group) pair fits the resident CTAs at once): one round of CTAs of nearly
+//     equal size, the smallest run length for which all CTAs are resident together.  The kernel is bound by HBM, which
+//     the resident CTAs share evenly whatever SM they sit on, so equal CTAs finish together; every further round would
+//     pay the start-up of a CTA (page table, first tiles: ~2.5 us) again, with all its neighbours doing the same.
+//     The 4-bit kernel is bound by instruction issue, where balance between SMs counts for more: two rounds when the
+//     runs stay long.
+// (2) Many sequences: 16 CTAs per SM over the run, so that the tail is short; small launches fill one round with up
+//     to 8 pages per split instead of one page per CTA.
+int64_t decode_pages_per_split(const b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int64_t window, bool use_mma, int nz) {
+    const int Hkv = c->L.Hkv;
+    auto pages_of = [&](int i) {
+        const SeqState& s = c->seqs[seqs[i]];
+        const int64_t first = std::max<int64_t>(s.start, window > 0 ? s.len - window : 0);
+        return (s.len + PAGE_TOKENS - 1) / PAGE_TOKENS - first / PAGE_TOKENS;
+    };
+    int64_t total_pages = 0, max_pages = 1;
+    for (int i = 0; i < n_seqs; i++) total_pages += pages_of(i), max_pages = std::max<int64_t>(max_pages, pages_of(i));
+    const int64_t work = total_pages * Hkv * nz, target_ctas = 148 * 16, one_wave = 148 * 3;
+    int64_t chunk = std::max<int64_t>((work + target_ctas - 1) / target_ctas, std::min<int64_t>((work + one_wave - 1) / one_wave, 8));
+    const int resident = use_mma ? (c->L.fmt == B200KV_FMT_Q4_0 ? 4 : (c->L.fmt == B200KV_FMT_Q8_1 ? 3 : 2)) : 3;
+    int64_t slots = 148 * resident;
+    if (use_mma && c->L.fmt == B200KV_FMT_Q4_0 && work >= 2 * slots * 16) slots *= 2;
+    if ((int64_t)n_seqs * Hkv * nz <= slots) {
+        int64_t cand = std::max<int64_t>(1, work / slots);
+        for (; cand < max_pages; cand += std::max<int64_t>(1, cand / 32)) {  // the count falls as cand grows; at max_pages it is one CTA per pair
+            int64_t n = 0;
+            for (int i = 0; i < n_seqs; i++) n += std::min<int64_t>(64, (pages_of(i) + cand - 1) / cand);
+            if (n * Hkv * nz <= slots) break;
+        }
+        chunk = std::min(cand, max_pages);
+    }
+    return std::max<int64_t>(chunk, 1);
+}
+
 int launch_decode(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t n_q_heads, const void* q,
                   const int64_t* qs, void* out, const int64_t* os, int32_t dtype, float scale, cudaStream_t stream, int64_t window,
                   const QueryRope* rope) {
@@ -417,11 +452,7 @@ int launch_decode(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t 
         if (s.len <= 0) return fail("sequence %d is empty: nothing to attend to", seqs[i]);
         total_pages += (s.len + PAGE_TOKENS - 1) / PAGE_TOKENS - first_of(s) / PAGE_TOKENS;
     }
-    // Pages per split.  Large launches: 16 CTAs per SM over the run, so that the tail is short.  Small launches would get
-    // one page per CTA that way, several waves of CTAs that are all set-up: they fill one wave (3 CTAs per SM) with up to
-    // 8 pages per split instead, and stay at 8 pages until the large-launch rule asks for more.
-    const int64_t work = total_pages * Hkv * nz, target_ctas = 148 * 16, one_wave = 148 * 3;
-    const int64_t chunk = std::max<int64_t>((work + target_ctas - 1) / target_ctas, std::min<int64_t>((work + one_wave - 1) / one_wave, 8));
+    const int64_t chunk = decode_pages_per_split(c, n_seqs, seqs, window, use_mma, nz);
     // one entry per sequence: {table row, length, first work item, splits}; the work items follow from it
     InlineBatch ib{};
     std::vector<int4> ent((size_t)n_seqs);

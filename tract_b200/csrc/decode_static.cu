@@ -68,9 +68,7 @@ extern "C" int b200kv_attend_static_scratch(b200kv_cache* c, int32_t n_seqs, con
         if (len <= 0) return fail("sequence %d is empty: nothing to attend to", seqs[i]);
         total_pages += (len + PAGE_TOKENS - 1) / PAGE_TOKENS;
     }
-    const int64_t target_ctas = 148 * 16;
-    int64_t chunk = (total_pages * Hkv * nz + target_ctas - 1) / target_ctas;
-    if (chunk < 1) chunk = 1;
+    int64_t chunk = decode_pages_per_split(c, n_seqs, seqs, 0, use_mma, nz);
     // size the work list first, so that nothing is enqueued when the fixed array is too small
     size_t n_items = 0;
     for (int i = 0; i < n_seqs; i++) {

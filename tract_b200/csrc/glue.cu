@@ -54,9 +54,28 @@ __global__ void argmax_kernel(const float* __restrict__ x, int64_t stride, int n
     const float* row = x + (int64_t)blockIdx.x * stride;
     float best = -INFINITY;
     int idx = 0x7fffffff;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
-        const float v = row[i];
+    auto take = [&](float v, int i) {
         if (v > best || (v == best && i < idx)) best = v, idx = i;
+    };
+    if (((uintptr_t)row & 15) == 0) {  // 16-byte loads, four of them in flight per thread
+        const float4* r4 = (const float4*)row;
+        const int n4 = n / 4;
+        for (int i = threadIdx.x; i < n4; i += 4 * blockDim.x) {
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const int k = i + u * blockDim.x;
+                v[u] = k < n4 ? r4[k] : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const int k = i + u * blockDim.x;
+                if (k < n4) take(v[u].x, 4 * k), take(v[u].y, 4 * k + 1), take(v[u].z, 4 * k + 2), take(v[u].w, 4 * k + 3);
+            }
+        }
+        for (int i = n4 * 4 + threadIdx.x; i < n; i += blockDim.x) take(row[i], i);
+    } else {
+        for (int i = threadIdx.x; i < n; i += blockDim.x) take(row[i], i);
     }
     auto merge = [&](float ov, int oi) {
         if (ov > best || (ov == best && oi < idx)) best = ov, idx = oi;

@@ -132,6 +132,7 @@ struct QueryRope {  // ApplyRope of the query inside the decode kernels: one cos
     const void* sin;
     int64_t stride_b;  // elements
 };
+int64_t decode_pages_per_split(const b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int64_t window, bool use_mma, int nz);
 int launch_decode(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t n_q_heads, const void* q,
                   const int64_t* q_strides, void* out, const int64_t* out_strides, int32_t dtype, float scale,
                   cudaStream_t stream, int64_t window = 0, const QueryRope* rope = nullptr);

@@ -96,8 +96,11 @@ __global__ void q40_quant_act_kernel(const void* __restrict__ a, int64_t a_strid
 }
 
 // One CTA per activation row slot: v = x (+ residual), stored to x_out when given; then RmsNorm(v) * weight, quantised.
-// The same arithmetic, in the same order, as the add, RmsNorm and quantiser kernels run one after the other.
-__global__ void q40_norm_quant_kernel(const float* __restrict__ x, int64_t x_stride, const float* residual, int64_t res_stride,
+// The same arithmetic, in the same order, as the add, RmsNorm and quantiser kernels run one after the other.  A thread
+// keeps its EPT values of the row (elements tid, tid + threads, ...) in registers: every load of the row is in flight at
+// once, and the second pass reads nothing but the weight (from L2).
+template <int EPT>
+__global__ void __launch_bounds__(512) q40_norm_quant_kernel(const float* x, int64_t x_stride, const float* residual, int64_t res_stride,
                                       const float* __restrict__ weight, float eps, float* x_out, int64_t xo_stride, int32_t m, int d,
                                       uint8_t* __restrict__ act, int* __restrict__ status) {
     __shared__ float part[32];
@@ -107,34 +110,50 @@ __global__ void q40_norm_quant_kernel(const float* __restrict__ x, int64_t x_str
     const int slot = (int)(mi % 8), lane = threadIdx.x & 31;
     uint8_t* dst = act + (mi / 8) * nb * Q_ACT_BLOCK;
     const bool valid = mi < m;
+    float v[EPT];
+#pragma unroll
+    for (int j = 0; j < EPT; j++) {
+        const int i = threadIdx.x + j * blockDim.x;
+        v[j] = (valid && i < d) ? x[mi * x_stride + i] : 0.f;
+    }
+    if (residual) {
+        float r[EPT];
+#pragma unroll
+        for (int j = 0; j < EPT; j++) {
+            const int i = threadIdx.x + j * blockDim.x;
+            r[j] = (valid && i < d) ? residual[mi * res_stride + i] : 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < EPT; j++) v[j] = __fadd_rn(v[j], r[j]);
+    }
     float ss = 0.f;
-    if (valid)
-        for (int i = threadIdx.x; i < d; i += blockDim.x) {
-            float v = x[mi * x_stride + i];
-            if (residual) v = __fadd_rn(v, residual[mi * res_stride + i]);
-            if (x_out) x_out[mi * xo_stride + i] = v;
-            ss = fmaf(v, v, ss);
+#pragma unroll
+    for (int j = 0; j < EPT; j++) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (valid && i < d) {
+            if (x_out) x_out[mi * xo_stride + i] = v[j];
+            ss = fmaf(v[j], v[j], ss);  // ascending j: the order of the stand-alone kernel's loop
         }
+    }
     const float inv = rms_norm_inv(ss, part, d, eps);
-    for (int i = threadIdx.x; i < d; i += blockDim.x) {  // d and the CTA are multiples of 32: a warp covers one block per turn
-        float v = 0.f;
-        if (valid) {
-            // the thread that stored x_out[i] reads it back; without x_out the sum is formed again from the inputs
-            v = x_out ? x_out[mi * xo_stride + i] : (residual ? __fadd_rn(x[mi * x_stride + i], residual[mi * res_stride + i]) : x[mi * x_stride + i]);
-            v = __fmul_rn(v, inv);
-            if (weight) v = __fmul_rn(v, weight[i]);
+#pragma unroll
+    for (int j = 0; j < EPT; j++) {  // d and the CTA are multiples of 32: a warp covers one block per turn
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < d) {
+            float t = __fmul_rn(v[j], inv);
+            if (weight) t = __fmul_rn(t, weight[i]);
+            q40_quantize_block(t, valid, dst + (int64_t)(i / QK) * Q_ACT_BLOCK, slot, lane);
         }
-        q40_quantize_block(v, valid, dst + (int64_t)(i / QK) * Q_ACT_BLOCK, slot, lane);
     }
 }
 
 struct Q40Gemm {
     const uint8_t* packed;
     const uint8_t* act;
-    float* out;
+    void* out;  // [m][n] of out_dtype: the f32 result, rounded once on the way out when the type is narrower
     int* status;
     int64_t n, nb, out_stride;
-    int32_t m;
+    int32_t m, out_dtype;
 };
 
 __device__ inline void mma_u8s8(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
@@ -287,12 +306,12 @@ __global__ void __launch_bounds__(Q_WARPS * 32, MG == 1 ? 2 : 1) q40_gemm_kernel
                 if (*fail_s) acc = make_float4(__int_as_float(0x7fc00000), __int_as_float(0x7fc00000), __int_as_float(0x7fc00000), __int_as_float(0x7fc00000));
                 const int64_t row = tile * Q_TILE_ROWS + r, m0 = (g0 + gi) * 8 + 2 * c;
                 if (row < p.n) {
-                    if (m0 < p.m) p.out[m0 * p.out_stride + row] = acc.x;
-                    if (m0 + 1 < p.m) p.out[(m0 + 1) * p.out_stride + row] = acc.y;
+                    if (m0 < p.m) st_from_f32(p.out, p.out_dtype, m0 * p.out_stride + row, acc.x);
+                    if (m0 + 1 < p.m) st_from_f32(p.out, p.out_dtype, (m0 + 1) * p.out_stride + row, acc.y);
                 }
                 if (row + 8 < p.n) {
-                    if (m0 < p.m) p.out[m0 * p.out_stride + row + 8] = acc.z;
-                    if (m0 + 1 < p.m) p.out[(m0 + 1) * p.out_stride + row + 8] = acc.w;
+                    if (m0 < p.m) st_from_f32(p.out, p.out_dtype, m0 * p.out_stride + row + 8, acc.z);
+                    if (m0 + 1 < p.m) st_from_f32(p.out, p.out_dtype, (m0 + 1) * p.out_stride + row + 8, acc.w);
                 }
             }
         }
@@ -366,17 +385,25 @@ extern "C" int b200kv_q40_add_rms_norm_quantize(const float* x, int64_t x_stride
                                                 void* scratch, void* stream) {
     if (q40_check_shape(scratch, k, m) != B200KV_OK) return B200KV_KO;
     if (!x) return fail("null pointer");
-    if (k > INT32_MAX) return fail("row too long");
+    if (k > 32 * 512) return fail("rows of at most %d values", 32 * 512);
     if (x_stride < k || (residual && residual_stride < k) || (x_out && x_out_stride < k)) return fail("strides shorter than the rows");
-    q40_norm_quant_kernel<<<(unsigned)((m + 7) / 8 * 8), rms_norm_threads((int)k), 0, (cudaStream_t)stream>>>(
-        x, x_stride, residual, residual_stride, weight, eps, x_out, x_out_stride, m, (int)k, (uint8_t*)scratch + Q_HEADER, (int*)scratch);
+    const int threads = rms_norm_threads((int)k);
+    const dim3 grid((unsigned)((m + 7) / 8 * 8));
+    uint8_t* act = (uint8_t*)scratch + Q_HEADER;
+    if (k <= 8 * threads)
+        q40_norm_quant_kernel<8><<<grid, threads, 0, (cudaStream_t)stream>>>(x, x_stride, residual, residual_stride, weight, eps, x_out,
+                                                                             x_out_stride, m, (int)k, act, (int*)scratch);
+    else
+        q40_norm_quant_kernel<32><<<grid, threads, 0, (cudaStream_t)stream>>>(x, x_stride, residual, residual_stride, weight, eps, x_out,
+                                                                              x_out_stride, m, (int)k, act, (int*)scratch);
     B200KV_CUDA(cudaGetLastError());
     return B200KV_OK;
 }
 
-extern "C" int b200kv_q40_gemm_quantized(const void* packed, int64_t n, int64_t k, int32_t m, void* scratch, float* out, int64_t out_stride,
-                                         void* stream_) {
+extern "C" int b200kv_q40_gemm_quantized_as(const void* packed, int64_t n, int64_t k, int32_t m, void* scratch, void* out, int64_t out_stride,
+                                            int32_t out_dtype, void* stream_) {
     if (q40_check_shape(scratch, k, m) != B200KV_OK) return B200KV_KO;
+    if (out_dtype < B200KV_F32 || out_dtype > B200KV_BF16) return fail("unknown dtype %d", out_dtype);
     if (!packed || !out) return fail("null pointer");
     if (n <= 0) return fail("n must be positive");
     if ((uintptr_t)packed % 16) return fail("packed weights must be 16-byte aligned");
@@ -386,7 +413,7 @@ extern "C" int b200kv_q40_gemm_quantized(const void* packed, int64_t n, int64_t 
     uint8_t* act = (uint8_t*)scratch + Q_HEADER;
     Q40Gemm p{};
     p.packed = (const uint8_t*)packed, p.act = act, p.out = out, p.status = (int*)scratch;
-    p.n = n, p.nb = nb, p.out_stride = out_stride, p.m = m;
+    p.n = n, p.nb = nb, p.out_stride = out_stride, p.m = m, p.out_dtype = out_dtype;
     // warps per tile: enough stages per warp (>= 4) that the start-up of a CTA is amortised
     const int64_t n_stages = (nb + Q_STAGE_BLOCKS - 1) / Q_STAGE_BLOCKS;
     const int tile_warps = n_stages >= 32 ? 8 : (n_stages >= 16 ? 4 : 2);
@@ -421,6 +448,11 @@ extern "C" int b200kv_q40_gemm_quantized(const void* packed, int64_t n, int64_t 
         else B200KV_CUDA(launch_after_predecessor(q40_gemm_kernel<2, 4>, grid, block, smem, stream, p));
     }
     return B200KV_OK;
+}
+
+extern "C" int b200kv_q40_gemm_quantized(const void* packed, int64_t n, int64_t k, int32_t m, void* scratch, float* out, int64_t out_stride,
+                                         void* stream) {
+    return b200kv_q40_gemm_quantized_as(packed, n, k, m, scratch, out, out_stride, B200KV_F32, stream);
 }
 
 extern "C" int b200kv_q40_gemm(const void* packed, int64_t n, int64_t k, const void* a, int64_t a_stride, int32_t m, int32_t dtype,

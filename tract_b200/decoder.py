@@ -94,7 +94,6 @@ class Decoder:
         B, f32 = n_seqs, torch.float32
         z = lambda *s, dt=f32: torch.zeros(s, dtype=dt, device=dev)
         self.x = z(B, sh.hidden)  # the residual stream
-        self.qkv = z(B, qkv_rows)
         # q, k and v of one step in the cache's tensor type: one buffer (one cast launch), three strided views of it
         nq, nk = sh.n_q_heads * sh.head_dim, sh.n_kv_heads * sh.head_dim
         self.qkv16 = z(B, nq + 2 * nk, dt=self.kv_dtype)
@@ -120,8 +119,8 @@ class Decoder:
         sh = self.shape
         kv.q40_add_rms_norm_quantize(self.x, self.scratch, sh.eps, weight=L["attn_norm"], residual=None if first else self.proj,
                                      x_out=None if first else self.x)
-        L["wqkv"].gemm_quantized(self.B, self.qkv, scratch=self.scratch)
-        kv.cast(self.qkv, self.qkv16)  # the query is rotated where the decode kernel loads it (attend_rope)
+        # q | k | v leave the GEMM in the cache's tensor type; the query is rotated where the decode kernel loads it (attend_rope)
+        L["wqkv"].gemm_quantized(self.B, self.qkv16, scratch=self.scratch)
 
     def _post_attention(self, L):
         sh = self.shape
@@ -196,7 +195,6 @@ class Decoder:
         ids = prompt.to(dev, torch.int32).reshape(R).contiguous()
         x = kv.gather_rows(self.embed, ids)
         scratch = torch.empty(kv.Q40Linear.scratch_bytes(max(sh.hidden, sh.ffn, nq), R), dtype=torch.uint8, device=dev)
-        qkv = torch.empty((R, nq + 2 * nk), dtype=f32, device=dev)
         # 16-bit q | k | v rows, seen by the cache ops as [B, H, S, D] tensors through their strides
         qkv16 = torch.empty((R, nq + 2 * nk), dtype=kdt, device=dev)
         bhsd = lambda lo, n: qkv16[:, lo:lo + n * sh.head_dim].unflatten(1, (n, sh.head_dim)).unflatten(0, (B, S)).permute(0, 2, 1, 3)
@@ -208,8 +206,7 @@ class Decoder:
         cos, sin = self.cos[pos0:pos0 + S].unsqueeze(0), self.sin[pos0:pos0 + S].unsqueeze(0)  # [1, S, D]: the same for every sequence
         for i, L in enumerate(self.layers):
             kv.q40_add_rms_norm_quantize(x, scratch, sh.eps, weight=L["attn_norm"], residual=proj if i else None, x_out=x if i else None)
-            L["wqkv"].gemm_quantized(R, qkv, scratch=scratch)
-            kv.cast(qkv, qkv16)
+            L["wqkv"].gemm_quantized(R, qkv16, scratch=scratch)
             kv.rope(q16, cos, sin, out=q16r)
             L["cache"].append_rope(self.seqs[i], k16, v16, cos, sin)
             L["cache"].attend(self.seqs[i], q16r, causal=True, out=attn16.permute(0, 2, 1, 3))
