@@ -652,8 +652,9 @@ def run_decoder(args, rank, world):
     for _ in range(max(args.warmup, 3)):
         step()
     sampler.mark()
-    n_e2e = max(2, args.steps // 4)
-    ms = timed(step, args.steps - n_e2e) / (args.steps - n_e2e)
+    n_e2e = max(1, min(args.steps // 4, args.steps - 1))  # the steps are shared between the device-timed and the end-to-end loop
+    n_dev = max(1, args.steps - n_e2e)
+    ms = timed(step, n_dev) / n_dev
     clocks = sampler.stop() if rank == 0 else None
     ms_e2e = timed(step_e2e, n_e2e) / n_e2e
     # the hot-path share: one layer's cache kernels, timed by the library's own event pairs

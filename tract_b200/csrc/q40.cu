@@ -76,6 +76,7 @@ __device__ inline void q40_quantize_block(float x, bool valid, uint8_t* dst, int
 __global__ void q40_quant_act_kernel(const void* __restrict__ a, int64_t a_stride, const void* __restrict__ up, int64_t up_stride, int32_t m,
                                      int32_t dtype, int64_t nb, uint8_t* __restrict__ act, int* __restrict__ status) {
     grid_launch_dependents();  // the GEMM may be scheduled: it starts pulling weights and waits for this grid before it reads `act`
+    grid_dependency_wait();    // the kernel before has written the activation (and has finished with `act`, if it was a GEMM)
     if (blockIdx.x == 0 && threadIdx.x == 0) *status = 0;
     const int lane = threadIdx.x & 31;
     const int64_t wid = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -105,6 +106,16 @@ __global__ void __launch_bounds__(512) q40_norm_quant_kernel(const float* x, int
                                       uint8_t* __restrict__ act, int* __restrict__ status) {
     __shared__ float part[32];
     grid_launch_dependents();
+    constexpr int WPT = EPT <= 8 ? EPT : 1;  // short rows: the weights wait in registers, fetched while the kernel before drains
+    float w[WPT];
+    if (EPT <= 8) {
+#pragma unroll
+        for (int j = 0; j < WPT; j++) {
+            const int i = threadIdx.x + j * blockDim.x;
+            w[j] = (weight && i < d) ? weight[i] : 1.f;
+        }
+    }
+    grid_dependency_wait();  // the kernel before (the GEMM that wrote `residual`, and read `act`) is done
     if (blockIdx.x == 0 && threadIdx.x == 0) *status = 0;
     const int64_t mi = blockIdx.x, nb = d / QK;
     const int slot = (int)(mi % 8), lane = threadIdx.x & 31;
@@ -141,7 +152,7 @@ __global__ void __launch_bounds__(512) q40_norm_quant_kernel(const float* x, int
         const int i = threadIdx.x + j * blockDim.x;
         if (i < d) {
             float t = __fmul_rn(v[j], inv);
-            if (weight) t = __fmul_rn(t, weight[i]);
+            if (weight) t = __fmul_rn(t, EPT <= 8 ? w[j < WPT ? j : 0] : weight[i]);
             q40_quantize_block(t, valid, dst + (int64_t)(i / QK) * Q_ACT_BLOCK, slot, lane);
         }
     }
@@ -228,7 +239,8 @@ __global__ void __launch_bounds__(Q_WARPS * 32, MG == 1 ? 2 : 1) q40_gemm_kernel
     if (lane == 0)  // the weights do not depend on the launch before: start pulling them
         for (int d = 0; d < Q_DEPTH; d++)
             if (warp + d * Q_WARPS < n_stages) issue(warp + d * Q_WARPS, true, false);
-    grid_dependency_wait();  // the activation quantiser has finished
+    grid_launch_dependents();  // whatever consumes the result may be scheduled and do its own set-up; it waits for this grid before it reads
+    grid_dependency_wait();    // the activation quantiser has finished
     if (lane == 0)
         for (int d = 0; d < Q_DEPTH; d++)
             if (warp + d * Q_WARPS < n_stages) issue(warp + d * Q_WARPS, false, true);
@@ -361,9 +373,8 @@ extern "C" int b200kv_q40_quantize(const void* a, int64_t a_stride, int32_t m, i
     if (dtype < B200KV_F32 || dtype > B200KV_BF16) return fail("unknown dtype %d", dtype);
     if (a_stride < k) return fail("strides shorter than the rows");
     const int64_t nb = k / QK, warps = (int64_t)((m + 7) / 8) * nb * 8;
-    q40_quant_act_kernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(a, a_stride, nullptr, 0, m, dtype, nb,
-                                                                                            (uint8_t*)scratch + Q_HEADER, (int*)scratch);
-    B200KV_CUDA(cudaGetLastError());
+    B200KV_CUDA(launch_after_predecessor(q40_quant_act_kernel, dim3((unsigned)((warps * 32 + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, a,
+                                         a_stride, (const void*)nullptr, (int64_t)0, m, dtype, nb, (uint8_t*)scratch + Q_HEADER, (int*)scratch));
     return B200KV_OK;
 }
 
@@ -374,9 +385,8 @@ extern "C" int b200kv_q40_silu_mul_quantize(const void* gate, int64_t gate_strid
     if (dtype < B200KV_F32 || dtype > B200KV_BF16) return fail("unknown dtype %d", dtype);
     if (gate_stride < k || up_stride < k) return fail("strides shorter than the rows");
     const int64_t nb = k / QK, warps = (int64_t)((m + 7) / 8) * nb * 8;
-    q40_quant_act_kernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(gate, gate_stride, up, up_stride, m, dtype, nb,
-                                                                                            (uint8_t*)scratch + Q_HEADER, (int*)scratch);
-    B200KV_CUDA(cudaGetLastError());
+    B200KV_CUDA(launch_after_predecessor(q40_quant_act_kernel, dim3((unsigned)((warps * 32 + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, gate,
+                                         gate_stride, up, up_stride, m, dtype, nb, (uint8_t*)scratch + Q_HEADER, (int*)scratch));
     return B200KV_OK;
 }
 
@@ -390,13 +400,14 @@ extern "C" int b200kv_q40_add_rms_norm_quantize(const float* x, int64_t x_stride
     const int threads = rms_norm_threads((int)k);
     const dim3 grid((unsigned)((m + 7) / 8 * 8));
     uint8_t* act = (uint8_t*)scratch + Q_HEADER;
+    int* status = (int*)scratch;
+    const int d = (int)k;
     if (k <= 8 * threads)
-        q40_norm_quant_kernel<8><<<grid, threads, 0, (cudaStream_t)stream>>>(x, x_stride, residual, residual_stride, weight, eps, x_out,
-                                                                             x_out_stride, m, (int)k, act, (int*)scratch);
+        B200KV_CUDA(launch_after_predecessor(q40_norm_quant_kernel<8>, grid, dim3(threads), 0, (cudaStream_t)stream, x, x_stride, residual,
+                                             residual_stride, weight, eps, x_out, x_out_stride, m, d, act, status));
     else
-        q40_norm_quant_kernel<32><<<grid, threads, 0, (cudaStream_t)stream>>>(x, x_stride, residual, residual_stride, weight, eps, x_out,
-                                                                              x_out_stride, m, (int)k, act, (int*)scratch);
-    B200KV_CUDA(cudaGetLastError());
+        B200KV_CUDA(launch_after_predecessor(q40_norm_quant_kernel<32>, grid, dim3(threads), 0, (cudaStream_t)stream, x, x_stride, residual,
+                                             residual_stride, weight, eps, x_out, x_out_stride, m, d, act, status));
     return B200KV_OK;
 }
 
@@ -416,9 +427,12 @@ extern "C" int b200kv_q40_gemm_quantized_as(const void* packed, int64_t n, int64
     p.n = n, p.nb = nb, p.out_stride = out_stride, p.m = m, p.out_dtype = out_dtype;
     // warps per tile: enough stages per warp (>= 4) that the start-up of a CTA is amortised
     const int64_t n_stages = (nb + Q_STAGE_BLOCKS - 1) / Q_STAGE_BLOCKS;
-    const int tile_warps = n_stages >= 32 ? 8 : (n_stages >= 16 ? 4 : 2);
+    // A matrix of few tiles (at most two CTAs of 8 warps per SM, all resident at once) leaves the GPU short of warps: 8 warps
+    // per tile put every stage of a K = 4096 tile in flight at once (+10 % on [4096 x 4096]); with more tiles, 4 are faster.
     // more than 8 activation rows: 4 groups share each weight stage (a prompt pass re-reads the weights M / 32 times, from L2)
     const int mg = groups > 1 ? 4 : 1;
+    const int64_t n_tiles = (n + Q_TILE_ROWS - 1) / Q_TILE_ROWS;
+    const int tile_warps = n_stages >= 32 ? 8 : (n_stages >= 16 ? (mg == 1 && n_tiles <= 2 * 148 ? 8 : 4) : 2);
     auto smem_of = [](int w, int g) {
         return (size_t)w * Q_DEPTH * (Q_STAGE_BYTES + g * Q_STAGE_BLOCKS * Q_ACT_BLOCK) + (size_t)w * g * 32 * 16 + (w * Q_DEPTH + w * g) * 8 + 16;
     };
