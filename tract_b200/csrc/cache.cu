@@ -123,6 +123,7 @@ __global__ void __launch_bounds__(256) append_kernel(AppendParams p, const __gri
     constexpr int EPU = elems_in_bytes<FMT>(16);  // elements per unit
     const int kv = p.has_v ? (int)(blockIdx.z & 1) : 0;
     grid_launch_dependents();  // a decode launch that follows may be scheduled now; it waits for this grid before reading pages
+    grid_dependency_wait();    // the kernel before has written k_new / v_new, and is done with the pages and the table
     if (blockIdx.x == 0 && blockIdx.z == 0)  // publish the new page-table entries (replaces a separate launch)
         for (int i = threadIdx.x; i < p.n_upd; i += blockDim.x) {
             const int2 u = ia.n ? ia.upd[i] : ((const int2*)p.upd)[i];
@@ -455,7 +456,7 @@ static void launch_append_fmt(const AppendParams& p, const InlineAppend& ia, int
         }
     }
     dim3 grid((unsigned)((per_entry + 255) / 256), 1, (unsigned)(p.n_seqs * n_kv));
-    append_kernel<FMT><<<grid, 256, 0, stream>>>(p, ia);
+    (void)launch_after_predecessor(append_kernel<FMT>, grid, dim3(256), 0, stream, p, ia);  // the caller reads cudaGetLastError
 }
 
 int launch_export(b200kv_cache* c, int32_t seq, void* k_out, const int64_t* ks, void* v_out, const int64_t* vs,
