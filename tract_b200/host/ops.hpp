@@ -218,7 +218,29 @@ struct Q40MatMul {
         if (!packed) throw Error("Q4_0 weights were not packed");
         ck(b200kv_q40_gemm(packed, n, k, a, a_stride, m, (int)dt, scratch, out, out_stride, stream));
     }
+    // The product with the m activation rows `scratch` already holds in quantised form (one of the producers below ran on
+    // the same stream); `out` is of type out_dt: the Cast that follows the MatMul in the graph, folded into the store.
+    void eval_quantized(int32_t m, void* scratch, void* out, int64_t out_stride, DatumType out_dt, void* stream) const {
+        if (!packed) throw Error("Q4_0 weights were not packed");
+        ck(b200kv_q40_gemm_quantized_as(packed, n, k, m, scratch, out, out_stride, (int)out_dt, stream));
+    }
 };
+
+// Producers of the quantised activation of a Q40MatMul (Q4_0::quantize_row_q8, linalg/src/frame/block_quant/q4_0.rs:199-222),
+// alone or fused with the nodes before the MatMul; each gives the bits of the separate nodes run one after the other.
+inline void q40_quantize(const void* a, int64_t a_stride, int32_t m, DatumType dt, int64_t k, void* scratch, void* stream) {
+    ck(b200kv_q40_quantize(a, a_stride, m, (int)dt, k, scratch, stream));
+}
+// Silu(gate) * up -> quantise
+inline void q40_silu_mul_quantize(const void* gate, int64_t gate_stride, const void* up, int64_t up_stride, int32_t m, DatumType dt, int64_t k,
+                                  void* scratch, void* stream) {
+    ck(b200kv_q40_silu_mul_quantize(gate, gate_stride, up, up_stride, m, (int)dt, k, scratch, stream));
+}
+// v = x + residual (residual may be null; v stored to x_out when given) -> RmsNorm(v, eps) * weight -> quantise; f32
+inline void q40_add_rms_norm_quantize(const float* x, int64_t x_stride, const float* residual, int64_t residual_stride, const float* weight,
+                                      float eps, float* x_out, int64_t x_out_stride, int32_t m, int64_t k, void* scratch, void* stream) {
+    ck(b200kv_q40_add_rms_norm_quantize(x, x_stride, residual, residual_stride, weight, eps, x_out, x_out_stride, m, k, scratch, stream));
+}
 
 // RmsNorm over the last axis (core/src/ops/nn/rms_norm.rs), optionally fused with the Mul by a weight vector that follows it.
 struct RmsNorm {
