@@ -249,6 +249,10 @@ int b200kv_q40_silu_mul_quantize(const void* gate, int64_t gate_stride, const vo
 int b200kv_q40_add_rms_norm_quantize(const float* x, int64_t x_stride, const float* residual, int64_t residual_stride,
                                      const float* weight, float eps, float* x_out, int64_t x_out_stride, int32_t m, int64_t k,
                                      void* scratch, void* stream);
+/* Ordering on the stream.  The GEMM and the producers are scheduled behind the kernel before them with a programmatic
+ * dependency: they read activations, residuals and scratch only after that kernel has finished, but the packed weights
+ * and the norm `weight` vector are fetched earlier.  Those two are constants of the model: they must be complete before
+ * the kernel that precedes the call was enqueued (b200kv_q40_pack takes care of this for the matrix it packs). */
 /* Synchronises `stream` and reports whether a bounded wait of the last GEMM that used `scratch` expired. */
 int b200kv_q40_check(const void* scratch, void* stream);
 

@@ -339,6 +339,10 @@ __global__ void __launch_bounds__(Q_WARPS * 32, MG == 1 ? 2 : 1) q40_gemm_kernel
 
 using namespace b200kv;
 
+// The GEMM requests weight stages before it waits for the kernel before it.  This empty kernel, launched the ordinary way
+// behind the repacking, separates the two: whatever is scheduled early behind it starts after the packed weights are complete.
+__global__ void q40_pack_done_kernel() {}
+
 extern "C" int64_t b200kv_q40_packed_bytes(int64_t n, int64_t k) {
     if (n <= 0 || k <= 0 || k % QK) return -1;
     return (n + Q_TILE_ROWS - 1) / Q_TILE_ROWS * (k / QK) * Q_BLOCK_BYTES;
@@ -355,6 +359,7 @@ extern "C" int b200kv_q40_pack(const void* blocks, int64_t n, int64_t k, void* p
     if ((uintptr_t)blocks % 2 || (uintptr_t)packed % 16) return fail("blocks must be 2-byte aligned and the packed buffer 16-byte aligned");
     const int64_t nb = k / QK, total = (n + Q_TILE_ROWS - 1) / Q_TILE_ROWS * Q_TILE_ROWS * nb;
     q40_pack_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>((const uint8_t*)blocks, n, nb, (uint8_t*)packed);
+    q40_pack_done_kernel<<<1, 32, 0, (cudaStream_t)stream>>>();
     B200KV_CUDA(cudaGetLastError());
     return B200KV_OK;
 }
