@@ -70,3 +70,20 @@ def test_add_argmax_gather(kv):
     table = normal(64, (1000, 256)).astype(np.float16)
     ids = np.array([5, 999, 0, 5, 123], np.int32)
     assert np.array_equal(kv.gather_rows(torch.from_numpy(table).cuda(), torch.from_numpy(ids).cuda()).cpu().numpy(), table[ids])
+
+
+@pytest.mark.parametrize("n,offset", [(1, 0), (3, 0), (1027, 0), (1027, 1), (4096, 2), (4099, 3), (128256, 0), (20001, 1)])
+def test_argmax_rows_of_any_length_and_alignment(kv, n, offset):
+    # rows that start off a 16-byte boundary take the scalar walk, aligned ones the 16-byte loads plus a scalar tail;
+    # the maximum sits in the tail, at the front and on a tie in turn
+    rows = 5
+    wide = torch.from_numpy(normal(71 + n, (rows, n + 8)).astype(np.float32)).cuda()
+    x = wide[:, offset:offset + n]
+    host = x.cpu().numpy().copy()
+    host[0, n - 1] = 50.0
+    host[1, 0] = 50.0
+    host[2, n // 2] = host[2, n - 1] = 50.0
+    host[3, :] = -np.inf
+    x.copy_(torch.from_numpy(host))
+    want = np.array([n - 1, 0, n // 2, 0, int(np.argmax(host[4]))], np.int32)
+    assert np.array_equal(kv.argmax(x).cpu().numpy(), want)

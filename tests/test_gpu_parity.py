@@ -447,6 +447,28 @@ def test_decode_with_rope_on_the_query_load(kv, fmt, io, D, G):
     cache.close()
 
 
+def test_rope_on_the_query_load_refuses_what_it_cannot_do(kv):
+    D, Hkv = 128, 2
+    q = to_dev(normal(6500, (1, 4, 1, D)).astype(np.float16))
+    cs = to_dev(np.ones((1, D), np.float16))
+    kivi = kv.KvCache("kivi8", Hkv, D, max_seqs=1, max_seq_tokens=128)
+    s = kivi.new_seq()
+    kivi.append([s], to_dev(normal(6501, (1, Hkv, 40, D)).astype(np.float16)), to_dev(normal(6502, (1, Hkv, 40, D)).astype(np.float16)))
+    with pytest.raises(kv.B200KvError):  # a KIVI cache takes its query already rotated
+        kivi.attend_rope([s], q, cs, cs)
+    kivi.close()
+    cache = kv.KvCache("f16", Hkv, D, max_seqs=1, max_seq_tokens=128)
+    s = cache.new_seq()
+    with pytest.raises(kv.B200KvError):  # an empty sequence: nothing to attend to
+        cache.attend_rope([s], q, cs, cs)
+    cache.append([s], to_dev(normal(6503, (1, Hkv, 3, D)).astype(np.float16)), to_dev(normal(6504, (1, Hkv, 3, D)).astype(np.float16)))
+    with pytest.raises(kv.B200KvError):  # 3 query heads over 2 kv heads
+        cache.attend_rope([s], q[:, :3], cs, cs)
+    cache.attend_rope([s], q, cs, cs)
+    cache.check()
+    cache.close()
+
+
 def _sweep_cases():
     rng = np.random.default_rng(20260)
     cases = []
