@@ -53,7 +53,7 @@ OVERRIDE = {}  # --seqs / --past: smaller cases of a workload, for profiler capt
 # DRAM traffic of the decode kernel per algorithmic byte (dram__bytes_read + dram__bytes_write over the K/V bytes of the
 # launch), from the ncu captures summarised under profiles/ on a smaller case of the same workload (traffic grows in
 # proportion to the tokens streamed, so it is scaled to the full launch by the units processed).
-NCU_TRAFFIC_RATIO = {"q8_1": 1.028}
+NCU_TRAFFIC_RATIO = {"q8_1": 1.018}
 ROW_BYTES = {"f32": 512, "f16": 256, "bf16": 256, "q8_1": 128 + 8, "q4_0": 64 + 8,
              # KIVI: K = codes + 2 x D f32 parameters per 32 tokens, V = codes + 8 bytes per token; mean of K and V
              "kivi8": 128 + (32 + 8) // 2, "kivi4": 64 + (32 + 8) // 2}  # stored bytes per token-head (codes + scales)
@@ -193,10 +193,12 @@ def run_ours(args, rank, world):
     k_new = torch.randn((n_seq, HKV, 1, D), generator=gen, device="cuda").to(io_dt)
     v_new = torch.randn((n_seq, HKV, 1, D), generator=gen, device="cuda").to(io_dt)
     out = torch.empty_like(q)
-    # host-side copies for the end-to-end leg
-    hq, hk, hv = (t.cpu().pin_memory() for t in (q, k_new, v_new))
+    # host-side copy for the end-to-end leg: q | k | v of a step as the rows of one pinned buffer (what a fused q/k/v
+    # projection leaves behind), one host-to-device copy per step; the cache calls take the three windows through strides
+    hqkv = torch.cat([q, k_new, v_new], 1).cpu().pin_memory()
+    dqkv = torch.empty((n_seq, HQ + 2 * HKV, 1, D), dtype=io_dt, device="cuda")
+    dq, dk, dv = dqkv[:, :HQ], dqkv[:, HQ:HQ + HKV], dqkv[:, HQ + HKV:]
     hout = torch.empty_like(out, device="cpu").pin_memory()
-    dq, dk, dv = torch.empty_like(q), torch.empty_like(k_new), torch.empty_like(v_new)
 
     def step():
         cache.append(seqs, k_new, v_new)
@@ -206,7 +208,7 @@ def run_ours(args, rank, world):
                 cache.truncate(s, n)
 
     def step_e2e():
-        dq.copy_(hq, non_blocking=True), dk.copy_(hk, non_blocking=True), dv.copy_(hv, non_blocking=True)
+        dqkv.copy_(hqkv, non_blocking=True)
         cache.append(seqs, dk, dv)
         cache.attend(seqs, dq, causal=True, out=out)
         hout.copy_(out, non_blocking=True)
@@ -276,7 +278,7 @@ def run_ours(args, rank, world):
         ms_step = ms / args.steps
         dec_ms = statistics.mean(per_kernel["decode"])
         achieved = total_bytes / (dec_ms * 1e-3) / 1e9
-        h2d = sum(t.numel() * t.element_size() for t in (hq, hk, hv))
+        h2d = hqkv.numel() * hqkv.element_size()
         d2h = hout.numel() * hout.element_size()
         result = {
             "metric": "decode-attn KV-read GB/s (sum over GPUs; per GPU = value / n_gpus)",

@@ -329,6 +329,11 @@ __global__ void combine_kernel(CombineParams p, const __grid_constant__ InlineBa
     const int first = ib.n ? ib.ent[b].z : p.batch_info[2 * b], n = ib.n ? ib.ent[b].w : p.batch_info[2 * b + 1];
     const int64_t stride = (int64_t)p.Hkv * p.G;
     const int64_t base = ((int64_t)first * p.Hkv + kvh) * p.G + g;
+    // the first eight partial outputs of this channel do not depend on the weights: they travel while the weights are made
+    const float* src = p.part_o + base * p.D + ch;
+    float v[8];
+#pragma unroll
+    for (int k = 0; k < 8; k++) v[k] = (k < n) ? src[(int64_t)k * stride * p.D] : 0.f;
     if (ch < n) {
         const float2 ml = *(const float2*)(p.part_ml + (base + ch * stride) * 2);
         wgt_s[ch] = ml.x, sum_s[ch] = ml.y;
@@ -346,10 +351,10 @@ __global__ void combine_kernel(CombineParams p, const __grid_constant__ InlineBa
     }
     __syncthreads();
     float num = 0.f;
-    const float* src = p.part_o + base * p.D + ch;
+#pragma unroll
+    for (int k = 0; k < 8; k++) num = fmaf((k < n) ? wgt_s[k] : 0.f, v[k], num);
 #pragma unroll 1
-    for (int i0 = 0; i0 < n; i0 += 8) {  // eight partials in flight per round
-        float v[8];
+    for (int i0 = 8; i0 < n; i0 += 8) {  // eight partials in flight per round
 #pragma unroll
         for (int k = 0; k < 8; k++) v[k] = (i0 + k < n) ? src[(int64_t)(i0 + k) * stride * p.D] : 0.f;
 #pragma unroll
