@@ -109,3 +109,47 @@ def test_decoder_prompt_pass_matches_token_by_token_oracle():
         tokens = dec.tokens.cpu().numpy().astype(np.int32)
     dec.check()
     dec.close()
+
+
+def test_chunked_prompt_and_rollback_repeat_bit_for_bit():
+    # a prompt fed in chunks fills the caches as one pass does (chunked prefill: causal_llm/src/lib.rs:325-377): bit for bit
+    # in the first layer, whose K / V come through row-independent kernels only; within the decoder tolerance further down
+    # (the prompt attention rounds a row's probabilities in a way that depends on the other rows of its tile).  A rollback
+    # (truncate, :383-408) followed by the same tokens reproduces the same logits bit for bit.
+    from tract_b200.decoder import Decoder, Shape
+
+    sh = Shape(hidden=256, n_layers=2, n_q_heads=4, n_kv_heads=2, head_dim=128, ffn=512, vocab=640, rope_theta=10000.0)
+    prompt = torch.from_numpy(np.random.default_rng(5).integers(0, sh.vocab, (2, 80)).astype(np.int32))
+    one = Decoder(sh, n_seqs=2, max_tokens=160, kv_format="f16", seed=9, use_graphs=True)
+    one.prefill(prompt)
+    chunked = Decoder(sh, n_seqs=2, max_tokens=160, kv_format="f16", seed=9, use_graphs=True)
+    for lo, hi in ((0, 64), (64, 72), (72, 80)):
+        chunked.prefill(prompt[:, lo:hi].contiguous())
+    for layer, (L1, L2, s1, s2) in enumerate(zip(one.layers, chunked.layers, one.seqs, chunked.seqs)):
+        for a, b in zip(s1, s2):
+            k1, v1 = L1["cache"].export(a, torch.float16)
+            k2, v2 = L2["cache"].export(b, torch.float16)
+            assert k1.shape == k2.shape == (sh.n_kv_heads, 80, sh.head_dim)
+            if layer == 0:
+                assert torch.equal(k1, k2) and torch.equal(v1, v2)
+            else:
+                for x, y in ((k1, k2), (v1, v2)):
+                    x, y = x.float(), y.float()
+                    assert ((x - y).abs().mean() / x.pow(2).mean().sqrt()).item() <= 2e-2
+    one.close()
+    # three accepted steps, two more "drafted" ones, rollback of the drafts, the same two tokens again
+    dec = chunked
+    for _ in range(3):
+        dec.step()
+    kept = dec.tokens.clone()
+    logits = []
+    for _ in range(2):
+        dec.step()
+        logits.append(dec.logits.clone())
+    dec.truncate(83)
+    dec.set_tokens(kept.cpu())
+    for i in range(2):
+        dec.step()
+        assert torch.equal(dec.logits, logits[i]), i
+    dec.check()
+    dec.close()

@@ -229,6 +229,17 @@ class Decoder:
         self.pos.zero_()
         self.lengths = [0] * self.B
 
+    def truncate(self, n_tokens):
+        """Rolls every sequence of every layer back to its first n_tokens cached tokens (the reference's `truncate`, used to
+        drop rejected draft tokens in speculative decoding: examples/causal_llm/src/lib.rs:383-408).  The next step or
+        prompt pass continues from position n_tokens."""
+        assert all(n_tokens <= n for n in self.lengths)
+        for i, L in enumerate(self.layers):
+            for s in self.seqs[i]:
+                L["cache"].truncate(s, n_tokens)
+        self.pos.fill_(n_tokens)
+        self.lengths = [n_tokens] * self.B
+
     def prefill_synthetic(self, n_tokens, seed=1):
         """Fills every layer's cache with n_tokens of random K / V per sequence and moves the positions there: a stand-in for
         a long prompt where only the decode steps are of interest."""
