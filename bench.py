@@ -684,7 +684,7 @@ def run_decoder(args, rank, world):
                        "launch": "CUDA-graph segments between cache calls; cache calls from the host"},
             "e2e": {"value": world * B / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": B * 4, "d2h_bytes_per_step": B * 4,
                     "ms_per_step": ms_e2e},
-            "gpu_launches": sh.n_layers * 11 + 6,  # per layer: 4 GEMMs, 4 quantising producers, append, decode, combine
+            "gpu_launches": sh.n_layers * 10 + 6,  # per layer: 4 GEMMs, 3 quantising producers, append, decode, combine (which quantises for wo)
             "kernels_ms": {k: statistics.mean(v) for k, v in recs.items()},
             "prompt_pass": pp,
             "roofline": {"bound": "hbm", "kernel": "whole step (Q4_0 GEMMs dominate)", "achieved": (weight_bytes + kv_bytes) / (ms * 1e-3) / 1e9,

@@ -169,6 +169,15 @@ int b200kv_attend_rope(b200kv_cache* cache, int32_t n_seqs, const int32_t* seqs,
                        const int64_t q_strides[3], const void* cos, const void* sin, int64_t rope_stride, void* out,
                        const int64_t out_strides[3], int32_t dtype, float scale, void* stream);
 
+/* Decode attention whose result lands as the quantised activation of the W4A8 GEMM that follows it (the o-projection of
+ * a decoder block): b200kv_attend with n_new = 1 (b200kv_attend_rope when cos / sin are given) followed by
+ * b200kv_q40_quantize of the [n_seqs, n_q_heads * D] result, bit for bit, without the quantiser launch.  `out` may be null
+ * when only the GEMM reads the result.  `scratch`: b200kv_q40_scratch_bytes(n_q_heads * D, n_seqs) bytes, 16-byte aligned;
+ * follow with b200kv_q40_gemm_quantized(.., m = n_seqs, scratch, ..) on the same stream.  Not for the KIVI formats. */
+int b200kv_attend_q40(b200kv_cache* cache, int32_t n_seqs, const int32_t* seqs, int32_t n_q_heads, const void* q,
+                      const int64_t q_strides[3], const void* cos, const void* sin, int64_t rope_stride, void* out,
+                      const int64_t out_strides[3], void* scratch, int32_t dtype, float scale, void* stream);
+
 /* Gives the pages that lie wholly before the last `keep_last` tokens of a sequence back to the pool: the bounded memory of
  * the reference's ring buffer (window_kv_cache.rs:77-137) on the paged store.  The sequence keeps its length (positions go
  * on counting); from now on attention sees at most the tokens from len - keep_last on, export / fork / truncation below

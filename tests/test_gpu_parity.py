@@ -447,6 +447,50 @@ def test_decode_with_rope_on_the_query_load(kv, fmt, io, D, G):
     cache.close()
 
 
+@pytest.mark.parametrize("fmt,io,D,G,B", [("f16", "f16", 128, 4, 8), ("q8_1", "f16", 128, 4, 5), ("bf16", "bf16", 64, 2, 11), ("f32", "f32", 128, 1, 3),
+                                          ("q4_0", "bf16", 128, 8, 16)])
+def test_decode_result_as_quantised_activation(kv, fmt, io, D, G, B):
+    # the decode result left as the quantised activation of a W4A8 GEMM: the bits of attend (+ rope) -> quantise, on both
+    # decode kernels, with row counts on and off the groups of 8 and the result tensor present or not
+    import oracle as orc
+
+    Hkv = 2
+    Hq = Hkv * G
+    lens = [1 + 37 * b for b in range(B)]
+    cache = kv.KvCache(fmt, Hkv, D, max_seqs=B, max_seq_tokens=max(lens))
+    seqs = [cache.new_seq() for _ in range(B)]
+    for b in range(B):
+        cache.append([seqs[b]], to_dev(normal(6600 + b, (1, Hkv, lens[b], D)).astype(np_dtype(io))),
+                     to_dev(normal_with_outliers(6700 + b, (1, Hkv, lens[b], D)).astype(np_dtype(io))))
+    q = to_dev(normal(6800, (B, Hq, 1, D)).astype(np_dtype(io)))
+    ang = np.random.default_rng(6801).uniform(-np.pi, np.pi, size=(B, D // 2)).astype(np.float32)
+    cos = to_dev(np.concatenate([np.cos(ang), np.cos(ang)], -1).astype(np_dtype(io)))
+    sin = to_dev(np.concatenate([np.sin(ang), np.sin(ang)], -1).astype(np_dtype(io)))
+    n, k = 48, Hq * D
+    sc, pk = orc.q4_0_quant(normal(6802, (n, k)).astype(np.float32))
+    blob = np.empty((n, k // 32, 18), np.uint8)
+    blob[:, :, :2] = sc.reshape(n, k // 32, 1).view(np.uint8)
+    blob[:, :, 2:] = pk.reshape(n, k // 32, 16)
+    lin = kv.Q40Linear(torch.from_numpy(blob).cuda(), max_m=16)
+    scratch = torch.empty(kv.Q40Linear.scratch_bytes(k, B), dtype=torch.uint8, device="cuda")
+    for force_simt in (False, True):
+        cache.profile(False, force_simt=force_simt)
+        for rope in (False, True):
+            plain = cache.attend_rope(seqs, q, cos, sin) if rope else cache.attend(seqs, q, causal=True)
+            want = lin.gemm(plain.view(B, k))
+            out = torch.zeros_like(plain)
+            cache.attend_q40(seqs, q, scratch, cos=cos if rope else None, sin=sin if rope else None, out=out)
+            got = lin.gemm_quantized(B, scratch=scratch)
+            assert torch.equal(out.view(torch.uint8), plain.view(torch.uint8)) and torch.equal(got, want), (force_simt, rope)
+            scratch.fill_(0xA5)  # no result tensor: the padding rows of the last group must still come out as zeros
+            cache.attend_q40(seqs, q, scratch, cos=cos if rope else None, sin=sin if rope else None)
+            assert torch.equal(lin.gemm_quantized(B, scratch=scratch), want), (force_simt, rope)
+    lin.check(scratch)
+    cache.check()
+    cache.profile(False)
+    cache.close()
+
+
 def test_rope_on_the_query_load_refuses_what_it_cannot_do(kv):
     D, Hkv = 128, 2
     q = to_dev(normal(6500, (1, 4, 1, D)).astype(np.float16))

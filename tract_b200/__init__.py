@@ -26,7 +26,7 @@ EXPORTS = [
     "b200kv_profile_read", "b200kv_attend_static_scratch", "b200kv_export_kivi", "b200kv_append_rope", "b200kv_rope",
     "b200kv_q40_packed_bytes", "b200kv_q40_pack", "b200kv_q40_scratch_bytes", "b200kv_q40_gemm", "b200kv_q40_check",
     "b200kv_rms_norm", "b200kv_silu_mul", "b200kv_add", "b200kv_argmax", "b200kv_gather_rows", "b200kv_cast",
-    "b200kv_attend_window", "b200kv_trim", "b200kv_attend_rope", "b200kv_q40_quantize", "b200kv_q40_gemm_quantized", "b200kv_q40_gemm_quantized_as",
+    "b200kv_attend_window", "b200kv_trim", "b200kv_attend_rope", "b200kv_attend_q40", "b200kv_q40_quantize", "b200kv_q40_gemm_quantized", "b200kv_q40_gemm_quantized_as",
     "b200kv_q40_silu_mul_quantize", "b200kv_q40_add_rms_norm_quantize",
 ]
 KERNEL_NAMES = {0: "table_scatter", 1: "append", 2: "decode", 3: "combine", 4: "export", 5: "sdpa_dense", 6: "prefill"}
@@ -81,6 +81,7 @@ def lib():
         L.b200kv_sdpa.argtypes = [vp, i64p, vp, i64p, vp, i64p, vp, i64p, i32, vp, i64p, i32, i32, i32, i32, i32, i32,
                                   i32, C.c_float, i32, vp]
         L.b200kv_attend_rope.argtypes = [vp, i32, i32p, i32, vp, i64p, vp, vp, i64, vp, i64p, i32, C.c_float, vp]
+        L.b200kv_attend_q40.argtypes = [vp, i32, i32p, i32, vp, i64p, vp, vp, i64, vp, i64p, vp, i32, C.c_float, vp]
         L.b200kv_attend_window.argtypes = [vp, i32, i32p, i32, vp, i64p, vp, i64p, i32, C.c_float, i64, vp]
         L.b200kv_trim.argtypes = [vp, i32, i64]
         _lib = L
@@ -279,6 +280,24 @@ class KvCache:
         _ck(lib().b200kv_attend_rope(self._h, len(seqs), _ids(seqs), q.shape[1], q.data_ptr(), _strides(q, 3), cos.data_ptr(),
                                      sin.data_ptr(), C.c_int64(cos.stride(0)), out.data_ptr(), _strides(out, 3), _dtype_code(q),
                                      C.c_float(scale or 0.0), _stream()))
+        return out
+
+    def attend_q40(self, seqs, q, scratch, cos=None, sin=None, scale=None, out=None):
+        """Decode attention (of ApplyRope(q) when cos / sin are given) left in `scratch` as the quantised activation of a
+        Q40Linear over [n_seqs, Hq * D]; also written to `out` when given.  Follow with Q40Linear.gemm_quantized(n_seqs, ..)."""
+        assert q.dim() == 4 and q.shape[0] == len(seqs) and q.shape[2] == 1
+        assert scratch.numel() >= Q40Linear.scratch_bytes(q.shape[1] * q.shape[3], len(seqs))
+        stride = 0
+        if cos is not None:
+            cos, sin = cos.reshape(len(seqs), -1), sin.reshape(len(seqs), -1)
+            assert cos.dtype == q.dtype and sin.dtype == q.dtype and cos.stride(1) == 1 and sin.stride(1) == 1
+            assert cos.stride(0) == sin.stride(0) and cos.shape[1] == q.shape[3]
+            stride = cos.stride(0)
+        _ck(lib().b200kv_attend_q40(self._h, len(seqs), _ids(seqs), q.shape[1], q.data_ptr(), _strides(q, 3),
+                                    cos.data_ptr() if cos is not None else None, sin.data_ptr() if sin is not None else None,
+                                    C.c_int64(stride), out.data_ptr() if out is not None else None,
+                                    _strides(out, 3) if out is not None else None, scratch.data_ptr(), _dtype_code(q),
+                                    C.c_float(scale or 0.0), _stream()))
         return out
 
     def fork(self, seq) -> int:

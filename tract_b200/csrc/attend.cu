@@ -99,6 +99,30 @@ extern "C" int b200kv_attend_rope(b200kv_cache* c, int32_t n_seqs, const int32_t
     if (c->L.D % 2 != 0) return fail("ApplyRope needs an even head_dim");
     if (scale <= 0.f) scale = 1.0f / sqrtf((float)c->L.D);
     DeviceGuard guard(c->cfg.device);
-    const QueryRope rope{cos, sin, rope_stride};
+    const QueryRope rope{cos, sin, rope_stride, nullptr};
     return launch_decode(c, n_seqs, seqs, n_q_heads, q, q_strides, out, out_strides, dtype, scale, (cudaStream_t)stream_, 0, &rope);
+}
+
+// Decode attention whose result lands as the quantised activation of the W4A8 GEMM that follows it (the o-projection of a
+// decoder block): b200kv_attend (or b200kv_attend_rope, when cos / sin are given) followed by b200kv_q40_quantize of the
+// [n_seqs, n_q_heads * D] result, bit for bit, without the quantiser launch.  `out` may be null when only the GEMM reads
+// the result.  `scratch`: b200kv_q40_scratch_bytes(n_q_heads * D, n_seqs) bytes; then b200kv_q40_gemm_quantized with m = n_seqs.
+extern "C" int b200kv_attend_q40(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t n_q_heads, const void* q,
+                                 const int64_t q_strides[3], const void* cos, const void* sin, int64_t rope_stride, void* out,
+                                 const int64_t out_strides[3], void* scratch, int32_t dtype, float scale, void* stream_) {
+    if (validate_seqs(c, n_seqs, seqs) != B200KV_OK) return B200KV_KO;
+    if (!c->L.has_v) return fail("this cache holds one tensor only: attention needs K and V");
+    if (fmt_is_kivi(c->L.fmt)) return fail("a KIVI cache has no fused epilogue: b200kv_attend, then b200kv_q40_quantize");
+    if (!q || !q_strides || !scratch || (out && !out_strides)) return fail("null tensor or strides");
+    if ((cos == nullptr) != (sin == nullptr)) return fail("cos and sin come together");
+    if ((uintptr_t)scratch % 16) return fail("scratch must be 16-byte aligned");
+    if (n_q_heads <= 0 || n_q_heads % c->L.Hkv != 0)
+        return fail("n_q_heads (%d) must be a positive multiple of n_kv_heads (%d)", n_q_heads, c->L.Hkv);
+    if (dtype < B200KV_F32 || dtype > B200KV_BF16) return fail("unknown dtype %d", dtype);
+    if (c->L.D % 32 != 0) return fail("the quantised epilogue needs head_dim a multiple of 32");
+    if (scale <= 0.f) scale = 1.0f / sqrtf((float)c->L.D);
+    DeviceGuard guard(c->cfg.device);
+    const QueryRope ends{cos, sin, rope_stride, scratch};
+    const int64_t no_strides[3] = {0, 0, 0};
+    return launch_decode(c, n_seqs, seqs, n_q_heads, q, q_strides, out, out ? out_strides : no_strides, dtype, scale, (cudaStream_t)stream_, 0, &ends);
 }

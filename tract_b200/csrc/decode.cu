@@ -13,6 +13,7 @@
 #include <vector>
 
 #include "decode_common.h"
+#include "q40_common.cuh"
 
 namespace b200kv {
 
@@ -312,9 +313,14 @@ struct CombineParams {
     const float* part_o;
     const float* part_ml;
     const int32_t* batch_info;  // per batch entry: {first item, item count}
-    void* out;
+    void* out;  // may be null when `act` is given
     int64_t ob, oh;
     int32_t Hkv, G, D, dtype;
+    // The result as the quantised activation of a W4A8 GEMM (rows = batch entries, columns = (q head, channel)): null, or
+    // the block records of q40_common.cuh.  The grid then covers the rows up to the next multiple of 8, which are zero.
+    uint8_t* act;
+    int* act_status;
+    int32_t n_rows;
 };
 
 // Second pass: out = sum_i e^{m_i - M} O_i / sum_i e^{m_i - M} l_i over the splits of one (sequence, q-head).
@@ -326,6 +332,16 @@ __global__ void combine_kernel(CombineParams p, const __grid_constant__ InlineBa
     const int b = blockIdx.x, hq = blockIdx.y, ch = threadIdx.x;
     const int kvh = hq / p.G, g = hq % p.G;
     grid_dependency_wait();  // the decode kernel has published every partial
+    uint8_t* act_dst = nullptr;
+    if (p.act) {  // a warp holds one block of 32 columns of row b
+        const int64_t nb = (int64_t)p.Hkv * p.G * p.D / QK;
+        act_dst = p.act + ((int64_t)(b >> 3) * nb + (int64_t)hq * (p.D / QK) + (ch >> 5)) * Q_ACT_BLOCK;
+        if (b == 0 && hq == 0 && ch == 0) *p.act_status = 0;
+        if (b >= p.n_rows) {
+            q40_quantize_block(0.f, false, act_dst, b & 7, ch & 31);
+            return;
+        }
+    }
     const int first = ib.n ? ib.ent[b].z : p.batch_info[2 * b], n = ib.n ? ib.ent[b].w : p.batch_info[2 * b + 1];
     const int64_t stride = (int64_t)p.Hkv * p.G;
     const int64_t base = ((int64_t)first * p.Hkv + kvh) * p.G + g;
@@ -360,7 +376,9 @@ __global__ void combine_kernel(CombineParams p, const __grid_constant__ InlineBa
 #pragma unroll
         for (int k = 0; k < 8; k++) num = fmaf((i0 + k < n) ? wgt_s[i0 + k] : 0.f, v[k], num);
     }
-    st_from_f32(p.out, p.dtype, (int64_t)b * p.ob + (int64_t)hq * p.oh + ch, num / den_s);
+    const float res = num / den_s;
+    if (p.out) st_from_f32(p.out, p.dtype, (int64_t)b * p.ob + (int64_t)hq * p.oh + ch, res);
+    if (p.act) q40_quantize_block(round_to_dtype(res, p.dtype), true, act_dst, b & 7, ch & 31);  // what a quantiser would read back from `out`
 }
 
 template <int FMT, int D, int GT>
@@ -498,7 +516,7 @@ int launch_decode(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t 
     DecodeParams p{};
     p.pool = c->pool, p.table = c->d_table, p.items = (const WorkItem*)d, p.status = c->d_status;
     p.q = q, p.qb = qs[0], p.qh = qs[1];
-    if (rope) p.q_cos = rope->cos, p.q_sin = rope->sin, p.rope_b = rope->stride_b;
+    if (rope && rope->cos) p.q_cos = rope->cos, p.q_sin = rope->sin, p.rope_b = rope->stride_b;
     p.part_o = (float*)c->ws;
     p.part_ml = p.part_o + n_part * D;
     p.page_bytes = c->L.page_bytes, p.n_pages = (int32_t)c->n_pages, p.max_pages_per_seq = c->max_pages_per_seq;
@@ -524,7 +542,9 @@ int launch_decode(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t 
         cp.part_o = p.part_o, cp.part_ml = p.part_ml, cp.batch_info = (const int32_t*)(d + items_bytes);
         cp.out = out, cp.ob = os[0], cp.oh = os[1];
         cp.Hkv = Hkv, cp.G = G, cp.D = D, cp.dtype = dtype;
-        if (launch_after_predecessor(combine_kernel, dim3(n_seqs, n_q_heads), dim3(D), 0, stream, cp, ib) != cudaSuccess)
+        if (rope && rope->act_scratch) cp.act = (uint8_t*)rope->act_scratch + Q_HEADER, cp.act_status = (int*)rope->act_scratch, cp.n_rows = n_seqs;
+        const unsigned rows = cp.act ? (unsigned)((n_seqs + 7) / 8 * 8) : (unsigned)n_seqs;
+        if (launch_after_predecessor(combine_kernel, dim3(rows, n_q_heads), dim3(D), 0, stream, cp, ib) != cudaSuccess)
             rc = fail("combine launch failed: %s", cudaGetErrorString(cudaGetLastError()));
     }
     if (slot >= 0) staging_release(c, slot, stream);

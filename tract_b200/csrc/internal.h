@@ -127,10 +127,11 @@ struct ProfScope {
 };
 
 // decode.cu
-struct QueryRope {  // ApplyRope of the query inside the decode kernels: one cos / sin row of D values per batch entry
-    const void* cos;
+struct QueryRope {  // what a decode call may fold in at its two ends
+    const void* cos;   // ApplyRope of the query inside the decode kernels: one cos / sin row of D values per batch entry, or null
     const void* sin;
     int64_t stride_b;  // elements
+    void* act_scratch; // the result also (or only) as the quantised activation of a W4A8 GEMM, or null
 };
 int64_t decode_pages_per_split(const b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int64_t window, bool use_mma, int nz);
 int launch_decode(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t n_q_heads, const void* q,

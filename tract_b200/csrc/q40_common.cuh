@@ -1,0 +1,40 @@
+// Layout of the quantised activations of the W4A8 GEMM, and the quantiser of one block: shared by the GEMM's own producers
+// and by the attention kernels that leave their result in that form.
+#pragma once
+#include <cstdint>
+#include <cuda_runtime.h>
+
+namespace b200kv {
+
+constexpr int QK = 32;                    // block length
+constexpr int Q_TILE_ROWS = 16;           // output rows per warp (the M of the MMA)
+constexpr int Q_BLOCK_BYTES = 16 * 16 + 16 * 2;  // one block of a tile: 256 nibble bytes + 16 f16 scales
+constexpr int Q_STAGE_BLOCKS = 8;
+constexpr int Q_STAGE_BYTES = Q_STAGE_BLOCKS * Q_BLOCK_BYTES;  // 2304
+constexpr int Q_DEPTH = 2;                // stages in flight per warp
+constexpr int Q_ACT_BLOCK = 2 * 8 * 16 + 8 * 4 + 8 * 4;  // per block and group of 8 activation rows: codes [2 halves][8][16], scales f32 [8], sums i32 [8]
+constexpr int Q_HEADER = 256;             // scratch header: the status word
+constexpr int Q_RING_STAGE = Q_STAGE_BYTES + Q_STAGE_BLOCKS * Q_ACT_BLOCK;  // weights then activations of 8 blocks: 4864 bytes
+
+// Q4_0::quantize_row_q8 (q4_0.rs:199-222) for one block: the 32 lanes of a warp hold its 32 values.  Writes the codes,
+// the scale and the code sum of activation row slot `slot` into the block's record.  `valid` false (a slot past the last
+// row): zero codes, scale 0.
+__device__ inline void q40_quantize_block(float x, bool valid, uint8_t* dst, int slot, int lane) {
+    if (!valid) x = 0.f;
+    float amax = fabsf(x);
+#pragma unroll
+    for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));  // fmaxf ignores a NaN operand, as f32::max does
+    amax = fmaxf(0.f, amax);                                                                 // the fold starts from 0: an all-NaN block gives 0
+    const float scale = amax > 0.f ? __fdiv_rn(amax, 127.0f) : 1.0f;
+    const float r = __fdiv_rn(1.0f, scale);
+    const float t = roundf(__fmul_rn(x, r));  // NaN for a NaN input and for inf * 0
+    const int q = (t != t) ? 0 : (int)fminf(fmaxf(t, -127.f), 127.f);  // f32::clamp keeps a NaN, the cast to i8 makes it 0
+    const int sum = __reduce_add_sync(0xffffffffu, q);
+    dst[(lane >> 4) * 128 + slot * 16 + (lane & 15)] = (uint8_t)(int8_t)q;
+    if (lane == 0) {
+        ((float*)(dst + 256))[slot] = valid ? scale : 0.f;
+        ((int32_t*)(dst + 288))[slot] = sum;
+    }
+}
+
+}  // namespace b200kv

@@ -99,7 +99,6 @@ class Decoder:
         self.qkv16 = z(B, nq + 2 * nk, dt=self.kv_dtype)
         heads = lambda lo, n: self.qkv16[:, lo:lo + n * sh.head_dim].unflatten(1, (n, 1, sh.head_dim))
         self.q16, self.k16, self.v16 = heads(0, sh.n_q_heads), heads(nq, sh.n_kv_heads), heads(nq + nk, sh.n_kv_heads)
-        self.attn16 = z(B, sh.n_q_heads, 1, sh.head_dim, dt=self.kv_dtype)
         self.proj, self.gate_up = z(B, sh.hidden), z(B, 2 * sh.ffn)
         # the quantised activation of the GEMM in flight; every producer and GEMM of a step runs on one stream, in order
         self.scratch = torch.empty(kv.Q40Linear.scratch_bytes(max(sh.hidden, sh.ffn, nq), B), dtype=torch.uint8, device=dev)
@@ -124,7 +123,7 @@ class Decoder:
 
     def _post_attention(self, L):
         sh = self.shape
-        L["wo"].gemm(self.attn16.view(self.B, -1), self.proj, scratch=self.scratch)
+        L["wo"].gemm_quantized(self.B, self.proj, scratch=self.scratch)  # the attention left its result quantised (attend_q40)
         kv.q40_add_rms_norm_quantize(self.x, self.scratch, sh.eps, weight=L["ffn_norm"], residual=self.proj, x_out=self.x)
         L["wgu"].gemm_quantized(self.B, self.gate_up, scratch=self.scratch)
         kv.q40_silu_mul_quantize(self.gate_up[:, :sh.ffn], self.gate_up[:, sh.ffn:], self.scratch)
@@ -173,7 +172,7 @@ class Decoder:
         for i, L in enumerate(self.layers):
             ids = self.seqs[i]
             L["cache"].append_rope(ids, self.k16, self.v16, self.cos_t.view(self.B, 1, -1), self.sin_t.view(self.B, 1, -1))
-            L["cache"].attend_rope(ids, self.q16, self.cos_t, self.sin_t, out=self.attn16)
+            L["cache"].attend_q40(ids, self.q16, self.scratch, cos=self.cos_t, sin=self.sin_t)
             run(i + 1)
         self.pos += 1
         self.lengths = [n + 1 for n in self.lengths]

@@ -163,6 +163,13 @@ class KvState {
         ck(b200kv_attend_rope(cache_, 1, &seq_, (int32_t)q.shape[1], q.ptr, q.strides, cos.ptr, sin.ptr, 0, out.ptr, out.strides,
                               (int)q.dt, scale, stream));
     }
+    // Sdpa at S = 1 whose only consumer is a Q4_0 MatMul: the result lands in `scratch` as that MatMul's quantised activation
+    // (Q40MatMul::eval_quantized with m = 1 follows).  cos / sin (ApplyRope on q) and out are optional.
+    void attend_q40(const DeviceTensor& q, const void* cos, const void* sin, void* out, const int64_t* out_strides, void* scratch,
+                    float scale, void* stream) {
+        ck(b200kv_attend_q40(cache_, 1, &seq_, (int32_t)q.shape[1], q.ptr, q.strides, cos, sin, 0, out, out_strides, scratch, (int)q.dt,
+                             scale, stream));
+    }
     void check(void* stream) { ck(b200kv_check(cache_, stream)); }
     const CacheSpec& spec() const { return spec_; }
 
