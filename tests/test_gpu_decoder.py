@@ -153,3 +153,28 @@ def test_chunked_prompt_and_rollback_repeat_bit_for_bit():
         assert torch.equal(dec.logits, logits[i]), i
     dec.check()
     dec.close()
+
+
+@pytest.mark.parametrize("kv_format", ["f16", "q8_1"])
+def test_decoder_runs_repeat_bit_for_bit(kv_format):
+    # Every kernel of a step is scheduled behind its predecessor with a programmatic dependency and fetches part of its
+    # input early; a step that read anything too early would not repeat.  Two runs of 40 steps from the same prompt, on a
+    # model large enough that the kernels overlap for real, must agree in every logit of every step.
+    from tract_b200.decoder import Decoder, Shape
+
+    sh = Shape(hidden=1024, n_layers=4, n_q_heads=8, n_kv_heads=2, head_dim=128, ffn=4096, vocab=8192, rope_theta=10000.0)
+    dec = Decoder(sh, n_seqs=8, max_tokens=400, kv_format=kv_format, seed=21, use_graphs=True)
+    prompt = torch.from_numpy(np.random.default_rng(22).integers(0, sh.vocab, (8, 200)).astype(np.int32))
+    runs = []
+    for _ in range(2):
+        dec.reset()
+        dec.prefill(prompt)
+        steps = [dec.logits.clone()]
+        for _ in range(40):
+            dec.step()
+            steps.append(dec.logits.clone())
+        runs.append(torch.stack(steps))
+    assert torch.isfinite(runs[0]).all()
+    assert torch.equal(runs[0], runs[1])
+    dec.check()
+    dec.close()
