@@ -445,7 +445,17 @@ int64_t decode_pages_per_split(const b200kv_cache* c, int32_t n_seqs, const int3
     for (int i = 0; i < n_seqs; i++) total_pages += pages_of(i), max_pages = std::max<int64_t>(max_pages, pages_of(i));
     const int64_t work = total_pages * Hkv * nz, target_ctas = 148 * 16, one_wave = 148 * 3;
     int64_t chunk = std::max<int64_t>((work + target_ctas - 1) / target_ctas, std::min<int64_t>((work + one_wave - 1) / one_wave, 8));
-    const int resident = use_mma ? (c->L.fmt == B200KV_FMT_Q4_0 ? 4 : (c->L.fmt == B200KV_FMT_Q8_1 ? 3 : 2)) : 3;
+    int resident;
+    if (use_mma) {
+        resident = c->L.fmt == B200KV_FMT_Q4_0 ? 4 : (c->L.fmt == B200KV_FMT_Q8_1 ? 3 : 2);
+    } else {  // the CUDA-core kernel: its ring of stages (Geo<FMT, D>) decides how many CTAs share an SM
+        const int D = c->L.D, fmt = c->L.fmt;
+        const int row = fmt == B200KV_FMT_F32 ? D * 4 : (fmt == B200KV_FMT_F16 || fmt == B200KV_FMT_BF16) ? D * 2 : fmt == B200KV_FMT_Q8_1 ? D : D / 2;
+        const int scales = (fmt == B200KV_FMT_Q8_1 || fmt == B200KV_FMT_Q4_0) ? PAGE_TOKENS * (D / 32) * 2 : 0;
+        const int stage = 2 * (PAGE_TOKENS * row + scales);
+        const int ns = std::min(4, std::max(2, 98304 / stage));
+        resident = std::max(1, std::min(4, (227 * 1024) / (ns * stage + 4096)));
+    }
     int64_t slots = 148 * resident;
     if (use_mma && c->L.fmt == B200KV_FMT_Q4_0 && work >= 2 * slots * 16) slots *= 2;
     if ((int64_t)n_seqs * Hkv * nz <= slots) {
