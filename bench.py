@@ -201,16 +201,14 @@ def run_ours(args, rank, world):
     hout = torch.empty_like(out, device="cpu").pin_memory()
 
     def step():
-        cache.append(seqs, k_new, v_new)
-        cache.attend(seqs, q, causal=True, out=out)
+        cache.append_attend(seqs, k_new, v_new, q, causal=True, out=out)
         if not grows:
             for s, n in zip(seqs, lens):  # host bookkeeping only: keep the past length fixed from step to step
                 cache.truncate(s, n)
 
     def step_e2e():
         dqkv.copy_(hqkv, non_blocking=True)
-        cache.append(seqs, dk, dv)
-        cache.attend(seqs, dq, causal=True, out=out)
+        cache.append_attend(seqs, dk, dv, dq, causal=True, out=out)
         hout.copy_(out, non_blocking=True)
         if not grows:
             for s, n in zip(seqs, lens):

@@ -153,6 +153,15 @@ int b200kv_export_codes(b200kv_cache* cache, int32_t seq, int32_t which, void* c
 int b200kv_export_kivi(b200kv_cache* cache, int32_t seq, int32_t which, void* codes, float* lo, float* scale,
                        float* sink, float* residual, void* stream);
 
+/* The fused cache + attention op as one call (InPlaceKvSdpa::eval, transformers/src/ops/inplace_kv_cache.rs:190-216: push
+ * K_new / V_new, then Sdpa of Q over the accumulated cache): b200kv_append followed by b200kv_attend with the same n_new,
+ * one transition from the host instead of two.  If the attention is refused after the append went through, the appended
+ * tokens stay (b200kv_truncate takes them back). */
+int b200kv_append_attend(b200kv_cache* cache, int32_t n_seqs, const int32_t* seqs, int32_t n_new, const void* k_new,
+                         const int64_t k_strides[3], const void* v_new, const int64_t v_strides[3], int32_t n_q_heads,
+                         const void* q, const int64_t q_strides[3], void* out, const int64_t out_strides[3], int32_t dtype,
+                         float scale, int32_t causal, void* stream);
+
 /* Sliding-window decode attention (WindowKvSdpa, transformers/src/ops/window_kv_cache.rs:160-228: K / V ring buffers of
  * `window` slots, attention over the valid slots without a mask): the one query of every sequence (q, out:
  * [n_seqs, n_q_heads, 1, D]) attends over its last `window` cached tokens.  Call after b200kv_append, like b200kv_attend.

@@ -491,6 +491,26 @@ def test_decode_result_as_quantised_activation(kv, fmt, io, D, G, B):
     cache.close()
 
 
+@pytest.mark.parametrize("fmt,io,S", [("f16", "f16", 1), ("q8_1", "f16", 1), ("f32", "f32", 1), ("f16", "f16", 70), ("kivi8", "f16", 1)])
+def test_fused_cache_and_attention_call(kv, fmt, io, S):
+    # InPlaceKvSdpa as one call: the bits of append followed by attend, step after step
+    Hkv, G, D, B = 2, 4, 128, 3
+    a = kv.KvCache(fmt, Hkv, D, max_seqs=B, max_seq_tokens=512)
+    b = kv.KvCache(fmt, Hkv, D, max_seqs=B, max_seq_tokens=512)
+    sa, sb = [a.new_seq() for _ in range(B)], [b.new_seq() for _ in range(B)]
+    for step in range(4):
+        k = to_dev(normal(7000 + step, (B, Hkv, S, D)).astype(np_dtype(io)))
+        v = to_dev(normal_with_outliers(7100 + step, (B, Hkv, S, D)).astype(np_dtype(io)))
+        q = to_dev(normal(7200 + step, (B, Hkv * G, S, D)).astype(np_dtype(io)))
+        a.append(sa, k, v)
+        two = a.attend(sa, q, causal=True)
+        one = b.append_attend(sb, k, v, q, causal=True)
+        assert torch.equal(one.view(torch.uint8), two.view(torch.uint8)), step
+    assert [a.seq_len(s) for s in sa] == [b.seq_len(s) for s in sb] == [4 * S] * B
+    a.check(), b.check()
+    a.close(), b.close()
+
+
 def test_rope_on_the_query_load_refuses_what_it_cannot_do(kv):
     D, Hkv = 128, 2
     q = to_dev(normal(6500, (1, 4, 1, D)).astype(np.float16))

@@ -26,7 +26,7 @@ EXPORTS = [
     "b200kv_profile_read", "b200kv_attend_static_scratch", "b200kv_export_kivi", "b200kv_append_rope", "b200kv_rope",
     "b200kv_q40_packed_bytes", "b200kv_q40_pack", "b200kv_q40_scratch_bytes", "b200kv_q40_gemm", "b200kv_q40_check",
     "b200kv_rms_norm", "b200kv_silu_mul", "b200kv_add", "b200kv_argmax", "b200kv_gather_rows", "b200kv_cast",
-    "b200kv_attend_window", "b200kv_trim", "b200kv_attend_rope", "b200kv_attend_q40", "b200kv_q40_quantize", "b200kv_q40_gemm_quantized", "b200kv_q40_gemm_quantized_as",
+    "b200kv_attend_window", "b200kv_trim", "b200kv_attend_rope", "b200kv_attend_q40", "b200kv_append_attend", "b200kv_q40_quantize", "b200kv_q40_gemm_quantized", "b200kv_q40_gemm_quantized_as",
     "b200kv_q40_silu_mul_quantize", "b200kv_q40_add_rms_norm_quantize",
 ]
 KERNEL_NAMES = {0: "table_scatter", 1: "append", 2: "decode", 3: "combine", 4: "export", 5: "sdpa_dense", 6: "prefill"}
@@ -68,6 +68,7 @@ def lib():
         L.b200kv_append.argtypes = [vp, i32, i32p, i32, vp, i64p, vp, i64p, i32, vp]
         L.b200kv_append_rope.argtypes = [vp, i32, i32p, i32, vp, i64p, vp, i64p, vp, vp, i64p, i32, vp]
         L.b200kv_rope.argtypes = [vp, i64p, vp, vp, i64p, vp, i64p, i32, i32, i32, i32, i32, vp]
+        L.b200kv_append_attend.argtypes = [vp, i32, i32p, i32, vp, i64p, vp, i64p, i32, vp, i64p, vp, i64p, i32, C.c_float, i32, vp]
         L.b200kv_attend.argtypes = [vp, i32, i32p, i32, i32, vp, i64p, vp, i64p, i32, C.c_float, i32, vp]
         L.b200kv_export.argtypes = [vp, i32, vp, i64p, vp, i64p, i32, vp]
         L.b200kv_export_codes.argtypes = [vp, i32, i32, vp, vp, vp]
@@ -192,6 +193,19 @@ class KvCache:
         _ck(lib().b200kv_attend(self._h, len(seqs), _ids(seqs), q.shape[1], q.shape[2], q.data_ptr(), _strides(q, 3),
                                 out.data_ptr(), _strides(out, 3), _dtype_code(q), float(scale or 0.0), int(causal),
                                 _stream()))
+        return out
+
+    def append_attend(self, seqs, k_new, v_new, q, scale=None, causal=True, out=None):
+        """append(seqs, k_new, v_new) then attend(seqs, q): the fused cache + attention op as one call into the library."""
+        import torch
+
+        assert k_new.dim() == 4 and q.dim() == 4 and q.shape[0] == len(seqs) == k_new.shape[0] and q.shape[2] == k_new.shape[2]
+        assert q.dtype == k_new.dtype
+        if out is None:
+            out = torch.empty_like(q, memory_format=torch.contiguous_format)
+        _ck(lib().b200kv_append_attend(self._h, len(seqs), _ids(seqs), k_new.shape[2], k_new.data_ptr(), _strides(k_new, 3),
+                                       v_new.data_ptr(), _strides(v_new, 3), q.shape[1], q.data_ptr(), _strides(q, 3), out.data_ptr(),
+                                       _strides(out, 3), _dtype_code(q), float(scale or 0.0), int(causal), _stream()))
         return out
 
     def attend_static_scratch(self, seqs, q, scale=None, out=None):

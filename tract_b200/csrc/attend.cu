@@ -126,3 +126,15 @@ extern "C" int b200kv_attend_q40(b200kv_cache* c, int32_t n_seqs, const int32_t*
     const int64_t no_strides[3] = {0, 0, 0};
     return launch_decode(c, n_seqs, seqs, n_q_heads, q, q_strides, out, out ? out_strides : no_strides, dtype, scale, (cudaStream_t)stream_, 0, &ends);
 }
+
+// The fused cache + attention op as one call (InPlaceKvSdpa::eval, transformers/src/ops/inplace_kv_cache.rs:190-216: push
+// K_new / V_new, then Sdpa of Q over the accumulated cache): b200kv_append followed by b200kv_attend, one transition
+// from the host instead of two.
+extern "C" int b200kv_append_attend(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t n_new, const void* k_new,
+                                    const int64_t k_strides[3], const void* v_new, const int64_t v_strides[3], int32_t n_q_heads,
+                                    const void* q, const int64_t q_strides[3], void* out, const int64_t out_strides[3], int32_t dtype,
+                                    float scale, int32_t causal, void* stream) {
+    if (!q || !out || !q_strides || !out_strides) return fail("null tensor or strides");  // before anything is appended
+    if (b200kv_append(c, n_seqs, seqs, n_new, k_new, k_strides, v_new, v_strides, dtype, stream) != B200KV_OK) return B200KV_KO;
+    return b200kv_attend(c, n_seqs, seqs, n_q_heads, n_new, q, q_strides, out, out_strides, dtype, scale, causal, stream);
+}

@@ -146,6 +146,13 @@ class KvState {
         ck(b200kv_append(cache_, 1, &seq_, (int32_t)k.shape[2], k.ptr, k.strides, v ? v->ptr : nullptr, v ? v->strides : nullptr,
                          (int)k.dt, stream));
     }
+    // push K_new / V_new, then attend: InPlaceKvSdpa::eval as one call into the library
+    void append_attend(const DeviceTensor& k, const DeviceTensor& v, const DeviceTensor& q, const DeviceTensor& out, float scale, bool causal,
+                       void* stream) {
+        if (k.shape[0] != 1) throw Error("one State holds one sequence: batch must be 1");
+        ck(b200kv_append_attend(cache_, 1, &seq_, (int32_t)k.shape[2], k.ptr, k.strides, v.ptr, v.strides, (int32_t)q.shape[1], q.ptr,
+                                q.strides, out.ptr, out.strides, (int)q.dt, scale, causal ? 1 : 0, stream));
+    }
     void attend(const DeviceTensor& q, const DeviceTensor& out, float scale, bool causal, void* stream) {
         ck(b200kv_attend(cache_, 1, &seq_, (int32_t)q.shape[1], (int32_t)q.shape[2], q.ptr, q.strides, out.ptr, out.strides, (int)q.dt,
                          scale, causal ? 1 : 0, stream));
@@ -201,8 +208,7 @@ struct PagedKvSdpa {
     KvState* state(int device) const { return new KvState(spec, /*has_values=*/true, device); }
     void eval(KvState& st, const DeviceTensor& q, const DeviceTensor& k_new, const DeviceTensor& v_new, const DeviceTensor& out,
               void* stream) const {
-        st.append(k_new, &v_new, stream);
-        st.attend(q, out, scale, is_causal, stream);
+        st.append_attend(k_new, v_new, q, out, scale, is_causal, stream);
     }
 };
 
