@@ -39,13 +39,17 @@ def ggml_blocks(sc, pk):
     (13, 40, 352, "f32"),     # two groups of activation rows, a last stage of 3 blocks
     (40, 64, 4096, "f32"),    # five groups of 8 rows: a CTA row with four groups sharing the weight stages, one with a single group
     (33, 32, 14336, "f16"),   # 8 warps per tile, a last group with one live row
+    (257, 48, 4096, "f32"),   # many rows: 33 groups over 5 blocks of 8 warps, the last block with one warp, the last group with one row
+    (64, 40, 14336, "f16"),   # exactly one block of 8 full groups, 56 stages through a 4-deep weight ring
+    (100, 24, 352, "bf16"),   # a last stage of 3 blocks, fewer stages than the activation ring is deep... and a ragged tile
+    (32, 16, 64, "f32"),      # one stage only
 ])
 def test_q40_gemm_bit_exact(kv, m, n, k, adt):
     w = normal_with_outliers(11, (n, k)).astype(np.float32)
     tdt = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}[adt]
     a_t = torch.from_numpy(normal(12, (m, k)).astype(np.float32)).to(tdt)
     sc, pk = oracle.q4_0_quant(w)
-    lin = kv.Q40Linear(torch.from_numpy(ggml_blocks(sc, pk)).cuda(), max_m=64)
+    lin = kv.Q40Linear(torch.from_numpy(ggml_blocks(sc, pk)).cuda(), max_m=max(64, m))
     got = lin.gemm(a_t.cuda()).cpu().numpy()
     lin.check()
     want = oracle.w4a8_gemm(sc, pk, a_t.float().numpy())

@@ -305,6 +305,129 @@ __global__ void __launch_bounds__(Q_WARPS * 32, MG == 1 ? 2 : 1) q40_gemm_kernel
     }
 }
 
+// ---- many activation rows (a prompt pass) ------------------------------------------------------------------------
+// grid: (tiles of 16 output rows, blocks of R_WARPS * R_GPW groups of 8 activation rows).  Every warp owns R_GPW groups and
+// walks ALL stages of the tile in order, so its accumulators never leave its registers and the additions are in the
+// reference's order by construction.  The weight stages are shared: a producer warp pulls them into a ring that the
+// R_WARPS consumer warps read (full / empty barriers); every consumer pulls the quantised activations of its own rows.
+constexpr int R_WARPS = 8;     // consumer warps per CTA
+constexpr int R_GPW = 2;       // groups of 8 activation rows per warp: the unpacked weights of a block serve both
+constexpr int R_WDEPTH = 4;    // weight stages in flight per CTA
+constexpr int R_ADEPTH = 2;    // activation stages in flight per warp
+constexpr int R_ASTAGE = Q_STAGE_BLOCKS * Q_ACT_BLOCK;  // one group's blocks of a stage: 2560 bytes
+constexpr size_t R_SMEM = (size_t)R_WDEPTH * Q_STAGE_BYTES + (size_t)R_WARPS * R_ADEPTH * R_GPW * R_ASTAGE + (2 * R_WDEPTH + R_WARPS * R_ADEPTH) * 8 + 16;
+
+__global__ void __launch_bounds__((R_WARPS + 1) * 32, 2) q40_gemm_rows_kernel(Q40Gemm p) {
+    extern __shared__ __align__(128) uint8_t ring[];
+    uint8_t* aring = ring + R_WDEPTH * Q_STAGE_BYTES;                           // [R_WARPS][R_ADEPTH][R_GPW] activation stages
+    uint64_t* wfull = (uint64_t*)(aring + R_WARPS * R_ADEPTH * R_GPW * R_ASTAGE);  // [R_WDEPTH] weight bytes landed
+    uint64_t* wempty = wfull + R_WDEPTH;                                        // [R_WDEPTH] consumer warps done with the slot
+    uint64_t* afull = wempty + R_WDEPTH;                                        // [R_WARPS][R_ADEPTH]
+    volatile int* fail_s = (volatile int*)(afull + R_WARPS * R_ADEPTH);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, r = lane >> 2, c = lane & 3;
+    const int64_t tile = blockIdx.x, groups = (p.m + 7) / 8, g0 = (int64_t)blockIdx.y * (R_WARPS * R_GPW);
+    const int nw = (int)min((int64_t)R_WARPS, (groups - g0 + R_GPW - 1) / R_GPW);  // consumer warps with rows
+    const uint8_t* wsrc = p.packed + tile * p.nb * Q_BLOCK_BYTES;
+    const int n_stages = (int)((p.nb + Q_STAGE_BLOCKS - 1) / Q_STAGE_BLOCKS);
+    auto blocks_of = [&](int s) { return (uint32_t)min((int64_t)Q_STAGE_BLOCKS, p.nb - (int64_t)s * Q_STAGE_BLOCKS); };
+    if (tid == 0) {
+        for (int i = 0; i < R_WDEPTH; i++) mbar_init(&wfull[i], 1), mbar_init(&wempty[i], nw);
+        for (int i = 0; i < R_WARPS * R_ADEPTH; i++) mbar_init(&afull[i], 1);
+        *fail_s = 0;
+        mbar_fence_init();
+    }
+    __syncthreads();
+    grid_launch_dependents();
+    if (warp == R_WARPS) {  // ---- producer of the weight stages (one lane) ----
+        if (lane == 0)
+            for (int s = 0; s < n_stages; s++) {
+                const int sl = s % R_WDEPTH;
+                if (s >= R_WDEPTH) q40_wait(&wempty[sl], (uint32_t)((s / R_WDEPTH - 1) & 1), fail_s);
+                if (*fail_s) break;
+                mbar_expect_tx(&wfull[sl], blocks_of(s) * Q_BLOCK_BYTES);
+                bulk_g2s(ring + sl * Q_STAGE_BYTES, wsrc + (int64_t)s * Q_STAGE_BYTES, blocks_of(s) * Q_BLOCK_BYTES, &wfull[sl]);
+            }
+    } else if (warp < nw) {  // ---- consumers ----
+        const int64_t gw = g0 + (int64_t)warp * R_GPW;                 // first group of this warp
+        const int ngw = (int)min((int64_t)R_GPW, groups - gw);        // its live groups
+        const uint8_t* asrc = p.act + gw * p.nb * Q_ACT_BLOCK;
+        uint8_t* mine = aring + warp * R_ADEPTH * R_GPW * R_ASTAGE;
+        auto pull = [&](int s) {  // lane 0
+            const int sl = s % R_ADEPTH;
+            mbar_expect_tx(&afull[warp * R_ADEPTH + sl], ngw * blocks_of(s) * Q_ACT_BLOCK);
+            for (int gi = 0; gi < ngw; gi++)
+                bulk_g2s(mine + (sl * R_GPW + gi) * R_ASTAGE, asrc + ((int64_t)gi * p.nb + (int64_t)s * Q_STAGE_BLOCKS) * Q_ACT_BLOCK,
+                         blocks_of(s) * Q_ACT_BLOCK, &afull[warp * R_ADEPTH + sl]);
+        };
+        grid_dependency_wait();  // the activation quantiser has finished
+        if (lane == 0)
+            for (int d = 0; d < R_ADEPTH && d < n_stages; d++) pull(d);
+        float4 acc[R_GPW];  // per group: (row r, act 2c), (r, 2c + 1), (r + 8, 2c), (r + 8, 2c + 1)
+#pragma unroll
+        for (int gi = 0; gi < R_GPW; gi++) acc[gi] = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int s = 0; s < n_stages; s++) {
+            const int nblk = (int)blocks_of(s), wsl = s % R_WDEPTH, asl = s % R_ADEPTH;
+            q40_wait(&wfull[wsl], (uint32_t)((s / R_WDEPTH) & 1), fail_s);
+            const uint8_t* st = ring + wsl * Q_STAGE_BYTES;
+            uint32_t af[Q_STAGE_BLOCKS][4];
+            float wsA[Q_STAGE_BLOCKS], wsB[Q_STAGE_BLOCKS];
+#pragma unroll
+            for (int j = 0; j < Q_STAGE_BLOCKS; j++) {
+                const uint8_t* wb = st + j * Q_BLOCK_BYTES;
+                const uint32_t wa = *(const uint32_t*)(wb + r * 16 + 4 * c), wc = *(const uint32_t*)(wb + (r + 8) * 16 + 4 * c);
+                af[j][0] = wa & 0x0f0f0f0fu, af[j][1] = wc & 0x0f0f0f0fu, af[j][2] = (wa >> 4) & 0x0f0f0f0fu, af[j][3] = (wc >> 4) & 0x0f0f0f0fu;
+                wsA[j] = __half2float(*(const __half*)(wb + 256 + 2 * r)), wsB[j] = __half2float(*(const __half*)(wb + 256 + 2 * (r + 8)));
+            }
+            __syncwarp();
+            if (lane == 0) q40_arrive(&wempty[wsl]);  // the weights of the stage are in registers
+            q40_wait(&afull[warp * R_ADEPTH + asl], (uint32_t)((s / R_ADEPTH) & 1), fail_s);
+#pragma unroll
+            for (int gi = 0; gi < R_GPW; gi++) {
+                if (gi < ngw) {  // warp-uniform
+                    const uint8_t* as = mine + (asl * R_GPW + gi) * R_ASTAGE;
+#pragma unroll
+                    for (int j = 0; j < Q_STAGE_BLOCKS; j++) {
+                        const uint8_t* ab = as + j * Q_ACT_BLOCK;
+                        const uint32_t b0 = *(const uint32_t*)(ab + r * 16 + 4 * c), b1 = *(const uint32_t*)(ab + 128 + r * 16 + 4 * c);
+                        const float2 asc = *((const float2*)(ab + 256) + c);
+                        const int2 asum = *((const int2*)(ab + 288) + c);
+                        int d[4] = {0, 0, 0, 0};
+                        mma_u8s8(d, af[j], b0, b1);
+                        if (j < nblk) {  // the blocks of a short last stage hold stale bytes: leave them out
+                            acc[gi].x = __fadd_rn(acc[gi].x, __fmul_rn(__fmul_rn((float)(d[0] - 8 * asum.x), wsA[j]), asc.x));
+                            acc[gi].y = __fadd_rn(acc[gi].y, __fmul_rn(__fmul_rn((float)(d[1] - 8 * asum.y), wsA[j]), asc.y));
+                            acc[gi].z = __fadd_rn(acc[gi].z, __fmul_rn(__fmul_rn((float)(d[2] - 8 * asum.x), wsB[j]), asc.x));
+                            acc[gi].w = __fadd_rn(acc[gi].w, __fmul_rn(__fmul_rn((float)(d[3] - 8 * asum.y), wsB[j]), asc.y));
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0 && s + R_ADEPTH < n_stages) pull(s + R_ADEPTH);  // every lane has read the stage: refill its slot
+        }
+#pragma unroll
+        for (int gi = 0; gi < R_GPW; gi++) {
+            if (gi >= ngw) break;
+            float4 a = acc[gi];
+            if (*fail_s) a = make_float4(__int_as_float(0x7fc00000), __int_as_float(0x7fc00000), __int_as_float(0x7fc00000), __int_as_float(0x7fc00000));
+            const int64_t row = tile * Q_TILE_ROWS + r, m0 = (gw + gi) * 8 + 2 * c;
+            if (row < p.n) {
+                if (m0 < p.m) st_from_f32(p.out, p.out_dtype, m0 * p.out_stride + row, a.x);
+                if (m0 + 1 < p.m) st_from_f32(p.out, p.out_dtype, (m0 + 1) * p.out_stride + row, a.y);
+            }
+            if (row + 8 < p.n) {
+                if (m0 < p.m) st_from_f32(p.out, p.out_dtype, m0 * p.out_stride + row + 8, a.z);
+                if (m0 + 1 < p.m) st_from_f32(p.out, p.out_dtype, (m0 + 1) * p.out_stride + row + 8, a.w);
+            }
+        }
+    }
+    __syncthreads();
+    if (*fail_s) {
+        if (tid == 0) atomicOr(p.status, STATUS_WAIT_EXPIRED);
+        __nanosleep(200000);  // copies that may still be in flight land before the CTA's memory is released
+    }
+}
+
 }  // namespace b200kv
 
 using namespace b200kv;
@@ -400,6 +523,18 @@ extern "C" int b200kv_q40_gemm_quantized_as(const void* packed, int64_t n, int64
     Q40Gemm p{};
     p.packed = (const uint8_t*)packed, p.act = act, p.out = out, p.status = (int*)scratch;
     p.n = n, p.nb = nb, p.out_stride = out_stride, p.m = m, p.out_dtype = out_dtype;
+    if (groups >= 4) {  // a prompt pass: every warp keeps the accumulators of its own 8 rows, the weight stages are shared by 8 warps
+        static thread_local int rows_attr_device = -1;
+        int dev = 0;
+        B200KV_CUDA(cudaGetDevice(&dev));
+        if (rows_attr_device != dev) {
+            B200KV_CUDA(cudaFuncSetAttribute(q40_gemm_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)R_SMEM));
+            rows_attr_device = dev;
+        }
+        dim3 rgrid((unsigned)((n + Q_TILE_ROWS - 1) / Q_TILE_ROWS), (unsigned)((groups + R_WARPS * R_GPW - 1) / (R_WARPS * R_GPW)));
+        B200KV_CUDA(launch_after_predecessor(q40_gemm_rows_kernel, rgrid, dim3((R_WARPS + 1) * 32), R_SMEM, stream, p));
+        return B200KV_OK;
+    }
     // warps per tile: enough stages per warp (>= 4) that the start-up of a CTA is amortised
     const int64_t n_stages = (nb + Q_STAGE_BLOCKS - 1) / Q_STAGE_BLOCKS;
     // A matrix of few tiles (at most two CTAs of 8 warps per SM, all resident at once) leaves the GPU short of warps: 8 warps
