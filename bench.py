@@ -440,6 +440,8 @@ LINEAR = {
     "q40-ffn-down": dict(n=4096, k=14336, m=8, layers=8, desc="FFN down projection [4096 x 14336], Q4_0, 8 activation rows"),
     "q40-attn-proj": dict(n=4096, k=4096, m=8, layers=32, desc="attention q / o projection [4096 x 4096], Q4_0, 8 activation rows"),
     "q40-gemv": dict(n=14336, k=4096, m=1, layers=8, desc="FFN gate/up projection, one activation row (GEMV)"),
+    # a prompt pass: 512 activation rows through the same matrix (the many-rows kernel; bound by the per-block f32 scaling, not by HBM)
+    "q40-ffn-up-m512": dict(n=14336, k=4096, m=512, layers=2, desc="FFN gate/up projection [14336 x 4096], Q4_0, 512 activation rows (prompt pass)"),
 }
 
 
@@ -550,7 +552,7 @@ def run_linear(args, rank, world):
             "e2e": {"value": world * weight_bytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": m * k * 4,
                     "d2h_bytes_per_step": m * n * 4, "ms_per_step": ms_e2e},
             "gpu_launches": 2 * layers,
-            "roofline": {"bound": "hbm", "kernel": "q40_gemm_kernel (+ activation quantiser)", "achieved": achieved, "peak": pk["hbm_gbs"],
+            "roofline": {"bound": "hbm", "kernel": ("q40_gemm_rows_kernel" if m > 24 else "q40_gemm_kernel") + " (+ activation quantiser)", "achieved": achieved, "peak": pk["hbm_gbs"],
                          "unit": "GB/s", "frac": achieved / pk["hbm_gbs"], "peak_kind": pk_kind, "traffic": None,
                          "algorithmic_bytes": weight_bytes},
             "clocks": clocks,

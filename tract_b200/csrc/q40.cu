@@ -14,6 +14,8 @@
 // of one mma.sync.m16n8k32 (u8 nibbles x s8 activations -> s32: 16 rows x 8 activation rows of exact dot products;
 // the -8 of the nibbles is removed with the block's activation sum), and adds the 8 contributions to the 16 x 8 f32
 // accumulators, which travel from warp to warp in stage order -- the order the reference adds the blocks in.
+#include <type_traits>
+
 #include "glue_math.cuh"
 #include "internal.h"
 #include "q40_common.cuh"
@@ -381,27 +383,33 @@ __global__ void __launch_bounds__((R_WARPS + 1) * 32, 2) q40_gemm_rows_kernel(Q4
             __syncwarp();
             if (lane == 0) q40_arrive(&wempty[wsl]);  // the weights of the stage are in registers
             q40_wait(&afull[warp * R_ADEPTH + asl], (uint32_t)((s / R_ADEPTH) & 1), fail_s);
+            // a full stage (all but, at most, the last) runs without the per-block test; a short one leaves its stale blocks out
+            auto contract = [&](auto full_stage) {
+                constexpr bool FULL = decltype(full_stage)::value;
 #pragma unroll
-            for (int gi = 0; gi < R_GPW; gi++) {
-                if (gi < ngw) {  // warp-uniform
-                    const uint8_t* as = mine + (asl * R_GPW + gi) * R_ASTAGE;
+                for (int gi = 0; gi < R_GPW; gi++) {
+                    if (gi < ngw) {  // warp-uniform
+                        const uint8_t* as = mine + (asl * R_GPW + gi) * R_ASTAGE;
 #pragma unroll
-                    for (int j = 0; j < Q_STAGE_BLOCKS; j++) {
-                        const uint8_t* ab = as + j * Q_ACT_BLOCK;
-                        const uint32_t b0 = *(const uint32_t*)(ab + r * 16 + 4 * c), b1 = *(const uint32_t*)(ab + 128 + r * 16 + 4 * c);
-                        const float2 asc = *((const float2*)(ab + 256) + c);
-                        const int2 asum = *((const int2*)(ab + 288) + c);
-                        int d[4] = {0, 0, 0, 0};
-                        mma_u8s8(d, af[j], b0, b1);
-                        if (j < nblk) {  // the blocks of a short last stage hold stale bytes: leave them out
-                            acc[gi].x = __fadd_rn(acc[gi].x, __fmul_rn(__fmul_rn((float)(d[0] - 8 * asum.x), wsA[j]), asc.x));
-                            acc[gi].y = __fadd_rn(acc[gi].y, __fmul_rn(__fmul_rn((float)(d[1] - 8 * asum.y), wsA[j]), asc.y));
-                            acc[gi].z = __fadd_rn(acc[gi].z, __fmul_rn(__fmul_rn((float)(d[2] - 8 * asum.x), wsB[j]), asc.x));
-                            acc[gi].w = __fadd_rn(acc[gi].w, __fmul_rn(__fmul_rn((float)(d[3] - 8 * asum.y), wsB[j]), asc.y));
+                        for (int j = 0; j < Q_STAGE_BLOCKS; j++) {
+                            const uint8_t* ab = as + j * Q_ACT_BLOCK;
+                            const uint32_t b0 = *(const uint32_t*)(ab + r * 16 + 4 * c), b1 = *(const uint32_t*)(ab + 128 + r * 16 + 4 * c);
+                            const float2 asc = *((const float2*)(ab + 256) + c);
+                            const int2 asum = *((const int2*)(ab + 288) + c);
+                            int d[4] = {0, 0, 0, 0};
+                            mma_u8s8(d, af[j], b0, b1);
+                            if (FULL || j < nblk) {
+                                acc[gi].x = __fadd_rn(acc[gi].x, __fmul_rn(__fmul_rn((float)(d[0] - 8 * asum.x), wsA[j]), asc.x));
+                                acc[gi].y = __fadd_rn(acc[gi].y, __fmul_rn(__fmul_rn((float)(d[1] - 8 * asum.y), wsA[j]), asc.y));
+                                acc[gi].z = __fadd_rn(acc[gi].z, __fmul_rn(__fmul_rn((float)(d[2] - 8 * asum.x), wsB[j]), asc.x));
+                                acc[gi].w = __fadd_rn(acc[gi].w, __fmul_rn(__fmul_rn((float)(d[3] - 8 * asum.y), wsB[j]), asc.y));
+                            }
                         }
                     }
                 }
-            }
+            };
+            if (nblk == Q_STAGE_BLOCKS) contract(std::true_type{});
+            else contract(std::false_type{});
             __syncwarp();
             if (lane == 0 && s + R_ADEPTH < n_stages) pull(s + R_ADEPTH);  // every lane has read the stage: refill its slot
         }
