@@ -63,7 +63,8 @@ typedef struct {
     int64_t pool_tokens;    /* capacity of the page pool in tokens, summed over sequences */
     int32_t flags;          /* bit 0: a lone (has_values == 0) KIVI cache quantises per token (the Value layout of
                                QuantizedDynKeyValueCache, per_channel = false) instead of per channel */
-    int32_t reserved;       /* 0 */
+    int32_t max_q_heads;    /* most query heads an attention call on this cache will bring (sizes the split-KV workspace,
+                               which is allocated once, here); 0 selects 8 * n_kv_heads */
 } b200kv_config;
 
 /* Thread-local message of the last failed call on this thread (tract_get_last_error analogue). */
@@ -78,6 +79,14 @@ const char* b200kv_version(void);
  * GpuDynKVCacheState::eval (gpu/src/ops/dyn_kv_cache.rs:88-108). */
 int b200kv_create(const b200kv_config* cfg, b200kv_cache** out);
 int b200kv_destroy(b200kv_cache* cache);
+
+/* Bytes of the split-KV workspace b200kv_create allocates for this configuration, beside the page pool: the partial
+ * outputs of decode attention (one (head_dim + 2)-float record per page run, kv head and query head of the group).  It is
+ * sized once from max_seqs and max_q_heads (the reference takes such buffers from the session arena,
+ * gpu/src/session_handler.rs:35-46); no call made after b200kv_create allocates or frees device memory: a decode call
+ * whose natural split would need more records than the workspace holds cuts its sequences into fewer, longer runs
+ * instead.  Returns -1 for a configuration b200kv_create would refuse. */
+int64_t b200kv_workspace_bytes(const b200kv_config* cfg);
 
 /* A sequence is one independent state (one tract `State`); ids are small integers reused after free. */
 int b200kv_seq_new(b200kv_cache* cache, int32_t* seq_out);
@@ -271,7 +280,7 @@ int b200kv_q40_add_rms_norm_quantize(const float* x, int64_t x_stride, const flo
  * dependency: they read activations, residuals and scratch only after that kernel has finished, but the packed weights
  * and the norm `weight` vector are fetched earlier.  Those two are constants of the model: they must be complete before
  * the kernel that precedes the call was enqueued (b200kv_q40_pack takes care of this for the matrix it packs). */
-/* Synchronises `stream` and reports whether a bounded wait of the last GEMM that used `scratch` expired. */
+/* Synchronises `stream` and reports (once) whether a bounded wait of any GEMM that used `scratch` since the last check expired. */
 int b200kv_q40_check(const void* scratch, void* stream);
 
 /* ---- decoder glue between the linear layers and the attention ----
@@ -305,7 +314,10 @@ int b200kv_cast(const void* src, int64_t src_stride, int32_t src_dtype, void* ds
  * `enable` is a bit set: bit 0 turns the timing on; bit 1 (a test hook) routes decode attention through the
  * CUDA-core kernel even where the tensor-core kernel applies (KIVI caches: through export + the generic kernel), so
  * the two can be checked against each other; bit 2 (a test hook) keeps KIVI decode attention on its CUDA-core
- * kernel alone. */
+ * kernel alone; bit 3 (a test hook, consumed by the next decode launch of a non-KIVI cache) exercises the give-up path of
+ * the bounded waits without any fault: one CTA of that launch issues no copies, its first wait runs out after 1 ms, it
+ * sets the status word, publishes an empty partial and returns -- b200kv_check then reports the expired wait, the
+ * output of that call is not meaningful, and the cache is usable as before. */
 int b200kv_profile(b200kv_cache* cache, int32_t enable);
 int b200kv_profile_read(b200kv_cache* cache, int32_t max_records, int32_t* kernel_ids, float* ms, int32_t* n_out);
 

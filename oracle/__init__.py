@@ -56,6 +56,7 @@ def lib():
         L.orc_kivi_new.argtypes = [ip, ip, ip]
         L.orc_kivi_free.argtypes = [C.c_void_p]
         L.orc_kivi_push.argtypes = [C.c_void_p, fp]
+        L.orc_kivi_push_rows.argtypes = [C.c_void_p, fp, C.c_int64, ip]
         L.orc_kivi_len.restype = C.c_int64
         L.orc_kivi_len.argtypes = [C.c_void_p]
         L.orc_kivi_counts.argtypes = [C.c_void_p] + [C.POINTER(C.c_int64)] * 3
@@ -221,9 +222,8 @@ class KiviStore:
             self._h = None
 
     def push(self, rows: np.ndarray):
-        rows = to_f32(rows).reshape(-1, self.d)
-        for r in rows:
-            lib().orc_kivi_push(self._h, _p(np.ascontiguousarray(r), C.c_float))
+        rows = np.ascontiguousarray(to_f32(rows).reshape(-1, self.d))
+        lib().orc_kivi_push_rows(self._h, _p(rows, C.c_float), rows.shape[0], self.d)
 
     def __len__(self):
         return int(lib().orc_kivi_len(self._h))

@@ -428,6 +428,11 @@ void orc_kivi_push(void* p, const float* row) {
         s->n_tokens_q++;
     }
 }
+// n rows of d values, pushed one after the other (the reference ingests token by token, quant_dyn_kv_cache.rs:462-472)
+void orc_kivi_push_rows(void* p, const float* rows, int64_t n, int d) {
+    for (int64_t i = 0; i < n; i++) orc_kivi_push(p, rows + i * d);
+}
+
 int64_t orc_kivi_len(void* p) {
     OrcKivi* s = (OrcKivi*)p;
     int ns = (int)(s->sink.size() / s->d);

@@ -101,6 +101,57 @@ def test_config4_quantised_long_context_decode(kv, fmt):
     cache.close(), twice.close()
 
 
+@pytest.mark.parametrize("fmt,bits", [("kivi8", 8), ("kivi4", 4)])
+def test_config4_kivi_long_context_decode(kv, fmt, bits):
+    # config 4 with tract's own storage quantisation (QuantizedDynKeyValueCache, quant_dyn_kv_cache.rs:98-250): 16
+    # sequences of 32768 tokens, then the decode step.  Whole (sequence, kv head) slices against the oracle's stores
+    # (codes, lo, scale, sinks, residual bit for bit) and against flash attention over the oracle's dequantised cache.
+    B, P = 16, 32768
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(44)
+    cache = kv.KvCache(fmt, HKV, D, max_seqs=B, max_seq_tokens=P + 128)
+    seqs = [cache.new_seq() for _ in range(B)]
+    checked = [(0, 0), (9, 5), (15, 7)]
+    kept = {c: ([], []) for c in checked}
+    for t0 in range(0, P, 4096):
+        k, v = outlier_normal(gen, (B, HKV, 4096, D), torch.float16), outlier_normal(gen, (B, HKV, 4096, D), torch.float16)
+        cache.append(seqs, k, v)
+        for (b, h) in checked:
+            kept[(b, h)][0].append(k[b, h].cpu().numpy()), kept[(b, h)][1].append(v[b, h].cpu().numpy())
+    k1, v1 = outlier_normal(gen, (B, HKV, 1, D), torch.float16), outlier_normal(gen, (B, HKV, 1, D), torch.float16)
+    q = torch.randn((B, HQ, 1, D), generator=gen, device="cuda").half()
+    cache.append(seqs, k1, v1)
+    out = cache.attend(seqs, q, causal=True)
+    cache.check()
+    assert all(cache.seq_len(s) == P + 1 for s in seqs)
+    G = HQ // HKV
+    raws = {}
+    for (b, h) in checked:
+        deq = []
+        for which, per_channel in ((0, True), (1, False)):
+            X = np.concatenate(kept[(b, h)][which] + [(k1 if which == 0 else v1)[b, h].cpu().numpy()])
+            st = oracle.KiviStore(per_channel, D, bits)
+            st.push(X)
+            want = st.raw()
+            if (b, which) not in raws:
+                raws[(b, which)] = {key: val.cpu().numpy() for key, val in cache.export_kivi(seqs[b], which, per_channel).items()}
+            raw = raws[(b, which)]
+            assert np.array_equal(raw["sink"][h], want["sink"])
+            assert np.array_equal(raw["codes"][h], want["codes"]), (b, h, which)
+            assert np.array_equal(raw["lo"][h].reshape(-1), want["lo"]) and np.array_equal(raw["scale"][h].reshape(-1), want["scale"])
+            if per_channel:
+                assert np.array_equal(raw["residual"][h], want["residual"])
+            deq.append(st.dequant())
+        want = oracle.flash_sdpa(q[b:b + 1, h * G:(h + 1) * G].cpu().numpy(), deq[0][None, None], deq[1][None, None], causal=True, threads=8)
+        got = out[b:b + 1, h * G:(h + 1) * G].float().cpu().numpy()
+        assert rel_err(got, want.astype(np.float32)) <= TOL["f16"], (b, h)
+    # a sequence alone is split differently from the same sequence inside the batch of 16
+    alone = cache.attend([seqs[5]], q[5:6], causal=True)
+    assert rel_err(alone.float().cpu().numpy(), out[5:6].float().cpu().numpy()) <= 1e-3
+    cache.check()
+    cache.close()
+
+
 def test_config3_ragged_batched_decode_bf16(kv):
     B = 256
     lens = [int(x) for x in np.random.Generator(np.random.Philox(key=3)).integers(512, 16385, size=B)]

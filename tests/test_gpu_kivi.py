@@ -134,7 +134,7 @@ def test_kivi_decode_kernel_ragged_batch(kv, fmt, bits, D, Hq, Hkv):
         Ks.append(k), Vs.append(v)
     q = normal(9, (len(lens), Hq, 1, D)).astype(np.float16)
     out = cache.attend(seqs, torch.from_numpy(q).cuda(), causal=True)
-    cache.profile(False, force_simt=True)  # the same through export + the generic kernel
+    cache.profile(False, force_simt=True)  # the same through the generic kernel, which dequantises element by element
     out_gen = cache.attend(seqs, torch.from_numpy(q).cuda(), causal=True)
     cache.profile(False)
     cache.check()
@@ -148,6 +148,27 @@ def test_kivi_decode_kernel_ragged_batch(kv, fmt, bits, D, Hq, Hkv):
         vd = np.stack([_deq(False, D, bits, Vs[b][0, h]) for h in range(Hkv)])[None]
         want = oracle.flash_sdpa(q[b:b + 1], kd, vd, causal=True)
         assert rel_err(out[b:b + 1].float().cpu().numpy(), want.astype(np.float32)) <= TOL["f16"], b
+    cache.close()
+
+
+@pytest.mark.parametrize("fmt,bits", [("kivi8", 8), ("kivi4", 4)])
+def test_kivi_one_long_sequence_uses_every_split_the_combine_pass_has(kv, fmt, bits):
+    # one sequence, 4 kv heads, more than 16.4k tokens: the split picker of the tensor-core kernel wants the most splits
+    # it may take, and the partial of the sinks / residual block comes on top; together they must fit the 64 slots of
+    # the combine pass
+    Hq, Hkv, D, n = 16, 4, 128, 17500
+    cache = kv.KvCache(fmt, Hkv, D, max_seqs=1, max_seq_tokens=n + 64)
+    sq = cache.new_seq()
+    k, v = normal_with_outliers(31, (1, Hkv, n, D)).astype(np.float16), normal_with_outliers(32, (1, Hkv, n, D)).astype(np.float16)
+    for t0 in range(0, n, 4096):
+        cache.append([sq], torch.from_numpy(k[:, :, t0:t0 + 4096]).cuda(), torch.from_numpy(v[:, :, t0:t0 + 4096]).cuda())
+    q = normal(33, (1, Hq, 1, D)).astype(np.float16)
+    out = cache.attend([sq], torch.from_numpy(q).cuda(), causal=True)
+    cache.check()
+    kd = np.stack([_deq(True, D, bits, k[0, h]) for h in range(Hkv)])[None]
+    vd = np.stack([_deq(False, D, bits, v[0, h]) for h in range(Hkv)])[None]
+    want = oracle.flash_sdpa(q, kd, vd, causal=True, threads=8)
+    assert rel_err(out.float().cpu().numpy(), want.astype(np.float32)) <= TOL["f16"]
     cache.close()
 
 

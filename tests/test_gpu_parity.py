@@ -47,6 +47,26 @@ def attn_err(out, io, q, k, v, **kw):
     return rel_err(to_np(out, io).astype(np.float32), want.astype(np.float32))
 
 
+LAYOUTS = ["plain", "window", "offset"]
+
+
+def as_layout(t, layout):
+    """The values of t ([B, H, S, D]) in a tensor laid out three ways, as the reference's test runtime runs every case
+    (test-rt/test-cuda/src/lib.rs:218-220): as they are; as a window of a wider buffer (every stride but the innermost
+    differs from the dense one); or dense but starting one element past a 16-byte boundary (a 2- or 4-byte aligned base)."""
+    if layout == "plain":
+        return t
+    B, H, S, D = t.shape
+    if layout == "window":
+        buf = torch.full((B + 1, H + 2, S + 1, D), 7.0, dtype=t.dtype, device=t.device)
+        w = buf[1:, 1:H + 1, 1:]
+    else:
+        flat = torch.full((t.numel() + 8,), 7.0, dtype=t.dtype, device=t.device)
+        w = flat[1:1 + t.numel()].view(B, H, S, D)
+    w.copy_(t)
+    return w
+
+
 def to_np(t, name):
     t = t.detach().cpu().contiguous()
     if name == "bf16":
@@ -190,8 +210,9 @@ DECODE_CASES = [
 ]
 
 
+@pytest.mark.parametrize("layout", LAYOUTS)
 @pytest.mark.parametrize("fmt,io,B,Hq,Hkv,D,lens", DECODE_CASES)
-def test_decode_matches_oracle(kv, fmt, io, B, Hq, Hkv, D, lens):
+def test_decode_matches_oracle(kv, fmt, io, B, Hq, Hkv, D, lens, layout):
     cache = kv.KvCache(fmt, Hkv, D, max_seqs=B, max_seq_tokens=max(lens) + 64)
     seqs = [cache.new_seq() for _ in range(B)]
     Ks, Vs = [], []
@@ -205,8 +226,9 @@ def test_decode_matches_oracle(kv, fmt, io, B, Hq, Hkv, D, lens):
     k_new = np.concatenate([k[:, :, -1:] for k in Ks], 0)
     v_new = np.concatenate([v[:, :, -1:] for v in Vs], 0)
     q = normal(7, (B, Hq, 1, D)).astype(np_dtype(io))
-    cache.append(seqs, to_dev(k_new), to_dev(v_new))
-    out = cache.attend(seqs, to_dev(q), causal=True)
+    cache.append(seqs, as_layout(to_dev(k_new), layout), as_layout(to_dev(v_new), layout))
+    dq = as_layout(to_dev(q), layout)
+    out = cache.attend(seqs, dq, causal=True, out=as_layout(torch.zeros_like(to_dev(q)), layout))
     cache.check()
     for b in range(B):
         kc, vc = oracle_cache_view(fmt, Ks[b], io), oracle_cache_view(fmt, Vs[b], io)
@@ -285,8 +307,18 @@ def test_decode_explicit_scale_and_reuse_after_truncate(kv):
     # enough query tiles for the double-tile CTAs (two 128-row tiles share each staged K/V chunk)
     ("f16", "f16", 32, 8, 128, 100, 1200),  # 1200 = 18 double tiles + 48 queries: the last CTA's second tile is half dead
     ("bf16", "bf16", 32, 8, 128, 37, 1250),
+    # quantised and head_dim 64 pages on the tensor-core kernel (operand tiles rebuilt in shared memory)
+    ("q8_1", "f16", 32, 8, 128, 1000, 300),
+    ("q4_0", "f16", 8, 2, 128, 130, 70),
+    ("q8_1", "bf16", 8, 2, 128, 64, 200),
+    ("q4_0", "bf16", 32, 8, 128, 37, 600),
+    ("f16", "f16", 32, 8, 64, 100, 300),
+    ("bf16", "bf16", 8, 2, 64, 5, 130),
+    ("q8_1", "f16", 8, 2, 64, 70, 100),
+    ("q8_1", "f32", 4, 2, 128, 70, 33),     # f32 queries: the generic kernel reading the pages in place
 ])
-def test_prefill_matches_oracle(kv, fmt, io, Hq, Hkv, D, P, S):
+@pytest.mark.parametrize("layout", LAYOUTS)
+def test_prefill_matches_oracle(kv, fmt, io, Hq, Hkv, D, P, S, layout):
     scale = 0.5 if io != "f32" else 1.0
     cache = kv.KvCache(fmt, Hkv, D, max_seqs=1, max_seq_tokens=P + S + 64)
     sq = cache.new_seq()
@@ -295,8 +327,8 @@ def test_prefill_matches_oracle(kv, fmt, io, Hq, Hkv, D, P, S):
     q = normal(3, (1, Hq, S, D), scale=scale).astype(np_dtype(io))
     if P:
         cache.append([sq], to_dev(k[:, :, :P]), to_dev(v[:, :, :P]))
-    cache.append([sq], to_dev(k[:, :, P:]), to_dev(v[:, :, P:]))
-    out = cache.attend([sq], to_dev(q), causal=True)
+    cache.append([sq], as_layout(to_dev(k[:, :, P:]), layout), as_layout(to_dev(v[:, :, P:]), layout))
+    out = cache.attend([sq], as_layout(to_dev(q), layout), causal=True, out=as_layout(torch.zeros_like(to_dev(q)), layout))
     cache.check()
     err = attn_err(out, io, q, oracle_cache_view(fmt, k, io), oracle_cache_view(fmt, v, io), causal=True, threads=8)
     assert err <= TOL[io], err

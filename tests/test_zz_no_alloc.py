@@ -53,3 +53,64 @@ def test_static_scratch_decode_matches_regular_decode_twice():
     big.check()
     big.close()
     cache.close()
+
+
+@pytest.mark.parametrize("fmt,io,D,Hq,Hkv", [("q8_1", "f32", 128, 8, 2), ("f16", "f16", 64, 6, 2), ("f32", "f32", 128, 4, 4)])
+def test_static_scratch_decode_on_the_cuda_core_kernel(fmt, io, D, Hq, Hkv):
+    # f32 queries and head_dim 64 are served by the CUDA-core decode kernel; through this entry point its partials go to
+    # the fixed array as well.  Two calls in a row, against the regular entry point.
+    import tract_b200 as kv
+
+    dt = np.float32 if io == "f32" else np.float16
+    lens = [900, 70, 300]
+    cache = kv.KvCache(fmt, Hkv, D, max_seqs=len(lens), max_seq_tokens=1024)
+    seqs = [cache.new_seq() for _ in lens]
+    for b, n in enumerate(lens):
+        cache.append([seqs[b]], torch.from_numpy(normal(150 + b, (1, Hkv, n, D)).astype(dt)).cuda(),
+                     torch.from_numpy(normal(160 + b, (1, Hkv, n, D)).astype(dt)).cuda())
+    for call in range(2):
+        q = torch.from_numpy(normal(170 + call, (len(lens), Hq, 1, D)).astype(dt)).cuda()
+        want = cache.attend(seqs, q, causal=True)
+        got = torch.full_like(want, float("nan"))
+        cache.attend_static_scratch(seqs, q, out=got)
+        cache.check()
+        assert rel_err(got.float().cpu().numpy(), want.float().cpu().numpy()) <= TOL[io], call
+        if call == 0:
+            cache.truncate(seqs[0], 200)
+    cache.close()
+
+
+def test_static_scratch_refusals_enqueue_nothing():
+    # What this entry point does not serve is refused during validation, before a descriptor slot is taken or anything is
+    # enqueued: the output buffer still holds what it held, and the next regular call works.
+    import tract_b200 as kv
+
+    Hq, Hkv, D = 8, 2, 128
+    sentinel = 3.25
+
+    def refused(cache, seqs, pattern):
+        q = torch.zeros((len(seqs), Hq, 1, D), dtype=torch.float16, device="cuda")
+        out = torch.full_like(q, sentinel)
+        with pytest.raises(kv.B200KvError, match=pattern):
+            cache.attend_static_scratch(seqs, q, out=out)
+        torch.cuda.synchronize()
+        assert bool((out == sentinel).all())
+        cache.attend(seqs, q, causal=True, out=out)  # the regular entry point serves the same call
+        cache.check()
+        assert torch.isfinite(out.float()).all() and not bool((out == sentinel).any())
+
+    # a KIVI cache has decode kernels of its own
+    kivi = kv.KvCache("kivi8", Hkv, D, max_seqs=1, max_seq_tokens=256)
+    s = kivi.new_seq()
+    x = torch.randn((1, Hkv, 100, D), device="cuda").half()
+    kivi.append([s], x, x)
+    refused(kivi, [s], "KIVI")
+    kivi.close()
+    # a sequence whose front pages were given back (sliding window)
+    cache = kv.KvCache("f16", Hkv, D, max_seqs=1, max_seq_tokens=512)
+    s = cache.new_seq()
+    x = torch.randn((1, Hkv, 300, D), device="cuda").half()
+    cache.append([s], x, x)
+    cache.trim(s, 100)
+    refused(cache, [s], "trimmed")
+    cache.close()

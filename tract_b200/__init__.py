@@ -27,7 +27,7 @@ EXPORTS = [
     "b200kv_q40_packed_bytes", "b200kv_q40_pack", "b200kv_q40_scratch_bytes", "b200kv_q40_gemm", "b200kv_q40_check",
     "b200kv_rms_norm", "b200kv_silu_mul", "b200kv_add", "b200kv_argmax", "b200kv_gather_rows", "b200kv_cast",
     "b200kv_attend_window", "b200kv_trim", "b200kv_attend_rope", "b200kv_attend_q40", "b200kv_append_attend", "b200kv_q40_quantize", "b200kv_q40_gemm_quantized", "b200kv_q40_gemm_quantized_as",
-    "b200kv_q40_silu_mul_quantize", "b200kv_q40_add_rms_norm_quantize",
+    "b200kv_q40_silu_mul_quantize", "b200kv_q40_add_rms_norm_quantize", "b200kv_workspace_bytes",
 ]
 KERNEL_NAMES = {0: "table_scatter", 1: "append", 2: "decode", 3: "combine", 4: "export", 5: "sdpa_dense", 6: "prefill"}
 
@@ -39,7 +39,7 @@ class B200KvError(RuntimeError):
 class Config(C.Structure):
     _fields_ = [("device", C.c_int32), ("format", C.c_int32), ("n_kv_heads", C.c_int32), ("head_dim", C.c_int32),
                 ("has_values", C.c_int32), ("max_seqs", C.c_int32), ("max_seq_tokens", C.c_int64),
-                ("pool_tokens", C.c_int64), ("flags", C.c_int32), ("reserved", C.c_int32)]
+                ("pool_tokens", C.c_int64), ("flags", C.c_int32), ("max_q_heads", C.c_int32)]
 
 
 _lib = None
@@ -57,6 +57,8 @@ def lib():
         L.b200kv_version.restype = C.c_char_p
         L.b200kv_create.argtypes = [C.POINTER(Config), C.POINTER(vp)]
         L.b200kv_destroy.argtypes = [vp]
+        L.b200kv_workspace_bytes.argtypes = [C.POINTER(Config)]
+        L.b200kv_workspace_bytes.restype = i64
         L.b200kv_seq_new.argtypes = [vp, i32p]
         L.b200kv_seq_free.argtypes = [vp, i32]
         L.b200kv_seq_len.argtypes = [vp, i32]
@@ -124,7 +126,7 @@ class KvCache:
     """One layer's paged K (and V) store for up to ``max_seqs`` independent sequences."""
 
     def __init__(self, fmt, n_kv_heads, head_dim, max_seqs, max_seq_tokens, pool_tokens=None, has_values=True,
-                 device=None, per_token=False):
+                 device=None, per_token=False, max_q_heads=0):
         import torch
 
         if not torch.cuda.is_available():
@@ -133,7 +135,8 @@ class KvCache:
         self.fmt = FORMATS[fmt] if isinstance(fmt, str) else int(fmt)
         self.n_kv_heads, self.head_dim, self.has_values = n_kv_heads, head_dim, bool(has_values)
         cfg = Config(self.device, self.fmt, n_kv_heads, head_dim, int(has_values), max_seqs, max_seq_tokens,
-                     pool_tokens if pool_tokens is not None else max_seqs * max_seq_tokens, int(bool(per_token)), 0)
+                     pool_tokens if pool_tokens is not None else max_seqs * max_seq_tokens, int(bool(per_token)), int(max_q_heads))
+        self.workspace_bytes = int(lib().b200kv_workspace_bytes(C.byref(cfg)))  # what create allocates beside the pages, once
         h = C.c_void_p()
         _ck(lib().b200kv_create(C.byref(cfg), C.byref(h)))
         self._h = h
@@ -322,8 +325,11 @@ class KvCache:
     def check(self):
         _ck(lib().b200kv_check(self._h, _stream()))
 
-    def profile(self, enable=True, force_simt=False, kivi_cuda_core=False):
-        _ck(lib().b200kv_profile(self._h, int(bool(enable)) | (2 if force_simt else 0) | (4 if kivi_cuda_core else 0)))
+    def profile(self, enable=True, force_simt=False, kivi_cuda_core=False, stall_next_decode=False):
+        """Timing records on / off and the test hooks of b200kv_profile (stall_next_decode: one CTA of the next decode
+        launch gives up on a copy nobody issued, after 1 ms)."""
+        _ck(lib().b200kv_profile(self._h, int(bool(enable)) | (2 if force_simt else 0) | (4 if kivi_cuda_core else 0) |
+                                 (8 if stall_next_decode else 0)))
 
     def profile_read(self, max_records=65536):
         """[(kernel name, milliseconds)] of the launches recorded since the last read."""

@@ -36,29 +36,13 @@ extern "C" int b200kv_attend(b200kv_cache* c, int32_t n_seqs, const int32_t* seq
     if (!kivi && !c->force_simt && prefill_tc_supported(c, n_q_heads, dtype, q, q_strides, out, out_strides))
         return launch_prefill_tc(c, n_seqs, seqs, n_q_heads, n_new, q, q_strides, out, out_strides, dtype, scale, causal, stream);
 
-    // otherwise: materialise K / V of one sequence at a time (dequantised to f32 for the quantised
-    // formats, a bit copy otherwise) and run the generic kernel on them.
-    const int Hkv = c->L.Hkv, D = c->L.D;
-    const int kv_dtype = (fmt_is_block_quant(c->L.fmt) || kivi) ? B200KV_F32 : c->L.fmt;
-    int64_t max_len = 0;
-    for (int i = 0; i < n_seqs; i++) max_len = std::max<int64_t>(max_len, c->seqs[seqs[i]].len);
-    const size_t one = (size_t)Hkv * max_len * D * dtype_size(kv_dtype);
-    if (ensure_workspace(c, 2 * one) != B200KV_OK) return B200KV_KO;
+    // otherwise (f32 queries, f32 caches): the generic kernel, one sequence at a time, reading the pages in place
     for (int i = 0; i < n_seqs; i++) {
-        const int64_t T = c->seqs[seqs[i]].len;
-        void* kbuf = c->ws;
-        void* vbuf = c->ws + one;
-        const int64_t st2[2] = {T * D, D};
-        if ((kivi ? kivi_export(c, seqs[i], kbuf, st2, vbuf, st2, kv_dtype, stream)
-                  : launch_export(c, seqs[i], kbuf, st2, vbuf, st2, kv_dtype, stream)) != B200KV_OK)
-            return B200KV_KO;
-        const int64_t ks[3] = {0, T * D, D};
         const int esz = dtype_size(dtype);
         const void* qi = (const uint8_t*)q + (int64_t)i * q_strides[0] * esz;
         void* oi = (uint8_t*)out + (int64_t)i * out_strides[0] * esz;
         ProfScope ps(c, K_DENSE, stream);
-        if (launch_sdpa_dense(qi, q_strides, kbuf, ks, vbuf, ks, nullptr, nullptr, 0, oi, out_strides, 1, n_q_heads, Hkv,
-                              n_new, (int)T, D, dtype, kv_dtype, scale, causal, stream) != B200KV_OK)
+        if (launch_sdpa_paged(c, seqs[i], qi, q_strides, oi, out_strides, n_q_heads, n_new, dtype, scale, causal, stream) != B200KV_OK)
             return B200KV_KO;
     }
     return B200KV_OK;

@@ -51,15 +51,13 @@ int staging_release(b200kv_cache* c, int slot, cudaStream_t stream) {
     c->st.used[slot] = true;
     return B200KV_OK;
 }
-int ensure_workspace(b200kv_cache* c, size_t bytes) {
-    if (bytes <= c->ws_bytes) return B200KV_OK;
-    size_t want = std::max(bytes, c->ws_bytes * 2);
-    if (c->ws) B200KV_CUDA(cudaFree(c->ws));  // cudaFree waits for work that may still read the old block
-    c->ws = nullptr;
-    c->ws_bytes = 0;
-    B200KV_CUDA(cudaMalloc(&c->ws, want));
-    c->ws_bytes = want;
-    return B200KV_OK;
+// Partial records (one per page run, kv head and query head of its group) the split-KV workspace is sized for.
+// A decode launch aims at 148 x 16 CTAs, each of which publishes at most 8 records (decode_pages_per_split), and every
+// sequence adds at most one run of its own to that: 148 * 16 * 8 + max_seqs * max_q_heads covers the natural split of
+// every call; a call that would need more (more query heads than announced) takes longer runs instead.
+int64_t workspace_records(const b200kv_config& cfg) {
+    const int64_t hq = cfg.max_q_heads > 0 ? cfg.max_q_heads : 8 * (int64_t)cfg.n_kv_heads;
+    return 148 * 16 * 8 + 2 * (int64_t)cfg.max_seqs * ((hq + 7) / 8 * 8);
 }
 int validate_seqs(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs) {
     if (!c) return fail("null cache");
@@ -360,15 +358,6 @@ struct ExportParams {
     int32_t dtype, has_v, which;
 };
 
-// Integer code of channel ch of a quantised row: Q8_1 -> -128..127, Q4_0 -> nibble 0..15.
-template <int FMT>
-__device__ inline int load_code(const uint8_t* chunk, int D, int kv, int t, int ch) {
-    const int pos = code_pos(FMT, D, kv, ch);
-    const uint32_t byte = chunk[chunk_addr(FMT, D, kv, t, pos)];
-    if (FMT == B200KV_FMT_Q8_1) return (int)byte - 128;
-    return code_nibble(FMT, D, kv, ch) ? (int)(byte >> 4) : (int)(byte & 0xf);
-}
-
 // One thread per 16 bytes of the natural row; mode 0: dequantised / bit-copied elements,
 // mode 1: raw codes (int8 two's complement / GGML nibble bytes) + scales.
 template <int FMT, int MODE>
@@ -505,6 +494,8 @@ int b200kv_create(const b200kv_config* cfg, b200kv_cache** out) {
     if (cfg->head_dim != 64 && cfg->head_dim != 128) return fail("head_dim must be 64 or 128, got %d", cfg->head_dim);
     if (cfg->n_kv_heads <= 0 || cfg->max_seqs <= 0 || cfg->max_seq_tokens <= 0 || cfg->pool_tokens <= 0)
         return fail("n_kv_heads, max_seqs, max_seq_tokens and pool_tokens must be positive");
+    if (cfg->max_q_heads < 0 || (cfg->max_q_heads > 0 && cfg->max_q_heads % cfg->n_kv_heads != 0))
+        return fail("max_q_heads (%d) must be 0 or a multiple of n_kv_heads (%d)", cfg->max_q_heads, cfg->n_kv_heads);
     int n_dev = 0;
     if (cudaGetDeviceCount(&n_dev) != cudaSuccess || n_dev == 0)
         return fail("no CUDA device: b200kv has no CPU fallback");
@@ -550,10 +541,20 @@ int b200kv_create(const b200kv_config* cfg, b200kv_cache** out) {
     for (int i = 0; i < Staging::SLOTS; i++)
         if (cudaEventCreateWithFlags(&c->st.ev[i], cudaEventDisableTiming) != cudaSuccess)
             return cleanup(fail("cannot create events"));
-    if (ensure_workspace(c, 8 << 20) != B200KV_OK) return cleanup(B200KV_KO);
+    // the only scratch the attention calls use: split-KV partials, sized once (no call after this one allocates)
+    c->ws_bytes = (size_t)workspace_records(*cfg) * (cfg->head_dim + 2) * sizeof(float);
+    if (cudaMalloc(&c->ws, c->ws_bytes) != cudaSuccess) return cleanup(fail("cannot allocate the %zu-byte split-KV workspace", c->ws_bytes));
     if (cudaDeviceSynchronize() != cudaSuccess) return cleanup(fail("device error during creation"));
     *out = c;
     return B200KV_OK;
+}
+
+int64_t b200kv_workspace_bytes(const b200kv_config* cfg) {
+    if (!cfg || cfg->n_kv_heads <= 0 || cfg->max_seqs <= 0 || (cfg->head_dim != 64 && cfg->head_dim != 128) || cfg->max_q_heads < 0) {
+        fail("configuration b200kv_create would refuse");
+        return -1;
+    }
+    return workspace_records(*cfg) * (cfg->head_dim + 2) * (int64_t)sizeof(float);
 }
 
 int b200kv_destroy(b200kv_cache* c) {
@@ -629,6 +630,9 @@ static int append_impl(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int
     if (dtype < B200KV_F32 || dtype > B200KV_BF16) return fail("unknown dtype %d", dtype);
     if (!fmt_is_block_quant(c->L.fmt) && !fmt_is_kivi(c->L.fmt) && dtype != c->L.fmt)
         return fail("a bit-copy cache of format %d takes input of the same type, got dtype %d", c->L.fmt, dtype);
+    if (!fmt_is_kivi(c->L.fmt) && ((int64_t)n_seqs * (c->L.has_v ? 2 : 1) > 65535 ||
+                                   (int64_t)c->L.Hkv * n_new * (c->L.row_bytes / 16) >= (1ll << 31)))
+        return fail("append of %d sequences x %d tokens exceeds the launch geometry: split the call", n_seqs, n_new);
     DeviceGuard guard(c->cfg.device);
 
     // host bookkeeping first, committed only if everything can be enqueued
@@ -714,8 +718,6 @@ static int append_impl(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int
     };
     p.vec_ok = aligned(k_new, k_strides) && aligned(v_new, v_strides);
     const int n_kv = c->L.has_v ? 2 : 1;
-    if (!fmt_is_kivi(c->L.fmt) && ((int64_t)n_seqs * n_kv > 65535 || (int64_t)p.H * p.S * p.units >= (1ll << 31)))
-        return fail("append of %d sequences x %d tokens exceeds the launch geometry: split the call", n_seqs, n_new);
     if (fmt_is_kivi(c->L.fmt)) {
         kivi_append(c, n_seqs, seqs, n_new, k_new, k_strides, v_new, v_strides, dtype, (const int32_t*)d, stream);
     } else {
@@ -838,31 +840,29 @@ int b200kv_fork(b200kv_cache* c, int32_t seq, int32_t* new_seq_out, void* stream
         b200kv_seq_free(c, ns);
         return B200KV_KO;
     }
-    int slot;
-    uint8_t *h, *d;
-    if (!upd.empty()) {
-        if (staging_acquire(c, upd.size() * 4, &slot, &h, &d) != B200KV_OK) {
-            b200kv_seq_free(c, ns);
-            return B200KV_KO;
-        }
-        memcpy(h, upd.data(), upd.size() * 4);
-        if (staging_upload(c, slot, upd.size() * 4, stream) != B200KV_OK) {
-            b200kv_seq_free(c, ns);
-            return B200KV_KO;
-        }
-        int n = (int)(upd.size() / 2);
-        table_scatter_kernel<<<(n + 255) / 256, 256, 0, stream>>>(c->d_table, (const int32_t*)d, n);
-        staging_release(c, slot, stream);
-        if (!fmt_is_kivi(c->L.fmt))
-            for (size_t i = 0; i < src.pages.size(); i++)
-                B200KV_CUDA(cudaMemcpyAsync(c->pool + (int64_t)dst.pages[i] * c->L.page_bytes,
-                                            c->pool + (int64_t)src.pages[i] * c->L.page_bytes, c->L.page_bytes,
-                                            cudaMemcpyDeviceToDevice, stream));
-    }
-    if (fmt_is_kivi(c->L.fmt) && kivi_fork(c, seq, ns, stream) != B200KV_OK) {
+    auto undo = [&](int rc) {  // the new sequence and its pages go back; copies already enqueued only touch pages that are free again
         b200kv_seq_free(c, ns);
-        return B200KV_KO;
+        return rc;
+    };
+    // the new page-table entries travel in slot-sized pieces, so that a sequence of any length can be forked
+    const size_t per_slot = c->st.slot_bytes / 8;  // (index, page) pairs per piece
+    for (size_t at = 0; at < upd.size() / 2; at += per_slot) {
+        const size_t n = std::min(per_slot, upd.size() / 2 - at);
+        int slot;
+        uint8_t *h, *d;
+        if (staging_acquire(c, n * 8, &slot, &h, &d) != B200KV_OK) return undo(B200KV_KO);
+        memcpy(h, upd.data() + 2 * at, n * 8);
+        if (staging_upload(c, slot, n * 8, stream) != B200KV_OK) return undo(B200KV_KO);
+        table_scatter_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(c->d_table, (const int32_t*)d, (int)n);
+        staging_release(c, slot, stream);
+        if (cudaGetLastError() != cudaSuccess) return undo(fail("page-table update launch failed"));
     }
+    if (!fmt_is_kivi(c->L.fmt))
+        for (size_t i = 0; i < src.pages.size(); i++)
+            if (cudaMemcpyAsync(c->pool + (int64_t)dst.pages[i] * c->L.page_bytes, c->pool + (int64_t)src.pages[i] * c->L.page_bytes,
+                                c->L.page_bytes, cudaMemcpyDeviceToDevice, stream) != cudaSuccess)
+                return undo(fail("page copy failed: %s", cudaGetErrorString(cudaGetLastError())));
+    if (fmt_is_kivi(c->L.fmt) && kivi_fork(c, seq, ns, stream) != B200KV_OK) return undo(B200KV_KO);
     dst.len = src.len;
     *new_seq_out = ns;
     return B200KV_OK;
@@ -873,6 +873,7 @@ int b200kv_profile(b200kv_cache* c, int32_t enable) {
     c->prof_on = (enable & 1) != 0;
     c->force_simt = (enable & 2) != 0;
     c->kivi_cuda_core = (enable & 4) != 0;
+    if (enable & 8) c->stall_next_decode = true;  // consumed by the next decode launch
     return B200KV_OK;
 }
 

@@ -215,6 +215,26 @@ __device__ inline void load_piece(const uint8_t* p, float* out) {
     }
 }
 
+// Integer code of channel ch of a quantised row: Q8_1 -> -128..127, Q4_0 -> nibble 0..15.
+template <int FMT>
+__device__ inline int load_code(const uint8_t* chunk, int D, int kv, int t, int ch) {
+    const int pos = code_pos(FMT, D, kv, ch);
+    const uint32_t byte = chunk[chunk_addr(FMT, D, kv, t, pos)];
+    if (FMT == B200KV_FMT_Q8_1) return (int)byte - 128;
+    return code_nibble(FMT, D, kv, ch) ? (int)(byte >> 4) : (int)(byte & 0xf);
+}
+
+// Element `ch` of token slot t of a chunk as a float: a bit copy widened, or code * f32(f16 scale) (q8_1.rs:50-63, q4_0.rs:82-95).
+__device__ inline float chunk_elem(const uint8_t* chunk, int fmt, int D, int kv, int t, int ch) {
+    if (fmt == B200KV_FMT_F32) return *(const float*)(chunk + chunk_addr(fmt, D, kv, t, ch * 4));
+    if (fmt == B200KV_FMT_F16) return __half2float(*(const __half*)(chunk + chunk_addr(fmt, D, kv, t, ch * 2)));
+    if (fmt == B200KV_FMT_BF16) return __bfloat162float(*(const __nv_bfloat16*)(chunk + chunk_addr(fmt, D, kv, t, ch * 2)));
+    const __half* scales = (const __half*)(chunk + PAGE_TOKENS * fmt_row_bytes(fmt, D));
+    const float d = __half2float(scales[scale_index(fmt, D, kv, t, ch / 32)]);
+    if (fmt == B200KV_FMT_Q8_1) return __fmul_rn((float)load_code<B200KV_FMT_Q8_1>(chunk, D, kv, t, ch), d);
+    return __fmul_rn((float)(load_code<B200KV_FMT_Q4_0>(chunk, D, kv, t, ch) - 8), d);
+}
+
 // ---- shared-memory barriers and bulk copies (sm_90+ PTX; no cluster multicast anywhere) -----
 __device__ inline uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -246,15 +266,15 @@ __device__ inline uint64_t globaltimer_ns() {
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
-// Waits for a barrier phase, giving up after ~1 s so that a copy that never lands cannot hang the GPU.
-__device__ inline bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+// Waits for a barrier phase, giving up after `limit_ns` (~1 s by default) so that a copy that never lands cannot hang the GPU.
+__device__ inline bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, uint64_t limit_ns = 1000000000ull) {
     if (mbar_try_wait(bar, parity)) return true;
     uint64_t t0 = globaltimer_ns();
     for (;;) {
 #pragma unroll 1
         for (int i = 0; i < 64; i++)
             if (mbar_try_wait(bar, parity)) return true;
-        if (globaltimer_ns() - t0 > 1000000000ull) return false;
+        if (globaltimer_ns() - t0 > limit_ns) return false;
     }
 }
 // Untiled bulk copy global -> this CTA's shared memory; completion is counted in bytes on `bar`.

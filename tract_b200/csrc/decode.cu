@@ -101,7 +101,8 @@ __global__ void __launch_bounds__(128) decode_kernel(DecodeParams p, const __gri
         for (int s = 0; s < NS; s++) mbar_init(&bars[s], 1);
         mbar_fence_init();
         // start streaming right away; the other threads first meet the barriers after the __syncthreads below
-        for (int i = 0; i < NS && i < n_tiles; i++) issue(i);
+        const bool stalled = (int)blockIdx.x == p.stall_item && blockIdx.y == 0 && blockIdx.z == 0;  // test hook, see DecodeParams
+        for (int i = 0; i < NS && i < n_tiles && !stalled; i++) issue(i);
     }
     __syncthreads();
 
@@ -129,7 +130,7 @@ __global__ void __launch_bounds__(128) decode_kernel(DecodeParams p, const __gri
 
     for (int i = 0; i < n_tiles; i++) {
         const int st = i % NS;
-        const bool ok = mbar_wait_bounded(&bars[st], (uint32_t)((i / NS) & 1));
+        const bool ok = mbar_wait_bounded(&bars[st], (uint32_t)((i / NS) & 1), p.wait_ns);
         if (__syncthreads_or(!ok)) {
             if (tid == 0) atomicOr(p.status, STATUS_WAIT_EXPIRED);
             failed = true;
@@ -327,7 +328,7 @@ struct CombineParams {
 // The pass is pure latency (a few KB per CTA), so nothing in it forms a chain of dependent round trips: the
 // (max, sum) pairs of all splits are fetched at once, and so are the partial outputs of each channel.
 __global__ void combine_kernel(CombineParams p, const __grid_constant__ InlineBatch ib) {
-    __shared__ float wgt_s[64], sum_s[64];  // at most 64 splits per sequence
+    __shared__ float wgt_s[MAX_SPLITS], sum_s[MAX_SPLITS];
     __shared__ float den_s;
     const int b = blockIdx.x, hq = blockIdx.y, ch = threadIdx.x;
     const int kvh = hq / p.G, g = hq % p.G;
@@ -336,7 +337,7 @@ __global__ void combine_kernel(CombineParams p, const __grid_constant__ InlineBa
     if (p.act) {  // a warp holds one block of 32 columns of row b
         const int64_t nb = (int64_t)p.Hkv * p.G * p.D / QK;
         act_dst = p.act + ((int64_t)(b >> 3) * nb + (int64_t)hq * (p.D / QK) + (ch >> 5)) * Q_ACT_BLOCK;
-        if (b == 0 && hq == 0 && ch == 0) *p.act_status = 0;
+        if (b == 0 && hq == 0 && ch == 0) q40_status_begin(p.act_status);
         if (b >= p.n_rows) {
             q40_quantize_block(0.f, false, act_dst, b & 7, ch & 31);
             return;
@@ -417,6 +418,8 @@ int launch_decode_simt(int fmt, int D, const DecodeParams& p, int n_items, cudaS
 int launch_combine(const DecodeParams& p, const int32_t* batch_info, void* out, int64_t ob, int64_t oh, int n_seqs,
                    int n_q_heads, int D, cudaStream_t stream, const InlineBatch* ibp) {
     const InlineBatch& ib = ibp ? *ibp : empty_inline_batch();
+    for (int i = 0; i < ib.n; i++)  // the combine pass holds the weights of one sequence's splits in MAX_SPLITS shared-memory slots
+        if (ib.ent[i].w > MAX_SPLITS) return fail("batch entry %d has %d splits, the combine pass takes at most %d", i, ib.ent[i].w, MAX_SPLITS);
     CombineParams cp{};
     cp.part_o = p.part_o, cp.part_ml = p.part_ml, cp.batch_info = batch_info;
     cp.out = out, cp.ob = ob, cp.oh = oh;
@@ -462,7 +465,7 @@ int64_t decode_pages_per_split(const b200kv_cache* c, int32_t n_seqs, const int3
         int64_t cand = std::max<int64_t>(1, work / slots);
         for (; cand < max_pages; cand += std::max<int64_t>(1, cand / 32)) {  // the count falls as cand grows; at max_pages it is one CTA per pair
             int64_t n = 0;
-            for (int i = 0; i < n_seqs; i++) n += std::min<int64_t>(64, (pages_of(i) + cand - 1) / cand);
+            for (int i = 0; i < n_seqs; i++) n += std::min<int64_t>(MAX_SPLITS, (pages_of(i) + cand - 1) / cand);
             if (n * Hkv * nz <= slots) break;
         }
         chunk = std::min(cand, max_pages);
@@ -485,24 +488,32 @@ int launch_decode(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t 
         if (s.len <= 0) return fail("sequence %d is empty: nothing to attend to", seqs[i]);
         total_pages += (s.len + PAGE_TOKENS - 1) / PAGE_TOKENS - first_of(s) / PAGE_TOKENS;
     }
-    const int64_t chunk = decode_pages_per_split(c, n_seqs, seqs, window, use_mma, nz);
+    int64_t chunk = decode_pages_per_split(c, n_seqs, seqs, window, use_mma, nz);
     // one entry per sequence: {table row, length, first work item, splits}; the work items follow from it
     InlineBatch ib{};
     std::vector<int4> ent((size_t)n_seqs);
     std::vector<int32_t> first((size_t)n_seqs);
     int n_items = 0;
-    for (int i = 0; i < n_seqs; i++) {
-        const SeqState& s = c->seqs[seqs[i]];
-        first[i] = (int32_t)first_of(s);
-        const int pages = (int)((s.len + PAGE_TOKENS - 1) / PAGE_TOKENS) - first[i] / PAGE_TOKENS;
-        const int splits = (int)std::min<int64_t>(64, (pages + chunk - 1) / chunk);
-        ent[i] = make_int4(seqs[i], (int)s.len, n_items, splits);
-        n_items += splits;
+    size_t n_part = 0;
+    for (;;) {
+        n_items = 0;
+        for (int i = 0; i < n_seqs; i++) {
+            const SeqState& s = c->seqs[seqs[i]];
+            first[i] = (int32_t)first_of(s);
+            const int pages = (int)((s.len + PAGE_TOKENS - 1) / PAGE_TOKENS) - first[i] / PAGE_TOKENS;
+            const int splits = (int)std::min<int64_t>(MAX_SPLITS, (pages + chunk - 1) / chunk);
+            ent[i] = make_int4(seqs[i], (int)s.len, n_items, splits);
+            n_items += splits;
+        }
+        n_part = (size_t)n_items * Hkv * G;
+        // the workspace was sized once, at create: a call whose natural split does not fit takes longer runs instead
+        if (n_part * (D + 2) * sizeof(float) <= c->ws_bytes) break;
+        if (n_items == n_seqs)
+            return fail("%d sequences x %d query heads need %zu bytes of split partials, the workspace holds %zu: create the cache "
+                        "with max_q_heads >= %d", n_seqs, n_q_heads, n_part * (D + 2) * sizeof(float), c->ws_bytes, n_q_heads);
+        chunk *= 2;
     }
     const bool inline_batch = n_seqs <= INLINE_BATCH;  // small batches travel as a kernel parameter: no copy, no slot
-    const size_t n_part = (size_t)n_items * Hkv * G;
-    const size_t ws_need = n_part * (D + 2) * sizeof(float);
-    if (ensure_workspace(c, ws_need) != B200KV_OK) return B200KV_KO;
     int slot = -1;
     uint8_t *h = nullptr, *d = nullptr;
     size_t items_bytes = 0;
@@ -531,6 +542,8 @@ int launch_decode(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t 
     p.part_ml = p.part_o + n_part * D;
     p.page_bytes = c->L.page_bytes, p.n_pages = (int32_t)c->n_pages, p.max_pages_per_seq = c->max_pages_per_seq;
     p.Hkv = Hkv, p.G = G, p.dtype = dtype, p.scale = scale;
+    p.wait_ns = c->wait_ns;
+    if (c->stall_next_decode) p.stall_item = 0, p.wait_ns = 1000000, c->stall_next_decode = false;  // one launch, 1 ms
     int rc;
     {
     ProfScope ps(c, K_DECODE, stream);

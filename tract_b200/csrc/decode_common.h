@@ -31,6 +31,10 @@ struct DecodeParams {
     int64_t page_bytes;
     int32_t n_pages, max_pages_per_seq, Hkv, G, dtype;
     float scale;
+    uint64_t wait_ns = 1000000000ull;  // limit of each bounded barrier wait
+    int32_t stall_item = -1;  // -1, or (a test hook) the work item whose CTA of kv head 0 never issues its copies: its first wait
+                         // runs out, it flags STATUS_WAIT_EXPIRED, publishes an empty partial and returns
+    int32_t pad0 = 0;
 };
 
 // Per-call batch description small enough to travel as a kernel parameter (no host-to-device copy, no
@@ -38,6 +42,7 @@ struct DecodeParams {
 // number of splits}.  The work items are a pure function of it: split k of a sequence with `pages` pages
 // covers pages [k * base + min(k, rem), ...) where base = pages / splits, rem = pages % splits.
 constexpr int INLINE_BATCH = 256;
+constexpr int MAX_SPLITS = 64;  // most partials per sequence the combine pass merges
 struct InlineBatch {
     int32_t n;  // entries in use; 0 = the kernels read p.items / batch_info from device memory instead
     int32_t pad[3];

@@ -89,7 +89,8 @@ __global__ void __launch_bounds__(128, MGeo<FMT>::MIN_CTAS) decode_mma_kernel(De
         for (int s = 0; s < NS; s++) mbar_init(&bars[s], 1);
         mbar_fence_init();
         // start streaming right away; the other threads first meet the barriers after the __syncthreads below
-        for (int i = 0; i < NS && i < n_tiles; i++) issue(i);
+        const bool stalled = (int)blockIdx.x == p.stall_item && blockIdx.y == 0 && blockIdx.z == 0;  // test hook, see DecodeParams
+        for (int i = 0; i < NS && i < n_tiles && !stalled; i++) issue(i);
     }
     // q of the group as f32 in shared memory, rows beyond the group zero
     for (int idx = tid; idx < 8 * MD; idx += 128) {
@@ -167,7 +168,7 @@ __global__ void __launch_bounds__(128, MGeo<FMT>::MIN_CTAS) decode_mma_kernel(De
 
     for (int i = 0; i < n_tiles; i++) {
         const int st = i % NS;
-        const bool ok = mbar_wait_bounded(&bars[st], (uint32_t)((i / NS) & 1));
+        const bool ok = mbar_wait_bounded(&bars[st], (uint32_t)((i / NS) & 1), p.wait_ns);
         if (__syncthreads_or(!ok)) {
             if (tid == 0) atomicOr(p.status, STATUS_WAIT_EXPIRED);
             failed = true;

@@ -4,9 +4,9 @@
 // Some callers must not trigger a device allocation while they run a step: a serving loop that has
 // handed all free HBM to its page pools, a plan whose device arena was sized once up front and that
 // treats any later cudaMalloc as a bug, or code that runs where an implicit device synchronisation
-// (which cudaMalloc / cudaFree imply) would stall every other stream.  b200kv_attend may grow the
-// cache's workspace with cudaFree + cudaMalloc when a call needs more split partials than any call
-// before it; this entry point never does.  It runs the same kernels, only the partials go to
+// (which cudaMalloc / cudaFree imply) would stall every other stream.  b200kv_attend keeps its split
+// partials in a workspace that b200kv_create allocates; this entry point needs no device memory of
+// the cache's own beyond the pages: it runs the same kernels, only the partials go to
 // g_decode_scratch below, which every GPU that loads this library holds from load until exit.
 #include <cmath>
 #include <cstring>
@@ -50,6 +50,8 @@ extern "C" int b200kv_attend_static_scratch(b200kv_cache* c, int32_t n_seqs, con
                                             const int64_t out_strides[3], int32_t dtype, float scale, void* stream_) {
     if (validate_seqs(c, n_seqs, seqs) != B200KV_OK) return B200KV_KO;
     if (!c->L.has_v) return fail("this cache holds one tensor only: attention needs K and V");
+    if (fmt_is_kivi(c->L.fmt))
+        return fail("a KIVI cache (format %d) has decode kernels of its own, which this entry point does not run: use b200kv_attend", c->L.fmt);
     if (!q || !out || !q_strides || !out_strides) return fail("null tensor or strides");
     if (n_q_heads <= 0 || n_q_heads % c->L.Hkv != 0)
         return fail("n_q_heads (%d) must be a positive multiple of n_kv_heads (%d)", n_q_heads, c->L.Hkv);
@@ -59,7 +61,7 @@ extern "C" int b200kv_attend_static_scratch(b200kv_cache* c, int32_t n_seqs, con
     DeviceGuard guard(c->cfg.device);
 
     const int Hkv = c->L.Hkv, D = c->L.D, G = n_q_heads / Hkv;
-    const bool use_mma = decode_mma_supported(c->L.fmt, D, dtype);
+    const bool use_mma = decode_mma_supported(c->L.fmt, D, dtype) && !c->force_simt;
     const int GT = use_mma ? 8 : (G == 1 ? 1 : 4), nz = (G + GT - 1) / GT;
     int64_t total_pages = 0;
     for (int i = 0; i < n_seqs; i++) {
@@ -108,7 +110,10 @@ extern "C" int b200kv_attend_static_scratch(b200kv_cache* c, int32_t n_seqs, con
             begin += n;
         }
     }
-    if (staging_upload(c, slot, desc_bytes, stream) != B200KV_OK) return B200KV_KO;
+    if (staging_upload(c, slot, desc_bytes, stream) != B200KV_OK) {
+        staging_release(c, slot, stream);  // the slot goes back to the ring; nothing that reads it was enqueued
+        return B200KV_KO;
+    }
 
     DecodeParams p{};
     p.pool = c->pool, p.table = c->d_table, p.items = (const WorkItem*)d, p.status = c->d_status;
@@ -119,6 +124,7 @@ extern "C" int b200kv_attend_static_scratch(b200kv_cache* c, int32_t n_seqs, con
     p.part_ml = scratch + n_part * D;
     p.page_bytes = c->L.page_bytes, p.n_pages = (int32_t)c->n_pages, p.max_pages_per_seq = c->max_pages_per_seq;
     p.Hkv = Hkv, p.G = G, p.dtype = dtype, p.scale = scale;
+    p.wait_ns = c->wait_ns;
     int rc = use_mma ? launch_decode_mma(c->L.fmt, p, (int)n_items, stream)
                      : launch_decode_simt(c->L.fmt, D, p, (int)n_items, stream);
     if (rc == B200KV_OK)

@@ -76,8 +76,10 @@ struct b200kv_cache {
     std::vector<int32_t> free_pages;
     std::vector<b200kv::SeqState> seqs;
     b200kv::Staging st;
-    uint8_t* ws = nullptr;  // scratch owned by the cache: split-KV partials, prefill staging
+    uint8_t* ws = nullptr;  // split-KV partials: allocated once at create, never grown
     size_t ws_bytes = 0;
+    uint64_t wait_ns = 1000000000ull;  // limit of every bounded barrier wait of the decode kernels
+    bool stall_next_decode = false;    // test hook: the next decode launch leaves one CTA waiting for a copy nobody issued
     // optional per-launch timing (the analogue of tract-cuda's event pairs around every launch,
     // cuda/src/context.rs:364-453): off by default
     bool kivi_cuda_core = false;  // test hook: KIVI decode through the CUDA-core kernel alone
@@ -98,8 +100,8 @@ int staging_acquire(b200kv_cache* c, size_t bytes, int* slot, uint8_t** host, ui
 int staging_upload(b200kv_cache* c, int slot, size_t bytes, cudaStream_t stream);
 // Marks the slot as consumed by everything enqueued on `stream` so far.
 int staging_release(b200kv_cache* c, int slot, cudaStream_t stream);
-// Makes sure the cache-owned scratch holds at least `bytes`.
-int ensure_workspace(b200kv_cache* c, size_t bytes);
+// Partial records the split-KV workspace of a configuration holds (it is allocated once, by b200kv_create).
+int64_t workspace_records(const b200kv_config& cfg);
 
 int validate_seqs(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs);
 
@@ -142,6 +144,8 @@ int launch_sdpa_dense(const void* q, const int64_t* qs, const void* k, const int
                       const int64_t* vs, const void* mask, const int64_t* ms, int mask_dtype, void* out,
                       const int64_t* os, int B, int Hq, int Hkv, int S, int T, int D, int dtype, int kv_dtype,
                       float scale, int causal, cudaStream_t stream);
+int launch_sdpa_paged(b200kv_cache* c, int32_t seq, const void* q, const int64_t* qs, void* out, const int64_t* os, int Hq, int S,
+                      int dtype, float scale, int causal, cudaStream_t stream);
 // kivi.cu
 bool fmt_is_kivi(int fmt);
 int kivi_create(b200kv_cache* c);

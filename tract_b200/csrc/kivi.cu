@@ -45,18 +45,6 @@ __device__ inline void kivi_store_code(const KiviView& v, int stream, int32_t pg
         if ((c & 1) == 0) row[c >> 1] = (uint8_t)((code & 0xf) | ((other & 0xf) << 4));
     }
 }
-__device__ inline uint32_t kivi_load_code(const KiviView& v, int stream, int32_t pg, int h, int slot, int c) {
-    if (kivi_mma_layout(v.bits, v.D)) {
-        const uint32_t b = v.codes[stream][((int64_t)pg * v.H + h) * PAGE_TOKENS * v.row_bytes + kivi_code_offset(v.bits, stream, slot, c)];
-        if (v.bits == 8) return b;
-        return code_nibble(B200KV_FMT_Q4_0, 128, stream, c) ? (b >> 4) : (b & 0xf);
-    }
-    const uint8_t* row = v.codes[stream] + (((int64_t)pg * v.H + h) * PAGE_TOKENS + slot) * v.row_bytes;
-    if (v.bits == 8) return row[c];
-    const uint32_t b = row[c >> 1];
-    return (c & 1) ? (b >> 4) : (b & 0xf);
-}
-
 struct KiviAppend {
     KiviView v;
     const int32_t* desc;  // per batch entry {sequence, length before the append, -, -}
@@ -172,26 +160,7 @@ __global__ void kivi_export_kernel(KiviExport e) {
     const KiviView& v = e.v;
     const int stream = blockIdx.z, h = blockIdx.y, c = threadIdx.x;
     const int64_t t = blockIdx.x;
-    float val;
-    if (t < SINK) {
-        val = v.sinks[((((int64_t)e.seq * v.H + h) * 2 + stream) * SINK + t) * v.D + c];
-    } else {
-        const int64_t i = t - SINK;
-        const int32_t pg = v.table[(int64_t)e.seq * v.max_pages_per_seq + i / PAGE_TOKENS];
-        const int slot = (int)(i % PAGE_TOKENS);
-        if (v.per_channel[stream]) {
-            const int64_t n_fin = (e.len - SINK) / KBLOCK;
-            if (i < n_fin * KBLOCK) {
-                const float* par = v.params[stream] + (((int64_t)pg * v.H + h) * 2 + slot / KBLOCK) * 2 * v.D;
-                val = kivi_dequant(kivi_load_code(v, stream, pg, h, slot, c), par[c], par[v.D + c]);
-            } else {
-                val = v.residual[((((int64_t)e.seq * v.H + h) * 2 + stream) * KBLOCK + i % KBLOCK) * v.D + c];
-            }
-        } else {
-            const float* par = v.params[stream] + (((int64_t)pg * v.H + h) * PAGE_TOKENS + slot) * 2;
-            val = kivi_dequant(kivi_load_code(v, stream, pg, h, slot, c), par[0], par[1]);
-        }
-    }
+    const float val = kivi_elem(v, e.seq, e.len, stream, h, t, c);
     st_from_f32(e.dst[stream], e.dtype, h * e.dh[stream] + t * e.dt[stream] + c, val);
 }
 
@@ -416,7 +385,8 @@ int kivi_decode(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t n_
         // pick the split count that fills whole waves of 148 x (CTAs per SM) best (the splits of a batch of
         // equally long sequences cost the same), with at least 4 pages per split and at most 4 waves
         const int64_t units = (int64_t)n_seqs * H * nz, slots = 148 * kivi_mma_ctas_per_sm(c->kivi.bits);
-        const int ns_max = (int)std::max<int64_t>(1, std::min<int64_t>(64, pages / 4));
+        // one slot of the combine pass goes to the partial of the sinks and the residual block
+        const int ns_max = (int)std::max<int64_t>(1, std::min<int64_t>(MAX_SPLITS - 1, pages / 4));
         double best = -1.0;
         ns = 1;
         for (int cand = 1; cand <= ns_max; cand++) {
@@ -430,15 +400,21 @@ int kivi_decode(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t n_
         // enough splits to cover the GPU a few times, at least 8 tiles (256 tokens) each
         const int64_t tiles = (std::max<int64_t>(max_len - SINK, 0) + KTILE - 1) / KTILE + 1;
         const int nz = (G + KGT - 1) / KGT;
-        ns = (int)std::min<int64_t>(64, std::max<int64_t>(1, (148 * 10 + (int64_t)n_seqs * H * nz - 1) / ((int64_t)n_seqs * H * nz)));
+        ns = (int)std::min<int64_t>(MAX_SPLITS, std::max<int64_t>(1, (148 * 10 + (int64_t)n_seqs * H * nz - 1) / ((int64_t)n_seqs * H * nz)));
         ns = (int)std::max<int64_t>(1, std::min<int64_t>(ns, tiles / 8));
         n_part_per_seq = ns;
     }
+    // the workspace was sized once, at create: a call whose natural split does not fit takes fewer, longer splits
+    const size_t per_split = (size_t)n_seqs * H * G * (D + 2) * sizeof(float);
+    while (ns > 1 && (size_t)(mma ? ns + 1 : ns) * per_split > c->ws_bytes) ns--;
+    n_part_per_seq = mma ? ns + 1 : ns;
+    if ((size_t)n_part_per_seq * per_split > c->ws_bytes)
+        return fail("%d sequences x %d query heads need %zu bytes of split partials, the workspace holds %zu: create the cache with "
+                    "max_q_heads >= %d", n_seqs, n_q_heads, (size_t)n_part_per_seq * per_split, c->ws_bytes, n_q_heads);
     InlineBatch ib{};
     ib.n = n_seqs;
     for (int i = 0; i < n_seqs; i++) ib.ent[i] = make_int4(seqs[i], (int)c->seqs[seqs[i]].len, i * n_part_per_seq, n_part_per_seq);
     const size_t n_part = (size_t)n_seqs * n_part_per_seq * H * G;
-    if (ensure_workspace(c, n_part * (D + 2) * sizeof(float)) != B200KV_OK) return B200KV_KO;
     KiviDecode p{};
     p.v = kivi_view(c);
     p.q = q, p.qb = qs[0], p.qh = qs[1];

@@ -34,6 +34,35 @@ __device__ inline uint32_t kivi_code_offset(int bits, int stream, int slot, int 
 // lo + code * scale, multiply then add (quant_dyn_kv_cache.rs:141-146, :231-240)
 __device__ inline float kivi_dequant(uint32_t code, float lo, float scale) { return __fadd_rn(lo, __fmul_rn((float)code, scale)); }
 
+__device__ inline uint32_t kivi_load_code(const KiviView& v, int stream, int32_t pg, int h, int slot, int c) {
+    if (kivi_mma_layout(v.bits, v.D)) {
+        const uint32_t b = v.codes[stream][((int64_t)pg * v.H + h) * PAGE_TOKENS * v.row_bytes + kivi_code_offset(v.bits, stream, slot, c)];
+        if (v.bits == 8) return b;
+        return code_nibble(B200KV_FMT_Q4_0, 128, stream, c) ? (b >> 4) : (b & 0xf);
+    }
+    const uint8_t* row = v.codes[stream] + (((int64_t)pg * v.H + h) * PAGE_TOKENS + slot) * v.row_bytes;
+    if (v.bits == 8) return row[c];
+    const uint32_t b = row[c >> 1];
+    return (c & 1) ? (b >> 4) : (b & 0xf);
+}
+
+// Element c of token t (0 .. len-1) of head h of one stream, as dequant_all gives it (quant_dyn_kv_cache.rs:132-148,
+// :222-249): the f32 sinks, quantised rows as lo + code * scale, the f32 residual rows of a per-channel stream verbatim.
+__device__ inline float kivi_elem(const KiviView& v, int32_t seq, int64_t len, int stream, int h, int64_t t, int c) {
+    if (t < SINK) return v.sinks[((((int64_t)seq * v.H + h) * 2 + stream) * SINK + t) * v.D + c];
+    const int64_t i = t - SINK;
+    const int32_t pg = v.table[(int64_t)seq * v.max_pages_per_seq + i / PAGE_TOKENS];
+    const int slot = (int)(i % PAGE_TOKENS);
+    if (v.per_channel[stream]) {
+        const int64_t n_fin = (len - SINK) / KBLOCK;
+        if (i >= n_fin * KBLOCK) return v.residual[((((int64_t)seq * v.H + h) * 2 + stream) * KBLOCK + i % KBLOCK) * v.D + c];
+        const float* par = v.params[stream] + (((int64_t)pg * v.H + h) * 2 + slot / KBLOCK) * 2 * v.D;
+        return kivi_dequant(kivi_load_code(v, stream, pg, h, slot, c), par[c], par[v.D + c]);
+    }
+    const float* par = v.params[stream] + (((int64_t)pg * v.H + h) * PAGE_TOKENS + slot) * 2;
+    return kivi_dequant(kivi_load_code(v, stream, pg, h, slot, c), par[0], par[1]);
+}
+
 KiviView kivi_view(const b200kv_cache* c);
 
 }  // namespace b200kv

@@ -49,7 +49,7 @@ __global__ void q40_quant_act_kernel(const void* __restrict__ a, int64_t a_strid
                                      int32_t dtype, int64_t nb, uint8_t* __restrict__ act, int* __restrict__ status) {
     grid_launch_dependents();  // the GEMM may be scheduled: it starts pulling weights and waits for this grid before it reads `act`
     grid_dependency_wait();    // the kernel before has written the activation (and has finished with `act`, if it was a GEMM)
-    if (blockIdx.x == 0 && threadIdx.x == 0) *status = 0;
+    if (blockIdx.x == 0 && threadIdx.x == 0) q40_status_begin(status);
     const int lane = threadIdx.x & 31;
     const int64_t wid = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int64_t groups = (m + 7) / 8;
@@ -88,7 +88,7 @@ __global__ void __launch_bounds__(512) q40_norm_quant_kernel(const float* x, int
         }
     }
     grid_dependency_wait();  // the kernel before (the GEMM that wrote `residual`, and read `act`) is done
-    if (blockIdx.x == 0 && threadIdx.x == 0) *status = 0;
+    if (blockIdx.x == 0 && threadIdx.x == 0) q40_status_begin(status);
     const int64_t mi = blockIdx.x, nb = d / QK;
     const int slot = (int)(mi % 8), lane = threadIdx.x & 31;
     uint8_t* dst = act + (mi / 8) * nb * Q_ACT_BLOCK;
@@ -302,7 +302,7 @@ __global__ void __launch_bounds__(Q_WARPS * 32, MG == 1 ? 2 : 1) q40_gemm_kernel
     }
     __syncthreads();
     if (*fail_s) {
-        if (tid == 0) atomicOr(p.status, STATUS_WAIT_EXPIRED);
+        if (tid == 0) q40_status_fail(p.status, STATUS_WAIT_EXPIRED);
         __nanosleep(200000);  // copies that may still be in flight land before the CTA's memory is released
     }
 }
@@ -431,7 +431,7 @@ __global__ void __launch_bounds__((R_WARPS + 1) * 32, 2) q40_gemm_rows_kernel(Q4
     }
     __syncthreads();
     if (*fail_s) {
-        if (tid == 0) atomicOr(p.status, STATUS_WAIT_EXPIRED);
+        if (tid == 0) q40_status_fail(p.status, STATUS_WAIT_EXPIRED);
         __nanosleep(200000);  // copies that may still be in flight land before the CTA's memory is released
     }
 }
@@ -597,9 +597,12 @@ extern "C" int b200kv_q40_gemm(const void* packed, int64_t n, int64_t k, const v
 
 extern "C" int b200kv_q40_check(const void* scratch, void* stream) {
     if (!scratch) return fail("null pointer");
-    int st = 0;
-    B200KV_CUDA(cudaMemcpyAsync(&st, scratch, 4, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    int st[3] = {0, 0, 0};
+    B200KV_CUDA(cudaMemcpyAsync(st, scratch, sizeof st, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
     B200KV_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
-    if (st & STATUS_WAIT_EXPIRED) return fail("a bounded wait in the Q4_0 GEMM kernel expired (a bulk copy never landed)");
+    const bool sticky = (uint32_t)st[2] == Q_MAGIC && (st[1] & STATUS_WAIT_EXPIRED);
+    if (sticky) B200KV_CUDA(cudaMemsetAsync((uint8_t*)const_cast<void*>(scratch) + 4, 0, 4, (cudaStream_t)stream));  // reported once
+    if (sticky || (st[0] & STATUS_WAIT_EXPIRED))
+        return fail("a bounded wait in a Q4_0 GEMM that used this scratch expired (a bulk copy never landed)");
     return B200KV_OK;
 }

@@ -13,7 +13,21 @@ constexpr int Q_STAGE_BLOCKS = 8;
 constexpr int Q_STAGE_BYTES = Q_STAGE_BLOCKS * Q_BLOCK_BYTES;  // 2304
 constexpr int Q_DEPTH = 2;                // stages in flight per warp
 constexpr int Q_ACT_BLOCK = 2 * 8 * 16 + 8 * 4 + 8 * 4;  // per block and group of 8 activation rows: codes [2 halves][8][16], scales f32 [8], sums i32 [8]
-constexpr int Q_HEADER = 256;             // scratch header: the status word
+constexpr int Q_HEADER = 256;             // scratch header: word 0 = status of the GEMMs since the last producer, word 1 = status of every
+                                          // GEMM since the last b200kv_q40_check (no producer clears it), word 2 = Q_MAGIC once word 1 is valid
+constexpr uint32_t Q_MAGIC = 0x51343041u;
+
+// Run by one thread of every kernel that produces the activation: word 0 starts a new epoch; the sticky word is zeroed
+// only the first time this scratch is seen (caller memory arrives uninitialised), so that a wait that expired in any
+// GEMM of a step stays visible until the host asks.
+__device__ inline void q40_status_begin(int* status) {
+    if ((uint32_t)status[2] != Q_MAGIC) status[1] = 0, status[2] = (int)Q_MAGIC;
+    status[0] = 0;
+}
+__device__ inline void q40_status_fail(int* status, int bits) {
+    atomicOr(status, bits);
+    atomicOr(status + 1, bits);
+}
 constexpr int Q_RING_STAGE = Q_STAGE_BYTES + Q_STAGE_BLOCKS * Q_ACT_BLOCK;  // weights then activations of 8 blocks: 4864 bytes
 
 // Q4_0::quantize_row_q8 (q4_0.rs:199-222) for one block: the 32 lanes of a warp hold its 32 values.  Writes the codes,

@@ -6,11 +6,24 @@
 // otherwise runs on the CPU.  It favours generality over speed: one warp per query row, keys taken 32
 // at a time (one per lane), f32 accumulation, online softmax.  The benchmark shapes go through the
 // specialised decode / prefill kernels instead.
+//
+// The same kernel also serves b200kv_attend for the cases its specialised kernels leave out (several queries per
+// sequence with f32 queries or an f32 cache): K and V are then read straight from the pages of one sequence, element
+// by element, dequantised as the reference's dequantise-on-read does -- nothing is materialised.
 #include <cmath>
 
-#include "internal.h"
+#include "kivi_common.cuh"
 
 namespace b200kv {
+
+// K / V of one sequence as they lie in a cache (PAGED instantiation of the kernel).
+struct PagedSrc {
+    const uint8_t* pool;
+    const int32_t* table_row;  // page ids of the sequence
+    int64_t page_bytes, len;
+    int32_t fmt, chunk_bytes, kivi, seq;
+    KiviView kv;  // the KIVI stores, when kivi != 0
+};
 
 struct DenseParams {
     const void *q, *k, *v, *mask;
@@ -19,11 +32,21 @@ struct DenseParams {
     int32_t B, Hq, Hkv, S, T, D;
     int32_t dtype, kv_dtype, mask_dtype, causal;
     float scale;
+    PagedSrc src;
 };
+
+// Channel d of token j of kv head h, K (which = 0) or V (1), of the sequence behind `s`.
+__device__ inline float paged_elem(const PagedSrc& s, int D, int which, int h, int j, int d) {
+    if (s.kivi) return kivi_elem(s.kv, s.seq, s.len, which, h, j, d);
+    const int32_t pg = s.table_row[j / PAGE_TOKENS];
+    const uint8_t* chunk = s.pool + (int64_t)pg * s.page_bytes + (int64_t)(h * 2 + which) * s.chunk_bytes;
+    return chunk_elem(chunk, s.fmt, D, which, j % PAGE_TOKENS, d);
+}
 
 constexpr int DENSE_WARPS = 4;
 constexpr int DENSE_MAX_D = 256;
 
+template <bool PAGED>
 __global__ void __launch_bounds__(DENSE_WARPS * 32) sdpa_dense_kernel(DenseParams p) {
     __shared__ float q_s[DENSE_WARPS][DENSE_MAX_D];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -57,7 +80,11 @@ __global__ void __launch_bounds__(DENSE_WARPS * 32) sdpa_dense_kernel(DenseParam
         if (j < kv_hi) {
             float dot = 0.f;
             const int64_t kr = kbase + j * p.ks[2];
-            for (int d = 0; d < D; d++) dot = fmaf(q_s[warp][d], ld_as_f32(p.k, p.kv_dtype, kr + d), dot);
+            if (PAGED) {
+                for (int d = 0; d < D; d++) dot = fmaf(q_s[warp][d], paged_elem(p.src, D, 0, kvh, j, d), dot);
+            } else {
+                for (int d = 0; d < D; d++) dot = fmaf(q_s[warp][d], ld_as_f32(p.k, p.kv_dtype, kr + d), dot);
+            }
             s = dot * p.scale;
             if (p.mask) s += ld_as_f32(p.mask, p.mask_dtype, mbase + j * p.ms[3]);
         }
@@ -82,7 +109,7 @@ __global__ void __launch_bounds__(DENSE_WARPS * 32) sdpa_dense_kernel(DenseParam
 #pragma unroll
             for (int r = 0; r < DENSE_MAX_D / 32; r++) {
                 const int d = lane + 32 * r;
-                if (d < D) acc[r] = fmaf(pw, ld_as_f32(p.v, p.kv_dtype, vr + d), acc[r]);
+                if (d < D) acc[r] = fmaf(pw, PAGED ? paged_elem(p.src, D, 1, kvh, c0 + jj, d) : ld_as_f32(p.v, p.kv_dtype, vr + d), acc[r]);
             }
         }
     }
@@ -107,7 +134,26 @@ int launch_sdpa_dense(const void* q, const int64_t* qs, const void* k, const int
     p.dtype = dtype, p.kv_dtype = kv_dtype, p.mask_dtype = mask_dtype, p.causal = causal, p.scale = scale;
     const int64_t rows = (int64_t)B * Hq * S;
     if (rows == 0) return B200KV_OK;
-    sdpa_dense_kernel<<<(unsigned)((rows + DENSE_WARPS - 1) / DENSE_WARPS), DENSE_WARPS * 32, 0, stream>>>(p);
+    sdpa_dense_kernel<false><<<(unsigned)((rows + DENSE_WARPS - 1) / DENSE_WARPS), DENSE_WARPS * 32, 0, stream>>>(p);
+    B200KV_CUDA(cudaGetLastError());
+    return B200KV_OK;
+}
+
+// The S queries of one sequence (its last S cached positions) over its pages: q, out [Hq, S, D] with strides {-, head, row}.
+int launch_sdpa_paged(b200kv_cache* c, int32_t seq, const void* q, const int64_t* qs, void* out, const int64_t* os, int Hq, int S,
+                      int dtype, float scale, int causal, cudaStream_t stream) {
+    DenseParams p{};
+    p.q = q, p.out = out;
+    for (int i = 0; i < 3; i++) p.qs[i] = qs[i], p.os[i] = os[i];
+    p.B = 1, p.Hq = Hq, p.Hkv = c->L.Hkv, p.S = S, p.T = (int)c->seqs[seq].len, p.D = c->L.D;
+    p.dtype = dtype, p.causal = causal, p.scale = scale;
+    p.src.pool = c->pool, p.src.table_row = c->d_table + (int64_t)seq * c->max_pages_per_seq;
+    p.src.page_bytes = c->L.page_bytes, p.src.len = c->seqs[seq].len, p.src.fmt = c->L.fmt, p.src.chunk_bytes = c->L.chunk_bytes;
+    p.src.kivi = fmt_is_kivi(c->L.fmt) ? 1 : 0, p.src.seq = seq;
+    if (p.src.kivi) p.src.kv = kivi_view(c);
+    const int64_t rows = (int64_t)Hq * S;
+    if (rows == 0) return B200KV_OK;
+    sdpa_dense_kernel<true><<<(unsigned)((rows + DENSE_WARPS - 1) / DENSE_WARPS), DENSE_WARPS * 32, 0, stream>>>(p);
     B200KV_CUDA(cudaGetLastError());
     return B200KV_OK;
 }
