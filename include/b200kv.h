@@ -206,6 +206,10 @@ int b200kv_trim(b200kv_cache* cache, int32_t seq, int64_t keep_last);
  * transformers/src/ops/dyn_kv_cache.rs:112-119 — on device, without the host round trip of
  * gpu/src/ops/dyn_kv_cache.rs:116-125).  Fails if len exceeds the current length. */
 int b200kv_truncate(b200kv_cache* cache, int32_t seq, int64_t len);
+/* The same for the sequences of a batch in one call (a decode loop rolls every sequence of a step back together, as
+ * examples/causal_llm/src/lib.rs:383-408 truncates every cache state of the model): lens[i] is the new length of seqs[i].
+ * All sequences are checked first; on KO none has changed. */
+int b200kv_truncate_many(b200kv_cache* cache, int32_t n_seqs, const int32_t* seqs, const int64_t* lens);
 
 /* Device-side copy of a sequence into a new one (OpStateFreeze::freeze / unfreeze keep the cache on
  * device, gpu/src/ops/dyn_kv_cache.rs:136-168). */

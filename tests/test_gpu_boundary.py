@@ -45,6 +45,11 @@ def test_no_device_allocation_after_create(kv, fmt):
     q1, qB = dev(normal(3, (1, Hq, 1, D)).astype(io)), dev(normal(4, (B, Hq, 1, D)).astype(io))
     qS = dev(normal(5, (2, Hq, 40, D)).astype(io))
     o1, oB, oS = torch.empty_like(q1), torch.empty_like(qB), torch.empty_like(qS)
+    # the first launch of a kernel may make the CUDA runtime load its code (device memory of the runtime's own): every
+    # kernel the calls below use is launched once, on the smallest case, before the first reading
+    cache.attend(seqs[:1], q1, out=o1)
+    cache.attend(seqs[:1], qS[:1], out=oS[:1])
+    cache.check()
     torch.cuda.synchronize()
     free0 = torch.cuda.mem_get_info()[0]
     cache.attend(seqs[:1], q1, out=o1)
@@ -164,7 +169,8 @@ def test_fork_of_a_sequence_longer_than_one_ring_slot(kv):
     Hkv, D, n = 1, 64, 64 * 8300
     cache = kv.KvCache("q4_0", Hkv, D, max_seqs=2, max_seq_tokens=n + 64)
     s = cache.new_seq()
-    x = torch.randn((1, Hkv, n, D), device="cuda").half()
+    x = torch.randn((1, Hkv, n // 2, D), device="cuda").half()
+    cache.append([s], x, x)  # (one append call may take up to a slot's worth of new pages: two calls)
     cache.append([s], x, x)
     f = cache.fork(s)
     q = torch.randn((2, 2, 1, D), device="cuda").half()

@@ -27,7 +27,7 @@ EXPORTS = [
     "b200kv_q40_packed_bytes", "b200kv_q40_pack", "b200kv_q40_scratch_bytes", "b200kv_q40_gemm", "b200kv_q40_check",
     "b200kv_rms_norm", "b200kv_silu_mul", "b200kv_add", "b200kv_argmax", "b200kv_gather_rows", "b200kv_cast",
     "b200kv_attend_window", "b200kv_trim", "b200kv_attend_rope", "b200kv_attend_q40", "b200kv_append_attend", "b200kv_q40_quantize", "b200kv_q40_gemm_quantized", "b200kv_q40_gemm_quantized_as",
-    "b200kv_q40_silu_mul_quantize", "b200kv_q40_add_rms_norm_quantize", "b200kv_workspace_bytes",
+    "b200kv_q40_silu_mul_quantize", "b200kv_q40_add_rms_norm_quantize", "b200kv_workspace_bytes", "b200kv_truncate_many",
 ]
 KERNEL_NAMES = {0: "table_scatter", 1: "append", 2: "decode", 3: "combine", 4: "export", 5: "sdpa_dense", 6: "prefill"}
 
@@ -75,6 +75,7 @@ def lib():
         L.b200kv_export.argtypes = [vp, i32, vp, i64p, vp, i64p, i32, vp]
         L.b200kv_export_codes.argtypes = [vp, i32, i32, vp, vp, vp]
         L.b200kv_truncate.argtypes = [vp, i32, i64]
+        L.b200kv_truncate_many.argtypes = [vp, i32, i32p, i64p]
         L.b200kv_fork.argtypes = [vp, i32, i32p, vp]
         L.b200kv_attend_static_scratch.argtypes = [vp, i32, i32p, i32, vp, i64p, vp, i64p, i32, C.c_float, vp]
         L.b200kv_export_kivi.argtypes = [vp, i32, i32, vp, vp, vp, vp, vp, vp]
@@ -268,6 +269,34 @@ class KvCache:
 
     def truncate(self, seq, length):
         _ck(lib().b200kv_truncate(self._h, seq, length))
+
+    def truncate_many(self, seqs, lengths):
+        """truncate() for a batch in one call: every sequence is checked before any changes."""
+        _ck(lib().b200kv_truncate_many(self._h, len(seqs), _ids(seqs), (C.c_int64 * len(seqs))(*[int(n) for n in lengths])))
+
+    def prepared_step(self, seqs, k_new, v_new, q, out, rollback_to=None, scale=None, causal=True):
+        """A zero-argument callable that runs append_attend(seqs, k_new, v_new, q, out=out) -- and, when `rollback_to`
+        (one length per sequence) is given, truncate_many(seqs, rollback_to) after it -- with every argument marshalled
+        once, here: what a serving loop that calls the C ABI directly pays per step, without Python's per-call packing.
+        The tensors must stay alive and in place; the current CUDA stream is looked up at every call."""
+        import torch
+
+        L, h, n = lib(), self._h, len(seqs)
+        ids = _ids(seqs)
+        ks, vs, qs, os_ = _strides(k_new, 3), _strides(v_new, 3), _strides(q, 3), _strides(out, 3)
+        kp, vp_, qp, op = (C.c_void_p(t.data_ptr()) for t in (k_new, v_new, q, out))
+        n_new, hq, dt, sc, ca = int(k_new.shape[2]), int(q.shape[1]), _dtype_code(q), C.c_float(scale or 0.0), int(causal)
+        lens = (C.c_int64 * n)(*[int(x) for x in rollback_to]) if rollback_to is not None else None
+        keep = (k_new, v_new, q, out)
+
+        def call(_keep=keep):
+            st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+            if L.b200kv_append_attend(h, n, ids, n_new, kp, ks, vp_, vs, hq, qp, qs, op, os_, dt, sc, ca, st) != 0:
+                raise B200KvError(L.b200kv_last_error().decode())
+            if lens is not None and L.b200kv_truncate_many(h, n, ids, lens) != 0:
+                raise B200KvError(L.b200kv_last_error().decode())
+
+        return call
 
     def trim(self, seq, keep_last):
         """Gives the pages before the last keep_last tokens back to the pool (sliding-window memory bound)."""

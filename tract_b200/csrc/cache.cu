@@ -807,6 +807,21 @@ int b200kv_truncate(b200kv_cache* c, int32_t seq, int64_t len) {
     return B200KV_OK;
 }
 
+// b200kv_truncate for a batch: every sequence is checked before any is changed.
+int b200kv_truncate_many(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, const int64_t* lens) {
+    if (validate_seqs(c, n_seqs, seqs) != B200KV_OK) return B200KV_KO;
+    if (!lens) return fail("null lengths");
+    for (int i = 0; i < n_seqs; i++) {
+        const SeqState& s = c->seqs[seqs[i]];
+        if (lens[i] < 0 || lens[i] > s.len)
+            return fail("cannot truncate sequence %d of %lld tokens to %lld", seqs[i], (long long)s.len, (long long)lens[i]);
+        if (lens[i] < s.start) return fail("cannot truncate sequence %d below token %lld: the pages before it were trimmed away", seqs[i], (long long)s.start);
+        if (fmt_is_kivi(c->L.fmt) && lens[i] != s.len) return fail("a KIVI cache cannot be truncated (blocks are frozen once quantised)");
+    }
+    for (int i = 0; i < n_seqs; i++) b200kv_truncate(c, seqs[i], lens[i]);
+    return B200KV_OK;
+}
+
 // Gives the pages that lie wholly before the last `keep_last` tokens back to the pool: the bounded memory of the
 // reference's sliding-window ring buffer (transformers/src/ops/window_kv_cache.rs:77-137) on a paged store.  Positions
 // keep counting from the sequence's real start; attention from now on sees tokens >= len - keep_last at most.

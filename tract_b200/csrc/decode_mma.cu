@@ -15,7 +15,11 @@
 // probabilities for V), so the products themselves are exact as in the CPU's f32 dequantise-then-dot.
 //
 // Each warp owns 16 of the 64 tokens of a page with its own running (max, sum, O) state; warps meet
-// once, at the end.  Chunks arrive through the same cp.async.bulk + mbarrier ring as the SIMT kernel.
+// once, at the end.  Chunks arrive by cp.async.bulk into a ring of stages, one mbarrier per stage; one
+// CTA barrier per page hands the stage back to thread 0, which refills it at once with a page id it
+// fetched from the page table one iteration earlier (the table read is off the critical path).
+// (Measured against a ring with full / empty barrier pairs, no CTA barrier and a refill one page late:
+// that lost 7 % on the 4-bit cache, because the ring runs one stage shallower.)
 // Semantics: transformers/src/ops/flash_sdpa.rs:239-341 with S = 1; replaces the decode use of
 // cuda/src/kernels/cu/flash_attn.cu.
 #include <algorithm>
@@ -43,7 +47,7 @@ struct MGeo {
 };
 
 // Shared memory after the stage ring: q as f32 [8][128], then the barriers.
-constexpr size_t MMA_TAIL = 8 * MD * 4 + 32 * 4 + 64;
+constexpr size_t MMA_TAIL = 8 * MD * 4 + 32 * 4 + 128;
 
 template <int FMT>
 __global__ void __launch_bounds__(128, MGeo<FMT>::MIN_CTAS) decode_mma_kernel(DecodeParams p, const __grid_constant__ InlineBatch ib) {
@@ -62,7 +66,7 @@ __global__ void __launch_bounds__(128, MGeo<FMT>::MIN_CTAS) decode_mma_kernel(De
     extern __shared__ __align__(1024) uint8_t stages[];
     float* q_s = (float*)(stages + (size_t)NS * Gm::STAGE);  // [8][128]
     float* qsum_s = q_s + 8 * MD;                             // [8 heads][4 blocks]
-    uint64_t* bars = (uint64_t*)(qsum_s + 32);
+    uint64_t* bars = (uint64_t*)(qsum_s + 32);     // [NS] the bytes of the stage have landed
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int r = lane >> 2, c = lane & 3;
@@ -72,9 +76,9 @@ __global__ void __launch_bounds__(128, MGeo<FMT>::MIN_CTAS) decode_mma_kernel(De
     const int ng = min(8, p.G - g0);  // q heads of this CTA
     const int n_tiles = w.n_pages;
 
-    auto issue = [&](int i) {  // thread 0 only
+    const int32_t* trow_p = p.table + (int64_t)w.trow * p.max_pages_per_seq + w.page_begin;
+    auto issue = [&](int i, int32_t pg) {  // thread 0 only
         int st = i % NS;
-        int32_t pg = p.table[(int64_t)w.trow * p.max_pages_per_seq + w.page_begin + i];
         if (pg < 0 || pg >= p.n_pages) {
             atomicOr(p.status, STATUS_PAGE_OOB);
             pg = 0;
@@ -85,12 +89,19 @@ __global__ void __launch_bounds__(128, MGeo<FMT>::MIN_CTAS) decode_mma_kernel(De
     };
     grid_dependency_wait();    // the append that precedes this launch has written its pages
     grid_launch_dependents();  // the combine pass may be scheduled; it waits for this grid before reading partials
+    int32_t pg_next = 0;  // thread 0: id of the next page to request
     if (tid == 0) {
         for (int s = 0; s < NS; s++) mbar_init(&bars[s], 1);
         mbar_fence_init();
         // start streaming right away; the other threads first meet the barriers after the __syncthreads below
         const bool stalled = (int)blockIdx.x == p.stall_item && blockIdx.y == 0 && blockIdx.z == 0;  // test hook, see DecodeParams
-        for (int i = 0; i < NS && i < n_tiles && !stalled; i++) issue(i);
+        int32_t first[NS];
+#pragma unroll
+        for (int i = 0; i < NS; i++) first[i] = i < n_tiles ? trow_p[i] : 0;  // the loads travel together
+#pragma unroll
+        for (int i = 0; i < NS; i++)
+            if (i < n_tiles && !stalled) issue(i, first[i]);
+        if (NS < n_tiles) pg_next = trow_p[NS];
     }
     // q of the group as f32 in shared memory, rows beyond the group zero
     for (int idx = tid; idx < 8 * MD; idx += 128) {
@@ -153,32 +164,30 @@ __global__ void __launch_bounds__(128, MGeo<FMT>::MIN_CTAS) decode_mma_kernel(De
     float m_run[2] = {-INFINITY, -INFINITY};
     float l_part[2] = {0.f, 0.f};  // this thread's share of the row sums (its two token rows only)
     float o[8][4];                 // O^T fragments: m-tile j = channels 16j..16j+15, columns = heads 2c, 2c+1
-    float ob[QUANT ? 4 : 1][4];    // offset term of the V side, one per block
+    // offset term of the V side, one per block: rows r of the constant operand only (rows r + 8 give the same value, for
+    // Q4_0 16 times it: exact either way), so the other half of each product lands in two registers nobody reads
+    float ob[QUANT ? 4 : 1][2];
+    float ob_unused0 = 0.f, ob_unused1 = 0.f;
 #pragma unroll
     for (int j = 0; j < 8; j++)
 #pragma unroll
         for (int e = 0; e < 4; e++) o[j][e] = 0.f;
 #pragma unroll
-    for (int b = 0; b < (QUANT ? 4 : 1); b++)
-#pragma unroll
-        for (int e = 0; e < 4; e++) ob[b][e] = 0.f;
+    for (int b = 0; b < (QUANT ? 4 : 1); b++) ob[b][0] = ob[b][1] = 0.f;
     bool failed = false;
 
     const int tA = warp * 16 + r, tB = tA + 8;  // the two token rows of this thread's C fragments
 
     for (int i = 0; i < n_tiles; i++) {
         const int st = i % NS;
+        // (warp-uniform: every lane waits on the same phase)  A warp whose wait ran out still walks on to the CTA barrier
+        // below, where every warp learns of it and the whole CTA leaves the loop together
         const bool ok = mbar_wait_bounded(&bars[st], (uint32_t)((i / NS) & 1), p.wait_ns);
-        if (__syncthreads_or(!ok)) {
-            if (tid == 0) atomicOr(p.status, STATUS_WAIT_EXPIRED);
-            failed = true;
-            break;
-        }
         const uint8_t* Ks = stages + (size_t)st * Gm::STAGE;
         const uint8_t* Vs = Ks + Gm::CHUNK;
         const int n_valid = min(PAGE_TOKENS, w.len - (w.page_begin + i) * PAGE_TOKENS);
         const int n_first = max(0, w.first - (w.page_begin + i) * PAGE_TOKENS);  // slots below it lie before the window
-        if (warp * 16 < n_valid) {  // warp-uniform: this warp has at least one live token in the tile
+        if (ok && warp * 16 < n_valid) {  // warp-uniform: this warp has at least one live token in the tile
             const bool vA = tA < n_valid && tA >= n_first, vB = tB < n_valid && tB >= n_first;
 
             // ================= scores: S^T[16 tokens x 8 heads] = K . Q^T =================
@@ -249,7 +258,8 @@ __global__ void __launch_bounds__(128, MGeo<FMT>::MIN_CTAS) decode_mma_kernel(De
                 for (int j = 0; j < 8; j++) o[j][0] *= al0, o[j][1] *= al1, o[j][2] *= al0, o[j][3] *= al1;
                 if (QUANT) {
 #pragma unroll
-                    for (int b = 0; b < (QUANT ? 4 : 1); b++) ob[b][0] *= al0, ob[b][1] *= al1, ob[b][2] *= al0, ob[b][3] *= al1;
+                    for (int b = 0; b < (QUANT ? 4 : 1); b++) ob[b][0] *= al0, ob[b][1] *= al1;
+                    ob_unused0 = ob_unused1 = 0.f;  // kept finite
                 }
             }
 
@@ -322,7 +332,7 @@ __global__ void __launch_bounds__(128, MGeo<FMT>::MIN_CTAS) decode_mma_kernel(De
                 constexpr uint32_t OFFS_HI = FMT == B200KV_FMT_Q4_0 ? 0x00800080u : OFFS_FRAG;  // rows r + 8 of Q4_0: 16 * 8
                 const uint32_t ofs[4] = {OFFS_FRAG, OFFS_HI, OFFS_FRAG, OFFS_HI};
 #pragma unroll
-                for (int b = 0; b < 4; b++) mma_f16(ob[b], ofs, pb[b][0], pb[b][1]);
+                for (int b = 0; b < 4; b++) mma_f16(ob[b][0], ob[b][1], ob_unused0, ob_unused1, ofs, pb[b][0], pb[b][1]);
             } else {
                 // lane -> address of one 8x8 matrix row of V: token (lane & 7) + 8 * bit4, channel half = bit 3
                 const int lt = warp * 16 + (lane & 7) + ((lane >> 4) & 1) * 8;
@@ -359,13 +369,20 @@ __global__ void __launch_bounds__(128, MGeo<FMT>::MIN_CTAS) decode_mma_kernel(De
                 }
             }
         }
-        __syncthreads();  // every warp is done with stage st
-        if (tid == 0 && i + NS < n_tiles) issue(i + NS);
+        if (__syncthreads_or(!ok)) {  // every warp is done with stage st; a wait that ran out anywhere ends the loop for all
+            failed = true;
+            break;
+        }
+        if (tid == 0 && i + NS < n_tiles) {
+            issue(i + NS, pg_next);
+            if (i + NS + 1 < n_tiles) pg_next = trow_p[i + NS + 1];
+        }
     }
 
     // ---- merge the four warps and publish the partial of this split ----
     const int64_t pbase = ((int64_t)blockIdx.x * p.Hkv + kvh) * p.G + g0;
     if (failed) {
+        if (tid == 0) atomicOr(p.status, STATUS_WAIT_EXPIRED);
         for (int idx = tid; idx < ng * MD; idx += 128) p.part_o[(pbase + idx / MD) * MD + idx % MD] = 0.f;
         if (tid < ng) p.part_ml[(pbase + tid) * 2] = -INFINITY, p.part_ml[(pbase + tid) * 2 + 1] = 0.f;
         return;
@@ -384,7 +401,8 @@ __global__ void __launch_bounds__(128, MGeo<FMT>::MIN_CTAS) decode_mma_kernel(De
             constexpr float UNDO = TWO24 / PSCALE;
             const int b = j >> 1;
             constexpr float UNDO_HI = FMT == B200KV_FMT_Q4_0 ? UNDO / 16.f : UNDO;
-            v0 = (v0 - ob[b][0]) * UNDO, v1 = (v1 - ob[b][1]) * UNDO, v2 = (v2 - ob[b][2]) * UNDO_HI, v3 = (v3 - ob[b][3]) * UNDO_HI;
+            constexpr float HI = FMT == B200KV_FMT_Q4_0 ? 16.f : 1.f;  // rows r + 8 of Q4_0 carry 16 * code and 16 * offset
+            v0 = (v0 - ob[b][0]) * UNDO, v1 = (v1 - ob[b][1]) * UNDO, v2 = (v2 - HI * ob[b][0]) * UNDO_HI, v3 = (v3 - HI * ob[b][1]) * UNDO_HI;
         }
         float* base = om + (warp * 8 + 2 * c) * MD + 16 * j + r;
         base[0] = v0, base[MD] = v1, base[8] = v2, base[MD + 8] = v3;

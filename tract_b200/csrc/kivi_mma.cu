@@ -16,7 +16,10 @@
 //           sum_t p_t m_t (exact weights) are kept per head.  Centring on the code of zero makes the rounding of a
 //           weight meet the value itself and not its distance from lo_t, which an outlier in the row makes large;
 // A CTA walks a run of 64-token pages of one (sequence, kv head); the four arrays of a page (K codes, V codes,
-// K parameters, V parameters) arrive by cp.async.bulk into one stage of a ring.  Sinks, the f32 residual block and
+// K parameters, V parameters) arrive by cp.async.bulk into one stage of a ring; one CTA barrier per page hands the
+// stage back to thread 0, which refills it at once with a page id it fetched from the page table one iteration
+// earlier.  (A ring with full / empty barrier pairs, a pair-of-warps barrier and a refill one page late measured 20 %
+// slower: with three stages, one of which the look-ahead of the q' rebuild holds, a late refill leaves nothing in flight.)  Sinks, the f32 residual block and
 // the value tokens that go with it are left to the CUDA-core formulation (kivi_simt.cuh), run by a few extra CTAs of
 // the same grid, which publish them as one more partial per sequence.
 #include <algorithm>
@@ -71,7 +74,7 @@ __global__ void __launch_bounds__(128, KGeo<BITS>::CTAS) kivi_mma_kernel(KiviMma
     uint4* qp_s = (uint4*)(stages + (size_t)KM_NS * KM_STAGE);  // B fragments of q' = q * scale: {hi k0..1, hi k2..3, lo k0..1, lo k2..3}
     float* bias_s = (float*)(qp_s + 2 * 2 * 8 * 32);            // q . lo of each block, in two halves of the channels
     float* q_s = (float*)(qp_s + 2 * 8 * 32);                   // [8][128] f32 during the set-up only: the second q' buffer, first written after a barrier
-    uint64_t* bars = (uint64_t*)(bias_s + 2 * 2 * 2 * 8);
+    uint64_t* bars = (uint64_t*)(bias_s + 2 * 2 * 2 * 8);  // [NS] the bytes of the stage have landed
 
     const KiviView& v = p.v;
     const int kvh_simt = blockIdx.y;
@@ -87,9 +90,9 @@ __global__ void __launch_bounds__(128, KGeo<BITS>::CTAS) kivi_mma_kernel(KiviMma
     const int pg_lo = (int)((int64_t)n_pg * split / p.n_splits), pg_hi = (int)((int64_t)n_pg * (split + 1) / p.n_splits);
     const int n_tiles = pg_hi - pg_lo;
 
-    auto issue = [&](int i) {  // thread 0 only
+    const int32_t* trow_p = v.table + (int64_t)seq * v.max_pages_per_seq + pg_lo;
+    auto issue = [&](int i, int32_t pg) {  // thread 0 only
         const int st = i % KM_NS;
-        int32_t pg = v.table[(int64_t)seq * v.max_pages_per_seq + pg_lo + i];
         if (pg < 0 || pg >= v.n_pages) {
             atomicOr(p.status, STATUS_PAGE_OOB);
             pg = 0;
@@ -113,10 +116,17 @@ __global__ void __launch_bounds__(128, KGeo<BITS>::CTAS) kivi_mma_kernel(KiviMma
         kivi_simt_body<KM_D>(d, ib, *reinterpret_cast<KiviSimtSmem<KM_D>*>(stages), e / nzs, kvh_simt, e % nzs);
         return;
     }
+    int32_t pg_next = 0;  // thread 0: id of the next page to request
     if (tid == 0) {
         for (int s = 0; s < KM_NS; s++) mbar_init(&bars[s], 1);
         mbar_fence_init();
-        for (int i = 0; i < KM_NS && i < n_tiles; i++) issue(i);
+        int32_t first[KM_NS];
+#pragma unroll
+        for (int i = 0; i < KM_NS; i++) first[i] = i < n_tiles ? trow_p[i] : 0;  // the loads travel together
+#pragma unroll
+        for (int i = 0; i < KM_NS; i++)
+            if (i < n_tiles) issue(i, first[i]);
+        if (KM_NS < n_tiles) pg_next = trow_p[KM_NS];
     }
     // q of the group, rounded to the f16 operand the tensor cores will see; rows beyond the group zero
     for (int idx = tid; idx < 8 * KM_D; idx += 128) {
@@ -180,15 +190,12 @@ __global__ void __launch_bounds__(128, KGeo<BITS>::CTAS) kivi_mma_kernel(KiviMma
     {  // page 0 is built before the loop, page i + 1 while page i is consumed: one barrier per page
         const bool ok0 = n_tiles == 0 || mbar_wait_bounded(&bars[0], 0);
         if (n_tiles && ok0) build(0);
-        if (__syncthreads_or(!ok0)) {
-            if (tid == 0) atomicOr(p.status, STATUS_WAIT_EXPIRED);
-            failed = true;
-        }
+        failed = __syncthreads_or(!ok0) != 0;
     }
     for (int i = 0; i < n_tiles && !failed; i++) {
         const int st = i % KM_NS;
         bool ok = true;
-        if (i + 1 < n_tiles) {
+        if (i + 1 < n_tiles) {  // a warp whose wait ran out walks on to the CTA barrier below, where every warp learns of it
             ok = mbar_wait_bounded(&bars[(i + 1) % KM_NS], (uint32_t)(((i + 1) / KM_NS) & 1));
             if (ok) build(i + 1);
         }
@@ -298,16 +305,19 @@ __global__ void __launch_bounds__(128, KGeo<BITS>::CTAS) kivi_mma_kernel(KiviMma
             }
         }
         if (__syncthreads_or(!ok)) {  // every warp is done with stage st and has built its share of the next page
-            if (tid == 0) atomicOr(p.status, STATUS_WAIT_EXPIRED);
             failed = true;
             break;
         }
-        if (tid == 0 && i + KM_NS < n_tiles) issue(i + KM_NS);
+        if (tid == 0 && i + KM_NS < n_tiles) {
+            issue(i + KM_NS, pg_next);
+            if (i + KM_NS + 1 < n_tiles) pg_next = trow_p[i + KM_NS + 1];
+        }
     }
 
     // ---- merge the four warps and publish the partial of this split ----
     const int64_t pbase = (((int64_t)b * p.part_stride + p.part_off + split) * v.H + kvh) * p.G + g0;
     if (failed) {
+        if (tid == 0) atomicOr(p.status, STATUS_WAIT_EXPIRED);
         for (int idx = tid; idx < ng * KM_D; idx += 128) p.part_o[(pbase + idx / KM_D) * KM_D + idx % KM_D] = 0.f;
         if (tid < ng) p.part_ml[(pbase + tid) * 2] = -INFINITY, p.part_ml[(pbase + tid) * 2 + 1] = 0.f;
         return;

@@ -158,9 +158,6 @@ __device__ inline float fast_exp2(float x) {
 }
 
 
-__device__ inline void mbar_arrive(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
 __device__ inline bool mbar_test(uint64_t* bar, uint32_t parity) {  // one look, never suspends
     uint32_t ok;
     asm volatile(

@@ -79,9 +79,10 @@ class HeadShardedAttention:
         """k_new / v_new: the FULL [B, Hkv, S, D] tensors (replicated input); the local head slice is a strided view."""
         self.cache.append(seqs, k_new[:, self.kv_lo:self.kv_hi], v_new[:, self.kv_lo:self.kv_hi])
 
-    def attend(self, seqs, q, causal=True, scale=None):
-        """q: the FULL [B, Hq, S, D]; returns the full output on every rank."""
+    def attend(self, seqs, q, causal=True, scale=None, buffer=None):
+        """q: the FULL [B, Hq, S, D]; returns the full output on every rank.  `buffer`: a gather_buffer() to reuse from
+        step to step (none is allocated then)."""
         b, _, s, d = q.shape
-        buf = gather_buffer(self._torch, self.world, b, self.q_hi - self.q_lo, s, d, q.dtype, q.device)
+        buf = buffer if buffer is not None else gather_buffer(self._torch, self.world, b, self.q_hi - self.q_lo, s, d, q.dtype, q.device)
         self.cache.attend(seqs, q[:, self.q_lo:self.q_hi], scale=scale, causal=causal, out=buf[self.rank])
         return all_gather_heads(buf, self.rank, self.group)
