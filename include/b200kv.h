@@ -220,16 +220,19 @@ int b200kv_fork(b200kv_cache* cache, int32_t seq, int32_t* new_seq_out, void* st
 int b200kv_check(b200kv_cache* cache, void* stream);
 
 /* Decode attention (one query per sequence: the n_new == 1 case of b200kv_attend, same arguments and
- * result) that performs no device allocation, for callers that cannot afford one while a step runs: a
- * server that has given every free byte of HBM to its page pools, a runtime whose device arena was sized
- * once and may not grow, or a latency-critical loop in which the device-wide synchronisation implied by
- * cudaMalloc / cudaFree would stall the other streams.  b200kv_attend keeps its split-KV partials in a
- * workspace that it re-allocates when a call needs more of them than any earlier call; this entry point
- * keeps them in a fixed 8 MiB device array inside the library (held by every GPU that loads the library,
- * from load to exit) and calls neither cudaMalloc nor cudaFree nor any allocating library routine.
+ * result) whose split-KV partials live in no allocation at all, for callers that cannot allocate device
+ * memory for them: a server that has given every free byte of HBM to page pools it made itself before it
+ * loaded this library, a runtime whose device arena was sized once and whose allocator hook refuses
+ * anything else, or a latency-critical loop in which the device-wide synchronisation implied by
+ * cudaMalloc / cudaFree would stall the other streams.  b200kv_attend keeps the partials in the workspace
+ * b200kv_create allocates; this entry point keeps them in a fixed 8 MiB device array inside the library
+ * (held by every GPU that loads the library, from load to exit) and calls neither cudaMalloc nor cudaFree
+ * nor any allocating library routine.
  *   - Limit: page runs x n_kv_heads x (n_q_heads / n_kv_heads) x (head_dim + 2) floats <= 2 Mi floats, where
  *     page runs is the number of splits of the batch (at most 64 per sequence).  A call beyond the limit
  *     fails with a message that states both numbers; nothing is enqueued.
+ *   - Not served (refused during validation, nothing enqueued): KIVI caches, which have decode kernels of
+ *     their own, and sequences whose front pages b200kv_trim gave back.  b200kv_attend serves both.
  *   - The first call on a device looks up the device address of the array (cudaGetSymbolAddress, with that
  *     device current); make that first call before any stream capture begins.
  *   - All calls on one device share the array, and a call leaves its partials behind; each call overwrites
@@ -329,12 +332,17 @@ int b200kv_profile_read(b200kv_cache* cache, int32_t max_records, int32_t* kerne
  *      CudaFlashAttention for an Sdpa node that is not fused with a cache) ----
  * q [B, Hq, S, D], k / v [B, Hkv, T, D], out [B, Hq, S, D]; strides {batch, head, row} in elements.
  * mask (may be NULL) is additive, [Mb, Mh, S, T] with Mb in {1, B} and Mh in {1, Hq}, strides
- * {batch, head, row, col} (0 to broadcast), element type mask_dtype.  Any D <= 256. */
+ * {batch, head, row, col} (0 to broadcast), element type mask_dtype.  Any D <= 256.  f16 / bf16 tensors at head_dim 64 or 128
+ * whose rows start on 16-byte boundaries run on the tensor cores (tcgen05); everything else on a generic CUDA-core kernel. */
 int b200kv_sdpa(const void* q, const int64_t q_strides[3], const void* k, const int64_t k_strides[3], const void* v,
                 const int64_t v_strides[3], const void* mask, const int64_t mask_strides[4], int32_t mask_dtype,
                 void* out, const int64_t out_strides[3], int32_t batch, int32_t n_q_heads, int32_t n_kv_heads,
                 int32_t q_len, int32_t kv_len, int32_t head_dim, int32_t dtype, float scale, int32_t causal,
                 void* stream);
+
+/* b200kv_sdpa has no cache handle to carry a status word: this synchronises `stream` and reports (once) whether a bounded
+ * wait of a b200kv_sdpa call on the current device expired (the analogue of b200kv_check). */
+int b200kv_sdpa_check(void* stream);
 
 #ifdef __cplusplus
 }

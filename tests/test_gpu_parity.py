@@ -647,6 +647,46 @@ def test_sdpa_reference_kernel_test_shapes(kv, b, hq, hkv, p, s, d, causal, with
     assert rel_err(out.float().cpu().numpy(), want.astype(np.float32)) <= TOL["f16"]
 
 
+@pytest.mark.parametrize("io,B,Hq,Hkv,P,S,D,mode", [
+    ("f16", 2, 8, 2, 400, 300, 128, "causal"),       # keys not a multiple of 64, past + chunk
+    ("f16", 1, 32, 8, 0, 1100, 128, "causal"),       # enough query tiles for the double-tile CTAs
+    ("bf16", 2, 8, 8, 100, 200, 128, "none"),        # no grouping, no mask at all
+    ("f16", 2, 6, 2, 37, 150, 64, "causal"),         # head_dim 64, G = 3
+    ("bf16", 1, 16, 4, 0, 513, 64, "mask"),
+    ("f16", 2, 8, 2, 130, 90, 128, "mask"),          # additive mask broadcast over the batch, with -inf stripes
+    ("f16", 1, 4, 1, 64, 64, 128, "mask_bh"),        # a mask of its own for every batch entry and head
+    ("f16", 3, 8, 2, 2000, 1, 128, "causal"),        # one query per sequence through the same kernel
+])
+def test_sdpa_on_the_tensor_cores(kv, io, B, Hq, Hkv, P, S, D, mode):
+    # the lone Sdpa at the sizes of the reference's kernel bench (cuda/benches/cuda_flash.rs:84-110) and smaller ragged
+    # ones: dense K / V given as strided windows ([B, T, Hkv, D] storage seen as [B, Hkv, T, D]), masks with -inf
+    T = P + S
+    q = normal(21, (B, Hq, S, D), scale=0.5).astype(np_dtype(io))
+    k = normal(22, (B, Hkv, T, D), scale=0.5).astype(np_dtype(io))
+    v = normal(23, (B, Hkv, T, D), scale=0.5).astype(np_dtype(io))
+    mask = None
+    if mode.startswith("mask"):
+        shape = (B, Hq, S, T) if mode == "mask_bh" else (1, 1, S, T)
+        mask = normal(24, shape).astype(np.float32)
+        mask[..., :, 5:T:7] = -np.inf         # whole key columns masked out
+        # a query that sees key 0 and the second half (a row whose first 32-key tile is masked out entirely comes out as
+        # NaN from the reference's tile recurrence, exp(-inf - -inf): not a case to hold a kernel to)
+        mask[..., 3, 1: T // 2] = -np.inf
+        mask = mask.astype(np.float16) if io == "f16" else mask
+    dk = to_dev(np.ascontiguousarray(np.swapaxes(k, 1, 2))).transpose(1, 2)  # [B, Hkv, T, D] view of [B, T, Hkv, D]
+    dv = to_dev(np.ascontiguousarray(np.swapaxes(v, 1, 2))).transpose(1, 2)
+    out = kv.sdpa(to_dev(q), dk, dv, mask=to_dev(mask) if mask is not None else None, causal=mode == "causal")
+    kv.sdpa_check()
+    if io == "bf16":
+        want = oracle.flash_sdpa(q.astype(np.float32), k.astype(np.float32), v.astype(np.float32),
+                                 mask=mask.astype(np.float32) if mask is not None else None, causal=mode == "causal", threads=8)
+        err = rel_err_bf16(to_np(out, io).astype(np.float32), want)
+    else:
+        want = oracle.flash_sdpa(q, k, v, mask=mask, causal=mode == "causal", threads=8)
+        err = rel_err(to_np(out, io).astype(np.float32), want.astype(np.float32))
+    assert err <= TOL[io], err
+
+
 def test_sdpa_property_sweep(kv):
     # strategy of test-rt/suite-unit/src/sdpa.rs:94-142 (values k/8, B 1-2, GQA repeat 1-4, kv heads 1-4,
     # P 0-4, S 2-4, optional scale, causal or additive mask broadcast over b / h), embed dims of the CPU

@@ -27,7 +27,7 @@ EXPORTS = [
     "b200kv_q40_packed_bytes", "b200kv_q40_pack", "b200kv_q40_scratch_bytes", "b200kv_q40_gemm", "b200kv_q40_check",
     "b200kv_rms_norm", "b200kv_silu_mul", "b200kv_add", "b200kv_argmax", "b200kv_gather_rows", "b200kv_cast",
     "b200kv_attend_window", "b200kv_trim", "b200kv_attend_rope", "b200kv_attend_q40", "b200kv_append_attend", "b200kv_q40_quantize", "b200kv_q40_gemm_quantized", "b200kv_q40_gemm_quantized_as",
-    "b200kv_q40_silu_mul_quantize", "b200kv_q40_add_rms_norm_quantize", "b200kv_workspace_bytes", "b200kv_truncate_many",
+    "b200kv_q40_silu_mul_quantize", "b200kv_q40_add_rms_norm_quantize", "b200kv_workspace_bytes", "b200kv_truncate_many", "b200kv_sdpa_check",
 ]
 KERNEL_NAMES = {0: "table_scatter", 1: "append", 2: "decode", 3: "combine", 4: "export", 5: "sdpa_dense", 6: "prefill"}
 
@@ -558,6 +558,12 @@ def rope(x, cos, sin, out=None):
         _ck(lib().b200kv_rope(x.data_ptr(), _strides(x, 3), cos.data_ptr(), sin.data_ptr(), rs, out.data_ptr(), _strides(out, 3),
                               x.shape[0], x.shape[1], x.shape[2], x.shape[3], _dtype_code(x), _stream()))
     return out
+
+
+def sdpa_check():
+    """Synchronises the current stream and raises if a bounded wait of an sdpa() call on this device expired."""
+    lib().b200kv_sdpa_check.argtypes = [C.c_void_p]
+    _ck(lib().b200kv_sdpa_check(_stream()))
 
 
 def sdpa(q, k, v, mask=None, scale=None, causal=False):

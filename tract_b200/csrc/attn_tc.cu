@@ -1,0 +1,636 @@
+// Flash attention of many queries on the 5th-generation tensor cores (tcgen05 + TMEM) for every source the specialised
+// f16 / bf16 head_dim-128 kernel of prefill_tc.cu does not read: block-quantised pages (Q8_1, Q4_0), head_dim 64, and
+// dense strided K / V tensors with an optional additive mask (the lone Sdpa node).
+//
+// Replaces cuda/src/kernels/cu/flash_attn.cu (`attention_kernel`, instantiated for head_dim 64 and 128, :587-627; Ampere
+// mma.sync, one q-head per CTA) behind CudaFlashAttn::dispatch_eval (cuda/src/kernels/flash_attn.rs:82-189), and gives
+// the quantised caches what the reference does by rebuilding the whole f32 cache for every chunk
+// (transformers/src/ops/quant_dyn_kv_cache.rs:432-449): here a chunk of queries walks the pages it needs and nothing
+// else, and each page is widened to 16 bits in shared memory on its way to the tensor cores.
+// Semantics: transformers/src/ops/flash_sdpa.rs:239-341 (scale, additive mask or causal aligned bottom-right, f32
+// accumulation); masks as transformers/src/ops/sdpa.rs:183-196 adds them.
+//
+// The pipeline is that of prefill_tc.cu: a query tile is 128 rows = (query, head-of-group) pairs of one (sequence, kv
+// head); per tile and per 64 keys  S = Q . K^T  (tcgen05.mma, operands in shared memory with the 128-byte swizzle, S
+// double-buffered in TMEM), softmax by two threads per row (tcgen05.ld, exponentials in the log2 domain against a
+// lazily raised reference maximum, P written over S with tcgen05.st as a 16-bit value plus its rounding remainder),
+// O += P . V  (A from TMEM, V as an MN-major operand).  What differs is who fills the K / V operand rings:
+//   SRC_PAGES16  a copy warp: one untiled cp.async.bulk per chunk, the page bytes ARE the operand tile (head_dim 64 here)
+//   SRC_PAGESQ   the raw quantised chunk pair of a page lands (cp.async.bulk) in a small ring; two converter warps turn
+//                codes * f32(f16 scale) (q8_1.rs:50-63, q4_0.rs:82-95: exact in f32) into 16-bit rows of the operand tile,
+//                and the first of them requests the raw pages
+//   SRC_DENSE    two loader warps gather 16-byte units of the strided K / V rows with cp.async straight into the
+//                swizzled tile, two pages in flight; rows past the end of K / V are zero-filled
+// Every wait is bounded; on expiry the CTA flags the status word, every role runs to the end of its loop without
+// waiting any more, the CTA frees its TMEM and returns.
+#include <cmath>
+
+#include "tc_common.cuh"
+
+namespace b200kv {
+
+constexpr int AM = 128;            // rows of a query tile
+constexpr int A_SM_THREADS = 256;  // softmax threads per query tile
+constexpr int A_FILL_THREADS = 64; // converter / loader threads
+constexpr int A_XCHG = 2 * AM + 8; // per tile and page parity: the two half-row maxima of every row, one flag per softmax warp
+constexpr float A_SKIP_FRACTION = 0.125f;
+enum { SRC_PAGES16 = 0, SRC_PAGESQ = 1, SRC_DENSE = 2 };
+
+template <int NQ, int D, int SRC>
+struct AGeo {
+    static constexpr int PLANES = D / 64;             // 128-byte wide column slabs of a row
+    static constexpr int CHUNK = PAGE_TOKENS * D * 2; // bytes of one K (or V) operand tile: 64 keys
+    static constexpr int QBYTES = AM * D * 2;
+    static constexpr bool FILL = SRC != SRC_PAGES16;
+    static constexpr int NK = NQ == 2 ? (D == 128 && SRC == SRC_PAGESQ ? 3 : 4) : 3;  // K stages
+    static constexpr int NV = NQ == 2 ? (D == 128 && SRC == SRC_PAGESQ ? 4 : 5) : 3;  // V stages
+    static constexpr int NR = 2;                                                          // raw stages (SRC_PAGESQ)
+    static constexpr int RAW_STAGE = SRC == SRC_PAGESQ ? 2 * (PAGE_TOKENS * D + PAGE_TOKENS * (D / 32) * 2) : 0;  // a Q8_1 chunk pair
+    // softmax threads, one MMA warp per tile, then either the copy warp (16-bit pages) or the two converter / loader warps
+    static constexpr int THREADS = NQ * A_SM_THREADS + 32 * NQ + (FILL ? A_FILL_THREADS : 32);
+    static constexpr int N_BARS = 2 * NK + 2 * NV + 6 * NQ + 2 * NR;
+    static constexpr uint32_t COL_S = D, COLS_PER_TILE = 256;  // TMEM: O in columns 0 .. D-1, the two S buffers after it
+    static constexpr size_t SMEM = (size_t)NQ * QBYTES + (size_t)(NK + NV) * CHUNK + (size_t)NR * RAW_STAGE + N_BARS * 8 + 32 +
+                                   NQ * 2 * A_XCHG * 4;
+};
+
+struct AttnParams {
+    const void* q;
+    void* out;
+    int64_t qb, qh, qs, ob, oh, os;
+    int* status;
+    int32_t Hkv, G, S, causal, is_bf16;
+    float scale, inv_scale, skip_fraction;
+    // paged sources
+    const uint8_t* pool;
+    const int32_t* table;
+    const int32_t* desc;  // per batch entry: {table row, cached length}
+    int64_t page_bytes;
+    int32_t n_pages, max_pages_per_seq, fmt, chunk_bytes;
+    // dense source: K / V [B, Hkv, T, D] with strides {batch, head, row} in elements, T keys
+    const void* k;
+    const void* v;
+    int64_t kb, kh, ks, vb, vh, vs;
+    int32_t T;
+    // additive mask [Mb, Mh, S, T], strides {batch, head, row, column} in elements (0 to broadcast); null: none
+    const void* mask;
+    int64_t mb, mh, mq, mk;
+    int32_t mask_dtype;
+};
+
+__device__ inline void cp_async16_zfill(void* dst_smem, const void* src, bool live) {
+    const uint32_t n = live ? 16u : 0u;  // 0 source bytes: the 16 destination bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst_smem)), "l"(__cvta_generic_to_global(src)), "r"(n) : "memory");
+}
+__device__ inline void cp_async_commit_group() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ inline void cp_async_wait_group() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ inline void fence_async_proxy() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// One K or V chunk of a block-quantised page (as it lies in the pool) -> the 16-bit operand tile: thread t of 64 takes the
+// 8 channels of unit u = t % (D / 8) of every (64 / (D / 8))-th token.  Rows from n_valid on are zero-filled.
+template <int D>
+__device__ inline void convert_chunk(const uint8_t* raw, uint8_t* dst, int fmt, int kv, bool is_bf16, int n_valid, int t) {
+    constexpr int UNITS = D / 8, TLN = A_FILL_THREADS / UNITS;
+    const int u = t % UNITS, tl = t / UNITS;
+    const int ch0 = 8 * u, blk = ch0 / 32;
+    const bool perm = v_permuted(fmt, D, kv);
+    const __half* scales = (const __half*)(raw + PAGE_TOKENS * fmt_row_bytes(fmt, D));
+    int pos[8];  // permuted rows: where the codes of this thread's 8 channels sit
+    if (perm) {
+#pragma unroll
+        for (int e = 0; e < 8; e++) pos[e] = code_pos(fmt, D, kv, ch0 + e);
+    }
+    const int nib = perm ? code_nibble(fmt, D, kv, ch0) : (ch0 % 32) / 16;  // Q4_0: the same for all 8 channels of a unit
+    const int pos0 = fmt == B200KV_FMT_Q8_1 ? ch0 : (ch0 / 32) * 16 + ch0 % 16;  // natural rows: 8 contiguous bytes
+#pragma unroll 2
+    for (int tt = 0; tt < PAGE_TOKENS / TLN; tt++) {
+        const int tok = tt * TLN + tl;
+        uint32_t w[4] = {0u, 0u, 0u, 0u};
+        if (tok < n_valid) {
+            const float sc = __half2float(scales[scale_index(fmt, D, kv, tok, blk)]);
+            uint32_t b[8];
+            if (perm) {
+#pragma unroll
+                for (int e = 0; e < 8; e++) b[e] = raw[chunk_addr(fmt, D, kv, tok, pos[e])];
+            } else {
+                const uint2 x = *(const uint2*)(raw + chunk_addr(fmt, D, kv, tok, pos0));
+#pragma unroll
+                for (int e = 0; e < 4; e++) b[e] = (x.x >> (8 * e)) & 0xffu, b[4 + e] = (x.y >> (8 * e)) & 0xffu;
+            }
+            float f[8];
+#pragma unroll
+            for (int e = 0; e < 8; e++) {
+                const int code = fmt == B200KV_FMT_Q8_1 ? (int)b[e] - 128 : (int)((b[e] >> (4 * nib)) & 0xfu) - 8;
+                f[e] = __fmul_rn((float)code, sc);
+            }
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                if (is_bf16) {
+                    const __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * e], f[2 * e + 1]);
+                    w[e] = *(const uint32_t*)&h;
+                } else {
+                    const __half2 h = __floats2half2_rn(f[2 * e], f[2 * e + 1]);
+                    w[e] = *(const uint32_t*)&h;
+                }
+            }
+        }
+        *(uint4*)(dst + (u / 8) * (PAGE_TOKENS * 128) + tok * 128 + (((u % 8) ^ (tok & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+}
+
+template <int NQ, int D, int SRC>
+__global__ void __launch_bounds__(AGeo<NQ, D, SRC>::THREADS, 1) attn_tc_kernel(const __grid_constant__ AttnParams p) {
+    using GEO = AGeo<NQ, D, SRC>;
+    constexpr int NK = GEO::NK, NV = GEO::NV, NR = GEO::NR, CHUNK = GEO::CHUNK, QBYTES = GEO::QBYTES, PLANES = GEO::PLANES;
+    constexpr int DH = D / 2;  // output channels per softmax thread
+    constexpr uint32_t COL_O = 0, COL_S = GEO::COL_S, COLS_PER_TILE = GEO::COLS_PER_TILE;
+    constexpr int FILL_ARRIVALS = SRC == SRC_PAGES16 ? 1 : A_FILL_THREADS / 32;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    uint8_t* q_s = smem;                                    // [NQ][PLANES][128 rows][128 B], swizzled
+    uint8_t* k_ring = smem + NQ * QBYTES;                   // NK K tiles
+    uint8_t* v_ring = k_ring + NK * CHUNK;                  // NV V tiles
+    uint8_t* raw_ring = v_ring + NV * CHUNK;                // NR raw chunk pairs (SRC_PAGESQ)
+    uint64_t* full_k = (uint64_t*)(raw_ring + NR * GEO::RAW_STAGE);  // [NK] the tile is complete
+    uint64_t* full_v = full_k + NK;                         // [NV]
+    uint64_t* free_k = full_v + NV;                         // [NK] every tile's Q.K^T on the stage has completed
+    uint64_t* free_v = free_k + NK;                         // [NV] every tile's P.V on the stage has completed
+    uint64_t* bar_s = free_v + NV;                          // [NQ][2] S buffer written
+    uint64_t* bar_p = bar_s + 2 * NQ;                       // [NQ][2] P written by the softmax warps
+    uint64_t* bar_o = bar_p + 2 * NQ;                       // [NQ][2] P.V of page j completed, on barrier j & 1
+    uint64_t* full_raw = bar_o + 2 * NQ;                    // [NR] raw bytes landed
+    uint64_t* free_raw = full_raw + NR;                     // [NR] both converter warps are done with the raw stage
+    uint32_t* tmem_slot = (uint32_t*)(((uintptr_t)(free_raw + NR) + 15) & ~(uintptr_t)15);
+    volatile int* fail_s = (volatile int*)(tmem_slot + 1);
+    float* xchg = (float*)(tmem_slot + 4);                  // [NQ][2 parities][A_XCHG]
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int kvh = blockIdx.y, b = blockIdx.z;
+    const int G = p.G, qpt = AM / G;                        // queries per tile
+    const int cta_tile = (int)(gridDim.x - 1 - blockIdx.x);  // late queries see the most keys: schedule them first
+    const int32_t trow = SRC == SRC_DENSE ? 0 : p.desc[2 * b], T = SRC == SRC_DENSE ? p.T : p.desc[2 * b + 1];
+    const int P0 = T - p.S;                                 // keys before the first query's own position
+    const int cta_q0 = cta_tile * NQ * qpt;
+    const int cta_q_last = min(cta_q0 + NQ * qpt, p.S) - 1;
+    // every tile of the CTA walks the pages up to the last key its last tile sees; a tile that ends earlier finds
+    // its extra page fully masked
+    const int n_tiles = (p.causal ? P0 + cta_q_last : T - 1) / PAGE_TOKENS + 1;
+
+    if (tid == 0) {
+        for (int s = 0; s < NK; s++) mbar_init(&full_k[s], FILL_ARRIVALS), mbar_init(&free_k[s], NQ);
+        for (int s = 0; s < NV; s++) mbar_init(&full_v[s], FILL_ARRIVALS), mbar_init(&free_v[s], NQ);
+        for (int i = 0; i < 2 * NQ; i++) mbar_init(&bar_s[i], 1), mbar_init(&bar_p[i], A_SM_THREADS / 32);
+        for (int i = 0; i < 2 * NQ; i++) mbar_init(&bar_o[i], 1);
+        for (int s = 0; s < NR; s++) mbar_init(&full_raw[s], 1), mbar_init(&free_raw[s], A_FILL_THREADS / 32);
+        *fail_s = (smem_u32(smem) & 1023u) ? 1 : 0;  // the swizzled operand tiles need a 1024-byte aligned base
+        mbar_fence_init();
+    }
+    if (warp == 0) tmem_alloc(tmem_slot, COLS_PER_TILE * NQ);
+
+    // per-thread tile geometry (softmax threads only; the other warps get harmless values)
+    const int qt = min(tid / A_SM_THREADS, NQ - 1), w8 = (tid % A_SM_THREADS) >> 5;
+    const int row = (w8 & 3) * 32 + lane, half = w8 >> 2;
+    const int q0 = cta_q0 + qt * qpt;
+    const int rq = row / G, rg = row % G;
+    const bool live = rq < qpt && q0 + rq < p.S;
+    const int q_last = max(min(q0 + qpt, p.S) - 1, 0);   // last live query of the tile (the tile may be all dead)
+    const int my_q = live ? q0 + rq : min(q_last, p.S - 1);
+    const int my_limit = p.causal ? P0 + my_q : T - 1;  // last visible key of this row
+    const int min_limit = p.causal ? P0 + min(q0, p.S - 1) : T - 1;  // last key EVERY row of the tile sees
+    const bool is_softmax = tid < NQ * A_SM_THREADS;
+
+    // ---- Q tile -> shared memory, K-major with the 128-byte swizzle (row r: 16-byte unit u of a plane at u ^ (r & 7));
+    //      this thread moves the DH channels of its half of its row ----
+    if (is_softmax) {
+        constexpr int NU = DH / 8;  // 16-byte units per thread
+        const int head = kvh * G + rg;
+        const uint4* src = (const uint4*)((const uint16_t*)p.q + (int64_t)b * p.qb + (int64_t)head * p.qh + (int64_t)my_q * p.qs) + half * NU;
+#pragma unroll
+        for (int uu = 0; uu < NU; uu++) {
+            const uint4 v = live ? src[uu] : make_uint4(0, 0, 0, 0);
+            const int unit = half * NU + uu, plane = unit / 8, u8 = unit % 8;
+            *(uint4*)(q_s + qt * QBYTES + plane * (AM * 128) + row * 128 + ((u8 ^ (row & 7)) << 4)) = v;
+        }
+        fence_async_proxy();  // generic-proxy writes -> visible to the tensor core
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (!is_softmax) {
+        // Every lane of these warps walks its loop (the values stay warp-uniform); one elected lane issues.
+        const int role = warp - NQ * (A_SM_THREADS / 32);  // 0 .. NQ - 1: MMAs of tile `role`; above: the copy warp, or the converter / loader warps
+        if (role >= NQ && SRC == SRC_PAGES16) {
+            // ================= page copies: the chunks of a 16-bit page are the operand tiles =================
+            const int32_t* trow_p = p.table + (int64_t)trow * p.max_pages_per_seq;
+            int32_t pg_next = trow_p[0];
+            for (int i = 0; i < n_tiles; i++) {
+                int32_t pg = pg_next;
+                if (i + 1 < n_tiles) pg_next = trow_p[i + 1];  // fetched one page ahead of its use
+                if (pg < 0 || pg >= p.n_pages) {
+                    if (lane == 0) atomicOr(p.status, STATUS_PAGE_OOB);
+                    pg = 0;
+                }
+                const uint8_t* src = p.pool + (int64_t)pg * p.page_bytes + (int64_t)kvh * (2 * p.chunk_bytes);
+                if (i >= NK) wait_or_fail(&free_k[i % NK], (uint32_t)((i / NK - 1) & 1), fail_s);
+                if (elect_one()) {
+                    mbar_expect_tx(&full_k[i % NK], CHUNK);
+                    bulk_g2s(k_ring + (i % NK) * CHUNK, src, CHUNK, &full_k[i % NK]);
+                }
+                __syncwarp();
+                if (i >= NV) wait_or_fail(&free_v[i % NV], (uint32_t)((i / NV - 1) & 1), fail_s);
+                if (elect_one()) {
+                    mbar_expect_tx(&full_v[i % NV], CHUNK);
+                    bulk_g2s(v_ring + (i % NV) * CHUNK, src + CHUNK, CHUNK, &full_v[i % NV]);
+                }
+                __syncwarp();
+            }
+        } else if (role < NQ) {
+            // ================= MMAs of tile t = role =================
+            const int t = role;
+            const uint32_t tm = tmem + t * COLS_PER_TILE;
+            const uint32_t idesc_s = instr_desc(p.is_bf16, 0, AM, PAGE_TOKENS);
+            const uint32_t idesc_o = instr_desc(p.is_bf16, 1, AM, D);
+            // descriptors of the ring bases; a byte offset inside the 256 KiB window adds offset / 16 to the address field
+            const uint64_t q_desc = smem_desc(smem_u32(q_s) + t * QBYTES, 0, 1024);
+            const uint64_t k_desc = smem_desc(smem_u32(k_ring), 0, 1024);
+            // V tile: planes of 64 channels 8192 bytes apart (leading dimension), 8-key groups 1024 bytes apart
+            const uint64_t v_desc = smem_desc(smem_u32(v_ring), PAGE_TOKENS * 128, 1024);
+            const bool adaptive = !p.is_bf16;
+            auto issue_qk = [&](int j) {  // S(j) = Q . K(j)^T into buffer j & 1
+                wait_or_fail(&full_k[j % NK], (uint32_t)((j / NK) & 1), fail_s);
+                tc_fence_after();
+                if (elect_one()) {
+                    const uint64_t kd = k_desc + (uint64_t)(((j % NK) * CHUNK) >> 4);
+#pragma unroll
+                    for (int pl = 0; pl < PLANES; pl++)
+#pragma unroll
+                        for (int kk = 0; kk < 4; kk++) {
+                            const uint64_t off = (uint64_t)((pl * (AM * 128) + kk * 32) >> 4);
+                            tc_mma_ss(tm + COL_S + 64 * (j & 1), q_desc + off, kd + (uint64_t)((pl * (PAGE_TOKENS * 128) + kk * 32) >> 4),
+                                      idesc_s, (pl | kk) ? 1u : 0u);
+                        }
+                    tc_commit(&bar_s[2 * t + (j & 1)]);
+                    tc_commit(&free_k[j % NK]);
+                }
+                __syncwarp();
+            };
+            issue_qk(0);
+            if (n_tiles > 1) issue_qk(1);
+            for (int j = 0; j < n_tiles; j++) {
+                // O += P(j) . V(j): 4 steps of 16 keys; the V tile is an MN-major operand
+                wait_or_fail(&full_v[j % NV], (uint32_t)((j / NV) & 1), fail_s);
+                wait_or_fail(&bar_p[2 * t + (j & 1)], (uint32_t)((j >> 1) & 1), fail_s);
+                tc_fence_after();
+                const int* flags = (const int*)(xchg + (2 * t + (j & 1)) * A_XCHG + 2 * AM);
+                const bool two = !adaptive || __any_sync(0xffffffffu, flags[lane & 7] != 0);
+                if (elect_one()) {
+                    const uint64_t vd = v_desc + (uint64_t)(((j % NV) * CHUNK) >> 4);
+                    const uint32_t pa = tm + COL_S + 64 * (j & 1);
+#pragma unroll
+                    for (int kk = 0; kk < 4; kk++) {
+                        tc_mma_ts(tm + COL_O, pa + kk * 8, vd + (uint64_t)((kk * 2048) >> 4), idesc_o, (j | kk) ? 1u : 0u);
+                        if (two) tc_mma_ts(tm + COL_O, pa + 32 + kk * 8, vd + (uint64_t)((kk * 2048) >> 4), idesc_o, 1u);
+                    }
+                    tc_commit(&bar_o[2 * t + (j & 1)]);
+                    tc_commit(&free_v[j % NV]);
+                }
+                __syncwarp();
+                // S(j + 2) reuses the buffer P(j) sits in: the tensor core runs one thread's MMAs in issue order
+                if (j + 2 < n_tiles) issue_qk(j + 2);
+            }
+        } else {
+            // ================= converter / loader warps: fill the operand rings =================
+            const int ft = tid - (NQ * A_SM_THREADS + 32 * NQ);  // 0 .. 63
+            if constexpr (SRC == SRC_PAGESQ) {
+                const bool requester = ft < 32;  // the first converter warp also requests the raw pages
+                const int32_t* trow_p = p.table + (int64_t)trow * p.max_pages_per_seq;
+                auto request = [&](int i, int32_t pg) {  // raw chunk pair of page i into stage i % NR
+                    if (pg < 0 || pg >= p.n_pages) {
+                        if (lane == 0) atomicOr(p.status, STATUS_PAGE_OOB);
+                        pg = 0;
+                    }
+                    if (elect_one()) {
+                        const uint8_t* src = p.pool + (int64_t)pg * p.page_bytes + (int64_t)kvh * (2 * p.chunk_bytes);
+                        mbar_expect_tx(&full_raw[i % NR], 2 * p.chunk_bytes);
+                        bulk_g2s(raw_ring + (i % NR) * GEO::RAW_STAGE, src, 2 * p.chunk_bytes, &full_raw[i % NR]);
+                    }
+                    __syncwarp();
+                };
+                int32_t pg_next = 0;
+                if (requester) {
+                    for (int i = 0; i < NR && i < n_tiles; i++) request(i, trow_p[i]);
+                    if (NR < n_tiles) pg_next = trow_p[NR];
+                }
+                for (int i = 0; i < n_tiles; i++) {
+                    const uint8_t* raw = raw_ring + (i % NR) * GEO::RAW_STAGE;
+                    const int n_valid = min(PAGE_TOKENS, T - i * PAGE_TOKENS);
+                    wait_or_fail(&full_raw[i % NR], (uint32_t)((i / NR) & 1), fail_s);
+                    if (i >= NK) wait_or_fail(&free_k[i % NK], (uint32_t)((i / NK - 1) & 1), fail_s);
+                    convert_chunk<D>(raw, k_ring + (i % NK) * CHUNK, p.fmt, 0, p.is_bf16 != 0, n_valid, ft);
+                    fence_async_proxy();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&full_k[i % NK]);
+                    if (i >= NV) wait_or_fail(&free_v[i % NV], (uint32_t)((i / NV - 1) & 1), fail_s);
+                    convert_chunk<D>(raw + p.chunk_bytes, v_ring + (i % NV) * CHUNK, p.fmt, 1, p.is_bf16 != 0, n_valid, ft);
+                    fence_async_proxy();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&full_v[i % NV]), mbar_arrive(&free_raw[i % NR]);
+                    if (requester && i + NR < n_tiles) {  // the stage is free once the other converter warp has left it too
+                        wait_or_fail(&free_raw[i % NR], (uint32_t)((i / NR) & 1), fail_s);
+                        request(i + NR, pg_next);
+                        if (i + NR + 1 < n_tiles) pg_next = trow_p[i + NR + 1];
+                    }
+                }
+            } else if constexpr (SRC == SRC_DENSE) {
+                constexpr int LAG = 2;            // pages in flight behind the one being requested
+                constexpr int UROW = D / 8;       // 16-byte units per row
+                constexpr int PER_THREAD = PAGE_TOKENS * UROW / A_FILL_THREADS;
+                const uint16_t* kbase = (const uint16_t*)p.k + (int64_t)b * p.kb + (int64_t)kvh * p.kh;
+                const uint16_t* vbase = (const uint16_t*)p.v + (int64_t)b * p.vb + (int64_t)kvh * p.vh;
+                for (int i = 0; i < n_tiles + LAG; i++) {
+                    if (i < n_tiles) {
+                        if (i >= NK) wait_or_fail(&free_k[i % NK], (uint32_t)((i / NK - 1) & 1), fail_s);
+                        if (i >= NV) wait_or_fail(&free_v[i % NV], (uint32_t)((i / NV - 1) & 1), fail_s);
+                        uint8_t* kd = k_ring + (i % NK) * CHUNK;
+                        uint8_t* vd = v_ring + (i % NV) * CHUNK;
+#pragma unroll
+                        for (int e = 0; e < PER_THREAD; e++) {
+                            const int x = e * A_FILL_THREADS + ft, r = x / UROW, u = x % UROW;
+                            const int key = i * PAGE_TOKENS + r;
+                            const bool ok = key < T;
+                            const int64_t kr = ok ? key : 0;
+                            const int off = (u / 8) * (PAGE_TOKENS * 128) + r * 128 + (((u % 8) ^ (r & 7)) << 4);
+                            cp_async16_zfill(kd + off, kbase + kr * p.ks + u * 8, ok);
+                            cp_async16_zfill(vd + off, vbase + kr * p.vs + u * 8, ok);
+                        }
+                    }
+                    cp_async_commit_group();
+                    if (i >= LAG) {
+                        cp_async_wait_group<LAG>();  // the group of page i - LAG (and everything older) has landed
+                        fence_async_proxy();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&full_k[(i - LAG) % NK]), mbar_arrive(&full_v[(i - LAG) % NV]);
+                    }
+                }
+                cp_async_wait_group<0>();
+            }
+        }
+    } else {
+        // ================= softmax threads =================
+        const uint32_t lane_base = tmem + qt * COLS_PER_TILE + ((uint32_t)((w8 & 3) * 32) << 16);  // this warp's lane quarter
+        const int pair_id = 1 + qt * 4 + (w8 & 3);        // named barrier of the two warps that share these 32 rows
+        const bool adaptive = !p.is_bf16;
+        const float sl2 = p.scale * 1.4426950408889634f;  // scores enter the exponent in log2 units
+        float m_ref = -INFINITY, l_run = 0.f;             // l_run: this thread's half of the row sum
+        // this row's mask values (dense source): element (my_q, key) at mrow + key * mk
+        const bool masked = SRC == SRC_DENSE && p.mask != nullptr;
+        const int64_t mrow = masked ? (int64_t)b * p.mb + (int64_t)(kvh * G + rg) * p.mh + (int64_t)my_q * p.mq : 0;
+
+        for (int j = 0; j < n_tiles; j++) {
+            const uint32_t sbuf = lane_base + COL_S + 64 * (j & 1);
+            wait_or_fail(&bar_s[2 * qt + (j & 1)], (uint32_t)((j >> 1) & 1), fail_s);
+            tc_fence_after();
+            // ---- this thread's 32 of the row's 64 scores ----
+            uint32_t sr[32];
+            tmem_ld32(sbuf + 32 * half, sr);
+            tmem_ld_wait();
+            float tmax = -INFINITY;
+            const int t0 = j * PAGE_TOKENS + 32 * half;
+            if (masked) {  // the mask is added to the scaled score: the raw score takes mask / scale
+#pragma unroll
+                for (int c = 0; c < 32; c++) {
+                    float s = -INFINITY;
+                    if (t0 + c <= my_limit) s = fmaf(ld_as_f32(p.mask, p.mask_dtype, mrow + (int64_t)(t0 + c) * p.mk), p.inv_scale, __uint_as_float(sr[c]));
+                    sr[c] = __float_as_uint(s);
+                    tmax = fmaxf(tmax, s);
+                }
+            } else if (j * PAGE_TOKENS + PAGE_TOKENS - 1 > min_limit) {  // only pages on the causal diagonal / past the end need a mask
+#pragma unroll
+                for (int c = 0; c < 32; c++) {
+                    const float s = (t0 + c <= my_limit) ? __uint_as_float(sr[c]) : -INFINITY;
+                    sr[c] = __float_as_uint(s);
+                    tmax = fmaxf(tmax, s);
+                }
+            } else {
+#pragma unroll
+                for (int c = 0; c < 32; c++) tmax = fmaxf(tmax, __uint_as_float(sr[c]));
+            }
+            float* xq = xchg + (2 * qt + (j & 1)) * A_XCHG;
+            int* flags = (int*)(xq + 2 * AM);
+            bool two = true;
+            // f16 weights skip the remainder product of a page once, for every row of the tile, what the rounding of the
+            // page can add is below 2^-12 / 8 of the row's scale; page 0 always keeps it (l_run is 0)
+            if (adaptive) {
+                const bool mine = j == 0 || !(fast_exp2(fmaf(tmax, sl2, -m_ref)) * 5.657f <= p.skip_fraction * l_run);
+                two = __any_sync(0xffffffffu, mine);
+                if (lane == 0) flags[w8] = two ? 1 : 0;
+            }
+            xq[half * AM + row] = tmax;
+            pair_barrier(pair_id);  // maxima exchanged; both halves of S(j) are in registers, so P may overwrite them
+            tmax = fmaxf(tmax, xq[(half ^ 1) * AM + row]) * sl2;
+            // raise the reference maximum only when it is exceeded by more than 2^8: the exponentials stay below
+            // 256, exact enough in 16 bits, and O has to be rescaled only rarely
+            float alpha = 1.f;
+            if (j == 0) {
+                m_ref = tmax;
+            } else if (tmax > m_ref + 8.f) {
+                alpha = fast_exp2(m_ref - tmax);  // m_ref = -inf (every key so far masked out): 0
+                m_ref = tmax;
+                l_run *= alpha;
+            }
+            if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+                // O must hold every page before this one: see prefill_tc.cu for why the wait on barrier (j - 1) & 1 cannot
+                // mistake the completion of P.V(j - 3) or P.V(j + 1) for that of P.V(j - 1)
+                wait_or_fail(&bar_o[2 * qt + ((j - 1) & 1)], (uint32_t)(((j - 1) >> 1) & 1), fail_s);
+                tc_fence_after();
+#pragma unroll
+                for (int cc = 0; cc < DH / 16; cc++) {  // this thread's half of the row's output channels
+                    uint32_t orow[16];
+                    tmem_ld16(lane_base + COL_O + DH * half + cc * 16, orow);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int c = 0; c < 16; c++) orow[c] = __float_as_uint(__uint_as_float(orow[c]) * alpha);
+                    tmem_st16(lane_base + COL_O + DH * half + cc * 16, orow);
+                }
+            }
+            // a row that has seen no key yet has m_ref = -inf: its weights are exp2(-inf - 0) = 0, not exp2(-inf + inf)
+            const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+            uint32_t pr[16], pr2[16];
+            float lsum = 0.f;
+#pragma unroll
+            for (int c = 0; c < 16; c++) {
+                const float p0 = fast_exp2(fmaf(__uint_as_float(sr[2 * c]), sl2, -m_use));
+                const float p1 = fast_exp2(fmaf(__uint_as_float(sr[2 * c + 1]), sl2, -m_use));
+                lsum += p0 + p1;
+                if (p.is_bf16) {
+                    const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+                    const __nv_bfloat162 l = __floats2bfloat162_rn(p0 - __low2float(h), p1 - __high2float(h));
+                    pr[c] = *(const uint32_t*)&h, pr2[c] = *(const uint32_t*)&l;
+                } else {
+                    const __half2 h = __floats2half2_rn(p0, p1);
+                    pr[c] = *(const uint32_t*)&h;
+                    if (two) {
+                        const __half2 l = __floats2half2_rn(p0 - __low2float(h), p1 - __high2float(h));
+                        pr2[c] = *(const uint32_t*)&l;
+                    } else {
+                        pr2[c] = 0u;
+                    }
+                }
+            }
+            tmem_st16(sbuf + 32 + 16 * half, pr2);
+            l_run += lsum;
+            tmem_st16(sbuf + 16 * half, pr);
+            tmem_st_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bar_p[2 * qt + (j & 1)]);
+        }
+        // ---- epilogue: wait for the last P.V, normalise, store ----
+        wait_or_fail(&bar_o[2 * qt + ((n_tiles - 1) & 1)], (uint32_t)(((n_tiles - 1) >> 1) & 1), fail_s);
+        tc_fence_after();
+        float* xq = xchg + (2 * qt + (n_tiles & 1)) * A_XCHG;  // the buffer page n_tiles - 2 used: everyone is past it
+        xq[half * AM + row] = l_run;
+        pair_barrier(pair_id);
+        if (!*fail_s) {
+            const float inv = 1.f / (l_run + xq[(half ^ 1) * AM + row]);  // no visible key: 0 * inf = NaN, as 0 / 0 in the reference
+            uint16_t* dst = (uint16_t*)p.out + (int64_t)b * p.ob + (int64_t)(kvh * G + rg) * p.oh + (int64_t)my_q * p.os + DH * half;
+#pragma unroll
+            for (int cc = 0; cc < DH / 32; cc++) {
+                uint32_t orow[32];
+                tmem_ld32(lane_base + COL_O + DH * half + cc * 32, orow);
+                tmem_ld_wait();
+                if (live) {
+#pragma unroll
+                    for (int c = 0; c < 32; c += 8) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int e = 0; e < 4; e++) {
+                            const float a = __uint_as_float(orow[c + 2 * e]) * inv, bb = __uint_as_float(orow[c + 2 * e + 1]) * inv;
+                            if (p.is_bf16) {
+                                const __nv_bfloat162 h = __floats2bfloat162_rn(a, bb);
+                                w[e] = *(const uint32_t*)&h;
+                            } else {
+                                const __half2 h = __floats2half2_rn(a, bb);
+                                w[e] = *(const uint32_t*)&h;
+                            }
+                        }
+                        *(uint4*)(dst + cc * 32 + c) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (*fail_s) {
+        if (tid == 0) atomicOr(p.status, STATUS_WAIT_EXPIRED);
+        __nanosleep(200000);  // give copies that may still be in flight time to land before the CTA's memory is released
+        __syncthreads();
+    }
+    if (warp == 0) tmem_dealloc(tmem, COLS_PER_TILE * NQ);
+}
+
+// ---- host side ------------------------------------------------------------------------------------------
+
+static bool aligned16(const void* ptr, const int64_t* st, int n) {
+    if ((uintptr_t)ptr % 16) return false;
+    for (int i = 0; i < n; i++)
+        if ((st[i] * 2) % 16) return false;
+    return true;
+}
+
+template <int NQ, int D, int SRC>
+static cudaError_t launch_attn(const AttnParams& p, int n_batch, cudaStream_t stream) {
+    using GEO = AGeo<NQ, D, SRC>;
+    cudaError_t e = cudaFuncSetAttribute(attn_tc_kernel<NQ, D, SRC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEO::SMEM);
+    if (e != cudaSuccess) return e;
+    const int per_cta = NQ * (AM / p.G);
+    dim3 grid((p.S + per_cta - 1) / per_cta, p.Hkv, n_batch);
+    attn_tc_kernel<NQ, D, SRC><<<grid, GEO::THREADS, GEO::SMEM, stream>>>(p);
+    return cudaGetLastError();
+}
+
+template <int D, int SRC>
+static cudaError_t launch_attn_nq(const AttnParams& p, int n_batch, cudaStream_t stream) {
+    // double tiles (K / V staged once for 2 x 128 rows) when they still fill the GPU
+    const int qpt = AM / p.G;
+    const int64_t double_ctas = (int64_t)((p.S + 2 * qpt - 1) / (2 * qpt)) * p.Hkv * n_batch;
+    return double_ctas >= 148 /* SMs of a B200 */ ? launch_attn<2, D, SRC>(p, n_batch, stream) : launch_attn<1, D, SRC>(p, n_batch, stream);
+}
+
+// Several queries per sequence over a paged cache: which caches this kernel reads (the f16 / bf16 head_dim-128 caches
+// have the kernel of prefill_tc.cu).
+bool attn_tc_supported(const b200kv_cache* c, int n_q_heads, int dtype, const void* q, const int64_t* qs, const void* out, const int64_t* os) {
+    const int fmt = c->L.fmt, D = c->L.D;
+    if (D != 64 && D != 128) return false;
+    if (dtype != B200KV_F16 && dtype != B200KV_BF16) return false;
+    const bool pages16 = (fmt == B200KV_FMT_F16 && dtype == B200KV_F16) || (fmt == B200KV_FMT_BF16 && dtype == B200KV_BF16);
+    if (!(pages16 && D == 64) && !fmt_is_block_quant(fmt)) return false;
+    const int G = n_q_heads / c->L.Hkv;
+    if (G < 1 || G > AM) return false;
+    return aligned16(q, qs, 3) && aligned16(out, os, 3);
+}
+
+int launch_attn_tc_paged(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t n_q_heads, int32_t n_new, const void* q, const int64_t* qs,
+                         void* out, const int64_t* os, int32_t dtype, float scale, int causal, cudaStream_t stream) {
+    int slot;
+    uint8_t *h, *d;
+    if (staging_acquire(c, (size_t)n_seqs * 8, &slot, &h, &d) != B200KV_OK) return B200KV_KO;
+    int32_t* hw = (int32_t*)h;
+    for (int i = 0; i < n_seqs; i++) hw[2 * i] = seqs[i], hw[2 * i + 1] = (int32_t)c->seqs[seqs[i]].len;
+    if (staging_upload(c, slot, (size_t)n_seqs * 8, stream) != B200KV_OK) {
+        staging_release(c, slot, stream);
+        return B200KV_KO;
+    }
+    AttnParams p{};
+    p.q = q, p.out = out, p.qb = qs[0], p.qh = qs[1], p.qs = qs[2], p.ob = os[0], p.oh = os[1], p.os = os[2];
+    p.status = c->d_status;
+    p.Hkv = c->L.Hkv, p.G = n_q_heads / c->L.Hkv, p.S = n_new, p.causal = causal, p.is_bf16 = dtype == B200KV_BF16;
+    p.scale = scale, p.inv_scale = 1.f / scale, p.skip_fraction = A_SKIP_FRACTION;
+    p.pool = c->pool, p.table = c->d_table, p.desc = (const int32_t*)d, p.page_bytes = c->L.page_bytes;
+    p.n_pages = (int32_t)c->n_pages, p.max_pages_per_seq = c->max_pages_per_seq, p.fmt = c->L.fmt, p.chunk_bytes = c->L.chunk_bytes;
+    cudaError_t e;
+    {
+        ProfScope ps(c, K_PREFILL, stream);
+        if (fmt_is_block_quant(c->L.fmt))
+            e = c->L.D == 128 ? launch_attn_nq<128, SRC_PAGESQ>(p, n_seqs, stream) : launch_attn_nq<64, SRC_PAGESQ>(p, n_seqs, stream);
+        else
+            e = launch_attn_nq<64, SRC_PAGES16>(p, n_seqs, stream);
+    }
+    staging_release(c, slot, stream);
+    if (e != cudaSuccess) return fail("attention launch failed: %s", cudaGetErrorString(e));
+    return B200KV_OK;
+}
+
+// The lone Sdpa on dense tensors: 0 when this kernel cannot take the call (the caller then runs the generic kernel).
+bool attn_tc_dense_supported(const void* q, const int64_t* qs, const void* k, const int64_t* ks, const void* v, const int64_t* vs,
+                             const void* mask, int mask_dtype, const void* out, const int64_t* os, int B, int Hq, int Hkv, int S, int T, int D,
+                             int dtype, int causal) {
+    if (D != 64 && D != 128) return false;
+    if (dtype != B200KV_F16 && dtype != B200KV_BF16) return false;
+    if (B <= 0 || S <= 0 || T <= 0 || B > 65535 || Hkv > 65535) return false;
+    if (causal && T < S) return false;  // queries that see no key at all: left to the generic kernel
+    if (mask && (mask_dtype < B200KV_F32 || mask_dtype > B200KV_BF16)) return false;
+    const int G = Hq / Hkv;
+    if (G < 1 || G > AM) return false;
+    return aligned16(q, qs, 3) && aligned16(out, os, 3) && aligned16(k, ks, 3) && aligned16(v, vs, 3);
+}
+
+int launch_attn_tc_dense(const void* q, const int64_t* qs, const void* k, const int64_t* ks, const void* v, const int64_t* vs, const void* mask,
+                         const int64_t* ms, int mask_dtype, void* out, const int64_t* os, int B, int Hq, int Hkv, int S, int T, int D, int dtype,
+                         float scale, int causal, int* status, cudaStream_t stream) {
+    AttnParams p{};
+    p.q = q, p.out = out, p.qb = qs[0], p.qh = qs[1], p.qs = qs[2], p.ob = os[0], p.oh = os[1], p.os = os[2];
+    p.status = status;
+    p.Hkv = Hkv, p.G = Hq / Hkv, p.S = S, p.causal = causal, p.is_bf16 = dtype == B200KV_BF16;
+    p.scale = scale, p.inv_scale = 1.f / scale, p.skip_fraction = A_SKIP_FRACTION;
+    p.k = k, p.v = v, p.kb = ks[0], p.kh = ks[1], p.ks = ks[2], p.vb = vs[0], p.vh = vs[1], p.vs = vs[2], p.T = T;
+    if (mask) p.mask = mask, p.mb = ms[0], p.mh = ms[1], p.mq = ms[2], p.mk = ms[3], p.mask_dtype = mask_dtype;
+    const cudaError_t e = D == 128 ? launch_attn_nq<128, SRC_DENSE>(p, B, stream) : launch_attn_nq<64, SRC_DENSE>(p, B, stream);
+    if (e != cudaSuccess) return fail("attention launch failed: %s", cudaGetErrorString(e));
+    return B200KV_OK;
+}
+
+}  // namespace b200kv

@@ -165,6 +165,16 @@ bool prefill_tc_supported(const b200kv_cache* c, int n_q_heads, int dtype, const
 int launch_prefill_tc(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t n_q_heads, int32_t n_new, const void* q,
                       const int64_t* qs, void* out, const int64_t* os, int32_t dtype, float scale, int causal,
                       cudaStream_t stream);
+// attn_tc.cu
+bool attn_tc_supported(const b200kv_cache* c, int n_q_heads, int dtype, const void* q, const int64_t* qs, const void* out, const int64_t* os);
+int launch_attn_tc_paged(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int32_t n_q_heads, int32_t n_new, const void* q, const int64_t* qs,
+                         void* out, const int64_t* os, int32_t dtype, float scale, int causal, cudaStream_t stream);
+bool attn_tc_dense_supported(const void* q, const int64_t* qs, const void* k, const int64_t* ks, const void* v, const int64_t* vs,
+                             const void* mask, int mask_dtype, const void* out, const int64_t* os, int B, int Hq, int Hkv, int S, int T, int D,
+                             int dtype, int causal);
+int launch_attn_tc_dense(const void* q, const int64_t* qs, const void* k, const int64_t* ks, const void* v, const int64_t* vs, const void* mask,
+                         const int64_t* ms, int mask_dtype, void* out, const int64_t* os, int B, int Hq, int Hkv, int S, int T, int D, int dtype,
+                         float scale, int causal, int* status, cudaStream_t stream);
 // cache.cu
 int launch_export(b200kv_cache* c, int32_t seq, void* k_out, const int64_t* ks, void* v_out, const int64_t* vs,
                   int32_t dtype, cudaStream_t stream);

@@ -160,7 +160,36 @@ int launch_sdpa_paged(b200kv_cache* c, int32_t seq, const void* q, const int64_t
 
 }  // namespace b200kv
 
+namespace b200kv {
+// Status word of the tensor-core kernel when it runs without a cache handle (the lone Sdpa): one per device.
+static __device__ int g_sdpa_status;
+static int* sdpa_status_ptr() {
+    static int* ptr[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (!ptr[dev]) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_sdpa_status) != cudaSuccess) return nullptr;
+        ptr[dev] = (int*)p;
+    }
+    return ptr[dev];
+}
+}  // namespace b200kv
+
 using namespace b200kv;
+
+extern "C" int b200kv_sdpa_check(void* stream) {
+    int* dptr = sdpa_status_ptr();
+    if (!dptr) return fail("no CUDA device");
+    int st = 0;
+    B200KV_CUDA(cudaMemcpyAsync(&st, dptr, sizeof st, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    B200KV_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    if (st) {
+        B200KV_CUDA(cudaMemsetAsync(dptr, 0, sizeof st, (cudaStream_t)stream));
+        return fail("device status %d: a bounded wait of a b200kv_sdpa call expired", st);
+    }
+    return B200KV_OK;
+}
 
 extern "C" int b200kv_sdpa(const void* q, const int64_t q_strides[3], const void* k, const int64_t k_strides[3],
                            const void* v, const int64_t v_strides[3], const void* mask, const int64_t mask_strides[4],
@@ -178,6 +207,15 @@ extern "C" int b200kv_sdpa(const void* q, const int64_t q_strides[3], const void
     int n_dev = 0;
     if (cudaGetDeviceCount(&n_dev) != cudaSuccess || n_dev == 0) return fail("no CUDA device: b200kv has no CPU fallback");
     if (scale <= 0.f) scale = 1.0f / sqrtf((float)head_dim);
+    if (batch == 0 || q_len == 0) return B200KV_OK;
+    // f16 / bf16 at head_dim 64 / 128 with 16-byte aligned rows: the tensor-core kernel; everything else the generic one
+    if (attn_tc_dense_supported(q, q_strides, k, k_strides, v, v_strides, mask, mask_dtype, out, out_strides, batch, n_q_heads, n_kv_heads,
+                                q_len, kv_len, head_dim, dtype, causal)) {
+        int* status = sdpa_status_ptr();
+        if (status)
+            return launch_attn_tc_dense(q, q_strides, k, k_strides, v, v_strides, mask, mask_strides, mask_dtype, out, out_strides, batch,
+                                        n_q_heads, n_kv_heads, q_len, kv_len, head_dim, dtype, scale, causal, status, (cudaStream_t)stream);
+    }
     return launch_sdpa_dense(q, q_strides, k, k_strides, v, v_strides, mask, mask_strides, mask_dtype, out, out_strides,
                              batch, n_q_heads, n_kv_heads, q_len, kv_len, head_dim, dtype, dtype, scale, causal,
                              (cudaStream_t)stream);
