@@ -172,6 +172,37 @@ def test_kivi_one_long_sequence_uses_every_split_the_combine_pass_has(kv, fmt, b
     cache.close()
 
 
+@pytest.mark.parametrize("fmt,bits,io,Hq,Hkv,P,S", [("kivi8", 8, "f16", 8, 2, 300, 200), ("kivi4", 4, "bf16", 32, 8, 37, 700),
+                                                    ("kivi8", 8, "f16", 4, 4, 0, 3), ("kivi4", 4, "f16", 8, 2, 2, 130)])
+def test_kivi_chunk_of_queries_on_the_tensor_cores(kv, fmt, bits, io, Hq, Hkv, P, S):
+    # several queries per sequence over the KIVI stores (head_dim 128, 16-bit queries): sinks, finalised blocks and the
+    # f32 residual block are widened to 16 bits in shared memory on their way to tcgen05; against flash attention over
+    # the oracle's dequantised cache
+    D = 128
+    tdt = torch.float16 if io == "f16" else torch.bfloat16
+    cache = kv.KvCache(fmt, Hkv, D, max_seqs=1, max_seq_tokens=P + S + 64)
+    sq = cache.new_seq()
+    k = torch.from_numpy(normal_with_outliers(41, (1, Hkv, P + S, D))).to(tdt)
+    v = torch.from_numpy(normal_with_outliers(42, (1, Hkv, P + S, D))).to(tdt)
+    q = torch.from_numpy(normal(43, (1, Hq, S, D), scale=0.5)).to(tdt)
+    if P:
+        cache.append([sq], k[:, :, :P].cuda(), v[:, :, :P].cuda())
+    cache.append([sq], k[:, :, P:].cuda(), v[:, :, P:].cuda())
+    out = cache.attend([sq], q.cuda(), causal=True)
+    cache.profile(False, force_simt=True)  # the generic kernel, element by element
+    out_gen = cache.attend([sq], q.cuda(), causal=True)
+    cache.profile(False)
+    cache.check()
+    kd = np.stack([_deq(True, D, bits, k[0, h].float().numpy()) for h in range(Hkv)])[None]
+    vd = np.stack([_deq(False, D, bits, v[0, h].float().numpy()) for h in range(Hkv)])[None]
+    want = oracle.flash_sdpa(q.float().numpy(), kd, vd, causal=True, threads=8).astype(np.float32)
+    got = out.float().cpu().numpy()
+    err = rel_err(got, want) if io == "f16" else rel_err_bf16(got, want)
+    assert err <= TOL[io], err
+    assert rel_err(got, out_gen.float().cpu().numpy()) <= (8e-3 if io == "bf16" else 2e-3)
+    cache.close()
+
+
 def _deq(per_channel, D, bits, rows):
     st = oracle.KiviStore(per_channel, D, bits)
     st.push(rows)

@@ -35,8 +35,8 @@ extern "C" int b200kv_attend(b200kv_cache* c, int32_t n_seqs, const int32_t* seq
 
     if (!kivi && !c->force_simt && prefill_tc_supported(c, n_q_heads, dtype, q, q_strides, out, out_strides))
         return launch_prefill_tc(c, n_seqs, seqs, n_q_heads, n_new, q, q_strides, out, out_strides, dtype, scale, causal, stream);
-    // block-quantised pages and head_dim 64: the same pipeline, with the operand tiles rebuilt in shared memory
-    if (!kivi && !c->force_simt && attn_tc_supported(c, n_q_heads, dtype, q, q_strides, out, out_strides))
+    // block-quantised pages, KIVI stores and head_dim 64: the same pipeline, with the operand tiles rebuilt in shared memory
+    if (!c->force_simt && attn_tc_supported(c, n_q_heads, dtype, q, q_strides, out, out_strides))
         return launch_attn_tc_paged(c, n_seqs, seqs, n_q_heads, n_new, q, q_strides, out, out_strides, dtype, scale, causal, stream);
 
     // otherwise (f32 queries, f32 caches, KIVI stores, unaligned tensors): the generic kernel, one sequence at a time, reading the pages in place

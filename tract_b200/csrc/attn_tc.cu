@@ -1,6 +1,7 @@
 // Flash attention of many queries on the 5th-generation tensor cores (tcgen05 + TMEM) for every source the specialised
 // f16 / bf16 head_dim-128 kernel of prefill_tc.cu does not read: block-quantised pages (Q8_1, Q4_0), head_dim 64, and
-// dense strided K / V tensors with an optional additive mask (the lone Sdpa node).
+// dense strided K / V tensors with an optional additive mask (the lone Sdpa node), and the KIVI stores of
+// QuantizedDynKeyValueCache at head_dim 128.
 //
 // Replaces cuda/src/kernels/cu/flash_attn.cu (`attention_kernel`, instantiated for head_dim 64 and 128, :587-627; Ampere
 // mma.sync, one q-head per CTA) behind CudaFlashAttn::dispatch_eval (cuda/src/kernels/flash_attn.rs:82-189), and gives
@@ -19,12 +20,18 @@
 //   SRC_PAGESQ   the raw quantised chunk pair of a page lands (cp.async.bulk) in a small ring; two converter warps turn
 //                codes * f32(f16 scale) (q8_1.rs:50-63, q4_0.rs:82-95: exact in f32) into 16-bit rows of the operand tile,
 //                and the first of them requests the raw pages
+//   SRC_KIVI     the same for the stores of transformers/src/ops/quant_dyn_kv_cache.rs: keys 0 .. 3 are the f32 sinks, key
+//                4 + i sits in slot i % 64 of storage page i / 64, so a tile of 64 keys is the last 4 slots of one page
+//                (carried over in shared memory from the tile before) and the first 60 of the next; keys of finalised
+//                32-token blocks are lo[c] + code * scale[c], the rest come from the f32 residual rows, values are
+//                lo_t + code * scale_t (:141-146, :231-240)
 //   SRC_DENSE    two loader warps gather 16-byte units of the strided K / V rows with cp.async straight into the
 //                swizzled tile, two pages in flight; rows past the end of K / V are zero-filled
 // Every wait is bounded; on expiry the CTA flags the status word, every role runs to the end of its loop without
 // waiting any more, the CTA frees its TMEM and returns.
 #include <cmath>
 
+#include "kivi_common.cuh"
 #include "tc_common.cuh"
 
 namespace b200kv {
@@ -34,7 +41,10 @@ constexpr int A_SM_THREADS = 256;  // softmax threads per query tile
 constexpr int A_FILL_THREADS = 64; // converter / loader threads
 constexpr int A_XCHG = 2 * AM + 8; // per tile and page parity: the two half-row maxima of every row, one flag per softmax warp
 constexpr float A_SKIP_FRACTION = 0.125f;
-enum { SRC_PAGES16 = 0, SRC_PAGESQ = 1, SRC_DENSE = 2 };
+enum { SRC_PAGES16 = 0, SRC_PAGESQ = 1, SRC_DENSE = 2, SRC_KIVI = 3 };
+constexpr int A_KIVI_KP = 2 * 2 * 128 * 4;        // K parameters of a page: 2 blocks x (lo[128], scale[128]) f32
+constexpr int A_KIVI_VP = PAGE_TOKENS * 2 * 4;    // V parameters of a page: (lo, scale) f32 per token
+constexpr int A_CARRY = 2 * SINK * 128 * 2;      // 16-bit K and V rows of the last 4 slots of a KIVI page: they open the next tile
 
 template <int NQ, int D, int SRC>
 struct AGeo {
@@ -42,16 +52,19 @@ struct AGeo {
     static constexpr int CHUNK = PAGE_TOKENS * D * 2; // bytes of one K (or V) operand tile: 64 keys
     static constexpr int QBYTES = AM * D * 2;
     static constexpr bool FILL = SRC != SRC_PAGES16;
-    static constexpr int NK = NQ == 2 ? (D == 128 && SRC == SRC_PAGESQ ? 3 : 4) : 3;  // K stages
-    static constexpr int NV = NQ == 2 ? (D == 128 && SRC == SRC_PAGESQ ? 4 : 5) : 3;  // V stages
+    static constexpr bool RAW = SRC == SRC_PAGESQ || SRC == SRC_KIVI;                   // a ring of raw page bytes beside the operand rings
+    static constexpr int NK = NQ == 2 ? (D == 128 && RAW ? 3 : 4) : 3;  // K stages
+    static constexpr int NV = NQ == 2 ? (D == 128 && RAW ? 4 : 5) : 3;  // V stages
     static constexpr int NR = 2;                                                          // raw stages (SRC_PAGESQ)
-    static constexpr int RAW_STAGE = SRC == SRC_PAGESQ ? 2 * (PAGE_TOKENS * D + PAGE_TOKENS * (D / 32) * 2) : 0;  // a Q8_1 chunk pair
+    static constexpr int RAW_STAGE = SRC == SRC_PAGESQ ? 2 * (PAGE_TOKENS * D + PAGE_TOKENS * (D / 32) * 2)   // a Q8_1 chunk pair
+                                     : SRC == SRC_KIVI ? 2 * PAGE_TOKENS * D + A_KIVI_KP + A_KIVI_VP  // int8 codes of K and V, their parameters
+                                                       : 0;
     // softmax threads, one MMA warp per tile, then either the copy warp (16-bit pages) or the two converter / loader warps
     static constexpr int THREADS = NQ * A_SM_THREADS + 32 * NQ + (FILL ? A_FILL_THREADS : 32);
     static constexpr int N_BARS = 2 * NK + 2 * NV + 6 * NQ + 2 * NR;
     static constexpr uint32_t COL_S = D, COLS_PER_TILE = 256;  // TMEM: O in columns 0 .. D-1, the two S buffers after it
     static constexpr size_t SMEM = (size_t)NQ * QBYTES + (size_t)(NK + NV) * CHUNK + (size_t)NR * RAW_STAGE + N_BARS * 8 + 32 +
-                                   NQ * 2 * A_XCHG * 4;
+                                   NQ * 2 * A_XCHG * 4 + (SRC == SRC_KIVI ? A_CARRY : 0);
 };
 
 struct AttnParams {
@@ -76,6 +89,8 @@ struct AttnParams {
     const void* mask;
     int64_t mb, mh, mq, mk;
     int32_t mask_dtype;
+    // KIVI stores (SRC_KIVI); desc then holds {sequence, cached length} per batch entry
+    KiviView kv;
 };
 
 __device__ inline void cp_async16_zfill(void* dst_smem, const void* src, bool live) {
@@ -146,6 +161,7 @@ __global__ void __launch_bounds__(AGeo<NQ, D, SRC>::THREADS, 1) attn_tc_kernel(c
     constexpr int DH = D / 2;  // output channels per softmax thread
     constexpr uint32_t COL_O = 0, COL_S = GEO::COL_S, COLS_PER_TILE = GEO::COLS_PER_TILE;
     constexpr int FILL_ARRIVALS = SRC == SRC_PAGES16 ? 1 : A_FILL_THREADS / 32;
+    static_assert(SRC != SRC_KIVI || D == 128, "the KIVI stores have their tensor-core layout at head_dim 128 only");
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* q_s = smem;                                    // [NQ][PLANES][128 rows][128 B], swizzled
     uint8_t* k_ring = smem + NQ * QBYTES;                   // NK K tiles
@@ -341,6 +357,154 @@ __global__ void __launch_bounds__(AGeo<NQ, D, SRC>::THREADS, 1) attn_tc_kernel(c
                         wait_or_fail(&free_raw[i % NR], (uint32_t)((i / NR) & 1), fail_s);
                         request(i + NR, pg_next);
                         if (i + NR + 1 < n_tiles) pg_next = trow_p[i + NR + 1];
+                    }
+                }
+            } else if constexpr (SRC == SRC_KIVI) {
+                const KiviView& kw = p.kv;
+                const int32_t seq = trow;
+                const int KC = PAGE_TOKENS * kw.row_bytes;          // bytes of the K (or V) codes of a page and head
+                const int lfmt = kivi_layout_fmt(kw.bits);          // the block format whose row layout the codes borrow
+                const bool int4 = kw.bits == 4;
+                const int n_fin = max(T - SINK, 0) / KBLOCK;        // finalised key blocks
+                const int n_sp = T > SINK ? (T - SINK + PAGE_TOKENS - 1) / PAGE_TOKENS : 0;  // storage pages the sequence holds
+                const int n_need = min(n_sp, n_tiles);              // tile j reads page j (and, through the carry, page j - 1)
+                uint8_t* carry = (uint8_t*)(xchg + NQ * 2 * A_XCHG);  // [K, V][4 rows][256 B]
+                const bool requester = ft < 32;
+                const int32_t* trow_p = kw.table + (int64_t)seq * kw.max_pages_per_seq;
+                auto request = [&](int i, int32_t pg) {  // the four arrays of storage page i into raw stage i % NR
+                    if (pg < 0 || pg >= kw.n_pages) {
+                        if (lane == 0) atomicOr(p.status, STATUS_PAGE_OOB);
+                        pg = 0;
+                    }
+                    if (elect_one()) {
+                        const int64_t ph = (int64_t)pg * kw.H + kvh;
+                        uint8_t* dst = raw_ring + (i % NR) * GEO::RAW_STAGE;
+                        mbar_expect_tx(&full_raw[i % NR], 2 * KC + A_KIVI_KP + A_KIVI_VP);
+                        bulk_g2s(dst, kw.codes[0] + ph * KC, KC, &full_raw[i % NR]);
+                        bulk_g2s(dst + KC, kw.codes[1] + ph * KC, KC, &full_raw[i % NR]);
+                        bulk_g2s(dst + 2 * KC, kw.params[0] + ph * (A_KIVI_KP / 4), A_KIVI_KP, &full_raw[i % NR]);
+                        bulk_g2s(dst + 2 * KC + A_KIVI_KP, kw.params[1] + ph * (A_KIVI_VP / 4), A_KIVI_VP, &full_raw[i % NR]);
+                    }
+                    __syncwarp();
+                };
+                int32_t pg_next = 0;
+                if (requester) {
+                    for (int i = 0; i < NR && i < n_need; i++) request(i, trow_p[i]);
+                    if (NR < n_need) pg_next = trow_p[NR];
+                }
+                const int u = ft % 16, tl = ft / 16, ch0 = 8 * u;   // this thread's 8 channels; token lane 0 .. 3
+                const int kpos0 = int4 ? (ch0 / 32) * 16 + ch0 % 16 : ch0, knib = int4 ? (ch0 % 32) / 16 : 0;
+                int vpos[8];
+#pragma unroll
+                for (int e = 0; e < 8; e++) vpos[e] = code_pos(lfmt, 128, 1, ch0 + e);
+                const int vnib = code_nibble(lfmt, 128, 1, ch0);
+                const float* sink_base = kw.sinks + (((int64_t)seq * kw.H + kvh) * 2) * SINK * D;
+                const float* resid = kw.residual + (((int64_t)seq * kw.H + kvh) * 2 + 0) * KBLOCK * D;
+                auto pack8 = [&](const float* f) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        if (p.is_bf16) {
+                            const __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * e], f[2 * e + 1]);
+                            w[e] = *(const uint32_t*)&h;
+                        } else {
+                            const __half2 h = __floats2half2_rn(f[2 * e], f[2 * e + 1]);
+                            w[e] = *(const uint32_t*)&h;
+                        }
+                    }
+                    return make_uint4(w[0], w[1], w[2], w[3]);
+                };
+                auto tile_addr = [&](uint8_t* base, int row) { return base + (u / 8) * (PAGE_TOKENS * 128) + row * 128 + (((u % 8) ^ (row & 7)) << 4); };
+                for (int j = 0; j < n_tiles; j++) {
+                    const bool has_page = j < n_sp;
+                    const uint8_t* raw = raw_ring + (j % NR) * GEO::RAW_STAGE;
+                    if (has_page) wait_or_fail(&full_raw[j % NR], (uint32_t)((j / NR) & 1), fail_s);
+                    // rows 0 .. 3 of the tile: the sinks (tile 0) or the last four slots of the page before; thread ft takes
+                    // unit u of row ft / 16 for K and for V
+                    uint4 head[2];
+#pragma unroll
+                    for (int st = 0; st < 2; st++) {
+                        head[st] = make_uint4(0u, 0u, 0u, 0u);
+                        if (j * PAGE_TOKENS + tl < T) {
+                            if (j == 0) {
+                                const float4* src = (const float4*)(sink_base + ((int64_t)st * SINK + tl) * D + ch0);
+                                const float4 a = src[0], b2 = src[1];
+                                const float f[8] = {a.x, a.y, a.z, a.w, b2.x, b2.y, b2.z, b2.w};
+                                head[st] = pack8(f);
+                            } else {
+                                head[st] = *(const uint4*)(carry + ((st * SINK + tl) * 16 + u) * 16);
+                            }
+                        }
+                    }
+                    asm volatile("bar.sync 9, 64;" ::: "memory");  // both converter warps have read the carry: it may be rewritten
+#pragma unroll 1
+                    for (int st = 0; st < 2; st++) {  // K, then V
+                        uint8_t* dst;
+                        if (st == 0) {
+                            if (j >= NK) wait_or_fail(&free_k[j % NK], (uint32_t)((j / NK - 1) & 1), fail_s);
+                            dst = k_ring + (j % NK) * CHUNK;
+                        } else {
+                            if (j >= NV) wait_or_fail(&free_v[j % NV], (uint32_t)((j / NV - 1) & 1), fail_s);
+                            dst = v_ring + (j % NV) * CHUNK;
+                        }
+                        *(uint4*)tile_addr(dst, tl) = head[st];
+                        const uint8_t* codes = raw + st * KC;
+                        const float* kpar = (const float*)(raw + 2 * KC);
+                        const float2* vpar = (const float2*)(raw + 2 * KC + A_KIVI_KP);
+#pragma unroll 2
+                        for (int tt = 0; tt < PAGE_TOKENS / 4; tt++) {
+                            const int s = tt * 4 + tl;                  // slot in storage page j
+                            const int i = j * PAGE_TOKENS + s;          // storage index; key i + 4
+                            float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                            if (has_page && i + SINK < T) {
+                                if (st == 0 && i >= n_fin * KBLOCK) {  // the partial key block: f32 rows, verbatim
+                                    const float4* src = (const float4*)(resid + (int64_t)(i % KBLOCK) * D + ch0);
+                                    const float4 a = src[0], b2 = src[1];
+                                    f[0] = a.x, f[1] = a.y, f[2] = a.z, f[3] = a.w, f[4] = b2.x, f[5] = b2.y, f[6] = b2.z, f[7] = b2.w;
+                                } else {
+                                    uint32_t cb[8];
+                                    if (st == 0) {
+                                        const uint2 x = *(const uint2*)(codes + chunk_addr(lfmt, 128, 0, s, kpos0));
+#pragma unroll
+                                        for (int e = 0; e < 4; e++) cb[e] = (x.x >> (8 * e)) & 0xffu, cb[4 + e] = (x.y >> (8 * e)) & 0xffu;
+                                    } else {
+#pragma unroll
+                                        for (int e = 0; e < 8; e++) cb[e] = codes[chunk_addr(lfmt, 128, 1, s, vpos[e])];
+                                    }
+                                    const int nib = st == 0 ? knib : vnib;
+                                    if (st == 0) {  // per channel: (lo, scale) of the slot's 32-token block
+                                        const float* par = kpar + (s / KBLOCK) * 2 * D + ch0;
+#pragma unroll
+                                        for (int e = 0; e < 8; e++) {
+                                            const uint32_t code = int4 ? (cb[e] >> (4 * nib)) & 0xfu : cb[e];
+                                            f[e] = kivi_dequant(code, par[e], par[D + e]);
+                                        }
+                                    } else {        // per token
+                                        const float2 ls = vpar[s];
+#pragma unroll
+                                        for (int e = 0; e < 8; e++) {
+                                            const uint32_t code = int4 ? (cb[e] >> (4 * nib)) & 0xfu : cb[e];
+                                            f[e] = kivi_dequant(code, ls.x, ls.y);
+                                        }
+                                    }
+                                }
+                            }
+                            const uint4 w = pack8(f);
+                            if (s < PAGE_TOKENS - SINK) *(uint4*)tile_addr(dst, s + SINK) = w;
+                            else *(uint4*)(carry + ((st * SINK + (s - (PAGE_TOKENS - SINK))) * 16 + u) * 16) = w;
+                        }
+                        fence_async_proxy();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(st == 0 ? &full_k[j % NK] : &full_v[j % NV]);
+                    }
+                    asm volatile("bar.sync 9, 64;" ::: "memory");  // the new carry is complete before the next tile reads it
+                    if (has_page) {
+                        if (lane == 0) mbar_arrive(&free_raw[j % NR]);
+                        if (requester && j + NR < n_need) {
+                            wait_or_fail(&free_raw[j % NR], (uint32_t)((j / NR) & 1), fail_s);
+                            request(j + NR, pg_next);
+                            if (j + NR + 1 < n_need) pg_next = trow_p[j + NR + 1];
+                        }
                     }
                 }
             } else if constexpr (SRC == SRC_DENSE) {
@@ -567,7 +731,8 @@ bool attn_tc_supported(const b200kv_cache* c, int n_q_heads, int dtype, const vo
     if (D != 64 && D != 128) return false;
     if (dtype != B200KV_F16 && dtype != B200KV_BF16) return false;
     const bool pages16 = (fmt == B200KV_FMT_F16 && dtype == B200KV_F16) || (fmt == B200KV_FMT_BF16 && dtype == B200KV_BF16);
-    if (!(pages16 && D == 64) && !fmt_is_block_quant(fmt)) return false;
+    const bool kivi = fmt_is_kivi(fmt) && D == 128 && c->L.has_v;
+    if (!(pages16 && D == 64) && !fmt_is_block_quant(fmt) && !kivi) return false;
     const int G = n_q_heads / c->L.Hkv;
     if (G < 1 || G > AM) return false;
     return aligned16(q, qs, 3) && aligned16(out, os, 3);
@@ -594,7 +759,10 @@ int launch_attn_tc_paged(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, i
     cudaError_t e;
     {
         ProfScope ps(c, K_PREFILL, stream);
-        if (fmt_is_block_quant(c->L.fmt))
+        if (fmt_is_kivi(c->L.fmt)) {
+            p.kv = kivi_view(c);
+            e = launch_attn_nq<128, SRC_KIVI>(p, n_seqs, stream);
+        } else if (fmt_is_block_quant(c->L.fmt))
             e = c->L.D == 128 ? launch_attn_nq<128, SRC_PAGESQ>(p, n_seqs, stream) : launch_attn_nq<64, SRC_PAGESQ>(p, n_seqs, stream);
         else
             e = launch_attn_nq<64, SRC_PAGES16>(p, n_seqs, stream);

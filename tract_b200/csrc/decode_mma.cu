@@ -61,6 +61,7 @@ __global__ void __launch_bounds__(128, MGeo<FMT>::MIN_CTAS) decode_mma_kernel(De
     constexpr uint32_t OFFS_FRAG = FMT == B200KV_FMT_Q8_1 ? 0x00800080u : 0x00080008u;
     constexpr float TWO24 = 16777216.f;
     constexpr float PSCALE = 1024.f;  // probabilities * V scale are lifted into the normal f16 range
+    constexpr float LAZY_MAX = 1.f;   // see the softmax below
 
     // declared aligned (not rounded up by hand) so that the compiler keeps every access in the shared window
     extern __shared__ __align__(1024) uint8_t stages[];
@@ -246,14 +247,16 @@ __global__ void __launch_bounds__(128, MGeo<FMT>::MIN_CTAS) decode_mma_kernel(De
             // ================= online softmax (log2 domain), heads 2c and 2c + 1 =================
             const float s0 = vA ? sacc[0] * sl2 : -INFINITY, s1 = vA ? sacc[1] * sl2 : -INFINITY;
             const float s2 = vB ? sacc[2] * sl2 : -INFINITY, s3 = vB ? sacc[3] * sl2 : -INFINITY;
-            const float mn0 = fmaxf(m_run[0], quad_row_max(fmaxf(s0, s2)));
-            const float mn1 = fmaxf(m_run[1], quad_row_max(fmaxf(s1, s3)));
-            const float al0 = fast_ex2(m_run[0] - mn0), al1 = fast_ex2(m_run[1] - mn1);
-            const float p0 = fast_ex2(s0 - mn0), p1 = fast_ex2(s1 - mn1), p2 = fast_ex2(s2 - mn0), p3 = fast_ex2(s3 - mn1);
-            m_run[0] = mn0, m_run[1] = mn1;
-            l_part[0] = fmaf(l_part[0], al0, p0 + p2);
-            l_part[1] = fmaf(l_part[1], al1, p1 + p3);
-            if (__any_sync(0xffffffffu, al0 != 1.f || al1 != 1.f)) {
+            // The reference maximum of a head is raised only when a score of this warp exceeds it by more than 2^LAZY_MAX (a
+            // warp-wide vote): most pages then cost no cross-lane maximum, no rescaling of O and no exponentials of the
+            // correction factor, and the weights stay below 2^LAZY_MAX = 2, safe for the 16-bit operands they become.
+            const float lm0 = fmaxf(s0, s2), lm1 = fmaxf(s1, s3);
+            if (__any_sync(0xffffffffu, lm0 > m_run[0] + LAZY_MAX || lm1 > m_run[1] + LAZY_MAX)) {
+                const float mn0 = fmaxf(m_run[0], quad_row_max(lm0)), mn1 = fmaxf(m_run[1], quad_row_max(lm1));
+                // a head whose keys were all masked so far keeps -inf: its sums and outputs are zero, factor 1
+                const float al0 = mn0 == -INFINITY ? 1.f : fast_ex2(m_run[0] - mn0), al1 = mn1 == -INFINITY ? 1.f : fast_ex2(m_run[1] - mn1);
+                m_run[0] = mn0, m_run[1] = mn1;
+                l_part[0] *= al0, l_part[1] *= al1;
 #pragma unroll
                 for (int j = 0; j < 8; j++) o[j][0] *= al0, o[j][1] *= al1, o[j][2] *= al0, o[j][3] *= al1;
                 if (QUANT) {
@@ -262,6 +265,10 @@ __global__ void __launch_bounds__(128, MGeo<FMT>::MIN_CTAS) decode_mma_kernel(De
                     ob_unused0 = ob_unused1 = 0.f;  // kept finite
                 }
             }
+            const float mu0 = m_run[0] == -INFINITY ? 0.f : m_run[0], mu1 = m_run[1] == -INFINITY ? 0.f : m_run[1];  // exp2(-inf - 0) = 0
+            const float p0 = fast_ex2(s0 - mu0), p1 = fast_ex2(s1 - mu1), p2 = fast_ex2(s2 - mu0), p3 = fast_ex2(s3 - mu1);
+            l_part[0] += p0 + p2;
+            l_part[1] += p1 + p3;
 
             // ================= O^T[128 ch x 8 heads] += V^T . P^T =================
             if constexpr (QUANT) {

@@ -236,11 +236,17 @@ __global__ void __launch_bounds__(128, KGeo<BITS>::CTAS) kivi_mma_kernel(KiviMma
             const float bias0 = bh0.x + bh1.x, bias1 = bh0.y + bh1.y;
             const float s0 = fmaf(sacc[0], TWO24, bias0) * sl2, s1 = fmaf(sacc[1], TWO24, bias1) * sl2;
             const float s2 = fmaf(sacc[2], TWO24, bias0) * sl2, s3 = fmaf(sacc[3], TWO24, bias1) * sl2;
-            const float mn0 = fmaxf(m_run[0], quad_row_max(fmaxf(s0, s2)));
-            const float mn1 = fmaxf(m_run[1], quad_row_max(fmaxf(s1, s3)));
-            const float al0 = fast_ex2(m_run[0] - mn0), al1 = fast_ex2(m_run[1] - mn1);
-            const float p0 = fast_ex2(s0 - mn0), p1 = fast_ex2(s1 - mn1), p2 = fast_ex2(s2 - mn0), p3 = fast_ex2(s3 - mn1);
-            m_run[0] = mn0, m_run[1] = mn1;
+            // the reference maximum of a head is raised only when a score of this warp exceeds it by more than 2 (one
+            // warp-wide vote per page instead of two cross-lane maxima, a rescale test and the correction exponentials)
+            const float lm0 = fmaxf(s0, s2), lm1 = fmaxf(s1, s3);
+            float al0 = 1.f, al1 = 1.f;
+            const bool raise = __any_sync(0xffffffffu, lm0 > m_run[0] + 1.f || lm1 > m_run[1] + 1.f);
+            if (raise) {
+                const float mn0 = fmaxf(m_run[0], quad_row_max(lm0)), mn1 = fmaxf(m_run[1], quad_row_max(lm1));
+                al0 = fast_ex2(m_run[0] - mn0), al1 = fast_ex2(m_run[1] - mn1);  // every token here is live: the maxima are finite
+                m_run[0] = mn0, m_run[1] = mn1;
+            }
+            const float p0 = fast_ex2(s0 - m_run[0]), p1 = fast_ex2(s1 - m_run[1]), p2 = fast_ex2(s2 - m_run[0]), p3 = fast_ex2(s3 - m_run[1]);
             l_part[0] = fmaf(l_part[0], al0, p0 + p2);
             l_part[1] = fmaf(l_part[1], al1, p1 + p3);
             const float2 vpA = *(const float2*)(Vp + tA * 2), vpB = *(const float2*)(Vp + tB * 2);  // (lo, scale) of the two tokens
@@ -255,7 +261,7 @@ __global__ void __launch_bounds__(128, KGeo<BITS>::CTAS) kivi_mma_kernel(KiviMma
             ob[1] = fmaf(ob[1], al1, fmaf(p1, mA, p3 * mB));
             oc[0] = fmaf(oc[0], al0, fmaf(wA.x, kA, wB.x * kB));
             oc[1] = fmaf(oc[1], al1, fmaf(wA.y, kA, wB.y * kB));
-            if (__any_sync(0xffffffffu, al0 != 1.f || al1 != 1.f)) {
+            if (raise) {
 #pragma unroll
                 for (int j = 0; j < 8; j++) o[j][0] *= al0, o[j][1] *= al1, o[j][2] *= al0, o[j][3] *= al1;
             }
