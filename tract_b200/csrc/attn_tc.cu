@@ -17,10 +17,13 @@
 // lazily raised reference maximum, P written over S with tcgen05.st as a 16-bit value plus its rounding remainder),
 // O += P . V  (A from TMEM, V as an MN-major operand).  What differs is who fills the K / V operand rings:
 //   SRC_PAGES16  a copy warp: one untiled cp.async.bulk per chunk, the page bytes ARE the operand tile (head_dim 64 here)
-//   SRC_PAGESQ   the raw quantised chunk pair of a page lands (cp.async.bulk) in a small ring; two converter warps turn
-//                codes * f32(f16 scale) (q8_1.rs:50-63, q4_0.rs:82-95: exact in f32) into 16-bit rows of the operand tile,
-//                and the first of them requests the raw pages
-//   SRC_KIVI     the same for the stores of transformers/src/ops/quant_dyn_kv_cache.rs: keys 0 .. 3 are the f32 sinks, key
+//   SRC_Q8, _Q4  the raw quantised chunk pair of a page lands (cp.async.bulk) in a small ring; two converter warps turn
+//                code * f32(f16 scale) (q8_1.rs:50-63, q4_0.rs:82-95) into f16 rows of the operand tiles, and the first of
+//                them requests the raw pages.  The operands are f16 whatever the query type (bf16 queries are widened
+//                to f16 on their way in: bf16 would keep 8 bits of a dequantised value), and K goes in as the rounded
+//                product plus its exact remainder (two tiles, two products per score): with sharply peaked attention
+//                the 2^-12 that rounding K to f16 loses is visible in the scores, while V tolerates it
+//   SRC_KIVI8/4  the same for the stores of transformers/src/ops/quant_dyn_kv_cache.rs: keys 0 .. 3 are the f32 sinks, key
 //                4 + i sits in slot i % 64 of storage page i / 64, so a tile of 64 keys is the last 4 slots of one page
 //                (carried over in shared memory from the tile before) and the first 60 of the next; keys of finalised
 //                32-token blocks are lo[c] + code * scale[c], the rest come from the f32 residual rows, values are
@@ -41,10 +44,12 @@ constexpr int A_SM_THREADS = 256;  // softmax threads per query tile
 constexpr int A_FILL_THREADS = 64; // converter / loader threads
 constexpr int A_XCHG = 2 * AM + 8; // per tile and page parity: the two half-row maxima of every row, one flag per softmax warp
 constexpr float A_SKIP_FRACTION = 0.125f;
-enum { SRC_PAGES16 = 0, SRC_PAGESQ = 1, SRC_DENSE = 2, SRC_KIVI = 3 };
+enum { SRC_PAGES16 = 0, SRC_Q8 = 1, SRC_DENSE = 2, SRC_KIVI8 = 3, SRC_Q4 = 4, SRC_KIVI4 = 5 };
+constexpr bool src_is_kivi(int src) { return src == SRC_KIVI8 || src == SRC_KIVI4; }
+constexpr bool src_is_block(int src) { return src == SRC_Q8 || src == SRC_Q4; }
 constexpr int A_KIVI_KP = 2 * 2 * 128 * 4;        // K parameters of a page: 2 blocks x (lo[128], scale[128]) f32
 constexpr int A_KIVI_VP = PAGE_TOKENS * 2 * 4;    // V parameters of a page: (lo, scale) f32 per token
-constexpr int A_CARRY = 2 * SINK * 128 * 2;      // 16-bit K and V rows of the last 4 slots of a KIVI page: they open the next tile
+constexpr int A_CARRY = 2 * SINK * 128 * 2;      // f16 K and V rows of the last 4 slots of a KIVI page: they open the next tile (the K remainders follow)
 
 template <int NQ, int D, int SRC>
 struct AGeo {
@@ -52,19 +57,21 @@ struct AGeo {
     static constexpr int CHUNK = PAGE_TOKENS * D * 2; // bytes of one K (or V) operand tile: 64 keys
     static constexpr int QBYTES = AM * D * 2;
     static constexpr bool FILL = SRC != SRC_PAGES16;
-    static constexpr bool RAW = SRC == SRC_PAGESQ || SRC == SRC_KIVI;                   // a ring of raw page bytes beside the operand rings
-    static constexpr int NK = NQ == 2 ? (D == 128 && RAW ? 3 : 4) : 3;  // K stages
-    static constexpr int NV = NQ == 2 ? (D == 128 && RAW ? 4 : 5) : 3;  // V stages
-    static constexpr int NR = 2;                                                          // raw stages (SRC_PAGESQ)
-    static constexpr int RAW_STAGE = SRC == SRC_PAGESQ ? 2 * (PAGE_TOKENS * D + PAGE_TOKENS * (D / 32) * 2)   // a Q8_1 chunk pair
-                                     : SRC == SRC_KIVI ? 2 * PAGE_TOKENS * D + A_KIVI_KP + A_KIVI_VP  // int8 codes of K and V, their parameters
-                                                       : 0;
+    static constexpr bool RAW = src_is_block(SRC) || src_is_kivi(SRC);  // a ring of raw page bytes beside the operand rings
+    static constexpr int KPARTS = RAW ? 2 : 1;                          // K operand tiles per 64 keys: value, or value + remainder
+    static constexpr int KSTAGE = KPARTS * CHUNK;
+    static constexpr int NK = RAW ? 2 : (NQ == 2 ? 4 : 3);              // K stages
+    static constexpr int NV = RAW ? 3 : (NQ == 2 ? 5 : 4);              // V stages
+    static constexpr int NR = 2;                                        // raw stages
+    static constexpr int RAW_STAGE = src_is_block(SRC) ? 2 * (PAGE_TOKENS * D + PAGE_TOKENS * (D / 32) * 2)   // a Q8_1 chunk pair (Q4_0: smaller)
+                                     : src_is_kivi(SRC) ? 2 * PAGE_TOKENS * D + A_KIVI_KP + A_KIVI_VP         // int8 codes of K and V, their parameters
+                                                        : 0;
     // softmax threads, one MMA warp per tile, then either the copy warp (16-bit pages) or the two converter / loader warps
     static constexpr int THREADS = NQ * A_SM_THREADS + 32 * NQ + (FILL ? A_FILL_THREADS : 32);
     static constexpr int N_BARS = 2 * NK + 2 * NV + 6 * NQ + 2 * NR;
     static constexpr uint32_t COL_S = D, COLS_PER_TILE = 256;  // TMEM: O in columns 0 .. D-1, the two S buffers after it
-    static constexpr size_t SMEM = (size_t)NQ * QBYTES + (size_t)(NK + NV) * CHUNK + (size_t)NR * RAW_STAGE + N_BARS * 8 + 32 +
-                                   NQ * 2 * A_XCHG * 4 + (SRC == SRC_KIVI ? A_CARRY : 0);
+    static constexpr size_t SMEM = (size_t)NQ * QBYTES + (size_t)NK * KSTAGE + (size_t)NV * CHUNK + (size_t)NR * RAW_STAGE + N_BARS * 8 + 32 +
+                                   NQ * 2 * A_XCHG * 4 + (src_is_kivi(SRC) ? A_CARRY + A_CARRY / 2 : 0);
 };
 
 struct AttnParams {
@@ -89,7 +96,7 @@ struct AttnParams {
     const void* mask;
     int64_t mb, mh, mq, mk;
     int32_t mask_dtype;
-    // KIVI stores (SRC_KIVI); desc then holds {sequence, cached length} per batch entry
+    // KIVI stores; desc then holds {sequence, cached length} per batch entry
     KiviView kv;
 };
 
@@ -102,55 +109,92 @@ template <int N>
 __device__ inline void cp_async_wait_group() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 __device__ inline void fence_async_proxy() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
-// One K or V chunk of a block-quantised page (as it lies in the pool) -> the 16-bit operand tile: thread t of 64 takes the
-// 8 channels of unit u = t % (D / 8) of every (64 / (D / 8))-th token.  Rows from n_valid on are zero-filled.
-template <int D>
-__device__ inline void convert_chunk(const uint8_t* raw, uint8_t* dst, int fmt, int kv, bool is_bf16, int n_valid, int t) {
-    constexpr int UNITS = D / 8, TLN = A_FILL_THREADS / UNITS;
-    const int u = t % UNITS, tl = t / UNITS;
-    const int ch0 = 8 * u, blk = ch0 / 32;
-    const bool perm = v_permuted(fmt, D, kv);
-    const __half* scales = (const __half*)(raw + PAGE_TOKENS * fmt_row_bytes(fmt, D));
-    int pos[8];  // permuted rows: where the codes of this thread's 8 channels sit
-    if (perm) {
-#pragma unroll
-        for (int e = 0; e < 8; e++) pos[e] = code_pos(fmt, D, kv, ch0 + e);
-    }
-    const int nib = perm ? code_nibble(fmt, D, kv, ch0) : (ch0 % 32) / 16;  // Q4_0: the same for all 8 channels of a unit
-    const int pos0 = fmt == B200KV_FMT_Q8_1 ? ch0 : (ch0 / 32) * 16 + ch0 % 16;  // natural rows: 8 contiguous bytes
+// ---- block-quantised chunk -> f16 operand tile(s) ----------------------------------------------------------------------
+// Codes become exact f16 integers with byte permutes and one packed subtraction (0x6400 | u is the f16 1024 + u), the
+// product with the f16 scale is one packed multiply, rounded once: RN_f16(code * scale), what rounding the reference's
+// exact f32 product to f16 gives; for K a packed FMA returns the remainder code * scale - RN(code * scale), exact.
+constexpr uint32_t H_MAGIC = 0x64646464u;  // source of the 0x64 high bytes
+__device__ inline uint32_t hsub2(uint32_t a, uint32_t b) {
+    const __half2 r = __hsub2(*(const __half2*)&a, *(const __half2*)&b);
+    return *(const uint32_t*)&r;
+}
+__device__ inline uint32_t hmul2(uint32_t a, uint32_t b) {
+    const __half2 r = __hmul2(*(const __half2*)&a, *(const __half2*)&b);
+    return *(const uint32_t*)&r;
+}
+__device__ inline uint32_t hfma2_rem(uint32_t a, uint32_t b, uint32_t prod) {  // a * b - prod
+    const __half2 r = __hfma2(*(const __half2*)&a, *(const __half2*)&b, __hneg2(*(const __half2*)&prod));
+    return *(const uint32_t*)&r;
+}
+// where unit u (8 channels, 16 bytes) of row `row` lies in an operand tile
+__device__ inline uint32_t tile_off(int u, int row) { return (u / 8) * (PAGE_TOKENS * 128) + row * 128 + (((u % 8) ^ (row & 7)) << 4); }
+
+// Thread t of the 64 converter threads takes item t % (D / 16) -- 16 channels, two units of 8 -- of every (64 * 16 / D)-th
+// token: the 16 codes of an item come from one 16- or 8-byte load of a natural row (Q4_0: low and high nibbles of the same
+// 8 bytes are the two units), or from 8 two-byte (Q8_1) / one-byte (Q4_0) loads of a permuted V row.  `lo_tile` (K): the
+// tile that takes the remainders.  Rows from n_valid on are zero-filled.
+template <int FMT, int D, int KV>
+__device__ inline void convert_chunk(const uint8_t* raw, uint8_t* hi_tile, uint8_t* lo_tile, int n_valid, int t) {
+    constexpr bool PERM = v_permuted(FMT, D, KV), Q8 = FMT == B200KV_FMT_Q8_1, SPLIT = KV == 0;
+    constexpr int ITEMS = D / 16, TLN = A_FILL_THREADS / ITEMS;
+    constexpr uint32_t BIAS = Q8 ? 0x64806480u : 0x64086408u;  // f16 pair 1024 + 128 | 1024 + 8: what the codes are offset by
+    const int item = t % ITEMS, tl = t / ITEMS;
+    const __half* scales = (const __half*)(raw + PAGE_TOKENS * fmt_row_bytes(FMT, D));
+    // the two units the item yields, and their blocks
+    int ua, ub;
+    if (Q8 || PERM) ua = 2 * item, ub = 2 * item + 1;
+    else ua = 4 * (item / 2) + (item % 2), ub = ua + 2;  // Q4_0 natural: bytes 16b + 8q .. hold channels 32b + 8q .. (low) and + 16 (high)
+    const int blk_a = ua / 4, blk_b = ub / 4;
 #pragma unroll 2
     for (int tt = 0; tt < PAGE_TOKENS / TLN; tt++) {
         const int tok = tt * TLN + tl;
-        uint32_t w[4] = {0u, 0u, 0u, 0u};
-        if (tok < n_valid) {
-            const float sc = __half2float(scales[scale_index(fmt, D, kv, tok, blk)]);
-            uint32_t b[8];
-            if (perm) {
+        uint32_t ca[4], cb[4];  // f16 pairs: the codes of unit ua / ub as 1024 + u
+        if constexpr (Q8 && !PERM) {
+            const uint4 x = *(const uint4*)(raw + chunk_addr(FMT, D, KV, tok, 16 * item));
+            ca[0] = __byte_perm(x.x, H_MAGIC, 0x4140), ca[1] = __byte_perm(x.x, H_MAGIC, 0x4342);
+            ca[2] = __byte_perm(x.y, H_MAGIC, 0x4140), ca[3] = __byte_perm(x.y, H_MAGIC, 0x4342);
+            cb[0] = __byte_perm(x.z, H_MAGIC, 0x4140), cb[1] = __byte_perm(x.z, H_MAGIC, 0x4342);
+            cb[2] = __byte_perm(x.w, H_MAGIC, 0x4140), cb[3] = __byte_perm(x.w, H_MAGIC, 0x4342);
+        } else if constexpr (Q8) {  // permuted V row: bytes 16r + 2 item, + 1 hold channels 16 item + r and + 8
 #pragma unroll
-                for (int e = 0; e < 8; e++) b[e] = raw[chunk_addr(fmt, D, kv, tok, pos[e])];
-            } else {
-                const uint2 x = *(const uint2*)(raw + chunk_addr(fmt, D, kv, tok, pos0));
-#pragma unroll
-                for (int e = 0; e < 4; e++) b[e] = (x.x >> (8 * e)) & 0xffu, b[4 + e] = (x.y >> (8 * e)) & 0xffu;
+            for (int i = 0; i < 4; i++) {
+                const uint32_t h0 = *(const uint16_t*)(raw + chunk_addr(FMT, D, KV, tok, 16 * (2 * i) + 2 * item));
+                const uint32_t h1 = *(const uint16_t*)(raw + chunk_addr(FMT, D, KV, tok, 16 * (2 * i + 1) + 2 * item));
+                const uint32_t both = __byte_perm(h0, h1, 0x5410);  // [low r, high r, low r + 1, high r + 1]
+                ca[i] = __byte_perm(both, H_MAGIC, 0x4240), cb[i] = __byte_perm(both, H_MAGIC, 0x4341);
             }
-            float f[8];
+        } else if constexpr (!PERM) {  // Q4_0 natural row
+            const uint2 x = *(const uint2*)(raw + chunk_addr(FMT, D, KV, tok, 16 * (item / 2) + 8 * (item % 2)));
+            const uint32_t l0 = x.x & 0x0f0f0f0fu, h0 = (x.x >> 4) & 0x0f0f0f0fu, l1 = x.y & 0x0f0f0f0fu, h1 = (x.y >> 4) & 0x0f0f0f0fu;
+            ca[0] = __byte_perm(l0, H_MAGIC, 0x4140), ca[1] = __byte_perm(l0, H_MAGIC, 0x4342);
+            ca[2] = __byte_perm(l1, H_MAGIC, 0x4140), ca[3] = __byte_perm(l1, H_MAGIC, 0x4342);
+            cb[0] = __byte_perm(h0, H_MAGIC, 0x4140), cb[1] = __byte_perm(h0, H_MAGIC, 0x4342);
+            cb[2] = __byte_perm(h1, H_MAGIC, 0x4140), cb[3] = __byte_perm(h1, H_MAGIC, 0x4342);
+        } else {  // Q4_0 permuted V row: byte 8r + item holds channel 16 item + r (low nibble) and + 8 (high nibble)
 #pragma unroll
-            for (int e = 0; e < 8; e++) {
-                const int code = fmt == B200KV_FMT_Q8_1 ? (int)b[e] - 128 : (int)((b[e] >> (4 * nib)) & 0xfu) - 8;
-                f[e] = __fmul_rn((float)code, sc);
-            }
-#pragma unroll
-            for (int e = 0; e < 4; e++) {
-                if (is_bf16) {
-                    const __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * e], f[2 * e + 1]);
-                    w[e] = *(const uint32_t*)&h;
-                } else {
-                    const __half2 h = __floats2half2_rn(f[2 * e], f[2 * e + 1]);
-                    w[e] = *(const uint32_t*)&h;
-                }
+            for (int i = 0; i < 4; i++) {
+                const uint32_t b0 = raw[chunk_addr(FMT, D, KV, tok, 8 * (2 * i) + item)], b1 = raw[chunk_addr(FMT, D, KV, tok, 8 * (2 * i + 1) + item)];
+                const uint32_t both = b0 | (b1 << 16);
+                ca[i] = (both & 0x000f000fu) | 0x64006400u, cb[i] = ((both >> 4) & 0x000f000fu) | 0x64006400u;
             }
         }
-        *(uint4*)(dst + (u / 8) * (PAGE_TOKENS * 128) + tok * 128 + (((u % 8) ^ (tok & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        const uint32_t sa16 = __half_as_ushort(scales[scale_index(FMT, D, KV, tok, blk_a)]);
+        const uint32_t sb16 = __half_as_ushort(scales[scale_index(FMT, D, KV, tok, blk_b)]);
+        const uint32_t sa = sa16 | (sa16 << 16), sb = sb16 | (sb16 << 16);
+        uint32_t ha[4], hb[4], la[4], lb[4];
+        const bool ok = tok < n_valid;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const uint32_t xa = hsub2(ca[i], BIAS), xb = hsub2(cb[i], BIAS);  // the codes themselves
+            ha[i] = ok ? hmul2(xa, sa) : 0u, hb[i] = ok ? hmul2(xb, sb) : 0u;
+            if (SPLIT) la[i] = ok ? hfma2_rem(xa, sa, ha[i]) : 0u, lb[i] = ok ? hfma2_rem(xb, sb, hb[i]) : 0u;
+        }
+        *(uint4*)(hi_tile + tile_off(ua, tok)) = make_uint4(ha[0], ha[1], ha[2], ha[3]);
+        *(uint4*)(hi_tile + tile_off(ub, tok)) = make_uint4(hb[0], hb[1], hb[2], hb[3]);
+        if (SPLIT) {
+            *(uint4*)(lo_tile + tile_off(ua, tok)) = make_uint4(la[0], la[1], la[2], la[3]);
+            *(uint4*)(lo_tile + tile_off(ub, tok)) = make_uint4(lb[0], lb[1], lb[2], lb[3]);
+        }
     }
 }
 
@@ -158,15 +202,17 @@ template <int NQ, int D, int SRC>
 __global__ void __launch_bounds__(AGeo<NQ, D, SRC>::THREADS, 1) attn_tc_kernel(const __grid_constant__ AttnParams p) {
     using GEO = AGeo<NQ, D, SRC>;
     constexpr int NK = GEO::NK, NV = GEO::NV, NR = GEO::NR, CHUNK = GEO::CHUNK, QBYTES = GEO::QBYTES, PLANES = GEO::PLANES;
+    constexpr int KSTAGE = GEO::KSTAGE, KPARTS = GEO::KPARTS;
+    constexpr bool RAW = GEO::RAW;  // converted sources: f16 operands whatever the query type
     constexpr int DH = D / 2;  // output channels per softmax thread
     constexpr uint32_t COL_O = 0, COL_S = GEO::COL_S, COLS_PER_TILE = GEO::COLS_PER_TILE;
     constexpr int FILL_ARRIVALS = SRC == SRC_PAGES16 ? 1 : A_FILL_THREADS / 32;
-    static_assert(SRC != SRC_KIVI || D == 128, "the KIVI stores have their tensor-core layout at head_dim 128 only");
+    static_assert(!src_is_kivi(SRC) || D == 128, "the KIVI stores have their tensor-core layout at head_dim 128 only");
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* q_s = smem;                                    // [NQ][PLANES][128 rows][128 B], swizzled
-    uint8_t* k_ring = smem + NQ * QBYTES;                   // NK K tiles
-    uint8_t* v_ring = k_ring + NK * CHUNK;                  // NV V tiles
-    uint8_t* raw_ring = v_ring + NV * CHUNK;                // NR raw chunk pairs (SRC_PAGESQ)
+    uint8_t* k_ring = smem + NQ * QBYTES;                   // NK K stages of KPARTS tiles
+    uint8_t* v_ring = k_ring + NK * KSTAGE;                 // NV V tiles
+    uint8_t* raw_ring = v_ring + NV * CHUNK;                // NR raw stages (converted sources)
     uint64_t* full_k = (uint64_t*)(raw_ring + NR * GEO::RAW_STAGE);  // [NK] the tile is complete
     uint64_t* full_v = full_k + NK;                         // [NV]
     uint64_t* free_k = full_v + NV;                         // [NK] every tile's Q.K^T on the stage has completed
@@ -214,6 +260,7 @@ __global__ void __launch_bounds__(AGeo<NQ, D, SRC>::THREADS, 1) attn_tc_kernel(c
     const int my_limit = p.causal ? P0 + my_q : T - 1;  // last visible key of this row
     const int min_limit = p.causal ? P0 + min(q0, p.S - 1) : T - 1;  // last key EVERY row of the tile sees
     const bool is_softmax = tid < NQ * A_SM_THREADS;
+    const int mma_bf16 = RAW ? 0 : p.is_bf16;  // type of the tensor-core operands (Q, K, V, P)
 
     // ---- Q tile -> shared memory, K-major with the 128-byte swizzle (row r: 16-byte unit u of a plane at u ^ (r & 7));
     //      this thread moves the DH channels of its half of its row ----
@@ -223,7 +270,15 @@ __global__ void __launch_bounds__(AGeo<NQ, D, SRC>::THREADS, 1) attn_tc_kernel(c
         const uint4* src = (const uint4*)((const uint16_t*)p.q + (int64_t)b * p.qb + (int64_t)head * p.qh + (int64_t)my_q * p.qs) + half * NU;
 #pragma unroll
         for (int uu = 0; uu < NU; uu++) {
-            const uint4 v = live ? src[uu] : make_uint4(0, 0, 0, 0);
+            uint4 v = live ? src[uu] : make_uint4(0, 0, 0, 0);
+            if (RAW && p.is_bf16) {  // bf16 queries over converted pages: every bf16 value is an f16 value (short of its range)
+                uint32_t* w = &v.x;
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const __half2 h = __floats2half2_rn(__uint_as_float(w[e] << 16), __uint_as_float(w[e] & 0xffff0000u));
+                    w[e] = *(const uint32_t*)&h;
+                }
+            }
             const int unit = half * NU + uu, plane = unit / 8, u8 = unit % 8;
             *(uint4*)(q_s + qt * QBYTES + plane * (AM * 128) + row * 128 + ((u8 ^ (row & 7)) << 4)) = v;
         }
@@ -266,27 +321,29 @@ __global__ void __launch_bounds__(AGeo<NQ, D, SRC>::THREADS, 1) attn_tc_kernel(c
             // ================= MMAs of tile t = role =================
             const int t = role;
             const uint32_t tm = tmem + t * COLS_PER_TILE;
-            const uint32_t idesc_s = instr_desc(p.is_bf16, 0, AM, PAGE_TOKENS);
-            const uint32_t idesc_o = instr_desc(p.is_bf16, 1, AM, D);
+            const uint32_t idesc_s = instr_desc(mma_bf16, 0, AM, PAGE_TOKENS);
+            const uint32_t idesc_o = instr_desc(mma_bf16, 1, AM, D);
             // descriptors of the ring bases; a byte offset inside the 256 KiB window adds offset / 16 to the address field
             const uint64_t q_desc = smem_desc(smem_u32(q_s) + t * QBYTES, 0, 1024);
             const uint64_t k_desc = smem_desc(smem_u32(k_ring), 0, 1024);
             // V tile: planes of 64 channels 8192 bytes apart (leading dimension), 8-key groups 1024 bytes apart
             const uint64_t v_desc = smem_desc(smem_u32(v_ring), PAGE_TOKENS * 128, 1024);
-            const bool adaptive = !p.is_bf16;
+            const bool adaptive = !mma_bf16;
             auto issue_qk = [&](int j) {  // S(j) = Q . K(j)^T into buffer j & 1
                 wait_or_fail(&full_k[j % NK], (uint32_t)((j / NK) & 1), fail_s);
                 tc_fence_after();
                 if (elect_one()) {
-                    const uint64_t kd = k_desc + (uint64_t)(((j % NK) * CHUNK) >> 4);
+                    const uint64_t kd = k_desc + (uint64_t)(((j % NK) * KSTAGE) >> 4);
 #pragma unroll
-                    for (int pl = 0; pl < PLANES; pl++)
+                    for (int part = 0; part < KPARTS; part++)  // K as value (+ remainder): both products land in the same S
 #pragma unroll
-                        for (int kk = 0; kk < 4; kk++) {
-                            const uint64_t off = (uint64_t)((pl * (AM * 128) + kk * 32) >> 4);
-                            tc_mma_ss(tm + COL_S + 64 * (j & 1), q_desc + off, kd + (uint64_t)((pl * (PAGE_TOKENS * 128) + kk * 32) >> 4),
-                                      idesc_s, (pl | kk) ? 1u : 0u);
-                        }
+                        for (int pl = 0; pl < PLANES; pl++)
+#pragma unroll
+                            for (int kk = 0; kk < 4; kk++) {
+                                const uint64_t off = (uint64_t)((pl * (AM * 128) + kk * 32) >> 4);
+                                tc_mma_ss(tm + COL_S + 64 * (j & 1), q_desc + off,
+                                          kd + (uint64_t)((part * CHUNK + pl * (PAGE_TOKENS * 128) + kk * 32) >> 4), idesc_s, (part | pl | kk) ? 1u : 0u);
+                            }
                     tc_commit(&bar_s[2 * t + (j & 1)]);
                     tc_commit(&free_k[j % NK]);
                 }
@@ -319,7 +376,8 @@ __global__ void __launch_bounds__(AGeo<NQ, D, SRC>::THREADS, 1) attn_tc_kernel(c
         } else {
             // ================= converter / loader warps: fill the operand rings =================
             const int ft = tid - (NQ * A_SM_THREADS + 32 * NQ);  // 0 .. 63
-            if constexpr (SRC == SRC_PAGESQ) {
+            if constexpr (src_is_block(SRC)) {
+                constexpr int FMT = SRC == SRC_Q8 ? B200KV_FMT_Q8_1 : B200KV_FMT_Q4_0;
                 const bool requester = ft < 32;  // the first converter warp also requests the raw pages
                 const int32_t* trow_p = p.table + (int64_t)trow * p.max_pages_per_seq;
                 auto request = [&](int i, int32_t pg) {  // raw chunk pair of page i into stage i % NR
@@ -344,12 +402,12 @@ __global__ void __launch_bounds__(AGeo<NQ, D, SRC>::THREADS, 1) attn_tc_kernel(c
                     const int n_valid = min(PAGE_TOKENS, T - i * PAGE_TOKENS);
                     wait_or_fail(&full_raw[i % NR], (uint32_t)((i / NR) & 1), fail_s);
                     if (i >= NK) wait_or_fail(&free_k[i % NK], (uint32_t)((i / NK - 1) & 1), fail_s);
-                    convert_chunk<D>(raw, k_ring + (i % NK) * CHUNK, p.fmt, 0, p.is_bf16 != 0, n_valid, ft);
+                    convert_chunk<FMT, D, 0>(raw, k_ring + (i % NK) * KSTAGE, k_ring + (i % NK) * KSTAGE + CHUNK, n_valid, ft);
                     fence_async_proxy();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&full_k[i % NK]);
                     if (i >= NV) wait_or_fail(&free_v[i % NV], (uint32_t)((i / NV - 1) & 1), fail_s);
-                    convert_chunk<D>(raw + p.chunk_bytes, v_ring + (i % NV) * CHUNK, p.fmt, 1, p.is_bf16 != 0, n_valid, ft);
+                    convert_chunk<FMT, D, 1>(raw + p.chunk_bytes, v_ring + (i % NV) * CHUNK, nullptr, n_valid, ft);
                     fence_async_proxy();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&full_v[i % NV]), mbar_arrive(&free_raw[i % NR]);
@@ -359,12 +417,13 @@ __global__ void __launch_bounds__(AGeo<NQ, D, SRC>::THREADS, 1) attn_tc_kernel(c
                         if (i + NR + 1 < n_tiles) pg_next = trow_p[i + NR + 1];
                     }
                 }
-            } else if constexpr (SRC == SRC_KIVI) {
+            } else if constexpr (src_is_kivi(SRC)) {
+                constexpr int BITS = SRC == SRC_KIVI8 ? 8 : 4;
                 const KiviView& kw = p.kv;
                 const int32_t seq = trow;
                 const int KC = PAGE_TOKENS * kw.row_bytes;          // bytes of the K (or V) codes of a page and head
-                const int lfmt = kivi_layout_fmt(kw.bits);          // the block format whose row layout the codes borrow
-                const bool int4 = kw.bits == 4;
+                constexpr int lfmt = kivi_layout_fmt(BITS);         // the block format whose row layout the codes borrow
+                constexpr bool int4 = BITS == 4;
                 const int n_fin = max(T - SINK, 0) / KBLOCK;        // finalised key blocks
                 const int n_sp = T > SINK ? (T - SINK + PAGE_TOKENS - 1) / PAGE_TOKENS : 0;  // storage pages the sequence holds
                 const int n_need = min(n_sp, n_tiles);              // tile j reads page j (and, through the carry, page j - 1)
@@ -400,40 +459,41 @@ __global__ void __launch_bounds__(AGeo<NQ, D, SRC>::THREADS, 1) attn_tc_kernel(c
                 const int vnib = code_nibble(lfmt, 128, 1, ch0);
                 const float* sink_base = kw.sinks + (((int64_t)seq * kw.H + kvh) * 2) * SINK * D;
                 const float* resid = kw.residual + (((int64_t)seq * kw.H + kvh) * 2 + 0) * KBLOCK * D;
-                auto pack8 = [&](const float* f) {
-                    uint32_t w[4];
+                // 8 f32 values -> their f16 roundings and (K) the f16 roundings of what that lost
+                auto pack8 = [&](const float* f, uint4& hi, uint4& lo) {
+                    uint32_t wh[4], wl[4];
 #pragma unroll
                     for (int e = 0; e < 4; e++) {
-                        if (p.is_bf16) {
-                            const __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * e], f[2 * e + 1]);
-                            w[e] = *(const uint32_t*)&h;
-                        } else {
-                            const __half2 h = __floats2half2_rn(f[2 * e], f[2 * e + 1]);
-                            w[e] = *(const uint32_t*)&h;
-                        }
+                        const __half2 h = __floats2half2_rn(f[2 * e], f[2 * e + 1]);
+                        const __half2 l = __floats2half2_rn(f[2 * e] - __low2float(h), f[2 * e + 1] - __high2float(h));
+                        wh[e] = *(const uint32_t*)&h, wl[e] = *(const uint32_t*)&l;
                     }
-                    return make_uint4(w[0], w[1], w[2], w[3]);
+                    hi = make_uint4(wh[0], wh[1], wh[2], wh[3]), lo = make_uint4(wl[0], wl[1], wl[2], wl[3]);
                 };
-                auto tile_addr = [&](uint8_t* base, int row) { return base + (u / 8) * (PAGE_TOKENS * 128) + row * 128 + (((u % 8) ^ (row & 7)) << 4); };
+                auto tile_addr = [&](uint8_t* base, int row) { return base + tile_off(u, row); };
+                uint8_t* carry_lo = carry + A_CARRY;  // the remainders of the carried K rows
                 for (int j = 0; j < n_tiles; j++) {
                     const bool has_page = j < n_sp;
                     const uint8_t* raw = raw_ring + (j % NR) * GEO::RAW_STAGE;
                     if (has_page) wait_or_fail(&full_raw[j % NR], (uint32_t)((j / NR) & 1), fail_s);
                     // rows 0 .. 3 of the tile: the sinks (tile 0) or the last four slots of the page before; thread ft takes
                     // unit u of row ft / 16 for K and for V
-                    uint4 head[2];
+                    uint4 head[2], head_lo = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
                     for (int st = 0; st < 2; st++) {
                         head[st] = make_uint4(0u, 0u, 0u, 0u);
                         if (j * PAGE_TOKENS + tl < T) {
+                            uint4 lo4 = make_uint4(0u, 0u, 0u, 0u);
                             if (j == 0) {
                                 const float4* src = (const float4*)(sink_base + ((int64_t)st * SINK + tl) * D + ch0);
                                 const float4 a = src[0], b2 = src[1];
                                 const float f[8] = {a.x, a.y, a.z, a.w, b2.x, b2.y, b2.z, b2.w};
-                                head[st] = pack8(f);
+                                pack8(f, head[st], lo4);
                             } else {
                                 head[st] = *(const uint4*)(carry + ((st * SINK + tl) * 16 + u) * 16);
+                                if (st == 0) lo4 = *(const uint4*)(carry_lo + (tl * 16 + u) * 16);
                             }
+                            if (st == 0) head_lo = lo4;
                         }
                     }
                     asm volatile("bar.sync 9, 64;" ::: "memory");  // both converter warps have read the carry: it may be rewritten
@@ -442,7 +502,8 @@ __global__ void __launch_bounds__(AGeo<NQ, D, SRC>::THREADS, 1) attn_tc_kernel(c
                         uint8_t* dst;
                         if (st == 0) {
                             if (j >= NK) wait_or_fail(&free_k[j % NK], (uint32_t)((j / NK - 1) & 1), fail_s);
-                            dst = k_ring + (j % NK) * CHUNK;
+                            dst = k_ring + (j % NK) * KSTAGE;
+                            *(uint4*)tile_addr(dst + CHUNK, tl) = head_lo;
                         } else {
                             if (j >= NV) wait_or_fail(&free_v[j % NV], (uint32_t)((j / NV - 1) & 1), fail_s);
                             dst = v_ring + (j % NV) * CHUNK;
@@ -489,9 +550,15 @@ __global__ void __launch_bounds__(AGeo<NQ, D, SRC>::THREADS, 1) attn_tc_kernel(c
                                     }
                                 }
                             }
-                            const uint4 w = pack8(f);
-                            if (s < PAGE_TOKENS - SINK) *(uint4*)tile_addr(dst, s + SINK) = w;
-                            else *(uint4*)(carry + ((st * SINK + (s - (PAGE_TOKENS - SINK))) * 16 + u) * 16) = w;
+                            uint4 w, wl;
+                            pack8(f, w, wl);
+                            if (s < PAGE_TOKENS - SINK) {
+                                *(uint4*)tile_addr(dst, s + SINK) = w;
+                                if (st == 0) *(uint4*)tile_addr(dst + CHUNK, s + SINK) = wl;
+                            } else {
+                                *(uint4*)(carry + ((st * SINK + (s - (PAGE_TOKENS - SINK))) * 16 + u) * 16) = w;
+                                if (st == 0) *(uint4*)(carry_lo + ((s - (PAGE_TOKENS - SINK)) * 16 + u) * 16) = wl;
+                            }
                         }
                         fence_async_proxy();
                         __syncwarp();
@@ -514,10 +581,18 @@ __global__ void __launch_bounds__(AGeo<NQ, D, SRC>::THREADS, 1) attn_tc_kernel(c
                 const uint16_t* kbase = (const uint16_t*)p.k + (int64_t)b * p.kb + (int64_t)kvh * p.kh;
                 const uint16_t* vbase = (const uint16_t*)p.v + (int64_t)b * p.vb + (int64_t)kvh * p.vh;
                 for (int i = 0; i < n_tiles + LAG; i++) {
+                    // Announce page i - LAG before waiting for room for page i: the products that free a stage are issued
+                    // behind products that need the pages still to be announced, so the other order can wait for ever.
+                    if (i >= LAG) {
+                        cp_async_wait_group<LAG - 1>();  // all but the LAG - 1 newest groups: page i - LAG has landed
+                        fence_async_proxy();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&full_k[(i - LAG) % NK]), mbar_arrive(&full_v[(i - LAG) % NV]);
+                    }
                     if (i < n_tiles) {
                         if (i >= NK) wait_or_fail(&free_k[i % NK], (uint32_t)((i / NK - 1) & 1), fail_s);
                         if (i >= NV) wait_or_fail(&free_v[i % NV], (uint32_t)((i / NV - 1) & 1), fail_s);
-                        uint8_t* kd = k_ring + (i % NK) * CHUNK;
+                        uint8_t* kd = k_ring + (i % NK) * KSTAGE;
                         uint8_t* vd = v_ring + (i % NV) * CHUNK;
 #pragma unroll
                         for (int e = 0; e < PER_THREAD; e++) {
@@ -525,18 +600,12 @@ __global__ void __launch_bounds__(AGeo<NQ, D, SRC>::THREADS, 1) attn_tc_kernel(c
                             const int key = i * PAGE_TOKENS + r;
                             const bool ok = key < T;
                             const int64_t kr = ok ? key : 0;
-                            const int off = (u / 8) * (PAGE_TOKENS * 128) + r * 128 + (((u % 8) ^ (r & 7)) << 4);
+                            const int off = tile_off(u, r);
                             cp_async16_zfill(kd + off, kbase + kr * p.ks + u * 8, ok);
                             cp_async16_zfill(vd + off, vbase + kr * p.vs + u * 8, ok);
                         }
                     }
                     cp_async_commit_group();
-                    if (i >= LAG) {
-                        cp_async_wait_group<LAG>();  // the group of page i - LAG (and everything older) has landed
-                        fence_async_proxy();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(&full_k[(i - LAG) % NK]), mbar_arrive(&full_v[(i - LAG) % NV]);
-                    }
                 }
                 cp_async_wait_group<0>();
             }
@@ -545,7 +614,7 @@ __global__ void __launch_bounds__(AGeo<NQ, D, SRC>::THREADS, 1) attn_tc_kernel(c
         // ================= softmax threads =================
         const uint32_t lane_base = tmem + qt * COLS_PER_TILE + ((uint32_t)((w8 & 3) * 32) << 16);  // this warp's lane quarter
         const int pair_id = 1 + qt * 4 + (w8 & 3);        // named barrier of the two warps that share these 32 rows
-        const bool adaptive = !p.is_bf16;
+        const bool adaptive = !mma_bf16;
         const float sl2 = p.scale * 1.4426950408889634f;  // scores enter the exponent in log2 units
         float m_ref = -INFINITY, l_run = 0.f;             // l_run: this thread's half of the row sum
         // this row's mask values (dense source): element (my_q, key) at mrow + key * mk
@@ -628,7 +697,7 @@ __global__ void __launch_bounds__(AGeo<NQ, D, SRC>::THREADS, 1) attn_tc_kernel(c
                 const float p0 = fast_exp2(fmaf(__uint_as_float(sr[2 * c]), sl2, -m_use));
                 const float p1 = fast_exp2(fmaf(__uint_as_float(sr[2 * c + 1]), sl2, -m_use));
                 lsum += p0 + p1;
-                if (p.is_bf16) {
+                if (mma_bf16) {
                     const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
                     const __nv_bfloat162 l = __floats2bfloat162_rn(p0 - __low2float(h), p1 - __high2float(h));
                     pr[c] = *(const uint32_t*)&h, pr2[c] = *(const uint32_t*)&l;
@@ -761,9 +830,11 @@ int launch_attn_tc_paged(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, i
         ProfScope ps(c, K_PREFILL, stream);
         if (fmt_is_kivi(c->L.fmt)) {
             p.kv = kivi_view(c);
-            e = launch_attn_nq<128, SRC_KIVI>(p, n_seqs, stream);
-        } else if (fmt_is_block_quant(c->L.fmt))
-            e = c->L.D == 128 ? launch_attn_nq<128, SRC_PAGESQ>(p, n_seqs, stream) : launch_attn_nq<64, SRC_PAGESQ>(p, n_seqs, stream);
+            e = c->L.fmt == B200KV_FMT_KIVI8 ? launch_attn_nq<128, SRC_KIVI8>(p, n_seqs, stream) : launch_attn_nq<128, SRC_KIVI4>(p, n_seqs, stream);
+        } else if (c->L.fmt == B200KV_FMT_Q8_1)
+            e = c->L.D == 128 ? launch_attn_nq<128, SRC_Q8>(p, n_seqs, stream) : launch_attn_nq<64, SRC_Q8>(p, n_seqs, stream);
+        else if (c->L.fmt == B200KV_FMT_Q4_0)
+            e = c->L.D == 128 ? launch_attn_nq<128, SRC_Q4>(p, n_seqs, stream) : launch_attn_nq<64, SRC_Q4>(p, n_seqs, stream);
         else
             e = launch_attn_nq<64, SRC_PAGES16>(p, n_seqs, stream);
     }
