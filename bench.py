@@ -476,7 +476,8 @@ def run_prefill(ctx, workload, steps, warmup, min_seconds, quick=False, primary=
             "e2e": {"value": world * useful / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": hout.numel() * hout.element_size(), "ms_per_step": ms_e2e},
             "gpu_launches": steps * reps * 2, "kernels_ms": {k: statistics.median(v) for k, v in per_kernel.items()},
-            "roofline": {"bound": "tensor", "kernel": "prefill_tc_kernel" if k_name == "prefill" else "sdpa_dense_kernel", "achieved": achieved,
+            "roofline": {"bound": "tensor", "kernel": ("prefill_tc_kernel" if fmt in ("f16", "bf16") else "attn_tc_kernel") if k_name == "prefill" else "sdpa_dense_kernel",
+                         "achieved": achieved,
                          "peak": peak, "unit": "TFLOP/s", "kernel_ms": k_ms,
                          "frac": achieved / peak, "peak_kind": pk_kind + " (bf16 cuBLAS burst)", "traffic": None,
                          "flops": "causal-useful (masked half of the diagonal tiles not counted)"},
@@ -773,7 +774,9 @@ def run_head_sharded(ctx, steps, warmup):
     full.check(), layer.cache.check()
     diff = (got.float() - want.float()).abs().max().item()
     scale = want.float().pow(2).mean().sqrt().item()
-    ok = diff <= 8e-3 * scale  # a different split of the work: within one bf16 ulp of the tensor's scale
+    # a different split of the work (Hkv / N heads per launch): every element within one bf16 unit in the last place of
+    # the unsharded result (2^-7 of its magnitude at most), small elements within 2e-3 of the tensor's scale
+    ok = bool(((got.float() - want.float()).abs() <= want.float().abs() * 2.0 ** -7 + 2e-3 * scale).all().item())
     ok_all = ctx.sum_over_ranks(1.0 if ok else 0.0)[0] == world
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
     att, gat = [], []

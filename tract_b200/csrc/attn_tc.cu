@@ -17,7 +17,7 @@
 // lazily raised reference maximum, P written over S with tcgen05.st as a 16-bit value plus its rounding remainder),
 // O += P . V  (A from TMEM, V as an MN-major operand).  What differs is who fills the K / V operand rings:
 //   SRC_PAGES16  a copy warp: one untiled cp.async.bulk per chunk, the page bytes ARE the operand tile (head_dim 64 here)
-//   SRC_Q8, _Q4  the raw quantised chunk pair of a page lands (cp.async.bulk) in a small ring; two converter warps turn
+//   SRC_Q8, _Q4  the raw quantised chunk pair of a page lands (cp.async.bulk) in a small ring; four converter warps turn
 //                code * f32(f16 scale) (q8_1.rs:50-63, q4_0.rs:82-95) into f16 rows of the operand tiles, and the first of
 //                them requests the raw pages.  The operands are f16 whatever the query type (bf16 queries are widened
 //                to f16 on their way in: bf16 would keep 8 bits of a dequantised value), and K goes in as the rounded
@@ -41,7 +41,7 @@ namespace b200kv {
 
 constexpr int AM = 128;            // rows of a query tile
 constexpr int A_SM_THREADS = 256;  // softmax threads per query tile
-constexpr int A_FILL_THREADS = 64; // converter / loader threads
+constexpr int A_FILL_THREADS = 64; // converter / loader threads (the KIVI converter and the dense loader; block formats: FT)
 constexpr int A_XCHG = 2 * AM + 8; // per tile and page parity: the two half-row maxima of every row, one flag per softmax warp
 constexpr float A_SKIP_FRACTION = 0.125f;
 enum { SRC_PAGES16 = 0, SRC_Q8 = 1, SRC_DENSE = 2, SRC_KIVI8 = 3, SRC_Q4 = 4, SRC_KIVI4 = 5 };
@@ -51,7 +51,7 @@ constexpr int A_KIVI_KP = 2 * 2 * 128 * 4;        // K parameters of a page: 2 b
 constexpr int A_KIVI_VP = PAGE_TOKENS * 2 * 4;    // V parameters of a page: (lo, scale) f32 per token
 constexpr int A_CARRY = 2 * SINK * 128 * 2;      // f16 K and V rows of the last 4 slots of a KIVI page: they open the next tile (the K remainders follow)
 
-template <int NQ, int D, int SRC>
+template <int NQ, int D, int SRC, int FT = A_FILL_THREADS>
 struct AGeo {
     static constexpr int PLANES = D / 64;             // 128-byte wide column slabs of a row
     static constexpr int CHUNK = PAGE_TOKENS * D * 2; // bytes of one K (or V) operand tile: 64 keys
@@ -67,7 +67,7 @@ struct AGeo {
                                      : src_is_kivi(SRC) ? 2 * PAGE_TOKENS * D + A_KIVI_KP + A_KIVI_VP         // int8 codes of K and V, their parameters
                                                         : 0;
     // softmax threads, one MMA warp per tile, then either the copy warp (16-bit pages) or the two converter / loader warps
-    static constexpr int THREADS = NQ * A_SM_THREADS + 32 * NQ + (FILL ? A_FILL_THREADS : 32);
+    static constexpr int THREADS = NQ * A_SM_THREADS + 32 * NQ + (FILL ? FT : 32);
     static constexpr int N_BARS = 2 * NK + 2 * NV + 6 * NQ + 2 * NR;
     static constexpr uint32_t COL_S = D, COLS_PER_TILE = 256;  // TMEM: O in columns 0 .. D-1, the two S buffers after it
     static constexpr size_t SMEM = (size_t)NQ * QBYTES + (size_t)NK * KSTAGE + (size_t)NV * CHUNK + (size_t)NR * RAW_STAGE + N_BARS * 8 + 32 +
@@ -133,10 +133,10 @@ __device__ inline uint32_t tile_off(int u, int row) { return (u / 8) * (PAGE_TOK
 // token: the 16 codes of an item come from one 16- or 8-byte load of a natural row (Q4_0: low and high nibbles of the same
 // 8 bytes are the two units), or from 8 two-byte (Q8_1) / one-byte (Q4_0) loads of a permuted V row.  `lo_tile` (K): the
 // tile that takes the remainders.  Rows from n_valid on are zero-filled.
-template <int FMT, int D, int KV>
+template <int FMT, int D, int KV, int FT>
 __device__ inline void convert_chunk(const uint8_t* raw, uint8_t* hi_tile, uint8_t* lo_tile, int n_valid, int t) {
     constexpr bool PERM = v_permuted(FMT, D, KV), Q8 = FMT == B200KV_FMT_Q8_1, SPLIT = KV == 0;
-    constexpr int ITEMS = D / 16, TLN = A_FILL_THREADS / ITEMS;
+    constexpr int ITEMS = D / 16, TLN = FT / ITEMS;
     constexpr uint32_t BIAS = Q8 ? 0x64806480u : 0x64086408u;  // f16 pair 1024 + 128 | 1024 + 8: what the codes are offset by
     const int item = t % ITEMS, tl = t / ITEMS;
     const __half* scales = (const __half*)(raw + PAGE_TOKENS * fmt_row_bytes(FMT, D));
@@ -145,8 +145,8 @@ __device__ inline void convert_chunk(const uint8_t* raw, uint8_t* hi_tile, uint8
     if (Q8 || PERM) ua = 2 * item, ub = 2 * item + 1;
     else ua = 4 * (item / 2) + (item % 2), ub = ua + 2;  // Q4_0 natural: bytes 16b + 8q .. hold channels 32b + 8q .. (low) and + 16 (high)
     const int blk_a = ua / 4, blk_b = ub / 4;
-#pragma unroll 2
-    for (int tt = 0; tt < PAGE_TOKENS / TLN; tt++) {
+#pragma unroll 4
+    for (int tt = 0; tt < PAGE_TOKENS / TLN; tt++) {  // independent tokens: unrolled so that their loads and chains overlap
         const int tok = tt * TLN + tl;
         uint32_t ca[4], cb[4];  // f16 pairs: the codes of unit ua / ub as 1024 + u
         if constexpr (Q8 && !PERM) {
@@ -198,15 +198,16 @@ __device__ inline void convert_chunk(const uint8_t* raw, uint8_t* hi_tile, uint8
     }
 }
 
-template <int NQ, int D, int SRC>
-__global__ void __launch_bounds__(AGeo<NQ, D, SRC>::THREADS, 1) attn_tc_kernel(const __grid_constant__ AttnParams p) {
-    using GEO = AGeo<NQ, D, SRC>;
+template <int NQ, int D, int SRC, int FT>
+__global__ void __launch_bounds__(AGeo<NQ, D, SRC, FT>::THREADS, 1) attn_tc_kernel(const __grid_constant__ AttnParams p) {
+    using GEO = AGeo<NQ, D, SRC, FT>;
     constexpr int NK = GEO::NK, NV = GEO::NV, NR = GEO::NR, CHUNK = GEO::CHUNK, QBYTES = GEO::QBYTES, PLANES = GEO::PLANES;
     constexpr int KSTAGE = GEO::KSTAGE, KPARTS = GEO::KPARTS;
     constexpr bool RAW = GEO::RAW;  // converted sources: f16 operands whatever the query type
     constexpr int DH = D / 2;  // output channels per softmax thread
     constexpr uint32_t COL_O = 0, COL_S = GEO::COL_S, COLS_PER_TILE = GEO::COLS_PER_TILE;
-    constexpr int FILL_ARRIVALS = SRC == SRC_PAGES16 ? 1 : A_FILL_THREADS / 32;
+    constexpr int FILL_ARRIVALS = SRC == SRC_PAGES16 ? 1 : FT / 32;
+    static_assert(FT == A_FILL_THREADS || src_is_block(SRC) || src_is_kivi(SRC), "the dense loader and the copy warp have a fixed thread count");
     static_assert(!src_is_kivi(SRC) || D == 128, "the KIVI stores have their tensor-core layout at head_dim 128 only");
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* q_s = smem;                                    // [NQ][PLANES][128 rows][128 B], swizzled
@@ -243,7 +244,7 @@ __global__ void __launch_bounds__(AGeo<NQ, D, SRC>::THREADS, 1) attn_tc_kernel(c
         for (int s = 0; s < NV; s++) mbar_init(&full_v[s], FILL_ARRIVALS), mbar_init(&free_v[s], NQ);
         for (int i = 0; i < 2 * NQ; i++) mbar_init(&bar_s[i], 1), mbar_init(&bar_p[i], A_SM_THREADS / 32);
         for (int i = 0; i < 2 * NQ; i++) mbar_init(&bar_o[i], 1);
-        for (int s = 0; s < NR; s++) mbar_init(&full_raw[s], 1), mbar_init(&free_raw[s], A_FILL_THREADS / 32);
+        for (int s = 0; s < NR; s++) mbar_init(&full_raw[s], 1), mbar_init(&free_raw[s], FT / 32);
         *fail_s = (smem_u32(smem) & 1023u) ? 1 : 0;  // the swizzled operand tiles need a 1024-byte aligned base
         mbar_fence_init();
     }
@@ -402,12 +403,12 @@ __global__ void __launch_bounds__(AGeo<NQ, D, SRC>::THREADS, 1) attn_tc_kernel(c
                     const int n_valid = min(PAGE_TOKENS, T - i * PAGE_TOKENS);
                     wait_or_fail(&full_raw[i % NR], (uint32_t)((i / NR) & 1), fail_s);
                     if (i >= NK) wait_or_fail(&free_k[i % NK], (uint32_t)((i / NK - 1) & 1), fail_s);
-                    convert_chunk<FMT, D, 0>(raw, k_ring + (i % NK) * KSTAGE, k_ring + (i % NK) * KSTAGE + CHUNK, n_valid, ft);
+                    convert_chunk<FMT, D, 0, FT>(raw, k_ring + (i % NK) * KSTAGE, k_ring + (i % NK) * KSTAGE + CHUNK, n_valid, ft);
                     fence_async_proxy();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&full_k[i % NK]);
                     if (i >= NV) wait_or_fail(&free_v[i % NV], (uint32_t)((i / NV - 1) & 1), fail_s);
-                    convert_chunk<FMT, D, 1>(raw + p.chunk_bytes, v_ring + (i % NV) * CHUNK, nullptr, n_valid, ft);
+                    convert_chunk<FMT, D, 1, FT>(raw + p.chunk_bytes, v_ring + (i % NV) * CHUNK, nullptr, n_valid, ft);
                     fence_async_proxy();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&full_v[i % NV]), mbar_arrive(&free_raw[i % NR]);
@@ -451,7 +452,9 @@ __global__ void __launch_bounds__(AGeo<NQ, D, SRC>::THREADS, 1) attn_tc_kernel(c
                     for (int i = 0; i < NR && i < n_need; i++) request(i, trow_p[i]);
                     if (NR < n_need) pg_next = trow_p[NR];
                 }
-                const int u = ft % 16, tl = ft / 16, ch0 = 8 * u;   // this thread's 8 channels; token lane 0 .. 3
+                constexpr int TLK = FT / 16;                          // token lanes
+                const int u = ft % 16, tl = ft / 16, ch0 = 8 * u;   // this thread's 8 channels; token lane 0 .. TLK - 1
+                const bool heads_row = tl < SINK;                    // the first 64 threads also place rows 0 .. 3 of a tile
                 const int kpos0 = int4 ? (ch0 / 32) * 16 + ch0 % 16 : ch0, knib = int4 ? (ch0 % 32) / 16 : 0;
                 int vpos[8];
 #pragma unroll
@@ -482,7 +485,7 @@ __global__ void __launch_bounds__(AGeo<NQ, D, SRC>::THREADS, 1) attn_tc_kernel(c
 #pragma unroll
                     for (int st = 0; st < 2; st++) {
                         head[st] = make_uint4(0u, 0u, 0u, 0u);
-                        if (j * PAGE_TOKENS + tl < T) {
+                        if (heads_row && j * PAGE_TOKENS + tl < T) {
                             uint4 lo4 = make_uint4(0u, 0u, 0u, 0u);
                             if (j == 0) {
                                 const float4* src = (const float4*)(sink_base + ((int64_t)st * SINK + tl) * D + ch0);
@@ -496,25 +499,25 @@ __global__ void __launch_bounds__(AGeo<NQ, D, SRC>::THREADS, 1) attn_tc_kernel(c
                             if (st == 0) head_lo = lo4;
                         }
                     }
-                    asm volatile("bar.sync 9, 64;" ::: "memory");  // both converter warps have read the carry: it may be rewritten
+                    asm volatile("bar.sync 9, %0;" ::"n"(FT) : "memory");  // every converter warp has read the carry: it may be rewritten
 #pragma unroll 1
                     for (int st = 0; st < 2; st++) {  // K, then V
                         uint8_t* dst;
                         if (st == 0) {
                             if (j >= NK) wait_or_fail(&free_k[j % NK], (uint32_t)((j / NK - 1) & 1), fail_s);
                             dst = k_ring + (j % NK) * KSTAGE;
-                            *(uint4*)tile_addr(dst + CHUNK, tl) = head_lo;
+                            if (heads_row) *(uint4*)tile_addr(dst + CHUNK, tl) = head_lo;
                         } else {
                             if (j >= NV) wait_or_fail(&free_v[j % NV], (uint32_t)((j / NV - 1) & 1), fail_s);
                             dst = v_ring + (j % NV) * CHUNK;
                         }
-                        *(uint4*)tile_addr(dst, tl) = head[st];
+                        if (heads_row) *(uint4*)tile_addr(dst, tl) = head[st];
                         const uint8_t* codes = raw + st * KC;
                         const float* kpar = (const float*)(raw + 2 * KC);
                         const float2* vpar = (const float2*)(raw + 2 * KC + A_KIVI_KP);
 #pragma unroll 2
-                        for (int tt = 0; tt < PAGE_TOKENS / 4; tt++) {
-                            const int s = tt * 4 + tl;                  // slot in storage page j
+                        for (int tt = 0; tt < PAGE_TOKENS / TLK; tt++) {
+                            const int s = tt * TLK + tl;                // slot in storage page j
                             const int i = j * PAGE_TOKENS + s;          // storage index; key i + 4
                             float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
                             if (has_page && i + SINK < T) {
@@ -564,7 +567,7 @@ __global__ void __launch_bounds__(AGeo<NQ, D, SRC>::THREADS, 1) attn_tc_kernel(c
                         __syncwarp();
                         if (lane == 0) mbar_arrive(st == 0 ? &full_k[j % NK] : &full_v[j % NV]);
                     }
-                    asm volatile("bar.sync 9, 64;" ::: "memory");  // the new carry is complete before the next tile reads it
+                    asm volatile("bar.sync 9, %0;" ::"n"(FT) : "memory");  // the new carry is complete before the next tile reads it
                     if (has_page) {
                         if (lane == 0) mbar_arrive(&free_raw[j % NR]);
                         if (requester && j + NR < n_need) {
@@ -774,14 +777,15 @@ static bool aligned16(const void* ptr, const int64_t* st, int n) {
     return true;
 }
 
-template <int NQ, int D, int SRC>
+template <int NQ, int D, int SRC, int FT = A_FILL_THREADS>
 static cudaError_t launch_attn(const AttnParams& p, int n_batch, cudaStream_t stream) {
-    using GEO = AGeo<NQ, D, SRC>;
-    cudaError_t e = cudaFuncSetAttribute(attn_tc_kernel<NQ, D, SRC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEO::SMEM);
+    using GEO = AGeo<NQ, D, SRC, FT>;
+    static_assert(GEO::SMEM <= 227 * 1024, "the operand rings do not fit the shared memory of an SM");
+    cudaError_t e = cudaFuncSetAttribute(attn_tc_kernel<NQ, D, SRC, FT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEO::SMEM);
     if (e != cudaSuccess) return e;
     const int per_cta = NQ * (AM / p.G);
     dim3 grid((p.S + per_cta - 1) / per_cta, p.Hkv, n_batch);
-    attn_tc_kernel<NQ, D, SRC><<<grid, GEO::THREADS, GEO::SMEM, stream>>>(p);
+    attn_tc_kernel<NQ, D, SRC, FT><<<grid, GEO::THREADS, GEO::SMEM, stream>>>(p);
     return cudaGetLastError();
 }
 
@@ -790,6 +794,11 @@ static cudaError_t launch_attn_nq(const AttnParams& p, int n_batch, cudaStream_t
     // double tiles (K / V staged once for 2 x 128 rows) when they still fill the GPU
     const int qpt = AM / p.G;
     const int64_t double_ctas = (int64_t)((p.S + 2 * qpt - 1) / (2 * qpt)) * p.Hkv * n_batch;
+    // converted sources: four converter warps (measured on 8 x 512 queries after 7680 int8 tokens: 1.32 ms with two, 1.02 ms
+    // with four; the softmax threads then work with 80 registers instead of 96)
+    if constexpr (src_is_block(SRC) || src_is_kivi(SRC))
+        return double_ctas >= 148 ? launch_attn<2, D, SRC, 128>(p, n_batch, stream) : launch_attn<1, D, SRC, 128>(p, n_batch, stream);
+    else
     return double_ctas >= 148 /* SMs of a B200 */ ? launch_attn<2, D, SRC>(p, n_batch, stream) : launch_attn<1, D, SRC>(p, n_batch, stream);
 }
 
