@@ -12,8 +12,9 @@
 // owns a tile and its warps take turns at the stages of 8 blocks: a warp pulls its stage, and the quantised activations
 // beside it (L2 resident, shared by every tile), through cp.async.bulk, turns each block into the A operand
 // of one mma.sync.m16n8k32 (u8 nibbles x s8 activations -> s32: 16 rows x 8 activation rows of exact dot products;
-// the -8 of the nibbles is removed with the block's activation sum), and adds the 8 contributions to the 16 x 8 f32
-// accumulators, which travel from warp to warp in stage order -- the order the reference adds the blocks in.
+// the -8 of the nibbles and the int -> f32 conversion are one exact float addition, see q40_common.cuh; the two
+// multiplications and the addition of a contribution are the packed f32x2 instructions, each lane rounded as the scalar
+// ones are), and adds the 8 contributions to the 16 x 8 f32 accumulators, which travel from warp to warp in stage order -- the order the reference adds the blocks in.
 #include <type_traits>
 
 #include "glue_math.cuh"
@@ -137,13 +138,57 @@ struct Q40Gemm {
     int* status;
     int64_t n, nb, out_stride;
     int32_t m, out_dtype;
+    float one;  // 1.0f, see f2_accumulate
 };
 
-__device__ inline void mma_u8s8(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm(
-        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+// D = A . B + c in every accumulator: 16 rows x 8 activation rows of exact dot products on top of the start value.
+__device__ inline void mma_u8s8(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1, int c) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(c));
+}
+
+// Two f32 values in a 64-bit register pair and the packed IEEE operations of sm_100 on them: each lane is rounded to
+// nearest on its own, exactly as the scalar instruction would, at half the instruction count.
+__device__ inline uint64_t f2_pack(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ inline uint64_t f2_pack_bits(int lo, int hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+    return r;
+}
+__device__ inline float2 f2_unpack(uint64_t v) {
+    float2 r;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(r.x), "=f"(r.y) : "l"(v));
+    return r;
+}
+__device__ inline uint64_t f2_add(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ inline uint64_t f2_mul(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+// acc + t as fma(t, 1, acc) with a 1 the compiler cannot see through (a kernel parameter): the assembler was seen to
+// contract mul.rn.f32x2 followed by add.rn.f32x2 into one fused multiply-add, which rounds once where the reference
+// rounds twice; a product that feeds the multiplicand of an fma cannot be contracted into it.
+__device__ inline uint64_t f2_accumulate(uint64_t acc, uint64_t t, uint64_t one2) {
+    uint64_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(t), "l"(one2), "l"(acc));
+    return r;
+}
+// The contributions of one block to two accumulators (one weight row, activation rows 2c and 2c + 1):
+// (dot as f32) * w_scale * a_scale, each operation rounded on its own.  d0, d1: finished MMA accumulators (started at
+// Q_F32_INT_BASE); par = {a_scale of the two rows, their offset terms}.
+__device__ inline uint64_t q40_contribution(int d0, int d1, uint64_t w_scale2, const float4& par) {
+    const uint64_t dot = f2_add(f2_pack_bits(d0, d1), f2_pack(par.z, par.w));
+    return f2_mul(f2_mul(dot, w_scale2), f2_pack(par.x, par.y));
 }
 
 // Waits for a barrier phase unless the CTA has already failed; gives up after ~1 s and marks the CTA failed.
@@ -227,41 +272,34 @@ __global__ void __launch_bounds__(Q_WARPS * 32, MG == 1 ? 2 : 1) q40_gemm_kernel
         const uint8_t* st = ring + sl * STAGE;
         // Passes over the blocks of the stage, so that the loads, the MMAs and the conversions of different blocks overlap.
         uint32_t af[Q_STAGE_BLOCKS][4];
-        float wsA[Q_STAGE_BLOCKS], wsB[Q_STAGE_BLOCKS];
+        uint64_t wsA[Q_STAGE_BLOCKS], wsB[Q_STAGE_BLOCKS];  // the block's scale of weight rows r and r + 8, in both lanes of a pair
 #pragma unroll
         for (int j = 0; j < Q_STAGE_BLOCKS; j++) {
             const uint8_t* wb = st + j * Q_BLOCK_BYTES;
             // bytes 4c .. 4c+3 of a row's 16: low nibbles = elements 4c .. 4c+3, high nibbles = elements 16 + 4c ..
             const uint32_t wa = *(const uint32_t*)(wb + r * 16 + 4 * c), wc = *(const uint32_t*)(wb + (r + 8) * 16 + 4 * c);
             af[j][0] = wa & 0x0f0f0f0fu, af[j][1] = wc & 0x0f0f0f0fu, af[j][2] = (wa >> 4) & 0x0f0f0f0fu, af[j][3] = (wc >> 4) & 0x0f0f0f0fu;
-            wsA[j] = __half2float(*(const __half*)(wb + 256 + 2 * r)), wsB[j] = __half2float(*(const __half*)(wb + 256 + 2 * (r + 8)));
+            const float sa = __half2float(*(const __half*)(wb + 256 + 2 * r)), sb = __half2float(*(const __half*)(wb + 256 + 2 * (r + 8)));
+            wsA[j] = f2_pack(sa, sa), wsB[j] = f2_pack(sb, sb);
         }
 #pragma unroll 1
         for (int gi = 0; gi < ng; gi++) {
-            uint32_t bf[Q_STAGE_BLOCKS][2];
-            float2 asc[Q_STAGE_BLOCKS];
-            int2 asum[Q_STAGE_BLOCKS];
+            uint2 bf[Q_STAGE_BLOCKS];
+            float4 par[Q_STAGE_BLOCKS];
 #pragma unroll
             for (int j = 0; j < Q_STAGE_BLOCKS; j++) {
                 const uint8_t* ab = st + Q_STAGE_BYTES + (gi * Q_STAGE_BLOCKS + j) * Q_ACT_BLOCK;
-                bf[j][0] = *(const uint32_t*)(ab + r * 16 + 4 * c);        // activation row r, elements 4c .. 4c+3
-                bf[j][1] = *(const uint32_t*)(ab + 128 + r * 16 + 4 * c);  // elements 16 + 4c ..
-                asc[j] = *((const float2*)(ab + 256) + c);                 // scales of activation rows 2c, 2c + 1
-                asum[j] = *((const int2*)(ab + 288) + c);
+                bf[j] = *(const uint2*)(ab + lane * 8);                          // activation row r: elements 4c .. 4c+3 | 16 + 4c ..
+                par[j] = *(const float4*)(ab + Q_ACT_PARAMS + c * 16);           // activation rows 2c, 2c + 1: scales, offset terms
             }
             int d[Q_STAGE_BLOCKS][4];
 #pragma unroll
-            for (int j = 0; j < Q_STAGE_BLOCKS; j++) {
-                d[j][0] = d[j][1] = d[j][2] = d[j][3] = 0;
-                mma_u8s8(d[j], af[j], bf[j][0], bf[j][1]);
-            }
-            float t[Q_STAGE_BLOCKS][4];  // (dot as f32) * w_scale * a_scale, each operation rounded on its own
+            for (int j = 0; j < Q_STAGE_BLOCKS; j++) mma_u8s8(d[j], af[j], bf[j].x, bf[j].y, Q_F32_INT_BASE);
+            uint64_t t01[Q_STAGE_BLOCKS], t23[Q_STAGE_BLOCKS];  // contributions to (row r; 2c, 2c + 1) and (row r + 8; 2c, 2c + 1)
 #pragma unroll
             for (int j = 0; j < Q_STAGE_BLOCKS; j++) {
-                t[j][0] = __fmul_rn(__fmul_rn((float)(d[j][0] - 8 * asum[j].x), wsA[j]), asc[j].x);
-                t[j][1] = __fmul_rn(__fmul_rn((float)(d[j][1] - 8 * asum[j].y), wsA[j]), asc[j].y);
-                t[j][2] = __fmul_rn(__fmul_rn((float)(d[j][2] - 8 * asum[j].x), wsB[j]), asc[j].x);
-                t[j][3] = __fmul_rn(__fmul_rn((float)(d[j][3] - 8 * asum[j].y), wsB[j]), asc[j].y);
+                t01[j] = q40_contribution(d[j][0], d[j][1], wsA[j], par[j]);
+                t23[j] = q40_contribution(d[j][2], d[j][3], wsB[j], par[j]);
             }
             if (gi == ng - 1) {  // the stage's bytes are in registers: refill the slot for this warp's stage after next
                 __syncwarp();
@@ -277,8 +315,10 @@ __global__ void __launch_bounds__(Q_WARPS * 32, MG == 1 ? 2 : 1) q40_gemm_kernel
 #pragma unroll
             for (int j = 0; j < Q_STAGE_BLOCKS; j++) {
                 if (j < nblk) {  // the blocks of a short last stage hold stale bytes: leave them out
-                    acc.x = __fadd_rn(acc.x, t[j][0]), acc.y = __fadd_rn(acc.y, t[j][1]);
-                    acc.z = __fadd_rn(acc.z, t[j][2]), acc.w = __fadd_rn(acc.w, t[j][3]);
+                    // scalar additions: this chain is the serial part of the tile, where latency counts and instruction slots do not
+                    const float2 lo = f2_unpack(t01[j]), hi = f2_unpack(t23[j]);
+                    acc.x = __fadd_rn(acc.x, lo.x), acc.y = __fadd_rn(acc.y, lo.y);
+                    acc.z = __fadd_rn(acc.z, hi.x), acc.w = __fadd_rn(acc.w, hi.y);
                 }
             }
             if (s + 1 < n_stages) {
@@ -331,6 +371,7 @@ __global__ void __launch_bounds__((R_WARPS + 1) * 32, 2) q40_gemm_rows_kernel(Q4
     const int nw = (int)min((int64_t)R_WARPS, (groups - g0 + R_GPW - 1) / R_GPW);  // consumer warps with rows
     const uint8_t* wsrc = p.packed + tile * p.nb * Q_BLOCK_BYTES;
     const int n_stages = (int)((p.nb + Q_STAGE_BLOCKS - 1) / Q_STAGE_BLOCKS);
+    const uint64_t one2 = f2_pack(p.one, p.one);
     auto blocks_of = [&](int s) { return (uint32_t)min((int64_t)Q_STAGE_BLOCKS, p.nb - (int64_t)s * Q_STAGE_BLOCKS); };
     if (tid == 0) {
         for (int i = 0; i < R_WDEPTH; i++) mbar_init(&wfull[i], 1), mbar_init(&wempty[i], nw);
@@ -364,21 +405,22 @@ __global__ void __launch_bounds__((R_WARPS + 1) * 32, 2) q40_gemm_rows_kernel(Q4
         grid_dependency_wait();  // the activation quantiser has finished
         if (lane == 0)
             for (int d = 0; d < R_ADEPTH && d < n_stages; d++) pull(d);
-        float4 acc[R_GPW];  // per group: (row r, act 2c), (r, 2c + 1), (r + 8, 2c), (r + 8, 2c + 1)
+        uint64_t acc01[R_GPW], acc23[R_GPW];  // per group, as packed pairs: (row r; act 2c, 2c + 1) and (row r + 8; 2c, 2c + 1)
 #pragma unroll
-        for (int gi = 0; gi < R_GPW; gi++) acc[gi] = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int gi = 0; gi < R_GPW; gi++) acc01[gi] = acc23[gi] = f2_pack(0.f, 0.f);
         for (int s = 0; s < n_stages; s++) {
             const int nblk = (int)blocks_of(s), wsl = s % R_WDEPTH, asl = s % R_ADEPTH;
             q40_wait(&wfull[wsl], (uint32_t)((s / R_WDEPTH) & 1), fail_s);
             const uint8_t* st = ring + wsl * Q_STAGE_BYTES;
             uint32_t af[Q_STAGE_BLOCKS][4];
-            float wsA[Q_STAGE_BLOCKS], wsB[Q_STAGE_BLOCKS];
+            uint64_t wsA[Q_STAGE_BLOCKS], wsB[Q_STAGE_BLOCKS];
 #pragma unroll
             for (int j = 0; j < Q_STAGE_BLOCKS; j++) {
                 const uint8_t* wb = st + j * Q_BLOCK_BYTES;
                 const uint32_t wa = *(const uint32_t*)(wb + r * 16 + 4 * c), wc = *(const uint32_t*)(wb + (r + 8) * 16 + 4 * c);
                 af[j][0] = wa & 0x0f0f0f0fu, af[j][1] = wc & 0x0f0f0f0fu, af[j][2] = (wa >> 4) & 0x0f0f0f0fu, af[j][3] = (wc >> 4) & 0x0f0f0f0fu;
-                wsA[j] = __half2float(*(const __half*)(wb + 256 + 2 * r)), wsB[j] = __half2float(*(const __half*)(wb + 256 + 2 * (r + 8)));
+                const float sa = __half2float(*(const __half*)(wb + 256 + 2 * r)), sb = __half2float(*(const __half*)(wb + 256 + 2 * (r + 8)));
+                wsA[j] = f2_pack(sa, sa), wsB[j] = f2_pack(sb, sb);
             }
             __syncwarp();
             if (lane == 0) q40_arrive(&wempty[wsl]);  // the weights of the stage are in registers
@@ -393,16 +435,13 @@ __global__ void __launch_bounds__((R_WARPS + 1) * 32, 2) q40_gemm_rows_kernel(Q4
 #pragma unroll
                         for (int j = 0; j < Q_STAGE_BLOCKS; j++) {
                             const uint8_t* ab = as + j * Q_ACT_BLOCK;
-                            const uint32_t b0 = *(const uint32_t*)(ab + r * 16 + 4 * c), b1 = *(const uint32_t*)(ab + 128 + r * 16 + 4 * c);
-                            const float2 asc = *((const float2*)(ab + 256) + c);
-                            const int2 asum = *((const int2*)(ab + 288) + c);
-                            int d[4] = {0, 0, 0, 0};
-                            mma_u8s8(d, af[j], b0, b1);
+                            const uint2 bq = *(const uint2*)(ab + lane * 8);
+                            const float4 par = *(const float4*)(ab + Q_ACT_PARAMS + c * 16);
+                            int d[4];
+                            mma_u8s8(d, af[j], bq.x, bq.y, Q_F32_INT_BASE);
                             if (FULL || j < nblk) {
-                                acc[gi].x = __fadd_rn(acc[gi].x, __fmul_rn(__fmul_rn((float)(d[0] - 8 * asum.x), wsA[j]), asc.x));
-                                acc[gi].y = __fadd_rn(acc[gi].y, __fmul_rn(__fmul_rn((float)(d[1] - 8 * asum.y), wsA[j]), asc.y));
-                                acc[gi].z = __fadd_rn(acc[gi].z, __fmul_rn(__fmul_rn((float)(d[2] - 8 * asum.x), wsB[j]), asc.x));
-                                acc[gi].w = __fadd_rn(acc[gi].w, __fmul_rn(__fmul_rn((float)(d[3] - 8 * asum.y), wsB[j]), asc.y));
+                                acc01[gi] = f2_accumulate(acc01[gi], q40_contribution(d[0], d[1], wsA[j], par), one2);
+                                acc23[gi] = f2_accumulate(acc23[gi], q40_contribution(d[2], d[3], wsB[j], par), one2);
                             }
                         }
                     }
@@ -416,7 +455,8 @@ __global__ void __launch_bounds__((R_WARPS + 1) * 32, 2) q40_gemm_rows_kernel(Q4
 #pragma unroll
         for (int gi = 0; gi < R_GPW; gi++) {
             if (gi >= ngw) break;
-            float4 a = acc[gi];
+            const float2 lo = f2_unpack(acc01[gi]), hi = f2_unpack(acc23[gi]);
+            float4 a = make_float4(lo.x, lo.y, hi.x, hi.y);
             if (*fail_s) a = make_float4(__int_as_float(0x7fc00000), __int_as_float(0x7fc00000), __int_as_float(0x7fc00000), __int_as_float(0x7fc00000));
             const int64_t row = tile * Q_TILE_ROWS + r, m0 = (gw + gi) * 8 + 2 * c;
             if (row < p.n) {
@@ -530,7 +570,7 @@ extern "C" int b200kv_q40_gemm_quantized_as(const void* packed, int64_t n, int64
     uint8_t* act = (uint8_t*)scratch + Q_HEADER;
     Q40Gemm p{};
     p.packed = (const uint8_t*)packed, p.act = act, p.out = out, p.status = (int*)scratch;
-    p.n = n, p.nb = nb, p.out_stride = out_stride, p.m = m, p.out_dtype = out_dtype;
+    p.n = n, p.nb = nb, p.out_stride = out_stride, p.m = m, p.out_dtype = out_dtype, p.one = 1.0f;
     if (groups >= 4) {  // a prompt pass: every warp keeps the accumulators of its own 8 rows, the weight stages are shared by 8 warps
         static thread_local int rows_attr_device = -1;
         int dev = 0;

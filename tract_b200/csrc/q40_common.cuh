@@ -12,7 +12,17 @@ constexpr int Q_BLOCK_BYTES = 16 * 16 + 16 * 2;  // one block of a tile: 256 nib
 constexpr int Q_STAGE_BLOCKS = 8;
 constexpr int Q_STAGE_BYTES = Q_STAGE_BLOCKS * Q_BLOCK_BYTES;  // 2304
 constexpr int Q_DEPTH = 2;                // stages in flight per warp
-constexpr int Q_ACT_BLOCK = 2 * 8 * 16 + 8 * 4 + 8 * 4;  // per block and group of 8 activation rows: codes [2 halves][8][16], scales f32 [8], sums i32 [8]
+// Per block and group of 8 activation rows (320 bytes), laid out as the lanes of the GEMM's MMA read it: codes
+// [row 8][quad 4][elements 4q .. 4q+3 | 16+4q .. 16+4q+3] (lane 4 row + quad takes its 8 bytes in one load), then per
+// quad four floats {scale of row 2q, scale of row 2q+1, -(Q_F32_BASE + 8 * code sum of row 2q), the same of row 2q+1}.
+// The MMA's int32 accumulators start at Q_F32_INT_BASE, the bits of the float Q_F32_BASE = 1.5 * 2^23: the finished
+// accumulator, read as a float, is Q_F32_BASE + (dot product with the unsigned nibbles) exactly, and one float addition
+// of the row's third parameter leaves (dot product with nibble - 8) as f32 -- the int -> float conversion and the offset
+// correction of the reference in one exact operation (every value involved is an integer below 2^24).
+constexpr int Q_ACT_BLOCK = 8 * 32 + 4 * 16;
+constexpr int Q_ACT_PARAMS = 256;         // byte offset of the per-quad parameters
+constexpr int32_t Q_F32_INT_BASE = 0x4B400000;
+constexpr float Q_F32_BASE = 12582912.f;
 constexpr int Q_HEADER = 256;             // scratch header: word 0 = status of the GEMMs since the last producer, word 1 = status of every
                                           // GEMM since the last b200kv_q40_check (no producer clears it), word 2 = Q_MAGIC once word 1 is valid
 constexpr uint32_t Q_MAGIC = 0x51343041u;
@@ -31,7 +41,7 @@ __device__ inline void q40_status_fail(int* status, int bits) {
 constexpr int Q_RING_STAGE = Q_STAGE_BYTES + Q_STAGE_BLOCKS * Q_ACT_BLOCK;  // weights then activations of 8 blocks: 4864 bytes
 
 // Q4_0::quantize_row_q8 (q4_0.rs:199-222) for one block: the 32 lanes of a warp hold its 32 values.  Writes the codes,
-// the scale and the code sum of activation row slot `slot` into the block's record.  `valid` false (a slot past the last
+// the scale and the offset term of activation row slot `slot` into the block's record.  `valid` false (a slot past the last
 // row): zero codes, scale 0.
 __device__ inline void q40_quantize_block(float x, bool valid, uint8_t* dst, int slot, int lane) {
     if (!valid) x = 0.f;
@@ -44,10 +54,11 @@ __device__ inline void q40_quantize_block(float x, bool valid, uint8_t* dst, int
     const float t = roundf(__fmul_rn(x, r));  // NaN for a NaN input and for inf * 0
     const int q = (t != t) ? 0 : (int)fminf(fmaxf(t, -127.f), 127.f);  // f32::clamp keeps a NaN, the cast to i8 makes it 0
     const int sum = __reduce_add_sync(0xffffffffu, q);
-    dst[(lane >> 4) * 128 + slot * 16 + (lane & 15)] = (uint8_t)(int8_t)q;
+    dst[slot * 32 + ((lane & 15) >> 2) * 8 + (lane >> 4) * 4 + (lane & 3)] = (uint8_t)(int8_t)q;
     if (lane == 0) {
-        ((float*)(dst + 256))[slot] = valid ? scale : 0.f;
-        ((int32_t*)(dst + 288))[slot] = sum;
+        uint8_t* par = dst + Q_ACT_PARAMS + (slot >> 1) * 16 + (slot & 1) * 4;
+        *(float*)par = valid ? scale : 0.f;
+        *(float*)(par + 8) = -(Q_F32_BASE + (float)(8 * sum));  // exact: |8 sum| <= 8 * 32 * 127
     }
 }
 
