@@ -418,15 +418,24 @@ def run_prefill(ctx, workload, steps, warmup, min_seconds, quick=False, primary=
     hout = torch.empty_like(out, device="cpu").pin_memory()
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k_new), torch.empty_like(v_new)
     if fmt.startswith("kivi"):
-        raise SystemExit("a KIVI cache cannot be rolled back between prefill steps: use the chunked q8 / q4 workloads")
-    back = [past] * n_seq
-    step = cache.prepared_step(seqs, k_new, v_new, q, out, rollback_to=back)
-    core_e2e = cache.prepared_step(seqs, dk, dv, dq, out, rollback_to=back)
+        # a KIVI store cannot be rolled back (a finalised key block does not come apart): the chunk is appended once, before
+        # the timed region, and a step is the attention of its S queries over the past + S cached tokens
+        cache.append(seqs, k_new, v_new)
+        step = lambda: cache.attend(seqs, q, out=out)
 
-    def step_e2e():
-        dq.copy_(hq, non_blocking=True), dk.copy_(hk, non_blocking=True), dv.copy_(hv, non_blocking=True)
-        core_e2e()
-        hout.copy_(out, non_blocking=True)
+        def step_e2e():
+            dq.copy_(hq, non_blocking=True)
+            cache.attend(seqs, dq, out=out)
+            hout.copy_(out, non_blocking=True)
+    else:
+        back = [past] * n_seq
+        step = cache.prepared_step(seqs, k_new, v_new, q, out, rollback_to=back)
+        core_e2e = cache.prepared_step(seqs, dk, dv, dq, out, rollback_to=back)
+
+        def step_e2e():
+            dq.copy_(hq, non_blocking=True), dk.copy_(hk, non_blocking=True), dv.copy_(hv, non_blocking=True)
+            core_e2e()
+            hout.copy_(out, non_blocking=True)
 
     sampler = ClockSampler(ctx.dev_index)
     if rank == 0 and primary:
@@ -460,7 +469,8 @@ def run_prefill(ctx, workload, steps, warmup, min_seconds, quick=False, primary=
         k_ms = statistics.median(per_kernel[k_name])
         achieved = useful / (k_ms * 1e-3) / 1e12
         peak = pk.get("bf16_tflops", 1590.0)
-        h2d = sum(t.numel() * t.element_size() for t in (hq, hk, hv))
+        kivi = fmt.startswith("kivi")
+        h2d = sum(t.numel() * t.element_size() for t in ((hq,) if kivi else (hq, hk, hv)))
         result = {
             "metric": "prefill causal-useful attention TFLOP/s (sum over GPUs)", "value": world * useful / (ms_step * 1e-3) / 1e12,
             "unit": "TFLOP/s", "n_gpus": world, "steps": steps, "warmup": max(warmup, 3), "ms_per_step": ms_step,
@@ -471,11 +481,13 @@ def run_prefill(ctx, workload, steps, warmup, min_seconds, quick=False, primary=
                        "parallelism": f"by-sequence x{world}, no collective",
                        "l2": "working set fits L2 (warm)" if (past + S) * n_seq * HKV * D * 4 < 100e6 else "inputs larger than L2",
                        "flops_per_step_per_gpu": useful,
+                       "step": "attention of the chunk's queries (the chunk is appended once, before the timed region)" if kivi
+                               else "append the chunk, attention of its queries, roll the cache back",
                        "timed_region": {"repeats_of_the_steps": reps, "ms": timed_ms, "min_seconds": min_seconds}},
             "tokens_per_s": world * n_seq * S / (ms_step * 1e-3),
             "e2e": {"value": world * useful / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": hout.numel() * hout.element_size(), "ms_per_step": ms_e2e},
-            "gpu_launches": steps * reps * 2, "kernels_ms": {k: statistics.median(v) for k, v in per_kernel.items()},
+            "gpu_launches": steps * reps * (1 if kivi else 2), "kernels_ms": {k: statistics.median(v) for k, v in per_kernel.items()},
             "roofline": {"bound": "tensor", "kernel": ("prefill_tc_kernel" if fmt in ("f16", "bf16") else "attn_tc_kernel") if k_name == "prefill" else "sdpa_dense_kernel",
                          "achieved": achieved,
                          "peak": peak, "unit": "TFLOP/s", "kernel_ms": k_ms,

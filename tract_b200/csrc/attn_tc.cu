@@ -13,7 +13,7 @@
 //
 // The pipeline is that of prefill_tc.cu: a query tile is 128 rows = (query, head-of-group) pairs of one (sequence, kv
 // head); per tile and per 64 keys  S = Q . K^T  (tcgen05.mma, operands in shared memory with the 128-byte swizzle, S
-// double-buffered in TMEM), softmax by two threads per row (tcgen05.ld, exponentials in the log2 domain against a
+// double-buffered in TMEM), softmax by one thread per row (tcgen05.ld, exponentials in the log2 domain against a
 // lazily raised reference maximum, P written over S with tcgen05.st as a 16-bit value plus its rounding remainder),
 // O += P . V  (A from TMEM, V as an MN-major operand).  What differs is who fills the K / V operand rings:
 //   SRC_PAGES16  a copy warp: one untiled cp.async.bulk per chunk, the page bytes ARE the operand tile (head_dim 64 here)
@@ -40,9 +40,9 @@
 namespace b200kv {
 
 constexpr int AM = 128;            // rows of a query tile
-constexpr int A_SM_THREADS = 256;  // softmax threads per query tile
+constexpr int A_SM_THREADS = 128;  // softmax threads per query tile: one per row
 constexpr int A_FILL_THREADS = 64; // converter / loader threads (the KIVI converter and the dense loader; block formats: FT)
-constexpr int A_XCHG = 2 * AM + 8; // per tile and page parity: the two half-row maxima of every row, one flag per softmax warp
+constexpr int A_XCHG = 8;          // per tile and page parity: one flag per softmax warp (does the page need its remainder product)
 constexpr float A_SKIP_FRACTION = 0.125f;
 enum { SRC_PAGES16 = 0, SRC_Q8 = 1, SRC_DENSE = 2, SRC_KIVI8 = 3, SRC_Q4 = 4, SRC_KIVI4 = 5 };
 constexpr bool src_is_kivi(int src) { return src == SRC_KIVI8 || src == SRC_KIVI4; }
@@ -204,7 +204,6 @@ __global__ void __launch_bounds__(AGeo<NQ, D, SRC, FT>::THREADS, 1) attn_tc_kern
     constexpr int NK = GEO::NK, NV = GEO::NV, NR = GEO::NR, CHUNK = GEO::CHUNK, QBYTES = GEO::QBYTES, PLANES = GEO::PLANES;
     constexpr int KSTAGE = GEO::KSTAGE, KPARTS = GEO::KPARTS;
     constexpr bool RAW = GEO::RAW;  // converted sources: f16 operands whatever the query type
-    constexpr int DH = D / 2;  // output channels per softmax thread
     constexpr uint32_t COL_O = 0, COL_S = GEO::COL_S, COLS_PER_TILE = GEO::COLS_PER_TILE;
     constexpr int FILL_ARRIVALS = SRC == SRC_PAGES16 ? 1 : FT / 32;
     static_assert(FT == A_FILL_THREADS || src_is_block(SRC) || src_is_kivi(SRC), "the dense loader and the copy warp have a fixed thread count");
@@ -251,8 +250,8 @@ __global__ void __launch_bounds__(AGeo<NQ, D, SRC, FT>::THREADS, 1) attn_tc_kern
     if (warp == 0) tmem_alloc(tmem_slot, COLS_PER_TILE * NQ);
 
     // per-thread tile geometry (softmax threads only; the other warps get harmless values)
-    const int qt = min(tid / A_SM_THREADS, NQ - 1), w8 = (tid % A_SM_THREADS) >> 5;
-    const int row = (w8 & 3) * 32 + lane, half = w8 >> 2;
+    const int qt = min(tid / A_SM_THREADS, NQ - 1), w4 = (tid % A_SM_THREADS) >> 5;
+    const int row = w4 * 32 + lane;
     const int q0 = cta_q0 + qt * qpt;
     const int rq = row / G, rg = row % G;
     const bool live = rq < qpt && q0 + rq < p.S;
@@ -264,11 +263,11 @@ __global__ void __launch_bounds__(AGeo<NQ, D, SRC, FT>::THREADS, 1) attn_tc_kern
     const int mma_bf16 = RAW ? 0 : p.is_bf16;  // type of the tensor-core operands (Q, K, V, P)
 
     // ---- Q tile -> shared memory, K-major with the 128-byte swizzle (row r: 16-byte unit u of a plane at u ^ (r & 7));
-    //      this thread moves the DH channels of its half of its row ----
+    //      this thread moves its row ----
     if (is_softmax) {
-        constexpr int NU = DH / 8;  // 16-byte units per thread
+        constexpr int NU = D / 8;  // 16-byte units per row
         const int head = kvh * G + rg;
-        const uint4* src = (const uint4*)((const uint16_t*)p.q + (int64_t)b * p.qb + (int64_t)head * p.qh + (int64_t)my_q * p.qs) + half * NU;
+        const uint4* src = (const uint4*)((const uint16_t*)p.q + (int64_t)b * p.qb + (int64_t)head * p.qh + (int64_t)my_q * p.qs);
 #pragma unroll
         for (int uu = 0; uu < NU; uu++) {
             uint4 v = live ? src[uu] : make_uint4(0, 0, 0, 0);
@@ -280,7 +279,7 @@ __global__ void __launch_bounds__(AGeo<NQ, D, SRC, FT>::THREADS, 1) attn_tc_kern
                     w[e] = *(const uint32_t*)&h;
                 }
             }
-            const int unit = half * NU + uu, plane = unit / 8, u8 = unit % 8;
+            const int plane = uu / 8, u8 = uu % 8;
             *(uint4*)(q_s + qt * QBYTES + plane * (AM * 128) + row * 128 + ((u8 ^ (row & 7)) << 4)) = v;
         }
         fence_async_proxy();  // generic-proxy writes -> visible to the tensor core
@@ -357,8 +356,8 @@ __global__ void __launch_bounds__(AGeo<NQ, D, SRC, FT>::THREADS, 1) attn_tc_kern
                 wait_or_fail(&full_v[j % NV], (uint32_t)((j / NV) & 1), fail_s);
                 wait_or_fail(&bar_p[2 * t + (j & 1)], (uint32_t)((j >> 1) & 1), fail_s);
                 tc_fence_after();
-                const int* flags = (const int*)(xchg + (2 * t + (j & 1)) * A_XCHG + 2 * AM);
-                const bool two = !adaptive || __any_sync(0xffffffffu, flags[lane & 7] != 0);
+                const int* flags = (const int*)(xchg + (2 * t + (j & 1)) * A_XCHG);
+                const bool two = !adaptive || __any_sync(0xffffffffu, flags[lane & 3] != 0);
                 if (elect_one()) {
                     const uint64_t vd = v_desc + (uint64_t)(((j % NV) * CHUNK) >> 4);
                     const uint32_t pa = tm + COL_S + 64 * (j & 1);
@@ -615,11 +614,10 @@ __global__ void __launch_bounds__(AGeo<NQ, D, SRC, FT>::THREADS, 1) attn_tc_kern
         }
     } else {
         // ================= softmax threads =================
-        const uint32_t lane_base = tmem + qt * COLS_PER_TILE + ((uint32_t)((w8 & 3) * 32) << 16);  // this warp's lane quarter
-        const int pair_id = 1 + qt * 4 + (w8 & 3);        // named barrier of the two warps that share these 32 rows
+        const uint32_t lane_base = tmem + qt * COLS_PER_TILE + ((uint32_t)(w4 * 32) << 16);  // this warp's lane quarter
         const bool adaptive = !mma_bf16;
         const float sl2 = p.scale * 1.4426950408889634f;  // scores enter the exponent in log2 units
-        float m_ref = -INFINITY, l_run = 0.f;             // l_run: this thread's half of the row sum
+        float m_ref = -INFINITY, l_run = 0.f, log_thresh = -INFINITY;
         // this row's mask values (dense source): element (my_q, key) at mrow + key * mk
         const bool masked = SRC == SRC_DENSE && p.mask != nullptr;
         const int64_t mrow = masked ? (int64_t)b * p.mb + (int64_t)(kvh * G + rg) * p.mh + (int64_t)my_q * p.mq : 0;
@@ -628,96 +626,69 @@ __global__ void __launch_bounds__(AGeo<NQ, D, SRC, FT>::THREADS, 1) attn_tc_kern
             const uint32_t sbuf = lane_base + COL_S + 64 * (j & 1);
             wait_or_fail(&bar_s[2 * qt + (j & 1)], (uint32_t)((j >> 1) & 1), fail_s);
             tc_fence_after();
-            // ---- this thread's 32 of the row's 64 scores ----
-            uint32_t sr[32];
-            tmem_ld32(sbuf + 32 * half, sr);
+            // ---- the row's 64 scores ----
+            uint32_t sr[64];
+            tmem_ld32(sbuf, sr);
+            tmem_ld32(sbuf + 32, sr + 32);
             tmem_ld_wait();
-            float tmax = -INFINITY;
-            const int t0 = j * PAGE_TOKENS + 32 * half;
+            const int t0 = j * PAGE_TOKENS;
             if (masked) {  // the mask is added to the scaled score: the raw score takes mask / scale
 #pragma unroll
-                for (int c = 0; c < 32; c++) {
-                    float s = -INFINITY;
-                    if (t0 + c <= my_limit) s = fmaf(ld_as_f32(p.mask, p.mask_dtype, mrow + (int64_t)(t0 + c) * p.mk), p.inv_scale, __uint_as_float(sr[c]));
-                    sr[c] = __float_as_uint(s);
-                    tmax = fmaxf(tmax, s);
+                for (int c = 0; c < 64; c++) {
+                    float sc = -INFINITY;
+                    if (t0 + c <= my_limit) sc = fmaf(ld_as_f32(p.mask, p.mask_dtype, mrow + (int64_t)(t0 + c) * p.mk), p.inv_scale, __uint_as_float(sr[c]));
+                    sr[c] = __float_as_uint(sc);
                 }
-            } else if (j * PAGE_TOKENS + PAGE_TOKENS - 1 > min_limit) {  // only pages on the causal diagonal / past the end need a mask
+            } else if (t0 + PAGE_TOKENS - 1 > min_limit) {  // only pages on the causal diagonal / past the end need a mask
 #pragma unroll
-                for (int c = 0; c < 32; c++) {
-                    const float s = (t0 + c <= my_limit) ? __uint_as_float(sr[c]) : -INFINITY;
-                    sr[c] = __float_as_uint(s);
-                    tmax = fmaxf(tmax, s);
-                }
-            } else {
-#pragma unroll
-                for (int c = 0; c < 32; c++) tmax = fmaxf(tmax, __uint_as_float(sr[c]));
+                for (int c = 0; c < 64; c++)
+                    if (t0 + c > my_limit) sr[c] = 0xff800000u;  // -inf
             }
-            float* xq = xchg + (2 * qt + (j & 1)) * A_XCHG;
-            int* flags = (int*)(xq + 2 * AM);
-            bool two = true;
-            // f16 weights skip the remainder product of a page once, for every row of the tile, what the rounding of the
-            // page can add is below 2^-12 / 8 of the row's scale; page 0 always keeps it (l_run is 0)
-            if (adaptive) {
-                const bool mine = j == 0 || !(fast_exp2(fmaf(tmax, sl2, -m_ref)) * 5.657f <= p.skip_fraction * l_run);
-                two = __any_sync(0xffffffffu, mine);
-                if (lane == 0) flags[w8] = two ? 1 : 0;
-            }
-            xq[half * AM + row] = tmax;
-            pair_barrier(pair_id);  // maxima exchanged; both halves of S(j) are in registers, so P may overwrite them
-            tmax = fmaxf(tmax, xq[(half ^ 1) * AM + row]) * sl2;
-            // raise the reference maximum only when it is exceeded by more than 2^8: the exponentials stay below
-            // 256, exact enough in 16 bits, and O has to be rescaled only rarely
+            const float tmax = row_max64(sr) * sl2;
+            int* flags = (int*)(xchg + (2 * qt + (j & 1)) * A_XCHG);
+            // Two questions per row, answered for the warp with one reduction.  Bit 0: f16 weights skip the remainder product of
+            // a page once, for every row of the tile, what the rounding of the page can add is below 2^-12 / 8 of the row's scale
+            // (sqrt(64) x the largest weight against skip_fraction x the running sum, compared in the log domain; page 0 always
+            // keeps it).  Bit 1: is the reference maximum exceeded by more than 2^8 -- it is raised only then (and set by the
+            // first page that shows the row a key), so the exponentials stay below 256, exact enough in 16 bits, and O is
+            // rescaled rarely.
+            const bool mine = adaptive && (j == 0 || !(tmax - m_ref + 3.f <= log_thresh));
+            const bool raise = tmax > m_ref + 8.f || (m_ref == -INFINITY && tmax > -INFINITY);
+            const uint32_t votes = __reduce_or_sync(0xffffffffu, (mine ? 1u : 0u) | (raise && j > 0 ? 2u : 0u));
+            const bool two = !adaptive || (votes & 1u);
+            if (adaptive && lane == 0) flags[w4] = two ? 1 : 0;  // the MMA warp issues the remainder product if any warp asks for it
             float alpha = 1.f;
-            if (j == 0) {
-                m_ref = tmax;
-            } else if (tmax > m_ref + 8.f) {
+            if (raise) {
                 alpha = fast_exp2(m_ref - tmax);  // m_ref = -inf (every key so far masked out): 0
                 m_ref = tmax;
                 l_run *= alpha;
             }
-            if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+            if (votes & 2u) {
                 // O must hold every page before this one: see prefill_tc.cu for why the wait on barrier (j - 1) & 1 cannot
                 // mistake the completion of P.V(j - 3) or P.V(j + 1) for that of P.V(j - 1)
                 wait_or_fail(&bar_o[2 * qt + ((j - 1) & 1)], (uint32_t)(((j - 1) >> 1) & 1), fail_s);
                 tc_fence_after();
 #pragma unroll
-                for (int cc = 0; cc < DH / 16; cc++) {  // this thread's half of the row's output channels
+                for (int cc = 0; cc < D / 16; cc++) {  // the row's output channels
                     uint32_t orow[16];
-                    tmem_ld16(lane_base + COL_O + DH * half + cc * 16, orow);
+                    tmem_ld16(lane_base + COL_O + cc * 16, orow);
                     tmem_ld_wait();
 #pragma unroll
                     for (int c = 0; c < 16; c++) orow[c] = __float_as_uint(__uint_as_float(orow[c]) * alpha);
-                    tmem_st16(lane_base + COL_O + DH * half + cc * 16, orow);
+                    tmem_st16(lane_base + COL_O + cc * 16, orow);
                 }
             }
             // a row that has seen no key yet has m_ref = -inf: its weights are exp2(-inf - 0) = 0, not exp2(-inf + inf)
             const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
-            uint32_t pr[16], pr2[16];
-            float lsum = 0.f;
-#pragma unroll
-            for (int c = 0; c < 16; c++) {
-                const float p0 = fast_exp2(fmaf(__uint_as_float(sr[2 * c]), sl2, -m_use));
-                const float p1 = fast_exp2(fmaf(__uint_as_float(sr[2 * c + 1]), sl2, -m_use));
-                lsum += p0 + p1;
-                if (mma_bf16) {
-                    const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-                    const __nv_bfloat162 l = __floats2bfloat162_rn(p0 - __low2float(h), p1 - __high2float(h));
-                    pr[c] = *(const uint32_t*)&h, pr2[c] = *(const uint32_t*)&l;
-                } else {
-                    const __half2 h = __floats2half2_rn(p0, p1);
-                    pr[c] = *(const uint32_t*)&h;
-                    if (two) {
-                        const __half2 l = __floats2half2_rn(p0 - __low2float(h), p1 - __high2float(h));
-                        pr2[c] = *(const uint32_t*)&l;
-                    } else {
-                        pr2[c] = 0u;
-                    }
-                }
-            }
-            tmem_st16(sbuf + 32 + 16 * half, pr2);
-            l_run += lsum;
-            tmem_st16(sbuf + 16 * half, pr);
+            uint32_t pr[32], pr2[32];
+            float page_sum;
+            if (mma_bf16) page_sum = softmax_exps<2>(sr, sl2, m_use, pr, pr2);
+            else if (two) page_sum = softmax_exps<1>(sr, sl2, m_use, pr, pr2);
+            else page_sum = softmax_exps<0>(sr, sl2, m_use, pr, pr2);
+            tmem_st32(sbuf + 32, pr2);
+            tmem_st32(sbuf, pr);
+            l_run += page_sum;
+            log_thresh = fast_log2(p.skip_fraction * l_run);
             tmem_st_wait();
             tc_fence_before();
             __syncwarp();
@@ -726,16 +697,13 @@ __global__ void __launch_bounds__(AGeo<NQ, D, SRC, FT>::THREADS, 1) attn_tc_kern
         // ---- epilogue: wait for the last P.V, normalise, store ----
         wait_or_fail(&bar_o[2 * qt + ((n_tiles - 1) & 1)], (uint32_t)(((n_tiles - 1) >> 1) & 1), fail_s);
         tc_fence_after();
-        float* xq = xchg + (2 * qt + (n_tiles & 1)) * A_XCHG;  // the buffer page n_tiles - 2 used: everyone is past it
-        xq[half * AM + row] = l_run;
-        pair_barrier(pair_id);
         if (!*fail_s) {
-            const float inv = 1.f / (l_run + xq[(half ^ 1) * AM + row]);  // no visible key: 0 * inf = NaN, as 0 / 0 in the reference
-            uint16_t* dst = (uint16_t*)p.out + (int64_t)b * p.ob + (int64_t)(kvh * G + rg) * p.oh + (int64_t)my_q * p.os + DH * half;
+            const float inv = 1.f / l_run;  // no visible key: 0 * inf = NaN, as 0 / 0 in the reference
+            uint16_t* dst = (uint16_t*)p.out + (int64_t)b * p.ob + (int64_t)(kvh * G + rg) * p.oh + (int64_t)my_q * p.os;
 #pragma unroll
-            for (int cc = 0; cc < DH / 32; cc++) {
+            for (int cc = 0; cc < D / 32; cc++) {
                 uint32_t orow[32];
-                tmem_ld32(lane_base + COL_O + DH * half + cc * 32, orow);
+                tmem_ld32(lane_base + COL_O + cc * 32, orow);
                 tmem_ld_wait();
                 if (live) {
 #pragma unroll

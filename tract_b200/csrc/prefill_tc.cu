@@ -12,19 +12,19 @@
 //   S[128 x 64]  = Q . K^T      tcgen05.mma, A = Q tile in shared memory (K-major, 128-byte swizzle),
 //                               B = the K chunk exactly as it lies in the page (same swizzle), D in TMEM;
 //                               S is double-buffered, so the product for page j+1 runs under the softmax of page j
-//   softmax                     two threads own a row: each tcgen05.ld's 32 of its 64 scores, masks, exponentiates in
-//                               the log2 domain against a lazily raised reference maximum and writes P (16-bit)
-//                               over the S buffer it came from with tcgen05.st
+//   softmax                     one thread owns a row: it tcgen05.ld's the 64 scores, masks, exponentiates in the log2
+//                               domain against a lazily raised reference maximum -- the exponentials issued as a software
+//                               pipeline, so that the MUFU unit (one warp instruction per 8 cycles) always has the warp's
+//                               next ones queued -- and writes P (16-bit) over the S buffer it came from with tcgen05.st
 //   O[128 x 128] += P . V       tcgen05.mma, A = P from TMEM, B = the V chunk as it lies in the page (MN-major
 //                               operand: channels contiguous), D accumulates in TMEM.  f16: one MMA per 16 tokens
 //                               (P carries 11 bits); bf16: P goes in as its 16-bit value plus the 16-bit rounding
 //                               remainder (two MMAs), or a row that sees few keys would carry the 2^-9 rounding
-// Roles: 256 softmax threads per tile; one warp that issues the K / V bulk copies (untiled cp.async.bulk into
+// Roles: 128 softmax threads per tile; one warp that issues the K / V bulk copies (untiled cp.async.bulk into
 // two rings); one warp per tile that issues its MMAs and their commits.  Every wait is bounded; on expiry the
 // CTA flags the status word, lets every role run to the end of its loop without waiting any more, frees its
 // TMEM and returns.
 #include <cmath>
-
 #include "tc_common.cuh"
 
 namespace b200kv {
@@ -33,7 +33,8 @@ constexpr int PD = 128;                        // head_dim
 constexpr int PM = 128;                        // rows of a query tile
 constexpr int P_CHUNK = PAGE_TOKENS * PD * 2;  // bytes of one K (or V) chunk: 16 KiB
 constexpr int P_QBYTES = PM * PD * 2;          // 32 KiB per query tile
-constexpr int SM_THREADS = 256;                // softmax threads per query tile
+constexpr int SM_THREADS = 128;                // softmax threads per query tile: one per row
+
 // TMEM columns of one query tile: O 0..127, S buffers at 128 and 192; P(j) overwrites S(j): value in columns
 // 0..31 of the buffer, rounding remainder in 32..63
 constexpr uint32_t COL_O = 0, COL_S = 128, COLS_PER_TILE = 256;
@@ -41,11 +42,11 @@ constexpr uint32_t COL_O = 0, COL_S = 128, COLS_PER_TILE = 256;
 // keeps the full 2^-12 of each weight, which measured 2.4e-3 of the output's scale on a 512-token causal chunk;
 // the remainder MMA removes it and is dropped page by page, see P_SKIP_FRACTION)
 
-// per query tile and per parity of the page index: the two half-row maxima of every row, then one flag per softmax warp
-constexpr int XCHG_FLOATS = 2 * PM + 8;
-// f16 weights skip the remainder MMA of a page once, for every row of the tile, sqrt(32) x the largest weight of the
-// page is below this fraction of the row's running sum (each half row tested on its own 32 columns): what the
-// rounding of such a page can add is then below 2^-12 / 8 of the row's scale
+// per query tile and per parity of the page index: one flag per softmax warp (does the page need its remainder product)
+constexpr int XCHG_FLOATS = 8;
+// f16 weights skip the remainder MMA of a page once, for every row of the tile, sqrt(64) x the largest weight of the
+// page is below this fraction of the row's running sum: what the rounding of such a page can add is then below
+// 2^-12 / 8 of the row's scale
 constexpr float P_SKIP_FRACTION = 0.125f;
 
 template <int NQ>
@@ -72,9 +73,8 @@ struct PrefillParams {
     float skip_fraction;
 };
 
-// Softmax threads of tile qt: warps w and w + 4 of the tile both address TMEM lanes 32 (w & 3) .. + 32 (a warp may
-// touch only the lane quarter of its index modulo 4); the first takes score columns 0..31 and output channels
-// 0..63 of its row, the second the other halves.
+// Softmax threads of tile qt: warp w of the tile addresses TMEM lanes 32 w .. + 32 (a warp may touch only the lane
+// quarter of its index modulo 4, and every tile has four softmax warps); lane l owns row 32 w + l.
 template <int NQ>
 __global__ void __launch_bounds__(PGeo<NQ>::THREADS, NQ == 2 ? 1 : 2) prefill_tc_kernel(PrefillParams p) {
     using GEO = PGeo<NQ>;
@@ -92,7 +92,7 @@ __global__ void __launch_bounds__(PGeo<NQ>::THREADS, NQ == 2 ? 1 : 2) prefill_tc
     uint64_t* bar_o = bar_p + 2 * NQ;                      // [NQ][2] P.V of page j completed, on barrier j & 1
     uint32_t* tmem_slot = (uint32_t*)(((uintptr_t)(bar_o + 2 * NQ) + 15) & ~(uintptr_t)15);
     volatile int* fail_s = (volatile int*)(tmem_slot + 1);
-    float* xchg = (float*)(tmem_slot + 4);                 // [NQ][2 parities][XCHG_FLOATS]: row maxima / sums and remainder flags
+    float* xchg = (float*)(tmem_slot + 4);                 // [NQ][2 parities][XCHG_FLOATS]: remainder flags of the softmax warps
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int kvh = blockIdx.y, b = blockIdx.z;
@@ -117,8 +117,8 @@ __global__ void __launch_bounds__(PGeo<NQ>::THREADS, NQ == 2 ? 1 : 2) prefill_tc
     if (warp == 0) tmem_alloc(tmem_slot, COLS_PER_TILE * NQ);
 
     // per-thread tile geometry (softmax threads only; the extra warp gets harmless values)
-    const int qt = min(tid / SM_THREADS, NQ - 1), w8 = (tid % SM_THREADS) >> 5;
-    const int row = (w8 & 3) * 32 + lane, half = w8 >> 2;
+    const int qt = min(tid / SM_THREADS, NQ - 1), w4 = (tid % SM_THREADS) >> 5;
+    const int row = w4 * 32 + lane;
     const int q0 = cta_q0 + qt * qpt;
     const int rq = row / G, rg = row % G;
     const bool live = rq < qpt && q0 + rq < p.S;
@@ -129,14 +129,14 @@ __global__ void __launch_bounds__(PGeo<NQ>::THREADS, NQ == 2 ? 1 : 2) prefill_tc
     const bool is_softmax = tid < NQ * SM_THREADS;
 
     // ---- Q tile -> shared memory, K-major with the 128-byte swizzle (row r: 16-byte unit u of plane pl at u ^ (r & 7));
-    //      this thread moves the 64 channels of plane `half` of its row ----
+    //      this thread moves its row ----
     if (is_softmax) {
         const int head = kvh * G + rg;
-        const uint4* src = (const uint4*)((const uint16_t*)p.q + (int64_t)b * p.qb + (int64_t)head * p.qh + (int64_t)my_q * p.qs) + half * 8;
+        const uint4* src = (const uint4*)((const uint16_t*)p.q + (int64_t)b * p.qb + (int64_t)head * p.qh + (int64_t)my_q * p.qs);
 #pragma unroll
-        for (int uu = 0; uu < 8; uu++) {
+        for (int uu = 0; uu < 16; uu++) {
             uint4 v = live ? src[uu] : make_uint4(0, 0, 0, 0);
-            *(uint4*)(q_s + qt * P_QBYTES + half * (PM * 128) + row * 128 + ((uu ^ (row & 7)) << 4)) = v;
+            *(uint4*)(q_s + qt * P_QBYTES + (uu >> 3) * (PM * 128) + row * 128 + (((uu & 7) ^ (row & 7)) << 4)) = v;
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the tensor core
     }
@@ -211,8 +211,8 @@ __global__ void __launch_bounds__(PGeo<NQ>::THREADS, NQ == 2 ? 1 : 2) prefill_tc
                 wait_or_fail(&bar_p[2 * t + (j & 1)], (uint32_t)((j >> 1) & 1), fail_s);
                 tc_fence_after();
                 // the softmax warps say, one flag each, whether this page's weights need their remainder
-                const int* flags = (const int*)(xchg + (2 * t + (j & 1)) * XCHG_FLOATS + 2 * PM);
-                const bool two = !adaptive || __any_sync(0xffffffffu, flags[lane & 7] != 0);
+                const int* flags = (const int*)(xchg + (2 * t + (j & 1)) * XCHG_FLOATS);
+                const bool two = !adaptive || __any_sync(0xffffffffu, flags[lane & 3] != 0);
                 if (elect_one()) {
                     const uint64_t vd = v_desc + (uint64_t)(((j % NV) * P_CHUNK) >> 4);
                     const uint32_t pa = tm + COL_S + 64 * (j & 1);
@@ -233,57 +233,46 @@ __global__ void __launch_bounds__(PGeo<NQ>::THREADS, NQ == 2 ? 1 : 2) prefill_tc
     } else {
 
         // ================= softmax threads =================
-        const uint32_t lane_base = tmem + qt * COLS_PER_TILE + ((uint32_t)((w8 & 3) * 32) << 16);  // this warp's lane quarter
-        const int pair_id = 1 + qt * 4 + (w8 & 3);        // named barrier of the two warps that share these 32 rows
+        const uint32_t lane_base = tmem + qt * COLS_PER_TILE + ((uint32_t)(w4 * 32) << 16);  // this warp's lane quarter
         const bool adaptive = !p.is_bf16;
         const float sl2 = p.scale * 1.4426950408889634f;  // scores enter the exponent in log2 units
-        float m_ref = -INFINITY, l_run = 0.f;             // l_run: this thread's half of the row sum
+        float m_ref = -INFINITY, l_run = 0.f, log_thresh = -INFINITY;
 
         for (int j = 0; j < n_tiles; j++) {
             const uint32_t sbuf = lane_base + COL_S + 64 * (j & 1);
             wait_or_fail(&bar_s[2 * qt + (j & 1)], (uint32_t)((j >> 1) & 1), fail_s);
             tc_fence_after();
-            // ---- this thread's 32 of the row's 64 scores ----
-            uint32_t sr[32];
-            tmem_ld32(sbuf + 32 * half, sr);
+            // ---- the row's 64 scores ----
+            uint32_t sr[64];
+            tmem_ld32(sbuf, sr);
+            tmem_ld32(sbuf + 32, sr + 32);
             tmem_ld_wait();
-            float tmax = -INFINITY;
             if (j * PAGE_TOKENS + PAGE_TOKENS - 1 > min_limit) {  // only pages on the causal diagonal / past the end need a mask
-                const int t0 = j * PAGE_TOKENS + 32 * half;
+                const int t0 = j * PAGE_TOKENS;
 #pragma unroll
-                for (int c = 0; c < 32; c++) {
-                    const float s = (t0 + c <= my_limit) ? __uint_as_float(sr[c]) : -INFINITY;
-                    sr[c] = __float_as_uint(s);
-                    tmax = fmaxf(tmax, s);
+                for (int c = 0; c < 64; c++)
+                    if (t0 + c > my_limit) sr[c] = 0xff800000u;  // -inf
+            }
+            float tmax = row_max64(sr);
+            int* flags = (int*)(xchg + (2 * qt + (j & 1)) * XCHG_FLOATS);
+            tmax *= sl2;
+            // Two questions per row, answered for the warp with one reduction.  Bit 0: does this page need the remainder
+            // product (see P_SKIP_FRACTION; compared in the log domain against log2(fraction x running sum), kept from the
+            // page before; page 0 always keeps it).  Bit 1: is the reference maximum exceeded by more than 2^8 -- it is
+            // raised only then, so the exponentials stay below 256, exact enough in 16 bits, and O is rescaled rarely.
+            const bool mine = adaptive && (j == 0 || tmax - m_ref + 3.f > log_thresh);
+            const bool raise = j > 0 && tmax > m_ref + 8.f;
+            const uint32_t votes = __reduce_or_sync(0xffffffffu, (mine ? 1u : 0u) | (raise ? 2u : 0u));
+            const bool two = !adaptive || (votes & 1u);
+            if (adaptive && lane == 0) flags[w4] = two ? 1 : 0;  // the MMA warp issues the remainder product if any warp asks for it
+            if (j == 0) m_ref = tmax;
+            if (votes & 2u) {
+                float alpha = 1.f;
+                if (raise) {
+                    alpha = fast_exp2(m_ref - tmax);
+                    m_ref = tmax;
+                    l_run *= alpha;
                 }
-            } else {
-#pragma unroll
-                for (int c = 0; c < 32; c++) tmax = fmaxf(tmax, __uint_as_float(sr[c]));
-            }
-            float* xq = xchg + (2 * qt + (j & 1)) * XCHG_FLOATS;
-            int* flags = (int*)(xq + 2 * PM);
-            bool two = true;
-            // see P_SKIP_FRACTION; page 0 always keeps its remainder (l_run is 0).  The MMA warp issues the remainder
-            // product if any warp asks for it, so a warp that does not need it writes zeros there
-            if (adaptive) {
-                const bool mine = j == 0 || fast_exp2(fmaf(tmax, sl2, -m_ref)) * 5.657f > p.skip_fraction * l_run;
-                two = __any_sync(0xffffffffu, mine);
-                if (lane == 0) flags[w8] = two ? 1 : 0;
-            }
-            xq[half * PM + row] = tmax;
-            pair_barrier(pair_id);  // maxima exchanged; both halves of S(j) are in registers, so P may overwrite them
-            tmax = fmaxf(tmax, xq[(half ^ 1) * PM + row]) * sl2;
-            // raise the reference maximum only when it is exceeded by more than 2^8: the exponentials stay below
-            // 256, exact enough in 16 bits, and O has to be rescaled only rarely
-            float alpha = 1.f;
-            if (j == 0) {
-                m_ref = tmax;
-            } else if (tmax > m_ref + 8.f) {
-                alpha = fast_exp2(m_ref - tmax);
-                m_ref = tmax;
-                l_run *= alpha;
-            }
-            if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
                 // O must hold every page before this one.  S(j) being there says that P.V(j - 2) has completed (Q.K(j) was
                 // issued behind it); P.V(j - 1) may or may not have.  A parity wait tells only two consecutive phases of a
                 // barrier apart, so the products alternate between two barriers: on barrier (j - 1) & 1 the phase before the one
@@ -292,61 +281,25 @@ __global__ void __launch_bounds__(PGeo<NQ>::THREADS, NQ == 2 ? 1 : 2) prefill_tc
                 wait_or_fail(&bar_o[2 * qt + ((j - 1) & 1)], (uint32_t)(((j - 1) >> 1) & 1), fail_s);
                 tc_fence_after();
 #pragma unroll
-                for (int cc = 0; cc < 4; cc++) {  // this thread's 64 of the row's 128 output channels
+                for (int cc = 0; cc < 8; cc++) {  // the row's 128 output channels
                     uint32_t orow[16];
-                    tmem_ld16(lane_base + COL_O + 64 * half + cc * 16, orow);
+                    tmem_ld16(lane_base + COL_O + cc * 16, orow);
                     tmem_ld_wait();
 #pragma unroll
                     for (int c = 0; c < 16; c++) orow[c] = __float_as_uint(__uint_as_float(orow[c]) * alpha);
-                    tmem_st16(lane_base + COL_O + 64 * half + cc * 16, orow);
+                    tmem_st16(lane_base + COL_O + cc * 16, orow);
                 }
             }
-            uint32_t pr[16];
-            float lsum = 0.f;
-            if (p.is_bf16) {
-                uint32_t pr2[16];
-#pragma unroll
-                for (int c = 0; c < 16; c++) {
-                    const float p0 = fast_exp2(fmaf(__uint_as_float(sr[2 * c]), sl2, -m_ref));
-                    const float p1 = fast_exp2(fmaf(__uint_as_float(sr[2 * c + 1]), sl2, -m_ref));
-                    lsum += p0 + p1;
-                    __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-                    __nv_bfloat162 l = __floats2bfloat162_rn(p0 - __low2float(h), p1 - __high2float(h));
-                    pr[c] = *(uint32_t*)&h, pr2[c] = *(uint32_t*)&l;
-                }
-                tmem_st16(sbuf + 32 + 16 * half, pr2);
-            } else if (two) {
-                uint32_t pr2[16];
-#pragma unroll
-                for (int c = 0; c < 16; c++) {
-                    const float p0 = fast_exp2(fmaf(__uint_as_float(sr[2 * c]), sl2, -m_ref));
-                    const float p1 = fast_exp2(fmaf(__uint_as_float(sr[2 * c + 1]), sl2, -m_ref));
-                    lsum += p0 + p1;
-                    __half2 h = __floats2half2_rn(p0, p1);
-                    __half2 l = __floats2half2_rn(p0 - __low2float(h), p1 - __high2float(h));
-                    pr[c] = *(uint32_t*)&h, pr2[c] = *(uint32_t*)&l;
-                }
-                tmem_st16(sbuf + 32 + 16 * half, pr2);
-            } else {
-                float lsum2 = 0.f;
-#pragma unroll
-                for (int c = 0; c < 16; c += 2) {
-                    const float p0 = fast_exp2(fmaf(__uint_as_float(sr[2 * c]), sl2, -m_ref));
-                    const float p1 = fast_exp2(fmaf(__uint_as_float(sr[2 * c + 1]), sl2, -m_ref));
-                    const float p2 = fast_exp2(fmaf(__uint_as_float(sr[2 * c + 2]), sl2, -m_ref));
-                    const float p3 = fast_exp2(fmaf(__uint_as_float(sr[2 * c + 3]), sl2, -m_ref));
-                    lsum += p0 + p1, lsum2 += p2 + p3;
-                    __half2 h = __floats2half2_rn(p0, p1), h2 = __floats2half2_rn(p2, p3);
-                    pr[c] = *(uint32_t*)&h, pr[c + 1] = *(uint32_t*)&h2;
-                }
-                lsum += lsum2;
-                uint32_t zero[16];
-#pragma unroll
-                for (int c = 0; c < 16; c++) zero[c] = 0u;
-                tmem_st16(sbuf + 32 + 16 * half, zero);
-            }
-            l_run += lsum;
-            tmem_st16(sbuf + 16 * half, pr);
+            // ---- P = 2^(s * scale * log2 e - m_ref), its 16-bit value and (when the page needs it) what that rounding lost ----
+            uint32_t pr[32], pr2[32];
+            float page_sum;
+            if (p.is_bf16) page_sum = softmax_exps<2>(sr, sl2, m_ref, pr, pr2);
+            else if (two) page_sum = softmax_exps<1>(sr, sl2, m_ref, pr, pr2);
+            else page_sum = softmax_exps<0>(sr, sl2, m_ref, pr, pr2);
+            tmem_st32(sbuf + 32, pr2);
+            tmem_st32(sbuf, pr);
+            l_run += page_sum;
+            log_thresh = fast_log2(p.skip_fraction * l_run);
             tmem_st_wait();
             tc_fence_before();
             __syncwarp();
@@ -355,16 +308,13 @@ __global__ void __launch_bounds__(PGeo<NQ>::THREADS, NQ == 2 ? 1 : 2) prefill_tc
         // ---- epilogue: wait for the last P.V, normalise, store ----
         wait_or_fail(&bar_o[2 * qt + ((n_tiles - 1) & 1)], (uint32_t)(((n_tiles - 1) >> 1) & 1), fail_s);  // see the rescale above
         tc_fence_after();
-        float* xq = xchg + (2 * qt + (n_tiles & 1)) * XCHG_FLOATS;  // the buffer page n_tiles - 2 used: everyone is past it
-        xq[half * PM + row] = l_run;
-        pair_barrier(pair_id);
         if (!*fail_s) {
-            const float inv = 1.f / (l_run + xq[(half ^ 1) * PM + row]);
-            uint16_t* dst = (uint16_t*)p.out + (int64_t)b * p.ob + (int64_t)(kvh * G + rg) * p.oh + (int64_t)my_q * p.os + 64 * half;
+            const float inv = 1.f / l_run;
+            uint16_t* dst = (uint16_t*)p.out + (int64_t)b * p.ob + (int64_t)(kvh * G + rg) * p.oh + (int64_t)my_q * p.os;
 #pragma unroll
-            for (int cc = 0; cc < 2; cc++) {
+            for (int cc = 0; cc < 4; cc++) {
                 uint32_t orow[32];
-                tmem_ld32(lane_base + COL_O + 64 * half + cc * 32, orow);
+                tmem_ld32(lane_base + COL_O + cc * 32, orow);
                 tmem_ld_wait();
                 if (live) {
 #pragma unroll
@@ -433,7 +383,10 @@ int launch_prefill_tc(b200kv_cache* c, int32_t n_seqs, const int32_t* seqs, int3
         hw[2 * i] = seqs[i];
         hw[2 * i + 1] = (int32_t)c->seqs[seqs[i]].len;
     }
-    if (staging_upload(c, slot, (size_t)n_seqs * 8, stream) != B200KV_OK) return B200KV_KO;
+    if (staging_upload(c, slot, (size_t)n_seqs * 8, stream) != B200KV_OK) {
+        staging_release(c, slot, stream);
+        return B200KV_KO;
+    }
     PrefillParams p{};
     p.pool = c->pool, p.table = c->d_table, p.desc = (const int32_t*)d, p.status = c->d_status;
     p.q = q, p.out = out;

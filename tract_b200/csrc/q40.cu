@@ -19,6 +19,7 @@
 
 #include "glue_math.cuh"
 #include "internal.h"
+#include "f32x2.cuh"
 #include "q40_common.cuh"
 
 namespace b200kv {
@@ -148,33 +149,6 @@ __device__ inline void mma_u8s8(int (&d)[4], const uint32_t (&a)[4], uint32_t b0
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(c));
 }
 
-// Two f32 values in a 64-bit register pair and the packed IEEE operations of sm_100 on them: each lane is rounded to
-// nearest on its own, exactly as the scalar instruction would, at half the instruction count.
-__device__ inline uint64_t f2_pack(float lo, float hi) {
-    uint64_t r;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-    return r;
-}
-__device__ inline uint64_t f2_pack_bits(int lo, int hi) {
-    uint64_t r;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
-    return r;
-}
-__device__ inline float2 f2_unpack(uint64_t v) {
-    float2 r;
-    asm("mov.b64 {%0, %1}, %2;" : "=f"(r.x), "=f"(r.y) : "l"(v));
-    return r;
-}
-__device__ inline uint64_t f2_add(uint64_t a, uint64_t b) {
-    uint64_t r;
-    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-    return r;
-}
-__device__ inline uint64_t f2_mul(uint64_t a, uint64_t b) {
-    uint64_t r;
-    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-    return r;
-}
 // acc + t as fma(t, 1, acc) with a 1 the compiler cannot see through (a kernel parameter): the assembler was seen to
 // contract mul.rn.f32x2 followed by add.rn.f32x2 into one fused multiply-add, which rounds once where the reference
 // rounds twice; a product that feeds the multiplicand of an fma cannot be contracted into it.
@@ -187,7 +161,7 @@ __device__ inline uint64_t f2_accumulate(uint64_t acc, uint64_t t, uint64_t one2
 // (dot as f32) * w_scale * a_scale, each operation rounded on its own.  d0, d1: finished MMA accumulators (started at
 // Q_F32_INT_BASE); par = {a_scale of the two rows, their offset terms}.
 __device__ inline uint64_t q40_contribution(int d0, int d1, uint64_t w_scale2, const float4& par) {
-    const uint64_t dot = f2_add(f2_pack_bits(d0, d1), f2_pack(par.z, par.w));
+    const uint64_t dot = f2_add(f2_pack_bits((uint32_t)d0, (uint32_t)d1), f2_pack(par.z, par.w));
     return f2_mul(f2_mul(dot, w_scale2), f2_pack(par.x, par.y));
 }
 
