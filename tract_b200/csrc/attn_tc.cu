@@ -33,6 +33,7 @@
 // Every wait is bounded; on expiry the CTA flags the status word, every role runs to the end of its loop without
 // waiting any more, the CTA frees its TMEM and returns.
 #include <cmath>
+#include <type_traits>
 
 #include "kivi_common.cuh"
 #include "tc_common.cuh"
@@ -133,8 +134,8 @@ __device__ inline uint32_t tile_off(int u, int row) { return (u / 8) * (PAGE_TOK
 // token: the 16 codes of an item come from one 16- or 8-byte load of a natural row (Q4_0: low and high nibbles of the same
 // 8 bytes are the two units), or from 8 two-byte (Q8_1) / one-byte (Q4_0) loads of a permuted V row.  `lo_tile` (K): the
 // tile that takes the remainders.  Rows from n_valid on are zero-filled.
-template <int FMT, int D, int KV, int FT>
-__device__ inline void convert_chunk(const uint8_t* raw, uint8_t* hi_tile, uint8_t* lo_tile, int n_valid, int t) {
+template <int FMT, int D, int KV, int FT, bool FULL>
+__device__ inline void convert_rows(const uint8_t* raw, uint8_t* hi_tile, uint8_t* lo_tile, int n_valid, int t) {
     constexpr bool PERM = v_permuted(FMT, D, KV), Q8 = FMT == B200KV_FMT_Q8_1, SPLIT = KV == 0;
     constexpr int ITEMS = D / 16, TLN = FT / ITEMS;
     constexpr uint32_t BIAS = Q8 ? 0x64806480u : 0x64086408u;  // f16 pair 1024 + 128 | 1024 + 8: what the codes are offset by
@@ -182,7 +183,7 @@ __device__ inline void convert_chunk(const uint8_t* raw, uint8_t* hi_tile, uint8
         const uint32_t sb16 = __half_as_ushort(scales[scale_index(FMT, D, KV, tok, blk_b)]);
         const uint32_t sa = sa16 | (sa16 << 16), sb = sb16 | (sb16 << 16);
         uint32_t ha[4], hb[4], la[4], lb[4];
-        const bool ok = tok < n_valid;
+        const bool ok = FULL || tok < n_valid;  // a full page (all but, at most, the last) runs without the sixteen selects
 #pragma unroll
         for (int i = 0; i < 4; i++) {
             const uint32_t xa = hsub2(ca[i], BIAS), xb = hsub2(cb[i], BIAS);  // the codes themselves
@@ -196,6 +197,12 @@ __device__ inline void convert_chunk(const uint8_t* raw, uint8_t* hi_tile, uint8
             *(uint4*)(lo_tile + tile_off(ub, tok)) = make_uint4(lb[0], lb[1], lb[2], lb[3]);
         }
     }
+}
+
+template <int FMT, int D, int KV, int FT>
+__device__ inline void convert_chunk(const uint8_t* raw, uint8_t* hi_tile, uint8_t* lo_tile, int n_valid, int t) {
+    if (n_valid >= PAGE_TOKENS) convert_rows<FMT, D, KV, FT, true>(raw, hi_tile, lo_tile, n_valid, t);
+    else convert_rows<FMT, D, KV, FT, false>(raw, hi_tile, lo_tile, n_valid, t);
 }
 
 template <int NQ, int D, int SRC, int FT>
@@ -472,6 +479,15 @@ __global__ void __launch_bounds__(AGeo<NQ, D, SRC, FT>::THREADS, 1) attn_tc_kern
                     }
                     hi = make_uint4(wh[0], wh[1], wh[2], wh[3]), lo = make_uint4(wl[0], wl[1], wl[2], wl[3]);
                 };
+                auto pack8_hi = [&](const float* f, uint4& hi) {  // values only (V tolerates the rounding)
+                    uint32_t wh[4];
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        const __half2 h = __floats2half2_rn(f[2 * e], f[2 * e + 1]);
+                        wh[e] = *(const uint32_t*)&h;
+                    }
+                    hi = make_uint4(wh[0], wh[1], wh[2], wh[3]);
+                };
                 auto tile_addr = [&](uint8_t* base, int row) { return base + tile_off(u, row); };
                 uint8_t* carry_lo = carry + A_CARRY;  // the remainders of the carried K rows
                 for (int j = 0; j < n_tiles; j++) {
@@ -499,8 +515,8 @@ __global__ void __launch_bounds__(AGeo<NQ, D, SRC, FT>::THREADS, 1) attn_tc_kern
                         }
                     }
                     asm volatile("bar.sync 9, %0;" ::"n"(FT) : "memory");  // every converter warp has read the carry: it may be rewritten
-#pragma unroll 1
-                    for (int st = 0; st < 2; st++) {  // K, then V
+                    auto fill = [&](auto st_c) {  // K (0), then V (1): one body, specialised at compile time
+                        constexpr int st = decltype(st_c)::value;
                         uint8_t* dst;
                         if (st == 0) {
                             if (j >= NK) wait_or_fail(&free_k[j % NK], (uint32_t)((j / NK - 1) & 1), fail_s);
@@ -525,11 +541,11 @@ __global__ void __launch_bounds__(AGeo<NQ, D, SRC, FT>::THREADS, 1) attn_tc_kern
                                     const float4 a = src[0], b2 = src[1];
                                     f[0] = a.x, f[1] = a.y, f[2] = a.z, f[3] = a.w, f[4] = b2.x, f[5] = b2.y, f[6] = b2.z, f[7] = b2.w;
                                 } else {
-                                    uint32_t cb[8];
+                                    uint32_t cb[8];  // the byte that holds each channel's code
                                     if (st == 0) {
                                         const uint2 x = *(const uint2*)(codes + chunk_addr(lfmt, 128, 0, s, kpos0));
 #pragma unroll
-                                        for (int e = 0; e < 4; e++) cb[e] = (x.x >> (8 * e)) & 0xffu, cb[4 + e] = (x.y >> (8 * e)) & 0xffu;
+                                        for (int e = 0; e < 4; e++) cb[e] = __byte_perm(x.x, 0u, 0x4440 + e), cb[4 + e] = __byte_perm(x.y, 0u, 0x4440 + e);
                                     } else {
 #pragma unroll
                                         for (int e = 0; e < 8; e++) cb[e] = codes[chunk_addr(lfmt, 128, 1, s, vpos[e])];
@@ -552,8 +568,9 @@ __global__ void __launch_bounds__(AGeo<NQ, D, SRC, FT>::THREADS, 1) attn_tc_kern
                                     }
                                 }
                             }
-                            uint4 w, wl;
-                            pack8(f, w, wl);
+                            uint4 w, wl = make_uint4(0u, 0u, 0u, 0u);
+                            if (st == 0) pack8(f, w, wl);
+                            else pack8_hi(f, w);
                             if (s < PAGE_TOKENS - SINK) {
                                 *(uint4*)tile_addr(dst, s + SINK) = w;
                                 if (st == 0) *(uint4*)tile_addr(dst + CHUNK, s + SINK) = wl;
@@ -565,7 +582,9 @@ __global__ void __launch_bounds__(AGeo<NQ, D, SRC, FT>::THREADS, 1) attn_tc_kern
                         fence_async_proxy();
                         __syncwarp();
                         if (lane == 0) mbar_arrive(st == 0 ? &full_k[j % NK] : &full_v[j % NV]);
-                    }
+                    };
+                    fill(std::integral_constant<int, 0>{});
+                    fill(std::integral_constant<int, 1>{});
                     asm volatile("bar.sync 9, %0;" ::"n"(FT) : "memory");  // the new carry is complete before the next tile reads it
                     if (has_page) {
                         if (lane == 0) mbar_arrive(&free_raw[j % NR]);

@@ -31,8 +31,10 @@ __device__ inline uint32_t kivi_code_offset(int bits, int stream, int slot, int 
     return chunk_addr(fmt, 128, stream, slot, code_pos(fmt, 128, stream, c));
 }
 
+// A code (below 2^23) as f32, exactly, without the conversion unit: 0x4B000000 | code is the float 2^23 + code.
+__device__ inline float kivi_code_f32(uint32_t code) { return __fsub_rn(__uint_as_float(0x4B000000u | code), 8388608.f); }
 // lo + code * scale, multiply then add (quant_dyn_kv_cache.rs:141-146, :231-240)
-__device__ inline float kivi_dequant(uint32_t code, float lo, float scale) { return __fadd_rn(lo, __fmul_rn((float)code, scale)); }
+__device__ inline float kivi_dequant(uint32_t code, float lo, float scale) { return __fadd_rn(lo, __fmul_rn(kivi_code_f32(code), scale)); }
 
 __device__ inline uint32_t kivi_load_code(const KiviView& v, int stream, int32_t pg, int h, int slot, int c) {
     if (kivi_mma_layout(v.bits, v.D)) {
