@@ -141,32 +141,39 @@ __device__ inline void convert_rows(const uint8_t* raw, uint8_t* hi_tile, uint8_
     constexpr uint32_t BIAS = Q8 ? 0x64806480u : 0x64086408u;  // f16 pair 1024 + 128 | 1024 + 8: what the codes are offset by
     const int item = t % ITEMS, tl = t / ITEMS;
     const __half* scales = (const __half*)(raw + PAGE_TOKENS * fmt_row_bytes(FMT, D));
-    // the two units the item yields, and their blocks
+    // The two units the item yields, and their blocks.  At head_dim 128 a quarter warp (one 16-byte store phase) is the eight
+    // items of one token, four per 64-channel plane, and the planes lie a multiple of the bank width apart: if every item
+    // stored its lower unit first, the planes would collide two ways in every store.  The items of the second plane
+    // therefore take their units in the other order (`sw`): each phase then covers eight different 16-byte slots.
+    const bool sw = D == 128 && (item & 4);
     int ua, ub;
-    if (Q8 || PERM) ua = 2 * item, ub = 2 * item + 1;
-    else ua = 4 * (item / 2) + (item % 2), ub = ua + 2;  // Q4_0 natural: bytes 16b + 8q .. hold channels 32b + 8q .. (low) and + 16 (high)
+    if (Q8 || PERM) ua = 2 * item + (sw ? 1 : 0), ub = 2 * item + (sw ? 0 : 1);
+    else ua = 4 * (item / 2) + (item % 2) + (sw ? 2 : 0), ub = 4 * (item / 2) + (item % 2) + (sw ? 0 : 2);  // Q4_0 natural: bytes 16b + 8q .. hold channels 32b + 8q .. (low) and + 16 (high)
     const int blk_a = ua / 4, blk_b = ub / 4;
+    const uint32_t sel_a = sw ? 0x4341u : 0x4240u, sel_b = sw ? 0x4240u : 0x4341u;  // permuted Q8_1 rows: which byte of a pair
+    const int sh_a = sw ? 4 : 0, sh_b = sw ? 0 : 4;                                  // permuted Q4_0 rows: which nibble
 #pragma unroll 4
     for (int tt = 0; tt < PAGE_TOKENS / TLN; tt++) {  // independent tokens: unrolled so that their loads and chains overlap
         const int tok = tt * TLN + tl;
         uint32_t ca[4], cb[4];  // f16 pairs: the codes of unit ua / ub as 1024 + u
         if constexpr (Q8 && !PERM) {
             const uint4 x = *(const uint4*)(raw + chunk_addr(FMT, D, KV, tok, 16 * item));
-            ca[0] = __byte_perm(x.x, H_MAGIC, 0x4140), ca[1] = __byte_perm(x.x, H_MAGIC, 0x4342);
-            ca[2] = __byte_perm(x.y, H_MAGIC, 0x4140), ca[3] = __byte_perm(x.y, H_MAGIC, 0x4342);
-            cb[0] = __byte_perm(x.z, H_MAGIC, 0x4140), cb[1] = __byte_perm(x.z, H_MAGIC, 0x4342);
-            cb[2] = __byte_perm(x.w, H_MAGIC, 0x4140), cb[3] = __byte_perm(x.w, H_MAGIC, 0x4342);
+            const uint32_t w0 = sw ? x.z : x.x, w1 = sw ? x.w : x.y, w2 = sw ? x.x : x.z, w3 = sw ? x.y : x.w;
+            ca[0] = __byte_perm(w0, H_MAGIC, 0x4140), ca[1] = __byte_perm(w0, H_MAGIC, 0x4342);
+            ca[2] = __byte_perm(w1, H_MAGIC, 0x4140), ca[3] = __byte_perm(w1, H_MAGIC, 0x4342);
+            cb[0] = __byte_perm(w2, H_MAGIC, 0x4140), cb[1] = __byte_perm(w2, H_MAGIC, 0x4342);
+            cb[2] = __byte_perm(w3, H_MAGIC, 0x4140), cb[3] = __byte_perm(w3, H_MAGIC, 0x4342);
         } else if constexpr (Q8) {  // permuted V row: bytes 16r + 2 item, + 1 hold channels 16 item + r and + 8
 #pragma unroll
             for (int i = 0; i < 4; i++) {
                 const uint32_t h0 = *(const uint16_t*)(raw + chunk_addr(FMT, D, KV, tok, 16 * (2 * i) + 2 * item));
                 const uint32_t h1 = *(const uint16_t*)(raw + chunk_addr(FMT, D, KV, tok, 16 * (2 * i + 1) + 2 * item));
                 const uint32_t both = __byte_perm(h0, h1, 0x5410);  // [low r, high r, low r + 1, high r + 1]
-                ca[i] = __byte_perm(both, H_MAGIC, 0x4240), cb[i] = __byte_perm(both, H_MAGIC, 0x4341);
+                ca[i] = __byte_perm(both, H_MAGIC, sel_a), cb[i] = __byte_perm(both, H_MAGIC, sel_b);
             }
         } else if constexpr (!PERM) {  // Q4_0 natural row
             const uint2 x = *(const uint2*)(raw + chunk_addr(FMT, D, KV, tok, 16 * (item / 2) + 8 * (item % 2)));
-            const uint32_t l0 = x.x & 0x0f0f0f0fu, h0 = (x.x >> 4) & 0x0f0f0f0fu, l1 = x.y & 0x0f0f0f0fu, h1 = (x.y >> 4) & 0x0f0f0f0fu;
+            const uint32_t l0 = (x.x >> sh_a) & 0x0f0f0f0fu, h0 = (x.x >> sh_b) & 0x0f0f0f0fu, l1 = (x.y >> sh_a) & 0x0f0f0f0fu, h1 = (x.y >> sh_b) & 0x0f0f0f0fu;
             ca[0] = __byte_perm(l0, H_MAGIC, 0x4140), ca[1] = __byte_perm(l0, H_MAGIC, 0x4342);
             ca[2] = __byte_perm(l1, H_MAGIC, 0x4140), ca[3] = __byte_perm(l1, H_MAGIC, 0x4342);
             cb[0] = __byte_perm(h0, H_MAGIC, 0x4140), cb[1] = __byte_perm(h0, H_MAGIC, 0x4342);
@@ -176,7 +183,7 @@ __device__ inline void convert_rows(const uint8_t* raw, uint8_t* hi_tile, uint8_
             for (int i = 0; i < 4; i++) {
                 const uint32_t b0 = raw[chunk_addr(FMT, D, KV, tok, 8 * (2 * i) + item)], b1 = raw[chunk_addr(FMT, D, KV, tok, 8 * (2 * i + 1) + item)];
                 const uint32_t both = b0 | (b1 << 16);
-                ca[i] = (both & 0x000f000fu) | 0x64006400u, cb[i] = ((both >> 4) & 0x000f000fu) | 0x64006400u;
+                ca[i] = ((both >> sh_a) & 0x000f000fu) | 0x64006400u, cb[i] = ((both >> sh_b) & 0x000f000fu) | 0x64006400u;
             }
         }
         const uint32_t sa16 = __half_as_ushort(scales[scale_index(FMT, D, KV, tok, blk_a)]);
