@@ -77,7 +77,8 @@ def test_decoder_steps_match_oracle_composition(use_graphs):
         # a maximum that a wiring mistake (wrong position, wrong cache, wrong slice: O(1) errors) cannot meet.
         rms = np.sqrt((want ** 2).mean())
         mean_err, max_err = np.abs(got - want).mean() / rms, rel_err(got, want)
-        assert (mean_err <= 1e-5 and max_err <= 1e-4) if step == 0 else (mean_err <= 2e-2 and max_err <= 0.15), (step, mean_err, max_err)
+        # (measured: 1.6e-7 / 4e-7 at step 0; 5e-3 .. 8.4e-3 mean and 0.017 .. 0.035 maximum afterwards)
+        assert (mean_err <= 2e-6 and max_err <= 1e-5) if step == 0 else (mean_err <= 1.2e-2 and max_err <= 0.06), (step, mean_err, max_err)
         tokens = dec.tokens.cpu().numpy().astype(np.int32)
         margin = np.sort(want, axis=1)[:, -1] - np.sort(want, axis=1)[:, -2]
         clear = margin > 0.1 * np.abs(want).max()
@@ -98,14 +99,14 @@ def test_decoder_prompt_pass_matches_token_by_token_oracle():
     dec.prefill(torch.from_numpy(prompt))
     got = dec.logits.cpu().numpy()
     rms = np.sqrt((want ** 2).mean())
-    assert np.abs(got - want).mean() / rms <= 2e-2 and rel_err(got, want) <= 0.15  # see the note in the decode-step test
+    assert np.abs(got - want).mean() / rms <= 1.2e-2 and rel_err(got, want) <= 0.06  # see the note in the decode-step test
     # and the decode steps carry on from the prompt's caches
     tokens = dec.tokens.cpu().numpy().astype(np.int32)
     for step in range(3):
         want = ref.step(tokens)
         dec.step()
         got = dec.logits.cpu().numpy()
-        assert np.abs(got - want).mean() / np.sqrt((want ** 2).mean()) <= 2e-2, step
+        assert np.abs(got - want).mean() / np.sqrt((want ** 2).mean()) <= 1.2e-2 and rel_err(got, want) <= 0.06, step
         tokens = dec.tokens.cpu().numpy().astype(np.int32)
     dec.check()
     dec.close()

@@ -6,21 +6,53 @@ import numpy as np
 TOL = {"f32": 1e-5, "f16": 2e-3, "bf16": 2e-3}
 
 
+class Err(float):
+    """A float that prints with the plain measures beside it: when `assert rel_err(...) <= tol` fails, pytest shows
+    the largest absolute difference, the largest plain relative difference among the elements whose reference is above
+    the rms, the rms itself and where the worst element is."""
+
+    def __new__(cls, value, **details):
+        self = super().__new__(cls, value)
+        self.details = details
+        return self
+
+    def __repr__(self):
+        extra = ", ".join(f"{k}={v:.4g}" if isinstance(v, float) else f"{k}={v}" for k, v in self.details.items())
+        return f"{float(self):.4g} ({extra})" if extra else f"{float(self):.4g}"
+
+    __str__ = __repr__
+
+
+def _plain_measures(got, ref, score):
+    diff = np.abs(got - ref)
+    rms = float(np.sqrt(np.mean(ref * ref)))
+    big = np.abs(ref) > rms
+    worst = np.unravel_index(int(np.argmax(score)), score.shape) if score.ndim else ()
+    return dict(max_abs=float(diff.max()), max_rel_above_rms=float((diff[big] / np.abs(ref[big])).max()) if big.any() else 0.0,
+                ref_rms=rms, worst_at=tuple(int(i) for i in worst), got=float(got[worst]), ref=float(ref[worst]))
+
+
 def rel_err(got, ref) -> float:
     """Max relative error with an RMS floor: max_i |got_i - ref_i| / (|ref_i| + rms(ref)).
 
     A purely element-wise ratio is undefined where the reference output crosses zero; dividing
     by the tensor maximum alone would hide errors on small entries.  Adding the RMS of the
-    reference to each denominator keeps the measure element-wise and finite.
+    reference to each denominator keeps the measure element-wise and finite.  The value returned
+    prints with the plain max-abs and max-relative measures beside it (see Err).
     """
     got = np.asarray(got, dtype=np.float64)
     ref = np.asarray(ref, dtype=np.float64)
     assert got.shape == ref.shape, (got.shape, ref.shape)
     if ref.size == 0:
-        return 0.0
+        return Err(0.0)
     rms = float(np.sqrt(np.mean(ref * ref)))
     den = np.abs(ref) + (rms if rms > 0 else 1.0)
-    return float(np.max(np.abs(got - ref) / den))
+    score = np.abs(got - ref) / den
+    with np.errstate(invalid="ignore"):
+        value = float(np.max(score))
+    if not np.isfinite(value):
+        return Err(value)
+    return Err(value, **_plain_measures(got, ref, score))
 
 
 def rel_err_bf16(got_bf16, ref_f32) -> float:
@@ -37,7 +69,11 @@ def rel_err_bf16(got_bf16, ref_f32) -> float:
     rms = float(np.sqrt(np.mean(ref * ref)))
     half_ulp = np.where(ref != 0, 2.0 ** (np.floor(np.log2(np.maximum(np.abs(ref), 1e-300))) - 8), 0.0)
     excess = np.maximum(np.abs(got - ref) - half_ulp, 0.0)
-    return float(np.max(excess / (np.abs(ref) + (rms if rms > 0 else 1.0))))
+    score = excess / (np.abs(ref) + (rms if rms > 0 else 1.0))
+    value = float(np.max(score))
+    if not np.isfinite(value) or ref.size == 0:
+        return Err(value)
+    return Err(value, **_plain_measures(got, ref, score))
 
 
 def rng(seed: int) -> np.random.Generator:
