@@ -349,15 +349,20 @@ __global__ void __launch_bounds__(AGeo<NQ, D, SRC, FT>::THREADS, 1) attn_tc_kern
                 if (elect_one()) {
                     const uint64_t kd = k_desc + (uint64_t)(((j % NK) * KSTAGE) >> 4);
 #pragma unroll
-                    for (int part = 0; part < KPARTS; part++)  // K as value (+ remainder): both products land in the same S
+                    for (int pl = 0; pl < PLANES; pl++)
 #pragma unroll
-                        for (int pl = 0; pl < PLANES; pl++)
-#pragma unroll
-                            for (int kk = 0; kk < 4; kk++) {
-                                const uint64_t off = (uint64_t)((pl * (AM * 128) + kk * 32) >> 4);
-                                tc_mma_ss(tm + COL_S + 64 * (j & 1), q_desc + off,
-                                          kd + (uint64_t)((part * CHUNK + pl * (PAGE_TOKENS * 128) + kk * 32) >> 4), idesc_s, (part | pl | kk) ? 1u : 0u);
+                        for (int kk = 0; kk < 4; kk++) {
+                            const uint64_t off = (uint64_t)((pl * (AM * 128) + kk * 32) >> 4);
+                            const uint64_t koff = (uint64_t)((pl * (PAGE_TOKENS * 128) + kk * 32) >> 4);
+                            if constexpr (KPARTS == 2) {
+                                // K as value + remainder: the two products of a k-step land in the same S and share their Q
+                                // slice, which the second takes from the collector buffer instead of shared memory
+                                tc_mma_ss_a<A_KEEP>(tm + COL_S + 64 * (j & 1), q_desc + off, kd + koff, idesc_s, (pl | kk) ? 1u : 0u);
+                                tc_mma_ss_a<A_REUSE_LAST>(tm + COL_S + 64 * (j & 1), q_desc + off, kd + (uint64_t)(CHUNK >> 4) + koff, idesc_s, 1u);
+                            } else {
+                                tc_mma_ss(tm + COL_S + 64 * (j & 1), q_desc + off, kd + koff, idesc_s, (pl | kk) ? 1u : 0u);
                             }
+                        }
                     tc_commit(&bar_s[2 * t + (j & 1)]);
                     tc_commit(&free_k[j % NK]);
                 }
