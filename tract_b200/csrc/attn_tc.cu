@@ -67,7 +67,7 @@ struct AGeo {
     static constexpr int RAW_STAGE = src_is_block(SRC) ? 2 * (PAGE_TOKENS * D + PAGE_TOKENS * (D / 32) * 2)   // a Q8_1 chunk pair (Q4_0: smaller)
                                      : src_is_kivi(SRC) ? 2 * PAGE_TOKENS * D + A_KIVI_KP + A_KIVI_VP         // int8 codes of K and V, their parameters
                                                         : 0;
-    // softmax threads, one MMA warp per tile, then either the copy warp (16-bit pages) or the two converter / loader warps
+    // softmax threads, one MMA warp per tile, then either the copy warp (16-bit pages) or the converter / loader warps
     static constexpr int THREADS = NQ * A_SM_THREADS + 32 * NQ + (FILL ? FT : 32);
     static constexpr int N_BARS = 2 * NK + 2 * NV + 6 * NQ + 2 * NR;
     static constexpr uint32_t COL_S = D, COLS_PER_TILE = 256;  // TMEM: O in columns 0 .. D-1, the two S buffers after it
@@ -130,7 +130,7 @@ __device__ inline uint32_t hfma2_rem(uint32_t a, uint32_t b, uint32_t prod) {  /
 // where unit u (8 channels, 16 bytes) of row `row` lies in an operand tile
 __device__ inline uint32_t tile_off(int u, int row) { return (u / 8) * (PAGE_TOKENS * 128) + row * 128 + (((u % 8) ^ (row & 7)) << 4); }
 
-// Thread t of the 64 converter threads takes item t % (D / 16) -- 16 channels, two units of 8 -- of every (64 * 16 / D)-th
+// Thread t of the FT converter threads takes item t % (D / 16) -- 16 channels, two units of 8 -- of every (16 FT / D)-th
 // token: the 16 codes of an item come from one 16- or 8-byte load of a natural row (Q4_0: low and high nibbles of the same
 // 8 bytes are the two units), or from 8 two-byte (Q8_1) / one-byte (Q4_0) loads of a permuted V row.  `lo_tile` (K): the
 // tile that takes the remainders.  Rows from n_valid on are zero-filled.
@@ -235,7 +235,7 @@ __global__ void __launch_bounds__(AGeo<NQ, D, SRC, FT>::THREADS, 1) attn_tc_kern
     uint64_t* bar_p = bar_s + 2 * NQ;                       // [NQ][2] P written by the softmax warps
     uint64_t* bar_o = bar_p + 2 * NQ;                       // [NQ][2] P.V of page j completed, on barrier j & 1
     uint64_t* full_raw = bar_o + 2 * NQ;                    // [NR] raw bytes landed
-    uint64_t* free_raw = full_raw + NR;                     // [NR] both converter warps are done with the raw stage
+    uint64_t* free_raw = full_raw + NR;                     // [NR] every converter warp is done with the raw stage
     uint32_t* tmem_slot = (uint32_t*)(((uintptr_t)(free_raw + NR) + 15) & ~(uintptr_t)15);
     volatile int* fail_s = (volatile int*)(tmem_slot + 1);
     float* xchg = (float*)(tmem_slot + 4);                  // [NQ][2 parities][A_XCHG]
@@ -394,7 +394,7 @@ __global__ void __launch_bounds__(AGeo<NQ, D, SRC, FT>::THREADS, 1) attn_tc_kern
             }
         } else {
             // ================= converter / loader warps: fill the operand rings =================
-            const int ft = tid - (NQ * A_SM_THREADS + 32 * NQ);  // 0 .. 63
+            const int ft = tid - (NQ * A_SM_THREADS + 32 * NQ);  // 0 .. FT - 1 (converters) or 0 .. 63 (loaders)
             if constexpr (src_is_block(SRC)) {
                 constexpr int FMT = SRC == SRC_Q8 ? B200KV_FMT_Q8_1 : B200KV_FMT_Q4_0;
                 const bool requester = ft < 32;  // the first converter warp also requests the raw pages
@@ -430,7 +430,7 @@ __global__ void __launch_bounds__(AGeo<NQ, D, SRC, FT>::THREADS, 1) attn_tc_kern
                     fence_async_proxy();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&full_v[i % NV]), mbar_arrive(&free_raw[i % NR]);
-                    if (requester && i + NR < n_tiles) {  // the stage is free once the other converter warp has left it too
+                    if (requester && i + NR < n_tiles) {  // the stage is free once the other converter warps have left it too
                         wait_or_fail(&free_raw[i % NR], (uint32_t)((i / NR) & 1), fail_s);
                         request(i + NR, pg_next);
                         if (i + NR + 1 < n_tiles) pg_next = trow_p[i + NR + 1];
