@@ -597,7 +597,7 @@ def run_linear(ctx, workload, steps, warmup, no_cpu=False):
         "e2e": {"value": world * weight_bytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": m * k * 4,
                 "d2h_bytes_per_step": m * n * 4, "ms_per_step": ms_e2e},
         "gpu_launches": 2 * layers * steps,
-        "roofline": {"bound": "hbm", "kernel": ("q40_gemm_rows_kernel" if m > 24 else "q40_gemm_kernel") + " (+ activation quantiser)", "achieved": achieved, "peak": pk["hbm_gbs"],
+        "roofline": {"bound": "hbm", "kernel": ("q40_gemm_tc_kernel" if m >= 128 else "q40_gemm_rows_kernel" if m > 24 else "q40_gemm_kernel") + " (+ activation quantiser)", "achieved": achieved, "peak": pk["hbm_gbs"],
                      "unit": "GB/s", "frac": achieved / pk["hbm_gbs"], "peak_kind": pk_kind, "traffic": None,
                      "algorithmic_bytes": weight_bytes, "kernel_ms": kern_ms},
         "clocks": clocks,

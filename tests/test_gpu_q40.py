@@ -43,6 +43,12 @@ def ggml_blocks(sc, pk):
     (64, 40, 14336, "f16"),   # exactly one block of 8 full groups, 56 stages through a 4-deep weight ring
     (100, 24, 352, "bf16"),   # a last stage of 3 blocks, fewer stages than the activation ring is deep... and a ragged tile
     (32, 16, 64, "f32"),      # one stage only
+    # 128 rows and more: the tcgen05 kernel over the tiled activation layout
+    (128, 130, 64, "f32"),    # one partly filled stage of two blocks; two column tiles, the second with two live columns
+    (130, 48, 4096, "f32"),   # two row tiles, the second with two live rows; fewer weight rows than a column tile
+    (512, 200, 352, "bf16"),  # 11 blocks: a last stage of 3; a ragged last column tile
+    (300, 16, 14336, "f16"),  # 448 blocks: 112 stages through the rings, 16 weight rows in a 128-column tile
+    (384, 256, 1024, "f32"),  # full tiles only
 ])
 def test_q40_gemm_bit_exact(kv, m, n, k, adt):
     w = normal_with_outliers(11, (n, k)).astype(np.float32)
@@ -80,13 +86,13 @@ def test_q40_errors(kv):
     assert lin.gemm(torch.zeros((1, 64), device="cuda")).abs().sum().item() == 0.0
 
 
-@pytest.mark.parametrize("m,n,k", [(1, 48, 64), (8, 64, 4096), (5, 32, 14336), (19, 48, 512), (40, 32, 2048)])
+@pytest.mark.parametrize("m,n,k", [(1, 48, 64), (8, 64, 4096), (5, 32, 14336), (19, 48, 512), (40, 32, 2048), (130, 48, 512), (200, 160, 2048)])
 def test_fused_producers_give_the_bits_of_the_separate_calls(kv, m, n, k):
     # add -> RmsNorm * weight -> quantise -> GEMM and Silu(gate) * up -> quantise -> GEMM, fused into the quantiser, against
     # the same ops launched one by one, and the first of them against the CPU restatements composed the same way
     w = normal_with_outliers(31, (n, k)).astype(np.float32)
     sc, pk = oracle.q4_0_quant(w)
-    lin = kv.Q40Linear(torch.from_numpy(ggml_blocks(sc, pk)).cuda(), max_m=64)
+    lin = kv.Q40Linear(torch.from_numpy(ggml_blocks(sc, pk)).cuda(), max_m=max(64, m))
     scratch = torch.empty(kv.Q40Linear.scratch_bytes(k, m), dtype=torch.uint8, device="cuda")
     x = torch.from_numpy(normal_with_outliers(32, (m, k)).astype(np.float32)).cuda()
     res = torch.from_numpy(normal(33, (m, k)).astype(np.float32)).cuda()

@@ -8,7 +8,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libb200kv.so")
-SOURCES = ["cache.cu", "decode.cu", "decode_mma.cu", "decode_static.cu", "prefill_tc.cu", "attn_tc.cu", "kivi.cu", "kivi_mma.cu", "q40.cu", "glue.cu", "rope.cu", "sdpa_dense.cu", "attend.cu"]
+SOURCES = ["cache.cu", "decode.cu", "decode_mma.cu", "decode_static.cu", "prefill_tc.cu", "attn_tc.cu", "kivi.cu", "kivi_mma.cu", "q40.cu", "q40_tc.cu", "glue.cu", "rope.cu", "sdpa_dense.cu", "attend.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",

@@ -333,13 +333,11 @@ __global__ void combine_kernel(CombineParams p, const __grid_constant__ InlineBa
     const int b = blockIdx.x, hq = blockIdx.y, ch = threadIdx.x;
     const int kvh = hq / p.G, g = hq % p.G;
     grid_dependency_wait();  // the decode kernel has published every partial
-    uint8_t* act_dst = nullptr;
+    const int64_t act_nb = (int64_t)p.Hkv * p.G * p.D / QK, act_blk = (int64_t)hq * (p.D / QK) + (ch >> 5);
     if (p.act) {  // a warp holds one block of 32 columns of row b
-        const int64_t nb = (int64_t)p.Hkv * p.G * p.D / QK;
-        act_dst = p.act + ((int64_t)(b >> 3) * nb + (int64_t)hq * (p.D / QK) + (ch >> 5)) * Q_ACT_BLOCK;
         if (b == 0 && hq == 0 && ch == 0) q40_status_begin(p.act_status);
         if (b >= p.n_rows) {
-            q40_quantize_block(0.f, false, act_dst, b & 7, ch & 31);
+            q40_quantize_block(0.f, false, p.act, p.n_rows, act_nb, b, act_blk, ch & 31);
             return;
         }
     }
@@ -379,7 +377,7 @@ __global__ void combine_kernel(CombineParams p, const __grid_constant__ InlineBa
     }
     const float res = num / den_s;
     if (p.out) st_from_f32(p.out, p.dtype, (int64_t)b * p.ob + (int64_t)hq * p.oh + ch, res);
-    if (p.act) q40_quantize_block(round_to_dtype(res, p.dtype), true, act_dst, b & 7, ch & 31);  // what a quantiser would read back from `out`
+    if (p.act) q40_quantize_block(round_to_dtype(res, p.dtype), true, p.act, p.n_rows, act_nb, b, act_blk, ch & 31);  // what a quantiser would read back from `out`
 }
 
 template <int FMT, int D, int GT>

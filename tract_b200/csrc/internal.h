@@ -179,4 +179,8 @@ int launch_attn_tc_dense(const void* q, const int64_t* qs, const void* k, const 
 int launch_export(b200kv_cache* c, int32_t seq, void* k_out, const int64_t* ks, void* v_out, const int64_t* vs,
                   int32_t dtype, cudaStream_t stream);
 
+// q40_tc.cu: the W4A8 GEMM for Q_TC_MIN_ROWS activation rows and more, on tcgen05
+int launch_q40_gemm_tc(const void* packed, const void* act, void* out, int* status, int64_t n, int64_t nb, int64_t out_stride, int32_t m,
+                       int32_t out_dtype, cudaStream_t stream);
+
 }  // namespace b200kv

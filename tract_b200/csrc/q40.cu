@@ -67,7 +67,7 @@ __global__ void q40_quant_act_kernel(const void* __restrict__ a, int64_t a_strid
             x = round_to_dtype(__fmul_rn(s, ld_as_f32(up, dtype, mi * up_stride + b * QK + lane)), dtype);
         }
     }
-    q40_quantize_block(x, mi < m, act + (g * nb + b) * Q_ACT_BLOCK, slot, lane);
+    q40_quantize_block(x, mi < m, act, m, nb, mi, b, lane);
 }
 
 // One CTA per activation row slot: v = x (+ residual), stored to x_out when given; then RmsNorm(v) * weight, quantised.
@@ -92,8 +92,7 @@ __global__ void __launch_bounds__(512) q40_norm_quant_kernel(const float* x, int
     grid_dependency_wait();  // the kernel before (the GEMM that wrote `residual`, and read `act`) is done
     if (blockIdx.x == 0 && threadIdx.x == 0) q40_status_begin(status);
     const int64_t mi = blockIdx.x, nb = d / QK;
-    const int slot = (int)(mi % 8), lane = threadIdx.x & 31;
-    uint8_t* dst = act + (mi / 8) * nb * Q_ACT_BLOCK;
+    const int lane = threadIdx.x & 31;
     const bool valid = mi < m;
     float v[EPT];
 #pragma unroll
@@ -127,7 +126,7 @@ __global__ void __launch_bounds__(512) q40_norm_quant_kernel(const float* x, int
         if (i < d) {
             float t = __fmul_rn(v[j], inv);
             if (weight) t = __fmul_rn(t, EPT <= 8 ? w[j < WPT ? j : 0] : weight[i]);
-            q40_quantize_block(t, valid, dst + (int64_t)(i / QK) * Q_ACT_BLOCK, slot, lane);
+            q40_quantize_block(t, valid, act, m, nb, mi, i / QK, lane);
         }
     }
 }
@@ -465,7 +464,7 @@ extern "C" int64_t b200kv_q40_packed_bytes(int64_t n, int64_t k) {
 
 extern "C" int64_t b200kv_q40_scratch_bytes(int64_t k, int32_t m) {
     if (m <= 0 || k <= 0 || k % QK) return -1;
-    return Q_HEADER + (int64_t)((m + 7) / 8) * (k / QK) * Q_ACT_BLOCK;
+    return Q_HEADER + q40_act_bytes(m, k / QK);  // the larger of the two activation layouts a call with up to m rows may use
 }
 
 extern "C" int b200kv_q40_pack(const void* blocks, int64_t n, int64_t k, void* packed, void* stream) {
@@ -545,7 +544,9 @@ extern "C" int b200kv_q40_gemm_quantized_as(const void* packed, int64_t n, int64
     Q40Gemm p{};
     p.packed = (const uint8_t*)packed, p.act = act, p.out = out, p.status = (int*)scratch;
     p.n = n, p.nb = nb, p.out_stride = out_stride, p.m = m, p.out_dtype = out_dtype, p.one = 1.0f;
-    if (groups >= 4) {  // a prompt pass: every warp keeps the accumulators of its own 8 rows, the weight stages are shared by 8 warps
+    if (q40_tiled(m))  // a prompt pass: the tcgen05 kernel over the tiled activation layout its producers wrote
+        return launch_q40_gemm_tc(packed, act, out, (int*)scratch, n, nb, out_stride, m, out_dtype, stream);
+    if (groups >= 4) {  // a few dozen rows: every warp keeps the accumulators of its own 8 rows, the weight stages are shared by 8 warps
         static thread_local int rows_attr_device = -1;
         int dev = 0;
         B200KV_CUDA(cudaGetDevice(&dev));
