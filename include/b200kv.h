@@ -255,7 +255,9 @@ int64_t b200kv_q40_packed_bytes(int64_t n, int64_t k);
  * nibble bytes, cuda/src/rewrite_rules/pad_q40_weights.rs does the reference's own repacking) into `packed`
  * (device memory, 16-byte aligned, b200kv_q40_packed_bytes long).  Done once per weight matrix. */
 int b200kv_q40_pack(const void* blocks, int64_t n, int64_t k, void* packed, void* stream);
-/* Bytes of device scratch a GEMM with m activation rows needs (quantised activations + a status word), or -1. */
+/* Bytes of device scratch a GEMM with up to m activation rows needs (quantised activations + a status word), or -1.
+ * The producers lay the activations out for the kernel that a call with that many rows runs (records of 8 rows below 128
+ * rows, tensor-core operand tiles of 128 rows from there on): a producer and the GEMM that reads it are given the same m. */
 int64_t b200kv_q40_scratch_bytes(int64_t k, int32_t m);
 /* out[m, n] = a[m, k] . W[n, k]^T.  `a` is device memory of type `dtype` (cast to f32 first, as the reference's callers
  * do), rows a_stride elements apart; `out` is f32, rows out_stride elements apart; `scratch` is caller-provided device
