@@ -77,6 +77,28 @@ def test_q40_gemm_special_activations(kv):
     assert got.tobytes() == want.tobytes()
 
 
+@pytest.mark.parametrize("m", [8, 40, 130])
+def test_q40_gemm_with_weight_scales_that_are_not_finite(kv, m):
+    # a weight block whose largest value overflows the f16 scale (inf), and one made of NaNs: the products with them are inf
+    # or NaN exactly where the reference's are -- in particular inf * 0 = NaN for a zero dot product
+    n, k = 48, 256
+    w = normal(41, (n, k)).astype(np.float32)
+    w[3, 32:64] = 9.0e5          # scale = max / -8 overflows f16
+    w[17, 0:32] = np.nan
+    a = normal(42, (m, k)).astype(np.float32)
+    a[1, 32:64] = 0.0            # a zero activation block against the infinite scale
+    sc, pk = oracle.q4_0_quant(w)
+    assert not np.isfinite(sc.view(np.float16).astype(np.float32)).all()
+    lin = kv.Q40Linear(torch.from_numpy(ggml_blocks(sc, pk)).cuda(), max_m=max(64, m))
+    got = lin.gemm(torch.from_numpy(a).cuda()).cpu().numpy()
+    lin.check()
+    want = oracle.w4a8_gemm(sc, pk, a)
+    assert np.array_equal(np.isnan(got), np.isnan(want))
+    ok = ~np.isnan(want)
+    assert got[ok].tobytes() == want[ok].tobytes()
+    assert np.isnan(want).any() or np.isinf(want).any()
+
+
 def test_q40_errors(kv):
     blocks = torch.zeros((4, 2, 18), dtype=torch.uint8, device="cuda")
     lin = kv.Q40Linear(blocks)
